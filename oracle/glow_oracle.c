@@ -1,0 +1,545 @@
+/*
+ * TEST INFRASTRUCTURE ONLY -- NOT PART OF THE PRODUCT.
+ *
+ * A plain-C restatement, on the CPU, of the arithmetic of pytorch/glow's quantized
+ * inference kernels.  It exists so the CUDA kernels can be checked against it and so the
+ * benchmark has a CPU baseline to time.  Only tests, the smoke check and the benchmark's
+ * CPU-baseline leg may load this library; the product never does.
+ *
+ * Parity pin: every function here is checked (tests/test_oracle_*.py) against
+ *   (1) the hand-computed expected tensors in the reference's own unit tests
+ *       (tests/unittests/OperatorTest.cpp, QuantizationTest.cpp), and
+ *   (2) the reference's own kernel sources (lib/LLVMIRCodeGen/libjit/*.cpp) compiled
+ *       unmodified into oracle/_ref/libjit_strict.so, bit for bit on seeded inputs.
+ * The 4-bit / fp16 paths exist only in the reference's Interpreter (which cannot be
+ * compiled without LLVM); those are pinned by (1) only.
+ *
+ * Each function cites the reference file:line (paths inside pytorch/glow) it follows.
+ * All float arithmetic is written as separate multiply and add steps and the file is
+ * built with -ffp-contract=off so no FMA is formed: that is the canonical operation
+ * order of the reference's C++ source.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ORC_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------------------------ */
+/* fp16 <-> fp32.  The reference converts with the FP16 library's                        */
+/* fp16_ieee_from_fp32_value / fp16_ieee_to_fp32_value (include/glow/Support/Float16.h:  */
+/* 38,81; un-vendored submodule Maratyszcza/FP16, no pinned version): IEEE binary16,     */
+/* round-to-nearest-even, subnormals kept, overflow to infinity.  Written out on bits.   */
+/* ------------------------------------------------------------------------------------ */
+static inline uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float bits_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+ORC_API uint16_t orc_f32_to_f16(float f) {
+  uint32_t x = f32_bits(f);
+  uint32_t sign = (x >> 16) & 0x8000u;
+  uint32_t absx = x & 0x7fffffffu;
+  if (absx > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);       /* NaN */
+  if (absx >= 0x47800000u) return (uint16_t)(sign | 0x7c00u);      /* >= 65536 -> inf (also inf) */
+  if (absx < 0x38800000u) {                                        /* below 2^-14: subnormal half */
+    if (absx < 0x33000000u) return (uint16_t)sign;                 /* < 2^-25 rounds to 0 */
+    /* value = m * 2^(e-150) with the implicit bit; target unit is 2^-24 */
+    uint32_t e = absx >> 23;
+    uint32_t m = (absx & 0x7fffffu) | 0x800000u;
+    uint32_t shift = 126u - e;                                     /* 14..24 */
+    uint32_t q = m >> shift;
+    uint32_t rem = m & ((1u << shift) - 1u);
+    uint32_t half = 1u << (shift - 1u);
+    if (rem > half || (rem == half && (q & 1u))) q++;
+    return (uint16_t)(sign | q);
+  }
+  /* normal half (possibly rounding up into infinity) */
+  uint32_t e = (absx >> 23) - 112u;
+  uint32_t m = absx & 0x7fffffu;
+  uint32_t h = (e << 10) | (m >> 13);
+  uint32_t rem = m & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) h++;
+  return (uint16_t)(sign | h);
+}
+
+ORC_API float orc_f16_to_f32(uint16_t h) {
+  uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+  uint32_t e = (h >> 10) & 0x1fu;
+  uint32_t m = h & 0x3ffu;
+  if (e == 0x1fu) return bits_f32(sign | 0x7f800000u | (m << 13));
+  if (e == 0) {
+    float v = (float)m * 5.9604644775390625e-08f;                  /* m * 2^-24, exact */
+    return sign ? -v : v;
+  }
+  return bits_f32(sign | ((e + 112u) << 23) | (m << 13));
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Integer requantisation.                                                               */
+/* ------------------------------------------------------------------------------------ */
+
+/* libjit_scale<int32_t,int32_t>: lib/LLVMIRCodeGen/libjit/libjit_defs.h:158-173.
+ * Arithmetic right shifts, wrapping 32-bit multiply and add (done on uint32 here so the
+ * wrap is defined in C), rounding term only when post > 0, offset added last. */
+ORC_API int32_t orc_scale32(int32_t input, int32_t pre, int32_t post, int32_t scale,
+                            int32_t offset) {
+  int32_t rtn = (post > 0) ? (int32_t)(1u << (post - 1)) : 0;
+  int32_t a = input >> pre;
+  int32_t b = (int32_t)((uint32_t)a * (uint32_t)scale);
+  int32_t c = (int32_t)((uint32_t)b + (uint32_t)rtn);
+  return (int32_t)((uint32_t)(c >> post) + (uint32_t)offset);
+}
+
+/* libjit_clip_i8: libjit_defs.h:146-148. */
+ORC_API int8_t orc_clip_i8(int32_t v) { return (int8_t)(v < -128 ? -128 : (v > 127 ? 127 : v)); }
+
+/* libjit_div_round_i32: libjit_defs.h:238-244. */
+static inline int32_t div_round_i32(int32_t input, int32_t divider) {
+  int32_t rnd = divider >> 1;
+  return (input > 0) ? ((input + rnd) / divider) : ((input - rnd) / divider);
+}
+
+/* libjit_activation_i32: libjit_defs.h:206-233 (0 none, 1 relu, 2 clip, 5 leaky relu). */
+static inline int32_t activation_i32(int32_t x, int32_t offset, int32_t actType,
+                                     const int32_t *actArgs) {
+  if (actType == 0) return x;
+  if (actType == 1) return x > offset ? x : offset;
+  if (actType == 2) { int32_t t = x > actArgs[0] ? x : actArgs[0]; return t < actArgs[1] ? t : actArgs[1]; }
+  if (actType == 3 || actType == 4) return x;
+  return (x >= offset) ? x : orc_scale32(x - offset, actArgs[0], actArgs[1], actArgs[2], offset);
+}
+
+/* quantizeScaleOffset32To8: lib/Quantization/Base/Base.cpp:234-359, with
+ * isFloatPowerOf2 / getFloat2Exp (:793-799).  `scale` stays a float throughout. */
+ORC_API void orc_quantize_scale_offset_32to8(float scale, int32_t *pre, int32_t *post,
+                                             int32_t *iscale) {
+  int e;
+  float mant = frexpf(scale, &e);
+  if (fabsf(mant) == 0.5f) {
+    int ex = ilogbf(scale);
+    if (ex > 0) { *pre = 0; *post = 0; *iscale = (int)scale; }
+    else        { *pre = 0; *post = -ex; *iscale = 1; }
+    return;
+  }
+  int preShift = 0, postShift = 0;
+  while (scale < 0.5 || (scale < 256 && postShift < 15)) { scale *= 2; postShift++; }
+  while (scale < 255 && preShift < (postShift / 2)) { scale *= 2; preShift++; }
+  *pre = preShift; *post = postShift; *iscale = (int)roundf(scale);
+}
+
+/* Per-row triples of RowwiseQuantizedFullyConnected and per-channel triples of
+ * ChannelwiseQuantizedConvolution: lib/LLVMIRCodeGen/LLVMIRGen.cpp:2245-2251 and
+ * :2726-2730.  matMulScale = inScale * wScale[j] in fp32; bias from biasScale[j]/matMul,
+ * output from matMul/outScale.  bias_scales has n entries, or 1 (bias_scales_n == 1) for
+ * the rowwise FC whose bias has one type-level scale. */
+ORC_API void orc_rowwise_requant_params(const float *w_scales, int64_t n, float in_scale,
+                                        const float *bias_scales, int64_t bias_scales_n,
+                                        float out_scale, int32_t *bias_pre, int32_t *bias_post,
+                                        int32_t *bias_scale, int32_t *out_pre, int32_t *out_post,
+                                        int32_t *out_scale_i) {
+  for (int64_t j = 0; j < n; j++) {
+    float mm = in_scale * w_scales[j];
+    float bs = bias_scales[bias_scales_n == 1 ? 0 : j];
+    orc_quantize_scale_offset_32to8(bs / mm, &bias_pre[j], &bias_post[j], &bias_scale[j]);
+    orc_quantize_scale_offset_32to8(mm / out_scale, &out_pre[j], &out_post[j], &out_scale_i[j]);
+  }
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Fused-rowwise tables.                                                                 */
+/* kind: 0 UInt8FusedQTy (fp32 scale/offset), 1 UInt8FusedFP16QTy, 2 UInt4FusedQTy,      */
+/*       3 UInt4FusedFP16QTy   (include/glow/Base/Type.h:424-433).                       */
+/* ------------------------------------------------------------------------------------ */
+static inline int kind_is4(int kind) { return kind >= 2; }
+static inline int kind_fp16so(int kind) { return kind & 1; }
+
+/* Scale/offset sit in the last 2*sizeof(T) bytes of a row: include/glow/Base/Tensor.h:1585-1607. */
+static inline void row_scale_offset(const uint8_t *row_end, int kind, float *scale, float *offset) {
+  if (kind_fp16so(kind)) {
+    uint16_t s, o;
+    memcpy(&s, row_end - 4, 2); memcpy(&o, row_end - 2, 2);
+    *scale = orc_f16_to_f32(s); *offset = orc_f16_to_f32(o);
+  } else {
+    memcpy(scale, row_end - 8, 4); memcpy(offset, row_end - 4, 4);
+  }
+}
+
+/* tensorFusedRowwiseQuantization<T>: include/glow/Quantization/Base/Base.h:598-678 with
+ * quantizeWithFloatOffset / quantize4BitsWithFloatOffset (:361-379).  in: fp32 [rows, cols];
+ * out: uint8 [rows, out_line] where out_line = cols (+8 or +4) or cols/2 (+8 or +4). */
+ORC_API void orc_fused_rowwise_quantize(const float *in, int64_t rows, int64_t cols, int kind,
+                                        uint8_t *out, int64_t out_line) {
+  const float range = kind_is4(kind) ? 15.0f : 255.0f;
+  for (int64_t i = 0; i < rows; i++) {
+    const float *src = in + i * cols;
+    uint8_t *dst = out + i * out_line;
+    float mn = src[0], mx = src[0];
+    for (int64_t j = 1; j < cols; j++) { if (src[j] < mn) mn = src[j]; if (src[j] > mx) mx = src[j]; }
+    const float scale = ((mx - mn) < 1e-10f) ? 1.0f : (float)(((double)mx - (double)mn) / range);
+    const float offset = mn;
+    for (int64_t j = 0; j < cols; j++) {
+      float r = roundf((src[j] - offset) / scale);
+      if (!kind_is4(kind)) {
+        dst[j] = (uint8_t)(uint16_t)r;
+      } else {
+        int q = (int)r; q = q < 0 ? 0 : (q > 15 ? 15 : q);
+        if ((j & 1) == 0) dst[j / 2] = (uint8_t)q; else dst[j / 2] |= (uint8_t)(q << 4);
+      }
+    }
+    uint8_t *tail = dst + out_line;
+    if (kind_fp16so(kind)) {
+      uint16_t s = orc_f32_to_f16(scale), o = orc_f32_to_f16(offset);
+      memcpy(tail - 4, &s, 2); memcpy(tail - 2, &o, 2);
+    } else {
+      memcpy(tail - 8, &scale, 4); memcpy(tail - 4, &offset, 4);
+    }
+  }
+}
+
+static inline int64_t load_index(const void *indices, int idx64, int64_t i) {
+  return idx64 ? ((const int64_t *)indices)[i] : (int64_t)((const int32_t *)indices)[i];
+}
+
+/* libjit_fused_rowwise_quantized_sparse_lengths_weighted_sum_generic (and its _f_u / _f_i32
+ * entry points): lib/LLVMIRCodeGen/libjit/libjit.cpp:1253-1276, :2416-2452.
+ * UInt8FusedQTy table, fp32 weights, fp32 result. */
+ORC_API void orc_frwq_slws_u8_f32(float *dest, const uint8_t *data, const float *weights,
+                                  const void *indices, int idx64, const int32_t *lengths,
+                                  int64_t segments, int64_t in_line, int64_t out_line) {
+  memset(dest, 0, (size_t)(segments * out_line) * sizeof(float));
+  int64_t cur = 0;
+  for (int64_t i = 0; i < segments; i++) {
+    for (int32_t j = 0, e = lengths[i]; j < e; j++) {
+      const float weight = weights[cur];
+      const int64_t line = load_index(indices, idx64, cur);
+      const uint8_t *row = data + line * in_line;
+      float scale, offset;
+      memcpy(&scale, row + in_line - 8, 4);
+      memcpy(&offset, row + in_line - 4, 4);
+      for (int64_t k = 0; k < out_line; k++) {
+        const float fData = (scale * (float)row[k]) + offset;
+        dest[i * out_line + k] += weight * fData;
+      }
+      cur++;
+    }
+  }
+}
+
+/* One bag of the Interpreter's kernel, shared by the lengths and the offsets forms:
+ * lib/Backends/Interpreter/InterpreterNodes.cpp:5797-5840 (and :5936-5978), with
+ * dequantizeWithFloatOffset / dequantize4BitWithFloatOffset
+ * (include/glow/Quantization/Base/Base.h:385-406) and the float16 class
+ * (include/glow/Support/Float16.h:34-88).
+ *   out_fp16 : result and weights are fp16 (T = float16_t) instead of fp32
+ *   fp16_acc : AccumT = float16_t -- the addend d*w is rounded to fp16, added to the fp16
+ *              running sum in fp32, and the sum rounded to fp16, at every step.        */
+static void interp_bag(void *dest_row, const uint8_t *data, int kind, const void *weights,
+                       const void *indices, int idx64, int64_t begin, int64_t end,
+                       int64_t in_line, int64_t out_line, int out_fp16, int fp16_acc,
+                       float *accum_f, uint16_t *accum_h) {
+  if (fp16_acc) memset(accum_h, 0, (size_t)out_line * 2);   /* float16(0.0f) has bits 0 */
+  else for (int64_t k = 0; k < out_line; k++) accum_f[k] = 0.0f;
+  for (int64_t c = begin; c < end; c++) {
+    const float weight = out_fp16 ? orc_f16_to_f32(((const uint16_t *)weights)[c])
+                                  : ((const float *)weights)[c];
+    const int64_t rowIdx = load_index(indices, idx64, c);
+    const uint8_t *row = data + rowIdx * in_line;
+    float scale, offset;
+    row_scale_offset(row + in_line, kind, &scale, &offset);
+    for (int64_t k = 0; k < out_line; k++) {
+      float q;
+      if (!kind_is4(kind)) {
+        q = (float)row[k];
+      } else {
+        uint8_t b = row[k / 2];
+        if (k & 1) b >>= 4;
+        q = (float)(b & 0x0f);
+      }
+      const float d = (q * scale) + offset;
+      const float p = d * weight;
+      if (fp16_acc) {
+        const float addend = orc_f16_to_f32(orc_f32_to_f16(p));
+        accum_h[k] = orc_f32_to_f16(orc_f16_to_f32(accum_h[k]) + addend);
+      } else {
+        accum_f[k] += p;
+      }
+    }
+  }
+  for (int64_t k = 0; k < out_line; k++) {
+    if (out_fp16) ((uint16_t *)dest_row)[k] = fp16_acc ? accum_h[k] : orc_f32_to_f16(accum_f[k]);
+    else ((float *)dest_row)[k] = accum_f[k];
+  }
+}
+
+/* fwdFusedRowwiseQuantizedSparseLengthsWeightedSumImpl<T,AccumT,TI> and its dispatcher:
+ * InterpreterNodes.cpp:5764-5889.  All four fused kinds; fp32 or fp16 result. */
+ORC_API void orc_frwq_slws_interp(void *dest, const uint8_t *data, int kind, const void *weights,
+                                  const void *indices, int idx64, const int32_t *lengths,
+                                  int64_t segments, int64_t in_line, int64_t out_line,
+                                  int out_fp16, int fp16_acc) {
+  /* the dispatcher only accumulates in fp16 for an fp16 result on an fp16-scale table */
+  if (!(out_fp16 && kind_fp16so(kind))) fp16_acc = 0;
+  float *accum_f = (float *)malloc((size_t)(out_line > 0 ? out_line : 1) * sizeof(float));
+  uint16_t *accum_h = (uint16_t *)malloc((size_t)(out_line > 0 ? out_line : 1) * 2);
+  const size_t esz = out_fp16 ? 2 : 4;
+  int64_t cur = 0;
+  for (int64_t i = 0; i < segments; i++) {
+    int64_t len = lengths[i];
+    interp_bag((char *)dest + (size_t)(i * out_line) * esz, data, kind, weights, indices, idx64,
+               cur, cur + len, in_line, out_line, out_fp16, fp16_acc, accum_f, accum_h);
+    cur += len;
+  }
+  free(accum_f); free(accum_h);
+}
+
+/* libjit_embedding_bag_byte_rowwise_offsets_f: libjit.cpp:2454-2481 (int32 indices/offsets on
+ * the CPU backend), and fwdEmbeddingBagByteRowwiseOffsetsImpl: InterpreterNodes.cpp:5896-5986.
+ * `segments` counts the entries of `offsets` (so it includes the end offset when present).
+ * A segment whose start is not below its end contributes nothing. */
+ORC_API void orc_embedding_bag_byte_rowwise_offsets(void *dest, const uint8_t *data, int kind,
+                                                    const void *weights, const void *indices,
+                                                    const void *offsets, int idx64,
+                                                    int64_t segments, int64_t num_indices,
+                                                    int64_t in_line, int64_t out_line,
+                                                    int has_end_offset, int out_fp16,
+                                                    int fp16_acc) {
+  if (!(out_fp16 && kind_fp16so(kind))) fp16_acc = 0;
+  if (has_end_offset) --segments;
+  float *accum_f = (float *)malloc((size_t)(out_line > 0 ? out_line : 1) * sizeof(float));
+  uint16_t *accum_h = (uint16_t *)malloc((size_t)(out_line > 0 ? out_line : 1) * 2);
+  const size_t esz = out_fp16 ? 2 : 4;
+  for (int64_t i = 0; i < segments; i++) {
+    int64_t start = load_index(offsets, idx64, i);
+    int64_t end = (!has_end_offset && i == segments - 1) ? num_indices : load_index(offsets, idx64, i + 1);
+    if (end < start) end = start;
+    interp_bag((char *)dest + (size_t)(i * out_line) * esz, data, kind, weights, indices, idx64,
+               start, end, in_line, out_line, out_fp16, fp16_acc, accum_f, accum_h);
+  }
+  free(accum_f); free(accum_h);
+}
+
+/* libjit_sparse_lengths_weighted_sum_generic: libjit.cpp:1182-1198 (fp32 table). */
+ORC_API void orc_sparse_lengths_weighted_sum_f32(float *dest, const float *data,
+                                                 const float *weights, const void *indices,
+                                                 int idx64, const int32_t *lengths,
+                                                 int64_t segments, int64_t line) {
+  memset(dest, 0, (size_t)(segments * line) * sizeof(float));
+  int64_t cur = 0;
+  for (int64_t i = 0; i < segments; i++)
+    for (int32_t j = 0; j < lengths[i]; j++, cur++) {
+      const float w = weights[cur];
+      const int64_t r = load_index(indices, idx64, cur);
+      for (int64_t k = 0; k < line; k++) dest[i * line + k] += w * data[r * line + k];
+    }
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Dense int8 layers.  Integer arithmetic wraps mod 2^32 like the reference's int32.      */
+/* Callers that want more host threads split the batch rows over them (oracle.py).       */
+/* ------------------------------------------------------------------------------------ */
+
+/* libjit_rowwise_quantized_fc_generic<int8_t,int32_t>: libjit_matmul.cpp:284-316.
+ * in [M,K], weights [N,K] (not transposed), out [M,N]. */
+ORC_API void orc_rowwise_quantized_fc_i8_i32(
+    int8_t *out, const int8_t *in, const int8_t *w, const int32_t *bias,
+    const int32_t *w_offsets, const int32_t *bias_pre, const int32_t *bias_post,
+    const int32_t *bias_scale, const int32_t *out_pre, const int32_t *out_post,
+    const int32_t *out_scale, int64_t M, int64_t K, int64_t N, int32_t out_offset,
+    int32_t in_offset, int32_t bias_offset) {
+  for (int64_t i = 0; i < M; i++) {
+    for (int64_t j = 0; j < N; j++) {
+      uint32_t sum = 0;
+      const int32_t wo = w_offsets[j];
+      for (int64_t k = 0; k < K; k++)
+        sum += (uint32_t)(((int32_t)w[j * K + k] - wo) * ((int32_t)in[i * K + k] - in_offset));
+      int32_t B = orc_scale32(bias[j] - bias_offset, bias_pre[j], bias_post[j], bias_scale[j], 0);
+      sum += (uint32_t)B;
+      out[i * N + j] = orc_clip_i8(orc_scale32((int32_t)sum, out_pre[j], out_post[j], out_scale[j], out_offset));
+    }
+  }
+}
+
+/* libjit_fc_generic<int8_t,int32_t>: libjit_matmul.cpp:254-280.  weights [K,N]. */
+ORC_API void orc_fc_i8_i32(int8_t *out, const int8_t *in, const int8_t *w, const int32_t *bias,
+                           int64_t M, int64_t K, int64_t N, int32_t out_offset, int32_t in_offset,
+                           int32_t w_offset, int32_t bias_offset, int32_t bias_pre,
+                           int32_t bias_post, int32_t bias_scale, int32_t out_pre,
+                           int32_t out_post, int32_t out_scale) {
+  for (int64_t i = 0; i < M; i++) {
+    for (int64_t j = 0; j < N; j++) {
+      uint32_t sum = (uint32_t)orc_scale32(bias[j] - bias_offset, bias_pre, bias_post, bias_scale, 0);
+      for (int64_t k = 0; k < K; k++)
+        sum += (uint32_t)(((int32_t)in[i * K + k] - in_offset) * ((int32_t)w[k * N + j] - w_offset));
+      out[i * N + j] = orc_clip_i8(orc_scale32((int32_t)sum, out_pre, out_post, out_scale, out_offset));
+    }
+  }
+}
+
+/* libjit_matmul_i8: libjit_matmul.cpp:353-371.  lhs [M,K], rhs [K,N]. */
+ORC_API void orc_matmul_i8(int8_t *out, const int8_t *lhs, const int8_t *rhs, int64_t M, int64_t K,
+                           int64_t N, int32_t out_offset, int32_t lhs_offset, int32_t rhs_offset,
+                           int32_t out_pre, int32_t out_post, int32_t out_scale) {
+  for (int64_t x = 0; x < M; x++) {
+    for (int64_t y = 0; y < N; y++) {
+      uint32_t sum = 0;
+      for (int64_t i = 0; i < K; i++)
+        sum += (uint32_t)(((int32_t)lhs[x * K + i] - lhs_offset) * ((int32_t)rhs[i * N + y] - rhs_offset));
+      out[x * N + y] = orc_clip_i8(orc_scale32((int32_t)sum, out_pre, out_post, out_scale, out_offset));
+    }
+  }
+}
+
+/* libjit_channelwise_quantized_conv2d_generic<int8_t,int32_t>: libjit_conv.cpp:151-239, and
+ * (per_channel == 0, every array of length 1) libjit_quantized_conv2d_generic: :49-147.
+ * NHWC input, filter [outC,kH,kW,inC/group], taps outside the input are skipped, only
+ * pads[0] (top) and pads[1] (left) are read. */
+ORC_API void orc_conv2d_i8_i32(
+    int8_t *out, const int8_t *in, const int8_t *filter, const int32_t *bias,
+    const int64_t *out_dims, const int64_t *in_dims, const int64_t *filter_dims,
+    const int64_t *kernels, const int64_t *strides, const int64_t *pads, int64_t group,
+    const int64_t *dilation, int32_t out_offset, int32_t in_offset, int per_channel,
+    const int32_t *filter_offsets, const int32_t *bias_offsets, const int32_t *bias_pre,
+    const int32_t *bias_post, const int32_t *bias_scale, const int32_t *out_pre,
+    const int32_t *out_post, const int32_t *out_scale, int32_t act_type,
+    const int32_t *act_args) {
+  const int64_t inC = in_dims[3], outC = out_dims[3];
+  const int64_t inCperG = inC / group, outCperG = outC / group;
+  const int64_t IH = in_dims[1], IW = in_dims[2], OH = out_dims[1], OW = out_dims[2];
+  const int64_t kh = kernels[0], kw = kernels[1];
+  const int64_t fstride = filter_dims[1] * filter_dims[2] * filter_dims[3];
+  for (int64_t n = 0; n < in_dims[0]; n++) {
+    for (int64_t ax = 0; ax < OH; ax++) {
+      const int64_t x = ax * strides[0] - pads[0];
+      for (int64_t ay = 0; ay < OW; ay++) {
+        const int64_t y = ay * strides[1] - pads[1];
+        for (int64_t d = 0; d < outC; d++) {
+          const int64_t g = d / outCperG;
+          const int64_t c = per_channel ? d : 0;
+          const int32_t fo = filter_offsets[c];
+          uint32_t sum = (uint32_t)orc_scale32(bias[d] - bias_offsets[c], bias_pre[c], bias_post[c], bias_scale[c], 0);
+          for (int64_t fx = 0; fx < kh; fx++) {
+            for (int64_t fy = 0; fy < kw; fy++) {
+              const int64_t ox = x + fx * dilation[0], oy = y + fy * dilation[1];
+              if (ox < 0 || oy < 0 || ox >= IH || oy >= IW) continue;
+              const int8_t *ip = in + ((n * IH + ox) * IW + oy) * inC + g * inCperG;
+              const int8_t *fp = filter + d * fstride + (fx * filter_dims[2] + fy) * filter_dims[3];
+              for (int64_t fd = 0; fd < inCperG; fd++)
+                sum += (uint32_t)(((int32_t)fp[fd] - fo) * ((int32_t)ip[fd] - in_offset));
+            }
+          }
+          int32_t s = orc_scale32((int32_t)sum, out_pre[c], out_post[c], out_scale[c], out_offset);
+          s = activation_i32(s, out_offset, act_type, act_args);
+          out[((n * OH + ax) * OW + ay) * outC + d] = orc_clip_i8(s);
+        }
+      }
+    }
+  }
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* Int8 glue operators of a quantized network.                                           */
+/* ------------------------------------------------------------------------------------ */
+
+/* libjit_element_add_kernel_i8 (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED): libjit.cpp:1593-1603. */
+ORC_API void orc_element_add_i8(int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n,
+                                int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset,
+                                int32_t lhs_pre, int32_t lhs_post, int32_t lhs_scale,
+                                int32_t rhs_pre, int32_t rhs_post, int32_t rhs_scale) {
+  for (int64_t i = 0; i < n; i++) {
+    int32_t l = orc_scale32(lhs[i] - lhs_offset, lhs_pre, lhs_post, lhs_scale, 0);
+    int32_t r = orc_scale32(rhs[i] - rhs_offset, rhs_pre, rhs_post, rhs_scale, 0);
+    dest[i] = orc_clip_i8(l + r + dest_offset);
+  }
+}
+
+/* libjit_element_relu_i8: libjit.cpp:1850-1858: max(x, srcOffset) then rescale. */
+ORC_API void orc_element_relu_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t src_offset,
+                                 int32_t dest_offset, int32_t pre, int32_t post, int32_t scale) {
+  for (int64_t i = 0; i < n; i++) {
+    int32_t v = src[i] > src_offset ? src[i] : src_offset;
+    dest[i] = orc_clip_i8(orc_scale32(v - src_offset, pre, post, scale, dest_offset));
+  }
+}
+
+/* libjit_element_maxsplat_kernel_i8: lib/Backends/CPU/libjit_cpu/libjit_cpu.cpp:39-44. */
+ORC_API void orc_element_maxsplat_i8(int8_t *dest, const int8_t *src, int64_t n, int8_t splat) {
+  for (int64_t i = 0; i < n; i++) dest[i] = src[i] > splat ? src[i] : splat;
+}
+
+/* libjit_element_rescale_kernel_i8: libjit.cpp:3030-3038. */
+ORC_API void orc_element_rescale_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t out_offset,
+                                    int32_t in_offset, int32_t pre, int32_t post, int32_t scale) {
+  for (int64_t i = 0; i < n; i++)
+    dest[i] = orc_clip_i8(orc_scale32(src[i] - in_offset, pre, post, scale, out_offset));
+}
+
+/* libjit_element_quantize_kernel_i8: libjit.cpp:2997-3002 (nearbyintf, round-half-even). */
+ORC_API void orc_element_quantize_i8(int8_t *dest, const float *src, int64_t n, float scale,
+                                     int32_t offset) {
+  for (int64_t i = 0; i < n; i++) {
+    float t = src[i] / scale;
+    t = t + (float)offset;
+    dest[i] = orc_clip_i8((int32_t)nearbyintf(t));
+  }
+}
+
+/* libjit_element_dequantize_kernel_i8: libjit.cpp:3014-3018. */
+ORC_API void orc_element_dequantize_i8(float *dest, const int8_t *src, int64_t n, float scale,
+                                       int32_t offset) {
+  for (int64_t i = 0; i < n; i++) dest[i] = scale * (float)(src[i] - offset);
+}
+
+/* libjit_max_pool_generic<int8_t>: libjit.cpp:811-860 via libjit_max_pool_i8 :2592-2597.
+ * NHWC; window cells outside the input are skipped; an empty window yields the output
+ * offset (the `defaultValue`). */
+ORC_API void orc_max_pool_i8(const int8_t *in, int8_t *out, const int64_t *in_dims,
+                             const int64_t *out_dims, const int64_t *kernels,
+                             const int64_t *strides, const int64_t *pads, int32_t out_offset) {
+  const int64_t IH = in_dims[1], IW = in_dims[2], C = in_dims[3], OH = out_dims[1], OW = out_dims[2];
+  for (int64_t n = 0; n < in_dims[0]; n++)
+    for (int64_t oh = 0; oh < OH; oh++)
+      for (int64_t ow = 0; ow < OW; ow++)
+        for (int64_t c = 0; c < C; c++) {
+          int first = 1; int8_t best = (int8_t)out_offset;
+          for (int64_t fh = 0; fh < kernels[0]; fh++)
+            for (int64_t fw = 0; fw < kernels[1]; fw++) {
+              int64_t ih = oh * strides[0] - pads[0] + fh, iw = ow * strides[1] - pads[1] + fw;
+              if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+              int8_t v = in[((n * IH + ih) * IW + iw) * C + c];
+              if (first || v > best) { best = v; first = 0; }
+            }
+          out[((n * OH + oh) * OW + ow) * C + c] = best;
+        }
+}
+
+/* libjit_avg_pool_i8: libjit.cpp:2812-2897. */
+ORC_API void orc_avg_pool_i8(const int8_t *in, int8_t *out, const int64_t *in_dims,
+                             const int64_t *out_dims, const int64_t *kernels,
+                             const int64_t *strides, const int64_t *pads, int count_include_pads,
+                             int32_t out_offset, int32_t in_offset, int32_t out_pre,
+                             int32_t out_post, int32_t out_scale) {
+  const int64_t IH = in_dims[1], IW = in_dims[2], C = in_dims[3], OH = out_dims[1], OW = out_dims[2];
+  for (int64_t n = 0; n < in_dims[0]; n++)
+    for (int64_t oh = 0; oh < OH; oh++)
+      for (int64_t ow = 0; ow < OW; ow++)
+        for (int64_t c = 0; c < C; c++) {
+          int32_t sum = 0, area = 0;
+          for (int64_t fh = 0; fh < kernels[0]; fh++)
+            for (int64_t fw = 0; fw < kernels[1]; fw++) {
+              int64_t ih = oh * strides[0] - pads[0] + fh, iw = ow * strides[1] - pads[1] + fw;
+              if (ih < 0 || iw < 0 || ih >= IH || iw >= IW) continue;
+              sum += in[((n * IH + ih) * IW + iw) * C + c] - in_offset;
+              area++;
+            }
+          int8_t r;
+          if (count_include_pads) {
+            r = orc_clip_i8(orc_scale32(sum, out_pre, out_post, out_scale, out_offset));
+          } else if (area == 0) {
+            r = (int8_t)out_offset;
+          } else {
+            int32_t s = orc_scale32(sum, out_pre, out_post, out_scale, 0);
+            r = orc_clip_i8(div_round_i32(s, area) + out_offset);
+          }
+          out[((n * OH + oh) * OW + ow) * C + c] = r;
+        }
+}
