@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the embedding gather-pool hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload ("step" = one pooled lookup of one batch over all tables of a rank):
+FusedRowwiseQuantizedSparseLengthsWeightedSum with the first benchmark configuration's table
+and bag law -- 1,000,000 x 64 uint8 rows fused with fp32 scale/offset (72 B per row), 1024
+bags per table, lengths clamp(Poisson(32),1,128), int64 indices uniform over the rows, fp32
+weights U(0,1) -- over T distinct tables in ONE launch (the reference's SLS benchmark does the
+same with numSLSNodes, tests/benchmark/SLSBench.cpp:49-104).  One table alone moves 3 MB per
+launch out of an L2-resident 72 MB table, which measures launch latency, not HBM; T tables
+(18 GB, far beyond the 126 MB L2) make it a bandwidth measurement.  At N > 1 every rank owns
+T tables of its own (table-wise sharding, no data-path collective): weak scaling.
+
+metric: algorithmic GB/s = [sum(lengths) * (72 + 8 + 4) + bags * (4 + 256)] / time.
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, DIM, BATCH = 1_000_000, 64, 1024
+IN_LINE = DIM + 8
+METRIC = "frwq_slws_hbm_gbps"
+UNIT = "GB/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tables", type=int, default=256, help="tables per GPU (T)")
+    ap.add_argument("--requests", type=int, default=4, help="distinct pre-generated batches rotated over the steps")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline leg")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak_hbm():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def algorithmic_bytes(num_indices, bags):
+    return num_indices * (IN_LINE + 8 + 4) + bags * (4 + DIM * 4)
+
+
+def request_host(tables, seed):
+    """One batch for `tables` tables: lengths [T, B], and per-table indices / weights."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    lengths = np.clip(rng.poisson(32, (tables, BATCH)), 1, 128).astype(np.int32)
+    n = lengths.sum(1)
+    total = int(n.sum())
+    indices = rng.integers(0, ROWS, total, dtype=np.int64)
+    weights = rng.random(total, dtype=np.float32)
+    starts = np.concatenate([[0], np.cumsum(n)]).astype(np.int64)
+    return lengths, indices, weights, starts
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_reference_rate(tables_host, reqs, seconds, threads):
+    """Times the reference's own kernel (libjit, fast-math build as Glow ships it; the plain-C
+    port when that build is absent) on host threads, one table per call, tables spread over the
+    threads the way Glow runs one CPU device per core.  -> (GB/s, kind, passes)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import oracle as orc
+    if orc.ref_available("fast"):
+        ref = orc.LibjitRef("fast")
+        fn, kind = ref.frwq_slws, "reference"
+    else:
+        orc.lib()
+        fn, kind = (lambda t, w, i, l: orc.frwq_slws_u8_f32(t, w, i, l)), "port"
+    lengths, indices, weights, starts = reqs
+    S = len(tables_host)
+
+    def one(k):
+        a, b = starts[k], starts[k + 1]
+        fn(tables_host[k], weights[a:b], indices[a:b], lengths[k])
+
+    nbytes = algorithmic_bytes(int(starts[S]), S * BATCH)
+    with ThreadPoolExecutor(threads) as ex:
+        list(ex.map(one, range(S)))  # warm-up pass
+        passes, t0 = 0, time.perf_counter()
+        while True:
+            list(ex.map(one, range(S)))
+            passes += 1
+            dt = time.perf_counter() - t0
+            if dt >= seconds:
+                break
+    return nbytes * passes / dt / 1e9, kind, passes, dt
+
+
+def make_table_host(seed):
+    from glow_b200 import workloads
+    return workloads.fused_table_u8(ROWS, DIM, seed, 0)
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU kernel on this box's host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    S = min(args.tables, max(threads, 16))
+    tables = [make_table_host(1000 + k) for k in range(S)]
+    reqs = request_host(S, 7)
+    per_step = max(0.5, min(4.0, 60.0 / max(1, args.steps + args.warmup)))
+    vals = []
+    kind = "port"
+    for i in range(args.warmup + args.steps):
+        v, kind, passes, dt = cpu_reference_rate(tables, reqs, per_step, threads)
+        if i >= args.warmup:
+            vals.append(v)
+    value = float(np.mean(vals)) if vals else 0.0
+    nbytes = algorithmic_bytes(int(reqs[3][S]), S * BATCH)
+    sample = "%d of %d tables per pass, passes repeated for %.1f s per step" % (S, args.tables, per_step)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": nbytes / (value * 1e9) * 1e3 if value else None,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.tables),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def workload_config(T):
+    return {"workload": "FRWQ-SLWS uint8 fused rows (config 1 law): %d tables x 1,000,000 rows x 64 cols "
+                        "(72 B rows), 1024 bags/table, lengths clamp(Poisson(32),1,128), int64 indices, fp32 "
+                        "weights, one batched launch per step" % T,
+            "tables_per_gpu": T, "rows": ROWS, "dim": DIM, "bags_per_table": BATCH,
+            "l2_policy": "inputs larger than L2 (18.4 GB of tables per GPU, indices drawn uniformly)"}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from glow_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    T, R = args.tables, args.requests
+
+    # ---- tables: resident in HBM before anything is timed.  Generated on the device from a
+    # seeded torch generator (same value law as workloads.fused_table_u8).
+    g = torch.Generator(device=dev).manual_seed(0x610B200 + rank)
+    tables = []
+    for k in range(T):
+        t = torch.randint(0, 256, (ROWS, IN_LINE), dtype=torch.uint8, device=dev, generator=g)
+        sc = torch.empty(ROWS, device=dev).uniform_(0.001, 0.01, generator=g)
+        of = torch.empty(ROWS, device=dev).uniform_(-1, 1, generator=g)
+        t[:, DIM:DIM + 4] = sc.view(torch.uint8).view(ROWS, 4)
+        t[:, DIM + 4:] = of.view(torch.uint8).view(ROWS, 4)
+        tables.append(t)
+    del sc, of
+
+    # ---- requests: pinned host copies (for the end-to-end leg) and device copies
+    host, devr = [], []
+    for r in range(R):
+        lengths, indices, weights, starts = request_host(T, 99 + 1000 * rank + r)
+        hl = torch.from_numpy(lengths).pin_memory()
+        hi = torch.from_numpy(indices).pin_memory()
+        hw = torch.from_numpy(weights).pin_memory()
+        host.append((hl, hi, hw, starts))
+        devr.append((hl.to(dev), hi.to(dev), hw.to(dev)))
+    max_n = max(int(h[3][T]) for h in host)
+    out = torch.empty((T, BATCH, DIM), dtype=torch.float32, device=dev)
+    status = ops.new_status(dev)
+
+    def batch_for(lengths_d, indices_d, weights_d, starts):
+        b = ops.SlwsBatch(ops.UINT8_FUSED, IN_LINE, torch.int64, device=dev)
+        b.bind(tables, [weights_d[starts[k]:starts[k + 1]] for k in range(T)],
+               [indices_d[starts[k]:starts[k + 1]] for k in range(T)], [lengths_d[k] for k in range(T)],
+               [out[k] for k in range(T)])
+        return b
+
+    batches = [batch_for(*devr[r], host[r][3]) for r in range(R)]
+    bytes_per_step = [algorithmic_bytes(int(host[r][3][T]), T * BATCH) for r in range(R)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for i in range(args.warmup):
+        batches[i % R].run(status)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    ev[0].record()
+    for i in range(args.steps):
+        batches[i % R].run(status)
+        ev[i + 1].record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    moved = sum(bytes_per_step[i % R] for i in range(args.steps))
+    assert int(status.item()) == 0, "kernel reported invalid input"
+
+    # ---- end to end: pinned host buffers in, host buffer out, through the same public call
+    stage_l = torch.empty((T, BATCH), dtype=torch.int32, device=dev)
+    stage_i = torch.empty(max_n, dtype=torch.int64, device=dev)
+    stage_w = torch.empty(max_n, dtype=torch.float32, device=dev)
+    out_host = torch.empty((T, BATCH, DIM), dtype=torch.float32).pin_memory()
+    e2e_batches = [batch_for(stage_l, stage_i, stage_w, host[r][3]) for r in range(R)]
+
+    def e2e_step(r):
+        hl, hi, hw, starts = host[r]
+        n = int(starts[T])
+        stage_l.copy_(hl, non_blocking=True)
+        stage_i[:n].copy_(hi, non_blocking=True)
+        stage_w[:n].copy_(hw, non_blocking=True)
+        e2e_batches[r].run(status)
+        out_host.copy_(out, non_blocking=True)
+        return n
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for i in range(2):
+        e2e_step(i % R)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    h2d = d2h = e2e_moved = 0
+    for i in range(e2e_steps):
+        n = e2e_step(i % R)
+        h2d += T * BATCH * 4 + n * 12
+        d2h += out.numel() * 4
+        e2e_moved += bytes_per_step[i % R]
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    # ---- max over ranks
+    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    sums = torch.tensor([moved, e2e_moved], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    total_ms_all, e2e_ms_all = float(times[0]), float(times[1])
+    value = float(sums[0]) / (total_ms_all * 1e-3) / 1e9
+    e2e_value = float(sums[1]) / (e2e_ms_all * 1e-3) / 1e9
+
+    if rank == 0:
+        peak, peak_src = measured_peak_hbm()
+        launch_us = float(np.mean(step_ms)) * 1e3
+        achieved = (moved / args.steps) / (np.mean(step_ms) * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms_all / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(T),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
+                         "kernel": "slws_gather_kernel (+ slws_segments_from_lengths_kernel, timed together)",
+                         "launch_us": launch_us, "algorithmic_bytes_per_launch": moved / args.steps},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d // e2e_steps,
+                    "d2h_bytes_per_step": d2h // e2e_steps, "steps": e2e_steps,
+                    "ms_per_step": e2e_ms_all / e2e_steps},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            S = min(T, max(threads, 16))
+            sample_tables = [tables[k].cpu().numpy() for k in range(S)]
+            hl, hi, hw, starts = host[0]
+            reqs = (hl.numpy()[:S], hi.numpy(), hw.numpy(), starts[:S + 1])
+            v, kind, passes, dt = cpu_reference_rate(sample_tables, reqs, args.cpu_seconds, threads)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": kind,
+                                    "sample": "first %d of %d tables of request 0, %d passes in %.1f s, one table "
+                                              "per libjit call, tables spread over %d host threads"
+                                              % (S, T, passes, dt, threads)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

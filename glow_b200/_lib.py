@@ -1,0 +1,59 @@
+"""ctypes binding of glow_b200/lib/libglow_b200.so (the C ABI of include/glow_b200.h).
+
+There is no fallback: if the CUDA library has not been built, importing an operator raises.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libglow_b200.so")
+
+_vp, _i64, _i32, _int, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_int, C.c_size_t
+
+
+class SlwsJob(C.Structure):
+    """struct glowb200_slws_job"""
+    _fields_ = [("data", _vp), ("weights", _vp), ("indices", _vp), ("lengths", _vp), ("dest", _vp),
+                ("rows", _i64), ("num_indices", _i64), ("dest_stride", _i64), ("segments", _i64)]
+
+
+# name -> (restype, argtypes); also the list the symbol-export test walks.
+SIGNATURES = {
+    "glowb200_last_error": (C.c_char_p, []),
+    "glowb200_version": (C.c_char_p, []),
+    "glowb200_slws_workspace_bytes": (_sz, [_i64, _i64]),
+    "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum": (
+        _int, [_vp, _vp, _int, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp, _vp]),
+    "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched": (
+        _int, [_vp, _i64, _i64, _int, _int, _i64, _i64, _int, _int, _vp, _sz, _vp, _vp]),
+    "glowb200_embedding_bag_byte_rowwise_offsets": (
+        _int, [_vp, _vp, _int, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _sz, _vp,
+               _vp]),
+}
+
+_lib = None
+
+
+class GlowB200Error(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__("glow_b200 error %d: %s" % (code, message))
+        self.code = code
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s is missing: build it with `python -m glow_b200.build` "
+                              "(there is no CPU fallback)" % LIB_PATH)
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = l
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise GlowB200Error(rc, lib().glowb200_last_error().decode())

@@ -1,0 +1,52 @@
+// Shared host/device helpers of the glow_b200 kernels.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "glow_b200.h"
+
+namespace glowb200 {
+
+// Thread-local message behind glowb200_last_error().
+char *last_error_buffer();
+int set_error(int code, const char *fmt, ...);
+
+#define GLOWB200_CUDA_OK(expr)                                                                  \
+  do {                                                                                          \
+    cudaError_t e__ = (expr);                                                                   \
+    if (e__ != cudaSuccess)                                                                     \
+      return ::glowb200::set_error(GLOWB200_ERR_CUDA, "%s failed: %s", #expr,                   \
+                                   cudaGetErrorString(e__));                                    \
+  } while (0)
+
+#define GLOWB200_REQUIRE(cond, ...)                                                             \
+  do {                                                                                          \
+    if (!(cond)) return ::glowb200::set_error(GLOWB200_ERR_INVALID_ARGUMENT, __VA_ARGS__);      \
+  } while (0)
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// ---- integer requantisation (device side) ----------------------------------------------
+// libjit_scale<int32,int32> (lib/LLVMIRCodeGen/libjit/libjit_defs.h:158-173): arithmetic
+// shifts, 32-bit wrapping multiply/add, rounding term only when post > 0, offset added last.
+__host__ __device__ __forceinline__ int32_t scale32(int32_t input, int32_t pre, int32_t post,
+                                                    int32_t scale, int32_t offset) {
+  const uint32_t rtn = (post > 0) ? (1u << (post - 1)) : 0u;
+  const int32_t a = input >> pre;
+  const int32_t c = (int32_t)((uint32_t)a * (uint32_t)scale + rtn);
+  return (int32_t)((uint32_t)(c >> post) + (uint32_t)offset);
+}
+
+// libjit_clip_i8 (libjit_defs.h:146-148).
+__host__ __device__ __forceinline__ int32_t clip_i8(int32_t v) {
+  return v < -128 ? -128 : (v > 127 ? 127 : v);
+}
+
+}  // namespace glowb200

@@ -1,0 +1,627 @@
+// Embedding gather-pool kernels for fused-rowwise quantized tables on sm_100a:
+// FusedRowwiseQuantizedSparseLengthsWeightedSum (uint8 and 4-bit rows, fp32 or fp16
+// scale/offset, fp32 or fp16 result) and EmbeddingBagByteRowwiseOffsets.
+//
+// The work is a random gather of short rows out of HBM, so the design goal is bytes in
+// flight, not arithmetic:
+//   * a "segments" kernel turns lengths (or offsets) into validated bag boundaries in the
+//     caller's workspace, one int64 array per table;
+//   * the gather kernel gives each bag to a group of `lpr` lanes (a power of two, 1..32).
+//     A lane owns P chunks of 8 columns; chunk c of a row is one 8-byte (uint8 rows) or
+//     4-byte (4-bit rows) read-only load, and the lanes of a group read consecutive chunks,
+//     so one load instruction covers a contiguous piece of the row.  Indices and weights
+//     are read coalesced, `lpr` at a time, and handed round inside the group by shuffles;
+//     kUnroll rows are requested before the first is consumed.
+//
+// Arithmetic.  The reference computes dest[k] += w * (scale * q[k] + offset) row by row
+// (lib/LLVMIRCodeGen/libjit/libjit.cpp:1253-1276; InterpreterNodes.cpp:5797-5836).  With
+// fp32 accumulation this kernel evaluates the same sum as
+//     sum_j (w_j*scale_j) * q_jk  +  sum_j (w_j*offset_j)
+// with one FMA per element: the reference's CPU backend is itself compiled with fast-math,
+// so its float result is defined only up to reassociation (tolerance 1e-5 relative).
+// With fp16 accumulation the reference rounds at every step, and the kernel does exactly
+// that, step by step.
+#include "common.cuh"
+
+namespace glowb200 {
+namespace {
+
+constexpr int kGatherThreads = 256;
+constexpr int kUnroll = 4;
+constexpr int kSegThreads = 1024;
+
+struct SlwsLaunch {
+  const glowb200_slws_job *jobs;  // device array, or nullptr when `single` is the only job
+  glowb200_slws_job single;
+  int64_t *seg_begin;  // workspace: per job an int64 [segments + 1] array
+  int64_t seg_stride;  // int64 elements between the arrays of consecutive jobs
+  int32_t *status;
+  int32_t in_line, out_line;
+  int32_t lpr_log2;
+};
+
+__device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
+  if (status != nullptr && bits != 0) atomicOr(status, bits);
+}
+
+__device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
+  uint32_t v;
+  asm("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_stream_u64(const void *p) {
+  uint2 v;
+  asm("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------
+// Bag boundaries.  One block per table.
+//   lengths form : seg_begin[i] = min(sum(max(lengths[0..i), 0)), num_indices)
+//   offsets form : seg_begin[i] = clamp(offsets[i], 0, num_indices); the closing entry is
+//                  offsets[segments] when an end offset is present, else num_indices
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ int64_t block_exclusive_scan(int64_t v, int64_t *warp_tot, int64_t &block_total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int64_t inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    int64_t t = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += t;
+  }
+  if (lane == 31) warp_tot[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int64_t w = (lane < (int)(blockDim.x >> 5)) ? warp_tot[lane] : 0;
+    int64_t winc = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int64_t t = __shfl_up_sync(0xffffffffu, winc, d);
+      if (lane >= d) winc += t;
+    }
+    warp_tot[lane] = winc - w;  // exclusive prefix of warp totals
+    if (lane == 31) warp_tot[32] = winc;
+  }
+  __syncthreads();
+  const int64_t res = warp_tot[warp] + inc - v;
+  block_total = warp_tot[32];
+  __syncthreads();
+  return res;
+}
+
+__global__ void __launch_bounds__(kSegThreads) slws_segments_from_lengths_kernel(const __grid_constant__ SlwsLaunch p) {
+  __shared__ int64_t warp_tot[33];
+  const glowb200_slws_job job = p.jobs ? p.jobs[blockIdx.x] : p.single;
+  int64_t *out = p.seg_begin + (int64_t)blockIdx.x * p.seg_stride;
+  const int64_t S = job.segments, N = job.num_indices;
+  constexpr int kItems = 4;
+  int64_t carry = 0;
+  int32_t flags = 0;
+  for (int64_t tile = 0; tile < S; tile += (int64_t)kSegThreads * kItems) {
+    const int64_t first = tile + (int64_t)threadIdx.x * kItems;
+    int64_t v[kItems], sum = 0;
+#pragma unroll
+    for (int i = 0; i < kItems; i++) {
+      int64_t l = (first + i < S) ? (int64_t)job.lengths[first + i] : 0;
+      if (l < 0) { l = 0; flags |= GLOWB200_STATUS_NEGATIVE_LENGTH; }
+      v[i] = l;
+      sum += l;
+    }
+    int64_t tile_total;
+    int64_t run = carry + block_exclusive_scan(sum, warp_tot, tile_total);
+#pragma unroll
+    for (int i = 0; i < kItems; i++) {
+      if (first + i < S) out[first + i] = run < N ? run : N;
+      run += v[i];
+    }
+    carry += tile_total;
+  }
+  if (threadIdx.x == 0) {
+    if (carry > N) flags |= GLOWB200_STATUS_LENGTHS_OVERRUN;
+    out[S] = carry < N ? carry : N;
+  }
+  raise(p.status, flags);
+}
+
+template <typename IdxT>
+__global__ void __launch_bounds__(256) slws_segments_from_offsets_kernel(const __grid_constant__ SlwsLaunch p,
+                                                                           const IdxT *offsets, int has_end) {
+  const int64_t S = p.single.segments, N = p.single.num_indices;
+  int32_t flags = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i <= S; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t v = (i < S || has_end) ? (int64_t)offsets[i] : N;
+    if (v < 0) { v = 0; flags |= GLOWB200_STATUS_BAD_OFFSETS; }
+    if (v > N) { v = N; flags |= GLOWB200_STATUS_BAD_OFFSETS; }
+    p.seg_begin[i] = v;
+  }
+  raise(p.status, flags);
+}
+
+// ------------------------------------------------------------------------------------------
+// Row decoding
+// ------------------------------------------------------------------------------------------
+template <int BITS, bool SO16>
+struct RowLoad {
+  // 8-byte loads need 8-byte aligned rows: only the uint8 / fp32-scale layout (D + 8 bytes,
+  // D a multiple of 8) guarantees that.
+  static constexpr bool kWide = (BITS == 8) && !SO16;
+
+  struct Chunk { uint32_t lo, hi; };
+
+  __device__ static __forceinline__ Chunk payload(const uint8_t *row, int chunk) {
+    Chunk c;
+    if constexpr (BITS == 4) {
+      c.lo = ldg_stream_u32(row + chunk * 4);
+      c.hi = 0;
+    } else if constexpr (kWide) {
+      uint2 v = ldg_stream_u64(row + chunk * 8);
+      c.lo = v.x; c.hi = v.y;
+    } else {
+      c.lo = ldg_stream_u32(row + chunk * 8);
+      c.hi = ldg_stream_u32(row + chunk * 8 + 4);
+    }
+    return c;
+  }
+
+  // raw scale/offset words from the end of the row
+  __device__ static __forceinline__ uint2 tail(const uint8_t *row_end) {
+    if constexpr (SO16) {
+      return make_uint2(ldg_stream_u32(row_end - 4), 0u);
+    } else if constexpr (kWide) {
+      return ldg_stream_u64(row_end - 8);
+    } else {
+      return make_uint2(ldg_stream_u32(row_end - 8), ldg_stream_u32(row_end - 4));
+    }
+  }
+
+  __device__ static __forceinline__ void scale_offset(uint2 t, float &scale, float &offset) {
+    if constexpr (SO16) {
+      const __half2 h = *reinterpret_cast<const __half2 *>(&t.x);
+      scale = __low2float(h);
+      offset = __high2float(h);
+    } else {
+      scale = __uint_as_float(t.x);
+      offset = __uint_as_float(t.y);
+    }
+  }
+
+  // Column i (0..7) of a chunk as an exact float: the byte / nibble is dropped into the
+  // mantissa of 2^23 and 2^23 is subtracted.  4-bit rows keep column 2m in the low nibble of
+  // byte m and column 2m+1 in the high nibble (include/glow/Quantization/Base/Base.h:399-406).
+  __device__ static __forceinline__ float column(const Chunk &c, int i) {
+    uint32_t m;
+    if constexpr (BITS == 8) {
+      const uint32_t w = i < 4 ? c.lo : c.hi;
+      m = __byte_perm(w, 0x4B000000u, 0x7440 + (i & 3));  // {byte i, 0, 0, 0x4B}
+    } else {
+      m = ((c.lo >> (4 * i)) & 0xFu) | 0x4B000000u;
+    }
+    return __uint_as_float(m) - 8388608.0f;
+  }
+};
+
+template <bool OUT16>
+__device__ __forceinline__ float load_weight(const void *weights, int64_t i) {
+  if constexpr (OUT16) return __half2float(reinterpret_cast<const __half *>(weights)[i]);
+  else return reinterpret_cast<const float *>(weights)[i];
+}
+
+// ------------------------------------------------------------------------------------------
+// Gather-pool.  grid = (ceil(max_segments / bags_per_block), num_jobs).
+// ------------------------------------------------------------------------------------------
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P>
+__global__ void __launch_bounds__(kGatherThreads) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
+  using RL = RowLoad<BITS, SO16>;
+  const int job_id = blockIdx.y;
+  const glowb200_slws_job *jp = p.jobs ? (p.jobs + job_id) : &p.single;
+  const int64_t segments = jp->segments;
+  const int lpr = 1 << p.lpr_log2;
+  const int gl = threadIdx.x & (lpr - 1);
+  const int64_t bag = (int64_t)blockIdx.x * (kGatherThreads >> p.lpr_log2) + (threadIdx.x >> p.lpr_log2);
+  if (bag >= segments) return;  // whole groups leave together
+
+  const uint8_t *data = reinterpret_cast<const uint8_t *>(jp->data);
+  const IdxT *indices = reinterpret_cast<const IdxT *>(jp->indices);
+  const void *weights = jp->weights;
+  const int64_t rows = jp->rows;
+  const int64_t *sb = p.seg_begin + (int64_t)job_id * p.seg_stride;
+  const int64_t in_line = p.in_line;
+  const int chunks = p.out_line >> 3;
+
+  const unsigned lane = threadIdx.x & 31u;
+  const unsigned gmask = (lpr == 32) ? 0xffffffffu : (((1u << lpr) - 1u) << (lane & ~(unsigned)(lpr - 1)));
+
+  int64_t begin = sb[bag], end = sb[bag + 1];
+  int32_t flags = 0;
+  if (end < begin) { end = begin; flags |= GLOWB200_STATUS_BAD_OFFSETS; }
+
+  bool has[P];
+#pragma unroll
+  for (int c = 0; c < P; c++) has[c] = (c * lpr + gl) < chunks;
+
+  float acc[P][8];
+#pragma unroll
+  for (int c = 0; c < P; c++)
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[c][i] = 0.0f;
+  float bias_sum = 0.0f;  // sum_j w_j * offset_j (fp32 accumulation only)
+
+  for (int64_t base = begin; base < end; base += lpr) {
+    const int64_t mine = base + gl;
+    int64_t r_mine = -1;
+    float w_mine = 0.0f;
+    if (mine < end) {
+      r_mine = (int64_t)indices[mine];
+      w_mine = load_weight<OUT16>(weights, mine);
+      if (r_mine < 0 || r_mine >= rows) { r_mine = -1; flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE; }
+    }
+    const int n = (int)((end - base) < (int64_t)lpr ? (end - base) : (int64_t)lpr);
+    for (int t = 0; t < n; t += kUnroll) {
+      int64_t r[kUnroll];
+      float w[kUnroll];
+      typename RL::Chunk pay[kUnroll][P];
+      uint2 tl[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) {
+        r[u] = __shfl_sync(gmask, r_mine, t + u, lpr);
+        w[u] = __shfl_sync(gmask, w_mine, t + u, lpr);
+        if (t + u >= n) r[u] = -1;
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) {
+        if (r[u] >= 0) {
+          const uint8_t *row = data + r[u] * in_line;
+#pragma unroll
+          for (int c = 0; c < P; c++)
+            if (has[c]) pay[u][c] = RL::payload(row, c * lpr + gl);
+          tl[u] = RL::tail(row + in_line);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) {
+        if (r[u] >= 0) {
+          float scale, offset;
+          RL::scale_offset(tl[u], scale, offset);
+          if constexpr (ACC16) {
+            // AccumT = float16 (InterpreterNodes.cpp:5799,5832; Float16.h:38-56): the addend
+            // d*w is rounded to fp32 then to fp16, the fp16 sum is widened, added and rounded.
+            // q*scale is exact in fp32 for an fp16 scale, so the FMA equals multiply-then-add.
+#pragma unroll
+            for (int c = 0; c < P; c++)
+              if (has[c]) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                  const float d = __fmaf_rn(RL::column(pay[u][c], i), scale, offset);
+                  const float addend = __half2float(__float2half_rn(__fmul_rn(d, w[u])));
+                  acc[c][i] = __half2float(__float2half_rn(__fadd_rn(acc[c][i], addend)));
+                }
+              }
+          } else {
+            const float a = w[u] * scale;
+            bias_sum = fmaf(w[u], offset, bias_sum);
+#pragma unroll
+            for (int c = 0; c < P; c++)
+              if (has[c]) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[c][i] = fmaf(a, RL::column(pay[u][c], i), acc[c][i]);
+              }
+          }
+        }
+      }
+    }
+  }
+
+  // Every bag writes its row, empty bags write zeros (the reference zero-fills dest first).
+  const int64_t dest_stride = jp->dest_stride;
+#pragma unroll
+  for (int c = 0; c < P; c++) {
+    if (!has[c]) continue;
+    const int64_t col = (int64_t)(c * lpr + gl) * 8;
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i] = ACC16 ? acc[c][i] : (acc[c][i] + bias_sum);
+    if constexpr (OUT16) {
+      __half *d = reinterpret_cast<__half *>(jp->dest) + bag * dest_stride + col;
+      __half2 h[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) h[i] = __floats2half2_rn(o[2 * i], o[2 * i + 1]);
+      if ((reinterpret_cast<uintptr_t>(d) & 15u) == 0) {
+        *reinterpret_cast<uint4 *>(d) = *reinterpret_cast<const uint4 *>(h);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) *reinterpret_cast<__half2 *>(d + 2 * i) = h[i];
+      }
+    } else {
+      float *d = reinterpret_cast<float *>(jp->dest) + bag * dest_stride + col;
+      if ((reinterpret_cast<uintptr_t>(d) & 15u) == 0) {
+        *reinterpret_cast<float4 *>(d) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4 *>(d + 4) = make_float4(o[4], o[5], o[6], o[7]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) d[i] = o[i];
+      }
+    }
+  }
+  raise(p.status, flags);
+}
+
+// ------------------------------------------------------------------------------------------
+// Any-shape gather-pool: rows of any width and alignment (a column count that is not a
+// multiple of 8, a table that is not 8-byte aligned).  One warp per bag, byte loads, column
+// tiles of 128; the row-by-row arithmetic of the reference in its order, without FMA
+// contraction.  Correct for everything, fast for nothing -- real tables take the kernel above.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) slws_gather_any_kernel(const __grid_constant__ SlwsLaunch p, int bits,
+                                                               int so16, int out16, int acc16, int idx64) {
+  const int job_id = blockIdx.y;
+  const glowb200_slws_job *jp = p.jobs ? (p.jobs + job_id) : &p.single;
+  const int64_t bag = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (bag >= jp->segments) return;
+  const int lane = threadIdx.x & 31;
+  const uint8_t *data = reinterpret_cast<const uint8_t *>(jp->data);
+  const int64_t *sb = p.seg_begin + (int64_t)job_id * p.seg_stride;
+  int64_t begin = sb[bag], end = sb[bag + 1];
+  int32_t flags = 0;
+  if (end < begin) { end = begin; flags |= GLOWB200_STATUS_BAD_OFFSETS; }
+  const int64_t in_line = p.in_line;
+  const int D = p.out_line;
+  for (int tile = 0; tile < D; tile += 128) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int64_t j = begin; j < end; j++) {
+      const int64_t r = idx64 ? reinterpret_cast<const int64_t *>(jp->indices)[j]
+                              : (int64_t) reinterpret_cast<const int32_t *>(jp->indices)[j];
+      if (r < 0 || r >= jp->rows) { flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE; continue; }
+      const float w = out16 ? __half2float(reinterpret_cast<const __half *>(jp->weights)[j])
+                            : reinterpret_cast<const float *>(jp->weights)[j];
+      const uint8_t *row = data + r * in_line;
+      float scale, offset;
+      if (so16) {
+        const uint8_t *t = row + in_line - 4;
+        scale = __half2float(__ushort_as_half((unsigned short)(t[0] | (t[1] << 8))));
+        offset = __half2float(__ushort_as_half((unsigned short)(t[2] | (t[3] << 8))));
+      } else {
+        const uint8_t *t = row + in_line - 8;
+        scale = __uint_as_float(t[0] | (t[1] << 8) | (t[2] << 16) | ((uint32_t)t[3] << 24));
+        offset = __uint_as_float(t[4] | (t[5] << 8) | (t[6] << 16) | ((uint32_t)t[7] << 24));
+      }
+#pragma unroll
+      for (int s = 0; s < 4; s++) {
+        const int k = tile + s * 32 + lane;
+        if (k < D) {
+          uint32_t q;
+          if (bits == 8) q = row[k];
+          else { q = row[k >> 1]; q = (k & 1) ? (q >> 4) : (q & 0xFu); }
+          const float d = __fadd_rn(__fmul_rn((float)q, scale), offset);
+          const float prod = __fmul_rn(d, w);
+          if (acc16) acc[s] = __half2float(__float2half_rn(__fadd_rn(acc[s], __half2float(__float2half_rn(prod)))));
+          else acc[s] = __fadd_rn(acc[s], prod);
+        }
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+      const int k = tile + s * 32 + lane;
+      if (k < D) {
+        if (out16) reinterpret_cast<__half *>(jp->dest)[bag * jp->dest_stride + k] = __float2half_rn(acc[s]);
+        else reinterpret_cast<float *>(jp->dest)[bag * jp->dest_stride + k] = acc[s];
+      }
+    }
+  }
+  raise(p.status, flags);
+}
+
+// ------------------------------------------------------------------------------------------
+// Host dispatch
+// ------------------------------------------------------------------------------------------
+struct GatherConfig {
+  int kind, idx64, out16, acc16;
+};
+
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT>
+cudaError_t launch_gather_p(const SlwsLaunch &L, int P, dim3 grid, cudaStream_t s) {
+  switch (P) {
+    case 1: slws_gather_kernel<BITS, SO16, OUT16, ACC16, IdxT, 1><<<grid, kGatherThreads, 0, s>>>(L); break;
+    case 2: slws_gather_kernel<BITS, SO16, OUT16, ACC16, IdxT, 2><<<grid, kGatherThreads, 0, s>>>(L); break;
+    default: slws_gather_kernel<BITS, SO16, OUT16, ACC16, IdxT, 4><<<grid, kGatherThreads, 0, s>>>(L); break;
+  }
+  return cudaGetLastError();
+}
+
+template <int BITS, bool SO16, bool OUT16, bool ACC16>
+cudaError_t launch_gather_idx(const SlwsLaunch &L, int idx64, int P, dim3 grid, cudaStream_t s) {
+  return idx64 ? launch_gather_p<BITS, SO16, OUT16, ACC16, int64_t>(L, P, grid, s)
+               : launch_gather_p<BITS, SO16, OUT16, ACC16, int32_t>(L, P, grid, s);
+}
+
+template <int BITS, bool SO16>
+cudaError_t launch_gather_out(const SlwsLaunch &L, const GatherConfig &g, int P, dim3 grid, cudaStream_t s) {
+  if (g.out16) {
+    if constexpr (SO16) {
+      if (g.acc16) return launch_gather_idx<BITS, SO16, true, true>(L, g.idx64, P, grid, s);
+    }
+    return launch_gather_idx<BITS, SO16, true, false>(L, g.idx64, P, grid, s);
+  }
+  return launch_gather_idx<BITS, SO16, false, false>(L, g.idx64, P, grid, s);
+}
+
+int payload_bytes(int kind, int64_t out_line) { return (int)(kind >= 2 ? out_line / 2 : out_line); }
+int tail_bytes(int kind) { return (kind & 1) ? 4 : 8; }
+
+// Validates the shape arguments shared by every entry point and decides between the vector
+// kernel (P > 0, lpr_log2 set) and the any-shape kernel (P == 0).
+int plan(int kind, int64_t in_line, int64_t out_line, bool pointers_aligned, int &P, int &lpr_log2) {
+  GLOWB200_REQUIRE(kind >= 0 && kind <= 3, "unknown fused table kind %d", kind);
+  GLOWB200_REQUIRE(out_line >= 0 && in_line > 0 && in_line < (1 << 30), "bad line sizes");
+  GLOWB200_REQUIRE(kind < 2 || (out_line % 2) == 0, "4-bit rows need an even column count");
+  GLOWB200_REQUIRE(in_line == payload_bytes(kind, out_line) + tail_bytes(kind),
+                   "in_line_size %lld does not match %lld columns of kind %d", (long long)in_line,
+                   (long long)out_line, kind);
+  P = 0;
+  lpr_log2 = 0;
+  const int align = (kind == GLOWB200_UINT8_FUSED) ? 8 : 4;
+  if (out_line == 0 || (out_line % 8) != 0 || (in_line % align) != 0 || !pointers_aligned) return GLOWB200_OK;
+  const int chunks = (int)(out_line / 8);
+  if (chunks > 128) return GLOWB200_OK;  // > 1024 columns: any-shape kernel
+  // Two chunks per lane once a row has 8 or more chunks: halves the per-row bookkeeping per
+  // byte; four only when 32 lanes cannot cover the row otherwise.
+  P = chunks > 64 ? 4 : (chunks >= 8 ? 2 : 1);
+  int lpr = 1;
+  while (lpr * P < chunks) lpr <<= 1;
+  lpr_log2 = 0;
+  while ((1 << lpr_log2) < lpr) lpr_log2++;
+  return GLOWB200_OK;
+}
+
+int run_gather(SlwsLaunch &L, const GatherConfig &g, int P, int64_t max_segments, int64_t num_jobs,
+               cudaStream_t s) {
+  if (max_segments == 0 || num_jobs == 0) return GLOWB200_OK;
+  cudaError_t e;
+  if (P == 0) {
+    dim3 grid((unsigned)((max_segments + 7) / 8), (unsigned)num_jobs);
+    slws_gather_any_kernel<<<grid, 256, 0, s>>>(L, g.kind >= 2 ? 4 : 8, g.kind & 1, g.out16, g.acc16, g.idx64);
+    e = cudaGetLastError();
+  } else {
+    const int bags_per_block = kGatherThreads >> L.lpr_log2;
+    dim3 grid((unsigned)((max_segments + bags_per_block - 1) / bags_per_block), (unsigned)num_jobs);
+    switch (g.kind) {
+      case GLOWB200_UINT8_FUSED: e = launch_gather_out<8, false>(L, g, P, grid, s); break;
+      case GLOWB200_UINT8_FUSED_FP16: e = launch_gather_out<8, true>(L, g, P, grid, s); break;
+      case GLOWB200_UINT4_FUSED: e = launch_gather_out<4, false>(L, g, P, grid, s); break;
+      default: e = launch_gather_out<4, true>(L, g, P, grid, s); break;
+    }
+  }
+  if (e != cudaSuccess) return set_error(GLOWB200_ERR_CUDA, "gather-pool launch failed: %s", cudaGetErrorString(e));
+  return GLOWB200_OK;
+}
+
+size_t seg_stride_elems(int64_t max_segments) { return align_up((size_t)(max_segments + 1) * 8, 256) / 8; }
+
+bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+}  // namespace
+}  // namespace glowb200
+
+using namespace glowb200;
+
+extern "C" size_t glowb200_slws_workspace_bytes(int64_t max_segments, int64_t num_jobs) {
+  if (max_segments < 0 || num_jobs <= 0) return 0;
+  return seg_stride_elems(max_segments) * 8 * (size_t)num_jobs;
+}
+
+extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched(
+    const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_segments, int kind, int indices_are_int64,
+    int64_t in_line_size, int64_t out_line_size, int out_is_fp16, int use_fp16_accumulation, void *workspace,
+    size_t workspace_bytes, int32_t *status, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(num_jobs >= 0 && num_jobs <= 65535, "num_jobs must be in [0, 65535]");
+  GLOWB200_REQUIRE(max_segments >= 0 && max_segments < (1ll << 31), "max_segments out of range");
+  if (num_jobs == 0 || max_segments == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(jobs != nullptr, "jobs is NULL");
+  int P, lpr_log2;
+  // Table / result pointers of a batched launch live in device memory: the descriptors are
+  // required to hold 16-byte aligned tables, which every cudaMalloc'ed slab offset that keeps
+  // Glow's 64-byte TensorAlignment satisfies.
+  if (int rc = plan(kind, in_line_size, out_line_size, true, P, lpr_log2)) return rc;
+  const size_t need = glowb200_slws_workspace_bytes(max_segments, num_jobs);
+  if (workspace == nullptr || workspace_bytes < need)
+    return set_error(GLOWB200_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  GLOWB200_REQUIRE(aligned_to(workspace, 8), "workspace must be 8-byte aligned");
+  SlwsLaunch L{};
+  L.jobs = jobs;
+  L.seg_begin = reinterpret_cast<int64_t *>(workspace);
+  L.seg_stride = (int64_t)seg_stride_elems(max_segments);
+  L.status = status;
+  L.in_line = (int32_t)in_line_size;
+  L.out_line = (int32_t)out_line_size;
+  L.lpr_log2 = lpr_log2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  slws_segments_from_lengths_kernel<<<(unsigned)num_jobs, kSegThreads, 0, s>>>(L);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  GatherConfig g{kind, indices_are_int64 ? 1 : 0, out_is_fp16 ? 1 : 0,
+                 (use_fp16_accumulation && out_is_fp16 && (kind & 1)) ? 1 : 0};
+  return run_gather(L, g, P, max_segments, num_jobs, s);
+}
+
+namespace {
+int fill_single(SlwsLaunch &L, GatherConfig &g, int &P, void *dest, const void *data, int kind, int64_t rows,
+                const void *weights, const void *indices, int idx64, const int32_t *lengths, int64_t segments,
+                int64_t num_indices, int64_t in_line, int64_t out_line, int out16, int acc16, void *workspace,
+                size_t workspace_bytes, int32_t *status) {
+  GLOWB200_REQUIRE(segments >= 0 && segments < (1ll << 31), "segments out of range");
+  GLOWB200_REQUIRE(rows >= 0 && num_indices >= 0, "negative rows / num_indices");
+  GLOWB200_REQUIRE(segments == 0 || (dest && (num_indices == 0 || (data && weights && indices))),
+                   "NULL tensor pointer");
+  const bool al = aligned_to(data, kind == GLOWB200_UINT8_FUSED ? 8 : 4) && aligned_to(dest, out16 ? 2 : 4) &&
+                  aligned_to(weights, out16 ? 2 : 4) && aligned_to(indices, idx64 ? 8 : 4);
+  int lpr_log2;
+  if (int rc = plan(kind, in_line, out_line, al, P, lpr_log2)) return rc;
+  const size_t need = glowb200_slws_workspace_bytes(segments, 1);
+  if (segments > 0 && (workspace == nullptr || workspace_bytes < need))
+    return set_error(GLOWB200_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  GLOWB200_REQUIRE(aligned_to(workspace, 8), "workspace must be 8-byte aligned");
+  L = SlwsLaunch{};
+  L.jobs = nullptr;
+  L.single.data = data;
+  L.single.weights = weights;
+  L.single.indices = indices;
+  L.single.lengths = lengths;
+  L.single.dest = dest;
+  L.single.rows = rows;
+  L.single.num_indices = num_indices;
+  L.single.dest_stride = out_line;
+  L.single.segments = segments;
+  L.seg_begin = reinterpret_cast<int64_t *>(workspace);
+  L.seg_stride = (int64_t)seg_stride_elems(segments);
+  L.status = status;
+  L.in_line = (int32_t)in_line;
+  L.out_line = (int32_t)out_line;
+  L.lpr_log2 = lpr_log2;
+  g = GatherConfig{kind, idx64 ? 1 : 0, out16 ? 1 : 0, (acc16 && out16 && (kind & 1)) ? 1 : 0};
+  return GLOWB200_OK;
+}
+}  // namespace
+
+extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
+    void *dest, const void *data, int kind, int64_t rows, const void *weights, const void *indices,
+    int indices_are_int64, const int32_t *lengths, int64_t segments, int64_t num_indices, int64_t in_line_size,
+    int64_t out_line_size, int out_is_fp16, int use_fp16_accumulation, void *workspace, size_t workspace_bytes,
+    int32_t *status, glowb200_stream_t stream) {
+  SlwsLaunch L;
+  GatherConfig g;
+  int P;
+  if (int rc = fill_single(L, g, P, dest, data, kind, rows, weights, indices, indices_are_int64, lengths, segments,
+                           num_indices, in_line_size, out_line_size, out_is_fp16, use_fp16_accumulation, workspace,
+                           workspace_bytes, status))
+    return rc;
+  if (segments == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return run_gather(L, g, P, segments, 1, s);
+}
+
+extern "C" int glowb200_embedding_bag_byte_rowwise_offsets(
+    void *dest, const void *data, int kind, int64_t rows, const void *weights, const void *indices,
+    const void *offsets, int indices_are_int64, int64_t num_offsets, int64_t num_indices, int64_t in_line_size,
+    int64_t out_line_size, int has_end_offset, int out_is_fp16, int use_fp16_accumulation, void *workspace,
+    size_t workspace_bytes, int32_t *status, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(num_offsets >= 0, "negative num_offsets");
+  const int64_t segments = has_end_offset ? num_offsets - 1 : num_offsets;
+  if (segments <= 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(offsets != nullptr, "offsets is NULL");
+  SlwsLaunch L;
+  GatherConfig g;
+  int P;
+  if (int rc = fill_single(L, g, P, dest, data, kind, rows, weights, indices, indices_are_int64, nullptr, segments,
+                           num_indices, in_line_size, out_line_size, out_is_fp16, use_fp16_accumulation, workspace,
+                           workspace_bytes, status))
+    return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned blocks = (unsigned)((segments + 1 + 255) / 256 < 1024 ? (segments + 1 + 255) / 256 : 1024);
+  if (indices_are_int64)
+    slws_segments_from_offsets_kernel<int64_t><<<blocks, 256, 0, s>>>(L, reinterpret_cast<const int64_t *>(offsets), has_end_offset ? 1 : 0);
+  else
+    slws_segments_from_offsets_kernel<int32_t><<<blocks, 256, 0, s>>>(L, reinterpret_cast<const int32_t *>(offsets), has_end_offset ? 1 : 0);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return run_gather(L, g, P, segments, 1, s);
+}

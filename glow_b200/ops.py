@@ -1,0 +1,179 @@
+"""Operator front end over the C ABI, for callers that hold torch CUDA tensors.
+
+Names and argument meaning follow the reference's kernel entry points
+(lib/LLVMIRCodeGen/libjit/libjit.cpp) and node creators (lib/Graph/Graph.cpp); torch is used
+only for device memory and streams.  Every function enqueues on torch's current stream.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import SlwsJob, check
+
+UINT8_FUSED, UINT8_FUSED_FP16, UINT4_FUSED, UINT4_FUSED_FP16 = 0, 1, 2, 3
+
+STATUS_INDEX_OUT_OF_RANGE = 1
+STATUS_LENGTHS_OVERRUN = 2
+STATUS_NEGATIVE_LENGTH = 4
+STATUS_BAD_OFFSETS = 8
+STATUS_WAIT_TIMEOUT = 16
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _cuda(t, name, dtypes=None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise TypeError("%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise ValueError("%s must be contiguous" % name)
+    if dtypes is not None and t.dtype not in dtypes:
+        raise TypeError("%s has dtype %s, expected one of %s" % (name, t.dtype, dtypes))
+    return t
+
+
+def out_columns(in_line_size, kind):
+    """Columns of the result for a fused table whose rows are in_line_size bytes."""
+    payload = in_line_size - (4 if (kind & 1) else 8)
+    return payload * 2 if kind >= 2 else payload
+
+
+def result_dtype(kind):
+    """UInt8FusedQTy/UInt4FusedQTy -> fp32, the FP16 kinds -> fp16 (lib/Graph/Graph.cpp:2446-2476)."""
+    return torch.float16 if (kind & 1) else torch.float32
+
+
+def slws_workspace_bytes(max_segments, num_jobs=1):
+    return int(_lib.lib().glowb200_slws_workspace_bytes(int(max_segments), int(num_jobs)))
+
+
+def new_status(device):
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def _workspace(workspace, need, device):
+    if workspace is None:
+        return torch.empty(max(need, 8), dtype=torch.uint8, device=device)
+    _cuda(workspace, "workspace")
+    return workspace
+
+
+def fused_rowwise_quantized_sparse_lengths_weighted_sum(data, weights, indices, lengths, kind=UINT8_FUSED, *,
+                                                        use_fp16_accumulation=False, out=None, status=None,
+                                                        workspace=None, num_indices=None):
+    """FusedRowwiseQuantizedSparseLengthsWeightedSum.  data: uint8 [rows, in_line] fused table;
+    weights: result dtype [n]; indices: int32/int64 [n]; lengths: int32 [segments]."""
+    _cuda(data, "data", (torch.uint8,))
+    _cuda(indices, "indices", (torch.int32, torch.int64))
+    _cuda(lengths, "lengths", (torch.int32,))
+    rows, in_line = data.shape
+    out_line = out_columns(in_line, kind)
+    odt = result_dtype(kind) if out is None else out.dtype
+    _cuda(weights, "weights", (odt,))
+    segments = lengths.shape[0]
+    if out is None:
+        out = torch.empty((segments, out_line), dtype=odt, device=data.device)
+    n = indices.shape[0] if num_indices is None else int(num_indices)
+    need = slws_workspace_bytes(segments, 1)
+    ws = _workspace(workspace, need, data.device)
+    check(_lib.lib().glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
+        _p(out), _p(data), kind, rows, _p(weights), _p(indices), int(indices.dtype == torch.int64), _p(lengths),
+        segments, n, in_line, out_line, int(odt == torch.float16), int(use_fp16_accumulation), _p(ws), ws.numel(),
+        _p(status), _stream()))
+    return out
+
+
+def fused_rowwise_quantized_sparse_lengths_sum(data, indices, lengths, kind=UINT8_FUSED, **kw):
+    """Unweighted form = weighted with weights of one (lib/Optimizer/Lower/Lower.cpp:1590-1606)."""
+    odt = result_dtype(kind)
+    ones = torch.ones(indices.shape[0], dtype=odt, device=data.device)
+    return fused_rowwise_quantized_sparse_lengths_weighted_sum(data, ones, indices, lengths, kind, **kw)
+
+
+def embedding_bag_byte_rowwise_offsets(data, weights, indices, offsets, kind=UINT8_FUSED, *, has_end_offset=True,
+                                       use_fp16_accumulation=False, out=None, status=None, workspace=None,
+                                       num_indices=None):
+    """EmbeddingBagByteRowwiseOffsets: bags given by offsets (same integer type as indices)."""
+    _cuda(data, "data", (torch.uint8,))
+    _cuda(indices, "indices", (torch.int32, torch.int64))
+    _cuda(offsets, "offsets", (indices.dtype,))
+    rows, in_line = data.shape
+    out_line = out_columns(in_line, kind)
+    odt = result_dtype(kind) if out is None else out.dtype
+    _cuda(weights, "weights", (odt,))
+    num_offsets = offsets.shape[0]
+    segments = num_offsets - 1 if has_end_offset else num_offsets
+    if out is None:
+        out = torch.empty((max(segments, 0), out_line), dtype=odt, device=data.device)
+    n = indices.shape[0] if num_indices is None else int(num_indices)
+    need = slws_workspace_bytes(max(segments, 0), 1)
+    ws = _workspace(workspace, need, data.device)
+    check(_lib.lib().glowb200_embedding_bag_byte_rowwise_offsets(
+        _p(out), _p(data), kind, rows, _p(weights), _p(indices), _p(offsets), int(indices.dtype == torch.int64),
+        num_offsets, n, in_line, out_line, int(has_end_offset), int(odt == torch.float16),
+        int(use_fp16_accumulation), _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
+class SlwsBatch:
+    """A fixed set of tables of one kind and row width, pooled by ONE launch per request.
+
+    The descriptor array lives on the device; `bind` rewrites it (one small H2D copy) when the
+    request buffers move, `run` launches.  dest_stride / dest pointers may address slices of a
+    wider [segments, tables * D] buffer so the tables' results land concatenated.
+    """
+
+    def __init__(self, kind, in_line, index_dtype=torch.int64, use_fp16_accumulation=False, device="cuda"):
+        self.kind, self.in_line = kind, in_line
+        self.out_line = out_columns(in_line, kind)
+        self.index_dtype = index_dtype
+        self.fp16_acc = use_fp16_accumulation
+        self.device = torch.device(device)
+        self.jobs_dev = None
+        self.num_jobs = 0
+        self.max_segments = 0
+        self.workspace = None
+        self._keep = None
+
+    def bind(self, tables, weights, indices, lengths, dests, dest_stride=None):
+        n = len(tables)
+        arr = (SlwsJob * n)()
+        odt = result_dtype(self.kind)
+        self.max_segments = 0
+        for i in range(n):
+            _cuda(tables[i], "table", (torch.uint8,))
+            _cuda(weights[i], "weights", (dests[i].dtype,))
+            _cuda(indices[i], "indices", (self.index_dtype,))
+            _cuda(lengths[i], "lengths", (torch.int32,))
+            if tables[i].shape[1] != self.in_line:
+                raise ValueError("all tables of a batch share one row width")
+            if dests[i].dtype != odt and not (dests[i].dtype == torch.float16):
+                raise TypeError("bad result dtype")
+            j = arr[i]
+            j.data, j.weights, j.indices = tables[i].data_ptr(), weights[i].data_ptr(), indices[i].data_ptr()
+            j.lengths, j.dest = lengths[i].data_ptr(), dests[i].data_ptr()
+            j.rows, j.num_indices = tables[i].shape[0], indices[i].shape[0]
+            j.dest_stride = self.out_line if dest_stride is None else dest_stride
+            j.segments = lengths[i].shape[0]
+            self.max_segments = max(self.max_segments, j.segments)
+        self.out_fp16 = int(dests[0].dtype == torch.float16) if n else 0
+        host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8) if n else torch.empty(0, dtype=torch.uint8)
+        self.jobs_dev = host.to(self.device)
+        self.num_jobs = n
+        need = slws_workspace_bytes(self.max_segments, max(n, 1))
+        if self.workspace is None or self.workspace.numel() < need:
+            self.workspace = torch.empty(max(need, 8), dtype=torch.uint8, device=self.device)
+        self._keep = (tables, weights, indices, lengths, dests)
+        return self
+
+    def run(self, status=None):
+        check(_lib.lib().glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched(
+            _p(self.jobs_dev), self.num_jobs, self.max_segments, self.kind,
+            int(self.index_dtype == torch.int64), self.in_line, self.out_line, self.out_fp16, int(self.fp16_acc),
+            _p(self.workspace), self.workspace.numel(), _p(status), _stream()))

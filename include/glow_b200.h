@@ -1,0 +1,126 @@
+/*
+ * glow_b200 -- C ABI of the B200 (sm_100a) kernels behind pytorch/glow's quantized
+ * inference hot path.
+ *
+ * Every entry point is the device-side counterpart of one `extern "C" libjit_*` kernel that
+ * Glow's CPU backend calls from JIT-ed code (or of one Interpreter `fwd*Inst` where the CPU
+ * backend has none); the comment on each names the reference interface it replaces.  The
+ * argument meaning is the reference's, with these changes that hold for all of them:
+ *   - every tensor pointer is a DEVICE pointer (the caller owns all buffers; the library
+ *     allocates nothing -- scratch memory is passed in as `workspace`);
+ *   - dims are passed as int64 scalars instead of `dim_t*` arrays;
+ *   - `stream` is a cudaStream_t (as void*); all work is enqueued on it, nothing synchronises;
+ *   - `status` (may be NULL) is a device int32 that kernels OR the GLOWB200_STATUS_* bits
+ *     into when they meet invalid input; the kernel still returns normally and skips the
+ *     offending element (libjit itself does no bounds checks; the rules are those of Glow's
+ *     lib/Runtime/InputSanitizer.cpp:31-110);
+ *   - the int return value is GLOWB200_OK or a GLOWB200_ERR_* code for argument / launch
+ *     errors detected on the host; glowb200_last_error() gives the message.  No exceptions
+ *     cross this boundary.
+ * Entry points are re-entrant; calls on one stream are ordered.
+ */
+#ifndef GLOW_B200_H
+#define GLOW_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GLOWB200_OK 0
+#define GLOWB200_ERR_INVALID_ARGUMENT 1
+#define GLOWB200_ERR_UNSUPPORTED 2
+#define GLOWB200_ERR_WORKSPACE_TOO_SMALL 3
+#define GLOWB200_ERR_CUDA 4
+
+/* Bits OR-ed into *status by kernels. */
+#define GLOWB200_STATUS_INDEX_OUT_OF_RANGE 1 /* an index outside [0, rows): that row is skipped   */
+#define GLOWB200_STATUS_LENGTHS_OVERRUN 2    /* sum(lengths) > len(indices): bags are truncated   */
+#define GLOWB200_STATUS_NEGATIVE_LENGTH 4    /* a negative length: treated as 0                   */
+#define GLOWB200_STATUS_BAD_OFFSETS 8        /* offsets not monotone / out of range: bag is empty */
+#define GLOWB200_STATUS_WAIT_TIMEOUT 16      /* a bounded device-side wait gave up                */
+
+/* Fused-rowwise table kinds (glow::ElemKind, include/glow/Base/Type.h:424-433).  A row is the
+ * quantized payload followed by scale then offset (include/glow/Base/Tensor.h:1585-1607). */
+#define GLOWB200_UINT8_FUSED 0      /* UInt8FusedQTy:     D bytes   + fp32 scale + fp32 offset */
+#define GLOWB200_UINT8_FUSED_FP16 1 /* UInt8FusedFP16QTy: D bytes   + fp16 scale + fp16 offset */
+#define GLOWB200_UINT4_FUSED 2      /* UInt4FusedQTy:     D/2 bytes + fp32 scale + fp32 offset */
+#define GLOWB200_UINT4_FUSED_FP16 3 /* UInt4FusedFP16QTy: D/2 bytes + fp16 scale + fp16 offset */
+
+typedef void *glowb200_stream_t;
+
+/* Message of the last error returned on this host thread ("" if none). */
+const char *glowb200_last_error(void);
+/* Library version string. */
+const char *glowb200_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Embedding gather-pool
+ * ------------------------------------------------------------------------------------- */
+
+/* One table's worth of work in a batched launch (all pointers are device pointers). */
+typedef struct glowb200_slws_job {
+  const void *data;       /* fused table [rows, in_line_size] bytes                         */
+  const void *weights;    /* per-index weights, the result's element type, [num_indices]     */
+  const void *indices;    /* int32 or int64 [num_indices]                                    */
+  const int32_t *lengths; /* [segments]                                                      */
+  void *dest;             /* result, row i at dest + i * dest_stride elements                */
+  int64_t rows;           /* table rows (for the index range check)                          */
+  int64_t num_indices;    /* entries readable in indices / weights                           */
+  int64_t dest_stride;    /* elements between consecutive result rows (>= out_line_size)     */
+  int64_t segments;       /* number of bags                                                  */
+} glowb200_slws_job;
+
+/* Bytes of scratch the gather-pool entry points need for `num_jobs` tables of at most
+ * `max_segments` bags each (segment start offsets, one int64 array per table). */
+size_t glowb200_slws_workspace_bytes(int64_t max_segments, int64_t num_jobs);
+
+/* FusedRowwiseQuantizedSparseLengthsWeightedSum.
+ * Replaces libjit_fused_rowwise_quantized_sparse_lengths_weighted_sum_f_u / _f_i32 / _f
+ * (lib/LLVMIRCodeGen/libjit/libjit.cpp:2416-2452, generic body :1253-1276; call emitted at
+ * lib/LLVMIRCodeGen/LLVMIRGen.cpp:3638-3659) for UInt8FusedQTy, and
+ * BoundInterpreterFunction::fwdFusedRowwiseQuantizedSparseLengthsWeightedSumInst
+ * (lib/Backends/Interpreter/InterpreterNodes.cpp:5764-5889) for the other three kinds.
+ *   dest [segments, out_line_size] fp32, or fp16 when out_is_fp16; weights have dest's type;
+ *   data [rows, in_line_size] bytes of `kind`; lengths int32 [segments];
+ *   use_fp16_accumulation as the node flag (honoured only for an fp16 result on an
+ *   fp16-scale table, like the reference's dispatcher).
+ * The unweighted FusedRowwiseQuantizedSparseLengthsSum is this call with weights of 1
+ * (lib/Optimizer/Lower/Lower.cpp:1590-1606). */
+int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
+    void *dest, const void *data, int kind, int64_t rows, const void *weights, const void *indices,
+    int indices_are_int64, const int32_t *lengths, int64_t segments, int64_t num_indices,
+    int64_t in_line_size, int64_t out_line_size, int out_is_fp16, int use_fp16_accumulation,
+    void *workspace, size_t workspace_bytes, int32_t *status, glowb200_stream_t stream);
+
+/* The same operator over `num_jobs` tables of one kind and one row width in ONE launch
+ * (how Glow's SLS benchmark and the SparseNN partitioner present many tables to a device:
+ * tests/benchmark/SLSBench.cpp:49-104, lib/Partitioner/Partitioner.cpp:1611-1685).
+ * `jobs` is a DEVICE array of `num_jobs` descriptors; `max_segments` bounds jobs[i].segments.
+ * dest_stride lets every table write its bags straight into a wider row (a concatenated
+ * [batch, tables*D] activation or a per-peer send buffer). */
+int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched(
+    const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_segments, int kind,
+    int indices_are_int64, int64_t in_line_size, int64_t out_line_size, int out_is_fp16,
+    int use_fp16_accumulation, void *workspace, size_t workspace_bytes, int32_t *status,
+    glowb200_stream_t stream);
+
+/* EmbeddingBagByteRowwiseOffsets (and its 4-bit form).
+ * Replaces libjit_embedding_bag_byte_rowwise_offsets_f (libjit.cpp:2454-2481) and
+ * fwdEmbeddingBagByteRowwiseOffsetsImpl (InterpreterNodes.cpp:5896-5986).  `offsets` has the
+ * indices' integer type and `num_offsets` entries; bag i spans offsets[i]..offsets[i+1], the
+ * last one ending at num_indices unless has_end_offset (then the last entry only closes the
+ * previous bag).  dest has num_offsets - has_end_offset rows. */
+int glowb200_embedding_bag_byte_rowwise_offsets(
+    void *dest, const void *data, int kind, int64_t rows, const void *weights, const void *indices,
+    const void *offsets, int indices_are_int64, int64_t num_offsets, int64_t num_indices,
+    int64_t in_line_size, int64_t out_line_size, int has_end_offset, int out_is_fp16,
+    int use_fp16_accumulation, void *workspace, size_t workspace_bytes, int32_t *status,
+    glowb200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLOW_B200_H */

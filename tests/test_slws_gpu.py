@@ -1,0 +1,296 @@
+"""Parity of the CUDA gather-pool kernels (through the C ABI) with the CPU oracle.
+
+Tolerances (stated by the benchmark definition): fp32 accumulation 1e-5 relative, fp16 result
+2e-3 relative.  "Relative" is taken against the bag's sum of magnitudes sum_j |w_j * d_jk|,
+the quantity rounding error actually scales with (an element whose terms cancel to ~0 has no
+meaningful relative error of its own).  fp16 accumulation is defined step by step by the
+reference and is compared bit for bit.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from glow_b200 import ops, workloads
+
+pytestmark = pytest.mark.gpu
+
+G = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_unit_vectors.json")))
+DEV = "cuda"
+
+
+def t(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def magnitudes(oracle, table, kind, w, idx, lengths):
+    """sum_j |w_j * d_jk| per bag, from the oracle's own dequantisation."""
+    n = int(np.sum(lengths))
+    rows = np.arange(table.shape[0], dtype=np.int64)
+    ones = np.ones(table.shape[0], np.float16 if kind & 1 else np.float32)
+    deq = oracle.frwq_slws_interp(table, kind, ones, rows, np.ones(table.shape[0], np.int32)).astype(np.float64)
+    terms = np.abs(deq[np.asarray(idx[:n], np.int64)] * np.asarray(w[:n], np.float64)[:, None])
+    out = np.zeros((len(lengths), deq.shape[1]))
+    ends = np.cumsum(lengths)
+    starts = ends - lengths
+    for i, (s, e) in enumerate(zip(starts, ends)):
+        out[i] = terms[s:e].sum(0)
+    return out
+
+
+def assert_close(got, want, mag, rel):
+    got, want = got.astype(np.float64), want.astype(np.float64)
+    bound = rel * np.maximum(mag, np.abs(want)) + 1e-30
+    bad = np.abs(got - want) > bound
+    assert not bad.any(), "max err/bound = %g" % np.max(np.abs(got - want) / bound)
+
+
+def run_slws(table, kind, w, idx, lengths, fp16_acc=False, **kw):
+    st = ops.new_status(DEV)
+    wd = np.float16 if kind & 1 else np.float32
+    out = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(
+        t(table), t(np.asarray(w, wd)), t(idx), t(np.asarray(lengths, np.int32)), kind,
+        use_fp16_accumulation=fp16_acc, status=st, **kw)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), int(st.item())
+
+
+# ------------------------------------------------------------------ reference unit-test vectors
+SLWS_CASES = ["frwq_slws_single_column", "frwq_sls_two_column", "frwq_slws_two_column", "frwq_slws_all_lengths_one"]
+
+
+@pytest.mark.parametrize("case", SLWS_CASES)
+@pytest.mark.parametrize("idt", [np.int64, np.int32])
+def test_reference_unit_vectors(oracle, case, idt):
+    g = G[case]
+    for v in g["variants"]:
+        kind = v["kind"]
+        table = oracle.fused_rowwise_quantize(np.array(g["data"], np.float32), kind)
+        got, status = run_slws(table, kind, g["weights"], np.array(g["indices"], idt), g["lengths"], v["fp16_acc"])
+        assert status == 0
+        np.testing.assert_allclose(got.astype(np.float32), np.array(g["expected"], np.float32), atol=v["tol"], rtol=0)
+
+
+@pytest.mark.parametrize("mode", ["no_end", "with_end", "partial"])
+def test_embedding_bag_reference_vectors(oracle, mode):
+    g = G["embedding_bag_byte_rowwise_offsets"]
+    for v in g["variants"]:
+        kind = v["kind"]
+        wd = np.float16 if kind & 1 else np.float32
+        table = oracle.fused_rowwise_quantize(np.array(g["data"], np.float32), kind)
+        w, idx = np.array(g["weights"], wd), np.array(g["indices"], np.int32)
+        exp = np.array(g["expected"], np.float32)
+        off = np.array(g["offsets_no_end" if mode == "no_end" else "offsets_with_end"], np.int32)
+        if mode == "partial":
+            p = g["partial"]
+            w = np.concatenate([w, np.zeros(p["weights_len"] - w.size, wd)])
+            idx = np.concatenate([idx, np.zeros(p["indices_len"] - idx.size, np.int32)])
+            off = np.concatenate([off, np.zeros(p["offsets_len"] - off.size, np.int32)])
+            exp = np.array(p["expected"], np.float32)
+        out = ops.embedding_bag_byte_rowwise_offsets(t(table), t(w), t(idx), t(off), kind,
+                                                     has_end_offset=(mode != "no_end"),
+                                                     use_fp16_accumulation=v["fp16_acc"])
+        np.testing.assert_allclose(out.cpu().numpy().astype(np.float32), exp, atol=v["tol"], rtol=0)
+
+
+# ------------------------------------------------------------------ seeded parity with the oracle
+def make_table(kind, rows, dim, seed):
+    if kind >= 2:
+        return workloads.fused_table_u4(rows, dim, seed, 0, fp16_scale_offset=bool(kind & 1))
+    return workloads.fused_table_u8(rows, dim, seed, 0, fp16_scale_offset=bool(kind & 1))
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+@pytest.mark.parametrize("dim", [8, 32, 64, 72, 128, 256, 520, 1024])
+@pytest.mark.parametrize("idt", [np.int64, np.int32])
+def test_parity_fp32_accumulation(oracle, kind, dim, idt):
+    rows, B = 20000, 300
+    table = make_table(kind, rows, dim, 1000 + dim)
+    wd = np.float16 if kind & 1 else np.float32
+    lengths, idx, w = workloads.bags_poisson(B, 20, 0, 70, rows, 77 + dim, 1, idt, wd)
+    lengths[5] = 0
+    w = (w * 2 - 1).astype(wd)  # signed weights: exercises cancellation
+    got, status = run_slws(table, kind, w, idx, lengths)
+    assert status == 0
+    want = oracle.frwq_slws_interp(table, kind, w, idx, lengths)
+    assert got.dtype == want.dtype
+    mag = magnitudes(oracle, table, kind, w, idx, lengths)
+    assert_close(got, want, mag, 2e-3 if kind & 1 else 1e-5)
+    if kind == 0:
+        assert_close(got, oracle.frwq_slws_u8_f32(table, w, idx, lengths), mag, 1e-5)
+    assert not np.any(got[5])
+
+
+@pytest.mark.parametrize("kind", [1, 3])
+@pytest.mark.parametrize("dim", [16, 64, 200, 256])
+def test_parity_fp16_accumulation_is_bit_exact(oracle, kind, dim):
+    rows, B = 5000, 200
+    table = make_table(kind, rows, dim, 31 + dim)
+    lengths, idx, w = workloads.bags_poisson(B, 24, 0, 64, rows, 5 + dim, 1, np.int64, np.float16)
+    got, status = run_slws(table, kind, w, idx, lengths, fp16_acc=True)
+    want = oracle.frwq_slws_interp(table, kind, w, idx, lengths, fp16_acc=True)
+    assert status == 0
+    np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("kind,dim", [(0, 1), (0, 3), (0, 12), (1, 6), (2, 2), (3, 10), (3, 36), (0, 2000)])
+def test_any_shape_rows_are_bit_exact(oracle, kind, dim):
+    """Odd widths take the any-shape kernel, which keeps the reference's operation order."""
+    rows, B = 3000, 70
+    table = make_table(kind, rows, dim, 9 + dim)
+    wd = np.float16 if kind & 1 else np.float32
+    lengths, idx, w = workloads.bags_poisson(B, 9, 0, 30, rows, 13 + dim, 1, np.int32, wd)
+    got, status = run_slws(table, kind, w, idx, lengths)
+    want = oracle.frwq_slws_interp(table, kind, w, idx, lengths)
+    assert status == 0
+    np.testing.assert_array_equal(got.view(np.uint8), want.view(np.uint8))
+
+
+def test_config1_full_size(oracle):
+    """The benchmark's first configuration at full size, against the oracle and -- when it was
+    built -- the reference's own libjit (strict and fast-math flavours)."""
+    table, w, idx, lengths = workloads.config1()
+    got, status = run_slws(table, 0, w, idx, lengths)
+    assert status == 0 and got.shape == (1024, 64)
+    want = oracle.frwq_slws_u8_f32(table, w, idx, lengths)
+    rel = np.abs(got - want) / np.maximum(np.abs(want), 1e-3)
+    assert rel.max() < 1e-5  # weights and most terms are positive here: plain elementwise bound holds
+    for flavour in ("strict", "fast"):
+        if oracle.ref_available(flavour):
+            ref = oracle.LibjitRef(flavour).frwq_slws(table, w, idx, lengths)
+            assert (np.abs(got - ref) / np.maximum(np.abs(ref), 1e-3)).max() < 1e-5
+
+
+# ------------------------------------------------------------------ edge cases
+def test_all_bags_empty_and_trailing_indices(oracle):
+    table = make_table(0, 100, 64, 1)
+    idx = np.arange(10, dtype=np.int64)
+    got, status = run_slws(table, 0, np.ones(10, np.float32), idx, np.zeros(17, np.int32))
+    assert status == 0 and got.shape == (17, 64) and not got.any()
+    got, status = run_slws(table, 0, np.ones(10, np.float32), idx, np.array([2, 3], np.int32))  # 5 of 10 used
+    np.testing.assert_allclose(got, oracle.frwq_slws_u8_f32(table, np.ones(10, np.float32), idx, [2, 3]), rtol=1e-5)
+    assert status == 0
+
+
+def test_invalid_input_is_reported_not_trapped(oracle):
+    table = make_table(0, 100, 64, 2)
+    w = np.ones(6, np.float32)
+    idx = np.array([1, 2, 100, 3, -1, 4], np.int64)  # 100 and -1 are outside [0, 100)
+    got, status = run_slws(table, 0, w, idx, [3, 3])
+    assert status == ops.STATUS_INDEX_OUT_OF_RANGE
+    ok = oracle.frwq_slws_u8_f32(table, np.ones(4, np.float32), np.array([1, 2, 3, 4], np.int64), [2, 2])
+    np.testing.assert_allclose(got, ok, rtol=1e-5)
+    # more lengths than indices: bags are truncated at len(indices)
+    got, status = run_slws(table, 0, w[:4], np.array([1, 2, 3, 4], np.int64), [3, 3])
+    assert status == ops.STATUS_LENGTHS_OVERRUN
+    ok = oracle.frwq_slws_u8_f32(table, w[:4], np.array([1, 2, 3, 4], np.int64), [3, 1])
+    np.testing.assert_allclose(got, ok, rtol=1e-5)
+    got, status = run_slws(table, 0, w[:4], np.array([1, 2, 3, 4], np.int64), [2, -5, 2])
+    assert status == ops.STATUS_NEGATIVE_LENGTH
+    np.testing.assert_allclose(got, oracle.frwq_slws_u8_f32(table, w[:4], np.array([1, 2, 3, 4], np.int64), [2, 0, 2]),
+                               rtol=1e-5)
+
+
+def test_many_segments_scan(oracle):
+    """More bags than one scan tile (4096) and lengths of 0/1/2."""
+    rng = np.random.default_rng(4)
+    table = make_table(0, 500, 64, 3)
+    lengths = rng.integers(0, 3, 20011).astype(np.int32)
+    n = int(lengths.sum())
+    idx = rng.integers(0, 500, n).astype(np.int32)
+    w = rng.uniform(0, 1, n).astype(np.float32)
+    got, status = run_slws(table, 0, w, idx, lengths)
+    assert status == 0
+    np.testing.assert_allclose(got, oracle.frwq_slws_u8_f32(table, w, idx, lengths), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("kind,dim", [(0, 64), (3, 128)])
+def test_embedding_bag_parity(oracle, kind, dim):
+    rng = np.random.default_rng(6)
+    rows, B = 4000, 150
+    table = make_table(kind, rows, dim, 17)
+    wd = np.float16 if kind & 1 else np.float32
+    lens = rng.integers(0, 40, B)
+    offs = np.concatenate([[0], np.cumsum(lens)])
+    n = int(offs[-1])
+    for idt in (np.int32, np.int64):
+        idx = rng.integers(0, rows, n).astype(idt)
+        w = rng.uniform(-1, 1, n).astype(wd)
+        for has_end in (True, False):
+            o = (offs if has_end else offs[:-1]).astype(idt)
+            out = ops.embedding_bag_byte_rowwise_offsets(t(table), t(w), t(idx), t(o), kind, has_end_offset=has_end)
+            want = oracle.embedding_bag_byte_rowwise_offsets(table, kind, w, idx, o, has_end)
+            mag = magnitudes(oracle, table, kind, w, idx, lens.astype(np.int32))
+            assert_close(out.cpu().numpy(), want, mag, 2e-3 if kind & 1 else 1e-5)
+
+
+def test_batched_tables_equal_single_launches(oracle):
+    """T tables in one launch, results written side by side into one [B, T*D] buffer, must be
+    bit-identical to T separate launches (the reference requires partitioned == unpartitioned:
+    tests/unittests/RecommendationSystemTest.cpp:1155-1226)."""
+    T, rows, dim, B = 5, 3000, 64, 257
+    tables, ws, idxs, lens = [], [], [], []
+    for k in range(T):
+        tables.append(t(workloads.fused_table_u8(rows + 10 * k, dim, 50, k)))
+        l, i, w = workloads.bags_poisson(B - k, 11, 0, 40, rows, 60, k)
+        lens.append(t(l)); idxs.append(t(i)); ws.append(t(w))
+    wide = torch.full((B, T * dim), float("nan"), device=DEV)
+    dests = [wide[:, k * dim:(k + 1) * dim] for k in range(T)]
+    st = ops.new_status(DEV)
+    batch = ops.SlwsBatch(ops.UINT8_FUSED, dim + 8)
+    # the destinations are column slices of `wide`: base pointer + row stride
+    batch.bind(tables, ws, idxs, lens, [_View(d) for d in dests], dest_stride=T * dim)
+    batch.run(status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    for k in range(T):
+        single = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(tables[k], ws[k], idxs[k], lens[k])
+        assert torch.equal(wide[:B - k, k * dim:(k + 1) * dim], single)
+        assert torch.isnan(wide[B - k:, k * dim:(k + 1) * dim]).all()  # rows beyond a table's bags untouched
+
+
+class _View:
+    """A strided destination: only the base pointer and dtype matter to the descriptor."""
+
+    def __init__(self, v):
+        self.v, self.dtype, self.is_cuda = v, v.dtype, True
+
+    def data_ptr(self):
+        return self.v.data_ptr()
+
+
+# ------------------------------------------------------------------ size-independent properties at full table sizes
+def test_properties_on_a_large_table():
+    """2 GB table (larger than L2): permuting the indices inside bags leaves results within
+    rounding; doubling the weights doubles the result exactly; pooling with one-hot weights
+    returns the dequantised row."""
+    rows, dim, B = 15_000_000, 128, 4096
+    g = torch.Generator(device=DEV).manual_seed(3)
+    table = torch.randint(0, 256, (rows, dim + 8), dtype=torch.uint8, device=DEV, generator=g)
+    scale = torch.empty(rows, device=DEV).uniform_(0.001, 0.01, generator=g)
+    offset = torch.empty(rows, device=DEV).uniform_(-1, 1, generator=g)
+    table[:, dim:dim + 4] = scale.view(torch.uint8).view(rows, 4)
+    table[:, dim + 4:] = offset.view(torch.uint8).view(rows, 4)
+    L = 40
+    lengths = torch.full((B,), L, dtype=torch.int32, device=DEV)
+    idx = torch.randint(0, rows, (B * L,), device=DEV, generator=g)
+    w = torch.rand(B * L, device=DEV, generator=g)
+    f = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum
+    base = f(table, w, idx, lengths)
+    # linearity in the weights (power-of-two factor: exact)
+    assert torch.equal(f(table, w * 2, idx, lengths), base * 2)
+    # order inside a bag only changes rounding
+    perm = torch.argsort(torch.rand(B, L, device=DEV, generator=g), dim=1) + (torch.arange(B, device=DEV) * L)[:, None]
+    perm = perm.reshape(-1)
+    shuffled = f(table, w[perm], idx[perm], lengths)
+    assert torch.allclose(shuffled, base, rtol=1e-5, atol=1e-5)
+    # a bag of one index with weight 1 is the dequantised row, exactly
+    one = f(table, torch.ones(B, device=DEV), idx[:B].contiguous(), torch.ones(B, dtype=torch.int32, device=DEV))
+    r = idx[:B]
+    want = table[r, :dim].float() * scale[r, None] + offset[r, None]
+    assert torch.allclose(one, want, rtol=1e-6, atol=1e-6)
+    # against a torch fp32 restatement of the pooled sum
+    ref = ((table[idx, :dim].float() * scale[idx, None] + offset[idx, None]) * w[:, None]).view(B, L, dim).sum(1)
+    assert torch.allclose(base, ref, rtol=1e-5, atol=1e-5)
