@@ -86,7 +86,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -122,10 +122,12 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_reference_rate(tables_host, reqs, seconds, threads):
+def cpu_reference_rate(tables_host, seconds, threads, distinct=24):
     """Times the reference's own kernel (libjit, fast-math build as Glow ships it; the plain-C
     port when that build is absent) on host threads, one table per call, tables spread over the
-    threads the way Glow runs one CPU device per core.  -> (GB/s, kind, passes)."""
+    threads the way Glow runs one CPU device per core.  Every pass pools a different batch
+    (`distinct` pre-generated batches, cycled) so the rows it gathers are not cache-resident
+    from the pass before.  -> (GB/s, kind, passes, seconds)."""
     from concurrent.futures import ThreadPoolExecutor
     from oracle import oracle as orc
     if orc.ref_available("fast"):
@@ -134,24 +136,27 @@ def cpu_reference_rate(tables_host, reqs, seconds, threads):
     else:
         orc.lib()
         fn, kind = (lambda t, w, i, l: orc.frwq_slws_u8_f32(t, w, i, l)), "port"
-    lengths, indices, weights, starts = reqs
     S = len(tables_host)
+    reqs = [request_host(S, 5000 + i) for i in range(distinct)]
 
-    def one(k):
+    def one(args):
+        k, (lengths, indices, weights, starts) = args
         a, b = starts[k], starts[k + 1]
         fn(tables_host[k], weights[a:b], indices[a:b], lengths[k])
 
-    nbytes = algorithmic_bytes(int(starts[S]), S * BATCH)
+    moved = 0
     with ThreadPoolExecutor(threads) as ex:
-        list(ex.map(one, range(S)))  # warm-up pass
+        list(ex.map(one, [(k, reqs[0]) for k in range(S)]))  # warm-up pass
         passes, t0 = 0, time.perf_counter()
         while True:
-            list(ex.map(one, range(S)))
+            rq = reqs[(passes + 1) % distinct]
+            list(ex.map(one, [(k, rq) for k in range(S)]))
+            moved += algorithmic_bytes(int(rq[3][S]), S * BATCH)
             passes += 1
             dt = time.perf_counter() - t0
             if dt >= seconds:
                 break
-    return nbytes * passes / dt / 1e9, kind, passes, dt
+    return moved / dt / 1e9, kind, passes, dt
 
 
 def make_table_host(seed):
@@ -167,17 +172,17 @@ def run_reference(args):
     threads = os.cpu_count() or 1
     S = min(args.tables, max(threads, 16))
     tables = [make_table_host(1000 + k) for k in range(S)]
-    reqs = request_host(S, 7)
     per_step = max(0.5, min(4.0, 60.0 / max(1, args.steps + args.warmup)))
     vals = []
     kind = "port"
     for i in range(args.warmup + args.steps):
-        v, kind, passes, dt = cpu_reference_rate(tables, reqs, per_step, threads)
+        v, kind, passes, dt = cpu_reference_rate(tables, per_step, threads)
         if i >= args.warmup:
             vals.append(v)
     value = float(np.mean(vals)) if vals else 0.0
-    nbytes = algorithmic_bytes(int(reqs[3][S]), S * BATCH)
-    sample = "%d of %d tables per pass, passes repeated for %.1f s per step" % (S, args.tables, per_step)
+    nbytes = algorithmic_bytes(int(S * BATCH * 32.0), S * BATCH)
+    sample = ("%d of %d tables per pass, a different batch each pass, passes repeated for %.1f s per step"
+              % (S, args.tables, per_step))
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": nbytes / (value * 1e9) * 1e3 if value else None,
@@ -256,11 +261,11 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident timing
+    sampler = ClockSampler(local)
+    sampler.start()
     for i in range(args.warmup):
         batches[i % R].run(status)
-    sampler = ClockSampler(local)
     barrier()
-    sampler.start()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
     ev[0].record()
@@ -268,7 +273,6 @@ def main():
         batches[i % R].run(status)
         ev[i + 1].record()
     barrier()
-    clocks = sampler.stop()
     total_ms = ev[0].elapsed_time(ev[-1])
     step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     moved = sum(bytes_per_step[i % R] for i in range(args.steps))
@@ -306,6 +310,15 @@ def main():
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    # keep the GPU under the same load until the sampler has seen it (a short timed region can
+    # fall between two nvidia-smi samples); these extra launches are not timed
+    t_end = time.time() + 1.0
+    while len(sampler.lines) < 8 and time.time() < t_end:
+        for i in range(R):
+            batches[i].run(status)
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    clocks["window"] = "warm-up, timed steps, end-to-end steps and up to 1 s of the same launches after them"
 
     # ---- max over ranks
     times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
@@ -340,12 +353,10 @@ def main():
             threads = os.cpu_count() or 1
             S = min(T, max(threads, 16))
             sample_tables = [tables[k].cpu().numpy() for k in range(S)]
-            hl, hi, hw, starts = host[0]
-            reqs = (hl.numpy()[:S], hi.numpy(), hw.numpy(), starts[:S + 1])
-            v, kind, passes, dt = cpu_reference_rate(sample_tables, reqs, args.cpu_seconds, threads)
+            v, kind, passes, dt = cpu_reference_rate(sample_tables, args.cpu_seconds, threads)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": kind,
-                                    "sample": "first %d of %d tables of request 0, %d passes in %.1f s, one table "
-                                              "per libjit call, tables spread over %d host threads"
+                                    "sample": "first %d of %d tables, %d passes (a different batch each) in %.1f s, one "
+                                              "table per libjit call, tables spread over %d host threads"
                                               % (S, T, passes, dt, threads)}
         print(json.dumps(line))
     if world > 1:

@@ -210,7 +210,7 @@ __device__ __forceinline__ float load_weight(const void *weights, int64_t i) {
 // Gather-pool.  grid = (ceil(max_segments / bags_per_block), num_jobs).
 // ------------------------------------------------------------------------------------------
 template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P>
-__global__ void __launch_bounds__(kGatherThreads) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
+__global__ void __launch_bounds__(kGatherThreads, P == 4 ? 2 : 4) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
   using RL = RowLoad<BITS, SO16>;
   const int job_id = blockIdx.y;
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + job_id) : &p.single;
@@ -246,18 +246,27 @@ __global__ void __launch_bounds__(kGatherThreads) slws_gather_kernel(const __gri
     for (int i = 0; i < 8; i++) acc[c][i] = 0.0f;
   float bias_sum = 0.0f;  // sum_j w_j * offset_j (fp32 accumulation only)
 
-  for (int64_t base = begin; base < end; base += lpr) {
-    const int64_t mine = base + gl;
-    int64_t r_mine = -1;
-    float w_mine = 0.0f;
-    if (mine < end) {
-      r_mine = (int64_t)indices[mine];
-      w_mine = load_weight<OUT16>(weights, mine);
-      if (r_mine < 0 || r_mine >= rows) { r_mine = -1; flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE; }
+  // Row numbers travel as int32 inside the group (-1 = skip): tables have fewer than 2^31 rows
+  // (checked on the host).  The next `lpr` indices are requested before the current ones are
+  // consumed, so the index fetch overlaps the row fetches.
+  auto fetch = [&](int64_t pos, int32_t &r, float &w) {
+    r = -1;
+    w = 0.0f;
+    if (pos < end) {
+      const int64_t v = (int64_t)indices[pos];
+      w = load_weight<OUT16>(weights, pos);
+      if (v < 0 || v >= rows) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;
+      else r = (int32_t)v;
     }
+  };
+  int32_t r_mine, r_next;
+  float w_mine, w_next;
+  fetch(begin + gl, r_mine, w_mine);
+  for (int64_t base = begin; base < end; base += lpr) {
+    fetch(base + lpr + gl, r_next, w_next);
     const int n = (int)((end - base) < (int64_t)lpr ? (end - base) : (int64_t)lpr);
     for (int t = 0; t < n; t += kUnroll) {
-      int64_t r[kUnroll];
+      int32_t r[kUnroll];
       float w[kUnroll];
       typename RL::Chunk pay[kUnroll][P];
       uint2 tl[kUnroll];
@@ -270,7 +279,7 @@ __global__ void __launch_bounds__(kGatherThreads) slws_gather_kernel(const __gri
 #pragma unroll
       for (int u = 0; u < kUnroll; u++) {
         if (r[u] >= 0) {
-          const uint8_t *row = data + r[u] * in_line;
+          const uint8_t *row = data + (int64_t)r[u] * in_line;
 #pragma unroll
           for (int c = 0; c < P; c++)
             if (has[c]) pay[u][c] = RL::payload(row, c * lpr + gl);
@@ -309,6 +318,8 @@ __global__ void __launch_bounds__(kGatherThreads) slws_gather_kernel(const __gri
         }
       }
     }
+    r_mine = r_next;
+    w_mine = w_next;
   }
 
   // Every bag writes its row, empty bags write zeros (the reference zero-fills dest first).
@@ -547,7 +558,7 @@ int fill_single(SlwsLaunch &L, GatherConfig &g, int &P, void *dest, const void *
                 int64_t num_indices, int64_t in_line, int64_t out_line, int out16, int acc16, void *workspace,
                 size_t workspace_bytes, int32_t *status) {
   GLOWB200_REQUIRE(segments >= 0 && segments < (1ll << 31), "segments out of range");
-  GLOWB200_REQUIRE(rows >= 0 && num_indices >= 0, "negative rows / num_indices");
+  GLOWB200_REQUIRE(rows >= 0 && rows < (1ll << 31) && num_indices >= 0, "rows must be in [0, 2^31), num_indices >= 0");
   GLOWB200_REQUIRE(segments == 0 || (dest && (num_indices == 0 || (data && weights && indices))),
                    "NULL tensor pointer");
   const bool al = aligned_to(data, kind == GLOWB200_UINT8_FUSED ? 8 : 4) && aligned_to(dest, out16 ? 2 : 4) &&
