@@ -6,7 +6,9 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libglow_b200.so")
+# GLOW_B200_LIBRARY selects another build of the same library (e.g. one compiled with
+# different tuning macros); the default is the in-tree build.
+LIB_PATH = os.environ.get("GLOW_B200_LIBRARY") or os.path.join(_HERE, "lib", "libglow_b200.so")
 
 _vp, _i64, _i32, _int, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_int, C.c_size_t
 

@@ -44,14 +44,35 @@ __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
   if (status != nullptr && bits != 0) atomicOr(status, bits);
 }
 
+// Tuning knobs, with the values measured best on B200 for 72-byte rows (256 tables x 1M rows):
+// 3 resident blocks per SM (<= 85 registers) pooled 2278 GB/s, 2 blocks 2096, 4 blocks (64
+// registers, spills) 1486; letting the row loads allocate in L1 or not, and prefetching the
+// next index chunk or not, changed nothing measurable.
+#ifndef GLOWB200_SLWS_L1_NOALLOC
+#define GLOWB200_SLWS_L1_NOALLOC 0
+#endif
+#ifndef GLOWB200_SLWS_MIN_BLOCKS
+#define GLOWB200_SLWS_MIN_BLOCKS 3
+#endif
+#ifndef GLOWB200_SLWS_PREFETCH
+#define GLOWB200_SLWS_PREFETCH 1
+#endif
 __device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
   uint32_t v;
+#if GLOWB200_SLWS_L1_NOALLOC
   asm("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+#else
+  asm("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+#endif
   return v;
 }
 __device__ __forceinline__ uint2 ldg_stream_u64(const void *p) {
   uint2 v;
+#if GLOWB200_SLWS_L1_NOALLOC
   asm("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+#else
+  asm("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+#endif
   return v;
 }
 
@@ -210,7 +231,7 @@ __device__ __forceinline__ float load_weight(const void *weights, int64_t i) {
 // Gather-pool.  grid = (ceil(max_segments / bags_per_block), num_jobs).
 // ------------------------------------------------------------------------------------------
 template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P>
-__global__ void __launch_bounds__(kGatherThreads, P == 4 ? 2 : 4) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
+__global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
   using RL = RowLoad<BITS, SO16>;
   const int job_id = blockIdx.y;
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + job_id) : &p.single;
@@ -263,7 +284,9 @@ __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 2 : 4) slws_gather_ke
   float w_mine, w_next;
   fetch(begin + gl, r_mine, w_mine);
   for (int64_t base = begin; base < end; base += lpr) {
+#if GLOWB200_SLWS_PREFETCH
     fetch(base + lpr + gl, r_next, w_next);
+#endif
     const int n = (int)((end - base) < (int64_t)lpr ? (end - base) : (int64_t)lpr);
     for (int t = 0; t < n; t += kUnroll) {
       int32_t r[kUnroll];
@@ -318,8 +341,12 @@ __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 2 : 4) slws_gather_ke
         }
       }
     }
+#if GLOWB200_SLWS_PREFETCH
     r_mine = r_next;
     w_mine = w_next;
+#else
+    fetch(base + lpr + gl, r_mine, w_mine);
+#endif
   }
 
   // Every bag writes its row, empty bags write zeros (the reference zero-fills dest first).
