@@ -28,6 +28,9 @@ SIGNATURES = {
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp, _vp]),
     "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched": (
         _int, [_vp, _i64, _i64, _int, _int, _i64, _i64, _int, _int, _vp, _sz, _vp, _vp]),
+    "glowb200_slws_static_scratch_max_segments": (_i64, []),
+    "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_static_scratch": (
+        _int, [_vp, _vp, _int, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _vp]),
     "glowb200_embedding_bag_byte_rowwise_offsets": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _sz, _vp,
                _vp]),

@@ -23,6 +23,8 @@
 // that, step by step.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace glowb200 {
 namespace {
 
@@ -660,6 +662,92 @@ extern "C" int glowb200_embedding_bag_byte_rowwise_offsets(
     slws_segments_from_offsets_kernel<int64_t><<<blocks, 256, 0, s>>>(L, reinterpret_cast<const int64_t *>(offsets), has_end_offset ? 1 : 0);
   else
     slws_segments_from_offsets_kernel<int32_t><<<blocks, 256, 0, s>>>(L, reinterpret_cast<const int32_t *>(offsets), has_end_offset ? 1 : 0);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return run_gather(L, g, P, segments, 1, s);
+}
+
+// ------------------------------------------------------------------------------------------
+// Pooling with no caller-provided workspace and no allocation of any kind.
+//
+// Who needs this: code that serves requests after all device memory has been handed out.  A
+// Glow DeviceManager sizes its slabs when a network is loaded and accounts every byte against
+// the device's budget; on its request thread a cudaMalloc could fail against that budget and,
+// succeed or fail, stalls every stream of the device while the driver takes its allocator
+// lock.  A plug-in that is only ever handed buffers by its host has no allocator at all.  Such
+// callers cannot size a workspace per request either, so the bag boundaries go into a fixed
+// array that is part of the library image.
+//
+// The array costs kStaticScratchMaxSegments * 8 bytes (+ padding) of device memory on every
+// GPU that loads the library, for the life of the process.
+// ------------------------------------------------------------------------------------------
+namespace glowb200 {
+namespace {
+constexpr int64_t kStaticScratchMaxSegments = 65536;
+constexpr size_t kStaticScratchBytes = ((kStaticScratchMaxSegments + 1) * 8 + 255) / 256 * 256;
+constexpr int kStaticScratchMaxDevices = 64;
+}  // namespace
+}  // namespace glowb200
+
+// Device storage.  In host code this name is only a handle for the runtime's symbol lookup --
+// it is NOT a device address and must never be passed to a kernel as one.
+static __device__ __align__(256) unsigned char g_slws_static_scratch[glowb200::kStaticScratchBytes];
+
+namespace glowb200 {
+namespace {
+// Device address of g_slws_static_scratch on the CURRENT device, looked up once per device.
+int static_scratch_address(void **out) {
+  static void *cached[kStaticScratchMaxDevices] = {nullptr};
+  static bool known[kStaticScratchMaxDevices] = {false};
+  static std::mutex lock;
+  int dev = -1;
+  GLOWB200_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kStaticScratchMaxDevices)
+    return set_error(GLOWB200_ERR_UNSUPPORTED, "device ordinal %d is beyond the %d this entry point tracks", dev,
+                     kStaticScratchMaxDevices);
+  std::lock_guard<std::mutex> guard(lock);
+  if (!known[dev]) {
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_slws_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return set_error(GLOWB200_ERR_CUDA, "cudaGetSymbolAddress(static scratch) on device %d failed: %s", dev,
+                       cudaGetErrorString(e));
+    cached[dev] = ptr;
+    known[dev] = true;
+  }
+  *out = cached[dev];
+  return GLOWB200_OK;
+}
+}  // namespace
+}  // namespace glowb200
+
+extern "C" int64_t glowb200_slws_static_scratch_max_segments(void) { return glowb200::kStaticScratchMaxSegments; }
+
+extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_static_scratch(
+    void *dest, const void *data, int kind, int64_t rows, const void *weights, const void *indices,
+    int indices_are_int64, const int32_t *lengths, int64_t segments, int64_t num_indices, int64_t in_line_size,
+    int64_t out_line_size, int out_is_fp16, int use_fp16_accumulation, int32_t *status, glowb200_stream_t stream) {
+  if (segments > kStaticScratchMaxSegments)
+    return set_error(GLOWB200_ERR_UNSUPPORTED,
+                     "%lld bags exceed the %lld the built-in scratch array holds; use the entry point that takes a "
+                     "workspace", (long long)segments, (long long)kStaticScratchMaxSegments);
+  if (segments <= 0) {
+    GLOWB200_REQUIRE(segments == 0, "segments out of range");
+    return GLOWB200_OK;
+  }
+  void *scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  SlwsLaunch L;
+  GatherConfig g;
+  int P;
+  if (int rc = fill_single(L, g, P, dest, data, kind, rows, weights, indices, indices_are_int64, lengths, segments,
+                           num_indices, in_line_size, out_line_size, out_is_fp16, use_fp16_accumulation, scratch,
+                           kStaticScratchBytes, status))
+    return rc;
+  GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // The segments kernel rewrites all segments + 1 boundaries this call reads; nothing in the
+  // array has to start at zero, and whatever an earlier call left beyond them is never read.
+  slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return run_gather(L, g, P, segments, 1, s);
 }

@@ -89,6 +89,27 @@ def fused_rowwise_quantized_sparse_lengths_weighted_sum(data, weights, indices, 
     return out
 
 
+def fused_rowwise_quantized_sparse_lengths_weighted_sum_static_scratch(data, weights, indices, lengths,
+                                                                       kind=UINT8_FUSED, *, out,
+                                                                       use_fp16_accumulation=False, status=None,
+                                                                       num_indices=None):
+    """The same operator for callers that must not allocate: `out` is required, no workspace is
+    taken (the bag boundaries go into an array built into the library) and nothing is allocated
+    here either.  At most static_scratch_max_segments() bags; calls that may overlap on the GPU
+    must be serialised by the caller."""
+    rows, in_line = data.shape
+    n = indices.shape[0] if num_indices is None else int(num_indices)
+    check(_lib.lib().glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_static_scratch(
+        _p(out), _p(data), kind, rows, _p(weights), _p(indices), int(indices.dtype == torch.int64), _p(lengths),
+        lengths.shape[0], n, in_line, out_columns(in_line, kind), int(out.dtype == torch.float16),
+        int(use_fp16_accumulation), _p(status), _stream()))
+    return out
+
+
+def static_scratch_max_segments():
+    return int(_lib.lib().glowb200_slws_static_scratch_max_segments())
+
+
 def fused_rowwise_quantized_sparse_lengths_sum(data, indices, lengths, kind=UINT8_FUSED, **kw):
     """Unweighted form = weighted with weights of one (lib/Optimizer/Lower/Lower.cpp:1590-1606)."""
     odt = result_dtype(kind)

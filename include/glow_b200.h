@@ -120,6 +120,30 @@ int glowb200_embedding_bag_byte_rowwise_offsets(
     int use_fp16_accumulation, void *workspace, size_t workspace_bytes, int32_t *status,
     glowb200_stream_t stream);
 
+/* FusedRowwiseQuantizedSparseLengthsWeightedSum for callers that can neither allocate device
+ * memory nor size a workspace per request.  (No counterpart in the reference: its CPU kernels
+ * need no scratch.)  Think of a DeviceManager's request thread after every byte of HBM was
+ * budgeted at network-load time -- a cudaMalloc there can fail against the budget and blocks
+ * all streams of the device while it runs -- or of a plug-in that only ever receives buffers
+ * from its host.  Same arguments and results as
+ * glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum minus the workspace pair: the bag
+ * boundaries go into an array built into the library (about 0.5 MB of device memory on every
+ * GPU that loads it, held until the process exits).
+ *   - At most glowb200_slws_static_scratch_max_segments() (65536) bags per call; more is
+ *     refused with GLOWB200_ERR_UNSUPPORTED and a message, nothing is launched.
+ *   - The first call on each device looks the array's device address up (with that device
+ *     current).  Make that first call during set-up, before any stream capture is begun.
+ *   - All calls on a device share the one array.  Calls on the same stream are ordered and
+ *     safe; calls that can overlap on the GPU (different streams, different host threads on
+ *     different streams) race on it and must be serialised by the caller.
+ *   - This entry point calls no cudaMalloc / cudaFree or any other allocating routine. */
+int64_t glowb200_slws_static_scratch_max_segments(void);
+int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_static_scratch(
+    void *dest, const void *data, int kind, int64_t rows, const void *weights, const void *indices,
+    int indices_are_int64, const int32_t *lengths, int64_t segments, int64_t num_indices,
+    int64_t in_line_size, int64_t out_line_size, int out_is_fp16, int use_fp16_accumulation,
+    int32_t *status, glowb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
