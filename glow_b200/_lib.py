@@ -10,7 +10,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # different tuning macros); the default is the in-tree build.
 LIB_PATH = os.environ.get("GLOW_B200_LIBRARY") or os.path.join(_HERE, "lib", "libglow_b200.so")
 
-_vp, _i64, _i32, _int, _sz = C.c_void_p, C.c_int64, C.c_int32, C.c_int, C.c_size_t
+_vp, _i64, _i32, _int, _sz, _f32 = C.c_void_p, C.c_int64, C.c_int32, C.c_int, C.c_size_t, C.c_float
 
 
 class SlwsJob(C.Structure):
@@ -31,6 +31,16 @@ SIGNATURES = {
     "glowb200_slws_static_scratch_max_segments": (_i64, []),
     "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_static_scratch": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _vp]),
+    "glowb200_quantize_scale_offset_32to8": (None, [_f32, _vp, _vp, _vp]),
+    "glowb200_rowwise_requant_params": (_int, [_vp, _i64, _f32, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "glowb200_i8_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "glowb200_i8_row_sums": (_int, [_vp, _i64, _i64, _vp, _vp]),
+    "glowb200_rowwise_quantized_fc_i8_i32": (
+        _int, [_vp] * 11 + [_i64, _i64, _i64, _i32, _i32, _i32, _vp, _int, _vp, _sz, _vp, _vp]),
+    "glowb200_fc_i8_i32": (
+        _int, [_vp] * 4 + [_i64] * 3 + [_i32] * 10 + [_vp, _int, _vp, _sz, _vp, _vp]),
+    "glowb200_matmul_i8": (
+        _int, [_vp] * 3 + [_i64] * 3 + [_i32] * 6 + [_int, _vp, _sz, _vp, _vp]),
     "glowb200_embedding_bag_byte_rowwise_offsets": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _sz, _vp,
                _vp]),

@@ -1,0 +1,597 @@
+// Int8 contraction for Glow's quantized dense layers on the sm_100a tensor cores:
+// RowwiseQuantizedFullyConnected, FullyConnected (int8) and MatMul (int8).
+//
+//   out[i,j] = clip8( scale32( sum_k (A[i,k]-aOff)*(B[j,k]-bOff_j) + biasTerm_j ,
+//                              outPre_j, outPost_j, outScale_j, outOffset ) )
+//
+// The tensor cores contract the raw int8 values (tcgen05.mma kind::i8, int32 accumulators in
+// tensor memory); the offsets are folded in afterwards, exactly, in 32-bit wrapping arithmetic:
+//   sum_k (A-a0)(B-b0) = sum_k A*B - a0*rowsum(B_j) - b0_j*rowsum(A_i) + K*a0*b0_j .
+// The epilogue then applies Glow's integer requantisation (libjit_scale, libjit_clip_i8).
+//
+// One CTA computes a 128 x BLOCK_N tile.  Warp 0 feeds shared memory with TMA (128-byte
+// swizzled K-major tiles of 128 bytes of K), warp 1 issues the MMAs and owns the tensor-memory
+// allocation, warps 2-5 build the tile's per-column constants while the main loop runs and
+// then drain the accumulators (tcgen05.ld), requantise and store int8.
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel raises
+// GLOWB200_STATUS_WAIT_TIMEOUT, all roles leave their loops, tensor memory is released and the
+// kernel returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace glowb200 {
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 128;          // bytes of K per pipeline stage = one 128B swizzle atom
+constexpr int kUmmaK = 32;            // K per tcgen05.mma for 8-bit operands
+constexpr int kGemmThreads = 192;     // 6 warps
+constexpr long long kWaitCycles = 2000000000ll;  // ~1 s: far beyond any legitimate wait
+
+struct GemmParams {
+  int8_t *out;                // [M, N]
+  const int32_t *bias;        // [N] or nullptr (MatMul)
+  const int32_t *b_offsets;   // weight offsets; index j * stride_b_off
+  const int32_t *bias_pre, *bias_post, *bias_scale;  // index j * stride_q
+  const int32_t *out_pre, *out_post, *out_scale;      // index j * stride_q
+  const int32_t *b_row_sums;  // [N] sum_k B[j,k]
+  const int32_t *a_row_sums;  // [M] sum_k A[i,k], or nullptr when every b offset is 0
+  int32_t *status;
+  int M, N, K;
+  int32_t a_offset, bias_offset, out_offset;
+  // per-tensor layers: one set of scalars for every column instead of the arrays above
+  int uniform;
+  int32_t u_b_offset, u_bias_pre, u_bias_post, u_bias_scale, u_out_pre, u_out_post, u_out_scale;
+};
+
+struct ColQuant {
+  int32_t b_off, bias_pre, bias_post, bias_scale, out_pre, out_post, out_scale;
+};
+__device__ __forceinline__ ColQuant col_quant(const GemmParams &p, int j) {
+  if (p.uniform) return {p.u_b_offset, p.u_bias_pre, p.u_bias_post, p.u_bias_scale, p.u_out_pre, p.u_out_post, p.u_out_scale};
+  return {p.b_offsets[j], p.bias ? p.bias_pre[j] : 0, p.bias ? p.bias_post[j] : 0, p.bias ? p.bias_scale[j] : 0,
+          p.out_pre[j], p.out_post[j], p.out_scale[j]};
+}
+
+struct ColParams {  // per output column, built once per tile in shared memory
+  int32_t c;        // bias term - aOff*rowsum(B_j) + K*aOff*bOff_j
+  int32_t b_off;
+  int32_t shifts;   // pre | post << 8
+  int32_t scale;
+};
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up (or another role already did).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    for (int i = 0; i < 64; i++)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are 1024
+// bytes apart (stride byte offset), the leading byte offset is unused and set to 16 bytes,
+// descriptor version 1 (sm_100), layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::i8: D = s32, A = B = signed 8-bit, both K-major, dense.
+__host__ __device__ constexpr uint32_t idesc_i8(int m, int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------
+// The tile kernel
+// ---------------------------------------------------------------------------------------
+template <int BLOCK_N, int STAGES>
+struct GemmSmem {
+  static constexpr int kABytes = kBlockM * kBlockK;
+  static constexpr int kBBytes = BLOCK_N * kBlockK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTileBytes = STAGES * kStageBytes;
+  static constexpr int kColBytes = BLOCK_N * (int)sizeof(ColParams);
+  static constexpr int kTotal = kTileBytes + kColBytes + 256 /*barriers*/ + 1024 /*alignment slack*/;
+};
+
+template <int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ GemmParams p) {
+  using S = GemmSmem<BLOCK_N, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled tiles must start on 1024-byte boundaries.
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  ColParams *cols = reinterpret_cast<ColParams *>(smem + S::kTileBytes);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + S::kTileBytes + S::kColBytes);
+  uint64_t *empty = full + STAGES;
+  uint64_t *acc_ready = empty + STAGES;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kBlockM, n0 = blockIdx.x * BLOCK_N;
+  const int k_blocks = (p.K + kBlockK - 1) / kBlockK;
+  constexpr uint32_t kTmemCols = BLOCK_N < 32 ? 32 : BLOCK_N;  // power of two >= 32
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; kb++) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1, abort_flag)) break;
+        uint8_t *a_dst = smem + s * S::kStageBytes;
+        uint8_t *b_dst = a_dst + S::kABytes;
+        mbar_expect_tx(&full[s], S::kStageBytes);
+        tma_load_2d(a_dst, &map_a, kb * kBlockK, m0, &full[s]);
+        tma_load_2d(b_dst, &map_b, kb * kBlockK, n0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_i8(kBlockM, BLOCK_N);
+      for (int kb = 0; kb < k_blocks; kb++) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
+        const uint32_t b_addr = a_addr + S::kABytes;
+        const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < kBlockK / kUmmaK; k++) {
+          // advancing K inside the swizzle atom = advancing the start address by 32 bytes
+          umma_i8(tmem_base, a_desc + (uint64_t)(k * (kUmmaK >> 4)), b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc,
+                  (kb | k) != 0);
+        }
+        umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+      }
+      umma_commit(acc_ready);    // accumulators complete
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5 ----------------
+    const int et = threadIdx.x - 64;  // 0..127
+    // (1) per-column constants of this tile, while the main loop runs
+    for (int c = et; c < BLOCK_N; c += 128) {
+      const int j = n0 + c;
+      ColParams cp = {0, 0, 0, 0};
+      if (j < p.N) {
+        const ColQuant q = col_quant(p, j);
+        int32_t term = 0;
+        if (p.bias) term = scale32(p.bias[j] - p.bias_offset, q.bias_pre, q.bias_post, q.bias_scale, 0);
+        const uint32_t corr = (uint32_t)term - (uint32_t)p.a_offset * (uint32_t)p.b_row_sums[j] +
+                              (uint32_t)p.K * (uint32_t)p.a_offset * (uint32_t)q.b_off;
+        cp.c = (int32_t)corr;
+        cp.b_off = q.b_off;
+        cp.shifts = q.out_pre | (q.out_post << 8);
+        cp.scale = q.out_scale;
+      }
+      cols[c] = cp;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
+    // (2) drain the accumulators
+    const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row = m0 + quarter * 32 + lane;
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0, abort_flag));
+    tc_fence_after();
+    if (ok) {
+      const int32_t a_sum = (p.a_row_sums && row < p.M) ? p.a_row_sums[row] : 0;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      int8_t *out_row = p.out + (size_t)row * p.N + n0;
+      const bool vec_ok = ((p.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+        uint32_t acc[32];
+        tmem_ld_32x32b_x32(lane_addr + (uint32_t)c0, acc);
+        tmem_ld_wait();
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const ColParams cp = cols[c0 + i];
+          uint32_t v = acc[i] + (uint32_t)cp.c - (uint32_t)cp.b_off * (uint32_t)a_sum;
+          const int32_t pre = cp.shifts & 0xff, post = cp.shifts >> 8;
+          const int32_t r = clip_i8(scale32((int32_t)v, pre, post, cp.scale, p.out_offset));
+          if ((i & 3) == 0) packed[i >> 2] = 0;
+          packed[i >> 2] |= (uint32_t)(r & 0xff) << (8 * (i & 3));
+        }
+        if (row < p.M) {
+          if (vec_ok && n0 + c0 + 32 <= p.N) {
+            *reinterpret_cast<uint4 *>(out_row + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            *reinterpret_cast<uint4 *>(out_row + c0 + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+            for (int i = 0; i < 32; i++)
+              if (n0 + c0 + i < p.N) out_row[c0 + i] = (int8_t)((packed[i >> 2] >> (8 * (i & 3))) & 0xff);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up.  Report it, then give copies that may still be in flight towards this
+    // CTA's shared memory a bounded time to land before the CTA retires.
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, GLOWB200_STATUS_WAIT_TIMEOUT);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000ll) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Row sums of an int8 matrix [rows, K] -> int32 [rows]   (one warp per row, dp4a)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) i8_row_sums_kernel(const int8_t *__restrict__ x, int rows, int K, int32_t *__restrict__ out) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int8_t *r = x + (size_t)row * K;
+  int32_t acc = 0;
+  if ((K & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    for (int k = lane * 16; k < K; k += 512) {
+      const int4 v = *reinterpret_cast<const int4 *>(r + k);
+      acc = __dp4a(v.x, 0x01010101, acc);
+      acc = __dp4a(v.y, 0x01010101, acc);
+      acc = __dp4a(v.z, 0x01010101, acc);
+      acc = __dp4a(v.w, 0x01010101, acc);
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) acc += r[k];
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  if (lane == 0) out[row] = acc;
+}
+
+// ---------------------------------------------------------------------------------------
+// Any-shape contraction (K not a multiple of 16, unaligned pointers): one thread per output,
+// the reference's loop as written.  Also the cross-check of the tensor-core kernel in tests.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) i8_gemm_requant_any_kernel(const int8_t *__restrict__ a, const int8_t *__restrict__ b,
+                                                                   const __grid_constant__ GemmParams p) {
+  const int j = blockIdx.x * 16 + (threadIdx.x & 15), i = blockIdx.y * 16 + (threadIdx.x >> 4);
+  if (i >= p.M || j >= p.N) return;
+  const ColQuant q = col_quant(p, j);
+  uint32_t sum = 0;
+  for (int k = 0; k < p.K; k++)
+    sum += (uint32_t)(((int32_t)b[(size_t)j * p.K + k] - q.b_off) * ((int32_t)a[(size_t)i * p.K + k] - p.a_offset));
+  if (p.bias) sum += (uint32_t)scale32(p.bias[j] - p.bias_offset, q.bias_pre, q.bias_post, q.bias_scale, 0);
+  p.out[(size_t)i * p.N + j] = (int8_t)clip_i8(scale32((int32_t)sum, q.out_pre, q.out_post, q.out_scale, p.out_offset));
+}
+
+// [R, C] int8 -> [C, R] int8 (32x32 tiles through shared memory)
+__global__ void __launch_bounds__(256) i8_transpose_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int R, int C) {
+  __shared__ int8_t tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int y = threadIdx.y; y < 32; y += 8) {
+    const int r = r0 + y, c = c0 + threadIdx.x;
+    tile[y][threadIdx.x] = (r < R && c < C) ? in[(size_t)r * C + c] : (int8_t)0;
+  }
+  __syncthreads();
+  for (int y = threadIdx.y; y < 32; y += 8) {
+    const int c = c0 + y, r = r0 + threadIdx.x;
+    if (c < C && r < R) out[(size_t)c * R + r] = tile[threadIdx.x][y];
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// int8 [rows, K] row-major -> 2-D map with a {128 bytes of K, box_rows} box, 128-byte swizzle;
+// out-of-range elements read as zero.
+int make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return set_error(GLOWB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(GLOWB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return GLOWB200_OK;
+}
+
+template <int BLOCK_N, int STAGES>
+int launch_tile_kernel(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, cudaStream_t s) {
+  using S = GemmSmem<BLOCK_N, STAGES>;
+  // per device and cheap: set on every launch rather than tracked
+  GLOWB200_CUDA_OK(cudaFuncSetAttribute(i8_gemm_requant_kernel<BLOCK_N, STAGES>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  dim3 grid((p.N + BLOCK_N - 1) / BLOCK_N, (p.M + kBlockM - 1) / kBlockM);
+  i8_gemm_requant_kernel<BLOCK_N, STAGES><<<grid, kGemmThreads, S::kTotal, s>>>(ma, mb, p);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+bool ptr16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Runs out = requant(A[M,K] x B[N,K]^T ...) choosing the tensor-core or the any-shape kernel.
+// `ws` holds b_row_sums (when not supplied) and a_row_sums (when needed).
+int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_row_sums_in, bool b_offsets_zero,
+             int force_any, void *ws, size_t ws_bytes, cudaStream_t s) {
+  if (p.M == 0 || p.N == 0) return GLOWB200_OK;
+  const bool tc = !force_any && p.K > 0 && (p.K % 16) == 0 && ptr16(a) && ptr16(b);
+  if (!tc) {
+    dim3 grid((p.N + 15) / 16, (p.M + 15) / 16);
+    i8_gemm_requant_any_kernel<<<grid, 256, 0, s>>>(a, b, p);
+    GLOWB200_CUDA_OK(cudaGetLastError());
+    return GLOWB200_OK;
+  }
+  const size_t need = align_up((size_t)p.N * 4, 256) + align_up((size_t)p.M * 4, 256);
+  if (ws == nullptr || ws_bytes < need)
+    return set_error(GLOWB200_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", ws_bytes, need);
+  int32_t *bs = reinterpret_cast<int32_t *>(ws);
+  int32_t *as = reinterpret_cast<int32_t *>(reinterpret_cast<uint8_t *>(ws) + align_up((size_t)p.N * 4, 256));
+  if (b_row_sums_in) {
+    p.b_row_sums = b_row_sums_in;
+  } else {
+    i8_row_sums_kernel<<<(p.N + 7) / 8, 256, 0, s>>>(b, p.N, p.K, bs);
+    GLOWB200_CUDA_OK(cudaGetLastError());
+    p.b_row_sums = bs;
+  }
+  if (!b_offsets_zero) {
+    i8_row_sums_kernel<<<(p.M + 7) / 8, 256, 0, s>>>(a, p.M, p.K, as);
+    GLOWB200_CUDA_OK(cudaGetLastError());
+    p.a_row_sums = as;
+  } else {
+    p.a_row_sums = nullptr;
+  }
+  CUtensorMap ma, mb;
+  if (p.N > 64) {
+    if (int rc = make_map(&ma, a, p.M, p.K, kBlockM)) return rc;
+    if (int rc = make_map(&mb, b, p.N, p.K, 256)) return rc;
+    return launch_tile_kernel<256, 4>(ma, mb, p, s);
+  }
+  if (int rc = make_map(&ma, a, p.M, p.K, kBlockM)) return rc;
+  if (int rc = make_map(&mb, b, p.N, p.K, 64)) return rc;
+  return launch_tile_kernel<64, 6>(ma, mb, p, s);
+}
+
+int check_dims(int64_t M, int64_t K, int64_t N) {
+  GLOWB200_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 24),
+                   "matrix dimensions out of range");
+  return GLOWB200_OK;
+}
+
+}  // namespace
+}  // namespace glowb200
+
+using namespace glowb200;
+
+extern "C" size_t glowb200_i8_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N) {
+  if (M < 0 || N < 0 || K < 0) return 0;
+  // row sums of both operands + room for a transposed copy of a [K, N] right-hand side
+  return align_up((size_t)N * 4, 256) + align_up((size_t)M * 4, 256) + align_up((size_t)N * (size_t)K, 256);
+}
+
+extern "C" int glowb200_i8_row_sums(const int8_t *matrix, int64_t rows, int64_t K, int32_t *sums, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(rows >= 0 && K >= 0 && rows < (1ll << 31) && K < (1ll << 31), "bad dimensions");
+  if (rows == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(matrix && sums, "NULL pointer");
+  i8_row_sums_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(matrix, (int)rows, (int)K, sums);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_rowwise_quantized_fc_i8_i32(
+    int8_t *out, const int8_t *in, const int8_t *weights, const int32_t *bias, const int32_t *weights_offsets,
+    const int32_t *bias_pre, const int32_t *bias_post, const int32_t *bias_scale, const int32_t *out_pre,
+    const int32_t *out_post, const int32_t *out_scale, int64_t M, int64_t K, int64_t N, int32_t out_offset,
+    int32_t in_offset, int32_t bias_offset, const int32_t *weights_row_sums, int flags, void *workspace,
+    size_t workspace_bytes, int32_t *status, glowb200_stream_t stream) {
+  if (int rc = check_dims(M, K, N)) return rc;
+  if (M == 0 || N == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(out && in && weights && bias && weights_offsets && bias_pre && bias_post && bias_scale && out_pre &&
+                       out_post && out_scale, "NULL tensor pointer");
+  GemmParams p{};
+  p.out = out;
+  p.bias = bias;
+  p.b_offsets = weights_offsets;
+  p.bias_pre = bias_pre; p.bias_post = bias_post; p.bias_scale = bias_scale;
+  p.out_pre = out_pre; p.out_post = out_post; p.out_scale = out_scale;
+  p.status = status;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.uniform = 0;
+  p.a_offset = in_offset; p.bias_offset = bias_offset; p.out_offset = out_offset;
+  return run_gemm(p, in, weights, weights_row_sums, (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) != 0,
+                  (flags & GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL) != 0, workspace, workspace_bytes,
+                  reinterpret_cast<cudaStream_t>(stream));
+}
+
+namespace {
+// Shared tail of the two per-tensor entry points, whose right-hand side is [K, N]: transposes it
+// into the workspace (unless the caller already holds the [N, K] form) and runs the contraction
+// with every per-column array read at stride 0.
+int run_per_tensor(GemmParams p, const int8_t *lhs, const int8_t *rhs_kn, const int8_t *rhs_nk, int flags, void *workspace,
+                   size_t workspace_bytes, cudaStream_t s) {
+  const size_t sums = align_up((size_t)p.N * 4, 256) + align_up((size_t)p.M * 4, 256);
+  const int8_t *b = rhs_nk;
+  if (b == nullptr) {
+    const size_t need = sums + align_up((size_t)p.N * (size_t)p.K, 256);
+    if (workspace == nullptr || workspace_bytes < need)
+      return set_error(GLOWB200_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+    int8_t *t = reinterpret_cast<int8_t *>(workspace) + sums;
+    if (p.K > 0) {
+      dim3 grid((p.N + 31) / 32, (p.K + 31) / 32), block(32, 8);
+      i8_transpose_kernel<<<grid, block, 0, s>>>(rhs_kn, t, p.K, p.N);
+      GLOWB200_CUDA_OK(cudaGetLastError());
+    }
+    b = t;
+  }
+  return run_gemm(p, lhs, b, nullptr, (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) != 0,
+                  (flags & GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL) != 0, workspace, workspace_bytes, s);
+}
+}  // namespace
+
+extern "C" int glowb200_fc_i8_i32(int8_t *out, const int8_t *in, const int8_t *weights, const int32_t *bias, int64_t M,
+                                  int64_t K, int64_t N, int32_t out_offset, int32_t in_offset, int32_t weights_offset,
+                                  int32_t bias_offset, int32_t bias_pre, int32_t bias_post, int32_t bias_scale,
+                                  int32_t out_pre, int32_t out_post, int32_t out_scale,
+                                  const int8_t *weights_transposed, int flags, void *workspace,
+                                  size_t workspace_bytes, int32_t *status, glowb200_stream_t stream) {
+  if (int rc = check_dims(M, K, N)) return rc;
+  if (M == 0 || N == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(out && in && (weights || weights_transposed) && bias, "NULL tensor pointer");
+  GemmParams p{};
+  p.out = out;
+  p.bias = bias;
+  p.status = status;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_offset = in_offset; p.bias_offset = bias_offset; p.out_offset = out_offset;
+  p.uniform = 1;
+  p.u_b_offset = weights_offset;
+  p.u_bias_pre = bias_pre; p.u_bias_post = bias_post; p.u_bias_scale = bias_scale;
+  p.u_out_pre = out_pre; p.u_out_post = out_post; p.u_out_scale = out_scale;
+  if (weights_offset == 0) flags |= GLOWB200_FC_WEIGHT_OFFSETS_ZERO;
+  return run_per_tensor(p, in, weights, weights_transposed, flags, workspace, workspace_bytes,
+                        reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int glowb200_matmul_i8(int8_t *out, const int8_t *lhs, const int8_t *rhs, int64_t M, int64_t K, int64_t N,
+                                  int32_t out_offset, int32_t lhs_offset, int32_t rhs_offset, int32_t out_pre,
+                                  int32_t out_post, int32_t out_scale, int flags, void *workspace,
+                                  size_t workspace_bytes, int32_t *status, glowb200_stream_t stream) {
+  if (int rc = check_dims(M, K, N)) return rc;
+  if (M == 0 || N == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(out && lhs && rhs, "NULL tensor pointer");
+  GemmParams p{};
+  p.out = out;
+  p.bias = nullptr;
+  p.status = status;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_offset = lhs_offset; p.bias_offset = 0; p.out_offset = out_offset;
+  p.uniform = 1;
+  p.u_b_offset = rhs_offset;
+  p.u_out_pre = out_pre; p.u_out_post = out_post; p.u_out_scale = out_scale;
+  if (rhs_offset == 0) flags |= GLOWB200_FC_WEIGHT_OFFSETS_ZERO;
+  return run_per_tensor(p, lhs, rhs, nullptr, flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}

@@ -142,6 +142,96 @@ def embedding_bag_byte_rowwise_offsets(data, weights, indices, offsets, kind=UIN
     return out
 
 
+# ------------------------------------------------------------------------------------------
+# Int8 dense layers
+# ------------------------------------------------------------------------------------------
+FC_WEIGHT_OFFSETS_ZERO = 1
+FC_FORCE_ANY_SHAPE_KERNEL = 2
+
+
+def quantize_scale_offset_32to8(scale):
+    """(pre, post, integer scale) for a float rescale factor -- host computation."""
+    out = (C.c_int32 * 3)()
+    base = C.addressof(out)
+    _lib.lib().glowb200_quantize_scale_offset_32to8(C.c_float(float(scale)), C.c_void_p(base), C.c_void_p(base + 4),
+                                                    C.c_void_p(base + 8))
+    return int(out[0]), int(out[1]), int(out[2])
+
+
+def rowwise_requant_params(row_scales, in_scale, bias_scales, out_scale):
+    """Host derivation of (bias_pre, bias_post, bias_scale, out_pre, out_post, out_scale) int32
+    numpy arrays for a rowwise FC / channelwise conv."""
+    import numpy as np
+    rs = np.ascontiguousarray(row_scales, np.float32)
+    bs = np.ascontiguousarray(np.atleast_1d(bias_scales), np.float32)
+    outs = [np.empty(rs.shape[0], np.int32) for _ in range(6)]
+    check(_lib.lib().glowb200_rowwise_requant_params(
+        C.c_void_p(rs.ctypes.data), rs.shape[0], C.c_float(float(in_scale)), C.c_void_p(bs.ctypes.data),
+        bs.shape[0], C.c_float(float(out_scale)), *[C.c_void_p(o.ctypes.data) for o in outs]))
+    return outs
+
+
+def i8_gemm_workspace_bytes(M, K, N):
+    return int(_lib.lib().glowb200_i8_gemm_workspace_bytes(int(M), int(K), int(N)))
+
+
+def i8_row_sums(matrix):
+    _cuda(matrix, "matrix", (torch.int8,))
+    out = torch.empty(matrix.shape[0], dtype=torch.int32, device=matrix.device)
+    check(_lib.lib().glowb200_i8_row_sums(_p(matrix), matrix.shape[0], matrix.shape[1], _p(out), _stream()))
+    return out
+
+
+def rowwise_quantized_fc(inp, weights, bias, weights_offsets, bias_triples, out_triples, out_offset, in_offset,
+                         bias_offset, *, weights_row_sums=None, flags=0, out=None, workspace=None, status=None):
+    """RowwiseQuantizedFullyConnected: inp int8 [M,K], weights int8 [N,K], bias int32 [N],
+    weights_offsets int32 [N], bias_triples/out_triples = three int32 [N] tensors each."""
+    _cuda(inp, "inp", (torch.int8,))
+    _cuda(weights, "weights", (torch.int8,))
+    M, K = inp.shape
+    N = weights.shape[0]
+    for t in (bias, weights_offsets, *bias_triples, *out_triples):
+        _cuda(t, "per-row parameter", (torch.int32,))
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int8, device=inp.device)
+    ws = _workspace(workspace, i8_gemm_workspace_bytes(M, K, N), inp.device)
+    check(_lib.lib().glowb200_rowwise_quantized_fc_i8_i32(
+        _p(out), _p(inp), _p(weights), _p(bias), _p(weights_offsets), _p(bias_triples[0]), _p(bias_triples[1]),
+        _p(bias_triples[2]), _p(out_triples[0]), _p(out_triples[1]), _p(out_triples[2]), M, K, N, int(out_offset),
+        int(in_offset), int(bias_offset), _p(weights_row_sums), int(flags), _p(ws), ws.numel(), _p(status),
+        _stream()))
+    return out
+
+
+def fully_connected_i8(inp, weights, bias, out_offset, in_offset, weights_offset, bias_offset, bias_triple,
+                       out_triple, *, weights_transposed=None, flags=0, out=None, workspace=None, status=None):
+    """FullyConnected (int8, per-tensor): inp [M,K], weights [K,N], bias int32 [N]."""
+    M, K = inp.shape
+    N = weights.shape[1] if weights is not None else weights_transposed.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int8, device=inp.device)
+    ws = _workspace(workspace, i8_gemm_workspace_bytes(M, K, N), inp.device)
+    check(_lib.lib().glowb200_fc_i8_i32(
+        _p(out), _p(inp), _p(weights), _p(bias), M, K, N, int(out_offset), int(in_offset), int(weights_offset),
+        int(bias_offset), *[int(v) for v in bias_triple], *[int(v) for v in out_triple], _p(weights_transposed),
+        int(flags), _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
+def matmul_i8(lhs, rhs, out_offset, lhs_offset, rhs_offset, out_triple, *, flags=0, out=None, workspace=None,
+              status=None):
+    """MatMul (int8): lhs [M,K], rhs [K,N]."""
+    M, K = lhs.shape
+    N = rhs.shape[1]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int8, device=lhs.device)
+    ws = _workspace(workspace, i8_gemm_workspace_bytes(M, K, N), lhs.device)
+    check(_lib.lib().glowb200_matmul_i8(
+        _p(out), _p(lhs), _p(rhs), M, K, N, int(out_offset), int(lhs_offset), int(rhs_offset),
+        *[int(v) for v in out_triple], int(flags), _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
 class SlwsBatch:
     """A fixed set of tables of one kind and row width, pooled by ONE launch per request.
 

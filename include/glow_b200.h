@@ -120,6 +120,74 @@ int glowb200_embedding_bag_byte_rowwise_offsets(
     int use_fp16_accumulation, void *workspace, size_t workspace_bytes, int32_t *status,
     glowb200_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Int8 dense layers (tensor cores: tcgen05 kind::i8, int32 accumulation, Glow's integer
+ * requantisation in the epilogue; results are bit-identical to the CPU backend's)
+ * ------------------------------------------------------------------------------------- */
+
+/* quantizeScaleOffset32To8 (lib/Quantization/Base/Base.cpp:234-359): the integer pre-shift,
+ * post-shift and multiplier that stand in for a float rescale factor.  HOST function. */
+void glowb200_quantize_scale_offset_32to8(float scale, int32_t *pre, int32_t *post,
+                                          int32_t *integer_scale);
+
+/* The six per-row (per-output-channel) integer arrays of RowwiseQuantizedFullyConnected and
+ * ChannelwiseQuantizedConvolution, derived as lib/LLVMIRCodeGen/LLVMIRGen.cpp:2245-2251 and
+ * :2726-2730 do: matMulScale = in_scale * row_scales[j]; bias from bias_scales[j] / matMulScale
+ * (num_bias_scales is 1 for the FC's single bias scale, else n); output from
+ * matMulScale / out_scale.  HOST function over host arrays of n entries. */
+int glowb200_rowwise_requant_params(const float *row_scales, int64_t n, float in_scale,
+                                    const float *bias_scales, int64_t num_bias_scales,
+                                    float out_scale, int32_t *bias_pre, int32_t *bias_post,
+                                    int32_t *bias_scale, int32_t *out_pre, int32_t *out_post,
+                                    int32_t *out_scale_int);
+
+/* Hints in `flags`. */
+#define GLOWB200_FC_WEIGHT_OFFSETS_ZERO 1      /* every weight offset is 0: skips the input row sums */
+#define GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL 2   /* run the plain one-thread-per-output kernel          */
+
+/* Scratch bytes the three entry points below may need for an [M,K] x [N,K]^T problem. */
+size_t glowb200_i8_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N);
+
+/* sums[r] = sum_k matrix[r,k] (int8 [rows,K] -> int32 [rows]).  Lets a caller compute the row
+ * sums of constant weights once, at network-load time, and pass them as `weights_row_sums`. */
+int glowb200_i8_row_sums(const int8_t *matrix, int64_t rows, int64_t K, int32_t *sums,
+                         glowb200_stream_t stream);
+
+/* RowwiseQuantizedFullyConnected, int8 with int32 bias.
+ * Replaces libjit_rowwise_quantized_fc_i8_i32 (lib/LLVMIRCodeGen/libjit/libjit_matmul.cpp:425-436,
+ * body :284-316).  in [M,K]; weights [N,K] (not transposed: out = in * weights^T); bias,
+ * weights_offsets and the six per-row requantisation arrays have N entries and are derived by
+ * the caller exactly as lib/LLVMIRCodeGen/LLVMIRGen.cpp:2222-2320 derives them.
+ * weights_row_sums: optional int32 [N] from glowb200_i8_row_sums (NULL: computed per call). */
+int glowb200_rowwise_quantized_fc_i8_i32(
+    int8_t *out, const int8_t *in, const int8_t *weights, const int32_t *bias,
+    const int32_t *weights_offsets, const int32_t *bias_pre, const int32_t *bias_post,
+    const int32_t *bias_scale, const int32_t *out_pre, const int32_t *out_post,
+    const int32_t *out_scale, int64_t M, int64_t K, int64_t N, int32_t out_offset,
+    int32_t in_offset, int32_t bias_offset, const int32_t *weights_row_sums, int flags,
+    void *workspace, size_t workspace_bytes, int32_t *status, glowb200_stream_t stream);
+
+/* FullyConnected, int8 with int32 bias, one quantisation per tensor.
+ * Replaces libjit_fc_i8_i32 (libjit_matmul.cpp:395-407, body :254-280; scalars derived at
+ * LLVMIRGen.cpp:2161-2220).  in [M,K]; weights [K,N].  weights_transposed: optional [N,K] copy
+ * of the weights (a constant can be transposed once at load time); NULL: transposed per call
+ * into the workspace. */
+int glowb200_fc_i8_i32(int8_t *out, const int8_t *in, const int8_t *weights, const int32_t *bias,
+                       int64_t M, int64_t K, int64_t N, int32_t out_offset, int32_t in_offset,
+                       int32_t weights_offset, int32_t bias_offset, int32_t bias_pre,
+                       int32_t bias_post, int32_t bias_scale, int32_t out_pre, int32_t out_post,
+                       int32_t out_scale, const int8_t *weights_transposed, int flags,
+                       void *workspace, size_t workspace_bytes, int32_t *status,
+                       glowb200_stream_t stream);
+
+/* MatMul, int8.  Replaces libjit_matmul_i8 (libjit_matmul.cpp:353-371; scalars derived at
+ * LLVMIRGen.cpp:2098-2137).  lhs [M,K], rhs [K,N]. */
+int glowb200_matmul_i8(int8_t *out, const int8_t *lhs, const int8_t *rhs, int64_t M, int64_t K,
+                       int64_t N, int32_t out_offset, int32_t lhs_offset, int32_t rhs_offset,
+                       int32_t out_pre, int32_t out_post, int32_t out_scale, int flags,
+                       void *workspace, size_t workspace_bytes, int32_t *status,
+                       glowb200_stream_t stream);
+
 /* FusedRowwiseQuantizedSparseLengthsWeightedSum for callers that can neither allocate device
  * memory nor size a workspace per request.  (No counterpart in the reference: its CPU kernels
  * need no scratch.)  Think of a DeviceManager's request thread after every byte of HBM was
