@@ -45,6 +45,9 @@ def parse():
     ap.add_argument("--requests", type=int, default=4, help="distinct pre-generated batches rotated over the steps")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="slws", choices=["slws", "int8_fc"],
+                    help="slws: the headline gather-pool line (default); int8_fc: the rowwise int8 FC line")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary int8 FC measurement")
     return ap.parse_args()
 
 
@@ -193,6 +196,141 @@ def run_reference(args):
         "gpu_launches": 0}))
 
 
+def measured_peak_int8():
+    """No int8 figure is written by the driver: the denominator is twice the measured bf16
+    burst throughput (int8 issues at twice the bf16 rate on this tensor core)."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return 2.0 * float(json.load(open(p))["bf16_tflops"]), "2 x measured bf16 burst"
+        except Exception:
+            pass
+    return 2.0 * 1590.0, "2 x fallback bf16"
+
+
+FC_M, FC_K, FC_N = 2048, 4096, 4096
+
+
+def int8_fc_measure(torch, ops, dev, steps, warmup, seed=0):
+    """RowwiseQuantizedFullyConnected M2048 K4096 N4096 (second benchmark configuration):
+    device-resident TOPS, end-to-end TOPS (activations in from pinned host memory, int8 result
+    out), and the library int8 GEMM (torch._int_mm -> cuBLASLt, int32 result, no requantisation)
+    on the same operands for context.  Weight row sums are precomputed once, as a backend does
+    at network-load time."""
+    from glow_b200 import workloads
+    c = workloads.config2(M=FC_M, K=FC_K, N=FC_N, seed=workloads.MASTER_SEED + seed)
+    params = ops.rowwise_requant_params(c["w_scales"], c["in_scale"], c["bias_scale"], c["out_scale"])
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    p = [to(a) for a in params]
+    w, bias, wo = to(c["w"]), to(c["bias"]), to(c["w_offsets"])
+    rs = ops.i8_row_sums(w)
+    # activations: several distinct batches so consecutive steps do not re-read an L2-resident input
+    host_in = [torch.from_numpy(np.random.default_rng(seed + i).integers(-128, 128, (FC_M, FC_K), dtype=np.int8)).pin_memory()
+               for i in range(4)]
+    dev_in = [h.to(dev) for h in host_in]
+    out = torch.empty((FC_M, FC_N), dtype=torch.int8, device=dev)
+    out_host = torch.empty((FC_M, FC_N), dtype=torch.int8).pin_memory()
+    stage = torch.empty((FC_M, FC_K), dtype=torch.int8, device=dev)
+    ws = torch.empty(ops.i8_gemm_workspace_bytes(FC_M, FC_K, FC_N), dtype=torch.uint8, device=dev)
+    status = ops.new_status(dev)
+
+    def run(x):
+        ops.rowwise_quantized_fc(x, w, bias, wo, p[:3], p[3:], c["out_offset"], c["in_offset"], c["bias_offset"],
+                                 weights_row_sums=rs, flags=ops.FC_WEIGHT_OFFSETS_ZERO, out=out, workspace=ws,
+                                 status=status)
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(n):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    for i in range(max(3, warmup)):
+        run(dev_in[i % 4])
+    ms = timed(lambda i: run(dev_in[i % 4]), steps)
+
+    def e2e(i):
+        stage.copy_(host_in[i % 4], non_blocking=True)
+        run(stage)
+        out_host.copy_(out, non_blocking=True)
+
+    for i in range(2):
+        e2e(i)
+    e2e_steps = max(3, min(steps, 20))
+    e2e_ms = timed(e2e, e2e_steps)
+    assert int(status.item()) == 0
+    ops_per_step = 2.0 * FC_M * FC_N * FC_K
+    lib_tops = None
+    try:
+        wt = w.t()
+        for i in range(3):
+            torch._int_mm(dev_in[i % 4], wt)
+        lib_ms = timed(lambda i: torch._int_mm(dev_in[i % 4], wt), steps)
+        lib_tops = ops_per_step / (lib_ms * 1e-3) / 1e12
+    except Exception:
+        pass
+    return {"ms": ms, "tops": ops_per_step / (ms * 1e-3) / 1e12, "e2e_ms": e2e_ms,
+            "e2e_tops": ops_per_step / (e2e_ms * 1e-3) / 1e12, "e2e_steps": e2e_steps,
+            "h2d": FC_M * FC_K, "d2h": FC_M * FC_N, "library_int8_gemm_tops": lib_tops, "ops": ops_per_step}
+
+
+def fc_config():
+    return {"workload": "RowwiseQuantizedFullyConnected int8: M=2048 K=4096 N=4096, activations U[-128,127] "
+                        "(scale 0.05, offset 3), weights U[-127,127] with per-row scales U(0.001,0.02) and zero "
+                        "offsets, int32 bias U[-2^16,2^16] (scale 5e-4), int8 result (scale 0.5, offset 0), "
+                        "integer requantisation fused in the epilogue; weight row sums precomputed",
+            "M": FC_M, "K": FC_K, "N": FC_N,
+            "l2_policy": "four distinct activation batches rotated; weights (16 MB) stay L2-resident as in serving"}
+
+
+def run_int8_fc_line(args):
+    """--workload int8_fc: the dense line.  At N > 1 every rank runs its own batch (batch-sharded
+    replicas, no collective): weak scaling."""
+    import torch
+    import torch.distributed as dist
+    from glow_b200 import ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        dist.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    r = int8_fc_measure(torch, ops, dev, args.steps, args.warmup, seed=rank)
+    t_end = time.time() + 1.0
+    while len(sampler.lines) < 8 and time.time() < t_end:
+        time.sleep(0.05)
+    clocks = sampler.stop()
+    times = torch.tensor([r["ms"], r["e2e_ms"]], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(times[0]), float(times[1])
+    if rank == 0:
+        peak, src = measured_peak_int8()
+        tops = world * r["ops"] / (ms * 1e-3) / 1e12
+        line = {"metric": "int8_fc_tops", "value": tops, "unit": "TOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "s8 x s8 -> s32", "data": "synthetic", "config": fc_config(),
+                "roofline": {"bound": "tensor", "achieved": r["tops"], "peak": peak, "unit": "TOP/s",
+                             "frac": r["tops"] / peak, "peak_source": src, "nominal_dense_int8_tops": 4500.0,
+                             "library_int8_gemm_tops": r["library_int8_gemm_tops"], "traffic": None,
+                             "kernel": "i8_gemm_requant_kernel<256,4>", "launch_us": r["ms"] * 1e3},
+                "e2e": {"value": world * r["ops"] / (e2e_ms * 1e-3) / 1e12, "unit": "TOP/s",
+                        "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"], "steps": r["e2e_steps"],
+                        "ms_per_step": e2e_ms},
+                "gpu_launches": args.steps, "clocks": clocks}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def workload_config(T):
     return {"workload": "FRWQ-SLWS uint8 fused rows (config 1 law): %d tables x 1,000,000 rows x 64 cols "
                         "(72 B rows), 1024 bags/table, lengths clamp(Poisson(32),1,128), int64 indices, fp32 "
@@ -205,6 +343,8 @@ def main():
     args = parse()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "int8_fc":
+        return run_int8_fc_line(args)
 
     import torch
     import torch.distributed as dist
@@ -349,6 +489,17 @@ def main():
             "gpu_launches": 2 * args.steps,
             "clocks": clocks,
         }
+        if world == 1 and not args.no_extras:
+            # secondary metric of the same benchmark definition: int8 FC throughput
+            del batches, e2e_batches
+            fc = int8_fc_measure(torch, ops, dev, max(10, min(args.steps, 50)), 3)
+            ipeak, isrc = measured_peak_int8()
+            line["extras"] = {"int8_fc": {
+                "metric": "int8_fc_tops", "value": fc["tops"], "unit": "TOP/s", "us_per_launch": fc["ms"] * 1e3,
+                "e2e_value": fc["e2e_tops"], "config": fc_config(),
+                "roofline": {"bound": "tensor", "achieved": fc["tops"], "peak": ipeak, "frac": fc["tops"] / ipeak,
+                             "peak_source": isrc, "nominal_dense_int8_tops": 4500.0,
+                             "library_int8_gemm_tops": fc["library_int8_gemm_tops"]}}}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             S = min(T, max(threads, 16))
