@@ -9,10 +9,11 @@
 //   sum_k (A-a0)(B-b0) = sum_k A*B - a0*rowsum(B_j) - b0_j*rowsum(A_i) + K*a0*b0_j .
 // The epilogue then applies Glow's integer requantisation (libjit_scale, libjit_clip_i8).
 //
-// One CTA computes a 128 x BLOCK_N tile.  Warp 0 feeds shared memory with TMA (128-byte
-// swizzled K-major tiles of 128 bytes of K), warp 1 issues the MMAs and owns the tensor-memory
-// allocation, warps 2-5 build the tile's per-column constants while the main loop runs and
-// then drain the accumulators (tcgen05.ld), requantise and store int8.
+// Persistent CTAs (one per SM) walk 128 x BLOCK_N output tiles.  Warp 0 feeds shared memory
+// with TMA (128-byte swizzled K-major tiles of 128 bytes of K), warp 1 issues the MMAs and owns
+// the tensor-memory allocation, warps 2-5 build each tile's per-column constants and drain its
+// accumulators (tcgen05.ld), requantise and store int8 -- overlapped with the next tile's main
+// loop through two accumulator buffers in tensor memory.
 //
 // Every wait on an mbarrier is bounded: when it runs out the kernel raises
 // GLOWB200_STATUS_WAIT_TIMEOUT, all roles leave their loops, tensor memory is released and the
@@ -181,6 +182,10 @@ struct GemmSmem {
   static constexpr int kTotal = kTileBytes + kColBytes + 256 /*barriers*/ + 1024 /*alignment slack*/;
 };
 
+// Persistent: gridDim.x CTAs walk the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...
+// (column-tile-major, so CTAs running together share weight tiles in L2).  The accumulators are
+// double-buffered in tensor memory: while the epilogue warps drain tile i, the MMA warp is
+// already accumulating tile i+1 into the other buffer.
 template <int BLOCK_N, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -192,21 +197,27 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   ColParams *cols = reinterpret_cast<ColParams *>(smem + S::kTileBytes);
   uint64_t *full = reinterpret_cast<uint64_t *>(smem + S::kTileBytes + S::kColBytes);
   uint64_t *empty = full + STAGES;
-  uint64_t *acc_ready = empty + STAGES;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+  uint64_t *acc_full = empty + STAGES;   // [2]
+  uint64_t *acc_empty = acc_full + 2;    // [2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kBlockM, n0 = blockIdx.x * BLOCK_N;
+  const int m_tiles = (p.M + kBlockM - 1) / kBlockM, n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const int tiles = m_tiles * n_tiles;
   const int k_blocks = (p.K + kBlockK - 1) / kBlockK;
-  constexpr uint32_t kTmemCols = BLOCK_N < 32 ? 32 : BLOCK_N;  // power of two >= 32
+  constexpr uint32_t kAccCols = BLOCK_N < 32 ? 32 : BLOCK_N;
+  constexpr uint32_t kTmemCols = 2 * kAccCols;  // a power of two >= 64
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(acc_ready, 1);
+    for (int b = 0; b < 2; b++) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -222,73 +233,108 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      for (int kb = 0; kb < k_blocks; kb++) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1, abort_flag)) break;
-        uint8_t *a_dst = smem + s * S::kStageBytes;
-        uint8_t *b_dst = a_dst + S::kABytes;
-        mbar_expect_tx(&full[s], S::kStageBytes);
-        tma_load_2d(a_dst, &map_a, kb * kBlockK, m0, &full[s]);
-        tma_load_2d(b_dst, &map_b, kb * kBlockK, n0, &full[s]);
+      int it = 0;  // k-blocks issued so far, over all tiles of this CTA
+      bool live = true;
+      for (int t = blockIdx.x; t < tiles && live; t += gridDim.x) {
+        const int m0 = (t % m_tiles) * kBlockM, n0 = (t / m_tiles) * BLOCK_N;
+        for (int kb = 0; kb < k_blocks; kb++, it++) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag)) { live = false; break; }
+          uint8_t *a_dst = smem + s * S::kStageBytes;
+          uint8_t *b_dst = a_dst + S::kABytes;
+          mbar_expect_tx(&full[s], S::kStageBytes);
+          tma_load_2d(a_dst, &map_a, kb * kBlockK, m0, &full[s]);
+          tma_load_2d(b_dst, &map_b, kb * kBlockK, n0, &full[s]);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_i8(kBlockM, BLOCK_N);
-      for (int kb = 0; kb < k_blocks; kb++) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(&full[s], (kb / STAGES) & 1, abort_flag)) break;
+      int it = 0, lt = 0;
+      bool live = true;
+      for (int t = blockIdx.x; t < tiles && live; t += gridDim.x, lt++) {
+        const int buf = lt & 1;
+        // wait until the epilogue has drained this buffer (passes at once on its first use)
+        if (!mbar_wait(&acc_empty[buf], ((lt >> 1) & 1) ^ 1, abort_flag)) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
-        const uint32_t b_addr = a_addr + S::kABytes;
-        const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
+        const uint32_t d_tmem = tmem_base + (uint32_t)buf * kAccCols;
+        for (int kb = 0; kb < k_blocks; kb++, it++) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { live = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
+          const uint32_t b_addr = a_addr + S::kABytes;
+          const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
 #pragma unroll
-        for (int k = 0; k < kBlockK / kUmmaK; k++) {
-          // advancing K inside the swizzle atom = advancing the start address by 32 bytes
-          umma_i8(tmem_base, a_desc + (uint64_t)(k * (kUmmaK >> 4)), b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc,
-                  (kb | k) != 0);
+          for (int k = 0; k < kBlockK / kUmmaK; k++) {
+            // advancing K inside the swizzle atom = advancing the start address by 32 bytes
+            umma_i8(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)), b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc,
+                    (kb | k) != 0);
+          }
+          umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
         }
-        umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+        if (live) umma_commit(&acc_full[buf]);  // this tile's accumulators are complete
       }
-      umma_commit(acc_ready);    // accumulators complete
     }
   } else {
     // ---------------- epilogue: warps 2..5 ----------------
     const int et = threadIdx.x - 64;  // 0..127
-    // (1) per-column constants of this tile, while the main loop runs
-    for (int c = et; c < BLOCK_N; c += 128) {
-      const int j = n0 + c;
-      ColParams cp = {0, 0, 0, 0};
-      if (j < p.N) {
-        const ColQuant q = col_quant(p, j);
-        int32_t term = 0;
-        if (p.bias) term = scale32(p.bias[j] - p.bias_offset, q.bias_pre, q.bias_post, q.bias_scale, 0);
-        const uint32_t corr = (uint32_t)term - (uint32_t)p.a_offset * (uint32_t)p.b_row_sums[j] +
-                              (uint32_t)p.K * (uint32_t)p.a_offset * (uint32_t)q.b_off;
-        cp.c = (int32_t)corr;
-        cp.b_off = q.b_off;
-        cp.shifts = q.out_pre | (q.out_post << 8);
-        cp.scale = q.out_scale;
+    const int quarter = warp & 3;     // TMEM lane quarter this warp may read
+    const bool vec_ok = ((p.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    int lt = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, lt++) {
+      const int m0 = (t % m_tiles) * kBlockM, n0 = (t / m_tiles) * BLOCK_N;
+      const int buf = lt & 1;
+      // (1) per-column constants of this tile (the main loop of this or the next tile is running)
+      for (int c = et; c < BLOCK_N; c += 128) {
+        const int j = n0 + c;
+        ColParams cp = {0, 0, 0, 0};
+        if (j < p.N) {
+          const ColQuant q = col_quant(p, j);
+          int32_t term = 0;
+          if (p.bias) term = scale32(p.bias[j] - p.bias_offset, q.bias_pre, q.bias_post, q.bias_scale, 0);
+          const uint32_t corr = (uint32_t)term - (uint32_t)p.a_offset * (uint32_t)p.b_row_sums[j] +
+                                (uint32_t)p.K * (uint32_t)p.a_offset * (uint32_t)q.b_off;
+          cp.c = (int32_t)corr;
+          cp.b_off = q.b_off;
+          cp.shifts = q.out_pre | (q.out_post << 8);
+          cp.scale = q.out_scale;
+        }
+        cols[c] = cp;
       }
-      cols[c] = cp;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
-    // (2) drain the accumulators
-    const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
-    const int row = m0 + quarter * 32 + lane;
-    const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0, abort_flag));
-    tc_fence_after();
-    if (ok) {
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
+      // (2) drain the accumulators of this tile
+      const int row = m0 + quarter * 32 + lane;
+      // All 128 epilogue threads agree on the outcome of the (bounded) wait through a reducing
+      // barrier, so either all of them drain the tile or all of them leave the loop.
+      const uint32_t mine = mbar_wait(&acc_full[buf], (lt >> 1) & 1, abort_flag) ? 1u : 0u;
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.u32 q, %1, 0;\n\t"
+          "barrier.cta.red.and.pred p, 1, 128, q;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(mine)
+          : "memory");
+      tc_fence_after();
+      if (!ok) break;
       const int32_t a_sum = (p.a_row_sums && row < p.M) ? p.a_row_sums[row] : 0;
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kAccCols;
       int8_t *out_row = p.out + (size_t)row * p.N + n0;
-      const bool vec_ok = ((p.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
 #pragma unroll 1
       for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
         uint32_t acc[32];
         tmem_ld_32x32b_x32(lane_addr + (uint32_t)c0, acc);
         tmem_ld_wait();
+        if (c0 + 32 >= BLOCK_N) {
+          // everything this warp needs from the buffer is in registers: hand it back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
         uint32_t packed[8];
 #pragma unroll
         for (int i = 0; i < 32; i++) {
@@ -309,6 +355,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           }
         }
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // cols[] is rewritten for the next tile
     }
   }
 
@@ -426,8 +473,9 @@ int launch_tile_kernel(const CUtensorMap &ma, const CUtensorMap &mb, const GemmP
   // per device and cheap: set on every launch rather than tracked
   GLOWB200_CUDA_OK(cudaFuncSetAttribute(i8_gemm_requant_kernel<BLOCK_N, STAGES>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-  dim3 grid((p.N + BLOCK_N - 1) / BLOCK_N, (p.M + kBlockM - 1) / kBlockM);
-  i8_gemm_requant_kernel<BLOCK_N, STAGES><<<grid, kGemmThreads, S::kTotal, s>>>(ma, mb, p);
+  const int tiles = ((p.N + BLOCK_N - 1) / BLOCK_N) * ((p.M + kBlockM - 1) / kBlockM);
+  const int sms = sm_count();
+  i8_gemm_requant_kernel<BLOCK_N, STAGES><<<tiles < sms ? tiles : sms, kGemmThreads, S::kTotal, s>>>(ma, mb, p);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }
