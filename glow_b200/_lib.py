@@ -41,6 +41,20 @@ SIGNATURES = {
         _int, [_vp] * 4 + [_i64] * 3 + [_i32] * 10 + [_vp, _int, _vp, _sz, _vp, _vp]),
     "glowb200_matmul_i8": (
         _int, [_vp] * 3 + [_i64] * 3 + [_i32] * 6 + [_int, _vp, _sz, _vp, _vp]),
+    "glowb200_conv2d_workspace_bytes": (_sz, [_vp] * 6 + [_i64, _vp]),
+    "glowb200_channelwise_quantized_conv2d_i8_i32": (
+        _int, [_vp] * 10 + [_i64, _vp, _i32, _i32] + [_vp] * 8 + [_i32, _vp, _vp, _int, _vp, _sz, _vp, _vp]),
+    "glowb200_conv2d_i8_i32": (
+        _int, [_vp] * 10 + [_i64] + [_i32] * 10 + [_vp, _i32, _vp, _int, _vp, _sz, _vp, _vp]),
+    "glowb200_element_add_i8": (_int, [_vp, _vp, _vp, _i64] + [_i32] * 9 + [_vp]),
+    "glowb200_element_relu_i8": (_int, [_vp, _vp, _i64] + [_i32] * 5 + [_vp]),
+    "glowb200_element_maxsplat_i8": (_int, [_vp, _vp, _i64, _i32, _vp]),
+    "glowb200_element_rescale_i8": (_int, [_vp, _vp, _i64] + [_i32] * 5 + [_vp]),
+    "glowb200_element_quantize_i8": (_int, [_vp, _vp, _i64, _f32, _i32, _vp]),
+    "glowb200_element_dequantize_i8": (_int, [_vp, _vp, _i64, _f32, _i32, _vp]),
+    "glowb200_max_pool_i8": (_int, [_vp] * 7 + [_i32, _vp]),
+    "glowb200_avg_pool_i8": (_int, [_vp] * 7 + [_int] + [_i32] * 5 + [_vp]),
+    "glowb200_transpose": (_int, [_vp, _vp, _vp, _vp, _int, _int, _vp]),
     "glowb200_embedding_bag_byte_rowwise_offsets": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _sz, _vp,
                _vp]),

@@ -1,0 +1,280 @@
+// Int8 2-D convolution (NHWC, filter [outC, kH, kW, inC/group]) for Glow's
+// ChannelwiseQuantizedConvolution and quantized Convolution.
+//
+// group == 1: the convolution is the int8 contraction of qgemm.cu over an im2col matrix
+//   A[n*OH*OW + oh*OW + ow, (kh*KW + kw)*C + c] = X[n, oh*SH - PT + kh*DH, ow*SW - PL + kw*DW, c]
+// whose result rows are exactly the NHWC output.  Taps outside the image are skipped by the
+// reference (libjit_conv.cpp:209-212), i.e. they contribute (x - inOffset) = 0: im2col writes
+// inOffset there.  The filter [outC, kH*kW*C] already is the K-major right-hand side.  A 1x1,
+// stride-1, unpadded convolution needs no im2col at all.  When kH*kW*C is not a multiple of 16
+// both operands are padded with zeros along K (zeros add nothing to the raw products or to the
+// row sums; the offset correction uses the true K).
+// group > 1 (and anything else unusual): a direct kernel, one thread per output, the
+// reference's loop nest as written.
+#include "common.cuh"
+#include "qgemm.cuh"
+
+namespace glowb200 {
+namespace {
+
+struct ConvGeom {
+  int N, H, W, C, OH, OW, OC, KH, KW, SH, SW, PT, PL, DH, DW, G;
+};
+
+// one thread per 16-byte chunk of the im2col matrix (C a multiple of 16: a chunk never
+// straddles two taps)
+__global__ void __launch_bounds__(256) im2col_i8_vec_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ a,
+                                                             const __grid_constant__ ConvGeom g, int Kpad, int pad_word) {
+  const int chunks_per_row = Kpad >> 4;
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * chunks_per_row;
+  const int c_chunks = g.C >> 4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / chunks_per_row;
+    const int ch = (int)(i - row * chunks_per_row);
+    const int tap = ch / c_chunks, cc = ch - tap * c_chunks;
+    int4 v = make_int4(0, 0, 0, 0);
+    if (tap < g.KH * g.KW) {
+      const int kh = tap / g.KW, kw = tap - kh * g.KW;
+      const int ow = (int)(row % g.OW);
+      const int64_t r2 = row / g.OW;
+      const int oh = (int)(r2 % g.OH), n = (int)(r2 / g.OH);
+      const int ih = oh * g.SH - g.PT + kh * g.DH, iw = ow * g.SW - g.PL + kw * g.DW;
+      if (ih >= 0 && iw >= 0 && ih < g.H && iw < g.W)
+        v = *reinterpret_cast<const int4 *>(x + (((int64_t)n * g.H + ih) * g.W + iw) * g.C + cc * 16);
+      else
+        v = make_int4(pad_word, pad_word, pad_word, pad_word);
+    }
+    *reinterpret_cast<int4 *>(a + row * Kpad + ch * 16) = v;
+  }
+}
+
+// any channel count: one thread per byte
+__global__ void __launch_bounds__(256) im2col_i8_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ a,
+                                                         const __grid_constant__ ConvGeom g, int K, int Kpad, int8_t pad) {
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * Kpad;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / Kpad;
+    const int k = (int)(i - row * Kpad);
+    int8_t v = 0;
+    if (k < K) {
+      const int tap = k / g.C, c = k - tap * g.C;
+      const int kh = tap / g.KW, kw = tap - kh * g.KW;
+      const int ow = (int)(row % g.OW);
+      const int64_t r2 = row / g.OW;
+      const int oh = (int)(r2 % g.OH), n = (int)(r2 / g.OH);
+      const int ih = oh * g.SH - g.PT + kh * g.DH, iw = ow * g.SW - g.PL + kw * g.DW;
+      v = (ih >= 0 && iw >= 0 && ih < g.H && iw < g.W) ? x[(((int64_t)n * g.H + ih) * g.W + iw) * g.C + c] : pad;
+    }
+    a[i] = v;
+  }
+}
+
+// [rows, K] -> [rows, Kpad], zero padded
+__global__ void __launch_bounds__(256) pad_rows_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int rows,
+                                                           int K, int Kpad) {
+  const int64_t total = (int64_t)rows * Kpad;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / Kpad;
+    const int k = (int)(i - r * Kpad);
+    out[i] = k < K ? in[r * K + k] : (int8_t)0;
+  }
+}
+
+// The reference's loop nest (libjit_conv.cpp:151-239 / :49-147), one thread per output element.
+__global__ void __launch_bounds__(256) conv2d_i8_direct_kernel(const int8_t *__restrict__ x, const int8_t *__restrict__ f,
+                                                                const __grid_constant__ ConvGeom g,
+                                                                const __grid_constant__ GemmParams p) {
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * g.OC;
+  const int icg = g.C / g.G, ocg = g.OC / g.G;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int d = (int)(i % g.OC);
+    int64_t r = i / g.OC;
+    const int ow = (int)(r % g.OW);
+    r /= g.OW;
+    const int oh = (int)(r % g.OH), n = (int)(r / g.OH);
+    const int grp = d / ocg;
+    const ColQuant q = col_quant(p, d);
+    uint32_t sum = (uint32_t)scale32(p.bias[d] - (p.bias_offsets ? p.bias_offsets[d] : p.bias_offset), q.bias_pre,
+                                     q.bias_post, q.bias_scale, 0);
+    for (int kh = 0; kh < g.KH; kh++)
+      for (int kw = 0; kw < g.KW; kw++) {
+        const int ih = oh * g.SH - g.PT + kh * g.DH, iw = ow * g.SW - g.PL + kw * g.DW;
+        if (ih < 0 || iw < 0 || ih >= g.H || iw >= g.W) continue;
+        const int8_t *xp = x + (((int64_t)n * g.H + ih) * g.W + iw) * g.C + grp * icg;
+        const int8_t *fp = f + (((int64_t)d * g.KH + kh) * g.KW + kw) * icg;
+        for (int c = 0; c < icg; c++) sum += (uint32_t)(((int32_t)fp[c] - q.b_off) * ((int32_t)xp[c] - p.a_offset));
+      }
+    p.out[i] = (int8_t)clip_i8(activation_i32(scale32((int32_t)sum, q.out_pre, q.out_post, q.out_scale, p.out_offset), p));
+  }
+}
+
+int geom_from_dims(ConvGeom &g, const int64_t *out_dims, const int64_t *in_dims, const int64_t *filter_dims,
+                   const int64_t *kernels, const int64_t *strides, const int64_t *pads, int64_t group,
+                   const int64_t *dilation) {
+  GLOWB200_REQUIRE(out_dims && in_dims && filter_dims && kernels && strides && pads && dilation, "NULL shape array");
+  for (int i = 0; i < 4; i++)
+    GLOWB200_REQUIRE(out_dims[i] >= 0 && in_dims[i] >= 0 && filter_dims[i] >= 0 && out_dims[i] < (1ll << 31) &&
+                         in_dims[i] < (1ll << 31) && filter_dims[i] < (1ll << 31), "dimension out of range");
+  g.N = (int)in_dims[0]; g.H = (int)in_dims[1]; g.W = (int)in_dims[2]; g.C = (int)in_dims[3];
+  g.OH = (int)out_dims[1]; g.OW = (int)out_dims[2]; g.OC = (int)out_dims[3];
+  g.KH = (int)kernels[0]; g.KW = (int)kernels[1];
+  g.SH = (int)strides[0]; g.SW = (int)strides[1];
+  g.PT = (int)pads[0]; g.PL = (int)pads[1];
+  g.DH = (int)dilation[0]; g.DW = (int)dilation[1];
+  g.G = (int)group;
+  GLOWB200_REQUIRE(out_dims[0] == in_dims[0], "batch sizes of input and output differ");
+  GLOWB200_REQUIRE(g.G >= 1 && g.C % g.G == 0 && g.OC % g.G == 0, "channels not divisible by the group count");
+  GLOWB200_REQUIRE(filter_dims[0] == g.OC && filter_dims[1] == g.KH && filter_dims[2] == g.KW &&
+                       filter_dims[3] == g.C / g.G, "filter dims do not match [outC, kH, kW, inC/group]");
+  GLOWB200_REQUIRE(g.SH >= 1 && g.SW >= 1 && g.DH >= 1 && g.DW >= 1 && g.KH >= 1 && g.KW >= 1, "bad stride/dilation/kernel");
+  return GLOWB200_OK;
+}
+
+struct ConvPlan {
+  bool direct;       // direct kernel (groups, empty)
+  bool need_im2col;  // else the input itself is the left-hand side
+  int K, Kpad;
+  int64_t M;
+  size_t a_bytes, f_bytes, core_bytes;
+};
+
+ConvPlan plan_conv(const ConvGeom &g, bool force_direct) {
+  ConvPlan pl{};
+  pl.M = (int64_t)g.N * g.OH * g.OW;
+  pl.K = g.KH * g.KW * g.C;
+  pl.Kpad = (pl.K + 15) / 16 * 16;
+  pl.direct = force_direct || g.G != 1 || pl.M >= (1ll << 31) || pl.K >= (1 << 24);
+  const bool pointwise = g.KH == 1 && g.KW == 1 && g.SH == 1 && g.SW == 1 && g.PT == 0 && g.PL == 0 && g.OH == g.H &&
+                         g.OW == g.W && (g.C % 16) == 0;
+  pl.need_im2col = !pl.direct && !pointwise;
+  pl.a_bytes = pl.need_im2col ? align_up((size_t)pl.M * pl.Kpad, 256) : 0;
+  pl.f_bytes = (!pl.direct && pl.Kpad != pl.K) ? align_up((size_t)g.OC * pl.Kpad, 256) : 0;
+  pl.core_bytes = pl.direct ? 0 : i8_gemm_core_workspace_bytes(pl.M, g.OC);
+  return pl;
+}
+
+int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeom &g, const int32_t *filter_row_sums,
+             int flags, void *workspace, size_t workspace_bytes, cudaStream_t s) {
+  const int64_t outputs = (int64_t)g.N * g.OH * g.OW * g.OC;
+  if (outputs == 0) return GLOWB200_OK;
+  const ConvPlan pl = plan_conv(g, (flags & GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL) != 0);
+  if (pl.direct) {
+    const int64_t blocks = (outputs + 255) / 256;
+    conv2d_i8_direct_kernel<<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, s>>>(in, filter, g, p);
+    GLOWB200_CUDA_OK(cudaGetLastError());
+    return GLOWB200_OK;
+  }
+  const size_t need = pl.a_bytes + pl.f_bytes + pl.core_bytes;
+  if (workspace == nullptr || workspace_bytes < need)
+    return set_error(GLOWB200_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  GLOWB200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+  uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
+  const int8_t *a = in;
+  if (pl.need_im2col) {
+    int8_t *abuf = reinterpret_cast<int8_t *>(ws);
+    const int8_t pad = (int8_t)p.a_offset;
+    if ((g.C % 16) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+      const int64_t chunks = pl.M * (pl.Kpad >> 4);
+      const int64_t blocks = (chunks + 255) / 256;
+      const uint32_t b = (uint8_t)pad;
+      im2col_i8_vec_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(
+          in, abuf, g, pl.Kpad, (int)(b | (b << 8) | (b << 16) | (b << 24)));
+    } else {
+      const int64_t blocks = (pl.M * pl.Kpad + 255) / 256;
+      im2col_i8_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(in, abuf, g, pl.K, pl.Kpad, pad);
+    }
+    GLOWB200_CUDA_OK(cudaGetLastError());
+    a = abuf;
+  }
+  const int8_t *b = filter;
+  if (pl.f_bytes) {
+    int8_t *fbuf = reinterpret_cast<int8_t *>(ws + pl.a_bytes);
+    const int64_t blocks = ((int64_t)g.OC * pl.Kpad + 255) / 256;
+    pad_rows_i8_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, s>>>(filter, fbuf, g.OC, pl.K, pl.Kpad);
+    GLOWB200_CUDA_OK(cudaGetLastError());
+    b = fbuf;
+    filter_row_sums = nullptr;  // recomputed over the padded copy (same values; keeps one code path)
+  }
+  p.M = (int)pl.M;
+  p.N = g.OC;
+  p.K = pl.Kpad;
+  p.k_corr = pl.K;
+  return run_gemm(p, a, b, filter_row_sums, (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) != 0, 0, ws + pl.a_bytes + pl.f_bytes,
+                  pl.core_bytes, s);
+}
+
+}  // namespace
+}  // namespace glowb200
+
+using namespace glowb200;
+
+extern "C" size_t glowb200_conv2d_workspace_bytes(const int64_t *out_dims, const int64_t *in_dims,
+                                                  const int64_t *filter_dims, const int64_t *kernels,
+                                                  const int64_t *strides, const int64_t *pads, int64_t group,
+                                                  const int64_t *dilation) {
+  ConvGeom g;
+  if (geom_from_dims(g, out_dims, in_dims, filter_dims, kernels, strides, pads, group, dilation) != GLOWB200_OK) return 0;
+  const ConvPlan pl = plan_conv(g, false);
+  return pl.a_bytes + pl.f_bytes + pl.core_bytes;
+}
+
+extern "C" int glowb200_channelwise_quantized_conv2d_i8_i32(
+    int8_t *out, const int8_t *in, const int8_t *filter, const int32_t *bias, const int64_t *out_dims,
+    const int64_t *in_dims, const int64_t *filter_dims, const int64_t *kernels, const int64_t *strides,
+    const int64_t *pads, int64_t group, const int64_t *dilation, int32_t out_offset, int32_t in_offset,
+    const int32_t *filter_offsets, const int32_t *bias_offsets, const int32_t *bias_pre, const int32_t *bias_post,
+    const int32_t *bias_scale, const int32_t *out_pre, const int32_t *out_post, const int32_t *out_scale, int32_t act_type,
+    const int32_t *act_args, const int32_t *filter_row_sums, int flags, void *workspace, size_t workspace_bytes,
+    int32_t *status, glowb200_stream_t stream) {
+  ConvGeom g;
+  if (int rc = geom_from_dims(g, out_dims, in_dims, filter_dims, kernels, strides, pads, group, dilation)) return rc;
+  if ((int64_t)g.N * g.OH * g.OW * g.OC == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(out && in && filter && bias && filter_offsets && bias_offsets && bias_pre && bias_post && bias_scale &&
+                       out_pre && out_post && out_scale, "NULL tensor pointer");
+  GLOWB200_REQUIRE(act_type >= 0 && act_type <= 5 && act_type != 3 && act_type != 4,
+                   "fused activation %d is not defined for quantized convolution", act_type);
+  GLOWB200_REQUIRE(act_type == 0 || act_type == 1 || act_args != nullptr, "activation arguments missing");
+  GemmParams p{};
+  p.out = out;
+  p.bias = bias;
+  p.b_offsets = filter_offsets;
+  p.bias_offsets = bias_offsets;
+  p.bias_pre = bias_pre; p.bias_post = bias_post; p.bias_scale = bias_scale;
+  p.out_pre = out_pre; p.out_post = out_post; p.out_scale = out_scale;
+  p.status = status;
+  p.a_offset = in_offset; p.out_offset = out_offset;
+  p.act_type = act_type;
+  if (act_type == 2) { p.act_args[0] = act_args[0]; p.act_args[1] = act_args[1]; }
+  if (act_type == 5) { p.act_args[0] = act_args[0]; p.act_args[1] = act_args[1]; p.act_args[2] = act_args[2]; }
+  return run_conv(p, in, filter, g, filter_row_sums, flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int glowb200_conv2d_i8_i32(
+    int8_t *out, const int8_t *in, const int8_t *filter, const int32_t *bias, const int64_t *out_dims,
+    const int64_t *in_dims, const int64_t *filter_dims, const int64_t *kernels, const int64_t *strides,
+    const int64_t *pads, int64_t group, int32_t out_offset, int32_t in_offset, int32_t filter_offset, int32_t bias_offset,
+    int32_t bias_pre, int32_t bias_post, int32_t bias_scale, int32_t out_pre, int32_t out_post, int32_t out_scale,
+    const int64_t *dilation, int32_t act_type, const int32_t *act_args, int flags, void *workspace, size_t workspace_bytes,
+    int32_t *status, glowb200_stream_t stream) {
+  ConvGeom g;
+  if (int rc = geom_from_dims(g, out_dims, in_dims, filter_dims, kernels, strides, pads, group, dilation)) return rc;
+  if ((int64_t)g.N * g.OH * g.OW * g.OC == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(out && in && filter && bias, "NULL tensor pointer");
+  GLOWB200_REQUIRE(act_type >= 0 && act_type <= 5 && act_type != 3 && act_type != 4,
+                   "fused activation %d is not defined for quantized convolution", act_type);
+  GLOWB200_REQUIRE(act_type == 0 || act_type == 1 || act_args != nullptr, "activation arguments missing");
+  GemmParams p{};
+  p.out = out;
+  p.bias = bias;
+  p.status = status;
+  p.a_offset = in_offset; p.out_offset = out_offset; p.bias_offset = bias_offset;
+  p.uniform = 1;
+  p.u_b_offset = filter_offset;
+  p.u_bias_pre = bias_pre; p.u_bias_post = bias_post; p.u_bias_scale = bias_scale;
+  p.u_out_pre = out_pre; p.u_out_post = out_post; p.u_out_scale = out_scale;
+  p.act_type = act_type;
+  if (act_type == 2) { p.act_args[0] = act_args[0]; p.act_args[1] = act_args[1]; }
+  if (act_type == 5) { p.act_args[0] = act_args[0]; p.act_args[1] = act_args[1]; p.act_args[2] = act_args[2]; }
+  if (filter_offset == 0) flags |= GLOWB200_FC_WEIGHT_OFFSETS_ZERO;
+  return run_conv(p, in, filter, g, nullptr, flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,287 @@
+// The int8 glue operators of a quantized network: element-wise add / relu / max-with-constant
+// / rescale, quantize, dequantize, max- and average-pooling, and NCHW <-> NHWC transposes.
+// All of them stream their operands once; each kernel restates one libjit kernel.
+#include "common.cuh"
+
+namespace glowb200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+inline unsigned grid_for(int64_t work_items) {
+  const int64_t blocks = (work_items + kThreads - 1) / kThreads;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  return (unsigned)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+}
+
+struct Triple { int32_t pre, post, scale; };
+
+// libjit_element_add_kernel_i8 (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED, libjit.cpp:1593-1603)
+__global__ void __launch_bounds__(kThreads) add_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
+                                                          const int8_t *__restrict__ rhs, int64_t n, int32_t dst_off,
+                                                          int32_t lhs_off, int32_t rhs_off, Triple lt, Triple rt) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t l = scale32((int32_t)lhs[i] - lhs_off, lt.pre, lt.post, lt.scale, 0);
+    const int32_t r = scale32((int32_t)rhs[i] - rhs_off, rt.pre, rt.post, rt.scale, 0);
+    dst[i] = (int8_t)clip_i8(l + r + dst_off);
+  }
+}
+
+// libjit_element_relu_i8 (libjit.cpp:1850-1858): max(x, srcOffset), then rescale
+__global__ void __launch_bounds__(kThreads) relu_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ src, int64_t n,
+                                                           int32_t src_off, int32_t dst_off, Triple t) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t v = (int32_t)src[i] > src_off ? (int32_t)src[i] : src_off;
+    dst[i] = (int8_t)clip_i8(scale32(v - src_off, t.pre, t.post, t.scale, dst_off));
+  }
+}
+
+// libjit_element_maxsplat_kernel_i8 (lib/Backends/CPU/libjit_cpu/libjit_cpu.cpp:39-44)
+__global__ void __launch_bounds__(kThreads) maxsplat_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ src,
+                                                               int64_t n, int8_t splat) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    dst[i] = src[i] > splat ? src[i] : splat;
+}
+
+// libjit_element_rescale_kernel_i8 (libjit.cpp:3030-3038)
+__global__ void __launch_bounds__(kThreads) rescale_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ src,
+                                                              int64_t n, int32_t out_off, int32_t in_off, Triple t) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    dst[i] = (int8_t)clip_i8(scale32((int32_t)src[i] - in_off, t.pre, t.post, t.scale, out_off));
+}
+
+// libjit_element_quantize_kernel_i8 (libjit.cpp:2997-3002): nearbyintf(x / scale + offset) in
+// fp32 with round-half-even, then clip.  The division and the addition are separate roundings.
+__global__ void __launch_bounds__(kThreads) quantize_i8_kernel(int8_t *__restrict__ dst, const float *__restrict__ src,
+                                                               int64_t n, float scale, int32_t offset) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float t = __fadd_rn(__fdiv_rn(src[i], scale), (float)offset);
+    // values beyond the int32 range clip either way; keep the conversion defined
+    const float c = fminf(fmaxf(nearbyintf(t), -2147483648.0f), 2147483520.0f);
+    dst[i] = (int8_t)clip_i8((int32_t)c);
+  }
+}
+
+// libjit_element_dequantize_kernel_i8 (libjit.cpp:3014-3018)
+__global__ void __launch_bounds__(kThreads) dequantize_i8_kernel(float *__restrict__ dst, const int8_t *__restrict__ src,
+                                                                 int64_t n, float scale, int32_t offset) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    dst[i] = __fmul_rn(scale, (float)((int32_t)src[i] - offset));
+}
+
+struct PoolGeom { int N, H, W, C, OH, OW, KH, KW, SH, SW, PT, PL; };
+
+// libjit_max_pool_generic<int8_t> (libjit.cpp:811-870): cells outside the image are skipped,
+// an empty window yields the default value (the output offset).
+__global__ void __launch_bounds__(kThreads) max_pool_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
+                                                               const __grid_constant__ PoolGeom g, int8_t def) {
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * g.C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % g.C);
+    int64_t r = i / g.C;
+    const int ow = (int)(r % g.OW);
+    r /= g.OW;
+    const int oh = (int)(r % g.OH), n = (int)(r / g.OH);
+    int best = -129;
+    for (int kh = 0; kh < g.KH; kh++)
+      for (int kw = 0; kw < g.KW; kw++) {
+        const int ih = oh * g.SH - g.PT + kh, iw = ow * g.SW - g.PL + kw;
+        if (ih < 0 || iw < 0 || ih >= g.H || iw >= g.W) continue;
+        const int v = in[(((int64_t)n * g.H + ih) * g.W + iw) * g.C + c];
+        best = v > best ? v : best;
+      }
+    out[i] = best == -129 ? def : (int8_t)best;
+  }
+}
+
+// libjit_avg_pool_i8 (libjit.cpp:2812-2897)
+__global__ void __launch_bounds__(kThreads) avg_pool_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
+                                                               const __grid_constant__ PoolGeom g, int count_include_pads,
+                                                               int32_t out_off, int32_t in_off, Triple t) {
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * g.C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % g.C);
+    int64_t r = i / g.C;
+    const int ow = (int)(r % g.OW);
+    r /= g.OW;
+    const int oh = (int)(r % g.OH), n = (int)(r / g.OH);
+    int32_t sum = 0, area = 0;
+    for (int kh = 0; kh < g.KH; kh++)
+      for (int kw = 0; kw < g.KW; kw++) {
+        const int ih = oh * g.SH - g.PT + kh, iw = ow * g.SW - g.PL + kw;
+        if (ih < 0 || iw < 0 || ih >= g.H || iw >= g.W) continue;
+        sum += (int32_t)in[(((int64_t)n * g.H + ih) * g.W + iw) * g.C + c] - in_off;
+        area++;
+      }
+    int32_t res;
+    if (count_include_pads) {
+      res = clip_i8(scale32(sum, t.pre, t.post, t.scale, out_off));
+    } else if (area == 0) {
+      res = out_off;
+    } else {
+      // libjit_div_round_i32 (libjit_defs.h:238-244): round half away from zero
+      const int32_t s = scale32(sum, t.pre, t.post, t.scale, 0);
+      const int32_t rnd = area >> 1;
+      res = clip_i8((s > 0 ? (s + rnd) / area : (s - rnd) / area) + out_off);
+    }
+    out[i] = (int8_t)res;
+  }
+}
+
+// 4-D transpose by an arbitrary permutation (libjit_transpose_*, libjit.cpp:1945-...):
+// dst dims = src dims permuted by `shuffle`; one thread per destination element.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) transpose4_kernel(const T *__restrict__ src, T *__restrict__ dst, int d0, int d1,
+                                                              int d2, int d3, int s0, int s1, int s2, int s3) {
+  // d*: destination dims; s*: source element stride of each destination axis
+  const int64_t total = (int64_t)d0 * d1 * d2 * d3;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int i3 = (int)(i % d3);
+    int64_t r = i / d3;
+    const int i2 = (int)(r % d2);
+    r /= d2;
+    const int i1 = (int)(r % d1), i0 = (int)(r / d1);
+    dst[i] = src[(int64_t)i0 * s0 + (int64_t)i1 * s1 + (int64_t)i2 * s2 + (int64_t)i3 * s3];
+  }
+}
+
+int pool_geom(PoolGeom &g, const int64_t *in_dims, const int64_t *out_dims, const int64_t *kernels, const int64_t *strides,
+              const int64_t *pads) {
+  GLOWB200_REQUIRE(in_dims && out_dims && kernels && strides && pads, "NULL shape array");
+  for (int i = 0; i < 4; i++)
+    GLOWB200_REQUIRE(in_dims[i] >= 0 && out_dims[i] >= 0 && in_dims[i] < (1ll << 31) && out_dims[i] < (1ll << 31),
+                     "dimension out of range");
+  GLOWB200_REQUIRE(in_dims[0] == out_dims[0] && in_dims[3] == out_dims[3], "pooling keeps batch and channels");
+  GLOWB200_REQUIRE(kernels[0] >= 1 && kernels[1] >= 1 && strides[0] >= 1 && strides[1] >= 1, "bad kernel/stride");
+  g.N = (int)in_dims[0]; g.H = (int)in_dims[1]; g.W = (int)in_dims[2]; g.C = (int)in_dims[3];
+  g.OH = (int)out_dims[1]; g.OW = (int)out_dims[2];
+  g.KH = (int)kernels[0]; g.KW = (int)kernels[1]; g.SH = (int)strides[0]; g.SW = (int)strides[1];
+  g.PT = (int)pads[0]; g.PL = (int)pads[1];
+  return GLOWB200_OK;
+}
+
+}  // namespace
+}  // namespace glowb200
+
+using namespace glowb200;
+
+#define GLOWB200_STREAM reinterpret_cast<cudaStream_t>(stream)
+#define GLOWB200_ELEMENTWISE_PROLOGUE(n, ...)                      \
+  GLOWB200_REQUIRE((n) >= 0, "negative element count");            \
+  if ((n) == 0) return GLOWB200_OK;                                \
+  GLOWB200_REQUIRE(__VA_ARGS__, "NULL tensor pointer");
+
+extern "C" int glowb200_element_add_i8(int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n, int32_t dest_offset,
+                                       int32_t lhs_offset, int32_t rhs_offset, int32_t lhs_pre, int32_t lhs_post,
+                                       int32_t lhs_scale, int32_t rhs_pre, int32_t rhs_post, int32_t rhs_scale,
+                                       glowb200_stream_t stream) {
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && lhs && rhs)
+  add_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset,
+                                                               Triple{lhs_pre, lhs_post, lhs_scale},
+                                                               Triple{rhs_pre, rhs_post, rhs_scale});
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_element_relu_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t src_offset, int32_t dest_offset,
+                                        int32_t dest_pre, int32_t dest_post, int32_t dest_scale, glowb200_stream_t stream) {
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
+  relu_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, src_offset, dest_offset,
+                                                                Triple{dest_pre, dest_post, dest_scale});
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_element_maxsplat_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t splat,
+                                            glowb200_stream_t stream) {
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
+  GLOWB200_REQUIRE(splat >= -128 && splat <= 127, "splat value outside int8");
+  maxsplat_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, (int8_t)splat);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_element_rescale_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t out_offset, int32_t in_offset,
+                                           int32_t pre, int32_t post, int32_t scale, glowb200_stream_t stream) {
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
+  rescale_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, out_offset, in_offset, Triple{pre, post, scale});
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_element_quantize_i8(int8_t *dest, const float *src, int64_t n, float scale, int32_t offset,
+                                            glowb200_stream_t stream) {
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
+  quantize_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, scale, offset);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_element_dequantize_i8(float *dest, const int8_t *src, int64_t n, float scale, int32_t offset,
+                                              glowb200_stream_t stream) {
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
+  dequantize_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, scale, offset);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_max_pool_i8(const int8_t *in, int8_t *out, const int64_t *in_dims, const int64_t *out_dims,
+                                    const int64_t *kernels, const int64_t *strides, const int64_t *pads, int32_t out_offset,
+                                    glowb200_stream_t stream) {
+  PoolGeom g;
+  if (int rc = pool_geom(g, in_dims, out_dims, kernels, strides, pads)) return rc;
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * g.C;
+  if (total == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(in && out, "NULL tensor pointer");
+  max_pool_i8_kernel<<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(in, out, g, (int8_t)out_offset);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_avg_pool_i8(const int8_t *in, int8_t *out, const int64_t *in_dims, const int64_t *out_dims,
+                                    const int64_t *kernels, const int64_t *strides, const int64_t *pads,
+                                    int count_include_pads, int32_t out_offset, int32_t in_offset, int32_t out_pre,
+                                    int32_t out_post, int32_t out_scale, glowb200_stream_t stream) {
+  PoolGeom g;
+  if (int rc = pool_geom(g, in_dims, out_dims, kernels, strides, pads)) return rc;
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * g.C;
+  if (total == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(in && out, "NULL tensor pointer");
+  avg_pool_i8_kernel<<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(in, out, g, count_include_pads ? 1 : 0, out_offset,
+                                                                        in_offset, Triple{out_pre, out_post, out_scale});
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_transpose(const void *src, void *dest, const int64_t *src_dims, const int32_t *shuffle, int num_dims,
+                                  int element_bytes, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(src_dims && shuffle && num_dims >= 1 && num_dims <= 4, "1 to 4 dimensions are supported");
+  GLOWB200_REQUIRE(element_bytes == 1 || element_bytes == 4, "element size must be 1 or 4 bytes");
+  int64_t sd[4] = {1, 1, 1, 1}, sstride[4];
+  int sh[4] = {0, 1, 2, 3};
+  const int lead = 4 - num_dims;  // pad with leading unit axes
+  bool seen[4] = {false, false, false, false};
+  for (int i = 0; i < num_dims; i++) {
+    GLOWB200_REQUIRE(src_dims[i] >= 0 && src_dims[i] < (1ll << 31), "dimension out of range");
+    GLOWB200_REQUIRE(shuffle[i] >= 0 && shuffle[i] < num_dims && !seen[shuffle[i]], "shuffle is not a permutation");
+    seen[shuffle[i]] = true;
+    sd[lead + i] = src_dims[i];
+    sh[lead + i] = lead + shuffle[i];
+  }
+  sstride[3] = 1;
+  for (int i = 2; i >= 0; i--) sstride[i] = sstride[i + 1] * sd[i + 1];
+  int64_t total = sd[0] * sd[1] * sd[2] * sd[3];
+  if (total == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(src && dest, "NULL tensor pointer");
+  GLOWB200_REQUIRE(total < (1ll << 31), "tensor too large for this kernel");
+  const int d0 = (int)sd[sh[0]], d1 = (int)sd[sh[1]], d2 = (int)sd[sh[2]], d3 = (int)sd[sh[3]];
+  const int s0 = (int)sstride[sh[0]], s1 = (int)sstride[sh[1]], s2 = (int)sstride[sh[2]], s3 = (int)sstride[sh[3]];
+  if (element_bytes == 1)
+    transpose4_kernel<int8_t><<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(
+        reinterpret_cast<const int8_t *>(src), reinterpret_cast<int8_t *>(dest), d0, d1, d2, d3, s0, s1, s2, s3);
+  else
+    transpose4_kernel<float><<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(
+        reinterpret_cast<const float *>(src), reinterpret_cast<float *>(dest), d0, d1, d2, d3, s0, s1, s2, s3);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}

@@ -23,6 +23,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "qgemm.cuh"
 
 namespace glowb200 {
 namespace {
@@ -32,31 +33,6 @@ constexpr int kBlockK = 128;          // bytes of K per pipeline stage = one 128
 constexpr int kUmmaK = 32;            // K per tcgen05.mma for 8-bit operands
 constexpr int kGemmThreads = 192;     // 6 warps
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s: far beyond any legitimate wait
-
-struct GemmParams {
-  int8_t *out;                // [M, N]
-  const int32_t *bias;        // [N] or nullptr (MatMul)
-  const int32_t *b_offsets;   // weight offsets; index j * stride_b_off
-  const int32_t *bias_pre, *bias_post, *bias_scale;  // index j * stride_q
-  const int32_t *out_pre, *out_post, *out_scale;      // index j * stride_q
-  const int32_t *b_row_sums;  // [N] sum_k B[j,k]
-  const int32_t *a_row_sums;  // [M] sum_k A[i,k], or nullptr when every b offset is 0
-  int32_t *status;
-  int M, N, K;
-  int32_t a_offset, bias_offset, out_offset;
-  // per-tensor layers: one set of scalars for every column instead of the arrays above
-  int uniform;
-  int32_t u_b_offset, u_bias_pre, u_bias_post, u_bias_scale, u_out_pre, u_out_post, u_out_scale;
-};
-
-struct ColQuant {
-  int32_t b_off, bias_pre, bias_post, bias_scale, out_pre, out_post, out_scale;
-};
-__device__ __forceinline__ ColQuant col_quant(const GemmParams &p, int j) {
-  if (p.uniform) return {p.u_b_offset, p.u_bias_pre, p.u_bias_post, p.u_bias_scale, p.u_out_pre, p.u_out_post, p.u_out_scale};
-  return {p.b_offsets[j], p.bias ? p.bias_pre[j] : 0, p.bias ? p.bias_post[j] : 0, p.bias ? p.bias_scale[j] : 0,
-          p.out_pre[j], p.out_post[j], p.out_scale[j]};
-}
 
 struct ColParams {  // per output column, built once per tile in shared memory
   int32_t c;        // bias term - aOff*rowsum(B_j) + K*aOff*bOff_j
@@ -294,9 +270,11 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         if (j < p.N) {
           const ColQuant q = col_quant(p, j);
           int32_t term = 0;
-          if (p.bias) term = scale32(p.bias[j] - p.bias_offset, q.bias_pre, q.bias_post, q.bias_scale, 0);
+          if (p.bias)
+            term = scale32(p.bias[j] - (p.bias_offsets ? p.bias_offsets[j] : p.bias_offset), q.bias_pre, q.bias_post,
+                           q.bias_scale, 0);
           const uint32_t corr = (uint32_t)term - (uint32_t)p.a_offset * (uint32_t)p.b_row_sums[j] +
-                                (uint32_t)p.K * (uint32_t)p.a_offset * (uint32_t)q.b_off;
+                                (uint32_t)p.k_corr * (uint32_t)p.a_offset * (uint32_t)q.b_off;
           cp.c = (int32_t)corr;
           cp.b_off = q.b_off;
           cp.shifts = q.out_pre | (q.out_post << 8);
@@ -341,7 +319,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const ColParams cp = cols[c0 + i];
           uint32_t v = acc[i] + (uint32_t)cp.c - (uint32_t)cp.b_off * (uint32_t)a_sum;
           const int32_t pre = cp.shifts & 0xff, post = cp.shifts >> 8;
-          const int32_t r = clip_i8(scale32((int32_t)v, pre, post, cp.scale, p.out_offset));
+          const int32_t r = clip_i8(activation_i32(scale32((int32_t)v, pre, post, cp.scale, p.out_offset), p));
           if ((i & 3) == 0) packed[i >> 2] = 0;
           packed[i >> 2] |= (uint32_t)(r & 0xff) << (8 * (i & 3));
         }
@@ -410,10 +388,13 @@ __global__ void __launch_bounds__(256) i8_gemm_requant_any_kernel(const int8_t *
   if (i >= p.M || j >= p.N) return;
   const ColQuant q = col_quant(p, j);
   uint32_t sum = 0;
-  for (int k = 0; k < p.K; k++)
+  for (int k = 0; k < p.k_corr; k++)
     sum += (uint32_t)(((int32_t)b[(size_t)j * p.K + k] - q.b_off) * ((int32_t)a[(size_t)i * p.K + k] - p.a_offset));
-  if (p.bias) sum += (uint32_t)scale32(p.bias[j] - p.bias_offset, q.bias_pre, q.bias_post, q.bias_scale, 0);
-  p.out[(size_t)i * p.N + j] = (int8_t)clip_i8(scale32((int32_t)sum, q.out_pre, q.out_post, q.out_scale, p.out_offset));
+  if (p.bias)
+    sum += (uint32_t)scale32(p.bias[j] - (p.bias_offsets ? p.bias_offsets[j] : p.bias_offset), q.bias_pre, q.bias_post,
+                             q.bias_scale, 0);
+  p.out[(size_t)i * p.N + j] =
+      (int8_t)clip_i8(activation_i32(scale32((int32_t)sum, q.out_pre, q.out_post, q.out_scale, p.out_offset), p));
 }
 
 // [R, C] int8 -> [C, R] int8 (32x32 tiles through shared memory)
@@ -484,9 +465,12 @@ bool ptr16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // Runs out = requant(A[M,K] x B[N,K]^T ...) choosing the tensor-core or the any-shape kernel.
 // `ws` holds b_row_sums (when not supplied) and a_row_sums (when needed).
+}  // namespace
+
 int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_row_sums_in, bool b_offsets_zero,
              int force_any, void *ws, size_t ws_bytes, cudaStream_t s) {
   if (p.M == 0 || p.N == 0) return GLOWB200_OK;
+  if (p.k_corr == 0) p.k_corr = p.K;
   const bool tc = !force_any && p.K > 0 && (p.K % 16) == 0 && ptr16(a) && ptr16(b);
   if (!tc) {
     dim3 grid((p.N + 15) / 16, (p.M + 15) / 16);
@@ -524,6 +508,7 @@ int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_ro
   return launch_tile_kernel<64, 6>(ma, mb, p, s);
 }
 
+namespace {
 int check_dims(int64_t M, int64_t K, int64_t N) {
   GLOWB200_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 24),
                    "matrix dimensions out of range");

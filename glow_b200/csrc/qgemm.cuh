@@ -1,0 +1,56 @@
+// Internal interface of the int8 contraction core (qgemm.cu), shared with the convolution
+// front end (conv.cu).
+#pragma once
+#include "common.cuh"
+
+namespace glowb200 {
+
+struct GemmParams {
+  int8_t *out;                // [M, N]
+  const int32_t *bias;        // [N] or nullptr (MatMul)
+  const int32_t *b_offsets;   // weight offsets; index j * stride_b_off
+  const int32_t *bias_pre, *bias_post, *bias_scale;  // index j * stride_q
+  const int32_t *out_pre, *out_post, *out_scale;      // index j * stride_q
+  const int32_t *b_row_sums;  // [N] sum_k B[j,k]
+  const int32_t *a_row_sums;  // [M] sum_k A[i,k], or nullptr when every b offset is 0
+  int32_t *status;
+  const int32_t *bias_offsets;  // per-column bias offsets (channelwise conv), or nullptr: bias_offset
+  int M, N, K;                  // K: row pitch of both operands in bytes (a multiple of 16 on the TMA path)
+  int k_corr;                   // number of real K entries (<= K; the rest is zero padding); 0 = K
+  int32_t a_offset, bias_offset, out_offset;
+  // fused activation on the requantised value (glow::FusedActivation: 0 none, 1 relu, 2 clip, 5 leaky relu)
+  int32_t act_type, act_args[3];
+  // per-tensor layers: one set of scalars for every column instead of the arrays above
+  int uniform;
+  int32_t u_b_offset, u_bias_pre, u_bias_post, u_bias_scale, u_out_pre, u_out_post, u_out_scale;
+};
+
+struct ColQuant {
+  int32_t b_off, bias_pre, bias_post, bias_scale, out_pre, out_post, out_scale;
+};
+__device__ __forceinline__ ColQuant col_quant(const GemmParams &p, int j) {
+  if (p.uniform) return {p.u_b_offset, p.u_bias_pre, p.u_bias_post, p.u_bias_scale, p.u_out_pre, p.u_out_post, p.u_out_scale};
+  return {p.b_offsets[j], p.bias ? p.bias_pre[j] : 0, p.bias ? p.bias_post[j] : 0, p.bias ? p.bias_scale[j] : 0,
+          p.out_pre[j], p.out_post[j], p.out_scale[j]};
+}
+
+// libjit_activation_i32 (lib/LLVMIRCodeGen/libjit/libjit_defs.h:206-233).
+__device__ __forceinline__ int32_t activation_i32(int32_t x, const GemmParams &p) {
+  if (p.act_type == 0) return x;
+  if (p.act_type == 1) return x > p.out_offset ? x : p.out_offset;
+  if (p.act_type == 2) { const int32_t t = x > p.act_args[0] ? x : p.act_args[0]; return t < p.act_args[1] ? t : p.act_args[1]; }
+  if (p.act_type == 3 || p.act_type == 4) return x;
+  return x >= p.out_offset ? x : scale32(x - p.out_offset, p.act_args[0], p.act_args[1], p.act_args[2], p.out_offset);
+}
+
+// out = requant(A[M,K] x B[N,K]^T) with the tensor-core kernel when the shapes allow it (K a
+// multiple of 16, 16-byte aligned operands), else the any-shape kernel.  `ws` must hold
+// i8_gemm_core_workspace_bytes(M, N) bytes.  b_row_sums_in may be nullptr (computed here).
+int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_row_sums_in, bool b_offsets_zero,
+             int force_any, void *ws, size_t ws_bytes, cudaStream_t s);
+
+inline size_t i8_gemm_core_workspace_bytes(int64_t M, int64_t N) {
+  return align_up((size_t)N * 4, 256) + align_up((size_t)M * 4, 256);
+}
+
+}  // namespace glowb200

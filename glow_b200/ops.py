@@ -232,6 +232,136 @@ def matmul_i8(lhs, rhs, out_offset, lhs_offset, rhs_offset, out_triple, *, flags
     return out
 
 
+# ------------------------------------------------------------------------------------------
+# Int8 convolution and glue operators
+# ------------------------------------------------------------------------------------------
+def _i64arr(v):
+    return (C.c_int64 * len(v))(*[int(x) for x in v])
+
+
+def conv_out_hw(in_hw, kernels, strides, pads, dilation=(1, 1)):
+    """Output height/width as Glow computes them (calculateConvPoolOutputDims)."""
+    oh = (in_hw[0] + pads[0] + pads[2] - ((kernels[0] - 1) * dilation[0] + 1)) // strides[0] + 1
+    ow = (in_hw[1] + pads[1] + pads[3] - ((kernels[1] - 1) * dilation[1] + 1)) // strides[1] + 1
+    return oh, ow
+
+
+def _conv_shapes(inp, filt, kernels, strides, pads, group, dilation):
+    n, h, w, c = inp.shape
+    oc = filt.shape[0]
+    oh, ow = conv_out_hw((h, w), kernels, strides, pads, dilation)
+    return (_i64arr((n, oh, ow, oc)), _i64arr(inp.shape), _i64arr(filt.shape), _i64arr(kernels), _i64arr(strides),
+            _i64arr(pads), int(group), _i64arr(dilation)), (n, oh, ow, oc)
+
+
+def channelwise_quantized_conv2d(inp, filt, bias, kernels, strides, pads, group, dilation, out_offset, in_offset,
+                                 filter_offsets, bias_offsets, bias_triples, out_triples, act_type=0, act_args=None,
+                                 *, filter_row_sums=None, flags=0, out=None, workspace=None, status=None):
+    """ChannelwiseQuantizedConvolution: inp int8 NHWC, filt int8 [outC,kH,kW,inC/group], bias int32."""
+    _cuda(inp, "inp", (torch.int8,))
+    _cuda(filt, "filt", (torch.int8,))
+    sh, odims = _conv_shapes(inp, filt, kernels, strides, pads, group, dilation)
+    if out is None:
+        out = torch.empty(odims, dtype=torch.int8, device=inp.device)
+    need = int(_lib.lib().glowb200_conv2d_workspace_bytes(sh[0], sh[1], sh[2], sh[3], sh[4], sh[5], sh[6], sh[7]))
+    ws = _workspace(workspace, need, inp.device)
+    aa = (C.c_int32 * 3)(*([int(v) for v in act_args] + [0, 0, 0])[:3]) if act_args is not None else None
+    check(_lib.lib().glowb200_channelwise_quantized_conv2d_i8_i32(
+        _p(out), _p(inp), _p(filt), _p(bias), sh[0], sh[1], sh[2], sh[3], sh[4], sh[5], sh[6], sh[7], int(out_offset),
+        int(in_offset), _p(filter_offsets), _p(bias_offsets), _p(bias_triples[0]), _p(bias_triples[1]),
+        _p(bias_triples[2]), _p(out_triples[0]), _p(out_triples[1]), _p(out_triples[2]), int(act_type), aa,
+        _p(filter_row_sums), int(flags), _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
+def conv2d_i8(inp, filt, bias, kernels, strides, pads, group, dilation, out_offset, in_offset, filter_offset,
+              bias_offset, bias_triple, out_triple, act_type=0, act_args=None, *, flags=0, out=None, workspace=None,
+              status=None):
+    """Convolution (int8, per-tensor quantisation)."""
+    sh, odims = _conv_shapes(inp, filt, kernels, strides, pads, group, dilation)
+    if out is None:
+        out = torch.empty(odims, dtype=torch.int8, device=inp.device)
+    need = int(_lib.lib().glowb200_conv2d_workspace_bytes(sh[0], sh[1], sh[2], sh[3], sh[4], sh[5], sh[6], sh[7]))
+    ws = _workspace(workspace, need, inp.device)
+    aa = (C.c_int32 * 3)(*([int(v) for v in act_args] + [0, 0, 0])[:3]) if act_args is not None else None
+    check(_lib.lib().glowb200_conv2d_i8_i32(
+        _p(out), _p(inp), _p(filt), _p(bias), sh[0], sh[1], sh[2], sh[3], sh[4], sh[5], sh[6], int(out_offset),
+        int(in_offset), int(filter_offset), int(bias_offset), *[int(v) for v in bias_triple],
+        *[int(v) for v in out_triple], sh[7], int(act_type), aa, int(flags), _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
+def element_add_i8(lhs, rhs, dest_offset, lhs_offset, rhs_offset, lhs_triple, rhs_triple, out=None):
+    out = torch.empty_like(lhs) if out is None else out
+    check(_lib.lib().glowb200_element_add_i8(_p(out), _p(lhs), _p(rhs), lhs.numel(), int(dest_offset), int(lhs_offset),
+                                             int(rhs_offset), *[int(v) for v in lhs_triple],
+                                             *[int(v) for v in rhs_triple], _stream()))
+    return out
+
+
+def element_relu_i8(src, src_offset, dest_offset, triple, out=None):
+    out = torch.empty_like(src) if out is None else out
+    check(_lib.lib().glowb200_element_relu_i8(_p(out), _p(src), src.numel(), int(src_offset), int(dest_offset),
+                                              *[int(v) for v in triple], _stream()))
+    return out
+
+
+def element_maxsplat_i8(src, splat, out=None):
+    out = torch.empty_like(src) if out is None else out
+    check(_lib.lib().glowb200_element_maxsplat_i8(_p(out), _p(src), src.numel(), int(splat), _stream()))
+    return out
+
+
+def element_rescale_i8(src, out_offset, in_offset, triple, out=None):
+    out = torch.empty_like(src) if out is None else out
+    check(_lib.lib().glowb200_element_rescale_i8(_p(out), _p(src), src.numel(), int(out_offset), int(in_offset),
+                                                 *[int(v) for v in triple], _stream()))
+    return out
+
+
+def element_quantize_i8(src, scale, offset, out=None):
+    out = torch.empty(src.shape, dtype=torch.int8, device=src.device) if out is None else out
+    check(_lib.lib().glowb200_element_quantize_i8(_p(out), _p(src), src.numel(), C.c_float(float(scale)), int(offset),
+                                                  _stream()))
+    return out
+
+
+def element_dequantize_i8(src, scale, offset, out=None):
+    out = torch.empty(src.shape, dtype=torch.float32, device=src.device) if out is None else out
+    check(_lib.lib().glowb200_element_dequantize_i8(_p(out), _p(src), src.numel(), C.c_float(float(scale)),
+                                                    int(offset), _stream()))
+    return out
+
+
+def max_pool_i8(inp, kernels, strides, pads, out_offset, out=None):
+    n, h, w, c = inp.shape
+    oh, ow = conv_out_hw((h, w), kernels, strides, pads)
+    out = torch.empty((n, oh, ow, c), dtype=torch.int8, device=inp.device) if out is None else out
+    check(_lib.lib().glowb200_max_pool_i8(_p(inp), _p(out), _i64arr(inp.shape), _i64arr(out.shape), _i64arr(kernels),
+                                          _i64arr(strides), _i64arr(pads), int(out_offset), _stream()))
+    return out
+
+
+def avg_pool_i8(inp, kernels, strides, pads, count_include_pads, out_offset, in_offset, triple, out=None):
+    n, h, w, c = inp.shape
+    oh, ow = conv_out_hw((h, w), kernels, strides, pads)
+    out = torch.empty((n, oh, ow, c), dtype=torch.int8, device=inp.device) if out is None else out
+    check(_lib.lib().glowb200_avg_pool_i8(_p(inp), _p(out), _i64arr(inp.shape), _i64arr(out.shape), _i64arr(kernels),
+                                          _i64arr(strides), _i64arr(pads), int(bool(count_include_pads)),
+                                          int(out_offset), int(in_offset), *[int(v) for v in triple], _stream()))
+    return out
+
+
+def transpose(src, shuffle):
+    """dest dims[i] = src dims[shuffle[i]] (NCHW -> NHWC is shuffle (0, 2, 3, 1))."""
+    if src.element_size() not in (1, 4):
+        raise TypeError("1- or 4-byte elements only")
+    out = torch.empty([src.shape[i] for i in shuffle], dtype=src.dtype, device=src.device)
+    check(_lib.lib().glowb200_transpose(_p(src), _p(out), _i64arr(src.shape), (C.c_int32 * len(shuffle))(*shuffle),
+                                        len(shuffle), src.element_size(), _stream()))
+    return out
+
+
 class SlwsBatch:
     """A fixed set of tables of one kind and row width, pooled by ONE launch per request.
 

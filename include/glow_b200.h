@@ -188,6 +188,91 @@ int glowb200_matmul_i8(int8_t *out, const int8_t *lhs, const int8_t *rhs, int64_
                        void *workspace, size_t workspace_bytes, int32_t *status,
                        glowb200_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Int8 convolution (NHWC activations, filter [outC, kH, kW, inC/group]).  The four-entry shape
+ * arrays are HOST arrays, laid out as the reference passes them: dims {N,H,W,C}, kernels {h,w},
+ * strides {h,w}, pads {top,left,bottom,right} (only top and left are read, like the reference),
+ * dilation {h,w}.  act_type / act_args follow glow::FusedActivation as libjit_activation_i32
+ * reads them (0 none, 1 relu, 2 clip {min,max}, 5 leaky relu {pre,post,scale}); act_args is a
+ * HOST array.
+ * ------------------------------------------------------------------------------------- */
+size_t glowb200_conv2d_workspace_bytes(const int64_t *out_dims, const int64_t *in_dims,
+                                       const int64_t *filter_dims, const int64_t *kernels,
+                                       const int64_t *strides, const int64_t *pads, int64_t group,
+                                       const int64_t *dilation);
+
+/* ChannelwiseQuantizedConvolution (2-D), int8 with int32 bias.
+ * Replaces libjit_channelwise_quantized_conv2d_i8_i32 (lib/LLVMIRCodeGen/libjit/libjit_conv.cpp:
+ * 530-545, body :151-239; per-channel integers derived at LLVMIRGen.cpp:2695-2798).
+ * filter_row_sums: optional int32 [outC] = glowb200_i8_row_sums(filter as [outC, kH*kW*inC]);
+ * flags: GLOWB200_FC_WEIGHT_OFFSETS_ZERO when every filter offset is 0 (symmetric filters). */
+int glowb200_channelwise_quantized_conv2d_i8_i32(
+    int8_t *out, const int8_t *in, const int8_t *filter, const int32_t *bias,
+    const int64_t *out_dims, const int64_t *in_dims, const int64_t *filter_dims,
+    const int64_t *kernels, const int64_t *strides, const int64_t *pads, int64_t group,
+    const int64_t *dilation, int32_t out_offset, int32_t in_offset,
+    const int32_t *filter_offsets, const int32_t *bias_offsets, const int32_t *bias_pre,
+    const int32_t *bias_post, const int32_t *bias_scale, const int32_t *out_pre,
+    const int32_t *out_post, const int32_t *out_scale, int32_t act_type, const int32_t *act_args,
+    const int32_t *filter_row_sums, int flags, void *workspace, size_t workspace_bytes,
+    int32_t *status, glowb200_stream_t stream);
+
+/* Convolution (2-D), int8 with int32 bias, one quantisation per tensor.
+ * Replaces libjit_conv2d_i8_i32 (libjit_conv.cpp:496-510, body :49-147; scalars derived at
+ * LLVMIRGen.cpp:2501-2599).  The reference's depthUnroll argument only blocks its loops and
+ * has no counterpart here. */
+int glowb200_conv2d_i8_i32(
+    int8_t *out, const int8_t *in, const int8_t *filter, const int32_t *bias,
+    const int64_t *out_dims, const int64_t *in_dims, const int64_t *filter_dims,
+    const int64_t *kernels, const int64_t *strides, const int64_t *pads, int64_t group,
+    int32_t out_offset, int32_t in_offset, int32_t filter_offset, int32_t bias_offset,
+    int32_t bias_pre, int32_t bias_post, int32_t bias_scale, int32_t out_pre, int32_t out_post,
+    int32_t out_scale, const int64_t *dilation, int32_t act_type, const int32_t *act_args,
+    int flags, void *workspace, size_t workspace_bytes, int32_t *status, glowb200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Int8 glue operators (n = element count; tensors are dense)
+ * ------------------------------------------------------------------------------------- */
+
+/* ElementAdd int8: libjit_element_add_kernel_i8 (libjit.cpp:1593-1603); the two triples come
+ * from lhsScale/destScale and rhsScale/destScale (LLVMIRGen.cpp:1716-1771). */
+int glowb200_element_add_i8(int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n,
+                            int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset,
+                            int32_t lhs_pre, int32_t lhs_post, int32_t lhs_scale, int32_t rhs_pre,
+                            int32_t rhs_post, int32_t rhs_scale, glowb200_stream_t stream);
+/* Relu int8: libjit_element_relu_i8 (libjit.cpp:1850-1858). */
+int glowb200_element_relu_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t src_offset,
+                             int32_t dest_offset, int32_t dest_pre, int32_t dest_post,
+                             int32_t dest_scale, glowb200_stream_t stream);
+/* max(x, constant): libjit_element_maxsplat_kernel_i8 (lib/Backends/CPU/libjit_cpu/libjit_cpu.cpp:
+ * 39-44), what the CPU backend turns a quantized Relu into (lib/Backends/CPU/Transforms.cpp:83-113). */
+int glowb200_element_maxsplat_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t splat,
+                                 glowb200_stream_t stream);
+/* RescaleQuantized int8: libjit_element_rescale_kernel_i8 (libjit.cpp:3030-3038). */
+int glowb200_element_rescale_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t out_offset,
+                                int32_t in_offset, int32_t pre, int32_t post, int32_t scale,
+                                glowb200_stream_t stream);
+/* Quantize fp32 -> int8: libjit_element_quantize_kernel_i8 (libjit.cpp:2997-3002). */
+int glowb200_element_quantize_i8(int8_t *dest, const float *src, int64_t n, float scale,
+                                 int32_t offset, glowb200_stream_t stream);
+/* Dequantize int8 -> fp32: libjit_element_dequantize_kernel_i8 (libjit.cpp:3014-3018). */
+int glowb200_element_dequantize_i8(float *dest, const int8_t *src, int64_t n, float scale,
+                                   int32_t offset, glowb200_stream_t stream);
+/* MaxPool int8, NHWC: libjit_max_pool_i8 (libjit.cpp:2592-2597, body :811-870). */
+int glowb200_max_pool_i8(const int8_t *in, int8_t *out, const int64_t *in_dims,
+                         const int64_t *out_dims, const int64_t *kernels, const int64_t *strides,
+                         const int64_t *pads, int32_t out_offset, glowb200_stream_t stream);
+/* AvgPool int8, NHWC: libjit_avg_pool_i8 (libjit.cpp:2812-2897). */
+int glowb200_avg_pool_i8(const int8_t *in, int8_t *out, const int64_t *in_dims,
+                         const int64_t *out_dims, const int64_t *kernels, const int64_t *strides,
+                         const int64_t *pads, int count_include_pads, int32_t out_offset,
+                         int32_t in_offset, int32_t out_pre, int32_t out_post, int32_t out_scale,
+                         glowb200_stream_t stream);
+/* Transpose of a tensor of up to 4 dimensions with 1- or 4-byte elements (libjit_transpose_i8 /
+ * _f, libjit.cpp:1945-...): dest dims[i] = src_dims[shuffle[i]].  src_dims / shuffle are HOST arrays. */
+int glowb200_transpose(const void *src, void *dest, const int64_t *src_dims, const int32_t *shuffle,
+                       int num_dims, int element_bytes, glowb200_stream_t stream);
+
 /* FusedRowwiseQuantizedSparseLengthsWeightedSum for callers that can neither allocate device
  * memory nor size a workspace per request.  (No counterpart in the reference: its CPU kernels
  * need no scratch.)  Think of a DeviceManager's request thread after every byte of HBM was

@@ -1,0 +1,134 @@
+"""Int8 convolution and glue operators against the CPU oracle: bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from glow_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def t(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+CONV_CASES = [
+    # n, ih, iw, ic, oc, kernel, stride, pads, group, dilation, act
+    (2, 14, 14, 64, 64, (3, 3), (1, 1), (1, 1, 1, 1), 1, (1, 1), 1),     # ResNet 3x3
+    (2, 14, 14, 64, 256, (1, 1), (1, 1), (0, 0, 0, 0), 1, (1, 1), 0),    # pointwise: no im2col
+    (2, 14, 14, 128, 256, (1, 1), (2, 2), (0, 0, 0, 0), 1, (1, 1), 0),   # strided shortcut
+    (1, 30, 30, 3, 64, (7, 7), (2, 2), (3, 3, 3, 3), 1, (1, 1), 1),      # stem: K = 147 -> padded to 160
+    (3, 9, 11, 32, 48, (3, 3), (2, 2), (1, 1, 1, 1), 1, (1, 1), 2),      # clip
+    (1, 11, 11, 16, 24, (3, 3), (1, 1), (2, 2, 2, 2), 1, (2, 2), 5),     # dilation, leaky relu
+    (1, 12, 10, 6, 8, (3, 3), (2, 2), (1, 1, 1, 1), 2, (1, 1), 1),       # groups -> direct kernel
+    (1, 5, 5, 8, 8, (3, 3), (1, 1), (1, 1, 1, 1), 8, (1, 1), 0),         # depthwise
+    (2, 7, 7, 20, 10, (1, 1), (1, 1), (0, 0, 0, 0), 1, (1, 1), 0),       # C not a multiple of 16
+]
+
+
+def _conv_inputs(oracle, case, symmetric):
+    n, ih, iw, ic, oc, k, s, p, g, d, act = case
+    rng = np.random.default_rng(ic * 1000 + oc * 7 + k[0])
+    K = k[0] * k[1] * ic // g
+    c = dict(
+        inp=rng.integers(-128, 128, (n, ih, iw, ic)).astype(np.int8),
+        filt=rng.integers(-127, 128, (oc, k[0], k[1], ic // g)).astype(np.int8),
+        bias=rng.integers(-3000, 3000, oc).astype(np.int32),
+        fo=np.zeros(oc, np.int32) if symmetric else rng.integers(-3, 4, oc).astype(np.int32),
+        bo=np.zeros(oc, np.int32) if symmetric else rng.integers(-5, 5, oc).astype(np.int32))
+    fs = rng.uniform(0.002, 0.02, oc).astype(np.float32)
+    in_scale = np.float32(0.04)
+    out_scale = np.float32(0.9 * np.sqrt(K / 72.0))
+    c["pp"] = oracle.rowwise_requant_params(fs, in_scale, in_scale * fs, out_scale)
+    c["act_args"] = {2: [-20, 60], 5: list(oracle.quantize_scale_offset_32to8(0.1))}.get(act)
+    return c
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+@pytest.mark.parametrize("symmetric", [True, False])
+def test_channelwise_conv_bit_exact(oracle, case, symmetric):
+    n, ih, iw, ic, oc, k, s, p, g, d, act = case
+    c = _conv_inputs(oracle, case, symmetric)
+    ohw = ops.conv_out_hw((ih, iw), k, s, p, d)
+    want = oracle.conv2d_i8_i32(c["inp"], c["filt"], c["bias"], ohw, k, s, p, g, d, 4, -2, c["fo"], c["bo"], c["pp"][:3],
+                                c["pp"][3:], act, c["act_args"])
+    pp = [t(a) for a in c["pp"]]
+    st = ops.new_status(DEV)
+    for flags in (ops.FC_WEIGHT_OFFSETS_ZERO if symmetric else 0, ops.FC_FORCE_ANY_SHAPE_KERNEL):
+        got = ops.channelwise_quantized_conv2d(t(c["inp"]), t(c["filt"]), t(c["bias"]), k, s, p, g, d, 4, -2, t(c["fo"]),
+                                               t(c["bo"]), pp[:3], pp[3:], act, c["act_args"], flags=flags, status=st)
+        np.testing.assert_array_equal(got.cpu().numpy(), want)
+    assert int(st.item()) == 0
+    assert len(np.unique(want)) > 10
+
+
+@pytest.mark.parametrize("case", [CONV_CASES[0], CONV_CASES[3], CONV_CASES[6]])
+def test_per_tensor_conv_bit_exact(oracle, case):
+    n, ih, iw, ic, oc, k, s, p, g, d, act = case
+    c = _conv_inputs(oracle, case, False)
+    ohw = ops.conv_out_hw((ih, iw), k, s, p, d)
+    bt = [int(x[0]) for x in c["pp"][:3]]
+    ot = [int(x[0]) for x in c["pp"][3:]]
+    want = oracle.conv2d_i8_i32(c["inp"], c["filt"], c["bias"], ohw, k, s, p, g, d, 4, -2, c["fo"][:1], c["bo"][:1], bt, ot,
+                                act, c["act_args"], per_channel=False)
+    got = ops.conv2d_i8(t(c["inp"]), t(c["filt"]), t(c["bias"]), k, s, p, g, d, 4, -2, int(c["fo"][0]), int(c["bo"][0]),
+                        bt, ot, act, c["act_args"])
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+
+
+def test_resnet_sized_conv_against_direct_kernel():
+    """A ResNet-50 layer at batch 64 (3x3, 128 channels, 28x28): the tensor-core path against the
+    direct kernel on the device (the CPU oracle covers the smaller cases above)."""
+    rng = np.random.default_rng(5)
+    n, hw, ch = 64, 28, 128
+    inp = t(rng.integers(-128, 128, (n, hw, hw, ch)).astype(np.int8))
+    filt = t(rng.integers(-127, 128, (ch, 3, 3, ch)).astype(np.int8))
+    bias = t(rng.integers(-3000, 3000, ch).astype(np.int32))
+    zeros = torch.zeros(ch, dtype=torch.int32, device=DEV)
+    fs = rng.uniform(0.002, 0.02, ch).astype(np.float32)
+    pp = [t(a) for a in ops.rowwise_requant_params(fs, 0.04, np.float32(0.04) * fs, np.float32(3.5))]
+    args = (inp, filt, bias, (3, 3), (1, 1), (1, 1, 1, 1), 1, (1, 1), 3, -5, zeros, zeros, pp[:3], pp[3:], 1, None)
+    a = ops.channelwise_quantized_conv2d(*args, flags=ops.FC_WEIGHT_OFFSETS_ZERO)
+    b = ops.channelwise_quantized_conv2d(*args, flags=ops.FC_FORCE_ANY_SHAPE_KERNEL)
+    assert torch.equal(a, b)
+    assert a.unique().numel() > 50
+
+
+def test_elementwise_and_pools_bit_exact(oracle):
+    rng = np.random.default_rng(13)
+    a = rng.integers(-128, 128, 100_003).astype(np.int8)
+    b = rng.integers(-128, 128, 100_003).astype(np.int8)
+    lt = ops.quantize_scale_offset_32to8(0.7)
+    rt = ops.quantize_scale_offset_32to8(1.9)
+    np.testing.assert_array_equal(ops.element_add_i8(t(a), t(b), 5, -3, 9, lt, rt).cpu().numpy(),
+                                  oracle.element_add_i8(a, b, 5, -3, 9, lt, rt))
+    np.testing.assert_array_equal(ops.element_relu_i8(t(a), -10, 4, lt).cpu().numpy(), oracle.element_relu_i8(a, -10, 4, lt))
+    np.testing.assert_array_equal(ops.element_maxsplat_i8(t(a), -7).cpu().numpy(), oracle.element_maxsplat_i8(a, -7))
+    np.testing.assert_array_equal(ops.element_rescale_i8(t(a), 3, -2, rt).cpu().numpy(), oracle.element_rescale_i8(a, 3, -2, rt))
+    f = (rng.standard_normal(50_000) * 3).astype(np.float32)
+    f[:8] = [0.5 * 0.05, 1.5 * 0.05, 2.5 * 0.05, -0.5 * 0.05, -1.5 * 0.05, 1000.0, -1000.0, 0.0]
+    np.testing.assert_array_equal(ops.element_quantize_i8(t(f), 0.05, 3).cpu().numpy(), oracle.element_quantize_i8(f, 0.05, 3))
+    np.testing.assert_array_equal(ops.element_dequantize_i8(t(a), 0.037, -4).cpu().numpy().view(np.uint32),
+                                  oracle.element_dequantize_i8(a, 0.037, -4).view(np.uint32))
+    x = rng.integers(-128, 128, (2, 23, 19, 24)).astype(np.int8)
+    for k, s, p in [((3, 3), (2, 2), (1, 1, 1, 1)), ((2, 2), (2, 2), (0, 0, 0, 0)), ((7, 7), (1, 1), (3, 3, 3, 3)),
+                    ((23, 19), (1, 1), (0, 0, 0, 0))]:
+        ohw = ops.conv_out_hw((23, 19), k, s, p)
+        np.testing.assert_array_equal(ops.max_pool_i8(t(x), k, s, p, -7).cpu().numpy(), oracle.max_pool_i8(x, ohw, k, s, p, -7))
+        for cip in (True, False):
+            area = np.float32(k[0] * k[1]) if cip else np.float32(1)
+            tr = ops.quantize_scale_offset_32to8(np.float32(0.03) / np.float32(0.05) / area)
+            np.testing.assert_array_equal(ops.avg_pool_i8(t(x), k, s, p, cip, 3, -4, tr).cpu().numpy(),
+                                          oracle.avg_pool_i8(x, ohw, k, s, p, cip, 3, -4, tr))
+
+
+def test_transpose():
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((3, 5, 7, 11)).astype(np.float32)
+    for sh in [(0, 2, 3, 1), (0, 3, 1, 2), (3, 2, 1, 0)]:
+        np.testing.assert_array_equal(ops.transpose(t(x), sh).cpu().numpy(), np.transpose(x, sh))
+    y = rng.integers(-128, 128, (6, 9, 4)).astype(np.int8)
+    np.testing.assert_array_equal(ops.transpose(t(y), (2, 0, 1)).cpu().numpy(), np.transpose(y, (2, 0, 1)))
+    z = rng.integers(-128, 128, (40, 33)).astype(np.int8)
+    np.testing.assert_array_equal(ops.transpose(t(z), (1, 0)).cpu().numpy(), z.T)
