@@ -16,7 +16,8 @@ _vp, _i64, _i32, _int, _sz, _f32 = C.c_void_p, C.c_int64, C.c_int32, C.c_int, C.
 class SlwsJob(C.Structure):
     """struct glowb200_slws_job"""
     _fields_ = [("data", _vp), ("weights", _vp), ("indices", _vp), ("lengths", _vp), ("dest", _vp),
-                ("rows", _i64), ("num_indices", _i64), ("dest_stride", _i64), ("segments", _i64)]
+                ("rows", _i64), ("num_indices", _i64), ("dest_stride", _i64), ("segments", _i64),
+                ("dests", _vp), ("bags_per_dest", _i64)]
 
 
 # name -> (restype, argtypes); also the list the symbol-export test walks.
@@ -33,6 +34,9 @@ SIGNATURES = {
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _vp]),
     "glowb200_quantize_scale_offset_32to8": (None, [_f32, _vp, _vp, _vp]),
     "glowb200_rowwise_requant_params": (_int, [_vp, _i64, _f32, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "glowb200_choose_quantization_params": (None, [_f32, _f32, _int, _int, _vp, _vp]),
+    "glowb200_tensor_rowwise_quantize_i8": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
+    "glowb200_quantize_bias_i32": (_int, [_vp, _i64, _f32, _i32, _vp]),
     "glowb200_i8_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "glowb200_i8_row_sums": (_int, [_vp, _i64, _i64, _vp, _vp]),
     "glowb200_rowwise_quantized_fc_i8_i32": (
@@ -55,6 +59,11 @@ SIGNATURES = {
     "glowb200_max_pool_i8": (_int, [_vp] * 7 + [_i32, _vp]),
     "glowb200_avg_pool_i8": (_int, [_vp] * 7 + [_int] + [_i32] * 5 + [_vp]),
     "glowb200_transpose": (_int, [_vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "glowb200_pairwise_dot_interaction": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _f32, _i32, _vp]),
+    "glowb200_peer_buffer_create": (_int, [_sz, _vp, _vp]),
+    "glowb200_peer_buffer_open": (_int, [_vp, _vp]),
+    "glowb200_peer_buffer_close": (_int, [_vp]),
+    "glowb200_peer_buffer_destroy": (_int, [_vp]),
     "glowb200_embedding_bag_byte_rowwise_offsets": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _sz, _vp,
                _vp]),

@@ -555,6 +555,7 @@ extern "C" int glowb200_rowwise_quantized_fc_i8_i32(
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.uniform = 0;
   p.a_offset = in_offset; p.bias_offset = bias_offset; p.out_offset = out_offset;
+  p.act_type = (flags & GLOWB200_FC_FUSE_RELU) ? 1 : 0;
   return run_gemm(p, in, weights, weights_row_sums, (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) != 0,
                   (flags & GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL) != 0, workspace, workspace_bytes,
                   reinterpret_cast<cudaStream_t>(stream));

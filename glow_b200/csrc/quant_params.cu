@@ -2,7 +2,10 @@
 // load time (Glow does it while emitting code, with the results baked into the JIT-ed call).
 // Float types and operation order follow the reference exactly, because the kernels' int8
 // results depend on every bit of these integers.
+#include <algorithm>
+#include <climits>
 #include <cmath>
+#include <limits>
 
 #include "common.cuh"
 
@@ -44,6 +47,95 @@ extern "C" int glowb200_rowwise_requant_params(const float *row_scales, int64_t 
     const float b = bias_scales[num_bias_scales == 1 ? 0 : j];
     glowb200::quantize_scale_32to8(b / mat_mul_scale, bias_pre[j], bias_post[j], bias_scale[j]);
     glowb200::quantize_scale_32to8(mat_mul_scale / out_scale, out_pre[j], out_post[j], out_scale_int[j]);
+  }
+  return GLOWB200_OK;
+}
+
+namespace glowb200 {
+
+// chooseQuantizationParams without calibration (lib/Quantization/Base/Base.cpp:433-565) for a
+// signed quantized range [qmin, qmax].  schema: 0 Asymmetric, 1 Symmetric, 2 SymmetricWithUnsigned,
+// 3 SymmetricWithPower2Scale (include/glow/Quantization/Base/Base.h Schema).
+void choose_quantization_params(float min, float max, int schema, int64_t qmin, int64_t qmax, float &scale_out,
+                                int32_t &offset_out) {
+  min = std::min(min, 0.f);
+  max = std::max(max, 0.f);
+  if (schema == 2) {
+    if (!(min >= 0.f)) schema = 1;
+  }
+  if (schema == 1 || schema == 3) {
+    const double rmin = min / (double)qmin;
+    const double rmax = max / (double)qmax;
+    if (rmin > rmax) max = (float)(rmin * qmax);
+    else min = (float)(rmax * qmin);
+  }
+  min = std::max(min, std::numeric_limits<float>::lowest());
+  max = std::min(max, std::numeric_limits<float>::max());
+  double scale = ((double)max - min) / ((double)qmax - qmin);
+  if (scale == 0) scale = 0.1;
+  const double zp_from_min = qmin - min / scale;
+  const double zp_from_max = qmax - max / scale;
+  const double err_min = std::abs((double)qmin) + std::abs(min / scale);
+  const double err_max = std::abs((double)qmax) + std::abs(max / scale);
+  double zp = err_min < err_max ? zp_from_min : zp_from_max;
+  const float difference = std::abs(max + min);
+  if (difference <= std::numeric_limits<float>::epsilon()) zp = 0;
+  int32_t nudged;
+  if (zp < qmin) nudged = (int32_t)qmin;
+  else if (zp > qmax) nudged = (int32_t)qmax;
+  else nudged = static_cast<int32_t>(std::round(zp));
+  if (schema == 3) scale = std::exp2(std::ceil(std::log2(scale)));
+  scale_out = static_cast<float>(scale);
+  offset_out = nudged;
+}
+
+// quantization::quantize<int8_t> (include/glow/Quantization/Base/Base.h:322-329)
+static inline int8_t quantize_i8(float x, float scale, int32_t offset) {
+  const float r = x / scale + (float)offset;
+  int64_t v = (int64_t)std::nearbyintf(r);
+  v = v < -128 ? -128 : (v > 127 ? 127 : v);
+  return (int8_t)v;
+}
+
+}  // namespace glowb200
+
+extern "C" void glowb200_choose_quantization_params(float min, float max, int schema, int quantized_bits, float *scale,
+                                                    int32_t *offset) {
+  // int8 / int16 use their full range; int32 is limited to 30 bits (getQuantizedRange, Base.cpp:361-403)
+  int64_t qmin = -128, qmax = 127;
+  if (quantized_bits == 16) { qmin = -32768; qmax = 32767; }
+  if (quantized_bits == 32) { qmin = (int64_t)INT32_MIN >> 2; qmax = (int64_t)INT32_MAX >> 2; }
+  glowb200::choose_quantization_params(min, max, schema, qmin, qmax, *scale, *offset);
+}
+
+// tensorRowwiseQuantization<float, int32_t, int8_t> (include/glow/Quantization/Base/Base.h:522-576):
+// every row gets its own (scale, offset) from its min/max.  HOST arrays.
+extern "C" int glowb200_tensor_rowwise_quantize_i8(const float *in, int64_t rows, int64_t cols, int schema, int8_t *out,
+                                                   float *scales, int32_t *offsets) {
+  GLOWB200_REQUIRE(rows >= 0 && cols > 0 && in && out && scales && offsets, "bad arguments");
+  for (int64_t i = 0; i < rows; i++) {
+    const float *r = in + i * cols;
+    float mn = r[0], mx = r[0];
+    for (int64_t j = 1; j < cols; j++) { mn = r[j] < mn ? r[j] : mn; mx = r[j] > mx ? r[j] : mx; }
+    float scale;
+    int32_t offset;
+    glowb200::choose_quantization_params(mn, mx, schema, -128, 127, scale, offset);
+    for (int64_t j = 0; j < cols; j++) out[i * cols + j] = glowb200::quantize_i8(r[j], scale, offset);
+    scales[i] = scale;
+    offsets[i] = offset;
+  }
+  return GLOWB200_OK;
+}
+
+// quantization::quantize<int32_t>-style bias quantisation with a given scale/offset
+// (quantizeTensor, lib/Quantization/Base/Base.cpp; the int32 range is the 30-bit one).
+extern "C" int glowb200_quantize_bias_i32(const float *in, int64_t n, float scale, int32_t offset, int32_t *out) {
+  GLOWB200_REQUIRE(n >= 0 && (n == 0 || (in && out)), "bad arguments");
+  const int64_t qmin = (int64_t)INT32_MIN >> 2, qmax = (int64_t)INT32_MAX >> 2;
+  for (int64_t i = 0; i < n; i++) {
+    const float r = in[i] / scale + (float)offset;
+    int64_t v = (int64_t)std::nearbyintf(r);
+    out[i] = (int32_t)(v < qmin ? qmin : (v > qmax ? qmax : v));
   }
   return GLOWB200_OK;
 }

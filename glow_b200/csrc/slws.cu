@@ -353,6 +353,13 @@ __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN
 
   // Every bag writes its row, empty bags write zeros (the reference zero-fills dest first).
   const int64_t dest_stride = jp->dest_stride;
+  void *dest_base = jp->dest;
+  int64_t dest_row = bag;
+  if (jp->bags_per_dest > 0) {  // scatter over several (possibly remote) destination buffers
+    const int64_t which = bag / jp->bags_per_dest;
+    dest_base = jp->dests[which];
+    dest_row = bag - which * jp->bags_per_dest;
+  }
 #pragma unroll
   for (int c = 0; c < P; c++) {
     if (!has[c]) continue;
@@ -361,7 +368,7 @@ __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN
 #pragma unroll
     for (int i = 0; i < 8; i++) o[i] = ACC16 ? acc[c][i] : (acc[c][i] + bias_sum);
     if constexpr (OUT16) {
-      __half *d = reinterpret_cast<__half *>(jp->dest) + bag * dest_stride + col;
+      __half *d = reinterpret_cast<__half *>(dest_base) + dest_row * dest_stride + col;
       __half2 h[4];
 #pragma unroll
       for (int i = 0; i < 4; i++) h[i] = __floats2half2_rn(o[2 * i], o[2 * i + 1]);
@@ -372,7 +379,7 @@ __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN
         for (int i = 0; i < 4; i++) *reinterpret_cast<__half2 *>(d + 2 * i) = h[i];
       }
     } else {
-      float *d = reinterpret_cast<float *>(jp->dest) + bag * dest_stride + col;
+      float *d = reinterpret_cast<float *>(dest_base) + dest_row * dest_stride + col;
       if ((reinterpret_cast<uintptr_t>(d) & 15u) == 0) {
         *reinterpret_cast<float4 *>(d) = make_float4(o[0], o[1], o[2], o[3]);
         *reinterpret_cast<float4 *>(d + 4) = make_float4(o[4], o[5], o[6], o[7]);
@@ -442,8 +449,15 @@ __global__ void __launch_bounds__(256) slws_gather_any_kernel(const __grid_const
     for (int s = 0; s < 4; s++) {
       const int k = tile + s * 32 + lane;
       if (k < D) {
-        if (out16) reinterpret_cast<__half *>(jp->dest)[bag * jp->dest_stride + k] = __float2half_rn(acc[s]);
-        else reinterpret_cast<float *>(jp->dest)[bag * jp->dest_stride + k] = acc[s];
+        void *dest_base = jp->dest;
+        int64_t dest_row = bag;
+        if (jp->bags_per_dest > 0) {
+          const int64_t which = bag / jp->bags_per_dest;
+          dest_base = jp->dests[which];
+          dest_row = bag - which * jp->bags_per_dest;
+        }
+        if (out16) reinterpret_cast<__half *>(dest_base)[dest_row * jp->dest_stride + k] = __float2half_rn(acc[s]);
+        else reinterpret_cast<float *>(dest_base)[dest_row * jp->dest_stride + k] = acc[s];
       }
     }
   }

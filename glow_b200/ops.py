@@ -147,6 +147,38 @@ def embedding_bag_byte_rowwise_offsets(data, weights, indices, offsets, kind=UIN
 # ------------------------------------------------------------------------------------------
 FC_WEIGHT_OFFSETS_ZERO = 1
 FC_FORCE_ANY_SHAPE_KERNEL = 2
+FC_FUSE_RELU = 4
+
+ASYMMETRIC, SYMMETRIC, SYMMETRIC_WITH_UNSIGNED, SYMMETRIC_WITH_POWER2_SCALE = 0, 1, 2, 3
+
+
+def choose_quantization_params(mn, mx, schema=ASYMMETRIC, bits=8):
+    """(scale, offset) for a float range -- host computation (chooseQuantizationParams)."""
+    sc, off = C.c_float(), C.c_int32()
+    _lib.lib().glowb200_choose_quantization_params(C.c_float(float(mn)), C.c_float(float(mx)), int(schema), int(bits),
+                                                   C.byref(sc), C.byref(off))
+    return float(sc.value), int(off.value)
+
+
+def tensor_rowwise_quantize_i8(w, schema=ASYMMETRIC):
+    """Host rowwise quantisation of a float32 numpy matrix -> (int8, scales, offsets) numpy arrays."""
+    import numpy as np
+    w = np.ascontiguousarray(w, np.float32)
+    rows, cols = w.shape
+    q, sc, off = np.empty((rows, cols), np.int8), np.empty(rows, np.float32), np.empty(rows, np.int32)
+    check(_lib.lib().glowb200_tensor_rowwise_quantize_i8(C.c_void_p(w.ctypes.data), rows, cols, int(schema),
+                                                         C.c_void_p(q.ctypes.data), C.c_void_p(sc.ctypes.data),
+                                                         C.c_void_p(off.ctypes.data)))
+    return q, sc, off
+
+
+def quantize_bias_i32(b, scale, offset=0):
+    import numpy as np
+    b = np.ascontiguousarray(b, np.float32)
+    out = np.empty(b.shape, np.int32)
+    check(_lib.lib().glowb200_quantize_bias_i32(C.c_void_p(b.ctypes.data), b.size, C.c_float(float(scale)), int(offset),
+                                                C.c_void_p(out.ctypes.data)))
+    return out
 
 
 def quantize_scale_offset_32to8(scale):
@@ -362,6 +394,60 @@ def transpose(src, shuffle):
     return out
 
 
+def pairwise_dot_interaction(dense, pooled, *, quant=None, out=None):
+    """dense fp32 [B, D]; pooled fp32 [B, T, D] (or [B, T*D]).  Returns fp32 [B, D + n(n-1)/2]
+    (n = T + 1), or int8 when quant=(scale, offset) (the following Quantize node fused)."""
+    _cuda(dense, "dense", (torch.float32,))
+    _cuda(pooled, "pooled", (torch.float32,))
+    B, D = dense.shape
+    T = pooled.numel() // (B * D) if B else 0
+    n = T + 1
+    width = D + n * (n - 1) // 2
+    if out is None:
+        out = torch.empty((B, width), dtype=torch.int8 if quant else torch.float32, device=dense.device)
+    q = quant or (1.0, 0)
+    check(_lib.lib().glowb200_pairwise_dot_interaction(
+        _p(dense), D, _p(pooled), T * D, B, T, D, None if quant else _p(out), _p(out) if quant else None, width,
+        C.c_float(float(q[0])), int(q[1]), _stream()))
+    return out
+
+
+class PeerBuffer:
+    """Device memory the other GPUs of the node can store into (set-up time object).
+    `handle` (64 bytes) is what the owning process sends to its peers; `open` maps a peer's."""
+
+    def __init__(self, nbytes):
+        ptr = C.c_void_p()
+        h = (C.c_ubyte * 64)()
+        check(_lib.lib().glowb200_peer_buffer_create(int(nbytes), C.byref(ptr), h))
+        self.ptr, self.nbytes, self.handle = int(ptr.value), int(nbytes), bytes(h)
+        self._opened = []
+
+    def open(self, handle):
+        ptr = C.c_void_p()
+        buf = (C.c_ubyte * 64).from_buffer_copy(handle)
+        check(_lib.lib().glowb200_peer_buffer_open(buf, C.byref(ptr)))
+        self._opened.append(int(ptr.value))
+        return int(ptr.value)
+
+    def as_tensor(self, shape, dtype):
+        """A torch view of the local buffer (no copy)."""
+        class _Raw:
+            pass
+        raw = _Raw()
+        typestr = {torch.float32: "<f4", torch.uint8: "|u1", torch.int8: "|i1", torch.float16: "<f2"}[dtype]
+        raw.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (self.ptr, False), "version": 3}
+        return torch.as_tensor(raw, device="cuda")
+
+    def release(self):
+        for p in self._opened:
+            _lib.lib().glowb200_peer_buffer_close(C.c_void_p(p))
+        self._opened = []
+        if self.ptr:
+            _lib.lib().glowb200_peer_buffer_destroy(C.c_void_p(self.ptr))
+            self.ptr = 0
+
+
 class SlwsBatch:
     """A fixed set of tables of one kind and row width, pooled by ONE launch per request.
 
@@ -382,28 +468,38 @@ class SlwsBatch:
         self.workspace = None
         self._keep = None
 
-    def bind(self, tables, weights, indices, lengths, dests, dest_stride=None):
+    def bind(self, tables, weights, indices, lengths, dests, dest_stride=None, scatter=None, bags_per_dest=0):
+        """scatter: optional list (one entry per table) of lists of destination base addresses
+        (ints, possibly in other GPUs' memory); bag b of table i then goes to row
+        b % bags_per_dest of scatter[i][b // bags_per_dest]."""
         n = len(tables)
         arr = (SlwsJob * n)()
         odt = result_dtype(self.kind)
         self.max_segments = 0
         for i in range(n):
             _cuda(tables[i], "table", (torch.uint8,))
-            _cuda(weights[i], "weights", (dests[i].dtype,))
+            _cuda(weights[i], "weights", (odt, torch.float16))
             _cuda(indices[i], "indices", (self.index_dtype,))
             _cuda(lengths[i], "lengths", (torch.int32,))
             if tables[i].shape[1] != self.in_line:
                 raise ValueError("all tables of a batch share one row width")
-            if dests[i].dtype != odt and not (dests[i].dtype == torch.float16):
-                raise TypeError("bad result dtype")
             j = arr[i]
             j.data, j.weights, j.indices = tables[i].data_ptr(), weights[i].data_ptr(), indices[i].data_ptr()
-            j.lengths, j.dest = lengths[i].data_ptr(), dests[i].data_ptr()
+            j.lengths = lengths[i].data_ptr()
+            j.dest = dests[i].data_ptr() if dests is not None else 0
             j.rows, j.num_indices = tables[i].shape[0], indices[i].shape[0]
             j.dest_stride = self.out_line if dest_stride is None else dest_stride
             j.segments = lengths[i].shape[0]
             self.max_segments = max(self.max_segments, j.segments)
-        self.out_fp16 = int(dests[0].dtype == torch.float16) if n else 0
+        self._scatter_dev = None
+        if scatter is not None:
+            per = len(scatter[0])
+            flat = torch.tensor([a for row in scatter for a in row], dtype=torch.int64).to(self.device)
+            self._scatter_dev = flat
+            for i in range(n):
+                arr[i].dests = flat.data_ptr() + 8 * per * i
+                arr[i].bags_per_dest = int(bags_per_dest)
+        self.out_fp16 = int(weights[0].dtype == torch.float16) if n else 0
         host = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8) if n else torch.empty(0, dtype=torch.uint8)
         self.jobs_dev = host.to(self.device)
         self.num_jobs = n

@@ -71,6 +71,13 @@ typedef struct glowb200_slws_job {
   int64_t num_indices;    /* entries readable in indices / weights                           */
   int64_t dest_stride;    /* elements between consecutive result rows (>= out_line_size)     */
   int64_t segments;       /* number of bags                                                  */
+  /* Optional scatter of the bags over several destination buffers -- the pooled-embedding
+   * exchange of a table-sharded model done by the pooling kernel itself: when bags_per_dest > 0,
+   * bag b is written to row b % bags_per_dest of dests[b / bags_per_dest] instead of `dest`.
+   * `dests` is a DEVICE array of pointers, which may address other GPUs' memory (see
+   * glowb200_peer_buffer_*); the stores are ordinary peer stores. */
+  void *const *dests;
+  int64_t bags_per_dest;
 } glowb200_slws_job;
 
 /* Bytes of scratch the gather-pool entry points need for `num_jobs` tables of at most
@@ -141,9 +148,27 @@ int glowb200_rowwise_requant_params(const float *row_scales, int64_t n, float in
                                     int32_t *bias_scale, int32_t *out_pre, int32_t *out_post,
                                     int32_t *out_scale_int);
 
+/* chooseQuantizationParams without calibration (lib/Quantization/Base/Base.cpp:433-565): scale
+ * and zero point for a float range.  schema: 0 Asymmetric, 1 Symmetric, 2 SymmetricWithUnsigned,
+ * 3 SymmetricWithPower2Scale; quantized_bits 8, 16 or 32 (32 uses Glow's 30-bit range).  HOST. */
+void glowb200_choose_quantization_params(float min, float max, int schema, int quantized_bits,
+                                         float *scale, int32_t *offset);
+
+/* tensorRowwiseQuantization<float,int32_t,int8_t> (include/glow/Quantization/Base/Base.h:522-576),
+ * what Function::createRowwiseQuantizedFullyConnected (lib/Graph/Graph.cpp:1198-1246) runs on a
+ * constant weight matrix at compile time.  HOST function over host arrays. */
+int glowb200_tensor_rowwise_quantize_i8(const float *in, int64_t rows, int64_t cols, int schema,
+                                        int8_t *out, float *scales, int32_t *offsets);
+
+/* Bias to int32 with a given scale / offset (quantization::quantize, Base.h:322-329, clipped to
+ * the 30-bit range of getQuantizedRange, Base.cpp:361-403).  HOST function. */
+int glowb200_quantize_bias_i32(const float *in, int64_t n, float scale, int32_t offset, int32_t *out);
+
 /* Hints in `flags`. */
 #define GLOWB200_FC_WEIGHT_OFFSETS_ZERO 1      /* every weight offset is 0: skips the input row sums */
 #define GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL 2   /* run the plain one-thread-per-output kernel          */
+#define GLOWB200_FC_FUSE_RELU 4                /* max(x, out_offset) in the epilogue: the int8 Relu that
+                                                  follows the layer when both share one output type    */
 
 /* Scratch bytes the three entry points below may need for an [M,K] x [N,K]^T problem. */
 size_t glowb200_i8_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N);
@@ -272,6 +297,33 @@ int glowb200_avg_pool_i8(const int8_t *in, int8_t *out, const int64_t *in_dims,
  * _f, libjit.cpp:1945-...): dest dims[i] = src_dims[shuffle[i]].  src_dims / shuffle are HOST arrays. */
 int glowb200_transpose(const void *src, void *dest, const int64_t *src_dims, const int32_t *shuffle,
                        int num_dims, int element_bytes, glowb200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Recommendation-model pieces
+ * ------------------------------------------------------------------------------------- */
+
+/* Pairwise-dot feature interaction.  For each of `batch` samples: n = tables + 1 vectors of `dim`
+ * fp32 values (v_0 = dense[b], v_t = pooled[b, t-1]); the result row is v_0 followed by the
+ * dot products v_i.v_j for j < i in row-major order (dim + n(n-1)/2 values), written as fp32
+ * (out_f32) or quantized to int8 with quant_scale / quant_offset (out_i8) -- exactly one of the
+ * two outputs is given.  ld_* are row pitches in elements.  The reference composes this from
+ * Concat / Reshape / BatchMatMul / flatten nodes
+ * (tests/unittests/RecommendationSystemTest.cpp:640-680) and has no single kernel for it. */
+int glowb200_pairwise_dot_interaction(const float *dense, int64_t ld_dense, const float *pooled,
+                                      int64_t ld_pooled, int64_t batch, int64_t tables, int64_t dim,
+                                      float *out_f32, int8_t *out_i8, int64_t ld_out,
+                                      float quant_scale, int32_t quant_offset,
+                                      glowb200_stream_t stream);
+
+/* Device buffers other GPUs of the node can store into (one process per GPU): create exports
+ * a 64-byte handle, open maps a peer's handle, close / destroy undo them.  Set-up time only:
+ * create and destroy allocate and free device memory.  The reference hands tensors between
+ * devices through host buffers (lib/Runtime/Executor/NetworkExecutionState.cpp:191-203); this
+ * replaces that hand-off for the pooled embeddings. */
+int glowb200_peer_buffer_create(size_t bytes, void **device_ptr, void *ipc_handle_64_bytes);
+int glowb200_peer_buffer_open(const void *ipc_handle_64_bytes, void **device_ptr);
+int glowb200_peer_buffer_close(void *device_ptr);
+int glowb200_peer_buffer_destroy(void *device_ptr);
 
 /* FusedRowwiseQuantizedSparseLengthsWeightedSum for callers that can neither allocate device
  * memory nor size a workspace per request.  (No counterpart in the reference: its CPU kernels

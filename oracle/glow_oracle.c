@@ -543,3 +543,71 @@ ORC_API void orc_avg_pool_i8(const int8_t *in, int8_t *out, const int64_t *in_di
           out[((n * OH + oh) * OW + ow) * C + c] = r;
         }
 }
+
+/* ------------------------------------------------------------------------------------ */
+/* Host-side weight preparation.                                                         */
+/* ------------------------------------------------------------------------------------ */
+
+/* chooseQuantizationParams, Calibration::None: lib/Quantization/Base/Base.cpp:433-565.
+ * schema 0 Asymmetric, 1 Symmetric, 2 SymmetricWithUnsigned, 3 SymmetricWithPower2Scale. */
+ORC_API void orc_choose_quantization_params(float min, float max, int schema, int64_t qmin, int64_t qmax,
+                                            float *scale_out, int32_t *offset_out) {
+  if (min > 0.f) min = 0.f;
+  if (max < 0.f) max = 0.f;
+  if (schema == 2 && !(min >= 0.f)) schema = 1;
+  if (schema == 1 || schema == 3) {
+    double rmin = min / (double)qmin, rmax = max / (double)qmax;
+    if (rmin > rmax) max = (float)(rmin * qmax); else min = (float)(rmax * qmin);
+  }
+  double scale = ((double)max - min) / ((double)qmax - qmin);
+  if (scale == 0) scale = 0.1;
+  double zmin = qmin - min / scale, zmax = qmax - max / scale;
+  double emin = fabs((double)qmin) + fabs(min / scale), emax = fabs((double)qmax) + fabs(max / scale);
+  double zp = emin < emax ? zmin : zmax;
+  if (fabsf(max + min) <= 1.1920928955078125e-07f) zp = 0;
+  int32_t nudged;
+  if (zp < qmin) nudged = (int32_t)qmin; else if (zp > qmax) nudged = (int32_t)qmax; else nudged = (int32_t)round(zp);
+  if (schema == 3) scale = exp2(ceil(log2(scale)));
+  *scale_out = (float)scale;
+  *offset_out = nudged;
+}
+
+/* tensorRowwiseQuantization<float,int32_t,int8_t>: include/glow/Quantization/Base/Base.h:522-576,
+ * with quantization::quantize (:322-329). */
+ORC_API void orc_tensor_rowwise_quantize_i8(const float *in, int64_t rows, int64_t cols, int schema, int8_t *out,
+                                            float *scales, int32_t *offsets) {
+  for (int64_t i = 0; i < rows; i++) {
+    const float *r = in + i * cols;
+    float mn = r[0], mx = r[0];
+    for (int64_t j = 1; j < cols; j++) { if (r[j] < mn) mn = r[j]; if (r[j] > mx) mx = r[j]; }
+    orc_choose_quantization_params(mn, mx, schema, -128, 127, &scales[i], &offsets[i]);
+    for (int64_t j = 0; j < cols; j++) {
+      float t = r[j] / scales[i] + (float)offsets[i];
+      int64_t v = (int64_t)nearbyintf(t);
+      out[i * cols + j] = (int8_t)(v < -128 ? -128 : (v > 127 ? 127 : v));
+    }
+  }
+}
+
+/* Pairwise-dot feature interaction of the benchmark's recommendation model: no single kernel in
+ * the reference (it composes Concat/Reshape/BatchMatMul, tests/unittests/
+ * RecommendationSystemTest.cpp:640-680); this restates the definition the CUDA kernel
+ * implements: out[b] = [v_0 | v_i.v_j for j < i, row-major], every dot product a sequential
+ * fp32 FMA chain over the components. */
+ORC_API void orc_pairwise_dot_interaction(const float *dense, const float *pooled, int64_t batch, int64_t tables,
+                                          int64_t dim, float *out) {
+  const int64_t n = tables + 1, width = dim + n * (n - 1) / 2;
+  for (int64_t b = 0; b < batch; b++) {
+    float *o = out + b * width;
+    for (int64_t k = 0; k < dim; k++) o[k] = dense[b * dim + k];
+    int64_t p = dim;
+    for (int64_t i = 1; i < n; i++)
+      for (int64_t j = 0; j < i; j++) {
+        const float *a = pooled + (b * tables + (i - 1)) * dim;
+        const float *c = j == 0 ? dense + b * dim : pooled + (b * tables + (j - 1)) * dim;
+        float acc = 0.0f;
+        for (int64_t k = 0; k < dim; k++) acc = fmaf(a[k], c[k], acc);
+        o[p++] = acc;
+      }
+  }
+}

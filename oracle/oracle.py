@@ -111,6 +111,23 @@ def f32_to_f16_bits(a):
     return np.array([f(float(x)) for x in a], dtype=np.uint16)
 
 
+def choose_quantization_params(mn, mx, schema=0, qmin=-128, qmax=127):
+    """-> (scale float32, offset int) of chooseQuantizationParams without calibration."""
+    sc, off = C.c_float(), C.c_int32()
+    lib().orc_choose_quantization_params(_f32(float(np.float32(mn))), _f32(float(np.float32(mx))), C.c_int(schema),
+                                         _i64(qmin), _i64(qmax), C.byref(sc), C.byref(off))
+    return np.float32(sc.value), int(off.value)
+
+
+def tensor_rowwise_quantize_i8(w, schema=0):
+    """-> (int8 [rows, cols], float32 scales [rows], int32 offsets [rows])."""
+    w = _c(w, np.float32)
+    rows, cols = w.shape
+    q, sc, off = np.empty((rows, cols), np.int8), np.empty(rows, np.float32), np.empty(rows, np.int32)
+    lib().orc_tensor_rowwise_quantize_i8(_ptr(w), _i64(rows), _i64(cols), C.c_int(schema), _ptr(q), _ptr(sc), _ptr(off))
+    return q, sc, off
+
+
 # ---------------------------------------------------------------------------- tables
 def fused_line_bytes(cols, kind):
     payload = cols // 2 if kind >= 2 else cols
@@ -363,6 +380,16 @@ def avg_pool_i8(inp, out_hw, kernels, strides, pads, count_include_pads, out_off
                           _ptr(_dims(*kernels)), _ptr(_dims(*strides)), _ptr(_dims(*pads)),
                           C.c_int(int(count_include_pads)), _i32(out_offset), _i32(in_offset),
                           *[_i32(int(v)) for v in triple])
+    return out
+
+
+def pairwise_dot_interaction(dense, pooled):
+    dense, pooled = _c(dense, np.float32), _c(pooled, np.float32)
+    B, D = dense.shape
+    T = pooled.size // (B * D)
+    n = T + 1
+    out = np.empty((B, D + n * (n - 1) // 2), np.float32)
+    lib().orc_pairwise_dot_interaction(_ptr(dense), _ptr(pooled), _i64(B), _i64(T), _i64(D), _ptr(out))
     return out
 
 

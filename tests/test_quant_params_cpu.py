@@ -38,3 +38,38 @@ def test_random_scales_match_oracle(ops, oracle):
         want = oracle.rowwise_requant_params(ws, 0.05, bias_scales, 0.5)
         for a, b in zip(got, want):
             np.testing.assert_array_equal(a, b)
+
+
+def test_choose_quantization_params_known_answers(ops, oracle):
+    """tests/unittests/QuantizationTest.cpp:1751-1857."""
+    asym = lambda a, b: ops.choose_quantization_params(a, b, ops.ASYMMETRIC)
+    sym = lambda a, b: ops.choose_quantization_params(a, b, ops.SYMMETRIC)
+    s, o = asym(0.0, 6.0); assert o == -128 and abs(s - 6.0 / 255) < 1e-3
+    s, o = asym(-3.0, 3.0); assert o == 0 and abs(s - 6.0 / 255) < 1e-3
+    s, o = asym(-2.0, 5.0); assert o == int(2.0 * 255 / 7.0 - 128) and abs(s - 7.0 / 255) < 1e-3
+    s, o = asym(2.0, 5.0); assert o == -128 and abs(s - 5.0 / 255) < 1e-3
+    s, o = asym(-8.0, -2.0); assert o == 127 and abs(s - 8.0 / 255) < 1e-3
+    for rng, want in [((0.0, 6.0), 12.0), ((-3.0, 3.0), 6.0), ((-2.0, 5.0), 10.0), ((2.0, 5.0), 10.0), ((-8.0, -2.0), 16.0)]:
+        s, o = sym(*rng)
+        assert o == 0 and abs(s - want / 255) < 1e-3
+    rng = np.random.default_rng(3)
+    for _ in range(2000):
+        a, b = np.sort(rng.standard_normal(2).astype(np.float32) * np.float32(10.0) ** rng.integers(-3, 3))
+        for schema in range(4):
+            got = ops.choose_quantization_params(a, b, schema)
+            want = oracle.choose_quantization_params(a, b, schema)
+            assert np.float32(got[0]) == want[0] and got[1] == want[1]
+
+
+def test_tensor_rowwise_quantize_matches_oracle(ops, oracle):
+    rng = np.random.default_rng(8)
+    w = (rng.standard_normal((200, 333)) * rng.uniform(0.01, 2, (200, 1))).astype(np.float32)
+    w[3] = 0
+    w[4] = np.abs(w[4])
+    for schema in (0, 1, 2):
+        got, want = ops.tensor_rowwise_quantize_i8(w, schema), oracle.tensor_rowwise_quantize_i8(w, schema)
+        for a, b in zip(got, want):
+            np.testing.assert_array_equal(a, b)
+    q, sc, off = ops.tensor_rowwise_quantize_i8(w, 0)
+    deq = sc[:, None] * (q.astype(np.float32) - off[:, None])
+    assert np.max(np.abs(deq - w) / np.maximum(np.abs(w).max(1, keepdims=True), 1e-6)) < 0.01
