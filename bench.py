@@ -331,6 +331,100 @@ def run_int8_fc_line(args):
         dist.destroy_process_group()
 
 
+def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges):
+    """DLRM-style model of the fourth benchmark configuration: 64 tables x 4,000,000 rows x 128
+    (uint8 fused rows), batch 4096, power-law bag lengths (mean 40, max 200) and row indices,
+    bottom MLP 256-512-256-128, pairwise-dot interaction (2208 wide), top MLP 2208-1024-1024-512-1,
+    all dense layers int8 rowwise FC.  Tables sharded by table over the ranks, dense layers
+    batch-sharded; samples/s = 4096 / (time per step), device-timed, max over ranks.
+    Returns {exchange: {...}} for every exchange form in `exchanges`."""
+    from glow_b200 import dlrm
+    cfg = dlrm.DLRMConfig()
+    mine = dlrm.tables_of_rank(cfg, rank, world)
+    tables = {t: dlrm.make_table(cfg, t, dev) for t in mine}
+    fm = dlrm.float_model(cfg)
+    ranges = dlrm.calibrate(cfg, fm, tables, dev, rank, world)
+    qm = dlrm.quantize_model(cfg, fm, ranges)
+    lo, hi = dlrm.batch_slice(cfg, rank, world)
+    R = 2
+    host = []
+    for r in range(R):
+        dense, lengths, indices = dlrm.make_request(cfg, 100 + r, tables=mine)
+        host.append((dense[lo:hi].contiguous().pin_memory(), {t: v.pin_memory() for t, v in lengths.items()},
+                     {t: v.pin_memory() for t, v in indices.items()}))
+    results = {}
+    for exchange in exchanges:
+        model = dlrm.DLRMRank(cfg, qm, tables, rank, world, dev, exchange)
+        if exchange == "fused":
+            model.connect_peers()
+        devr = [(h[0].to(dev), {t: v.to(dev) for t, v in h[1].items()}, {t: v.to(dev) for t, v in h[2].items()})
+                for h in host]
+        bound = [[model.prepare(d[1], d[2], slab) for slab in range(2)] for d in devr]
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        def step(i):
+            return model.forward(devr[i % R][0], bound[i % R])
+
+        for i in range(max(3, warmup)):
+            step(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            step(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        assert int(model.status.item()) == 0
+        # end to end: this rank's slice of the dense features and the lookups of its tables come
+        # from pinned host memory every step; the scores go back to the host
+        stage = [(torch.empty_like(d[0]), {t: torch.empty_like(v) for t, v in d[1].items()},
+                  {t: torch.empty_like(v) for t, v in d[2].items()}) for d in devr]
+        ebound = [[model.prepare(sg[1], sg[2], slab) for slab in range(2)] for sg in stage]
+        out_host = torch.empty((hi - lo, 1), dtype=torch.float32).pin_memory()
+        h2d = sum(host[0][0].numel() * 4 + sum(v.numel() * 4 for v in host[0][1].values()) +
+                  sum(v.numel() * 8 for v in host[0][2].values()) for _ in range(1))
+
+        def e2e_step(i):
+            h, sg = host[i % R], stage[i % R]
+            sg[0].copy_(h[0], non_blocking=True)
+            for t in mine:
+                sg[1][t].copy_(h[1][t], non_blocking=True)
+                sg[2][t].copy_(h[2][t], non_blocking=True)
+            out_host.copy_(model.forward(sg[0], ebound[i % R]), non_blocking=True)
+
+        for i in range(2):
+            e2e_step(i)
+        barrier()
+        n_e2e = max(3, min(steps, 10))
+        e0.record()
+        for i in range(n_e2e):
+            e2e_step(i)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / n_e2e
+        t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        results[exchange] = {"samples_per_s": cfg.batch / (float(t[0]) * 1e-3), "ms_per_step": float(t[0]),
+                             "e2e_samples_per_s": cfg.batch / (float(t[1]) * 1e-3), "e2e_ms_per_step": float(t[1]),
+                             "h2d_bytes_per_step_per_rank": int(h2d), "d2h_bytes_per_step_per_rank": (hi - lo) * 4,
+                             "launches_per_step": model.launches_per_step}
+        model.release()
+        del model, bound, ebound, devr, stage
+        torch.cuda.empty_cache()
+    del tables
+    torch.cuda.empty_cache()
+    return results, {"workload": "DLRM-style: 64 tables x 4,000,000 x 128 uint8 fused rows (table-sharded), batch 4096, "
+                                 "bag lengths power-law(1.05) mean 40 max 200, indices power-law(1.05) over rows, "
+                                 "int8 rowwise-FC MLPs 256-512-256-128 and 2208-1024-1024-512-1, pairwise-dot "
+                                 "interaction; dense layers batch-sharded", "tables": 64, "batch": 4096}
+
+
 def workload_config(T):
     return {"workload": "FRWQ-SLWS uint8 fused rows (config 1 law): %d tables x 1,000,000 rows x 64 cols "
                         "(72 B rows), 1024 bags/table, lengths clamp(Poisson(32),1,128), int64 indices, fp32 "
@@ -470,6 +564,23 @@ def main():
     value = float(sums[0]) / (total_ms_all * 1e-3) / 1e9
     e2e_value = float(sums[1]) / (e2e_ms_all * 1e-3) / 1e9
 
+    sample_tables = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        cpu_threads = os.cpu_count() or 1
+        S = min(T, max(cpu_threads, 16))
+        sample_tables = [tables[k].cpu().numpy() for k in range(S)]
+    dlrm_extra = None
+    if not args.no_extras:
+        # second headline of the same benchmark definition: the recommendation model, all ranks
+        del batches, e2e_batches, tables, devr, out, stage_i, stage_w, stage_l
+        torch.cuda.empty_cache()
+        forms = ["local"] if world == 1 else ["fused", "nccl"]
+        res, dcfg = dlrm_measure(torch, dist, dev, rank, world, max(10, min(args.steps, 30)), 3, forms)
+        best = max(res.values(), key=lambda r: r["samples_per_s"])
+        dlrm_extra = {"metric": "dlrm_samples_per_s", "value": best["samples_per_s"], "unit": "samples/s",
+                      "n_gpus": world, "scaling": "strong", "e2e_value": best["e2e_samples_per_s"],
+                      "by_exchange": res, "config": dcfg}
+
     if rank == 0:
         peak, peak_src = measured_peak_hbm()
         launch_us = float(np.mean(step_ms)) * 1e3
@@ -489,21 +600,20 @@ def main():
             "gpu_launches": 2 * args.steps,
             "clocks": clocks,
         }
+        if dlrm_extra is not None:
+            line.setdefault("extras", {})["dlrm"] = dlrm_extra
         if world == 1 and not args.no_extras:
             # secondary metric of the same benchmark definition: int8 FC throughput
-            del batches, e2e_batches
             fc = int8_fc_measure(torch, ops, dev, max(10, min(args.steps, 50)), 3)
             ipeak, isrc = measured_peak_int8()
-            line["extras"] = {"int8_fc": {
+            line.setdefault("extras", {})["int8_fc"] = {
                 "metric": "int8_fc_tops", "value": fc["tops"], "unit": "TOP/s", "us_per_launch": fc["ms"] * 1e3,
                 "e2e_value": fc["e2e_tops"], "config": fc_config(),
                 "roofline": {"bound": "tensor", "achieved": fc["tops"], "peak": ipeak, "frac": fc["tops"] / ipeak,
                              "peak_source": isrc, "nominal_dense_int8_tops": 4500.0,
-                             "library_int8_gemm_tops": fc["library_int8_gemm_tops"]}}}
+                             "library_int8_gemm_tops": fc["library_int8_gemm_tops"]}}
         if world == 1 and not args.no_cpu_baseline:
-            threads = os.cpu_count() or 1
-            S = min(T, max(threads, 16))
-            sample_tables = [tables[k].cpu().numpy() for k in range(S)]
+            threads, S = cpu_threads, len(sample_tables)
             v, kind, passes, dt = cpu_reference_rate(sample_tables, args.cpu_seconds, threads)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": kind,
                                     "sample": "first %d of %d tables, %d passes (a different batch each) in %.1f s, one "

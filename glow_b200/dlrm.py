@@ -372,18 +372,31 @@ class DLRMRank:
         return 2 + 1 + len(self.bottom) + 1 + 1 + len(self.top) + 1
 
 
-def calibrate(cfg, fm, tables_np_or_torch, device):
-    """Calibration pass: one seeded batch through the fp32 model (pooling in fp32 torch)."""
-    dense, lengths, indices = make_request(cfg, 999_983, device=device)
+def calibrate(cfg, fm, tables, device, rank=0, world=1, group=None):
+    """Calibration pass: one seeded batch through the fp32 model (pooling in fp32 torch).
+    `tables` holds this rank's tables; with world > 1 the pooled vectors of the calibration batch
+    are all-gathered so every rank derives the same ranges."""
+    mine = tables_of_rank(cfg, rank, world)
+    dense, lengths, indices = make_request(cfg, 999_983, tables=mine, device=device)
     D = cfg.dim
-    pooled = torch.empty((cfg.batch, cfg.tables, D), dtype=torch.float32, device=device)
-    for t in range(cfg.tables):
-        tab = tables_np_or_torch[t]
+    local = torch.empty((cfg.batch, len(mine), D), dtype=torch.float32, device=device)
+    for j, t in enumerate(mine):
+        tab = tables[t]
         rows = tab[indices[t]]
         sc = rows[:, D:D + 4].contiguous().view(torch.float32)
         of = rows[:, D + 4:].contiguous().view(torch.float32)
         deq = rows[:, :D].float() * sc + of
         seg = torch.repeat_interleave(torch.arange(cfg.batch, device=device), lengths[t].long())
-        pooled[:, t].zero_().index_add_(0, seg, deq)
+        local[:, j].zero_().index_add_(0, seg, deq)
+    pooled = torch.empty((cfg.batch, cfg.tables, D), dtype=torch.float32, device=device)
+    if world == 1:
+        pooled[:, mine] = local
+    else:
+        import torch.distributed as dist
+        for r in range(world):
+            tabs = tables_of_rank(cfg, r, world)
+            buf = local if r == rank else torch.empty((cfg.batch, len(tabs), D), dtype=torch.float32, device=device)
+            dist.broadcast(buf, src=r, group=group)
+            pooled[:, tabs] = buf
     _, ranges = float_forward(cfg, fm, dense, pooled)
     return ranges
