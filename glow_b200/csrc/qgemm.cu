@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "qgemm.cuh"
@@ -31,15 +32,31 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 128;          // bytes of K per pipeline stage = one 128B swizzle atom
 constexpr int kUmmaK = 32;            // K per tcgen05.mma for 8-bit operands
-constexpr int kGemmThreads = 192;     // 6 warps
+constexpr int kEpilogueWarps = 16;    // 4 per tensor-memory lane quarter: enough warps per scheduler to hide ALU latency
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+constexpr int kGemmThreads = 64 + kEpilogueThreads;  // TMA warp, MMA warp, epilogue warps
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s: far beyond any legitimate wait
 
-struct ColParams {  // per output column, built once per tile in shared memory
+// Per output column, built once per tile in shared memory and read back with ONE 16-byte
+// broadcast load per element.  Measured on B200: shared-memory loads issue at about one per
+// clock per SM and 32-bit integer instructions at about two warps per clock per SM, so the
+// epilogue spends integer work (unpacking the shifts, rebuilding the rounding term) to save
+// loads -- a 32-byte record with everything precomputed (two loads per element) was slower.
+struct __align__(16) ColParams {
   int32_t c;        // bias term - aOff*rowsum(B_j) + K*aOff*bOff_j
-  int32_t b_off;
+  int32_t scale;    // integer multiplier of the output rescale
   int32_t shifts;   // pre | post << 8
-  int32_t scale;
+  int32_t b_off;
 };
+
+// sat8(v3) sat8(v2) sat8(v1) sat8(v0) packed little-endian: libjit_clip_i8 on four values and the
+// byte packing in two instructions.
+__device__ __forceinline__ uint32_t clip_pack4(int32_t v0, int32_t v1, int32_t v2, int32_t v3) {
+  uint32_t hi, d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(v3), "r"(v2), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v1), "r"(v0), "r"(hi));
+  return d;
+}
 
 // ---------------------------------------------------------------------------------------
 // PTX wrappers
@@ -124,6 +141,15 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
@@ -144,6 +170,22 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 __host__ __device__ constexpr uint32_t idesc_i8(int m, int n) {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+
+// Optional phase tracing for tuning builds (-DGLOWB200_GEMM_TRACE): CTA 0 writes globaltimer
+// stamps to a device buffer the tuning harness reads back.  Compiled out by default.
+#ifdef GLOWB200_GEMM_TRACE
+__device__ unsigned long long g_gemm_trace[16];
+__device__ __forceinline__ void trace(int slot) {
+  if (blockIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_gemm_trace[slot] = t;
+  }
+}
+#define GEMM_TRACE(slot, cond) do { if (cond) trace(slot); } while (0)
+#else
+#define GEMM_TRACE(slot, cond) do { } while (0)
+#endif
 
 // ---------------------------------------------------------------------------------------
 // The tile kernel
@@ -179,6 +221,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  GEMM_TRACE(0, threadIdx.x == 0);
   const int m_tiles = (p.M + kBlockM - 1) / kBlockM, n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int tiles = m_tiles * n_tiles;
   const int k_blocks = (p.K + kBlockK - 1) / kBlockK;
@@ -192,7 +235,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], kEpilogueWarps);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -205,6 +248,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  GEMM_TRACE(1, threadIdx.x == 0);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -240,6 +284,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const int s = it % STAGES;
           if (!mbar_wait(&full[s], (it / STAGES) & 1, abort_flag)) { live = false; break; }
           tc_fence_after();
+          GEMM_TRACE(2, it == 0);
           const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
           const uint32_t b_addr = a_addr + S::kABytes;
           const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
@@ -252,19 +297,25 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
         }
         if (live) umma_commit(&acc_full[buf]);  // this tile's accumulators are complete
+        GEMM_TRACE(3, lt == 0);
       }
     }
   } else {
-    // ---------------- epilogue: warps 2..5 ----------------
-    const int et = threadIdx.x - 64;  // 0..127
-    const int quarter = warp & 3;     // TMEM lane quarter this warp may read
+    // ---------------- epilogue: warps 2..17 ----------------
+    // Warp w may read tensor-memory lanes 32*(w%4)..+31 only; the four warps that share a lane
+    // quarter split the tile's columns between them.
+    const int et = threadIdx.x - 64;          // 0..511
+    const int quarter = warp & 3;
+    const int col_group = (warp - 2) >> 2;     // 0..3
+    constexpr int kGroupCols = BLOCK_N / 4;    // columns per warp: 64 (BLOCK_N 256) or 16 (BLOCK_N 64)
+    constexpr int kChunk = kGroupCols >= 32 ? 32 : 16;
     const bool vec_ok = ((p.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     int lt = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, lt++) {
       const int m0 = (t % m_tiles) * kBlockM, n0 = (t / m_tiles) * BLOCK_N;
       const int buf = lt & 1;
       // (1) per-column constants of this tile (the main loop of this or the next tile is running)
-      for (int c = et; c < BLOCK_N; c += 128) {
+      for (int c = et; c < BLOCK_N; c += kEpilogueThreads) {
         const int j = n0 + c;
         ColParams cp = {0, 0, 0, 0};
         if (j < p.N) {
@@ -282,58 +333,92 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
         cols[c] = cp;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");  // epilogue warps only
       // (2) drain the accumulators of this tile
       const int row = m0 + quarter * 32 + lane;
-      // All 128 epilogue threads agree on the outcome of the (bounded) wait through a reducing
+      // All epilogue threads agree on the outcome of the (bounded) wait through a reducing
       // barrier, so either all of them drain the tile or all of them leave the loop.
       const uint32_t mine = mbar_wait(&acc_full[buf], (lt >> 1) & 1, abort_flag) ? 1u : 0u;
       uint32_t ok;
       asm volatile(
           "{\n\t.reg .pred p, q;\n\t"
           "setp.ne.u32 q, %1, 0;\n\t"
-          "barrier.cta.red.and.pred p, 1, 128, q;\n\t"
+          "barrier.cta.red.and.pred p, 1, %2, q;\n\t"
           "selp.u32 %0, 1, 0, p;\n\t}"
           : "=r"(ok)
-          : "r"(mine)
+          : "r"(mine), "n"(kEpilogueThreads)
           : "memory");
       tc_fence_after();
       if (!ok) break;
+      GEMM_TRACE(4, lt == 0 && et == 0);
       const int32_t a_sum = (p.a_row_sums && row < p.M) ? p.a_row_sums[row] : 0;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kAccCols;
       int8_t *out_row = p.out + (size_t)row * p.N + n0;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BLOCK_N; c0 += 32) {
+      for (int c0 = col_group * kGroupCols; c0 < (col_group + 1) * kGroupCols; c0 += kChunk) {
         uint32_t acc[32];
-        tmem_ld_32x32b_x32(lane_addr + (uint32_t)c0, acc);
+        if constexpr (kChunk == 32) tmem_ld_32x32b_x32(lane_addr + (uint32_t)c0, acc);
+        else tmem_ld_32x32b_x16(lane_addr + (uint32_t)c0, acc);
         tmem_ld_wait();
-        if (c0 + 32 >= BLOCK_N) {
+        GEMM_TRACE(7, lt == 0 && et == 0 && c0 == 0);
+        if (c0 + kChunk >= (col_group + 1) * kGroupCols) {
           // everything this warp needs from the buffer is in registers: hand it back
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
-        uint32_t packed[8];
+        uint32_t packed[kChunk / 4];
+        // the requantisation, specialised on the two things that are uniform over the launch:
+        // whether input row sums take part and which activation follows
+        auto requant = [&](auto with_row_sums, auto act) {
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const ColParams cp = cols[c0 + i];
-          uint32_t v = acc[i] + (uint32_t)cp.c - (uint32_t)cp.b_off * (uint32_t)a_sum;
-          const int32_t pre = cp.shifts & 0xff, post = cp.shifts >> 8;
-          const int32_t r = clip_i8(activation_i32(scale32((int32_t)v, pre, post, cp.scale, p.out_offset), p));
-          if ((i & 3) == 0) packed[i >> 2] = 0;
-          packed[i >> 2] |= (uint32_t)(r & 0xff) << (8 * (i & 3));
+          for (int i4 = 0; i4 < kChunk / 4; i4++) {
+            int32_t r[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const int4 cp = *reinterpret_cast<const int4 *>(&cols[c0 + 4 * i4 + e]);  // {c, scale, shifts, b_off}
+              uint32_t v = acc[4 * i4 + e] + (uint32_t)cp.x;
+              if constexpr (decltype(with_row_sums)::value) v -= (uint32_t)cp.w * (uint32_t)a_sum;
+              // libjit_scale: ((v >> pre) * scale + rtn) >> post, then + offset; rtn = 1 << (post-1), 0 for post 0
+              const int32_t pre = cp.z & 0xff, post = cp.z >> 8;
+              const uint32_t rtn = (1u << post) >> 1;
+              const int32_t m = (int32_t)((uint32_t)((int32_t)v >> pre) * (uint32_t)cp.y + rtn);
+              int32_t x = (int32_t)((uint32_t)(m >> post) + (uint32_t)p.out_offset);
+              if constexpr (decltype(act)::value == 1) x = x > p.out_offset ? x : p.out_offset;
+              if constexpr (decltype(act)::value == 2) x = activation_i32(x, p);
+              r[e] = x;
+            }
+            packed[i4] = clip_pack4(r[0], r[1], r[2], r[3]);
+          }
+        };
+        using std::integral_constant;
+        const int act_kind = p.act_type == 0 ? 0 : (p.act_type == 1 ? 1 : 2);
+        if (p.a_row_sums == nullptr) {
+          if (act_kind == 0) requant(integral_constant<bool, false>{}, integral_constant<int, 0>{});
+          else if (act_kind == 1) requant(integral_constant<bool, false>{}, integral_constant<int, 1>{});
+          else requant(integral_constant<bool, false>{}, integral_constant<int, 2>{});
+        } else {
+          if (act_kind == 0) requant(integral_constant<bool, true>{}, integral_constant<int, 0>{});
+          else if (act_kind == 1) requant(integral_constant<bool, true>{}, integral_constant<int, 1>{});
+          else requant(integral_constant<bool, true>{}, integral_constant<int, 2>{});
         }
+        GEMM_TRACE(8, lt == 0 && et == 0 && c0 == 0 && packed[0] != 0x12345678u);
         if (row < p.M) {
-          if (vec_ok && n0 + c0 + 32 <= p.N) {
-            *reinterpret_cast<uint4 *>(out_row + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            *reinterpret_cast<uint4 *>(out_row + c0 + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          if (vec_ok && n0 + c0 + kChunk <= p.N) {
+#pragma unroll
+            for (int v4 = 0; v4 < kChunk / 16; v4++)
+              *reinterpret_cast<uint4 *>(out_row + c0 + 16 * v4) =
+                  make_uint4(packed[4 * v4], packed[4 * v4 + 1], packed[4 * v4 + 2], packed[4 * v4 + 3]);
           } else {
-            for (int i = 0; i < 32; i++)
+            for (int i = 0; i < kChunk; i++)
               if (n0 + c0 + i < p.N) out_row[c0 + i] = (int8_t)((packed[i >> 2] >> (8 * (i & 3))) & 0xff);
           }
         }
+        GEMM_TRACE(9, lt == 0 && et == 0 && c0 == 0);
+        GEMM_TRACE(10, lt == 0 && et == 0 && c0 == 32);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // cols[] is rewritten for the next tile
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");  // cols[] is rewritten for the next tile
+      GEMM_TRACE(5, lt == 0 && et == 0);
     }
   }
 
@@ -352,6 +437,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  GEMM_TRACE(6, threadIdx.x == 32);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -519,6 +605,12 @@ int check_dims(int64_t M, int64_t K, int64_t N) {
 }  // namespace glowb200
 
 using namespace glowb200;
+
+#ifdef GLOWB200_GEMM_TRACE
+extern "C" int glowb200_debug_gemm_trace(unsigned long long *host16) {
+  return cudaMemcpyFromSymbol(host16, glowb200::g_gemm_trace, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 4;
+}
+#endif
 
 extern "C" size_t glowb200_i8_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N) {
   if (M < 0 || N < 0 || K < 0) return 0;
