@@ -23,6 +23,7 @@
 // that, step by step.
 #include "common.cuh"
 
+#include <climits>
 #include <mutex>
 
 namespace glowb200 {
@@ -40,6 +41,10 @@ struct SlwsLaunch {
   int32_t *status;
   int32_t in_line, out_line;
   int32_t lpr_log2;
+  // 1: the gather kernel picks, per table, the thread-to-bag mapping its bag-length profile
+  // favours (a word the segments kernel leaves behind the table's boundaries);
+  // 0: the group-per-bag mapping for every table.
+  int32_t select;
 };
 
 __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
@@ -120,6 +125,7 @@ __global__ void __launch_bounds__(kSegThreads) slws_segments_from_lengths_kernel
   constexpr int kItems = 4;
   int64_t carry = 0;
   int32_t flags = 0;
+  int64_t longest = 0;
   for (int64_t tile = 0; tile < S; tile += (int64_t)kSegThreads * kItems) {
     const int64_t first = tile + (int64_t)threadIdx.x * kItems;
     int64_t v[kItems], sum = 0;
@@ -129,6 +135,7 @@ __global__ void __launch_bounds__(kSegThreads) slws_segments_from_lengths_kernel
       if (l < 0) { l = 0; flags |= GLOWB200_STATUS_NEGATIVE_LENGTH; }
       v[i] = l;
       sum += l;
+      longest = l > longest ? l : longest;
     }
     int64_t tile_total;
     int64_t run = carry + block_exclusive_scan(sum, warp_tot, tile_total);
@@ -139,9 +146,22 @@ __global__ void __launch_bounds__(kSegThreads) slws_segments_from_lengths_kernel
     }
     carry += tile_total;
   }
+  // longest bag of the table (block-wide maximum through the scan's scratch)
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    const int64_t o = __shfl_xor_sync(0xffffffffu, longest, d);
+    longest = o > longest ? o : longest;
+  }
+  if ((threadIdx.x & 31) == 0) warp_tot[threadIdx.x >> 5] = longest;
+  __syncthreads();
   if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) longest = warp_tot[w] > longest ? warp_tot[w] : longest;
     if (carry > N) flags |= GLOWB200_STATUS_LENGTHS_OVERRUN;
     out[S] = carry < N ? carry : N;
+    // Bag-length profile: when the longest bag is more than 2.5 times the mean, bags that
+    // share a warp in lock step would wait for each other -- such a table goes to the kernel
+    // that gives every bag a whole warp.
+    out[S + 1] = (S > 0 && 2 * longest * S > 5 * carry) ? 1 : 0;
   }
   raise(p.status, flags);
 }
@@ -233,7 +253,7 @@ __device__ __forceinline__ float load_weight(const void *weights, int64_t i) {
 // Gather-pool.  grid = (ceil(max_segments / bags_per_block), num_jobs).
 // ------------------------------------------------------------------------------------------
 template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P>
-__global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
+__device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
   using RL = RowLoad<BITS, SO16>;
   const int job_id = blockIdx.y;
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + job_id) : &p.single;
@@ -392,6 +412,245 @@ __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN
   raise(p.status, flags);
 }
 
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P>
+__global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
+  gather_group_body<BITS, SO16, OUT16, ACC16, IdxT, P>(p);
+}
+
+// ------------------------------------------------------------------------------------------
+// Gather-pool, a WARP per run of consecutive bags (fp32 accumulation).
+//
+// The bags of a table are consecutive in its index array, so a warp that owns `bags_per_warp`
+// consecutive bags simply streams one contiguous piece of that array: 32 indices (one per
+// lane) are in hand, the next 32 are already requested, and bag boundaries only decide where
+// the running sums are reduced and stored.  The 32 lanes form 32/lpr row slots of lpr lanes;
+// the rows of a bag are dealt round-robin to the slots and the slots are summed with shuffles
+// when the bag ends.  Every lane of the warp works on the same bag, so bags of very different
+// lengths (power-law pooling factors) do not hold each other up the way they do when several
+// bags share a warp in lock step.  The summation order differs from the sequential one (inside
+// the fp32 tolerance); fp16 accumulation, whose rounding is defined step by step, stays on the
+// group-per-bag kernel above.
+// grid = (ceil(ceil(max_segments / bags_per_warp) / 8), num_jobs), 8 warps per block.
+// ------------------------------------------------------------------------------------------
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P>
+__device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_per_warp) {
+  using RL = RowLoad<BITS, SO16>;
+  constexpr int V = 8 * P;  // sums a lane carries
+  const int job_id = blockIdx.y;
+  const glowb200_slws_job *jp = p.jobs ? (p.jobs + job_id) : &p.single;
+  const int64_t segments = jp->segments;
+  const int64_t first_bag = ((int64_t)blockIdx.x * (kGatherThreads >> 5) + (threadIdx.x >> 5)) * bags_per_warp;
+  if (first_bag >= segments) return;  // whole warps leave together
+  const int n_bags = (int)((first_bag + bags_per_warp < segments ? first_bag + bags_per_warp : segments) - first_bag);
+  const int lane = threadIdx.x & 31;
+  const int lpr = 1 << p.lpr_log2, slots = 32 >> p.lpr_log2;
+  const int gl = lane & (lpr - 1), slot = lane >> p.lpr_log2;
+
+  const uint8_t *data = reinterpret_cast<const uint8_t *>(jp->data);
+  const int64_t rows = jp->rows;
+  const int64_t *sb = p.seg_begin + (int64_t)job_id * p.seg_stride + first_bag;
+  const int64_t run0 = sb[0];
+  // positions below are relative to run0 (a warp's run is far shorter than 2^31 indices)
+  const IdxT *indices = reinterpret_cast<const IdxT *>(jp->indices) + run0;
+  const void *weights = OUT16 ? (const void *)(reinterpret_cast<const __half *>(jp->weights) + run0)
+                              : (const void *)(reinterpret_cast<const float *>(jp->weights) + run0);
+  const int avail = (int)((jp->num_indices - run0) < (int64_t)INT32_MAX ? (jp->num_indices - run0) : (int64_t)INT32_MAX);
+  const int in_line = p.in_line;
+  const int chunks = p.out_line >> 3;
+  int32_t flags = 0;
+
+  bool has[P];
+#pragma unroll
+  for (int c = 0; c < P; c++) has[c] = (c * lpr + gl) < chunks;
+  float acc[V];
+  float bias_sum;
+  auto reset = [&]() {
+    bias_sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; i++) acc[i] = 0.0f;
+  };
+  reset();
+
+  // Row numbers travel as int32 (tables have fewer than 2^31 rows); -1 marks an index outside
+  // [0, rows), which is reported only if a bag really uses it (indices past the last bag are
+  // never looked at).
+  auto fetch = [&](int at, int32_t &r, float &w) {
+    r = -1;
+    w = 0.0f;
+    if (at < avail) {
+      const int64_t v = (int64_t)indices[at];
+      w = load_weight<OUT16>(weights, at);
+      if (v >= 0 && v < rows) r = (int32_t)v;
+    }
+  };
+
+  // Reduce the row slots and store the bag's row (the sums are consumed: reset() follows).
+  // Recursive halving: in every round a lane hands half of its values to its partner and keeps
+  // the other half, so after log2(slots) rounds the 8*P sums of a column group are spread over
+  // the slots (rounds that would go below one value per lane fall back to exchange-and-add).
+  auto flush = [&](int64_t bag) {
+    float bsum = bias_sum;
+    int first = 0, owned = V;
+#pragma unroll
+    for (int round = 0; round < 5; round++) {
+      const int off = 16 >> round;
+      if (off >= lpr) {
+        bsum += __shfl_xor_sync(0xffffffffu, bsum, off);
+        constexpr int kV = V;
+        const int nv = kV >> (round + 1);  // compile-time per round
+        const bool upper = (lane & off) != 0;
+        if (nv >= 1) {
+#pragma unroll
+          for (int i = 0; i < (nv > 0 ? nv : 1); i++) {
+            const float keep = upper ? acc[i + nv] : acc[i];
+            const float send = upper ? acc[i] : acc[i + nv];
+            acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+          }
+          first += upper ? nv : 0;
+          owned = nv;
+        } else {
+          acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
+          if (upper) owned = 0;
+        }
+      }
+    }
+    if (owned > 0) {
+      const int64_t dest_stride = jp->dest_stride;
+      void *dest_base = jp->dest;
+      int64_t dest_row = bag;
+      if (jp->bags_per_dest > 0) {  // scatter over several (possibly remote) destination buffers
+        const int64_t which = bag / jp->bags_per_dest;
+        dest_base = jp->dests[which];
+        dest_row = bag - which * jp->bags_per_dest;
+      }
+      const int c_first = first >> 3, i_first = first & 7;
+      if (owned >= 8) {  // whole chunks
+#pragma unroll
+        for (int c = 0; c < P; c++) {
+          if (c * 8 >= owned) break;
+          const int chunk = (c_first + c) * lpr + gl;
+          if (chunk >= chunks) continue;
+          const int64_t col = (int64_t)chunk * 8;
+          if constexpr (OUT16) {
+            __half *d = reinterpret_cast<__half *>(dest_base) + dest_row * dest_stride + col;
+            __half2 h[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) h[i] = __floats2half2_rn(acc[c * 8 + 2 * i] + bsum, acc[c * 8 + 2 * i + 1] + bsum);
+            if ((reinterpret_cast<uintptr_t>(d) & 15u) == 0) {
+              *reinterpret_cast<uint4 *>(d) = *reinterpret_cast<const uint4 *>(h);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; i++) *reinterpret_cast<__half2 *>(d + 2 * i) = h[i];
+            }
+          } else {
+            float *d = reinterpret_cast<float *>(dest_base) + dest_row * dest_stride + col;
+            if ((reinterpret_cast<uintptr_t>(d) & 15u) == 0) {
+              *reinterpret_cast<float4 *>(d) = make_float4(acc[c * 8] + bsum, acc[c * 8 + 1] + bsum, acc[c * 8 + 2] + bsum, acc[c * 8 + 3] + bsum);
+              *reinterpret_cast<float4 *>(d + 4) = make_float4(acc[c * 8 + 4] + bsum, acc[c * 8 + 5] + bsum, acc[c * 8 + 6] + bsum, acc[c * 8 + 7] + bsum);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; i++) d[i] = acc[c * 8 + i] + bsum;
+            }
+          }
+        }
+      } else {  // a piece of one chunk: 4, 2 or 1 consecutive columns
+        const int chunk = c_first * lpr + gl;
+        if (chunk < chunks) {
+          const int64_t col = (int64_t)chunk * 8 + i_first;
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            if (i >= owned) break;
+            if constexpr (OUT16) reinterpret_cast<__half *>(dest_base)[dest_row * dest_stride + col + i] = __float2half_rn(acc[i] + bsum);
+            else reinterpret_cast<float *>(dest_base)[dest_row * dest_stride + col + i] = acc[i] + bsum;
+          }
+        }
+      }
+    }
+  };
+
+  // The run is walked in blocks of 32 positions (the indices in hand).  Within a block the rows
+  // of the current bag are dealt to the slots kUnroll steps at a time: their loads are issued
+  // together, then pooled.  When the bag ends its sums are flushed and the next bag continues
+  // in the same block.
+  int bag = 0;
+  int pos = 0, bag_end = (int)(sb[1] - run0);
+  int blk = 0;  // the 32 indices in hand are positions blk .. blk + 31
+  int32_t r_mine, r_next;
+  float w_mine, w_next;
+  fetch(lane, r_mine, w_mine);
+  fetch(32 + lane, r_next, w_next);
+  while (true) {
+    const int lim = bag_end < blk + 32 ? bag_end : blk + 32;
+    const int q0 = pos - blk, n = lim - blk;
+    for (int k = 0; q0 + k * slots < n; k += kUnroll) {
+      int32_t r[kUnroll];
+      float w[kUnroll];
+      typename RL::Chunk pay[kUnroll][P];
+      uint2 tl[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) {
+        const int src = q0 + (k + u) * slots + slot;  // position of this slot's row in the block
+        r[u] = __shfl_sync(0xffffffffu, r_mine, src & 31);
+        w[u] = __shfl_sync(0xffffffffu, w_mine, src & 31);
+        if (src >= n) r[u] = -2;                       // no row for this slot in this step
+        else if (r[u] < 0) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) {
+        if (r[u] >= 0) {
+          const uint8_t *row = data + (int64_t)r[u] * in_line;
+#pragma unroll
+          for (int c = 0; c < P; c++)
+            if (has[c]) pay[u][c] = RL::payload(row, c * lpr + gl);
+          tl[u] = RL::tail(row + in_line);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) {
+        if (r[u] >= 0) {
+          float scale, offset;
+          RL::scale_offset(tl[u], scale, offset);
+          const float a = w[u] * scale;
+          bias_sum = fmaf(w[u], offset, bias_sum);
+#pragma unroll
+          for (int c = 0; c < P; c++)
+            if (has[c]) {
+#pragma unroll
+              for (int i = 0; i < 8; i++) acc[c * 8 + i] = fmaf(a, RL::column(pay[u][c], i), acc[c * 8 + i]);
+            }
+        }
+      }
+    }
+    pos = lim;
+    if (pos == bag_end) {  // the bag is complete
+      flush(first_bag + bag);
+      if (bag == n_bags - 1) break;
+      reset();
+      bag++;
+      bag_end = (int)(sb[bag + 1] - run0);  // bags of a lengths array are back to back: the next one starts at pos
+    }
+    if (pos == blk + 32) {  // the block is used up: the prefetched one becomes current
+      blk += 32;
+      r_mine = r_next;
+      w_mine = w_next;
+      fetch(blk + 32 + lane, r_next, w_next);
+    }
+  }
+  raise(p.status, flags);
+}
+
+// One launch, two thread-to-bag mappings: every table is pooled by the mapping its bag-length
+// profile favours (the word the segments kernel leaves behind the table's boundaries).
+// grid.x covers the larger of the two mappings' block counts; surplus blocks leave at once.
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P>
+__global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS)
+slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
+  const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
+  const bool skewed = p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
+  if (skewed) gather_warp_body<BITS, SO16, OUT16, IdxT, P>(p, bags_per_warp);
+  else gather_group_body<BITS, SO16, OUT16, false, IdxT, P>(p);
+}
+
 // ------------------------------------------------------------------------------------------
 // Any-shape gather-pool: rows of any width and alignment (a column count that is not a
 // multiple of 8, a table that is not 8-byte aligned).  One warp per bag, byte loads, column
@@ -471,8 +730,34 @@ struct GatherConfig {
   int kind, idx64, out16, acc16;
 };
 
+#ifndef GLOWB200_SLWS_WARP_PER_BAG
+#define GLOWB200_SLWS_WARP_PER_BAG 1
+#endif
+
 template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT>
 cudaError_t launch_gather_p(const SlwsLaunch &L, int P, dim3 grid, cudaStream_t s) {
+#if GLOWB200_SLWS_WARP_PER_BAG
+  if constexpr (!ACC16) {
+    if (L.select) {
+      // fp32 accumulation with lengths: the kernel that picks a mapping per table.  The
+      // warp-per-run mapping takes runs of up to 8 bags once that still leaves every SM a few
+      // waves of warps; single bags for small launches.
+      const int64_t max_segments = (int64_t)grid.x * (kGatherThreads >> L.lpr_log2);
+      const int64_t total = max_segments * grid.y, want = (int64_t)sm_count() * 24 * 4;
+      int bpw = (int)(total / want);
+      bpw = bpw < 1 ? 1 : (bpw > 8 ? 8 : bpw);
+      const int64_t warps = (max_segments + bpw - 1) / bpw;
+      const unsigned wblocks = (unsigned)((warps + 7) / 8);
+      dim3 sgrid(wblocks > grid.x ? wblocks : grid.x, grid.y);
+      switch (P) {
+        case 1: slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, 1><<<sgrid, kGatherThreads, 0, s>>>(L, bpw); break;
+        case 2: slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, 2><<<sgrid, kGatherThreads, 0, s>>>(L, bpw); break;
+        default: slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, 4><<<sgrid, kGatherThreads, 0, s>>>(L, bpw); break;
+      }
+      return cudaGetLastError();
+    }
+  }
+#endif
   switch (P) {
     case 1: slws_gather_kernel<BITS, SO16, OUT16, ACC16, IdxT, 1><<<grid, kGatherThreads, 0, s>>>(L); break;
     case 2: slws_gather_kernel<BITS, SO16, OUT16, ACC16, IdxT, 2><<<grid, kGatherThreads, 0, s>>>(L); break;
@@ -548,7 +833,7 @@ int run_gather(SlwsLaunch &L, const GatherConfig &g, int P, int64_t max_segments
   return GLOWB200_OK;
 }
 
-size_t seg_stride_elems(int64_t max_segments) { return align_up((size_t)(max_segments + 1) * 8, 256) / 8; }
+size_t seg_stride_elems(int64_t max_segments) { return align_up((size_t)(max_segments + 2) * 8, 256) / 8; }
 
 bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
@@ -587,11 +872,12 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batc
   L.in_line = (int32_t)in_line_size;
   L.out_line = (int32_t)out_line_size;
   L.lpr_log2 = lpr_log2;
+  GatherConfig g{kind, indices_are_int64 ? 1 : 0, out_is_fp16 ? 1 : 0,
+                 (use_fp16_accumulation && out_is_fp16 && (kind & 1)) ? 1 : 0};
+  L.select = (P != 0 && !g.acc16) ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   slws_segments_from_lengths_kernel<<<(unsigned)num_jobs, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
-  GatherConfig g{kind, indices_are_int64 ? 1 : 0, out_is_fp16 ? 1 : 0,
-                 (use_fp16_accumulation && out_is_fp16 && (kind & 1)) ? 1 : 0};
   return run_gather(L, g, P, max_segments, num_jobs, s);
 }
 
@@ -648,6 +934,7 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
     return rc;
   if (segments == 0) return GLOWB200_OK;
   GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
+  L.select = (P != 0 && !g.acc16) ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
@@ -697,7 +984,7 @@ extern "C" int glowb200_embedding_bag_byte_rowwise_offsets(
 namespace glowb200 {
 namespace {
 constexpr int64_t kStaticScratchMaxSegments = 65536;
-constexpr size_t kStaticScratchBytes = ((kStaticScratchMaxSegments + 1) * 8 + 255) / 256 * 256;
+constexpr size_t kStaticScratchBytes = ((kStaticScratchMaxSegments + 2) * 8 + 255) / 256 * 256;
 constexpr int kStaticScratchMaxDevices = 64;
 }  // namespace
 }  // namespace glowb200
@@ -758,9 +1045,11 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_stat
                            kStaticScratchBytes, status))
     return rc;
   GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
+  L.select = (P != 0 && !g.acc16) ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // The segments kernel rewrites all segments + 1 boundaries this call reads; nothing in the
-  // array has to start at zero, and whatever an earlier call left beyond them is never read.
+  // The segments kernel rewrites everything this call reads (segments + 1 boundaries and the
+  // table's profile word); nothing in the array has to start at zero, and whatever an earlier
+  // call left beyond them is never read.
   slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return run_gather(L, g, P, segments, 1, s);
