@@ -276,6 +276,7 @@ class DLRMRank:
         # receive slabs [per, T, D] (two, alternating by step) and, for "nccl", the send buffer
         self.step = 0
         self.peers = None
+        self.token = torch.zeros(1, dtype=torch.float32, device=dev)
         if exchange == "fused":
             self.slab_buf = [ops.PeerBuffer(per * T * D * 4) for _ in range(2)]
             self.slabs = [b.as_tensor((per, T, D), torch.float32) for b in self.slab_buf]
@@ -334,8 +335,10 @@ class DLRMRank:
         if self.exchange == "nccl":
             self.slabs[slab].copy_(exchange_all_to_all(self.send, self.cfg, self.rank, self.world, self.group))
         elif self.exchange == "fused":
-            # every rank's stores into every slab are complete once all pooling kernels have finished
-            dist.barrier(group=self.group)
+            # every rank's stores into every slab are complete once all pooling kernels have
+            # finished: a one-element all-reduce, enqueued on the stream, is that rendezvous (it
+            # never blocks the host and can be captured in a CUDA graph, unlike a barrier)
+            dist.all_reduce(self.token, group=self.group)
         return self.slabs[slab]
 
     # -- dense part ----------------------------------------------------------------------
