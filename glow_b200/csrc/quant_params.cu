@@ -139,3 +139,46 @@ extern "C" int glowb200_quantize_bias_i32(const float *in, int64_t n, float scal
   }
   return GLOWB200_OK;
 }
+
+// Host-side constant preparation of Function::createChannelwiseQuantizedConv
+// (lib/Graph/Graph.cpp:3525-3700) for a float filter and a float bias with an int8 filter and an
+// int32 bias: per-output-channel filter parameters (getTensorQuantizationParams along
+// dimension 0), per-channel bias parameters specialised with
+// specializeBiasWeightsQuantizationParams (lib/Quantization/Base/Base.cpp:595-629: the bias
+// offset is forced to 0 and its scale to in_scale * filter_scale, widening the filter scale when
+// that would saturate the bias), then both tensors quantized with the final parameters.
+// filter is [out_channels, k] (k = kH*kW*inC/group).  HOST arrays.
+extern "C" int glowb200_channelwise_conv_prepare(const float *filter, const float *bias, int64_t out_channels, int64_t k,
+                                                 float in_scale, int schema, int8_t *filter_q, float *filter_scales,
+                                                 int32_t *filter_offsets, int32_t *bias_q, float *bias_scales,
+                                                 int32_t *bias_offsets) {
+  GLOWB200_REQUIRE(out_channels >= 0 && k > 0 && filter && bias && filter_q && filter_scales && filter_offsets && bias_q &&
+                       bias_scales && bias_offsets, "bad arguments");
+  const int64_t qmin32 = (int64_t)INT32_MIN >> 2, qmax32 = (int64_t)INT32_MAX >> 2;
+  for (int64_t c = 0; c < out_channels; c++) {
+    const float *f = filter + c * k;
+    float mn = f[0], mx = f[0];
+    for (int64_t j = 1; j < k; j++) { mn = f[j] < mn ? f[j] : mn; mx = f[j] > mx ? f[j] : mx; }
+    float w_scale, b_scale;
+    int32_t w_off, b_off;
+    glowb200::choose_quantization_params(mn, mx, schema, -128, 127, w_scale, w_off);
+    glowb200::choose_quantization_params(bias[c], bias[c], schema, qmin32, qmax32, b_scale, b_off);
+    b_off = 0;
+    const bool bias_zero = bias[c] == 0.f;
+    if (in_scale * w_scale >= b_scale || bias_zero) {
+      b_scale = in_scale * w_scale;
+    } else {
+      w_scale = b_scale / in_scale;
+      b_scale = in_scale * w_scale;
+    }
+    for (int64_t j = 0; j < k; j++) filter_q[c * k + j] = glowb200::quantize_i8(f[j], w_scale, w_off);
+    filter_scales[c] = w_scale;
+    filter_offsets[c] = w_off;
+    const float r = bias[c] / b_scale + (float)b_off;
+    int64_t v = (int64_t)std::nearbyintf(r);
+    bias_q[c] = (int32_t)(v < qmin32 ? qmin32 : (v > qmax32 ? qmax32 : v));
+    bias_scales[c] = b_scale;
+    bias_offsets[c] = b_off;
+  }
+  return GLOWB200_OK;
+}

@@ -172,6 +172,25 @@ def tensor_rowwise_quantize_i8(w, schema=ASYMMETRIC):
     return q, sc, off
 
 
+def channelwise_conv_prepare(filt, bias, in_scale, schema=SYMMETRIC):
+    """Host preparation of a channelwise-quantized convolution's constants from a float filter
+    [outC, kH, kW, inC/group] and float bias [outC] (numpy).  Returns a dict of numpy arrays:
+    filter (int8, same shape), filter_scales, filter_offsets, bias (int32), bias_scales, bias_offsets."""
+    import numpy as np
+    filt = np.ascontiguousarray(filt, np.float32)
+    bias = np.ascontiguousarray(bias, np.float32)
+    oc = filt.shape[0]
+    k = filt.size // oc
+    out = dict(filter=np.empty(filt.shape, np.int8), filter_scales=np.empty(oc, np.float32),
+               filter_offsets=np.empty(oc, np.int32), bias=np.empty(oc, np.int32),
+               bias_scales=np.empty(oc, np.float32), bias_offsets=np.empty(oc, np.int32))
+    check(_lib.lib().glowb200_channelwise_conv_prepare(
+        C.c_void_p(filt.ctypes.data), C.c_void_p(bias.ctypes.data), oc, k, C.c_float(float(in_scale)), int(schema),
+        *[C.c_void_p(out[n].ctypes.data) for n in ("filter", "filter_scales", "filter_offsets", "bias", "bias_scales",
+                                                  "bias_offsets")]))
+    return out
+
+
 def quantize_bias_i32(b, scale, offset=0):
     import numpy as np
     b = np.ascontiguousarray(b, np.float32)

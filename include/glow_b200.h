@@ -164,6 +164,16 @@ int glowb200_tensor_rowwise_quantize_i8(const float *in, int64_t rows, int64_t c
  * the 30-bit range of getQuantizedRange, Base.cpp:361-403).  HOST function. */
 int glowb200_quantize_bias_i32(const float *in, int64_t n, float scale, int32_t offset, int32_t *out);
 
+/* Constants of a ChannelwiseQuantizedConvolution from a float filter [out_channels, k] and a
+ * float bias: what Function::createChannelwiseQuantizedConv (lib/Graph/Graph.cpp:3525-3700)
+ * computes at graph-construction time -- per-channel filter scale/offset, int32 bias with
+ * offset 0 and scale in_scale * filter_scale (specializeBiasWeightsQuantizationParams,
+ * lib/Quantization/Base/Base.cpp:595-629), both tensors quantized.  HOST function. */
+int glowb200_channelwise_conv_prepare(const float *filter, const float *bias, int64_t out_channels,
+                                      int64_t k, float in_scale, int schema, int8_t *filter_q,
+                                      float *filter_scales, int32_t *filter_offsets,
+                                      int32_t *bias_q, float *bias_scales, int32_t *bias_offsets);
+
 /* Hints in `flags`. */
 #define GLOWB200_FC_WEIGHT_OFFSETS_ZERO 1      /* every weight offset is 0: skips the input row sums */
 #define GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL 2   /* run the plain one-thread-per-output kernel          */
