@@ -45,8 +45,11 @@ def parse():
     ap.add_argument("--requests", type=int, default=4, help="distinct pre-generated batches rotated over the steps")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="slws", choices=["slws", "int8_fc"],
-                    help="slws: the headline gather-pool line (default); int8_fc: the rowwise int8 FC line")
+    ap.add_argument("--workload", default="slws", choices=["slws", "int8_fc", "slws4"],
+                    help="slws: the headline gather-pool line (default); int8_fc: the rowwise int8 FC line; "
+                         "slws4: the 4-bit fused-rowwise sweep point selected by --dim")
+    ap.add_argument("--dim", type=int, default=128, help="slws4: embedding width (32, 64, 128 or 256)")
+    ap.add_argument("--table-gb", type=float, default=40.0, help="slws4: total table bytes per GPU, in GB")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary int8 FC measurement")
     return ap.parse_args()
 
@@ -460,6 +463,160 @@ def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges):
                                  "interaction; dense layers batch-sharded", "tables": 64, "batch": 4096}
 
 
+def resnet_measure(torch, dev, steps):
+    """ResNet-50 v1.5, fully int8 channelwise-quantized, batch 64 at 224x224x3 (third benchmark
+    configuration): images/s with the batch resident in HBM (CUDA-graph replay of the whole
+    network) and end to end (fp32 NCHW batch from pinned host memory in, logits out)."""
+    from glow_b200 import resnet
+    layers = resnet.architecture()
+    w = resnet.float_weights(layers)
+    g = torch.Generator().manual_seed(7)
+    _, ranges = resnet.float_forward(layers, w, torch.randn((16, 3, 224, 224), generator=g), dev)
+    q = resnet.quantize_network(layers, w, ranges)
+    model = resnet.ResNet50Int8(layers, q, dev)
+    host_x = torch.randn((64, 3, 224, 224), generator=g).pin_memory()
+    x = host_x.to(dev)
+    for _ in range(3):
+        out = model.forward(x)
+    torch.cuda.synchronize()
+    launches = model.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = model.forward(x)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        n_e2e = max(3, min(steps, 10))
+        e0.record()
+        for _ in range(n_e2e):
+            x.copy_(host_x, non_blocking=True)
+            graph.replay()
+            out_host.copy_(out, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        e2e_ms = e0.elapsed_time(e1) / n_e2e
+    torch.cuda.current_stream().wait_stream(side)
+    assert int(model.status.item()) == 0
+    ops_per_batch = resnet.conv_ops_per_image(layers) * 64
+    return {"metric": "resnet50_int8_images_per_s", "value": 64 / (ms * 1e-3), "unit": "images/s", "ms_per_batch": ms,
+            "e2e_value": 64 / (e2e_ms * 1e-3), "e2e_ms_per_batch": e2e_ms, "h2d_bytes_per_step": host_x.numel() * 4,
+            "d2h_bytes_per_step": out.numel() * 4, "launches_per_batch": launches,
+            "effective_tops": ops_per_batch / (ms * 1e-3) / 1e12,
+            "config": {"workload": "ResNet-50 v1.5 int8: channelwise symmetric filters (He-normal, BN folded), asymmetric "
+                                   "int8 activations calibrated on 16 seeded N(0,1) images, int32 bias, batch 64 at "
+                                   "224x224x3, every node on the library's kernels", "batch": 64}}
+
+
+def run_slws4_line(args):
+    """--workload slws4: one point of the 4-bit embedding bandwidth sweep (fifth benchmark
+    configuration): UInt4FusedFP16QTy tables of 10,000,000 rows x D (D/2 + 4 bytes per row),
+    T tables so that they fill --table-gb per GPU, batch 8192 bags per table, lengths
+    Poisson(64), uniform int64 indices, fp16 weights U(0,1), fp16 result, fp32 accumulation.
+    At N > 1 every rank owns T tables of its own (weak scaling, no collective)."""
+    import torch
+    import torch.distributed as dist
+    from glow_b200 import ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    D, ROWS4, B = args.dim, 10_000_000, 8192
+    line_bytes = D // 2 + 4
+    T = max(1, int(args.table_gb * 1e9 / (ROWS4 * line_bytes)))
+    g = torch.Generator(device=dev).manual_seed(0x610B200 + 77 * rank + D)
+    tables = []
+    for k in range(T):
+        t = torch.randint(0, 256, (ROWS4, line_bytes), dtype=torch.uint8, device=dev, generator=g)
+        so = torch.stack([torch.empty(ROWS4, device=dev).uniform_(0.001, 0.01, generator=g),
+                          torch.empty(ROWS4, device=dev).uniform_(-1, 1, generator=g)], dim=1).to(torch.float16)
+        t[:, D // 2:] = so.view(torch.uint8).view(ROWS4, 4)
+        tables.append(t)
+    del so
+    R = 2
+    reqs = []
+    for r in range(R):
+        rng = np.random.Generator(np.random.PCG64(4242 + 1000 * rank + r))
+        lengths = rng.poisson(64, (T, B)).astype(np.int32)
+        n = lengths.sum(1)
+        starts = np.concatenate([[0], np.cumsum(n)]).astype(np.int64)
+        total = int(starts[-1])
+        gi = torch.Generator(device=dev).manual_seed(99 + r + 10 * rank)
+        indices = torch.randint(0, ROWS4, (total,), device=dev, generator=gi)
+        weights = torch.rand(total, device=dev, generator=gi).to(torch.float16)
+        reqs.append((torch.from_numpy(lengths).to(dev), indices, weights, starts))
+    out = torch.empty((T, B, D), dtype=torch.float16, device=dev)
+    status = ops.new_status(dev)
+    batches = []
+    for lengths_d, indices_d, weights_d, starts in reqs:
+        b = ops.SlwsBatch(ops.UINT4_FUSED_FP16, line_bytes, torch.int64, device=dev)
+        b.bind(tables, [weights_d[starts[k]:starts[k + 1]] for k in range(T)],
+               [indices_d[starts[k]:starts[k + 1]] for k in range(T)], [lengths_d[k] for k in range(T)],
+               [out[k] for k in range(T)])
+        batches.append(b)
+    nbytes = [int(rq[3][-1]) * (line_bytes + 8 + 2) + T * B * (4 + 2 * D) for rq in reqs]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for i in range(max(3, args.warmup)):
+        batches[i % R].run(status)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        batches[i % R].run(status)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t_end = time.time() + 1.0
+    while len(sampler.lines) < 8 and time.time() < t_end:
+        batches[0].run(status)
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    assert int(status.item()) == 0
+    moved = sum(nbytes[i % R] for i in range(args.steps))
+    tm = torch.tensor([ms], dtype=torch.float64, device=dev)
+    mv = torch.tensor([moved], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        dist.all_reduce(mv, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        peak, src = measured_peak_hbm()
+        value = float(mv[0]) / (float(tm[0]) * 1e-3) / 1e9
+        per_gpu = value / world
+        print(json.dumps({
+            "metric": "frwq_slws_4bit_hbm_gbps", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": float(tm[0]) / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u4 -> f32 accumulate -> f16", "data": "synthetic",
+            "config": {"workload": "4-bit fused-rowwise SLWS (UInt4FusedFP16QTy): %d tables x 10,000,000 rows x %d cols "
+                                   "(%d B rows, %.1f GB per GPU), 8192 bags/table, lengths Poisson(64), uniform int64 "
+                                   "indices, fp16 weights and result" % (T, D, line_bytes, T * ROWS4 * line_bytes / 1e9),
+                       "dim": D, "tables_per_gpu": T, "l2_policy": "tables far larger than L2, uniform indices"},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                         "peak_source": src, "traffic": None, "kernel": "slws_gather_select_kernel<4,1,1,long,P>",
+                         "rows_per_s": sum(int(reqs[i % R][3][-1]) for i in range(args.steps)) / (ms * 1e-3)},
+            "gpu_launches": 2 * args.steps, "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def workload_config(T):
     return {"workload": "FRWQ-SLWS uint8 fused rows (config 1 law): %d tables x 1,000,000 rows x 64 cols "
                         "(72 B rows), 1024 bags/table, lengths clamp(Poisson(32),1,128), int64 indices, fp32 "
@@ -474,6 +631,8 @@ def main():
         return run_reference(args)
     if args.workload == "int8_fc":
         return run_int8_fc_line(args)
+    if args.workload == "slws4":
+        return run_slws4_line(args)
 
     import torch
     import torch.distributed as dist
@@ -647,6 +806,8 @@ def main():
                 "roofline": {"bound": "tensor", "achieved": fc["tops"], "peak": ipeak, "frac": fc["tops"] / ipeak,
                              "peak_source": isrc, "nominal_dense_int8_tops": 4500.0,
                              "library_int8_gemm_tops": fc["library_int8_gemm_tops"]}}
+        if world == 1 and not args.no_extras:
+            line["extras"]["resnet50"] = resnet_measure(torch, dev, max(5, min(args.steps, 20)))
         if world == 1 and not args.no_cpu_baseline:
             threads, S = cpu_threads, len(sample_tables)
             v, kind, passes, dt = cpu_reference_rate(sample_tables, args.cpu_seconds, threads)

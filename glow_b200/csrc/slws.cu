@@ -30,7 +30,6 @@ namespace glowb200 {
 namespace {
 
 constexpr int kGatherThreads = 256;
-constexpr int kUnroll = 4;
 constexpr int kSegThreads = 1024;
 
 struct SlwsLaunch {
@@ -241,6 +240,38 @@ struct RowLoad {
     }
     return __uint_as_float(m) - 8388608.0f;
   }
+
+  // fp32 pooling of one chunk: acc[i] += (w*scale) * q_i.
+  //  * uint8 rows: q_i as above (byte into the mantissa of 2^23, minus 2^23), one FMA each.
+  //  * 4-bit rows are bound by instruction issue, not by memory, so the conversion is made
+  //    cheaper: the nibbles are spread into bytes 0x8q (three logic ops per 8 columns), a byte
+  //    permute drops each into bits 16..23 of 0x3F80'0000, which reads as m = 1 + q/128, and
+  //    acc[i] += (128*w*scale) * m.  The surplus sum_j 128*w_j*scale_j is the same for every
+  //    column and is taken out once per row through the shared offset sum (row_term).
+  //    m is exact; the products are about 8-128 times larger than the wanted a*q, which costs
+  //    at most 7 of the 24 mantissa bits -- inside the fp32 tolerance.
+  __device__ static __forceinline__ float scale_for_pooling(float a) { return BITS == 4 ? a * 128.0f : a; }
+  __device__ static __forceinline__ float row_term(float w, float offset, float a_eff, float sum) {
+    // sum += w*offset (and, 4-bit, minus the surplus a_eff)
+    sum = fmaf(w, offset, sum);
+    return BITS == 4 ? sum - a_eff : sum;
+  }
+  __device__ static __forceinline__ void pool(const Chunk &c, float a_eff, float *acc) {
+    if constexpr (BITS == 8) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) acc[i] = fmaf(a_eff, column(c, i), acc[i]);
+    } else {
+      const uint32_t lo = (c.lo & 0x0F0F0F0Fu) | 0x80808080u;         // columns 0,2,4,6 as bytes 0x8q
+      const uint32_t hi = ((c.lo >> 4) & 0x0F0F0F0Fu) | 0x80808080u;  // columns 1,3,5,7
+#pragma unroll
+      for (int b = 0; b < 4; b++) {
+        const float m0 = __uint_as_float(__byte_perm(lo, 0x3F000000u, 0x7044 + (b << 8)));  // {0, 0, byte b, 0x3F}
+        const float m1 = __uint_as_float(__byte_perm(hi, 0x3F000000u, 0x7044 + (b << 8)));
+        acc[2 * b] = fmaf(a_eff, m0, acc[2 * b]);
+        acc[2 * b + 1] = fmaf(a_eff, m1, acc[2 * b + 1]);
+      }
+    }
+  }
 };
 
 template <bool OUT16>
@@ -252,7 +283,7 @@ __device__ __forceinline__ float load_weight(const void *weights, int64_t i) {
 // ------------------------------------------------------------------------------------------
 // Gather-pool.  grid = (ceil(max_segments / bags_per_block), num_jobs).
 // ------------------------------------------------------------------------------------------
-template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P>
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int kUnroll>
 __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
   using RL = RowLoad<BITS, SO16>;
   const int job_id = blockIdx.y;
@@ -351,14 +382,11 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
                 }
               }
           } else {
-            const float a = w[u] * scale;
-            bias_sum = fmaf(w[u], offset, bias_sum);
+            const float a = RL::scale_for_pooling(w[u] * scale);
+            bias_sum = RL::row_term(w[u], offset, a, bias_sum);
 #pragma unroll
             for (int c = 0; c < P; c++)
-              if (has[c]) {
-#pragma unroll
-                for (int i = 0; i < 8; i++) acc[c][i] = fmaf(a, RL::column(pay[u][c], i), acc[c][i]);
-              }
+              if (has[c]) RL::pool(pay[u][c], a, acc[c]);
           }
         }
       }
@@ -412,9 +440,9 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
   raise(p.status, flags);
 }
 
-template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P>
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int U>
 __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
-  gather_group_body<BITS, SO16, OUT16, ACC16, IdxT, P>(p);
+  gather_group_body<BITS, SO16, OUT16, ACC16, IdxT, P, U>(p);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -432,7 +460,7 @@ __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN
 // group-per-bag kernel above.
 // grid = (ceil(ceil(max_segments / bags_per_warp) / 8), num_jobs), 8 warps per block.
 // ------------------------------------------------------------------------------------------
-template <int BITS, bool SO16, bool OUT16, typename IdxT, int P>
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int kUnroll>
 __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_per_warp) {
   using RL = RowLoad<BITS, SO16>;
   constexpr int V = 8 * P;  // sums a lane carries
@@ -610,14 +638,11 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
         if (r[u] >= 0) {
           float scale, offset;
           RL::scale_offset(tl[u], scale, offset);
-          const float a = w[u] * scale;
-          bias_sum = fmaf(w[u], offset, bias_sum);
+          const float a = RL::scale_for_pooling(w[u] * scale);
+          bias_sum = RL::row_term(w[u], offset, a, bias_sum);
 #pragma unroll
           for (int c = 0; c < P; c++)
-            if (has[c]) {
-#pragma unroll
-              for (int i = 0; i < 8; i++) acc[c * 8 + i] = fmaf(a, RL::column(pay[u][c], i), acc[c * 8 + i]);
-            }
+            if (has[c]) RL::pool(pay[u][c], a, acc + c * 8);
         }
       }
     }
@@ -642,13 +667,13 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
 // One launch, two thread-to-bag mappings: every table is pooled by the mapping its bag-length
 // profile favours (the word the segments kernel leaves behind the table's boundaries).
 // grid.x covers the larger of the two mappings' block counts; surplus blocks leave at once.
-template <int BITS, bool SO16, bool OUT16, typename IdxT, int P>
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U>
 __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS)
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
   const bool skewed = p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
-  if (skewed) gather_warp_body<BITS, SO16, OUT16, IdxT, P>(p, bags_per_warp);
-  else gather_group_body<BITS, SO16, OUT16, false, IdxT, P>(p);
+  if (skewed) gather_warp_body<BITS, SO16, OUT16, IdxT, P, U>(p, bags_per_warp);
+  else gather_group_body<BITS, SO16, OUT16, false, IdxT, P, U>(p);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -734,8 +759,11 @@ struct GatherConfig {
 #define GLOWB200_SLWS_WARP_PER_BAG 1
 #endif
 
-template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT>
-cudaError_t launch_gather_p(const SlwsLaunch &L, int P, dim3 grid, cudaStream_t s) {
+// (P, U) pairs that exist: chunks per lane P, rows requested per lane before the first is
+// consumed U.  Wide rows spread over 8 or more lanes leave few bags (or row slots) per warp,
+// so each lane keeps 8 rows in flight instead of 4 to hold the bytes in flight per warp up.
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int U>
+cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
 #if GLOWB200_SLWS_WARP_PER_BAG
   if constexpr (!ACC16) {
     if (L.select) {
@@ -749,21 +777,27 @@ cudaError_t launch_gather_p(const SlwsLaunch &L, int P, dim3 grid, cudaStream_t 
       const int64_t warps = (max_segments + bpw - 1) / bpw;
       const unsigned wblocks = (unsigned)((warps + 7) / 8);
       dim3 sgrid(wblocks > grid.x ? wblocks : grid.x, grid.y);
-      switch (P) {
-        case 1: slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, 1><<<sgrid, kGatherThreads, 0, s>>>(L, bpw); break;
-        case 2: slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, 2><<<sgrid, kGatherThreads, 0, s>>>(L, bpw); break;
-        default: slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, 4><<<sgrid, kGatherThreads, 0, s>>>(L, bpw); break;
-      }
+      slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U><<<sgrid, kGatherThreads, 0, s>>>(L, bpw);
       return cudaGetLastError();
     }
   }
 #endif
-  switch (P) {
-    case 1: slws_gather_kernel<BITS, SO16, OUT16, ACC16, IdxT, 1><<<grid, kGatherThreads, 0, s>>>(L); break;
-    case 2: slws_gather_kernel<BITS, SO16, OUT16, ACC16, IdxT, 2><<<grid, kGatherThreads, 0, s>>>(L); break;
-    default: slws_gather_kernel<BITS, SO16, OUT16, ACC16, IdxT, 4><<<grid, kGatherThreads, 0, s>>>(L); break;
-  }
+  slws_gather_kernel<BITS, SO16, OUT16, ACC16, IdxT, P, U><<<grid, kGatherThreads, 0, s>>>(L);
   return cudaGetLastError();
+}
+
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT>
+cudaError_t launch_gather_p(const SlwsLaunch &L, int P, dim3 grid, cudaStream_t s) {
+  switch (P) {
+    case 1: return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 1, 4>(L, grid, s);
+    case 2:
+      // (4-bit rows only: a uint8 chunk is two registers wide and 8 rows in flight would spill)
+      if constexpr (BITS == 4) {
+        if (L.lpr_log2 >= 3) return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 2, 8>(L, grid, s);
+      }
+      return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 2, 4>(L, grid, s);
+    default: return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 4, 4>(L, grid, s);
+  }
 }
 
 template <int BITS, bool SO16, bool OUT16, bool ACC16>
