@@ -65,6 +65,22 @@ SIGNATURES = {
     "glowb200_peer_buffer_open": (_int, [_vp, _vp]),
     "glowb200_peer_buffer_close": (_int, [_vp]),
     "glowb200_peer_buffer_destroy": (_int, [_vp]),
+    "glowb200_function_create": (_vp, [C.c_char_p]),
+    "glowb200_function_destroy": (None, [_vp]),
+    "glowb200_function_add_symbol": (_int, [_vp, C.c_char_p, _int, _sz, _vp]),
+    "glowb200_function_add_instruction": (_int, [_vp, _int, _vp, _int, _vp, _int, _vp, _int]),
+    "glowb200_function_compile": (_int, [_vp]),
+    "glowb200_function_constant_bytes": (_sz, [_vp]),
+    "glowb200_device_manager_create": (_vp, [_int, C.c_uint64]),
+    "glowb200_device_manager_init": (_int, [_vp]),
+    "glowb200_device_manager_add_network": (_int, [_vp, _vp]),
+    "glowb200_device_manager_evict_network": (_int, [_vp, C.c_char_p]),
+    "glowb200_device_manager_run_function": (_int, [_vp, C.c_char_p, _vp, _vp, _vp, _int]),
+    "glowb200_device_manager_maximum_memory": (C.c_uint64, [_vp]),
+    "glowb200_device_manager_available_memory": (C.c_uint64, [_vp]),
+    "glowb200_device_manager_is_memory_available": (_int, [_vp, C.c_uint64]),
+    "glowb200_device_manager_stop": (_int, [_vp]),
+    "glowb200_device_manager_destroy": (None, [_vp]),
     "glowb200_embedding_bag_byte_rowwise_offsets": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _sz, _vp,
                _vp]),

@@ -1,0 +1,504 @@
+// Host runtime above the kernel ABI: the part of a Glow backend that sits between
+// DeviceManager::runFunction and the kernels, written against this library instead of Glow's
+// headers (Glow itself needs LLVM, folly and glog to compile; the thin glue that adapts these
+// classes to glow::CompiledFunction / glow::DeviceManager is shown in INTEGRATION.md).
+//
+//   Function       what Backend::compile produces: a symbol table with byte offsets into three
+//                  slabs -- constants, placeholders ("mutable weights") and activations -- like
+//                  glow::RuntimeBundle (include/glow/Backend/BackendUtils.h:66-170), and a flat,
+//                  control-flow-free instruction list like Glow's low-level IR (docs/IR.md).
+//                  compile() does what LLVMIRGen does while emitting a call: it turns the float
+//                  scales of the node types into the integer pre/post/scale triples
+//                  (LLVMIRGen.cpp:2222-2320, 2695-2798, 1716-1771, 3003-3046).
+//   DeviceManager  one GPU: addNetwork uploads the constants slab and accounts its memory,
+//                  evictNetwork frees it, runFunction copies the bound inputs in, walks the
+//                  instructions, copies the outputs back and turns the kernels' status word into
+//                  an error -- the contract of CPUDeviceManager (lib/Backends/CPU/
+//                  CPUDeviceManager.cpp:65-179) with the copies of OpenCLDeviceManager
+//                  (lib/Backends/OpenCL/OpenCLDeviceManager.cpp:775-853).
+// Error codes carry the names of glow::ErrorValue::ErrorCode (include/glow/Support/Error.h).
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace glowb200 {
+void quantize_scale_32to8(float scale, int32_t &pre, int32_t &post, int32_t &iscale);
+}
+
+namespace {
+
+using glowb200::align_up;
+using glowb200::set_error;
+
+enum SymbolKind { kConstant = 0, kPlaceholder = 1, kActivation = 2 };
+
+struct Symbol {
+  std::string name;
+  int kind;
+  size_t bytes, offset;
+  std::vector<uint8_t> host;  // constants only
+};
+
+struct Instruction {
+  int kind;
+  std::vector<int> ops;       // symbol ids
+  std::vector<int64_t> ia;    // integer attributes
+  std::vector<float> fa;      // float attributes
+  std::vector<int> derived;   // ids of constants compile() added (triples, row sums ...)
+};
+
+}  // namespace
+
+struct glowb200_function {
+  std::string name;
+  std::vector<Symbol> symbols;
+  std::vector<Instruction> instrs;
+  bool compiled = false;
+  size_t slab_bytes[3] = {0, 0, 0};
+  size_t workspace_bytes = 0;
+  std::map<std::string, int> by_name;
+
+  int add_symbol(const std::string &n, int kind, size_t bytes, const void *data) {
+    if (by_name.count(n)) return -1;
+    Symbol s;
+    s.name = n;
+    s.kind = kind;
+    s.bytes = bytes;
+    s.offset = 0;
+    if (data) s.host.assign(static_cast<const uint8_t *>(data), static_cast<const uint8_t *>(data) + bytes);
+    symbols.push_back(std::move(s));
+    by_name[n] = (int)symbols.size() - 1;
+    return (int)symbols.size() - 1;
+  }
+  int add_i32_constant(const std::string &n, const std::vector<int32_t> &v) {
+    return add_symbol(n, kConstant, v.size() * 4, v.data());
+  }
+};
+
+namespace {
+
+struct LoadedNetwork {
+  glowb200_function *fn;
+  uint8_t *slab[3] = {nullptr, nullptr, nullptr};
+  uint8_t *workspace = nullptr;
+  size_t device_bytes = 0;
+};
+
+const float *host_f32(const glowb200_function *f, int id) { return reinterpret_cast<const float *>(f->symbols[id].host.data()); }
+
+// Triples for n rows from float scales: what LLVMIRGen bakes into the rowwise FC / channelwise
+// conv call.  Returns the ids of six int32 constants.
+std::vector<int> add_row_triples(glowb200_function *f, const std::string &tag, const float *row_scales, int64_t n, float in_scale,
+                                 const float *bias_scales, int64_t nb, float out_scale) {
+  std::vector<int32_t> v[6];
+  for (auto &x : v) x.resize(n);
+  for (int64_t j = 0; j < n; j++) {
+    const float mm = in_scale * row_scales[j];
+    glowb200::quantize_scale_32to8(bias_scales[nb == 1 ? 0 : j] / mm, v[0][j], v[1][j], v[2][j]);
+    glowb200::quantize_scale_32to8(mm / out_scale, v[3][j], v[4][j], v[5][j]);
+  }
+  std::vector<int> ids;
+  const char *names[6] = {".bias_pre", ".bias_post", ".bias_scale", ".out_pre", ".out_post", ".out_scale"};
+  for (int i = 0; i < 6; i++) ids.push_back(f->add_i32_constant(tag + names[i], v[i]));
+  return ids;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// Function building
+// ---------------------------------------------------------------------------------------------
+extern "C" glowb200_function *glowb200_function_create(const char *name) {
+  auto *f = new glowb200_function();
+  f->name = name ? name : "";
+  return f;
+}
+
+extern "C" void glowb200_function_destroy(glowb200_function *f) { delete f; }
+
+extern "C" int glowb200_function_add_symbol(glowb200_function *f, const char *name, int kind, size_t bytes, const void *host_data) {
+  if (!f || !name || f->compiled || kind < 0 || kind > 2 || (kind == kConstant) != (host_data != nullptr)) {
+    set_error(GLOWB200_RUNTIME_ERROR, "bad symbol '%s'", name ? name : "?");
+    return -1;
+  }
+  const int id = f->add_symbol(name, kind, bytes, host_data);
+  if (id < 0) set_error(GLOWB200_RUNTIME_ERROR, "symbol '%s' already exists", name);
+  return id;
+}
+
+extern "C" int glowb200_function_add_instruction(glowb200_function *f, int kind, const int32_t *operands, int num_operands,
+                                                 const int64_t *int_attrs, int num_int_attrs, const float *float_attrs,
+                                                 int num_float_attrs) {
+  if (!f || f->compiled) return set_error(GLOWB200_RUNTIME_ERROR, "function is NULL or already compiled");
+  Instruction in;
+  in.kind = kind;
+  for (int i = 0; i < num_operands; i++) {
+    if (operands[i] < -1 || operands[i] >= (int)f->symbols.size()) return set_error(GLOWB200_RUNTIME_ERROR, "operand %d: no such symbol", i);
+    in.ops.push_back(operands[i]);
+  }
+  in.ia.assign(int_attrs, int_attrs + num_int_attrs);
+  in.fa.assign(float_attrs, float_attrs + num_float_attrs);
+  f->instrs.push_back(std::move(in));
+  return GLOWB200_OK;
+}
+
+// Instruction operand / attribute layouts (ia = integer attributes, fa = float attributes):
+//  FRWQ_SLWS   ops {dest, data, weights, indices, lengths}  ia {kind, rows, in_line, out_line, segments, num_indices, idx64, out_fp16, fp16_acc}
+//  RWQ_FC      ops {dest, src, weights, scales(f32 const), offsets, bias}  ia {M, K, N, in_off, bias_off, out_off, relu}  fa {in_scale, bias_scale, out_scale}
+//  CWQ_CONV    ops {dest, src, filter, bias, filter_scales(f32 const), filter_offsets, bias_scales(f32 const), bias_offsets}
+//              ia {N,H,W,C, OH,OW,OC, KH,KW, SH,SW, PT,PL,PB,PR, group, DH,DW, in_off, out_off, act}  fa {in_scale, out_scale}
+//  ADD         ops {dest, lhs, rhs}  ia {n, dest_off, lhs_off, rhs_off}  fa {lhs_scale, rhs_scale, dest_scale}
+//  MAXSPLAT    ops {dest, src}  ia {n, splat}
+//  QUANTIZE    ops {dest, src}  ia {n, offset}  fa {scale}
+//  DEQUANTIZE  ops {dest, src}  ia {n, offset}  fa {scale}
+//  MAXPOOL     ops {dest, src}  ia {N,H,W,C, OH,OW, KH,KW, SH,SW, PT,PL, out_off}
+//  AVGPOOL     ops {dest, src}  ia {N,H,W,C, OH,OW, KH,KW, SH,SW, PT,PL, in_off, out_off, count_include_pads}  fa {in_scale, out_scale}
+//  TRANSPOSE   ops {dest, src}  ia {ndims, elem_bytes, d0..d3, s0..s3}
+//  COPY        ops {dest, src}  ia {bytes}
+extern "C" int glowb200_function_compile(glowb200_function *f) {
+  if (!f || f->compiled) return set_error(GLOWB200_RUNTIME_ERROR, "function is NULL or already compiled");
+  size_t ws = 256;
+  for (size_t ii = 0; ii < f->instrs.size(); ii++) {
+    Instruction &in = f->instrs[ii];
+    const std::string tag = "i" + std::to_string(ii);
+    auto need = [&](size_t nops, size_t nia, size_t nfa) {
+      return in.ops.size() == nops && in.ia.size() == nia && in.fa.size() == nfa;
+    };
+    switch (in.kind) {
+      case GLOWB200_INSTR_FRWQ_SLWS:
+        if (!need(5, 9, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed FRWQ_SLWS", ii);
+        ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[4], 1));
+        break;
+      case GLOWB200_INSTR_RWQ_FC: {
+        if (!need(6, 7, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed RWQ_FC", ii);
+        const int64_t N = in.ia[2];
+        if (f->symbols[in.ops[3]].host.size() != (size_t)N * 4) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: scales must be a float constant of N entries", ii);
+        in.derived = add_row_triples(f, tag, host_f32(f, in.ops[3]), N, in.fa[0], &in.fa[1], 1, in.fa[2]);
+        // row sums of the constant weights, computed once on the host
+        const Symbol &w = f->symbols[in.ops[2]];
+        if (w.host.size() != (size_t)N * in.ia[1]) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: weights must be an int8 constant [N,K]", ii);
+        std::vector<int32_t> rs(N);
+        for (int64_t j = 0; j < N; j++) {
+          int32_t s = 0;
+          for (int64_t k = 0; k < in.ia[1]; k++) s += (int8_t)w.host[j * in.ia[1] + k];
+          rs[j] = s;
+        }
+        in.derived.push_back(f->add_i32_constant(tag + ".row_sums", rs));
+        ws = std::max(ws, glowb200_i8_gemm_workspace_bytes(in.ia[0], in.ia[1], N));
+        break;
+      }
+      case GLOWB200_INSTR_CWQ_CONV: {
+        if (!need(8, 21, 2)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed CWQ_CONV", ii);
+        const int64_t OC = in.ia[6];
+        if (f->symbols[in.ops[4]].host.size() != (size_t)OC * 4 || f->symbols[in.ops[6]].host.size() != (size_t)OC * 4)
+          return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: filter/bias scales must be float constants of outC entries", ii);
+        in.derived = add_row_triples(f, tag, host_f32(f, in.ops[4]), OC, in.fa[0], host_f32(f, in.ops[6]), OC, in.fa[1]);
+        const int64_t od[4] = {in.ia[0], in.ia[4], in.ia[5], in.ia[6]}, id[4] = {in.ia[0], in.ia[1], in.ia[2], in.ia[3]};
+        const int64_t fd[4] = {in.ia[6], in.ia[7], in.ia[8], in.ia[3] / in.ia[15]}, k[2] = {in.ia[7], in.ia[8]}, s[2] = {in.ia[9], in.ia[10]};
+        const int64_t p[4] = {in.ia[11], in.ia[12], in.ia[13], in.ia[14]}, d[2] = {in.ia[16], in.ia[17]};
+        ws = std::max(ws, glowb200_conv2d_workspace_bytes(od, id, fd, k, s, p, in.ia[15], d));
+        break;
+      }
+      case GLOWB200_INSTR_ADD: {
+        if (!need(3, 4, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed ADD", ii);
+        std::vector<int32_t> t(6);
+        glowb200::quantize_scale_32to8(in.fa[0] / in.fa[2], t[0], t[1], t[2]);  // LLVMIRGen.cpp:1740-1743
+        glowb200::quantize_scale_32to8(in.fa[1] / in.fa[2], t[3], t[4], t[5]);
+        for (int32_t x : t) in.ia.push_back(x);
+        break;
+      }
+      case GLOWB200_INSTR_AVGPOOL: {
+        if (!need(2, 15, 2)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed AVGPOOL", ii);
+        // LLVMIRGen.cpp:3003-3046: the kernel area is folded into the scale when pads are counted
+        float sc = in.fa[0] / in.fa[1];
+        if (in.ia[14]) sc = sc / (float)(in.ia[6] * in.ia[7]);
+        int32_t a, b, c;
+        glowb200::quantize_scale_32to8(sc, a, b, c);
+        in.ia.push_back(a); in.ia.push_back(b); in.ia.push_back(c);
+        break;
+      }
+      case GLOWB200_INSTR_MAXSPLAT: if (!need(2, 2, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed MAXSPLAT", ii); break;
+      case GLOWB200_INSTR_QUANTIZE:
+      case GLOWB200_INSTR_DEQUANTIZE: if (!need(2, 2, 1)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed (de)quantize", ii); break;
+      case GLOWB200_INSTR_MAXPOOL: if (!need(2, 13, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed MAXPOOL", ii); break;
+      case GLOWB200_INSTR_TRANSPOSE: if (!need(2, 10, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed TRANSPOSE", ii); break;
+      case GLOWB200_INSTR_COPY: if (!need(2, 1, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed COPY", ii); break;
+      default: return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: unsupported kind %d (isOpSupported would refuse the node)", ii, in.kind);
+    }
+  }
+  // slab offsets: 64-byte alignment like glow::TensorAlignment (include/glow/Support/Memory.h:29)
+  for (Symbol &s : f->symbols) {
+    s.offset = f->slab_bytes[s.kind];
+    f->slab_bytes[s.kind] += align_up(s.bytes ? s.bytes : 1, 64);
+  }
+  f->workspace_bytes = align_up(ws, 256);
+  f->compiled = true;
+  return GLOWB200_OK;
+}
+
+extern "C" size_t glowb200_function_constant_bytes(const glowb200_function *f) { return f ? f->slab_bytes[kConstant] : 0; }
+
+// ---------------------------------------------------------------------------------------------
+// Device manager
+// ---------------------------------------------------------------------------------------------
+struct glowb200_device_manager {
+  int device = 0;
+  uint64_t max_memory = 0, used_memory = 0;
+  bool running = false;
+  cudaStream_t stream = nullptr;
+  int32_t *status_dev = nullptr;
+  std::map<std::string, LoadedNetwork> networks;
+  std::mutex lock;
+};
+
+extern "C" glowb200_device_manager *glowb200_device_manager_create(int device_id, uint64_t max_memory_bytes) {
+  auto *dm = new glowb200_device_manager();
+  dm->device = device_id;
+  dm->max_memory = max_memory_bytes;
+  return dm;
+}
+
+// DeviceManager::init: the CUDA context, the stream and the status word exist after this call, so
+// that the first request does not pay for them (Glow's tests wait 2 s for a run).
+extern "C" int glowb200_device_manager_init(glowb200_device_manager *dm) {
+  if (!dm) return set_error(GLOWB200_RUNTIME_ERROR, "NULL device manager");
+  std::lock_guard<std::mutex> g(dm->lock);
+  if (dm->running) return GLOWB200_OK;
+  if (cudaSetDevice(dm->device) != cudaSuccess) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "cannot select CUDA device %d", dm->device);
+  if (dm->max_memory == 0) {
+    size_t fr = 0, tot = 0;
+    if (cudaMemGetInfo(&fr, &tot) != cudaSuccess) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "cudaMemGetInfo failed");
+    dm->max_memory = fr;
+  }
+  if (cudaStreamCreateWithFlags(&dm->stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaMalloc(&dm->status_dev, 4) != cudaSuccess)
+    return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "cannot create stream / status word on device %d", dm->device);
+  cudaMemsetAsync(dm->status_dev, 0, 4, dm->stream);
+  dm->running = true;
+  return GLOWB200_OK;
+}
+
+extern "C" uint64_t glowb200_device_manager_maximum_memory(glowb200_device_manager *dm) { return dm ? dm->max_memory : 0; }
+extern "C" uint64_t glowb200_device_manager_available_memory(glowb200_device_manager *dm) {
+  return dm ? dm->max_memory - dm->used_memory : 0;
+}
+extern "C" int glowb200_device_manager_is_memory_available(glowb200_device_manager *dm, uint64_t estimate) {
+  return dm && dm->max_memory >= dm->used_memory + estimate;
+}
+
+static void free_network(LoadedNetwork &n) {
+  for (auto &p : n.slab) if (p) cudaFree(p);
+  if (n.workspace) cudaFree(n.workspace);
+}
+
+// addNetwork: name must be new, the network must fit the memory budget; uploads the constants.
+extern "C" int glowb200_device_manager_add_network(glowb200_device_manager *dm, glowb200_function *f) {
+  if (!dm || !f) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
+  std::lock_guard<std::mutex> g(dm->lock);
+  if (!dm->running) return set_error(GLOWB200_RUNTIME_ERROR, "device manager is not initialised");
+  if (!f->compiled) return set_error(GLOWB200_RUNTIME_ERROR, "function %s is not compiled", f->name.c_str());
+  if (dm->networks.count(f->name)) return set_error(GLOWB200_RUNTIME_ERROR, "Failed to add network: already have a function called %s", f->name.c_str());
+  const uint64_t total = f->slab_bytes[0] + f->slab_bytes[1] + f->slab_bytes[2] + f->workspace_bytes;
+  if (dm->used_memory + total > dm->max_memory) return set_error(GLOWB200_RUNTIME_OUT_OF_DEVICE_MEMORY, "Failed to add network: not enough memory");
+  cudaSetDevice(dm->device);
+  LoadedNetwork n;
+  n.fn = f;
+  n.device_bytes = total;
+  bool ok = true;
+  for (int k = 0; k < 3 && ok; k++)
+    if (f->slab_bytes[k]) ok = cudaMalloc(&n.slab[k], f->slab_bytes[k]) == cudaSuccess;
+  if (ok) ok = cudaMalloc(&n.workspace, f->workspace_bytes) == cudaSuccess;
+  if (ok)
+    for (const Symbol &s : f->symbols)
+      if (s.kind == kConstant && s.bytes)
+        ok = ok && cudaMemcpyAsync(n.slab[0] + s.offset, s.host.data(), s.bytes, cudaMemcpyHostToDevice, dm->stream) == cudaSuccess;
+  if (ok) ok = cudaStreamSynchronize(dm->stream) == cudaSuccess;
+  if (!ok) {
+    free_network(n);
+    cudaGetLastError();
+    return set_error(GLOWB200_RUNTIME_OUT_OF_DEVICE_MEMORY, "Failed to add network: device allocation or upload failed");
+  }
+  dm->used_memory += total;
+  dm->networks[f->name] = n;
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_device_manager_evict_network(glowb200_device_manager *dm, const char *name) {
+  if (!dm || !name) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
+  std::lock_guard<std::mutex> g(dm->lock);
+  auto it = dm->networks.find(name);
+  if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Could not find function with name %s to evict", name);
+  cudaSetDevice(dm->device);
+  cudaStreamSynchronize(dm->stream);
+  free_network(it->second);
+  dm->used_memory -= it->second.device_bytes;
+  dm->networks.erase(it);
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_device_manager_stop(glowb200_device_manager *dm) {
+  if (!dm) return GLOWB200_OK;
+  std::lock_guard<std::mutex> g(dm->lock);
+  if (!dm->running) return GLOWB200_OK;
+  cudaSetDevice(dm->device);
+  cudaStreamSynchronize(dm->stream);
+  for (auto &kv : dm->networks) free_network(kv.second);
+  dm->networks.clear();
+  dm->used_memory = 0;
+  cudaFree(dm->status_dev);
+  cudaStreamDestroy(dm->stream);
+  dm->status_dev = nullptr;
+  dm->stream = nullptr;
+  dm->running = false;
+  return GLOWB200_OK;
+}
+
+extern "C" void glowb200_device_manager_destroy(glowb200_device_manager *dm) {
+  if (dm) {
+    glowb200_device_manager_stop(dm);
+    delete dm;
+  }
+}
+
+namespace {
+
+int execute(glowb200_device_manager *dm, LoadedNetwork &n) {
+  glowb200_function *f = n.fn;
+  auto ptr = [&](int id) -> void * {
+    if (id < 0) return nullptr;
+    const Symbol &s = f->symbols[id];
+    return n.slab[s.kind] + s.offset;
+  };
+  void *st = dm->stream;
+  for (size_t ii = 0; ii < f->instrs.size(); ii++) {
+    const Instruction &in = f->instrs[ii];
+    const auto &a = in.ia;
+    int rc = GLOWB200_OK;
+    switch (in.kind) {
+      case GLOWB200_INSTR_FRWQ_SLWS:
+        rc = glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
+            ptr(in.ops[0]), ptr(in.ops[1]), (int)a[0], a[1], ptr(in.ops[2]), ptr(in.ops[3]), (int)a[6],
+            (const int32_t *)ptr(in.ops[4]), a[4], a[5], a[2], a[3], (int)a[7], (int)a[8], n.workspace, f->workspace_bytes,
+            dm->status_dev, st);
+        break;
+      case GLOWB200_INSTR_RWQ_FC: {
+        auto d = [&](int i) { return (const int32_t *)ptr(in.derived[i]); };
+        rc = glowb200_rowwise_quantized_fc_i8_i32(
+            (int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]), (const int32_t *)ptr(in.ops[5]),
+            (const int32_t *)ptr(in.ops[4]), d(0), d(1), d(2), d(3), d(4), d(5), a[0], a[1], a[2], (int32_t)a[5], (int32_t)a[3],
+            (int32_t)a[4], d(6), a[6] ? GLOWB200_FC_FUSE_RELU : 0, n.workspace, f->workspace_bytes, dm->status_dev, st);
+        break;
+      }
+      case GLOWB200_INSTR_CWQ_CONV: {
+        auto d = [&](int i) { return (const int32_t *)ptr(in.derived[i]); };
+        const int64_t od[4] = {a[0], a[4], a[5], a[6]}, id[4] = {a[0], a[1], a[2], a[3]}, fd[4] = {a[6], a[7], a[8], a[3] / a[15]};
+        const int64_t k[2] = {a[7], a[8]}, s[2] = {a[9], a[10]}, p[4] = {a[11], a[12], a[13], a[14]}, dl[2] = {a[16], a[17]};
+        rc = glowb200_channelwise_quantized_conv2d_i8_i32(
+            (int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]), (const int32_t *)ptr(in.ops[3]),
+            od, id, fd, k, s, p, a[15], dl, (int32_t)a[19], (int32_t)a[18], (const int32_t *)ptr(in.ops[5]),
+            (const int32_t *)ptr(in.ops[7]), d(0), d(1), d(2), d(3), d(4), d(5), (int32_t)a[20], nullptr, nullptr, 0, n.workspace,
+            f->workspace_bytes, dm->status_dev, st);
+        break;
+      }
+      case GLOWB200_INSTR_ADD:
+        rc = glowb200_element_add_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]), a[0],
+                                     (int32_t)a[1], (int32_t)a[2], (int32_t)a[3], (int32_t)a[4], (int32_t)a[5], (int32_t)a[6],
+                                     (int32_t)a[7], (int32_t)a[8], (int32_t)a[9], st);
+        break;
+      case GLOWB200_INSTR_MAXSPLAT:
+        rc = glowb200_element_maxsplat_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), a[0], (int32_t)a[1], st);
+        break;
+      case GLOWB200_INSTR_QUANTIZE:
+        rc = glowb200_element_quantize_i8((int8_t *)ptr(in.ops[0]), (const float *)ptr(in.ops[1]), a[0], in.fa[0], (int32_t)a[1], st);
+        break;
+      case GLOWB200_INSTR_DEQUANTIZE:
+        rc = glowb200_element_dequantize_i8((float *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), a[0], in.fa[0], (int32_t)a[1], st);
+        break;
+      case GLOWB200_INSTR_MAXPOOL: {
+        const int64_t id[4] = {a[0], a[1], a[2], a[3]}, od[4] = {a[0], a[4], a[5], a[3]}, k[2] = {a[6], a[7]}, s[2] = {a[8], a[9]};
+        const int64_t p[4] = {a[10], a[11], a[10], a[11]};
+        rc = glowb200_max_pool_i8((const int8_t *)ptr(in.ops[1]), (int8_t *)ptr(in.ops[0]), id, od, k, s, p, (int32_t)a[12], st);
+        break;
+      }
+      case GLOWB200_INSTR_AVGPOOL: {
+        const int64_t id[4] = {a[0], a[1], a[2], a[3]}, od[4] = {a[0], a[4], a[5], a[3]}, k[2] = {a[6], a[7]}, s[2] = {a[8], a[9]};
+        const int64_t p[4] = {a[10], a[11], a[10], a[11]};
+        rc = glowb200_avg_pool_i8((const int8_t *)ptr(in.ops[1]), (int8_t *)ptr(in.ops[0]), id, od, k, s, p, (int)a[14], (int32_t)a[13],
+                                  (int32_t)a[12], (int32_t)a[15], (int32_t)a[16], (int32_t)a[17], st);
+        break;
+      }
+      case GLOWB200_INSTR_TRANSPOSE: {
+        const int nd = (int)a[0];
+        int64_t dims[4];
+        int32_t sh[4];
+        for (int i = 0; i < nd; i++) { dims[i] = a[2 + i]; sh[i] = (int32_t)a[6 + i]; }
+        rc = glowb200_transpose(ptr(in.ops[1]), ptr(in.ops[0]), dims, sh, nd, (int)a[1], st);
+        break;
+      }
+      case GLOWB200_INSTR_COPY:
+        if (cudaMemcpyAsync(ptr(in.ops[0]), ptr(in.ops[1]), (size_t)a[0], cudaMemcpyDeviceToDevice, dm->stream) != cudaSuccess)
+          rc = set_error(GLOWB200_RUNTIME_ERROR, "copy failed");
+        break;
+    }
+    if (rc != GLOWB200_OK) {
+      // keep the kernel ABI's message, report it as a runtime error of this instruction
+      char msg[400];
+      snprintf(msg, sizeof(msg), "%s", glowb200_last_error());
+      return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu of %s failed: %s", ii, f->name.c_str(), msg);
+    }
+  }
+  return GLOWB200_OK;
+}
+
+}  // namespace
+
+// runFunction: `bindings` pairs placeholder names with HOST buffers (the PlaceholderBindings of
+// an ExecutionContext).  Every bound placeholder is copied to the device before the run and
+// every bound placeholder is copied back after it -- inputs come back unchanged, outputs carry
+// the results (LLVMCompiledFunction::loadPlaceholders / updatePlaceholders,
+// lib/LLVMIRCodeGen/LLVMCompiledFunction.cpp:33-71, do the same with memcpy).  A binding may be
+// shorter than the placeholder (a partial tensor, supportsPartialTensors): the rest is zeroed.
+extern "C" int glowb200_device_manager_run_function(glowb200_device_manager *dm, const char *name, const char *const *placeholder_names,
+                                                    void *const *host_buffers, const size_t *buffer_bytes, int num_bindings) {
+  if (!dm || !name) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
+  std::lock_guard<std::mutex> g(dm->lock);
+  if (!dm->running) return set_error(GLOWB200_RUNTIME_ERROR, "device manager is not initialised");
+  auto it = dm->networks.find(name);
+  if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Function %s not found", name);
+  LoadedNetwork &n = it->second;
+  glowb200_function *f = n.fn;
+  cudaSetDevice(dm->device);
+  std::vector<int> ids(num_bindings);
+  for (int b = 0; b < num_bindings; b++) {
+    auto s = f->by_name.find(placeholder_names[b]);
+    if (s == f->by_name.end() || f->symbols[s->second].kind != kPlaceholder)
+      return set_error(GLOWB200_RUNTIME_ERROR, "%s is not a placeholder of %s", placeholder_names[b], name);
+    ids[b] = s->second;
+    const Symbol &sym = f->symbols[ids[b]];
+    if (buffer_bytes[b] > sym.bytes) return set_error(GLOWB200_RUNTIME_ERROR, "binding of %s is larger than the placeholder", sym.name.c_str());
+    uint8_t *d = n.slab[kPlaceholder] + sym.offset;
+    bool ok = cudaMemcpyAsync(d, host_buffers[b], buffer_bytes[b], cudaMemcpyHostToDevice, dm->stream) == cudaSuccess;
+    if (ok && buffer_bytes[b] < sym.bytes) ok = cudaMemsetAsync(d + buffer_bytes[b], 0, sym.bytes - buffer_bytes[b], dm->stream) == cudaSuccess;
+    if (!ok) return set_error(GLOWB200_RUNTIME_ERROR, "host-to-device copy of %s failed", sym.name.c_str());
+  }
+  if (int rc = execute(dm, n)) return rc;
+  for (int b = 0; b < num_bindings; b++) {
+    const Symbol &sym = f->symbols[ids[b]];
+    if (cudaMemcpyAsync(host_buffers[b], n.slab[kPlaceholder] + sym.offset, buffer_bytes[b], cudaMemcpyDeviceToHost, dm->stream) != cudaSuccess)
+      return set_error(GLOWB200_RUNTIME_ERROR, "device-to-host copy of %s failed", sym.name.c_str());
+  }
+  int32_t status = 0;
+  cudaMemcpyAsync(&status, dm->status_dev, 4, cudaMemcpyDeviceToHost, dm->stream);
+  cudaMemsetAsync(dm->status_dev, 0, 4, dm->stream);
+  const cudaError_t e = cudaStreamSynchronize(dm->stream);
+  if (e != cudaSuccess) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "device error while running %s: %s", name, cudaGetErrorString(e));
+  if (status & GLOWB200_STATUS_WAIT_TIMEOUT) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "a device-side wait gave up while running %s", name);
+  if (status) return set_error(GLOWB200_RUNTIME_ERROR, "invalid sparse input to %s (status bits 0x%x: index out of range 1, lengths overrun 2, negative length 4, bad offsets 8)", name, status);
+  return GLOWB200_OK;
+}

@@ -1,0 +1,167 @@
+"""ctypes front end of the host runtime (glowb200_function_* / glowb200_device_manager_*).
+
+`Function` builds what Backend::compile would hand to a device manager -- symbols and a flat
+instruction list -- and `DeviceManager` is the addNetwork / evictNetwork / runFunction object.
+The helper methods only marshal arguments; parameter derivation and execution are in the
+library (glow_b200/csrc/runtime.cu).
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import GlowB200Error
+
+CONSTANT, PLACEHOLDER, ACTIVATION = 0, 1, 2
+(FRWQ_SLWS, RWQ_FC, CWQ_CONV, ADD, MAXSPLAT, QUANTIZE, DEQUANTIZE, MAXPOOL, AVGPOOL, TRANSPOSE, COPY) = range(1, 12)
+
+RUNTIME_ERROR, OUT_OF_DEVICE_MEMORY, NET_NOT_FOUND, DEVICE_NONRECOVERABLE = 101, 102, 103, 104
+
+
+def _check(rc):
+    if rc != 0:
+        raise GlowB200Error(rc, _lib.lib().glowb200_last_error().decode())
+
+
+class Function:
+    def __init__(self, name):
+        self.name = name
+        self.h = _lib.lib().glowb200_function_create(name.encode())
+        self.sizes = {}
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            _lib.lib().glowb200_function_destroy(self.h)
+            self.h = None
+
+    def _symbol(self, name, kind, nbytes, data=None):
+        sid = _lib.lib().glowb200_function_add_symbol(self.h, name.encode(), kind, int(nbytes),
+                                                      None if data is None else C.c_void_p(data.ctypes.data))
+        if sid < 0:
+            raise GlowB200Error(RUNTIME_ERROR, _lib.lib().glowb200_last_error().decode())
+        self.sizes[name] = int(nbytes)
+        return sid
+
+    def constant(self, name, array):
+        a = np.ascontiguousarray(array)
+        return self._symbol(name, CONSTANT, a.nbytes, a)
+
+    def placeholder(self, name, nbytes):
+        return self._symbol(name, PLACEHOLDER, nbytes)
+
+    def activation(self, name, nbytes):
+        return self._symbol(name, ACTIVATION, nbytes)
+
+    def instruction(self, kind, operands, int_attrs=(), float_attrs=()):
+        ops = (C.c_int32 * len(operands))(*operands)
+        ia = (C.c_int64 * max(1, len(int_attrs)))(*[int(v) for v in int_attrs])
+        fa = (C.c_float * max(1, len(float_attrs)))(*[float(v) for v in float_attrs])
+        _check(_lib.lib().glowb200_function_add_instruction(self.h, kind, ops, len(operands), ia, len(int_attrs), fa,
+                                                            len(float_attrs)))
+
+    # readable wrappers over the attribute layouts documented in runtime.cu
+    def frwq_slws(self, dest, data, weights, indices, lengths, *, kind, rows, in_line, out_line, segments, num_indices,
+                  idx64=True, out_fp16=False, fp16_acc=False):
+        self.instruction(FRWQ_SLWS, [dest, data, weights, indices, lengths],
+                         [kind, rows, in_line, out_line, segments, num_indices, int(idx64), int(out_fp16), int(fp16_acc)])
+
+    def rowwise_fc(self, dest, src, weights, scales, offsets, bias, *, M, K, N, in_tqp, bias_tqp, out_tqp, relu=False):
+        self.instruction(RWQ_FC, [dest, src, weights, scales, offsets, bias],
+                         [M, K, N, in_tqp[1], bias_tqp[1], out_tqp[1], int(relu)], [in_tqp[0], bias_tqp[0], out_tqp[0]])
+
+    def channelwise_conv(self, dest, src, filt, bias, filter_scales, filter_offsets, bias_scales, bias_offsets, *, in_dims,
+                         out_dims, kernels, strides, pads, group=1, dilation=(1, 1), in_tqp, out_tqp, act=0):
+        n, h, w, c = in_dims
+        _, oh, ow, oc = out_dims
+        self.instruction(CWQ_CONV, [dest, src, filt, bias, filter_scales, filter_offsets, bias_scales, bias_offsets],
+                         [n, h, w, c, oh, ow, oc, kernels[0], kernels[1], strides[0], strides[1], pads[0], pads[1], pads[2],
+                          pads[3], group, dilation[0], dilation[1], in_tqp[1], out_tqp[1], act], [in_tqp[0], out_tqp[0]])
+
+    def add(self, dest, lhs, rhs, *, n, lhs_tqp, rhs_tqp, dest_tqp):
+        self.instruction(ADD, [dest, lhs, rhs], [n, dest_tqp[1], lhs_tqp[1], rhs_tqp[1]], [lhs_tqp[0], rhs_tqp[0], dest_tqp[0]])
+
+    def maxsplat(self, dest, src, *, n, splat):
+        self.instruction(MAXSPLAT, [dest, src], [n, splat])
+
+    def quantize(self, dest, src, *, n, tqp):
+        self.instruction(QUANTIZE, [dest, src], [n, tqp[1]], [tqp[0]])
+
+    def dequantize(self, dest, src, *, n, tqp):
+        self.instruction(DEQUANTIZE, [dest, src], [n, tqp[1]], [tqp[0]])
+
+    def maxpool(self, dest, src, *, in_dims, out_hw, kernels, strides, pads, out_offset):
+        n, h, w, c = in_dims
+        self.instruction(MAXPOOL, [dest, src], [n, h, w, c, out_hw[0], out_hw[1], kernels[0], kernels[1], strides[0], strides[1],
+                                                pads[0], pads[1], out_offset])
+
+    def avgpool(self, dest, src, *, in_dims, out_hw, kernels, strides, pads, in_tqp, out_tqp, count_include_pads=True):
+        n, h, w, c = in_dims
+        self.instruction(AVGPOOL, [dest, src], [n, h, w, c, out_hw[0], out_hw[1], kernels[0], kernels[1], strides[0], strides[1],
+                                                pads[0], pads[1], in_tqp[1], out_tqp[1], int(count_include_pads)],
+                         [in_tqp[0], out_tqp[0]])
+
+    def transpose(self, dest, src, *, dims, shuffle, elem_bytes):
+        d = list(dims) + [1] * (4 - len(dims))
+        s = list(shuffle) + [0] * (4 - len(shuffle))
+        self.instruction(TRANSPOSE, [dest, src], [len(dims), elem_bytes] + d + s)
+
+    def copy(self, dest, src, *, nbytes):
+        self.instruction(COPY, [dest, src], [nbytes])
+
+    def compile(self):
+        _check(_lib.lib().glowb200_function_compile(self.h))
+        return self
+
+    @property
+    def constant_bytes(self):
+        return int(_lib.lib().glowb200_function_constant_bytes(self.h))
+
+
+class DeviceManager:
+    def __init__(self, device_id=0, max_memory_bytes=0):
+        self.h = _lib.lib().glowb200_device_manager_create(int(device_id), int(max_memory_bytes))
+        self._functions = {}
+
+    def init(self):
+        _check(_lib.lib().glowb200_device_manager_init(self.h))
+        return self
+
+    def add_network(self, fn):
+        _check(_lib.lib().glowb200_device_manager_add_network(self.h, fn.h))
+        self._functions[fn.name] = fn  # the device manager borrows the function
+
+    def evict_network(self, name):
+        _check(_lib.lib().glowb200_device_manager_evict_network(self.h, name.encode()))
+        self._functions.pop(name, None)
+
+    def run_function(self, name, bindings):
+        """bindings: dict placeholder name -> numpy array (inputs are read, every array is written back)."""
+        names = list(bindings)
+        arrs = [bindings[k] for k in names]
+        for a in arrs:
+            if not (isinstance(a, np.ndarray) and a.flags["C_CONTIGUOUS"] and a.flags["WRITEABLE"]):
+                raise TypeError("bindings must be writable C-contiguous numpy arrays")
+        cn = (C.c_char_p * len(names))(*[k.encode() for k in names])
+        cb = (C.c_void_p * len(names))(*[a.ctypes.data for a in arrs])
+        cs = (C.c_size_t * len(names))(*[a.nbytes for a in arrs])
+        _check(_lib.lib().glowb200_device_manager_run_function(self.h, name.encode(), cn, cb, cs, len(names)))
+
+    @property
+    def maximum_memory(self):
+        return int(_lib.lib().glowb200_device_manager_maximum_memory(self.h))
+
+    @property
+    def available_memory(self):
+        return int(_lib.lib().glowb200_device_manager_available_memory(self.h))
+
+    def is_memory_available(self, estimate):
+        return bool(_lib.lib().glowb200_device_manager_is_memory_available(self.h, int(estimate)))
+
+    def stop(self):
+        _check(_lib.lib().glowb200_device_manager_stop(self.h))
+        self._functions.clear()
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            _lib.lib().glowb200_device_manager_destroy(self.h)
+            self.h = None

@@ -35,6 +35,13 @@ extern "C" {
 #define GLOWB200_ERR_WORKSPACE_TOO_SMALL 3
 #define GLOWB200_ERR_CUDA 4
 
+/* Codes returned by the host runtime (glowb200_function_* / glowb200_device_manager_*), named
+ * after glow::ErrorValue::ErrorCode (include/glow/Support/Error.h:292-339). */
+#define GLOWB200_RUNTIME_ERROR 101
+#define GLOWB200_RUNTIME_OUT_OF_DEVICE_MEMORY 102
+#define GLOWB200_RUNTIME_NET_NOT_FOUND 103
+#define GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE 104
+
 /* Bits OR-ed into *status by kernels. */
 #define GLOWB200_STATUS_INDEX_OUT_OF_RANGE 1 /* an index outside [0, rows): that row is skipped   */
 #define GLOWB200_STATUS_LENGTHS_OVERRUN 2    /* sum(lengths) > len(indices): bags are truncated   */
@@ -334,6 +341,66 @@ int glowb200_peer_buffer_create(size_t bytes, void **device_ptr, void *ipc_handl
 int glowb200_peer_buffer_open(const void *ipc_handle_64_bytes, void **device_ptr);
 int glowb200_peer_buffer_close(void *device_ptr);
 int glowb200_peer_buffer_destroy(void *device_ptr);
+
+/* ---------------------------------------------------------------------------------------
+ * Host runtime: the compiled-function and device-manager layer of a Glow backend, written
+ * against this library (runtime.cu).  A function is a symbol table over three slabs
+ * (constants, placeholders, activations: glow::RuntimeBundle, include/glow/Backend/
+ * BackendUtils.h:66-170) plus a flat instruction list; glowb200_function_compile derives the
+ * integer requantisation parameters from the float scales the way LLVMIRGen does and lays the
+ * slabs out.  The device manager mirrors glow::DeviceManager (include/glow/Backends/
+ * DeviceManager.h:47-241) as CPUDeviceManager implements it
+ * (lib/Backends/CPU/CPUDeviceManager.cpp:65-179).  Calls are synchronous; a Glow
+ * QueueBackedDeviceManager would make them from its one worker thread.
+ * Operand and attribute layouts of every instruction kind are listed above
+ * glowb200_function_compile in runtime.cu.
+ * ------------------------------------------------------------------------------------- */
+#define GLOWB200_SYMBOL_CONSTANT 0
+#define GLOWB200_SYMBOL_PLACEHOLDER 1
+#define GLOWB200_SYMBOL_ACTIVATION 2
+
+#define GLOWB200_INSTR_FRWQ_SLWS 1
+#define GLOWB200_INSTR_RWQ_FC 2
+#define GLOWB200_INSTR_CWQ_CONV 3
+#define GLOWB200_INSTR_ADD 4
+#define GLOWB200_INSTR_MAXSPLAT 5
+#define GLOWB200_INSTR_QUANTIZE 6
+#define GLOWB200_INSTR_DEQUANTIZE 7
+#define GLOWB200_INSTR_MAXPOOL 8
+#define GLOWB200_INSTR_AVGPOOL 9
+#define GLOWB200_INSTR_TRANSPOSE 10
+#define GLOWB200_INSTR_COPY 11
+
+typedef struct glowb200_function glowb200_function;
+typedef struct glowb200_device_manager glowb200_device_manager;
+
+glowb200_function *glowb200_function_create(const char *name);
+void glowb200_function_destroy(glowb200_function *f);
+/* Returns the symbol id (>= 0) or -1.  Constants carry their host data (copied). */
+int glowb200_function_add_symbol(glowb200_function *f, const char *name, int kind, size_t bytes,
+                                 const void *host_data);
+int glowb200_function_add_instruction(glowb200_function *f, int kind, const int32_t *operands,
+                                      int num_operands, const int64_t *int_attrs, int num_int_attrs,
+                                      const float *float_attrs, int num_float_attrs);
+int glowb200_function_compile(glowb200_function *f);
+size_t glowb200_function_constant_bytes(const glowb200_function *f);
+
+/* max_memory_bytes 0 = the device's free memory at init. */
+glowb200_device_manager *glowb200_device_manager_create(int device_id, uint64_t max_memory_bytes);
+int glowb200_device_manager_init(glowb200_device_manager *dm);
+int glowb200_device_manager_add_network(glowb200_device_manager *dm, glowb200_function *f);
+int glowb200_device_manager_evict_network(glowb200_device_manager *dm, const char *name);
+/* Placeholder names paired with HOST buffers; every bound buffer is copied in before and out
+ * after the run; a buffer shorter than its placeholder is a partial tensor (rest zeroed). */
+int glowb200_device_manager_run_function(glowb200_device_manager *dm, const char *name,
+                                         const char *const *placeholder_names,
+                                         void *const *host_buffers, const size_t *buffer_bytes,
+                                         int num_bindings);
+uint64_t glowb200_device_manager_maximum_memory(glowb200_device_manager *dm);
+uint64_t glowb200_device_manager_available_memory(glowb200_device_manager *dm);
+int glowb200_device_manager_is_memory_available(glowb200_device_manager *dm, uint64_t estimate);
+int glowb200_device_manager_stop(glowb200_device_manager *dm);
+void glowb200_device_manager_destroy(glowb200_device_manager *dm);
 
 /* FusedRowwiseQuantizedSparseLengthsWeightedSum for callers that can neither allocate device
  * memory nor size a workspace per request.  (No counterpart in the reference: its CPU kernels

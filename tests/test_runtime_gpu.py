@@ -1,0 +1,200 @@
+"""The host runtime on a GPU: the reference's DeviceManager conformance cases
+(tests/unittests/DeviceManagerTest.cpp:132-973: Basic, MultiRun, MultiFunction, AvailableMemory,
+eviction and lookup errors, partial tensors) transposed to quantized functions, with every
+result checked against the CPU oracle."""
+import numpy as np
+import pytest
+
+from glow_b200 import ops, runtime, workloads
+from glow_b200._lib import GlowB200Error
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def dm():
+    d = runtime.DeviceManager(0).init()
+    yield d
+    d.stop()
+
+
+def slws_function(name, table, segments, max_indices):
+    rows, in_line = table.shape
+    f = runtime.Function(name)
+    data = f.constant(name + "_data", table)
+    w = f.placeholder(name + "_weights", max_indices * 4)
+    idx = f.placeholder(name + "_indices", max_indices * 8)
+    ln = f.placeholder(name + "_lengths", segments * 4)
+    out = f.placeholder(name + "_output", segments * (in_line - 8) * 4)
+    f.frwq_slws(out, data, w, idx, ln, kind=ops.UINT8_FUSED, rows=rows, in_line=in_line, out_line=in_line - 8,
+                segments=segments, num_indices=max_indices)
+    return f.compile()
+
+
+def run_slws(dm, name, w, idx, lengths, segments, dim, max_indices):
+    out = np.zeros((segments, dim), np.float32)
+    wp = np.zeros(max_indices, np.float32); wp[:w.size] = w
+    ip = np.zeros(max_indices, np.int64); ip[:idx.size] = idx
+    dm.run_function(name, {name + "_weights": wp, name + "_indices": ip, name + "_lengths": lengths.copy(),
+                           name + "_output": out})
+    return out
+
+
+def test_basic_and_multi_run(oracle, dm):
+    table = workloads.fused_table_u8(5000, 64, 1, 0)
+    f = slws_function("main", table, 128, 128 * 40)
+    dm.add_network(f)
+    for seed in (1, 2, 3):  # MultiRun: the same function, different requests
+        lengths, idx, w = workloads.bags_poisson(128, 20, 0, 40, 5000, seed, 1)
+        got = run_slws(dm, "main", w, idx, lengths, 128, 64, 128 * 40)
+        want = oracle.frwq_slws_u8_f32(table, w, idx, lengths)
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
+def test_multi_function_memory_accounting_and_errors(oracle, dm):
+    t1, t2 = workloads.fused_table_u8(3000, 64, 5, 0), workloads.fused_table_u8(2000, 64, 6, 0)
+    f1, f2 = slws_function("func1", t1, 32, 640), slws_function("func2", t2, 32, 640)
+    total = dm.available_memory
+    assert total == dm.maximum_memory
+    dm.add_network(f1)
+    after1 = dm.available_memory
+    assert total - after1 >= t1.nbytes
+    dm.add_network(f2)
+    assert dm.available_memory < after1
+    with pytest.raises(GlowB200Error, match="already have a function called func1") as e:
+        dm.add_network(f1)
+    assert e.value.code == runtime.RUNTIME_ERROR
+    for name, t in (("func1", t1), ("func2", t2)):
+        lengths, idx, w = workloads.bags_poisson(32, 10, 0, 20, t.shape[0], 9, 1)
+        np.testing.assert_allclose(run_slws(dm, name, w, idx, lengths, 32, 64, 640), oracle.frwq_slws_u8_f32(t, w, idx, lengths),
+                                   rtol=1e-5, atol=1e-5)
+    with pytest.raises(GlowB200Error) as e:
+        dm.run_function("nope", {})
+    assert e.value.code == runtime.NET_NOT_FOUND
+    dm.evict_network("func1")
+    dm.evict_network("func2")
+    assert dm.available_memory == total
+    with pytest.raises(GlowB200Error) as e:
+        dm.evict_network("func1")
+    assert e.value.code == runtime.NET_NOT_FOUND
+    dm.add_network(f1)  # a function can come back after eviction (ReuseModule)
+    assert dm.available_memory == after1
+
+
+def test_out_of_device_memory_is_an_error_not_a_crash():
+    small = runtime.DeviceManager(0, 1 << 20).init()
+    f = slws_function("big", workloads.fused_table_u8(50000, 64, 2, 0), 16, 160)
+    with pytest.raises(GlowB200Error) as e:
+        small.add_network(f)
+    assert e.value.code == runtime.OUT_OF_DEVICE_MEMORY
+    assert small.available_memory == 1 << 20
+    small.stop()
+
+
+def test_invalid_sparse_input_becomes_a_runtime_error(dm):
+    table = workloads.fused_table_u8(100, 64, 3, 0)
+    dm.add_network(slws_function("chk", table, 4, 16))
+    lengths = np.array([2, 2, 0, 0], np.int32)
+    with pytest.raises(GlowB200Error, match="invalid sparse input") as e:
+        run_slws(dm, "chk", np.ones(4, np.float32), np.array([1, 2, 100, 3], np.int64), lengths, 4, 64, 16)
+    assert e.value.code == runtime.RUNTIME_ERROR
+    # the device manager stays usable and the status word was cleared
+    got = run_slws(dm, "chk", np.ones(4, np.float32), np.array([1, 2, 4, 3], np.int64), lengths, 4, 64, 16)
+    assert np.isfinite(got).all() and got[:2].any()
+
+
+def test_partial_tensor_binding(oracle, dm):
+    """A binding shorter than its placeholder is a partial tensor: the rest reads as zero."""
+    table = workloads.fused_table_u8(1000, 64, 4, 0)
+    dm.add_network(slws_function("part", table, 8, 64))
+    lengths = np.array([3, 2, 0, 0, 0, 0, 0, 0], np.int32)
+    idx = np.array([5, 6, 7, 8, 9], np.int64)
+    w = np.ones(5, np.float32)
+    out = np.zeros((8, 64), np.float32)
+    dm.run_function("part", {"part_weights": w, "part_indices": idx, "part_lengths": lengths[:2].copy(), "part_output": out})
+    np.testing.assert_allclose(out, oracle.frwq_slws_u8_f32(table, w, idx, lengths), rtol=1e-5, atol=1e-5)
+
+
+def test_quantized_network_bit_exact(oracle, dm):
+    """NCHW fp32 -> Transpose -> Quantize -> conv3x3+Relu -> MaxPool -> [conv1x1, shortcut] -> Add -> Relu
+    -> AvgPool -> rowwise FC -> Dequantize, every integer parameter derived by the runtime's compile()."""
+    rng = np.random.default_rng(12)
+    n, cin, hw, c1, c2, classes = 3, 16, 12, 32, 32, 10
+    f = runtime.Function("net")
+    tq = dict(inp=(0.05, 2), c1=(0.11, -128), c2=(0.21, 5), sc=(0.17, -9), add=(0.3, -128), pool=(0.25, -128), fc=(0.4, 7))
+    conv_c = {}
+    for name, ci, co, k, in_name in (("c1", cin, c1, 3, "inp"), ("c2", c1, c2, 1, "c1"), ("sc", c1, c2, 1, "c1")):
+        w = (rng.standard_normal((co, k, k, ci)) * np.sqrt(2.0 / (k * k * ci))).astype(np.float32)
+        b = (rng.standard_normal(co) * 0.05).astype(np.float32)
+        conv_c[name] = ops.channelwise_conv_prepare(w, b, tq[in_name][0], ops.SYMMETRIC)
+    wf = (rng.standard_normal((classes, c2)) * 0.3).astype(np.float32)
+    fq, fs, fo = ops.tensor_rowwise_quantize_i8(wf, ops.ASYMMETRIC)
+    fbias_scale = np.float32(tq["pool"][0]) * np.float32(0.01)
+    fbias = ops.quantize_bias_i32((rng.standard_normal(classes) * 0.1).astype(np.float32), fbias_scale, 0)
+
+    oh = hw  # 3x3 pad 1
+    ph = (oh + 2 - 3) // 2 + 1
+    x_in = f.placeholder("input", n * cin * hw * hw * 4)
+    result = f.placeholder("result", n * classes * 4)
+    a_nhwc = f.activation("nhwc", n * hw * hw * cin * 4)
+    a_q = f.activation("q", n * hw * hw * cin)
+    a_c1 = f.activation("a_c1", n * oh * oh * c1)
+    a_p = f.activation("a_p", n * ph * ph * c1)
+    a_c2 = f.activation("a_c2", n * ph * ph * c2)
+    a_sc = f.activation("a_sc", n * ph * ph * c2)
+    a_add = f.activation("a_add", n * ph * ph * c2)
+    a_pool = f.activation("a_pool", n * c2)
+    a_fc = f.activation("a_fc", n * classes)
+
+    def conv_syms(name):
+        c = conv_c[name]
+        return [f.constant(name + "_" + k, c[k]) for k in ("filter", "bias", "filter_scales", "filter_offsets", "bias_scales", "bias_offsets")]
+
+    f.transpose(a_nhwc, x_in, dims=(n, cin, hw, hw), shuffle=(0, 2, 3, 1), elem_bytes=4)
+    f.quantize(a_q, a_nhwc, n=n * hw * hw * cin, tqp=tq["inp"])
+    s = conv_syms("c1")
+    f.channelwise_conv(a_c1, a_q, *s, in_dims=(n, hw, hw, cin), out_dims=(n, oh, oh, c1), kernels=(3, 3), strides=(1, 1),
+                       pads=(1, 1, 1, 1), in_tqp=tq["inp"], out_tqp=tq["c1"], act=1)
+    f.maxpool(a_p, a_c1, in_dims=(n, oh, oh, c1), out_hw=(ph, ph), kernels=(3, 3), strides=(2, 2), pads=(1, 1), out_offset=tq["c1"][1])
+    s = conv_syms("c2")
+    f.channelwise_conv(a_c2, a_p, *s, in_dims=(n, ph, ph, c1), out_dims=(n, ph, ph, c2), kernels=(1, 1), strides=(1, 1),
+                       pads=(0, 0, 0, 0), in_tqp=tq["c1"], out_tqp=tq["c2"], act=0)
+    s = conv_syms("sc")
+    f.channelwise_conv(a_sc, a_p, *s, in_dims=(n, ph, ph, c1), out_dims=(n, ph, ph, c2), kernels=(1, 1), strides=(1, 1),
+                       pads=(0, 0, 0, 0), in_tqp=tq["c1"], out_tqp=tq["sc"], act=0)
+    f.add(a_add, a_c2, a_sc, n=n * ph * ph * c2, lhs_tqp=tq["c2"], rhs_tqp=tq["sc"], dest_tqp=tq["add"])
+    f.maxsplat(a_add, a_add, n=n * ph * ph * c2, splat=tq["add"][1])
+    f.avgpool(a_pool, a_add, in_dims=(n, ph, ph, c2), out_hw=(1, 1), kernels=(ph, ph), strides=(1, 1), pads=(0, 0),
+              in_tqp=tq["add"], out_tqp=tq["pool"])
+    f.rowwise_fc(a_fc, a_pool, f.constant("fc_w", fq), f.constant("fc_scales", fs), f.constant("fc_offsets", fo),
+                 f.constant("fc_bias", fbias), M=n, K=c2, N=classes, in_tqp=tq["pool"], bias_tqp=(fbias_scale, 0), out_tqp=tq["fc"])
+    f.dequantize(result, a_fc, n=n * classes, tqp=tq["fc"])
+    f.compile()
+    dm.add_network(f)
+
+    x = rng.standard_normal((n, cin, hw, hw)).astype(np.float32)
+    out = np.zeros((n, classes), np.float32)
+    dm.run_function("net", {"input": x.copy(), "result": out})
+
+    # the same network through the oracle, with parameters derived by the oracle's own restatement
+    def oconv(name, t, in_name, out_name, k, pad, act):
+        c = conv_c[name]
+        pp = oracle.rowwise_requant_params(c["filter_scales"], tq[in_name][0], c["bias_scales"], tq[out_name][0])
+        ohw = ops.conv_out_hw(t.shape[1:3], (k, k), (1, 1), (pad,) * 4)
+        return oracle.conv2d_i8_i32(t, c["filter"], c["bias"], ohw, (k, k), (1, 1), (pad,) * 4, 1, (1, 1), tq[out_name][1],
+                                    tq[in_name][1], c["filter_offsets"], c["bias_offsets"], pp[:3], pp[3:], act, None)
+
+    t = oracle.element_quantize_i8(np.ascontiguousarray(x.transpose(0, 2, 3, 1)), *tq["inp"])
+    t = oconv("c1", t, "inp", "c1", 3, 1, 1)
+    t = oracle.max_pool_i8(t, (ph, ph), (3, 3), (2, 2), (1, 1, 1, 1), tq["c1"][1])
+    y, s_ = oconv("c2", t, "c1", "c2", 1, 0, 0), oconv("sc", t, "c1", "sc", 1, 0, 0)
+    lt = oracle.quantize_scale_offset_32to8(np.float32(tq["c2"][0]) / np.float32(tq["add"][0]))
+    rt = oracle.quantize_scale_offset_32to8(np.float32(tq["sc"][0]) / np.float32(tq["add"][0]))
+    t = oracle.element_maxsplat_i8(oracle.element_add_i8(y, s_, tq["add"][1], tq["c2"][1], tq["sc"][1], lt, rt), tq["add"][1])
+    tr = oracle.quantize_scale_offset_32to8(np.float32(tq["add"][0]) / np.float32(tq["pool"][0]) / np.float32(ph * ph))
+    t = oracle.avg_pool_i8(t, (1, 1), (ph, ph), (1, 1), (0, 0, 0, 0), True, tq["pool"][1], tq["add"][1], tr)
+    pp = oracle.rowwise_requant_params(fs, tq["pool"][0], fbias_scale, tq["fc"][0])
+    q = oracle.rowwise_quantized_fc_i8_i32(t.reshape(n, c2), fq, fbias, fo, pp[:3], pp[3:], tq["fc"][1], tq["pool"][1], 0)
+    want = oracle.element_dequantize_i8(q, *tq["fc"])
+    np.testing.assert_array_equal(out.view(np.uint32), want.view(np.uint32))
+    assert len(np.unique(q)) > 5
