@@ -1,0 +1,153 @@
+#include "B200Function.h"
+
+#include "glow/Graph/Graph.h"
+#include "glow/IR/Instrs.h"
+#include "glow/Support/Error.h"
+
+using namespace glow;
+
+namespace {
+int fusedKind(ElemKind k) {
+  switch (k) {
+  case ElemKind::UInt8FusedQTy: return GLOWB200_UINT8_FUSED;
+  case ElemKind::UInt8FusedFP16QTy: return GLOWB200_UINT8_FUSED_FP16;
+  case ElemKind::UInt4FusedQTy: return GLOWB200_UINT4_FUSED;
+  default: return GLOWB200_UINT4_FUSED_FP16;
+  }
+}
+Error fromRuntime(int rc) {
+  if (rc == GLOWB200_OK) return Error::success();
+  auto code = rc == GLOWB200_RUNTIME_NET_NOT_FOUND             ? ErrorValue::ErrorCode::RUNTIME_NET_NOT_FOUND
+              : rc == GLOWB200_RUNTIME_OUT_OF_DEVICE_MEMORY    ? ErrorValue::ErrorCode::RUNTIME_OUT_OF_DEVICE_MEMORY
+              : rc == GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE   ? ErrorValue::ErrorCode::RUNTIME_DEVICE_NONRECOVERABLE
+                                                               : ErrorValue::ErrorCode::RUNTIME_ERROR;
+  return MAKE_ERR(code, glowb200_last_error());
+}
+} // namespace
+
+B200Function::B200Function(std::unique_ptr<IRFunction> F, runtime::RuntimeBundle &&bundle)
+    : CompiledFunction(std::move(bundle)), F_(std::move(F)) {}
+
+B200Function::~B200Function() { glowb200_function_destroy(fn_); }
+
+void B200Function::collectConstants(const Module *module) {
+  if (fn_) return;
+  EXIT_ON_ERR(translate(module));
+}
+
+Error B200Function::translate(const Module *module) {
+  fn_ = glowb200_function_create(F_->getGraph()->getName().str().c_str());
+  std::unordered_map<const Value *, int> sym;
+  // WeightVars: constants carry their payload, placeholders are bound per request.
+  for (auto *W : F_->getWeights()) {
+    const size_t bytes = W->getType()->getSizeInBytes();
+    if (auto *C = module->getConstantByName(W->getName())) {
+      sym[W] = glowb200_function_add_symbol(fn_, W->getName().str().c_str(), GLOWB200_SYMBOL_CONSTANT, bytes,
+                                            C->getPayload().getUnsafePtr());
+    } else {
+      sym[W] = glowb200_function_add_symbol(fn_, W->getName().str().c_str(), GLOWB200_SYMBOL_PLACEHOLDER, bytes, nullptr);
+    }
+  }
+  auto S = [&](const Value *v) {  // symbol of a value, looking through tensor views
+    while (auto *TV = llvm::dyn_cast<TensorViewInst>(v)) v = TV->getSrc();
+    return sym.at(v);
+  };
+  for (const auto &I : F_->getInstrs()) {
+    switch (I.getKind()) {
+    case Kinded::Kind::AllocActivationInstKind:
+      sym[&I] = glowb200_function_add_symbol(fn_, I.getName().str().c_str(), GLOWB200_SYMBOL_ACTIVATION,
+                                             llvm::cast<AllocActivationInst>(&I)->getTy()->getSizeInBytes(), nullptr);
+      break;
+    case Kinded::Kind::DeallocActivationInstKind:
+    case Kinded::Kind::TensorViewInstKind:
+    case Kinded::Kind::TouchInstKind:
+      break;
+    case Kinded::Kind::FusedRowwiseQuantizedSparseLengthsWeightedSumInstKind: {
+      auto *N = llvm::cast<FusedRowwiseQuantizedSparseLengthsWeightedSumInst>(&I);
+      auto *D = N->getData();
+      const int32_t ops[5] = {S(N->getDest()), S(D), S(N->getWeights()), S(N->getIndices()), S(N->getLengths())};
+      const int64_t ia[9] = {fusedKind(D->getElementType()), (int64_t)D->dims()[0], (int64_t)D->dims()[1],
+                             (int64_t)N->getDest()->dims()[1], (int64_t)N->getLengths()->dims()[0],
+                             (int64_t)N->getIndices()->dims()[0], N->getIndices()->getElementType() == ElemKind::Int64ITy,
+                             N->getDest()->getElementType() == ElemKind::Float16Ty, N->getUseFP16Accumulation()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_FRWQ_SLWS, ops, 5, ia, 9, nullptr, 0)));
+      break;
+    }
+    case Kinded::Kind::RowwiseQuantizedFullyConnectedInstKind: {
+      auto *N = llvm::cast<RowwiseQuantizedFullyConnectedInst>(&I);
+      const int32_t ops[6] = {S(N->getDest()), S(N->getSrc()), S(N->getWeights()), S(N->getScales()), S(N->getOffsets()), S(N->getBias())};
+      const int64_t ia[7] = {(int64_t)N->getSrc()->dims()[0], (int64_t)N->getSrc()->dims()[1], (int64_t)N->getWeights()->dims()[0],
+                             N->getSrc()->getType()->getOffset(), N->getBias()->getType()->getOffset(),
+                             N->getDest()->getType()->getOffset(), 0};
+      const float fa[3] = {N->getSrc()->getType()->getScale(), N->getBias()->getType()->getScale(), N->getDest()->getType()->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_RWQ_FC, ops, 6, ia, 7, fa, 3)));
+      break;
+    }
+    case Kinded::Kind::ChannelwiseQuantizedConvolutionInstKind: {
+      auto *N = llvm::cast<ChannelwiseQuantizedConvolutionInst>(&I);
+      const int32_t ops[8] = {S(N->getDest()), S(N->getSrc()), S(N->getFilter()), S(N->getBias()), S(N->getFilterScales()),
+                              S(N->getFilterOffsets()), S(N->getBiasScales()), S(N->getBiasOffsets())};
+      auto in = N->getSrc()->dims(), out = N->getDest()->dims();
+      auto k = N->getKernels(), s = N->getStrides(), p = N->getPads(), d = N->getDilation();
+      const int64_t ia[21] = {(int64_t)in[0], (int64_t)in[1], (int64_t)in[2], (int64_t)in[3], (int64_t)out[1], (int64_t)out[2],
+                              (int64_t)out[3], k[0], k[1], s[0], s[1], p[0], p[1], p[2], p[3], N->getGroup(), d[0], d[1],
+                              N->getSrc()->getType()->getOffset(), N->getDest()->getType()->getOffset(),
+                              (int64_t)N->getFusedActivation()};
+      const float fa[2] = {N->getSrc()->getType()->getScale(), N->getDest()->getType()->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_CWQ_CONV, ops, 8, ia, 21, fa, 2)));
+      break;
+    }
+    case Kinded::Kind::ElementAddInstKind: {
+      auto *N = llvm::cast<ElementAddInst>(&I);
+      const int32_t ops[3] = {S(N->getDest()), S(N->getLHS()), S(N->getRHS())};
+      const int64_t ia[4] = {(int64_t)N->getDest()->size(), N->getDest()->getType()->getOffset(), N->getLHS()->getType()->getOffset(),
+                             N->getRHS()->getType()->getOffset()};
+      const float fa[3] = {N->getLHS()->getType()->getScale(), N->getRHS()->getType()->getScale(), N->getDest()->getType()->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_ADD, ops, 3, ia, 4, fa, 3)));
+      break;
+    }
+    case Kinded::Kind::QuantizeInstKind:
+    case Kinded::Kind::DequantizeInstKind: {
+      const bool q = I.getKind() == Kinded::Kind::QuantizeInstKind;
+      const Value *dst = I.getOperand(0).first, *src = I.getOperand(1).first;
+      const Type *qt = q ? dst->getType() : src->getType();
+      const int32_t ops[2] = {S(dst), S(src)};
+      const int64_t ia[2] = {(int64_t)dst->size(), qt->getOffset()};
+      const float fa[1] = {qt->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, q ? GLOWB200_INSTR_QUANTIZE : GLOWB200_INSTR_DEQUANTIZE, ops, 2, ia, 2, fa, 1)));
+      break;
+    }
+    case Kinded::Kind::CopyInstKind: {
+      auto *N = llvm::cast<CopyInst>(&I);
+      const int32_t ops[2] = {S(N->getDest()), S(N->getSrc())};
+      const int64_t ia[1] = {(int64_t)N->getDest()->getType()->getSizeInBytes()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_COPY, ops, 2, ia, 1, nullptr, 0)));
+      break;
+    }
+    // MaxPool / AvgPool / Transpose / Relu (as max with the quantized zero) follow the same pattern
+    // with GLOWB200_INSTR_MAXPOOL / _AVGPOOL / _TRANSPOSE / _MAXSPLAT.
+    default:
+      return MAKE_ERR(ErrorValue::ErrorCode::COMPILE_UNSUPPORTED_NODE_AFTER_OPTIMIZE,
+                      "B200: instruction " + std::string(I.getKindName()) + " is not supported");
+    }
+  }
+  return fromRuntime(glowb200_function_compile(fn_));
+}
+
+Error B200Function::execute(ExecutionContext *context) {
+  // Bind every placeholder the function uses to its host tensor; the device manager copies in,
+  // runs, and copies back (a shorter tensor is a partial tensor).
+  std::vector<std::string> names;
+  std::vector<const char *> cnames;
+  std::vector<void *> bufs;
+  std::vector<size_t> bytes;
+  for (auto &PH : context->getPlaceholderBindings()->pairs()) {
+    if (!getRuntimeBundle().isPlaceholder(PH.first->getName())) continue;  // helper name illustrative
+    names.push_back(PH.first->getName().str());
+    bufs.push_back(PH.second.getUnsafePtr());
+    bytes.push_back(PH.second.getUnpaddedSizeInBytes());
+  }
+  for (auto &n : names) cnames.push_back(n.c_str());
+  return fromRuntime(glowb200_device_manager_run_function(dm_, F_->getGraph()->getName().str().c_str(), cnames.data(), bufs.data(),
+                                                          bytes.data(), (int)names.size()));
+}
