@@ -786,7 +786,7 @@ def main():
             "config": workload_config(T),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
-                         "kernel": "slws_gather_kernel (+ slws_segments_from_lengths_kernel, timed together)",
+                         "kernel": "slws_gather_select_kernel<8,0,0,long,1,4> (+ slws_segments_from_lengths_kernel, timed together)",
                          "launch_us": launch_us, "algorithmic_bytes_per_launch": moved / args.steps},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d // e2e_steps,
                     "d2h_bytes_per_step": d2h // e2e_steps, "steps": e2e_steps,

@@ -17,7 +17,7 @@ class SlwsJob(C.Structure):
     """struct glowb200_slws_job"""
     _fields_ = [("data", _vp), ("weights", _vp), ("indices", _vp), ("lengths", _vp), ("dest", _vp),
                 ("rows", _i64), ("num_indices", _i64), ("dest_stride", _i64), ("segments", _i64),
-                ("dests", _vp), ("bags_per_dest", _i64)]
+                ("dests", _vp), ("bags_per_dest", _i64), ("row_begin", _i64), ("global_rows", _i64)]
 
 
 # name -> (restype, argtypes); also the list the symbol-export test walks.
@@ -29,9 +29,18 @@ SIGNATURES = {
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp, _vp]),
     "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched": (
         _int, [_vp, _i64, _i64, _int, _int, _i64, _i64, _int, _int, _vp, _sz, _vp, _vp]),
+    "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_row_sharded": (
+        _int, [_vp, _i64, _i64, _int, _int, _i64, _i64, _vp, _sz, _vp, _vp]),
     "glowb200_slws_static_scratch_max_segments": (_i64, []),
     "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_static_scratch": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _vp]),
+    "glowb200_sparse_lengths_weighted_sum_f32": (
+        _int, [_vp, _vp, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _sz, _vp, _vp]),
+    "glowb200_rowwise_quantized_sparse_lengths_weighted_sum_f32": (
+        _int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _sz, _vp, _vp]),
+    "glowb200_fused_rowwise_quantize": (_int, [_vp, _i64, _i64, _int, _vp, _i64]),
+    "glowb200_fused_rowwise_quantize_device": (_int, [_vp, _i64, _i64, _int, _vp, _i64, _vp]),
+    "glowb200_sum_partials": (_int, [_vp, _i64, _i64, _i64, _vp, _int, _vp]),
     "glowb200_quantize_scale_offset_32to8": (None, [_f32, _vp, _vp, _vp]),
     "glowb200_rowwise_requant_params": (_int, [_vp, _i64, _f32, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "glowb200_choose_quantization_params": (None, [_f32, _f32, _int, _int, _vp, _vp]),

@@ -33,6 +33,14 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Bag boundaries of one lengths array (defined beside the gather-pool kernels):
+// seg_begin[i] = min(sum(max(lengths[0..i), 0)), num_indices) for i in [0, segments]; the array
+// must hold glowb200_slws_workspace_bytes(segments, 1) bytes.  Raises the status bits of
+// negative lengths and of lengths that overrun num_indices.
+int launch_segments_from_lengths(const int32_t *lengths, int64_t segments, int64_t num_indices,
+                                 void *workspace, size_t workspace_bytes, int32_t *status,
+                                 cudaStream_t stream);
+
 // ---- integer requantisation (device side) ----------------------------------------------
 // libjit_scale<int32,int32> (lib/LLVMIRCodeGen/libjit/libjit_defs.h:158-173): arithmetic
 // shifts, 32-bit wrapping multiply/add, rounding term only when post > 0, offset added last.

@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <climits>
 #include <cmath>
+#include <cstring>
 #include <limits>
 
 #include "common.cuh"
@@ -179,6 +180,52 @@ extern "C" int glowb200_channelwise_conv_prepare(const float *filter, const floa
     bias_q[c] = (int32_t)(v < qmin32 ? qmin32 : (v > qmax32 ? qmax32 : v));
     bias_scales[c] = b_scale;
     bias_offsets[c] = b_off;
+  }
+  return GLOWB200_OK;
+}
+
+// tensorFusedRowwiseQuantization<T> (include/glow/Quantization/Base/Base.h:598-678) on the host:
+// per row scale = (max - min) / range in double (1 when max - min < 1e-10), offset = min;
+// values quantized with the fp32 scale/offset (quantizeWithFloatOffset, :361-379), which the
+// fp16 kinds then store rounded to fp16 (Tensor.h:1585-1607).  The fp16 rounding is cuda_fp16's
+// host-side round-to-nearest-even conversion.
+extern "C" int glowb200_fused_rowwise_quantize(const float *in, int64_t rows, int64_t cols, int kind, uint8_t *out,
+                                               int64_t out_line_size) {
+  GLOWB200_REQUIRE(kind >= 0 && kind <= 3, "unknown fused kind %d", kind);
+  GLOWB200_REQUIRE(rows >= 0 && cols > 0, "rows / cols out of range");
+  const bool four = kind >= 2, so16 = (kind & 1) != 0;
+  GLOWB200_REQUIRE(!four || cols % 2 == 0, "4-bit fused quantization needs an even number of columns");
+  const int64_t want = (four ? cols / 2 : cols) + (so16 ? 4 : 8);
+  GLOWB200_REQUIRE(out_line_size == want, "out_line_size must be %lld for %lld columns of kind %d", (long long)want,
+                   (long long)cols, kind);
+  if (rows == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(in != nullptr && out != nullptr, "NULL tensor pointer");
+  const float range = four ? 15.0f : 255.0f;
+  for (int64_t i = 0; i < rows; i++) {
+    const float *src = in + i * cols;
+    uint8_t *dst = out + i * out_line_size;
+    const auto mm = std::minmax_element(src, src + cols);
+    const float mn = *mm.first, mx = *mm.second;
+    const float scale = ((mx - mn) < 1e-10f) ? 1.0f : (float)(((double)mx - (double)mn) / range);
+    const float offset = mn;
+    if (!four) {
+      for (int64_t j = 0; j < cols; j++) dst[j] = (uint8_t)(uint16_t)std::round((src[j] - offset) / scale);
+    } else {
+      for (int64_t b = 0; b < cols / 2; b++) {
+        const int lo = std::max(0, std::min((int)std::round((src[2 * b] - offset) / scale), 15));
+        const int hi = std::max(0, std::min((int)std::round((src[2 * b + 1] - offset) / scale), 15));
+        dst[b] = (uint8_t)(lo | (hi << 4));
+      }
+    }
+    uint8_t *tail = dst + out_line_size;
+    if (so16) {
+      const __half s = __float2half_rn(scale), o = __float2half_rn(offset);
+      memcpy(tail - 4, &s, 2);
+      memcpy(tail - 2, &o, 2);
+    } else {
+      memcpy(tail - 8, &scale, 4);
+      memcpy(tail - 4, &offset, 4);
+    }
   }
   return GLOWB200_OK;
 }

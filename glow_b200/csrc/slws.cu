@@ -44,6 +44,8 @@ struct SlwsLaunch {
   // favours (a word the segments kernel leaves behind the table's boundaries);
   // 0: the group-per-bag mapping for every table.
   int32_t select;
+  // 1: the tables are row-range shards (row_begin / global_rows of the descriptors are honoured)
+  int32_t sharded;
 };
 
 __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
@@ -283,7 +285,7 @@ __device__ __forceinline__ float load_weight(const void *weights, int64_t i) {
 // ------------------------------------------------------------------------------------------
 // Gather-pool.  grid = (ceil(max_segments / bags_per_block), num_jobs).
 // ------------------------------------------------------------------------------------------
-template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int kUnroll>
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int kUnroll, bool SHARD = false>
 __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
   using RL = RowLoad<BITS, SO16>;
   const int job_id = blockIdx.y;
@@ -327,10 +329,12 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
     r = -1;
     w = 0.0f;
     if (pos < end) {
-      const int64_t v = (int64_t)indices[pos];
+      const int64_t g = (int64_t)indices[pos];
+      int64_t v = g;
+      if constexpr (SHARD) v -= jp->row_begin;
       w = load_weight<OUT16>(weights, pos);
-      if (v < 0 || v >= rows) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;
-      else r = (int32_t)v;
+      if (v >= 0 && v < rows) r = (int32_t)v;
+      else if (!SHARD || g < 0 || g >= jp->global_rows) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;  // else: another shard's row
     }
   };
   int32_t r_mine, r_next;
@@ -460,7 +464,7 @@ __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN
 // group-per-bag kernel above.
 // grid = (ceil(ceil(max_segments / bags_per_warp) / 8), num_jobs), 8 warps per block.
 // ------------------------------------------------------------------------------------------
-template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int kUnroll>
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int kUnroll, bool SHARD = false>
 __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_per_warp) {
   using RL = RowLoad<BITS, SO16>;
   constexpr int V = 8 * P;  // sums a lane carries
@@ -500,15 +504,18 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
   reset();
 
   // Row numbers travel as int32 (tables have fewer than 2^31 rows); -1 marks an index outside
-  // [0, rows), which is reported only if a bag really uses it (indices past the last bag are
-  // never looked at).
+  // the table, which is reported only if a bag really uses it (indices past the last bag are
+  // never looked at); -3 marks a row of another shard of a row-range sharded table.
   auto fetch = [&](int at, int32_t &r, float &w) {
     r = -1;
     w = 0.0f;
     if (at < avail) {
-      const int64_t v = (int64_t)indices[at];
+      const int64_t g = (int64_t)indices[at];
+      int64_t v = g;
+      if constexpr (SHARD) v -= jp->row_begin;
       w = load_weight<OUT16>(weights, at);
       if (v >= 0 && v < rows) r = (int32_t)v;
+      else if (SHARD && g >= 0 && g < jp->global_rows) r = -3;
     }
   };
 
@@ -621,7 +628,7 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
         r[u] = __shfl_sync(0xffffffffu, r_mine, src & 31);
         w[u] = __shfl_sync(0xffffffffu, w_mine, src & 31);
         if (src >= n) r[u] = -2;                       // no row for this slot in this step
-        else if (r[u] < 0) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;
+        else if (r[u] == -1) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;
       }
 #pragma unroll
       for (int u = 0; u < kUnroll; u++) {
@@ -667,13 +674,13 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
 // One launch, two thread-to-bag mappings: every table is pooled by the mapping its bag-length
 // profile favours (the word the segments kernel leaves behind the table's boundaries).
 // grid.x covers the larger of the two mappings' block counts; surplus blocks leave at once.
-template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U>
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false>
 __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS)
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
   const bool skewed = p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
-  if (skewed) gather_warp_body<BITS, SO16, OUT16, IdxT, P, U>(p, bags_per_warp);
-  else gather_group_body<BITS, SO16, OUT16, false, IdxT, P, U>(p);
+  if (skewed) gather_warp_body<BITS, SO16, OUT16, IdxT, P, U, SHARD>(p, bags_per_warp);
+  else gather_group_body<BITS, SO16, OUT16, false, IdxT, P, U, SHARD>(p);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -699,9 +706,14 @@ __global__ void __launch_bounds__(256) slws_gather_any_kernel(const __grid_const
   for (int tile = 0; tile < D; tile += 128) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int64_t j = begin; j < end; j++) {
-      const int64_t r = idx64 ? reinterpret_cast<const int64_t *>(jp->indices)[j]
-                              : (int64_t) reinterpret_cast<const int32_t *>(jp->indices)[j];
-      if (r < 0 || r >= jp->rows) { flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE; continue; }
+      int64_t r = idx64 ? reinterpret_cast<const int64_t *>(jp->indices)[j]
+                        : (int64_t) reinterpret_cast<const int32_t *>(jp->indices)[j];
+      const int64_t g = r;
+      if (p.sharded) r -= jp->row_begin;
+      if (r < 0 || r >= jp->rows) {
+        if (!p.sharded || g < 0 || g >= jp->global_rows) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;
+        continue;
+      }
       const float w = out16 ? __half2float(reinterpret_cast<const __half *>(jp->weights)[j])
                             : reinterpret_cast<const float *>(jp->weights)[j];
       const uint8_t *row = data + r * in_line;
@@ -777,6 +789,12 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
       const int64_t warps = (max_segments + bpw - 1) / bpw;
       const unsigned wblocks = (unsigned)((warps + 7) / 8);
       dim3 sgrid(wblocks > grid.x ? wblocks : grid.x, grid.y);
+      if constexpr (!OUT16) {  // shards give fp32 partial sums (checked by the entry point)
+        if (L.sharded) {
+          slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, true><<<sgrid, kGatherThreads, 0, s>>>(L, bpw);
+          return cudaGetLastError();
+        }
+      }
       slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U><<<sgrid, kGatherThreads, 0, s>>>(L, bpw);
       return cudaGetLastError();
     }
@@ -874,6 +892,28 @@ bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p
 }  // namespace
 }  // namespace glowb200
 
+int glowb200::launch_segments_from_lengths(const int32_t *lengths, int64_t segments, int64_t num_indices,
+                                           void *workspace, size_t workspace_bytes, int32_t *status,
+                                           cudaStream_t stream) {
+  GLOWB200_REQUIRE(segments >= 0 && segments < (1ll << 31) && num_indices >= 0, "segments / num_indices out of range");
+  if (segments == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
+  const size_t need = seg_stride_elems(segments) * 8;
+  if (workspace == nullptr || workspace_bytes < need)
+    return set_error(GLOWB200_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  GLOWB200_REQUIRE(aligned_to(workspace, 8), "workspace must be 8-byte aligned");
+  SlwsLaunch L{};
+  L.single.lengths = lengths;
+  L.single.segments = segments;
+  L.single.num_indices = num_indices;
+  L.seg_begin = reinterpret_cast<int64_t *>(workspace);
+  L.seg_stride = (int64_t)seg_stride_elems(segments);
+  L.status = status;
+  slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, stream>>>(L);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
 using namespace glowb200;
 
 extern "C" size_t glowb200_slws_workspace_bytes(int64_t max_segments, int64_t num_jobs) {
@@ -881,10 +921,10 @@ extern "C" size_t glowb200_slws_workspace_bytes(int64_t max_segments, int64_t nu
   return seg_stride_elems(max_segments) * 8 * (size_t)num_jobs;
 }
 
-extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched(
-    const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_segments, int kind, int indices_are_int64,
-    int64_t in_line_size, int64_t out_line_size, int out_is_fp16, int use_fp16_accumulation, void *workspace,
-    size_t workspace_bytes, int32_t *status, glowb200_stream_t stream) {
+namespace {
+int run_batched(const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_segments, int kind, int indices_are_int64,
+                int64_t in_line_size, int64_t out_line_size, int out_is_fp16, int use_fp16_accumulation,
+                void *workspace, size_t workspace_bytes, int32_t *status, glowb200_stream_t stream, bool sharded) {
   GLOWB200_REQUIRE(num_jobs >= 0 && num_jobs <= 65535, "num_jobs must be in [0, 65535]");
   GLOWB200_REQUIRE(max_segments >= 0 && max_segments < (1ll << 31), "max_segments out of range");
   if (num_jobs == 0 || max_segments == 0) return GLOWB200_OK;
@@ -909,10 +949,28 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batc
   GatherConfig g{kind, indices_are_int64 ? 1 : 0, out_is_fp16 ? 1 : 0,
                  (use_fp16_accumulation && out_is_fp16 && (kind & 1)) ? 1 : 0};
   L.select = (P != 0 && !g.acc16) ? 1 : 0;
+  L.sharded = sharded ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   slws_segments_from_lengths_kernel<<<(unsigned)num_jobs, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return run_gather(L, g, P, max_segments, num_jobs, s);
+}
+}  // namespace
+
+extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched(
+    const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_segments, int kind, int indices_are_int64,
+    int64_t in_line_size, int64_t out_line_size, int out_is_fp16, int use_fp16_accumulation, void *workspace,
+    size_t workspace_bytes, int32_t *status, glowb200_stream_t stream) {
+  return run_batched(jobs, num_jobs, max_segments, kind, indices_are_int64, in_line_size, out_line_size, out_is_fp16,
+                     use_fp16_accumulation, workspace, workspace_bytes, status, stream, false);
+}
+
+extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_row_sharded(
+    const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_segments, int kind, int indices_are_int64,
+    int64_t in_line_size, int64_t out_line_size, void *workspace, size_t workspace_bytes, int32_t *status,
+    glowb200_stream_t stream) {
+  return run_batched(jobs, num_jobs, max_segments, kind, indices_are_int64, in_line_size, out_line_size, 0, 0,
+                     workspace, workspace_bytes, status, stream, true);
 }
 
 namespace {

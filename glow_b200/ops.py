@@ -152,6 +152,90 @@ FC_FUSE_RELU = 4
 ASYMMETRIC, SYMMETRIC, SYMMETRIC_WITH_UNSIGNED, SYMMETRIC_WITH_POWER2_SCALE = 0, 1, 2, 3
 
 
+def sparse_lengths_weighted_sum(data, weights, indices, lengths, *, out=None, status=None, workspace=None,
+                                num_indices=None):
+    """SparseLengthsWeightedSum over an fp32 table [rows, D]; weights=None is SparseLengthsSum."""
+    _cuda(data, "data", (torch.float32,))
+    _cuda(indices, "indices", (torch.int32, torch.int64))
+    _cuda(lengths, "lengths", (torch.int32,))
+    if weights is not None:
+        _cuda(weights, "weights", (torch.float32,))
+    rows, line = data.shape
+    segments = lengths.shape[0]
+    if out is None:
+        out = torch.empty((segments, line), dtype=torch.float32, device=data.device)
+    n = indices.shape[0] if num_indices is None else int(num_indices)
+    ws = _workspace(workspace, slws_workspace_bytes(segments, 1), data.device)
+    check(_lib.lib().glowb200_sparse_lengths_weighted_sum_f32(
+        _p(out), _p(data), rows, _p(weights), _p(indices), int(indices.dtype == torch.int64), _p(lengths), segments, n,
+        line, _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
+def sparse_lengths_sum(data, indices, lengths, **kw):
+    return sparse_lengths_weighted_sum(data, None, indices, lengths, **kw)
+
+
+def rowwise_quantized_sparse_lengths_weighted_sum(data, scales, offsets, weights, indices, lengths, *, out=None,
+                                                  status=None, workspace=None, num_indices=None):
+    """RowwiseQuantizedSparseLengthsWeightedSum: uint8 table [rows, D] with fp32 scales/offsets [rows]."""
+    _cuda(data, "data", (torch.uint8,))
+    _cuda(scales, "scales", (torch.float32,))
+    _cuda(offsets, "offsets", (torch.float32,))
+    _cuda(weights, "weights", (torch.float32,))
+    _cuda(indices, "indices", (torch.int32, torch.int64))
+    _cuda(lengths, "lengths", (torch.int32,))
+    rows, line = data.shape
+    segments = lengths.shape[0]
+    if out is None:
+        out = torch.empty((segments, line), dtype=torch.float32, device=data.device)
+    n = indices.shape[0] if num_indices is None else int(num_indices)
+    ws = _workspace(workspace, slws_workspace_bytes(segments, 1), data.device)
+    check(_lib.lib().glowb200_rowwise_quantized_sparse_lengths_weighted_sum_f32(
+        _p(out), _p(data), _p(scales), _p(offsets), rows, _p(weights), _p(indices),
+        int(indices.dtype == torch.int64), _p(lengths), segments, n, line, _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
+def fused_row_bytes(cols, kind):
+    """Row width in bytes of a fused-rowwise table of `cols` columns."""
+    return (cols // 2 if kind in (UINT4_FUSED, UINT4_FUSED_FP16) else cols) + (4 if kind in (UINT8_FUSED_FP16, UINT4_FUSED_FP16) else 8)
+
+
+def fused_rowwise_quantize_host(table, kind=UINT8_FUSED):
+    """Host fused-rowwise quantisation of a float32 numpy matrix -> uint8 numpy [rows, row bytes]."""
+    import numpy as np
+    table = np.ascontiguousarray(table, np.float32)
+    rows, cols = table.shape
+    out = np.empty((rows, fused_row_bytes(cols, kind)), np.uint8)
+    check(_lib.lib().glowb200_fused_rowwise_quantize(C.c_void_p(table.ctypes.data), rows, cols, int(kind),
+                                                     C.c_void_p(out.ctypes.data), out.shape[1]))
+    return out
+
+
+def fused_rowwise_quantize(table, kind=UINT8_FUSED, out=None):
+    """Fused-rowwise quantisation of a CUDA float32 matrix on the device."""
+    _cuda(table, "table", (torch.float32,))
+    rows, cols = table.shape
+    if out is None:
+        out = torch.empty((rows, fused_row_bytes(cols, kind)), dtype=torch.uint8, device=table.device)
+    check(_lib.lib().glowb200_fused_rowwise_quantize_device(_p(table), rows, cols, int(kind), _p(out), out.shape[1],
+                                                            _stream()))
+    return out
+
+
+def sum_partials(partials, out_dtype=torch.float32, out=None):
+    """Sum of fp32 partial results [num, ...] over the first axis, cast once to out_dtype."""
+    _cuda(partials, "partials", (torch.float32,))
+    num = partials.shape[0]
+    n = partials[0].numel()
+    if out is None:
+        out = torch.empty(partials.shape[1:], dtype=out_dtype, device=partials.device)
+    check(_lib.lib().glowb200_sum_partials(_p(partials), num, partials.stride(0), n, _p(out),
+                                           int(out.dtype == torch.float16), _stream()))
+    return out
+
+
 def choose_quantization_params(mn, mx, schema=ASYMMETRIC, bits=8):
     """(scale, offset) for a float range -- host computation (chooseQuantizationParams)."""
     sc, off = C.c_float(), C.c_int32()
@@ -482,22 +566,27 @@ class SlwsBatch:
         self.fp16_acc = use_fp16_accumulation
         self.device = torch.device(device)
         self.jobs_dev = None
+        self.sharded = False
         self.num_jobs = 0
         self.max_segments = 0
         self.workspace = None
         self._keep = None
 
-    def bind(self, tables, weights, indices, lengths, dests, dest_stride=None, scatter=None, bags_per_dest=0):
+    def bind(self, tables, weights, indices, lengths, dests, dest_stride=None, scatter=None, bags_per_dest=0,
+             row_ranges=None):
         """scatter: optional list (one entry per table) of lists of destination base addresses
         (ints, possibly in other GPUs' memory); bag b of table i then goes to row
-        b % bags_per_dest of scatter[i][b // bags_per_dest]."""
+        b % bags_per_dest of scatter[i][b // bags_per_dest].
+        row_ranges: optional list (one entry per table) of (row_begin, global_rows) for tables
+        that are row-range shards: indices then number the whole table, and rows of other shards
+        are skipped, so the result is this shard's partial sum."""
         n = len(tables)
         arr = (SlwsJob * n)()
         odt = result_dtype(self.kind)
         self.max_segments = 0
         for i in range(n):
             _cuda(tables[i], "table", (torch.uint8,))
-            _cuda(weights[i], "weights", (odt, torch.float16))
+            _cuda(weights[i], "weights", (odt, torch.float16, torch.float32))
             _cuda(indices[i], "indices", (self.index_dtype,))
             _cuda(lengths[i], "lengths", (torch.int32,))
             if tables[i].shape[1] != self.in_line:
@@ -509,7 +598,10 @@ class SlwsBatch:
             j.rows, j.num_indices = tables[i].shape[0], indices[i].shape[0]
             j.dest_stride = self.out_line if dest_stride is None else dest_stride
             j.segments = lengths[i].shape[0]
+            if row_ranges is not None:
+                j.row_begin, j.global_rows = int(row_ranges[i][0]), int(row_ranges[i][1])
             self.max_segments = max(self.max_segments, j.segments)
+        self.sharded = row_ranges is not None
         self._scatter_dev = None
         if scatter is not None:
             per = len(scatter[0])
@@ -529,6 +621,14 @@ class SlwsBatch:
         return self
 
     def run(self, status=None):
+        if self.sharded:
+            if self.out_fp16 or self.fp16_acc:
+                raise ValueError("row-range shards take fp32 weights and give fp32 partial sums")
+            check(_lib.lib().glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_row_sharded(
+                _p(self.jobs_dev), self.num_jobs, self.max_segments, self.kind,
+                int(self.index_dtype == torch.int64), self.in_line, self.out_line,
+                _p(self.workspace), self.workspace.numel(), _p(status), _stream()))
+            return
         check(_lib.lib().glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched(
             _p(self.jobs_dev), self.num_jobs, self.max_segments, self.kind,
             int(self.index_dtype == torch.int64), self.in_line, self.out_line, self.out_fp16, int(self.fp16_acc),

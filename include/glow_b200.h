@@ -85,6 +85,14 @@ typedef struct glowb200_slws_job {
    * glowb200_peer_buffer_*); the stores are ordinary peer stores. */
   void *const *dests;
   int64_t bags_per_dest;
+  /* Row-range sharding of one table over several GPUs: `data` holds the table's rows
+   * [row_begin, row_begin + rows) and the indices are numbers of the whole table, which has
+   * global_rows rows.  An index inside the whole table but outside this shard is skipped
+   * silently (another shard pools it); the result is this shard's partial sum.  Honoured by
+   * glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_row_sharded only; every other
+   * entry point takes the table as whole. */
+  int64_t row_begin;
+  int64_t global_rows;
 } glowb200_slws_job;
 
 /* Bytes of scratch the gather-pool entry points need for `num_jobs` tables of at most
@@ -121,6 +129,18 @@ int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched(
     int use_fp16_accumulation, void *workspace, size_t workspace_bytes, int32_t *status,
     glowb200_stream_t stream);
 
+/* The batched operator over row-range SHARDS of tables (row_begin / global_rows of every
+ * descriptor are honoured): each launch gives the fp32 partial sums of the rows this GPU holds;
+ * weights and dest are fp32 for every kind (an fp16 weight widened is the same number), and
+ * glowb200_sum_partials adds the shards' results and rounds once to the result type.  No
+ * reference counterpart: Glow does not split an embedding table by rows
+ * (ParallelTransformKind splits SparseLengthsSum by batch only,
+ * lib/Optimizer/GraphOptimizer/GraphOptimizer.cpp:7263-7300). */
+int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_row_sharded(
+    const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_segments, int kind,
+    int indices_are_int64, int64_t in_line_size, int64_t out_line_size, void *workspace,
+    size_t workspace_bytes, int32_t *status, glowb200_stream_t stream);
+
 /* EmbeddingBagByteRowwiseOffsets (and its 4-bit form).
  * Replaces libjit_embedding_bag_byte_rowwise_offsets_f (libjit.cpp:2454-2481) and
  * fwdEmbeddingBagByteRowwiseOffsetsImpl (InterpreterNodes.cpp:5896-5986).  `offsets` has the
@@ -133,6 +153,51 @@ int glowb200_embedding_bag_byte_rowwise_offsets(
     int64_t in_line_size, int64_t out_line_size, int has_end_offset, int out_is_fp16,
     int use_fp16_accumulation, void *workspace, size_t workspace_bytes, int32_t *status,
     glowb200_stream_t stream);
+
+/* SparseLengthsWeightedSum / SparseLengthsSum over an fp32 table.
+ * Replaces libjit_sparse_lengths_weighted_sum_f_u / _f_i32 and libjit_sparse_lengths_sum_f_u /
+ * _f_i32 (lib/LLVMIRCodeGen/libjit/libjit.cpp:2318-2346, generic bodies :1164-1198).
+ *   dest [segments, line_size] fp32; data [rows, line_size] fp32; weights fp32 [num_indices],
+ *   or NULL for the unweighted sum (every row added as it is).
+ * Each result element is accumulated in index order with separate multiply and add, so the
+ * result is bit-identical to the reference kernel built without fast-math.
+ * workspace: glowb200_slws_workspace_bytes(segments, 1). */
+int glowb200_sparse_lengths_weighted_sum_f32(float *dest, const float *data, int64_t rows,
+                                             const float *weights, const void *indices,
+                                             int indices_are_int64, const int32_t *lengths,
+                                             int64_t segments, int64_t num_indices,
+                                             int64_t line_size, void *workspace,
+                                             size_t workspace_bytes, int32_t *status,
+                                             glowb200_stream_t stream);
+
+/* RowwiseQuantizedSparseLengthsWeightedSum: uint8 table with per-row fp32 scale and offset in
+ * separate vectors, value = scale[row] * q + offset[row].
+ * Replaces libjit_rowwise_quantized_sparse_lengths_weighted_sum_f_u / _f_i32
+ * (libjit.cpp:2400-2414, generic body :1232-1251).  Same ordering guarantee as above. */
+int glowb200_rowwise_quantized_sparse_lengths_weighted_sum_f32(
+    float *dest, const uint8_t *data, const float *scales, const float *offsets, int64_t rows,
+    const float *weights, const void *indices, int indices_are_int64, const int32_t *lengths,
+    int64_t segments, int64_t num_indices, int64_t line_size, void *workspace,
+    size_t workspace_bytes, int32_t *status, glowb200_stream_t stream);
+
+/* tensorFusedRowwiseQuantization<T> (include/glow/Quantization/Base/Base.h:598-678): an fp32
+ * [rows, cols] table into the fused-rowwise format of `kind`,
+ * out_line_size = cols (+8 | +4) for the 8-bit kinds, cols/2 (+8 | +4) for the 4-bit kinds.
+ * The first is a HOST function (host pointers); the _device form is the same arithmetic as a
+ * kernel over device pointers, for tables that are produced or already resident on the GPU.
+ * Both give the bytes the reference gives. */
+int glowb200_fused_rowwise_quantize(const float *in, int64_t rows, int64_t cols, int kind,
+                                    uint8_t *out, int64_t out_line_size);
+int glowb200_fused_rowwise_quantize_device(const float *in, int64_t rows, int64_t cols, int kind,
+                                           uint8_t *out, int64_t out_line_size,
+                                           glowb200_stream_t stream);
+
+/* Sum of the fp32 partial results of a row-range sharded table (one slab per shard,
+ * `partial_stride` floats apart, added in slab order) into dest [n], fp32 or fp16 -- the single
+ * rounding to fp16 that keeps the sharded operator on fp32 accumulation.  No reference
+ * counterpart: Glow does not split an embedding table by rows. */
+int glowb200_sum_partials(const float *partials, int64_t num_partials, int64_t partial_stride,
+                          int64_t n, void *dest, int dest_is_fp16, glowb200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Int8 dense layers (tensor cores: tcgen05 kind::i8, int32 accumulation, Glow's integer

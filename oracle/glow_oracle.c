@@ -333,6 +333,38 @@ ORC_API void orc_sparse_lengths_weighted_sum_f32(float *dest, const float *data,
     }
 }
 
+/* libjit_sparse_lengths_sum_generic: libjit.cpp:1164-1180 (fp32 table, rows added as they are). */
+ORC_API void orc_sparse_lengths_sum_f32(float *dest, const float *data, const void *indices, int idx64,
+                                        const int32_t *lengths, int64_t segments, int64_t line) {
+  memset(dest, 0, (size_t)(segments * line) * sizeof(float));
+  int64_t cur = 0;
+  for (int64_t i = 0; i < segments; i++)
+    for (int32_t j = 0; j < lengths[i]; j++, cur++) {
+      const int64_t r = load_index(indices, idx64, cur);
+      for (int64_t k = 0; k < line; k++) dest[i * line + k] += data[r * line + k];
+    }
+}
+
+/* libjit_rowwise_quantized_sparse_lengths_weighted_sum_generic: libjit.cpp:1232-1251
+ * (uint8 table, per-row fp32 scale and offset in separate vectors). */
+ORC_API void orc_rowwise_quantized_slws_f32(float *dest, const uint8_t *data, const float *scales,
+                                            const float *offsets, const float *weights,
+                                            const void *indices, int idx64, const int32_t *lengths,
+                                            int64_t segments, int64_t line) {
+  memset(dest, 0, (size_t)(segments * line) * sizeof(float));
+  int64_t cur = 0;
+  for (int64_t i = 0; i < segments; i++)
+    for (int32_t j = 0; j < lengths[i]; j++, cur++) {
+      const float w = weights[cur];
+      const int64_t r = load_index(indices, idx64, cur);
+      const float scale = scales[r], offset = offsets[r];
+      for (int64_t k = 0; k < line; k++) {
+        const float f = scale * (float)data[r * line + k] + offset;
+        dest[i * line + k] += w * f;
+      }
+    }
+}
+
 /* ------------------------------------------------------------------------------------ */
 /* Dense int8 layers.  Integer arithmetic wraps mod 2^32 like the reference's int32.      */
 /* Callers that want more host threads split the batch rows over them (oracle.py).       */

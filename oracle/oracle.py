@@ -222,6 +222,28 @@ def sparse_lengths_weighted_sum_f32(data, weights, indices, lengths):
     return dest
 
 
+def sparse_lengths_sum_f32(data, indices, lengths):
+    data = _c(data, np.float32)
+    indices, idx64 = _idx(indices)
+    lengths = _c(lengths, np.int32)
+    dest = np.empty((lengths.shape[0], data.shape[1]), np.float32)
+    lib().orc_sparse_lengths_sum_f32(_ptr(dest), _ptr(data), _ptr(indices), C.c_int(idx64), _ptr(lengths),
+                                     _i64(lengths.shape[0]), _i64(data.shape[1]))
+    return dest
+
+
+def rowwise_quantized_slws_f32(data, scales, offsets, weights, indices, lengths):
+    data = _c(data, np.uint8)
+    scales, offsets, weights = _c(scales, np.float32), _c(offsets, np.float32), _c(weights, np.float32)
+    indices, idx64 = _idx(indices)
+    lengths = _c(lengths, np.int32)
+    dest = np.empty((lengths.shape[0], data.shape[1]), np.float32)
+    lib().orc_rowwise_quantized_slws_f32(_ptr(dest), _ptr(data), _ptr(scales), _ptr(offsets), _ptr(weights),
+                                         _ptr(indices), C.c_int(idx64), _ptr(lengths), _i64(lengths.shape[0]),
+                                         _i64(data.shape[1]))
+    return dest
+
+
 # ---------------------------------------------------------------------------- dense int8
 def _split_rows(M, threads):
     threads = max(1, min(threads, M))
@@ -418,6 +440,35 @@ class LibjitRef:
               else self.l.libjit_fused_rowwise_quantized_sparse_lengths_weighted_sum_f_i32)
         fn(_ptr(dest), _ptr(data), _ptr(weights), _ptr(indices), _ptr(lengths), C.c_uint64(lengths.shape[0]),
            C.c_uint64(in_line), C.c_uint64(out_line))
+        return dest
+
+    def sparse_lengths_weighted_sum(self, data, weights, indices, lengths):
+        """libjit_sparse_lengths_weighted_sum_f_u / _f_i32; weights None -> libjit_sparse_lengths_sum_*."""
+        data = _c(data, np.float32)
+        indices, idx64 = _idx(indices)
+        lengths = _c(lengths, np.int32)
+        dest = np.empty((lengths.shape[0], data.shape[1]), np.float32)
+        sfx = "f_u" if idx64 else "f_i32"
+        if weights is None:
+            getattr(self.l, "libjit_sparse_lengths_sum_" + sfx)(
+                _ptr(dest), _ptr(data), _ptr(indices), _ptr(lengths), C.c_uint64(lengths.shape[0]),
+                C.c_uint64(data.shape[1]))
+        else:
+            weights = _c(weights, np.float32)
+            getattr(self.l, "libjit_sparse_lengths_weighted_sum_" + sfx)(
+                _ptr(dest), _ptr(data), _ptr(weights), _ptr(indices), _ptr(lengths), C.c_uint64(lengths.shape[0]),
+                C.c_uint64(data.shape[1]))
+        return dest
+
+    def rowwise_quantized_slws(self, data, scales, offsets, weights, indices, lengths):
+        data = _c(data, np.uint8)
+        scales, offsets, weights = _c(scales, np.float32), _c(offsets, np.float32), _c(weights, np.float32)
+        indices, idx64 = _idx(indices)
+        lengths = _c(lengths, np.int32)
+        dest = np.empty((lengths.shape[0], data.shape[1]), np.float32)
+        fn = getattr(self.l, "libjit_rowwise_quantized_sparse_lengths_weighted_sum_" + ("f_u" if idx64 else "f_i32"))
+        fn(_ptr(dest), _ptr(data), _ptr(scales), _ptr(offsets), _ptr(weights), _ptr(indices), _ptr(lengths),
+           C.c_uint64(lengths.shape[0]), C.c_uint64(data.shape[1]))
         return dest
 
     def embedding_bag_byte_rowwise_offsets(self, data, weights, indices, offsets, has_end_offset):

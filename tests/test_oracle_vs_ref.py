@@ -176,3 +176,26 @@ def test_pools_and_elementwise(oracle, libjit_ref):
     f = (rng.standard_normal(600) * 3).astype(np.float32)
     f[:8] = [0.5 * 0.05, 1.5 * 0.05, 2.5 * 0.05, -0.5 * 0.05, -1.5 * 0.05, 1000.0, -1000.0, 0.0]
     np.testing.assert_array_equal(oracle.element_quantize_i8(f, 0.05, 3), libjit_ref.element_quantize_i8(f, 0.05, 3))
+
+
+@pytest.mark.parametrize("d", [1, 5, 64, 130])
+@pytest.mark.parametrize("idt", [np.int64, np.int32])
+def test_plain_and_rowwise_quantized_slws(oracle, libjit_ref, d, idt):
+    rng = np.random.default_rng(300 + d)
+    rows, B = 4000, 80
+    lengths = np.clip(rng.poisson(10, B), 0, 40).astype(np.int32)
+    lengths[5] = 0
+    n = int(lengths.sum())
+    idx = rng.integers(0, rows, n).astype(idt)
+    w = rng.uniform(-1, 1, n).astype(np.float32)
+    table = rng.normal(0, 1, (rows, d)).astype(np.float32)
+    for weights in (w, None):
+        want = libjit_ref.sparse_lengths_weighted_sum(table, weights, idx, lengths)
+        got = (oracle.sparse_lengths_weighted_sum_f32(table, w, idx, lengths) if weights is not None
+               else oracle.sparse_lengths_sum_f32(table, idx, lengths))
+        np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+    q = rng.integers(0, 256, (rows, d), dtype=np.uint8)
+    sc, off = rng.uniform(0.001, 0.01, rows).astype(np.float32), rng.uniform(-1, 1, rows).astype(np.float32)
+    want = libjit_ref.rowwise_quantized_slws(q, sc, off, w, idx, lengths)
+    got = oracle.rowwise_quantized_slws_f32(q, sc, off, w, idx, lengths)
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))

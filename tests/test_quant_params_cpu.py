@@ -73,3 +73,26 @@ def test_tensor_rowwise_quantize_matches_oracle(ops, oracle):
     q, sc, off = ops.tensor_rowwise_quantize_i8(w, 0)
     deq = sc[:, None] * (q.astype(np.float32) - off[:, None])
     assert np.max(np.abs(deq - w) / np.maximum(np.abs(w).max(1, keepdims=True), 1e-6)) < 0.01
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+def test_fused_rowwise_quantize_host_matches_oracle(ops, oracle, kind):
+    rng = np.random.default_rng(50 + kind)
+    for cols in (2, 10, 64, 130):
+        table = rng.normal(0, 2, (300, cols)).astype(np.float32)
+        table[3] = -1.5            # constant row -> scale 1
+        table[4, 1] = 3e4          # wide range
+        table[7] *= 1e-12          # range below the equality threshold
+        got = ops.fused_rowwise_quantize_host(table, kind)
+        np.testing.assert_array_equal(got, oracle.fused_rowwise_quantize(table, kind))
+
+
+def test_fused_rowwise_quantize_host_known_answer(ops):
+    """The fused 4-bit case of the reference's quantisation unit test: a row 0..15 maps to itself."""
+    row = np.arange(16, dtype=np.float32)[None, :]
+    got = ops.fused_rowwise_quantize_host(row, 3)
+    assert got.shape == (1, 12)
+    assert got[0, :8].tolist() == [(2 * i) | ((2 * i + 1) << 4) for i in range(8)]
+    assert got[0, 8:].view(np.float16).tolist() == [1.0, 0.0]
+    with pytest.raises(Exception):
+        ops.fused_rowwise_quantize_host(np.zeros((2, 3), np.float32), 2)   # odd column count, 4-bit
