@@ -50,6 +50,8 @@ def parse():
                          "slws4: the 4-bit fused-rowwise sweep point selected by --dim")
     ap.add_argument("--dim", type=int, default=128, help="slws4: embedding width (32, 64, 128 or 256)")
     ap.add_argument("--table-gb", type=float, default=40.0, help="slws4: total table bytes per GPU, in GB")
+    ap.add_argument("--shard", default="tables", choices=["tables", "rows"],
+                    help="slws4 at N > 1: every rank owns whole tables (no exchange), or row ranges of every table")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary int8 FC measurement")
     return ap.parse_args()
 
@@ -617,6 +619,120 @@ def run_slws4_line(args):
         dist.destroy_process_group()
 
 
+def run_slws4_sharded_line(args):
+    """--workload slws4 --shard rows: the 4-bit sweep with every table cut into row ranges over the
+    GPUs (rank g holds rows [g*R/G, (g+1)*R/G) of EVERY table).  There are G times as many tables
+    as in the unsharded sweep, so each GPU still holds --table-gb of rows; every rank sees the
+    whole request, pools its rows into fp32 partial sums that it stores straight into the slab of
+    the rank owning the bag, and each rank adds the G slabs and rounds once to fp16.  The value
+    is the LOGICAL operator's algorithmic bytes per second (whole tables, whole request)."""
+    import torch
+    import torch.distributed as dist
+    from glow_b200 import ops, sharded
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    D, ROWS4, B = args.dim, 10_000_000, 8192
+    line_bytes = D // 2 + 4
+    T = max(1, int(args.table_gb * 1e9 / (ROWS4 * line_bytes))) * world      # logical tables
+    lo, hi = sharded.row_range(rank, world, ROWS4)
+    g = torch.Generator(device=dev).manual_seed(0x610B200 + 77 * rank + D)
+    shards = []
+    for k in range(T):
+        t = torch.randint(0, 256, (hi - lo, line_bytes), dtype=torch.uint8, device=dev, generator=g)
+        so = torch.stack([torch.empty(hi - lo, device=dev).uniform_(0.001, 0.01, generator=g),
+                          torch.empty(hi - lo, device=dev).uniform_(-1, 1, generator=g)], dim=1).to(torch.float16)
+        t[:, D // 2:] = so.view(torch.uint8).view(hi - lo, 4)
+        shards.append(t)
+    del so
+    R = 2
+    reqs = []
+    for r in range(R):                                   # the same request on every rank
+        rng = np.random.Generator(np.random.PCG64(4242 + r))
+        lengths = rng.poisson(64, (T, B)).astype(np.int32)
+        starts = np.concatenate([[0], np.cumsum(lengths.sum(1))]).astype(np.int64)
+        total = int(starts[-1])
+        gi = torch.Generator(device=dev).manual_seed(99 + r)
+        indices = torch.randint(0, ROWS4, (total,), device=dev, generator=gi)
+        weights = torch.rand(total, device=dev, generator=gi).to(torch.float16).float()   # fp16 values, widened
+        reqs.append((torch.from_numpy(lengths).to(dev), indices, weights, starts))
+    nbytes = [int(rq[3][-1]) * (line_bytes + 8 + 2) + T * B * (4 + 2 * D) for rq in reqs]
+    results = {}
+    clocks = None
+    for form in (["local"] if world == 1 else ["fused", "nccl"]):
+        op = sharded.RowShardedSLWS(ops.UINT4_FUSED_FP16, shards, [ROWS4] * T, B, rank, world, exchange=form)
+        if form == "fused":
+            op.connect_peers()
+        pair = []
+        for r, (lengths_d, indices_d, weights_d, starts) in enumerate(reqs):
+            pair.append(op.prepare([weights_d[starts[k]:starts[k + 1]] for k in range(T)],
+                                   [indices_d[starts[k]:starts[k + 1]] for k in range(T)],
+                                   [lengths_d[k] for k in range(T)], slab=r if form == "fused" else 0))
+
+        def step(i):
+            # request i % 2 is bound to receive slab i % 2, the slab the fused exchange uses at step i
+            if form == "fused":
+                return op.run(pair)
+            return op.run([pair[i % R]])
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        sampler = ClockSampler(local)
+        sampler.start()
+        op.step = 0
+        for i in range(2 * ((max(3, args.warmup) + 1) // 2)):
+            step(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        t_end = time.time() + 1.0
+        while world == 1 and len(sampler.lines) < 8 and time.time() < t_end:
+            step(0)
+            torch.cuda.synchronize()
+        clocks = sampler.stop()
+        assert int(op.status.item()) == 0
+        tm = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        moved = sum(nbytes[i % R] for i in range(args.steps))
+        results[form] = {"gbps": moved / (float(tm[0]) * 1e-3) / 1e9, "ms_per_step": float(tm[0]) / args.steps}
+        op.release()
+        del op, pair
+        torch.cuda.empty_cache()
+    if rank == 0:
+        peak, src = measured_peak_hbm()
+        best = max(results.values(), key=lambda r: r["gbps"])
+        per_gpu = best["gbps"] / world
+        print(json.dumps({
+            "metric": "frwq_slws_4bit_row_sharded_hbm_gbps", "value": best["gbps"], "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": best["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u4 -> f32 partial sums -> f16", "data": "synthetic",
+            "by_exchange": results,
+            "config": {"workload": "4-bit fused-rowwise SLWS, tables row-range sharded over the GPUs: %d tables x "
+                                   "10,000,000 rows x %d cols (%d B rows, %.1f GB per GPU), 8192 bags/table, lengths "
+                                   "Poisson(64), uniform int64 indices, fp16 weights and result; every rank reads the "
+                                   "whole request" % (T, D, line_bytes, T * (hi - lo) * line_bytes / 1e9),
+                       "dim": D, "tables": T, "l2_policy": "tables far larger than L2, uniform indices"},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                         "peak_source": src, "traffic": None,
+                         "kernel": "slws_gather_select_kernel<4,1,0,long,P,U,sharded> + sum_partials_kernel"},
+            "gpu_launches": 3 * args.steps, "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def workload_config(T):
     return {"workload": "FRWQ-SLWS uint8 fused rows (config 1 law): %d tables x 1,000,000 rows x 64 cols "
                         "(72 B rows), 1024 bags/table, lengths clamp(Poisson(32),1,128), int64 indices, fp32 "
@@ -632,7 +748,7 @@ def main():
     if args.workload == "int8_fc":
         return run_int8_fc_line(args)
     if args.workload == "slws4":
-        return run_slws4_line(args)
+        return run_slws4_sharded_line(args) if args.shard == "rows" else run_slws4_line(args)
 
     import torch
     import torch.distributed as dist
