@@ -50,6 +50,8 @@ def parse():
                          "slws4: the 4-bit fused-rowwise sweep point selected by --dim")
     ap.add_argument("--dim", type=int, default=128, help="slws4: embedding width (32, 64, 128 or 256)")
     ap.add_argument("--table-gb", type=float, default=40.0, help="slws4: total table bytes per GPU, in GB")
+    ap.add_argument("--row-bytes", type=int, default=0,
+                    help="slws: store the tables with rows padded to this many bytes (0: the dense 72-byte rows)")
     ap.add_argument("--shard", default="tables", choices=["tables", "rows"],
                     help="slws4 at N > 1: every rank owns whole tables (no exchange), or row ranges of every table")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary int8 FC measurement")
@@ -773,8 +775,11 @@ def main():
         of = torch.empty(ROWS, device=dev).uniform_(-1, 1, generator=g)
         t[:, DIM:DIM + 4] = sc.view(torch.uint8).view(ROWS, 4)
         t[:, DIM + 4:] = of.view(torch.uint8).view(ROWS, 4)
+        if args.row_bytes:
+            t = ops.pad_fused_rows(t, ops.UINT8_FUSED, args.row_bytes)
         tables.append(t)
     del sc, of
+    line = args.row_bytes or IN_LINE
 
     # ---- requests: pinned host copies (for the end-to-end leg) and device copies
     host, devr = [], []
@@ -790,7 +795,7 @@ def main():
     status = ops.new_status(dev)
 
     def batch_for(lengths_d, indices_d, weights_d, starts):
-        b = ops.SlwsBatch(ops.UINT8_FUSED, IN_LINE, torch.int64, device=dev)
+        b = ops.SlwsBatch(ops.UINT8_FUSED, line, torch.int64, device=dev, out_line=DIM)
         b.bind(tables, [weights_d[starts[k]:starts[k + 1]] for k in range(T)],
                [indices_d[starts[k]:starts[k + 1]] for k in range(T)], [lengths_d[k] for k in range(T)],
                [out[k] for k in range(T)])
@@ -879,6 +884,8 @@ def main():
         cpu_threads = os.cpu_count() or 1
         S = min(T, max(cpu_threads, 16))
         sample_tables = [tables[k].cpu().numpy() for k in range(S)]
+        if args.row_bytes:  # the CPU reference pools its own layout: dense 72-byte rows
+            sample_tables = [np.ascontiguousarray(np.concatenate([t[:, :DIM], t[:, -8:]], axis=1)) for t in sample_tables]
     dlrm_extra = None
     if not args.no_extras:
         # second headline of the same benchmark definition: the recommendation model, all ranks

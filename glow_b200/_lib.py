@@ -40,6 +40,7 @@ SIGNATURES = {
         _int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, _sz, _vp, _vp]),
     "glowb200_fused_rowwise_quantize": (_int, [_vp, _i64, _i64, _int, _vp, _i64]),
     "glowb200_fused_rowwise_quantize_device": (_int, [_vp, _i64, _i64, _int, _vp, _i64, _vp]),
+    "glowb200_fused_rows_pad": (_int, [_vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "glowb200_sum_partials": (_int, [_vp, _i64, _i64, _i64, _vp, _int, _vp]),
     "glowb200_quantize_scale_offset_32to8": (None, [_f32, _vp, _vp, _vp]),
     "glowb200_rowwise_requant_params": (_int, [_vp, _i64, _f32, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -844,8 +844,12 @@ int plan(int kind, int64_t in_line, int64_t out_line, bool pointers_aligned, int
   GLOWB200_REQUIRE(kind >= 0 && kind <= 3, "unknown fused table kind %d", kind);
   GLOWB200_REQUIRE(out_line >= 0 && in_line > 0 && in_line < (1 << 30), "bad line sizes");
   GLOWB200_REQUIRE(kind < 2 || (out_line % 2) == 0, "4-bit rows need an even column count");
-  GLOWB200_REQUIRE(in_line == payload_bytes(kind, out_line) + tail_bytes(kind),
-                   "in_line_size %lld does not match %lld columns of kind %d", (long long)in_line,
+  // Rows may be wider than payload + scale/offset: the columns come first, the scale/offset
+  // pair is the LAST bytes of the row (where the reference kernel looks for it,
+  // libjit.cpp:1263-1264), and whatever lies between is padding -- a table stored with its rows
+  // padded to a memory-friendly stride is pooled as it is.
+  GLOWB200_REQUIRE(in_line >= payload_bytes(kind, out_line) + tail_bytes(kind),
+                   "in_line_size %lld is too small for %lld columns of kind %d", (long long)in_line,
                    (long long)out_line, kind);
   P = 0;
   lpr_log2 = 0;

@@ -64,6 +64,23 @@ __global__ void __launch_bounds__(256) fused_rowwise_quantize_kernel(const float
   }
 }
 
+// One warp per row: payload bytes, zero padding, the scale/offset pair at the end.
+__global__ void __launch_bounds__(256) fused_rows_pad_kernel(const uint8_t *__restrict__ src, int64_t rows, int in_line,
+                                                              int tail, uint8_t *__restrict__ dst, int padded) {
+  const int lane = threadIdx.x & 31;
+  const int payload = in_line - tail;
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
+    const uint8_t *s = src + row * in_line;
+    uint8_t *d = dst + row * padded;
+    for (int j = lane; j < padded; j += 32) {
+      uint8_t v = 0;
+      if (j < payload) v = s[j];
+      else if (j >= padded - tail) v = s[payload + (j - (padded - tail))];
+      d[j] = v;
+    }
+  }
+}
+
 // dest[i] = cast(partials[0][i] + partials[1][i] + ...), added in slab order.
 template <bool OUT16>
 __global__ void __launch_bounds__(256) sum_partials_kernel(const float *__restrict__ partials, int num, int64_t stride,
@@ -110,6 +127,20 @@ extern "C" int glowb200_fused_rowwise_quantize_device(const float *in, int64_t r
   const int64_t want_blocks = (rows + 7) / 8, cap = (int64_t)sm_count() * 16;
   fused_rowwise_quantize_kernel<<<(unsigned)(want_blocks < cap ? want_blocks : cap), 256, 0,
                                   reinterpret_cast<cudaStream_t>(stream)>>>(in, rows, cols, kind, out, out_line_size);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_fused_rows_pad(const uint8_t *src, int64_t rows, int64_t in_line_size, int64_t tail_bytes,
+                                        uint8_t *dst, int64_t padded_line_size, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(tail_bytes == 4 || tail_bytes == 8, "tail_bytes must be 4 or 8");
+  GLOWB200_REQUIRE(rows >= 0 && in_line_size > tail_bytes && padded_line_size >= in_line_size && padded_line_size < (1 << 30),
+                   "rows / line sizes out of range");
+  if (rows == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(src != nullptr && dst != nullptr, "NULL tensor pointer");
+  const int64_t want_blocks = (rows + 7) / 8, cap = (int64_t)sm_count() * 32;
+  fused_rows_pad_kernel<<<(unsigned)(want_blocks < cap ? want_blocks : cap), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      src, rows, (int)in_line_size, (int)tail_bytes, dst, (int)padded_line_size);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }

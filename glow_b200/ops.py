@@ -66,14 +66,16 @@ def _workspace(workspace, need, device):
 
 def fused_rowwise_quantized_sparse_lengths_weighted_sum(data, weights, indices, lengths, kind=UINT8_FUSED, *,
                                                         use_fp16_accumulation=False, out=None, status=None,
-                                                        workspace=None, num_indices=None):
+                                                        workspace=None, num_indices=None, out_line=None):
     """FusedRowwiseQuantizedSparseLengthsWeightedSum.  data: uint8 [rows, in_line] fused table;
-    weights: result dtype [n]; indices: int32/int64 [n]; lengths: int32 [segments]."""
+    weights: result dtype [n]; indices: int32/int64 [n]; lengths: int32 [segments].
+    out_line: columns of the result when the rows are padded (see pad_fused_rows); default: the
+    whole row is payload + scale/offset."""
     _cuda(data, "data", (torch.uint8,))
     _cuda(indices, "indices", (torch.int32, torch.int64))
     _cuda(lengths, "lengths", (torch.int32,))
     rows, in_line = data.shape
-    out_line = out_columns(in_line, kind)
+    out_line = out_columns(in_line, kind) if out_line is None else int(out_line)
     odt = result_dtype(kind) if out is None else out.dtype
     _cuda(weights, "weights", (odt,))
     segments = lengths.shape[0]
@@ -221,6 +223,20 @@ def fused_rowwise_quantize(table, kind=UINT8_FUSED, out=None):
         out = torch.empty((rows, fused_row_bytes(cols, kind)), dtype=torch.uint8, device=table.device)
     check(_lib.lib().glowb200_fused_rowwise_quantize_device(_p(table), rows, cols, int(kind), _p(out), out.shape[1],
                                                             _stream()))
+    return out
+
+
+def pad_fused_rows(table, kind, row_bytes, out=None):
+    """A fused-rowwise CUDA table [rows, in_line] with every row padded to `row_bytes`: payload
+    first, zeros, scale/offset as the last bytes.  The gather-pool operators take the padded table
+    with out_line = the original column count and give bit-identical results; rows that fill whole
+    128-byte lines cost one DRAM access each instead of one and a half."""
+    _cuda(table, "table", (torch.uint8,))
+    rows, in_line = table.shape
+    tail = 4 if kind & 1 else 8
+    if out is None:
+        out = torch.empty((rows, row_bytes), dtype=torch.uint8, device=table.device)
+    check(_lib.lib().glowb200_fused_rows_pad(_p(table), rows, in_line, tail, _p(out), row_bytes, _stream()))
     return out
 
 
@@ -559,9 +575,10 @@ class SlwsBatch:
     wider [segments, tables * D] buffer so the tables' results land concatenated.
     """
 
-    def __init__(self, kind, in_line, index_dtype=torch.int64, use_fp16_accumulation=False, device="cuda"):
+    def __init__(self, kind, in_line, index_dtype=torch.int64, use_fp16_accumulation=False, device="cuda",
+                 out_line=None):
         self.kind, self.in_line = kind, in_line
-        self.out_line = out_columns(in_line, kind)
+        self.out_line = out_columns(in_line, kind) if out_line is None else int(out_line)
         self.index_dtype = index_dtype
         self.fp16_acc = use_fp16_accumulation
         self.device = torch.device(device)

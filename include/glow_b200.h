@@ -109,6 +109,9 @@ size_t glowb200_slws_workspace_bytes(int64_t max_segments, int64_t num_jobs);
  *   data [rows, in_line_size] bytes of `kind`; lengths int32 [segments];
  *   use_fp16_accumulation as the node flag (honoured only for an fp16 result on an
  *   fp16-scale table, like the reference's dispatcher).
+ *   in_line_size may exceed the bytes out_line_size columns and the scale/offset pair need:
+ *   the pair is the last bytes of the row, the bytes between are padding
+ *   (see glowb200_fused_rows_pad).
  * The unweighted FusedRowwiseQuantizedSparseLengthsSum is this call with weights of 1
  * (lib/Optimizer/Lower/Lower.cpp:1590-1606). */
 int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
@@ -191,6 +194,20 @@ int glowb200_fused_rowwise_quantize(const float *in, int64_t rows, int64_t cols,
 int glowb200_fused_rowwise_quantize_device(const float *in, int64_t rows, int64_t cols, int kind,
                                            uint8_t *out, int64_t out_line_size,
                                            glowb200_stream_t stream);
+
+/* Re-lays a fused-rowwise table [rows, in_line_size] out with rows of `padded_line_size` bytes:
+ * the payload (in_line_size - tail_bytes bytes) first, zero padding, then the scale/offset pair
+ * (tail_bytes = 8 for the fp32 kinds, 4 for the fp16 kinds) as the last bytes of the row.  The
+ * gather-pool entry points accept such a table with in_line_size = padded_line_size and the
+ * original out_line_size -- the reference kernel addresses a row the same way
+ * (lib/LLVMIRCodeGen/libjit/libjit.cpp:1263-1270: scale/offset at the end of inLineSize bytes,
+ * outLineSize columns from its start) -- and give bit-identical results.  Why: a 72-byte row at
+ * an 8-byte aligned address straddles 64-byte DRAM atoms and, half of the time, a 128-byte
+ * line; a row that fills one aligned 128-byte line is one access.  Costs HBM capacity, so it is
+ * the loader's choice (src and dst are device pointers and must not overlap). */
+int glowb200_fused_rows_pad(const uint8_t *src, int64_t rows, int64_t in_line_size,
+                            int64_t tail_bytes, uint8_t *dst, int64_t padded_line_size,
+                            glowb200_stream_t stream);
 
 /* Sum of the fp32 partial results of a row-range sharded table (one slab per shard,
  * `partial_stride` floats apart, added in slab order) into dest [n], fp32 or fp16 -- the single

@@ -255,3 +255,32 @@ def test_row_sharded_operator(oracle, kind, d, world):
         # fp16 result = one rounding of the fp32-accurate sum
         exact = pooled_f64(tables[i], kind, w32, idx, ln)
         assert np.all(np.abs(got[i] - exact) <= 1e-5 * scale + np.abs(exact) * 2.0 ** -11 + 1e-30)
+
+
+@pytest.mark.parametrize("kind,d,row_bytes", [(0, 64, 128), (0, 64, 80), (0, 128, 256), (3, 128, 128), (2, 64, 64),
+                                              (1, 64, 96), (0, 20, 32)])
+def test_padded_rows_pool_identically(oracle, kind, d, row_bytes):
+    """A table re-laid with padded rows (payload, zeros, scale/offset last) gives the bits the dense
+    table gives, and what the oracle gives when it is told the padded line size."""
+    rng = np.random.default_rng(70 + d + kind)
+    rows, B = 9000, 300
+    table = make_table(31 + kind, rows, d, kind)
+    lengths, idx, w = _request(rng, rows, B, 20, np.int64)
+    wd = np.float16 if kind & 1 else np.float32
+    dt, dw, di, dl = t(table), t(np.abs(w).astype(wd)), t(idx), t(lengths)
+    padded = ops.pad_fused_rows(dt, kind, row_bytes)
+    assert padded.shape == (rows, row_bytes)
+    host = padded.cpu().numpy()
+    tail = 4 if kind & 1 else 8
+    np.testing.assert_array_equal(host[:, :table.shape[1] - tail], table[:, :-tail])
+    np.testing.assert_array_equal(host[:, -tail:], table[:, -tail:])
+    assert not host[:, table.shape[1] - tail:-tail].any()
+    st = ops.new_status(DEV)
+    dense = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(dt, dw, di, dl, kind, status=st)
+    wide = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(padded, dw, di, dl, kind, status=st, out_line=d)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and torch.equal(dense, wide)
+    if kind == 0:   # the CPU kernel's own addressing of a wide row: columns first, scale/offset last
+        want = oracle.frwq_slws_u8_f32(host, np.abs(w), idx, lengths, out_line=d)
+        scale = pooled_f64(table, kind, np.abs(w), idx, lengths, full_scale=True)
+        assert close(wide.cpu().numpy().astype(np.float64), want.astype(np.float64), scale, 1e-5)
