@@ -62,9 +62,6 @@ __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
 #ifndef GLOWB200_SLWS_MIN_BLOCKS
 #define GLOWB200_SLWS_MIN_BLOCKS 3
 #endif
-#ifndef GLOWB200_SLWS_PREFETCH
-#define GLOWB200_SLWS_PREFETCH 1
-#endif
 __device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
   uint32_t v;
 #if GLOWB200_SLWS_L1_NOALLOC
@@ -181,6 +178,19 @@ __global__ void __launch_bounds__(256) slws_segments_from_offsets_kernel(const _
   raise(p.status, flags);
 }
 
+// 1: pool uint8 rows with the packed two-lane fp32 instructions of sm_100
+#ifndef GLOWB200_SLWS_F32X2
+#define GLOWB200_SLWS_F32X2 1
+#endif
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
 // ------------------------------------------------------------------------------------------
 // Row decoding
 // ------------------------------------------------------------------------------------------
@@ -260,8 +270,26 @@ struct RowLoad {
   }
   __device__ static __forceinline__ void pool(const Chunk &c, float a_eff, float *acc) {
     if constexpr (BITS == 8) {
+#if GLOWB200_SLWS_F32X2
+      // two columns per instruction: sm_100's packed fp32 add and fma (the same roundings as
+      // the scalar forms, element by element)
+      const uint64_t a2 = pack2(a_eff, a_eff), magic2 = pack2(-8388608.0f, -8388608.0f);
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        const uint32_t w = i < 4 ? c.lo : c.hi;
+        const uint32_t m0 = __byte_perm(w, 0x4B000000u, 0x7440 + (i & 3));  // {byte i, 0, 0, 0x4B} = 2^23 + q
+        const uint32_t m1 = __byte_perm(w, 0x4B000000u, 0x7440 + ((i + 1) & 3));
+        uint64_t q2, s2;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(q2) : "r"(m0), "r"(m1));
+        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(q2) : "l"(q2), "l"(magic2));
+        s2 = pack2(acc[i], acc[i + 1]);
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(s2) : "l"(a2), "l"(q2), "l"(s2));
+        unpack2(s2, acc[i], acc[i + 1]);
+      }
+#else
 #pragma unroll
       for (int i = 0; i < 8; i++) acc[i] = fmaf(a_eff, column(c, i), acc[i]);
+#endif
     } else {
       const uint32_t lo = (c.lo & 0x0F0F0F0Fu) | 0x80808080u;         // columns 0,2,4,6 as bytes 0x8q
       const uint32_t hi = ((c.lo >> 4) & 0x0F0F0F0Fu) | 0x80808080u;  // columns 1,3,5,7
@@ -324,26 +352,34 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
 
   // Row numbers travel as int32 inside the group (-1 = skip): tables have fewer than 2^31 rows
   // (checked on the host).  The next `lpr` indices are requested before the current ones are
-  // consumed, so the index fetch overlaps the row fetches.
-  auto fetch = [&](int64_t pos, int32_t &r, float &w) {
-    r = -1;
+  // consumed, so the index fetch overlaps the row fetches.  Asking for an index (`request`) and
+  // looking at it (`resolve`: range check, narrowing) are kept apart: nothing may depend on the
+  // loaded value -- not even a branch -- until the rows of the chunk before it are on their
+  // way, or the warp would sit out the index latency first and the row latency after it.
+  auto request = [&](int64_t pos, IdxT &v, float &w) {
+    v = 0;
     w = 0.0f;
     if (pos < end) {
-      const int64_t g = (int64_t)indices[pos];
-      int64_t v = g;
-      if constexpr (SHARD) v -= jp->row_begin;
+      v = indices[pos];
       w = load_weight<OUT16>(weights, pos);
-      if (v >= 0 && v < rows) r = (int32_t)v;
-      else if (!SHARD || g < 0 || g >= jp->global_rows) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;  // else: another shard's row
     }
   };
-  int32_t r_mine, r_next;
+  auto resolve = [&](int64_t pos, IdxT raw) -> int32_t {
+    if (pos >= end) return -1;
+    const int64_t g = (int64_t)raw;
+    int64_t v = g;
+    if constexpr (SHARD) v -= jp->row_begin;
+    if (v >= 0 && v < rows) return (int32_t)v;
+    if (!SHARD || g < 0 || g >= jp->global_rows) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;  // else: another shard's row
+    return -1;
+  };
+  int32_t r_mine;
+  IdxT v_next;
   float w_mine, w_next;
-  fetch(begin + gl, r_mine, w_mine);
+  request(begin + gl, v_next, w_mine);
+  r_mine = resolve(begin + gl, v_next);
   for (int64_t base = begin; base < end; base += lpr) {
-#if GLOWB200_SLWS_PREFETCH
-    fetch(base + lpr + gl, r_next, w_next);
-#endif
+    request(base + lpr + gl, v_next, w_next);
     const int n = (int)((end - base) < (int64_t)lpr ? (end - base) : (int64_t)lpr);
     for (int t = 0; t < n; t += kUnroll) {
       int32_t r[kUnroll];
@@ -395,12 +431,8 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
         }
       }
     }
-#if GLOWB200_SLWS_PREFETCH
-    r_mine = r_next;
+    r_mine = resolve(base + lpr + gl, v_next);
     w_mine = w_next;
-#else
-    fetch(base + lpr + gl, r_mine, w_mine);
-#endif
   }
 
   // Every bag writes its row, empty bags write zeros (the reference zero-fills dest first).
@@ -770,6 +802,7 @@ struct GatherConfig {
 #ifndef GLOWB200_SLWS_WARP_PER_BAG
 #define GLOWB200_SLWS_WARP_PER_BAG 1
 #endif
+
 
 // (P, U) pairs that exist: chunks per lane P, rows requested per lane before the first is
 // consumed U.  Wide rows spread over 8 or more lanes leave few bags (or row slots) per warp,
