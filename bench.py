@@ -31,6 +31,7 @@ sys.path.insert(0, ROOT)
 
 ROWS, DIM, BATCH = 1_000_000, 64, 1024
 IN_LINE = DIM + 8
+NCU_DRAM_BYTES_PER_ROW = 203.7  # 72-byte rows, uint8 gather kernel (see profiles/)
 METRIC = "frwq_slws_hbm_gbps"
 UNIT = "GB/s"
 
@@ -932,6 +933,7 @@ def main():
 
     if rank == 0:
         peak, peak_src = measured_peak_hbm()
+        rows_per_launch = float(np.mean([int(host[r][3][T]) for r in range(R)]))
         launch_us = float(np.mean(step_ms)) * 1e3
         achieved = (moved / args.steps) / (np.mean(step_ms) * 1e-3) / 1e9
         line = {
@@ -940,8 +942,12 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(T),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
-                         "kernel": "slws_gather_select_kernel<8,0,0,long,1,4> (+ slws_segments_from_lengths_kernel, timed together)",
+                         "frac": achieved / peak, "peak_source": peak_src,
+                         # DRAM bytes per launch: bytes per gathered row measured by ncu on a 32-table
+                         # launch (dram__bytes_read.sum + dram__bytes_write.sum over its rows; traffic is
+                         # proportional to rows) x the rows of this launch
+                         "traffic": (None if args.row_bytes else NCU_DRAM_BYTES_PER_ROW * rows_per_launch),
+                         "kernel": "slws_gather_select_kernel<8,0,0,long,2,4> (+ slws_segments_from_lengths_kernel, timed together)",
                          "launch_us": launch_us, "algorithmic_bytes_per_launch": moved / args.steps},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d // e2e_steps,
                     "d2h_bytes_per_step": d2h // e2e_steps, "steps": e2e_steps,
