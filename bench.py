@@ -53,8 +53,10 @@ def parse():
     ap.add_argument("--table-gb", type=float, default=40.0, help="slws4: total table bytes per GPU, in GB")
     ap.add_argument("--row-bytes", type=int, default=0,
                     help="slws: store the tables with rows padded to this many bytes (0: the dense 72-byte rows)")
-    ap.add_argument("--shard", default="tables", choices=["tables", "rows"],
-                    help="slws4 at N > 1: every rank owns whole tables (no exchange), or row ranges of every table")
+    ap.add_argument("--shard", default="tables", choices=["tables", "rows", "rows-routed"],
+                    help="slws4 at N > 1: every rank owns whole tables (no exchange); row ranges of every table, every "
+                         "rank filtering the whole request; or row ranges with the request routed to the owning rank "
+                         "beforehand (each rank is handed only the indices of its rows)")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary int8 FC measurement")
     return ap.parse_args()
 
@@ -653,7 +655,8 @@ def run_slws4_sharded_line(args):
         shards.append(t)
     del so
     R = 2
-    reqs = []
+    reqs, logical = [], []
+    routed = args.shard == "rows-routed"
     for r in range(R):                                   # the same request on every rank
         rng = np.random.Generator(np.random.PCG64(4242 + r))
         lengths = rng.poisson(64, (T, B)).astype(np.int32)
@@ -662,8 +665,20 @@ def run_slws4_sharded_line(args):
         gi = torch.Generator(device=dev).manual_seed(99 + r)
         indices = torch.randint(0, ROWS4, (total,), device=dev, generator=gi)
         weights = torch.rand(total, device=dev, generator=gi).to(torch.float16).float()   # fp16 values, widened
-        reqs.append((torch.from_numpy(lengths).to(dev), indices, weights, starts))
-    nbytes = [int(rq[3][-1]) * (line_bytes + 8 + 2) + T * B * (4 + 2 * D) for rq in reqs]
+        logical.append(total)
+        if routed:
+            # what a front end that routes every index to the GPU owning its row hands this rank:
+            # the entries of its rows (local row numbers) and their count per bag
+            keep = (indices >= lo) & (indices < hi)
+            bag_of = torch.repeat_interleave(torch.arange(T * B, device=dev), torch.from_numpy(lengths.reshape(-1)).to(dev).long())
+            sub_len = torch.bincount(bag_of[keep], minlength=T * B).to(torch.int32).view(T, B)
+            indices, weights = (indices[keep] - lo).contiguous(), weights[keep].contiguous()
+            starts = np.concatenate([[0], np.cumsum(sub_len.sum(1).cpu().numpy())]).astype(np.int64)
+            reqs.append((sub_len.contiguous(), indices, weights, starts))
+            del keep, bag_of
+        else:
+            reqs.append((torch.from_numpy(lengths).to(dev), indices, weights, starts))
+    nbytes = [n * (line_bytes + 8 + 2) + T * B * (4 + 2 * D) for n in logical]
     results = {}
     clocks = None
     for form in (["local"] if world == 1 else ["fused", "nccl"]):
@@ -674,7 +689,7 @@ def run_slws4_sharded_line(args):
         for r, (lengths_d, indices_d, weights_d, starts) in enumerate(reqs):
             pair.append(op.prepare([weights_d[starts[k]:starts[k + 1]] for k in range(T)],
                                    [indices_d[starts[k]:starts[k + 1]] for k in range(T)],
-                                   [lengths_d[k] for k in range(T)], slab=r if form == "fused" else 0))
+                                   [lengths_d[k] for k in range(T)], slab=r if form == "fused" else 0, routed=routed))
 
         def step(i):
             # request i % 2 is bound to receive slab i % 2, the slab the fused exchange uses at step i
@@ -725,8 +740,10 @@ def run_slws4_sharded_line(args):
             "by_exchange": results,
             "config": {"workload": "4-bit fused-rowwise SLWS, tables row-range sharded over the GPUs: %d tables x "
                                    "10,000,000 rows x %d cols (%d B rows, %.1f GB per GPU), 8192 bags/table, lengths "
-                                   "Poisson(64), uniform int64 indices, fp16 weights and result; every rank reads the "
-                                   "whole request" % (T, D, line_bytes, T * (hi - lo) * line_bytes / 1e9),
+                                   "Poisson(64), uniform int64 indices, fp16 weights and result; %s"
+                                   % (T, D, line_bytes, T * (hi - lo) * line_bytes / 1e9,
+                                      "each rank is handed the entries of its own rows" if routed
+                                      else "every rank reads the whole request"),
                        "dim": D, "tables": T, "l2_policy": "tables far larger than L2, uniform indices"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "peak_source": src, "traffic": None,
@@ -751,7 +768,7 @@ def main():
     if args.workload == "int8_fc":
         return run_int8_fc_line(args)
     if args.workload == "slws4":
-        return run_slws4_sharded_line(args) if args.shard == "rows" else run_slws4_line(args)
+        return run_slws4_sharded_line(args) if args.shard != "tables" else run_slws4_line(args)
 
     import torch
     import torch.distributed as dist

@@ -111,10 +111,12 @@ class RowShardedSLWS:
             for b in self.slab_buf:
                 b.release()
 
-    def prepare(self, weights, indices, lengths, slab=0):
+    def prepare(self, weights, indices, lengths, slab=0, routed=False):
         """Binds one request (lists over the tables; fp32 weights -- an fp16 weight widened is the
         same number -- int64/int32 indices of the WHOLE table, int32 lengths [batch]) to receive
-        slab `slab`."""
+        slab `slab`.  routed=True: the request was already cut down to this rank's rows by the
+        front end (`bucketize`: local row numbers, per-bag counts of this shard), so the kernel
+        has nothing to skip."""
         T, per, D = len(self.shards), self.per, self.D
         by_source = self.exchange in ("fused", "emulated")
         if by_source:
@@ -133,7 +135,7 @@ class RowShardedSLWS:
                 scatter.append([bases[h] + ((h * T + t) * per * D) * 4 for h in range(self.world)])
         b = ops.SlwsBatch(self.kind, self.in_line, indices[0].dtype, device=self.device)
         b.bind(self.shards, weights, indices, lengths, None, dest_stride=D, scatter=scatter, bags_per_dest=per,
-               row_ranges=self.row_ranges)
+               row_ranges=None if routed else self.row_ranges)
         return b
 
     def pool(self, bound):
