@@ -288,6 +288,36 @@ def int8_fc_measure(torch, ops, dev, steps, warmup, seed=0):
             "h2d": FC_M * FC_K, "d2h": FC_M * FC_N, "library_int8_gemm_tops": lib_tops, "ops": ops_per_step}
 
 
+def int8_fc_cpu_rate(seconds, threads):
+    """The reference's libjit_rowwise_quantized_fc_i8_i32 (fast-math build; the plain-C port when that
+    build is absent) on a slice of the batch rows of the same layer: 8 rows per host thread per call,
+    repeated for `seconds`.  The kernel's cost is linear in the rows, so TOP/s of the slice is
+    TOP/s of the layer.  -> (TOP/s, kind, sample description)."""
+    from oracle import oracle as orc
+    from glow_b200 import workloads
+    c = workloads.config2(M=FC_M, K=FC_K, N=FC_N)
+    pre = orc.rowwise_requant_params(c["w_scales"], c["in_scale"], c["bias_scale"], c["out_scale"])
+    if orc.ref_available("fast"):
+        fn, kind = orc.LibjitRef("fast").rowwise_quantized_fc_i8_i32, "reference"
+    else:
+        fn, kind = orc.rowwise_quantized_fc_i8_i32, "port"
+    rows = 8 * threads
+    x = np.ascontiguousarray(c["inp"][:rows])
+    call = lambda: fn(x, c["w"], c["bias"], c["w_offsets"], pre[:3], pre[3:], c["out_offset"], c["in_offset"],
+                      c["bias_offset"], threads=threads)
+    call()
+    n, t0 = 0, time.perf_counter()
+    while True:
+        call()
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds:
+            break
+    tops = n * 2.0 * rows * FC_N * FC_K / dt / 1e12
+    return tops, kind, "%d of %d batch rows per call (8 per thread, %d host threads), %d calls in %.1f s" % (
+        rows, FC_M, threads, n, dt)
+
+
 def fc_config():
     return {"workload": "RowwiseQuantizedFullyConnected int8: M=2048 K=4096 N=4096, activations U[-128,127] "
                         "(scale 0.05, offset 3), weights U[-127,127] with per-row scales U(0.001,0.02) and zero "
@@ -330,12 +360,18 @@ def run_int8_fc_line(args):
                 "vs_baseline": None, "dtype": "s8 x s8 -> s32", "data": "synthetic", "config": fc_config(),
                 "roofline": {"bound": "tensor", "achieved": r["tops"], "peak": peak, "unit": "TOP/s",
                              "frac": r["tops"] / peak, "peak_source": src, "nominal_dense_int8_tops": 4500.0,
-                             "library_int8_gemm_tops": r["library_int8_gemm_tops"], "traffic": None,
+                             "library_int8_gemm_tops": r["library_int8_gemm_tops"],
+                             # DRAM bytes per launch from the ncu capture in profiles/ (the 8 MB result stays in L2)
+                             "traffic": 25.4e6,
                              "kernel": "i8_gemm_requant_kernel<256,4>", "launch_us": r["ms"] * 1e3},
                 "e2e": {"value": world * r["ops"] / (e2e_ms * 1e-3) / 1e12, "unit": "TOP/s",
                         "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"], "steps": r["e2e_steps"],
                         "ms_per_step": e2e_ms},
                 "gpu_launches": args.steps, "clocks": clocks}
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            v, kind, sample = int8_fc_cpu_rate(min(args.cpu_seconds, 10.0), threads)
+            line["cpu_baseline"] = {"value": v, "unit": "TOP/s", "cores": threads, "kind": kind, "sample": sample}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
