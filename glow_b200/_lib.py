@@ -62,6 +62,7 @@ SIGNATURES = {
     "glowb200_conv2d_i8_i32": (
         _int, [_vp] * 10 + [_i64] + [_i32] * 10 + [_vp, _i32, _vp, _int, _vp, _sz, _vp, _vp]),
     "glowb200_element_add_i8": (_int, [_vp, _vp, _vp, _i64] + [_i32] * 9 + [_vp]),
+    "glowb200_element_add_maxsplat_i8": (_int, [_vp, _vp, _vp, _i64] + [_i32] * 10 + [_vp]),
     "glowb200_element_relu_i8": (_int, [_vp, _vp, _i64] + [_i32] * 5 + [_vp]),
     "glowb200_element_maxsplat_i8": (_int, [_vp, _vp, _i64, _i32, _vp]),
     "glowb200_element_rescale_i8": (_int, [_vp, _vp, _i64] + [_i32] * 5 + [_vp]),

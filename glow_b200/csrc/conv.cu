@@ -69,6 +69,60 @@ __global__ void __launch_bounds__(256) im2col_i8_kernel(const int8_t *__restrict
   }
 }
 
+// Any channel count, one block per output image row (n, oh): the KH input rows the image row
+// needs are staged in shared memory once (coalesced reads; rows outside the image are filled
+// with `pad`), then every thread assembles 16-byte pieces of the im2col rows from it -- walking
+// (kh, kw, c) with counters instead of dividing per byte -- and writes them whole.  For a 7 x 7
+// stride-2 stem over 3 channels this replaces 160 byte stores and 160 index decodes per output
+// pixel by 10 vector stores.  Needs KH * W * C bytes of shared memory (checked by the launcher).
+__global__ void __launch_bounds__(256) im2col_i8_rows_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ a,
+                                                              const __grid_constant__ ConvGeom g, int K, int Kpad, int8_t pad) {
+  extern __shared__ __align__(16) int8_t rows_smem[];
+  const int n = blockIdx.x / g.OH, oh = blockIdx.x - n * g.OH;
+  const int row_bytes = g.W * g.C;
+  for (int kh = 0; kh < g.KH; kh++) {
+    const int ih = oh * g.SH - g.PT + kh * g.DH;
+    int8_t *dst = rows_smem + kh * row_bytes;
+    if (ih < 0 || ih >= g.H) {
+      for (int j = threadIdx.x; j < row_bytes; j += blockDim.x) dst[j] = pad;
+    } else {
+      const int8_t *src = x + ((int64_t)n * g.H + ih) * row_bytes;
+      if (((reinterpret_cast<uintptr_t>(src) | (uintptr_t)row_bytes) & 15) == 0) {
+        for (int j = threadIdx.x * 16; j < row_bytes; j += blockDim.x * 16)
+          *reinterpret_cast<int4 *>(dst + j) = __ldg(reinterpret_cast<const int4 *>(src + j));
+      } else {
+        for (int j = threadIdx.x; j < row_bytes; j += blockDim.x) dst[j] = src[j];
+      }
+    }
+  }
+  __syncthreads();
+  const int chunks_per_row = Kpad >> 4;
+  const int total = g.OW * chunks_per_row;
+  int8_t *out = a + ((int64_t)n * g.OH + oh) * g.OW * Kpad;
+  for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+    const int ow = idx / chunks_per_row, ch = idx - ow * chunks_per_row;
+    int k = ch * 16;
+    int tap = k / g.C, c = k - tap * g.C;
+    int kh = tap / g.KW, kw = tap - kh * g.KW;
+    const int iw0 = ow * g.SW - g.PL;
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int b = 0; b < 16; b++, k++) {
+      int8_t v = 0;  // zero padding of K beyond the real taps
+      if (k < K) {
+        const int iw = iw0 + kw * g.DW;
+        v = (iw >= 0 && iw < g.W) ? rows_smem[kh * row_bytes + iw * g.C + c] : pad;
+        if (++c == g.C) {
+          c = 0;
+          if (++kw == g.KW) { kw = 0; kh++; }
+        }
+      }
+      w[b >> 2] |= (uint32_t)(uint8_t)v << (8 * (b & 3));
+    }
+    *reinterpret_cast<int4 *>(out + (int64_t)ow * Kpad + ch * 16) = make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]);
+  }
+}
+
 // [rows, K] -> [rows, Kpad], zero padded
 __global__ void __launch_bounds__(256) pad_rows_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int rows,
                                                            int K, int Kpad) {
@@ -94,7 +148,7 @@ __global__ void __launch_bounds__(256) conv2d_i8_direct_kernel(const int8_t *__r
     const int oh = (int)(r % g.OH), n = (int)(r / g.OH);
     const int grp = d / ocg;
     const ColQuant q = col_quant(p, d);
-    uint32_t sum = (uint32_t)scale32(p.bias[d] - (p.bias_offsets ? p.bias_offsets[d] : p.bias_offset), q.bias_pre,
+    uint32_t sum = (uint32_t)scale32(load_bias(p, d) - (p.bias_offsets ? p.bias_offsets[d] : p.bias_offset), q.bias_pre,
                                      q.bias_post, q.bias_scale, 0);
     for (int kh = 0; kh < g.KH; kh++)
       for (int kw = 0; kw < g.KW; kw++) {
@@ -179,6 +233,10 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
       const uint32_t b = (uint8_t)pad;
       im2col_i8_vec_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(
           in, abuf, g, pl.Kpad, (int)(b | (b << 8) | (b << 16) | (b << 24)));
+    } else if ((int64_t)g.KH * g.W * g.C <= 48 * 1024 && (int64_t)g.N * g.OH < (1ll << 31) &&
+               (reinterpret_cast<uintptr_t>(abuf) & 15) == 0) {
+      // the KH input rows of an output image row fit the default shared-memory window
+      im2col_i8_rows_kernel<<<(unsigned)(g.N * g.OH), 256, (size_t)g.KH * g.W * g.C, s>>>(in, abuf, g, pl.K, pl.Kpad, pad);
     } else {
       const int64_t blocks = (pl.M * pl.Kpad + 255) / 256;
       im2col_i8_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(in, abuf, g, pl.K, pl.Kpad, pad);
@@ -244,6 +302,7 @@ extern "C" int glowb200_channelwise_quantized_conv2d_i8_i32(
   p.status = status;
   p.a_offset = in_offset; p.out_offset = out_offset;
   p.act_type = act_type;
+  p.bias_is_i8 = (flags & GLOWB200_FC_BIAS_INT8) ? 1 : 0;
   if (act_type == 2) { p.act_args[0] = act_args[0]; p.act_args[1] = act_args[1]; }
   if (act_type == 5) { p.act_args[0] = act_args[0]; p.act_args[1] = act_args[1]; p.act_args[2] = act_args[2]; }
   return run_conv(p, in, filter, g, filter_row_sums, flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
@@ -273,6 +332,7 @@ extern "C" int glowb200_conv2d_i8_i32(
   p.u_bias_pre = bias_pre; p.u_bias_post = bias_post; p.u_bias_scale = bias_scale;
   p.u_out_pre = out_pre; p.u_out_post = out_post; p.u_out_scale = out_scale;
   p.act_type = act_type;
+  p.bias_is_i8 = (flags & GLOWB200_FC_BIAS_INT8) ? 1 : 0;
   if (act_type == 2) { p.act_args[0] = act_args[0]; p.act_args[1] = act_args[1]; }
   if (act_type == 5) { p.act_args[0] = act_args[0]; p.act_args[1] = act_args[1]; p.act_args[2] = act_args[2]; }
   if (filter_offset == 0) flags |= GLOWB200_FC_WEIGHT_OFFSETS_ZERO;

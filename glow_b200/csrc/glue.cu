@@ -27,6 +27,20 @@ __global__ void __launch_bounds__(kThreads) add_i8_kernel(int8_t *__restrict__ d
   }
 }
 
+// The Add followed by the int8 Relu of a residual block (libjit_element_add_kernel_i8, then
+// libjit_element_maxsplat_kernel_i8 on its result) in one pass over memory.
+__global__ void __launch_bounds__(kThreads) add_maxsplat_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
+                                                                   const int8_t *__restrict__ rhs, int64_t n, int32_t dst_off,
+                                                                   int32_t lhs_off, int32_t rhs_off, Triple lt, Triple rt,
+                                                                   int32_t splat) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t l = scale32((int32_t)lhs[i] - lhs_off, lt.pre, lt.post, lt.scale, 0);
+    const int32_t r = scale32((int32_t)rhs[i] - rhs_off, rt.pre, rt.post, rt.scale, 0);
+    const int32_t v = clip_i8(l + r + dst_off);
+    dst[i] = (int8_t)(v > splat ? v : splat);
+  }
+}
+
 // libjit_element_relu_i8 (libjit.cpp:1850-1858): max(x, srcOffset), then rescale
 __global__ void __launch_bounds__(kThreads) relu_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ src, int64_t n,
                                                            int32_t src_off, int32_t dst_off, Triple t) {
@@ -91,6 +105,40 @@ __global__ void __launch_bounds__(kThreads) max_pool_i8_kernel(const int8_t *__r
         best = v > best ? v : best;
       }
     out[i] = best == -129 ? def : (int8_t)best;
+  }
+}
+
+// The same for 16 channels per thread (C a multiple of 16, 16-byte aligned tensors): four
+// byte-wise signed maxima per instruction.
+__global__ void __launch_bounds__(kThreads) max_pool_i8_vec_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
+                                                                   const __grid_constant__ PoolGeom g, int8_t def) {
+  const int cc = g.C >> 4;
+  const int64_t total = (int64_t)g.N * g.OH * g.OW * cc;
+  const uint32_t lowest = 0x80808080u;  // four times -128
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % cc);
+    int64_t r = i / cc;
+    const int ow = (int)(r % g.OW);
+    r /= g.OW;
+    const int oh = (int)(r % g.OH), n = (int)(r / g.OH);
+    uint4 best = make_uint4(lowest, lowest, lowest, lowest);
+    bool any = false;
+    for (int kh = 0; kh < g.KH; kh++)
+      for (int kw = 0; kw < g.KW; kw++) {
+        const int ih = oh * g.SH - g.PT + kh, iw = ow * g.SW - g.PL + kw;
+        if (ih < 0 || iw < 0 || ih >= g.H || iw >= g.W) continue;
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(in + (((int64_t)n * g.H + ih) * g.W + iw) * g.C) + c);
+        best.x = __vmaxs4(best.x, v.x);
+        best.y = __vmaxs4(best.y, v.y);
+        best.z = __vmaxs4(best.z, v.z);
+        best.w = __vmaxs4(best.w, v.w);
+        any = true;
+      }
+    if (!any) {
+      const uint32_t d4 = 0x01010101u * (uint32_t)(uint8_t)def;
+      best = make_uint4(d4, d4, d4, d4);
+    }
+    reinterpret_cast<uint4 *>(out)[i] = best;
   }
 }
 
@@ -183,6 +231,19 @@ extern "C" int glowb200_element_add_i8(int8_t *dest, const int8_t *lhs, const in
   return GLOWB200_OK;
 }
 
+extern "C" int glowb200_element_add_maxsplat_i8(int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n,
+                                                int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset, int32_t lhs_pre,
+                                                int32_t lhs_post, int32_t lhs_scale, int32_t rhs_pre, int32_t rhs_post,
+                                                int32_t rhs_scale, int32_t splat, glowb200_stream_t stream) {
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && lhs && rhs)
+  GLOWB200_REQUIRE(splat >= -128 && splat <= 127, "splat value outside int8");
+  add_maxsplat_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset,
+                                                                        Triple{lhs_pre, lhs_post, lhs_scale},
+                                                                        Triple{rhs_pre, rhs_post, rhs_scale}, splat);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
 extern "C" int glowb200_element_relu_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t src_offset, int32_t dest_offset,
                                         int32_t dest_pre, int32_t dest_post, int32_t dest_scale, glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
@@ -233,7 +294,10 @@ extern "C" int glowb200_max_pool_i8(const int8_t *in, int8_t *out, const int64_t
   const int64_t total = (int64_t)g.N * g.OH * g.OW * g.C;
   if (total == 0) return GLOWB200_OK;
   GLOWB200_REQUIRE(in && out, "NULL tensor pointer");
-  max_pool_i8_kernel<<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(in, out, g, (int8_t)out_offset);
+  if ((g.C & 15) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+    max_pool_i8_vec_kernel<<<grid_for(total >> 4), kThreads, 0, GLOWB200_STREAM>>>(in, out, g, (int8_t)out_offset);
+  else
+    max_pool_i8_kernel<<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(in, out, g, (int8_t)out_offset);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }

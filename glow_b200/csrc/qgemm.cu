@@ -322,7 +322,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const ColQuant q = col_quant(p, j);
           int32_t term = 0;
           if (p.bias)
-            term = scale32(p.bias[j] - (p.bias_offsets ? p.bias_offsets[j] : p.bias_offset), q.bias_pre, q.bias_post,
+            term = scale32(load_bias(p, j) - (p.bias_offsets ? p.bias_offsets[j] : p.bias_offset), q.bias_pre, q.bias_post,
                            q.bias_scale, 0);
           const uint32_t corr = (uint32_t)term - (uint32_t)p.a_offset * (uint32_t)p.b_row_sums[j] +
                                 (uint32_t)p.k_corr * (uint32_t)p.a_offset * (uint32_t)q.b_off;
@@ -477,7 +477,7 @@ __global__ void __launch_bounds__(256) i8_gemm_requant_any_kernel(const int8_t *
   for (int k = 0; k < p.k_corr; k++)
     sum += (uint32_t)(((int32_t)b[(size_t)j * p.K + k] - q.b_off) * ((int32_t)a[(size_t)i * p.K + k] - p.a_offset));
   if (p.bias)
-    sum += (uint32_t)scale32(p.bias[j] - (p.bias_offsets ? p.bias_offsets[j] : p.bias_offset), q.bias_pre, q.bias_post,
+    sum += (uint32_t)scale32(load_bias(p, j) - (p.bias_offsets ? p.bias_offsets[j] : p.bias_offset), q.bias_pre, q.bias_post,
                              q.bias_scale, 0);
   p.out[(size_t)i * p.N + j] =
       (int8_t)clip_i8(activation_i32(scale32((int32_t)sum, q.out_pre, q.out_post, q.out_scale, p.out_offset), p));
@@ -648,6 +648,7 @@ extern "C" int glowb200_rowwise_quantized_fc_i8_i32(
   p.uniform = 0;
   p.a_offset = in_offset; p.bias_offset = bias_offset; p.out_offset = out_offset;
   p.act_type = (flags & GLOWB200_FC_FUSE_RELU) ? 1 : 0;
+  p.bias_is_i8 = (flags & GLOWB200_FC_BIAS_INT8) ? 1 : 0;
   return run_gemm(p, in, weights, weights_row_sums, (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) != 0,
                   (flags & GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL) != 0, workspace, workspace_bytes,
                   reinterpret_cast<cudaStream_t>(stream));
@@ -697,6 +698,7 @@ extern "C" int glowb200_fc_i8_i32(int8_t *out, const int8_t *in, const int8_t *w
   p.u_b_offset = weights_offset;
   p.u_bias_pre = bias_pre; p.u_bias_post = bias_post; p.u_bias_scale = bias_scale;
   p.u_out_pre = out_pre; p.u_out_post = out_post; p.u_out_scale = out_scale;
+  p.bias_is_i8 = (flags & GLOWB200_FC_BIAS_INT8) ? 1 : 0;
   if (weights_offset == 0) flags |= GLOWB200_FC_WEIGHT_OFFSETS_ZERO;
   return run_per_tensor(p, in, weights, weights_transposed, flags, workspace, workspace_bytes,
                         reinterpret_cast<cudaStream_t>(stream));

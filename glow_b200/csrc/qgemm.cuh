@@ -7,7 +7,7 @@ namespace glowb200 {
 
 struct GemmParams {
   int8_t *out;                // [M, N]
-  const int32_t *bias;        // [N] or nullptr (MatMul)
+  const int32_t *bias;        // [N] or nullptr (MatMul); int8 values when bias_is_i8 (the _i8_i8 kernels)
   const int32_t *b_offsets;   // weight offsets; index j * stride_b_off
   const int32_t *bias_pre, *bias_post, *bias_scale;  // index j * stride_q
   const int32_t *out_pre, *out_post, *out_scale;      // index j * stride_q
@@ -22,6 +22,7 @@ struct GemmParams {
   int32_t act_type, act_args[3];
   // per-tensor layers: one set of scalars for every column instead of the arrays above
   int uniform;
+  int bias_is_i8;
   int32_t u_b_offset, u_bias_pre, u_bias_post, u_bias_scale, u_out_pre, u_out_post, u_out_scale;
 };
 
@@ -32,6 +33,12 @@ __device__ __forceinline__ ColQuant col_quant(const GemmParams &p, int j) {
   if (p.uniform) return {p.u_b_offset, p.u_bias_pre, p.u_bias_post, p.u_bias_scale, p.u_out_pre, p.u_out_post, p.u_out_scale};
   return {p.b_offsets[j], p.bias ? p.bias_pre[j] : 0, p.bias ? p.bias_post[j] : 0, p.bias ? p.bias_scale[j] : 0,
           p.out_pre[j], p.out_post[j], p.out_scale[j]};
+}
+
+// bias[j] of either element type (libjit_fc_generic / libjit_rowwise_quantized_fc_generic /
+// libjit_*_conv2d_generic are templates over BiasElemTy: int32 for the _i8_i32 entry points, int8 for _i8_i8).
+__device__ __forceinline__ int32_t load_bias(const GemmParams &p, int j) {
+  return p.bias_is_i8 ? (int32_t) reinterpret_cast<const int8_t *>(p.bias)[j] : p.bias[j];
 }
 
 // libjit_activation_i32 (lib/LLVMIRCodeGen/libjit/libjit_defs.h:206-233).

@@ -150,6 +150,7 @@ def embedding_bag_byte_rowwise_offsets(data, weights, indices, offsets, kind=UIN
 FC_WEIGHT_OFFSETS_ZERO = 1
 FC_FORCE_ANY_SHAPE_KERNEL = 2
 FC_FUSE_RELU = 4
+FC_BIAS_INT8 = 8
 
 ASYMMETRIC, SYMMETRIC, SYMMETRIC_WITH_UNSIGNED, SYMMETRIC_WITH_POWER2_SCALE = 0, 1, 2, 3
 
@@ -341,7 +342,10 @@ def rowwise_quantized_fc(inp, weights, bias, weights_offsets, bias_triples, out_
     _cuda(weights, "weights", (torch.int8,))
     M, K = inp.shape
     N = weights.shape[0]
-    for t in (bias, weights_offsets, *bias_triples, *out_triples):
+    _cuda(bias, "bias", (torch.int32, torch.int8))
+    if bias.dtype == torch.int8:   # the reference's _i8_i8 form
+        flags |= FC_BIAS_INT8
+    for t in (weights_offsets, *bias_triples, *out_triples):
         _cuda(t, "per-row parameter", (torch.int32,))
     if out is None:
         out = torch.empty((M, N), dtype=torch.int8, device=inp.device)
@@ -356,7 +360,9 @@ def rowwise_quantized_fc(inp, weights, bias, weights_offsets, bias_triples, out_
 
 def fully_connected_i8(inp, weights, bias, out_offset, in_offset, weights_offset, bias_offset, bias_triple,
                        out_triple, *, weights_transposed=None, flags=0, out=None, workspace=None, status=None):
-    """FullyConnected (int8, per-tensor): inp [M,K], weights [K,N], bias int32 [N]."""
+    """FullyConnected (int8, per-tensor): inp [M,K], weights [K,N], bias int32 (or int8) [N]."""
+    if bias.dtype == torch.int8:   # the reference's _i8_i8 form
+        flags |= FC_BIAS_INT8
     M, K = inp.shape
     N = weights.shape[1] if weights is not None else weights_transposed.shape[0]
     if out is None:
@@ -447,6 +453,16 @@ def element_add_i8(lhs, rhs, dest_offset, lhs_offset, rhs_offset, lhs_triple, rh
     check(_lib.lib().glowb200_element_add_i8(_p(out), _p(lhs), _p(rhs), lhs.numel(), int(dest_offset), int(lhs_offset),
                                              int(rhs_offset), *[int(v) for v in lhs_triple],
                                              *[int(v) for v in rhs_triple], _stream()))
+    return out
+
+
+def element_add_maxsplat_i8(lhs, rhs, dest_offset, lhs_offset, rhs_offset, lhs_triple, rhs_triple, splat, out=None):
+    """element_add_i8 followed by element_maxsplat_i8(splat), fused."""
+    if out is None:
+        out = torch.empty_like(lhs)
+    check(_lib.lib().glowb200_element_add_maxsplat_i8(
+        _p(out), _p(lhs), _p(rhs), lhs.numel(), int(dest_offset), int(lhs_offset), int(rhs_offset),
+        *[int(v) for v in lhs_triple], *[int(v) for v in rhs_triple], int(splat), _stream()))
     return out
 
 

@@ -228,9 +228,9 @@ class ResNet50Int8:
                 sc = self._conv(l[3]["name"], x) if l[3] else x
                 a = self.q["add"][l[1]]
                 out_off = tqp[a["out"]][1]
-                x = ops.element_add_i8(y, sc, out_off, tqp[a["lhs"]][1], tqp[a["rhs"]][1], a["lhs_triple"], a["rhs_triple"])
-                x = ops.element_maxsplat_i8(x, out_off, out=x)
-                self.launches += 2
+                x = ops.element_add_maxsplat_i8(y, sc, out_off, tqp[a["lhs"]][1], tqp[a["rhs"]][1], a["lhs_triple"],
+                                                a["rhs_triple"], out_off)
+                self.launches += 1
             elif l[0] == "avgpool":
                 src = self.q["avgpool_in"]
                 hw = x.shape[1]

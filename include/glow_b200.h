@@ -268,6 +268,9 @@ int glowb200_channelwise_conv_prepare(const float *filter, const float *bias, in
 #define GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL 2   /* run the plain one-thread-per-output kernel          */
 #define GLOWB200_FC_FUSE_RELU 4                /* max(x, out_offset) in the epilogue: the int8 Relu that
                                                   follows the layer when both share one output type    */
+#define GLOWB200_FC_BIAS_INT8 8                /* `bias` holds int8 values: the reference's _i8_i8 entry
+                                                 points (libjit_matmul.cpp:409-422, :438-450;
+                                                 libjit_conv.cpp:512-527, :547-562).  Same arithmetic. */
 
 /* Scratch bytes the three entry points below may need for an [M,K] x [N,K]^T problem. */
 size_t glowb200_i8_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N);
@@ -364,6 +367,16 @@ int glowb200_element_add_i8(int8_t *dest, const int8_t *lhs, const int8_t *rhs, 
                             int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset,
                             int32_t lhs_pre, int32_t lhs_post, int32_t lhs_scale, int32_t rhs_pre,
                             int32_t rhs_post, int32_t rhs_scale, glowb200_stream_t stream);
+/* Add followed by the int8 Relu of a residual block -- glowb200_element_add_i8 then
+ * glowb200_element_maxsplat_i8(splat) on its result -- in one pass over memory (the pair is two
+ * instructions in Glow's IR: ElementAdd, then the CPU backend's CPUMaxSplat,
+ * lib/Backends/CPU/Transforms.cpp:83-113).  Bit-identical to the two calls. */
+int glowb200_element_add_maxsplat_i8(int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n,
+                                     int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset,
+                                     int32_t lhs_pre, int32_t lhs_post, int32_t lhs_scale,
+                                     int32_t rhs_pre, int32_t rhs_post, int32_t rhs_scale,
+                                     int32_t splat, glowb200_stream_t stream);
+
 /* Relu int8: libjit_element_relu_i8 (libjit.cpp:1850-1858). */
 int glowb200_element_relu_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t src_offset,
                              int32_t dest_offset, int32_t dest_pre, int32_t dest_post,

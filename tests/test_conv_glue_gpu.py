@@ -24,6 +24,9 @@ CONV_CASES = [
     (1, 12, 10, 6, 8, (3, 3), (2, 2), (1, 1, 1, 1), 2, (1, 1), 1),       # groups -> direct kernel
     (1, 5, 5, 8, 8, (3, 3), (1, 1), (1, 1, 1, 1), 8, (1, 1), 0),         # depthwise
     (2, 7, 7, 20, 10, (1, 1), (1, 1), (0, 0, 0, 0), 1, (1, 1), 0),       # C not a multiple of 16
+    (2, 64, 48, 3, 32, (7, 7), (2, 2), (3, 3, 3, 3), 1, (1, 1), 1),      # stem shape: rows staged in shared memory
+    (1, 17, 13, 5, 12, (3, 5), (1, 2), (1, 2, 1, 2), 1, (1, 1), 0),      # odd channel count, rectangular window
+    (1, 12, 12, 12, 16, (3, 3), (1, 1), (2, 2, 2, 2), 1, (2, 2), 0),     # dilation with C not a multiple of 16
 ]
 
 
@@ -103,6 +106,8 @@ def test_elementwise_and_pools_bit_exact(oracle):
     rt = ops.quantize_scale_offset_32to8(1.9)
     np.testing.assert_array_equal(ops.element_add_i8(t(a), t(b), 5, -3, 9, lt, rt).cpu().numpy(),
                                   oracle.element_add_i8(a, b, 5, -3, 9, lt, rt))
+    np.testing.assert_array_equal(ops.element_add_maxsplat_i8(t(a), t(b), 5, -3, 9, lt, rt, -20).cpu().numpy(),
+                                  oracle.element_maxsplat_i8(oracle.element_add_i8(a, b, 5, -3, 9, lt, rt), -20))
     np.testing.assert_array_equal(ops.element_relu_i8(t(a), -10, 4, lt).cpu().numpy(), oracle.element_relu_i8(a, -10, 4, lt))
     np.testing.assert_array_equal(ops.element_maxsplat_i8(t(a), -7).cpu().numpy(), oracle.element_maxsplat_i8(a, -7))
     np.testing.assert_array_equal(ops.element_rescale_i8(t(a), 3, -2, rt).cpu().numpy(), oracle.element_rescale_i8(a, 3, -2, rt))
@@ -121,6 +126,14 @@ def test_elementwise_and_pools_bit_exact(oracle):
             tr = ops.quantize_scale_offset_32to8(np.float32(0.03) / np.float32(0.05) / area)
             np.testing.assert_array_equal(ops.avg_pool_i8(t(x), k, s, p, cip, 3, -4, tr).cpu().numpy(),
                                           oracle.avg_pool_i8(x, ohw, k, s, p, cip, 3, -4, tr))
+
+
+def test_max_pool_sixteen_channels_per_thread(oracle):
+    rng = np.random.default_rng(29)
+    x = rng.integers(-128, 128, (3, 21, 18, 64)).astype(np.int8)
+    for k, s, p in [((3, 3), (2, 2), (1, 1, 1, 1)), ((2, 2), (2, 2), (0, 0, 0, 0)), ((5, 5), (3, 3), (2, 2, 2, 2))]:
+        ohw = ops.conv_out_hw((21, 18), k, s, p)
+        np.testing.assert_array_equal(ops.max_pool_i8(t(x), k, s, p, -7).cpu().numpy(), oracle.max_pool_i8(x, ohw, k, s, p, -7))
 
 
 def test_transpose():

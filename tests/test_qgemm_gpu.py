@@ -133,3 +133,31 @@ def test_row_sums():
     for rows, K in [(300, 4096), (17, 100), (1, 16)]:
         x = rng.integers(-128, 128, (rows, K)).astype(np.int8)
         np.testing.assert_array_equal(ops.i8_row_sums(t(x)).cpu().numpy(), x.astype(np.int32).sum(1))
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 512, 256), (64, 100, 30)])
+def test_int8_bias_forms(oracle, M, K, N):
+    """The reference's _i8_i8 entry points: an int8 bias goes through the same arithmetic as an
+    int32 bias holding the same values (tensor-core and any-shape kernels)."""
+    rng = np.random.default_rng(M + N)
+    c = make_rwq_fc(rng, M, K, N, True)
+    c["bias"] = rng.integers(-128, 128, N).astype(np.int32)
+    c["bias_offset"] = 5
+    # a bias scale that makes the small int8 bias matter in the result
+    c["params"] = ops.rowwise_requant_params(c["w_scales"], 0.05, np.float32(0.8), np.float32(0.5 * np.sqrt(K / 4096.0)))
+    want = oracle_rwq(oracle, c)
+    st = ops.new_status(DEV)
+    p = [t(a) for a in c["params"]]
+    got = ops.rowwise_quantized_fc(t(c["inp"]), t(c["w"]), t(c["bias"].astype(np.int8)), t(c["w_off"]), p[:3], p[3:],
+                                   c["out_offset"], c["in_offset"], c["bias_offset"], status=st).cpu().numpy()
+    np.testing.assert_array_equal(got, want)
+    got32, _ = run_rwq(c)
+    np.testing.assert_array_equal(got32, want)
+    assert int(st.item()) == 0
+    # per-tensor FullyConnected
+    w_kn = np.ascontiguousarray(c["w"].T)
+    bt, ot = oracle.quantize_scale_offset_32to8(np.float32(0.7)), oracle.quantize_scale_offset_32to8(np.float32(0.004))
+    want = oracle.fc_i8_i32(c["inp"], w_kn, c["bias"], 2, c["in_offset"], 1, c["bias_offset"], bt, ot)
+    got = ops.fully_connected_i8(t(c["inp"]), t(w_kn), t(c["bias"].astype(np.int8)), 2, c["in_offset"], 1,
+                                 c["bias_offset"], bt, ot).cpu().numpy()
+    np.testing.assert_array_equal(got, want)
