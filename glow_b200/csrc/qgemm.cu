@@ -84,17 +84,43 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when it gave up (or another role already did).
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          long long limit = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     for (int i = 0; i < 64; i++)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       return false;
     }
+  }
+}
+
+// The bounded wait, exercised on its own: one warp waits on a barrier that nothing will ever
+// complete, with a short limit; it must give up, say so through the status word and return, and
+// the other warp, polling the shared flag the way the kernel's other roles do, must leave too.
+__global__ void __launch_bounds__(64) wait_limit_selftest_kernel(long long limit, int32_t *status, int32_t *gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag_storage;
+  volatile int *abort_flag = &abort_flag_storage;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag_storage = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) {
+    ok = mbar_wait(&bar, 0, abort_flag, limit);  // phase 0 never completes: nobody arrives
+  } else if (threadIdx.x == 32) {
+    ok = mbar_wait(&bar, 0, abort_flag, 4 * limit);  // leaves as soon as the first waiter gave up
+  }
+  if (!ok) {
+    atomicAdd(gave_up, 1);
+    if (status != nullptr) atomicOr(status, GLOWB200_STATUS_WAIT_TIMEOUT);
   }
 }
 
@@ -616,6 +642,15 @@ extern "C" size_t glowb200_i8_gemm_workspace_bytes(int64_t M, int64_t K, int64_t
   if (M < 0 || N < 0 || K < 0) return 0;
   // row sums of both operands + room for a transposed copy of a [K, N] right-hand side
   return align_up((size_t)N * 4, 256) + align_up((size_t)M * 4, 256) + align_up((size_t)N * (size_t)K, 256);
+}
+
+extern "C" int glowb200_wait_limit_selftest(int64_t limit_cycles, int32_t *status, int32_t *waiters_that_gave_up,
+                                            glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(limit_cycles > 0 && limit_cycles <= 100000000ll, "limit_cycles must be in (0, 1e8]");
+  GLOWB200_REQUIRE(waiters_that_gave_up != nullptr, "NULL pointer");
+  wait_limit_selftest_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(limit_cycles, status, waiters_that_gave_up);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
 }
 
 extern "C" int glowb200_i8_row_sums(const int8_t *matrix, int64_t rows, int64_t K, int32_t *sums, glowb200_stream_t stream) {

@@ -323,6 +323,14 @@ def rowwise_requant_params(row_scales, in_scale, bias_scales, out_scale):
     return outs
 
 
+def wait_limit_selftest(limit_cycles, status):
+    """Runs the library's bounded device-side wait on a barrier nothing completes; returns how
+    many of the two waiting warps gave up (the status word gets STATUS_WAIT_TIMEOUT)."""
+    gave_up = torch.zeros(1, dtype=torch.int32, device=status.device)
+    check(_lib.lib().glowb200_wait_limit_selftest(int(limit_cycles), _p(status), _p(gave_up), _stream()))
+    return gave_up
+
+
 def i8_gemm_workspace_bytes(M, K, N):
     return int(_lib.lib().glowb200_i8_gemm_workspace_bytes(int(M), int(K), int(N)))
 

@@ -272,6 +272,17 @@ int glowb200_channelwise_conv_prepare(const float *filter, const float *bias, in
                                                  points (libjit_matmul.cpp:409-422, :438-450;
                                                  libjit_conv.cpp:512-527, :547-562).  Same arithmetic. */
 
+/* Every device-side wait of this library (the tensor-core kernels wait on mbarriers for TMA
+ * loads, MMA completion and buffer hand-over) is bounded: after about a second it gives up, raises
+ * GLOWB200_STATUS_WAIT_TIMEOUT in the status word, frees its tensor memory and returns, so the
+ * context stays usable and the host decides (the runtime reports RUNTIME_DEVICE_NONRECOVERABLE).
+ * This entry point runs that wait routine alone, on a barrier nothing ever completes, with a limit
+ * of `limit_cycles` SM clocks: two warps wait, the first must run out, the second must notice and
+ * leave; *waiters_that_gave_up (device int32, zeroed by the caller) counts them, the status word
+ * gets the time-out bit.  No reference counterpart. */
+int glowb200_wait_limit_selftest(int64_t limit_cycles, int32_t *status, int32_t *waiters_that_gave_up,
+                                 glowb200_stream_t stream);
+
 /* Scratch bytes the three entry points below may need for an [M,K] x [N,K]^T problem. */
 size_t glowb200_i8_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N);
 

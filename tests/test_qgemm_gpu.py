@@ -161,3 +161,18 @@ def test_int8_bias_forms(oracle, M, K, N):
     got = ops.fully_connected_i8(t(c["inp"]), t(w_kn), t(c["bias"].astype(np.int8)), 2, c["in_offset"], 1,
                                  c["bias_offset"], bt, ot).cpu().numpy()
     np.testing.assert_array_equal(got, want)
+
+
+def test_bounded_wait_gives_up_and_leaves_the_context_usable(oracle):
+    """A device-side wait that cannot complete runs out after its limit, reports through the status
+    word and returns; the next launch on the same context works."""
+    st = ops.new_status(DEV)
+    gave_up = ops.wait_limit_selftest(2_000_000, st)      # about a millisecond of SM clocks
+    torch.cuda.synchronize()
+    assert int(gave_up.item()) == 2
+    assert int(st.item()) == ops.STATUS_WAIT_TIMEOUT
+    rng = np.random.default_rng(1)
+    c = make_rwq_fc(rng, 128, 256, 256)
+    got, status = run_rwq(c)
+    assert status == 0
+    np.testing.assert_array_equal(got, oracle_rwq(oracle, c))
