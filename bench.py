@@ -46,9 +46,10 @@ def parse():
     ap.add_argument("--requests", type=int, default=4, help="distinct pre-generated batches rotated over the steps")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="slws", choices=["slws", "int8_fc", "slws4"],
+    ap.add_argument("--workload", default="slws", choices=["slws", "int8_fc", "slws4", "dlrm", "resnet50"],
                     help="slws: the headline gather-pool line (default); int8_fc: the rowwise int8 FC line; "
-                         "slws4: the 4-bit fused-rowwise sweep point selected by --dim")
+                         "slws4: the 4-bit fused-rowwise sweep point selected by --dim; dlrm / resnet50: the "
+                         "recommendation model / the int8 ResNet-50 alone (the default line carries both as extras)")
     ap.add_argument("--dim", type=int, default=128, help="slws4: embedding width (32, 64, 128 or 256)")
     ap.add_argument("--table-gb", type=float, default=40.0, help="slws4: total table bytes per GPU, in GB")
     ap.add_argument("--row-bytes", type=int, default=0,
@@ -634,6 +635,46 @@ def resnet_measure(torch, dev, steps):
                                    "224x224x3, every node on the library's kernels", "batch": 64}}
 
 
+def run_model_line(args):
+    """--workload dlrm | resnet50: the model measurements of the default line's extras, alone."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(local)
+    sampler.start()
+    if args.workload == "dlrm":
+        forms = ["local"] if world == 1 else ["fused", "nccl"]
+        res, cfg = dlrm_measure(torch, dist, dev, rank, world, max(10, args.steps), max(3, args.warmup), forms)
+        best = max(res.values(), key=lambda r: r["samples_per_s"])
+        line = {"metric": "dlrm_samples_per_s", "value": best["samples_per_s"], "unit": "samples/s", "n_gpus": world,
+                "steps": max(10, args.steps), "warmup": max(3, args.warmup), "ms_per_step": best["ms_per_step"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8 -> f32 pooling, s8 x s8 -> s32 layers",
+                "data": "synthetic", "config": cfg, "by_exchange": res,
+                "e2e": {"value": best["e2e_samples_per_s"], "unit": "samples/s",
+                        "h2d_bytes_per_step": best["h2d_bytes_per_step_per_rank"] * world,
+                        "d2h_bytes_per_step": best["d2h_bytes_per_step_per_rank"] * world},
+                "gpu_launches": best["launches_per_step"] * max(10, args.steps)}
+    else:
+        r = resnet_measure(torch, dev, max(5, args.steps))
+        line = {"metric": r["metric"], "value": r["value"], "unit": r["unit"], "n_gpus": 1, "steps": max(5, args.steps),
+                "warmup": 3, "ms_per_step": r["ms_per_batch"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "s8 x s8 -> s32", "data": "synthetic", "config": r["config"],
+                "e2e": {"value": r["e2e_value"], "unit": r["unit"], "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+                        "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
+                "effective_tops": r["effective_tops"], "gpu_launches": r["launches_per_batch"] * max(5, args.steps)}
+    line["clocks"] = sampler.stop()
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_slws4_line(args):
     """--workload slws4: one point of the 4-bit embedding bandwidth sweep (fifth benchmark
     configuration): UInt4FusedFP16QTy tables of 10,000,000 rows x D (D/2 + 4 bytes per row),
@@ -879,6 +920,8 @@ def main():
         return run_int8_fc_line(args)
     if args.workload == "slws4":
         return run_slws4_sharded_line(args) if args.shard != "tables" else run_slws4_line(args)
+    if args.workload in ("dlrm", "resnet50"):
+        return run_model_line(args)
 
     import torch
     import torch.distributed as dist
