@@ -337,10 +337,17 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     constexpr int kChunk = kGroupCols >= 32 ? 32 : 16;
     const bool vec_ok = ((p.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     int lt = 0;
+    int cols_n0 = -1;  // column block the records in shared memory belong to
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, lt++) {
       const int m0 = (t % m_tiles) * kBlockM, n0 = (t / m_tiles) * BLOCK_N;
       const int buf = lt & 1;
-      // (1) per-column constants of this tile (the main loop of this or the next tile is running)
+      // (1) per-column constants of this tile (the main loop of this or the next tile is running).
+      // Tiles are numbered row-block fastest, so a CTA's consecutive tiles mostly share their
+      // column block: the records are rebuilt only when it changes (all epilogue threads see the
+      // same n0, so the barriers stay matched).
+      if (n0 != cols_n0) {
+      if (cols_n0 >= 0) asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");  // everyone is done with the old records
+      cols_n0 = n0;
       for (int c = et; c < BLOCK_N; c += kEpilogueThreads) {
         const int j = n0 + c;
         ColParams cp = {0, 0, 0, 0};
@@ -360,6 +367,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         cols[c] = cp;
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");  // epilogue warps only
+      }
       // (2) drain the accumulators of this tile
       const int row = m0 + quarter * 32 + lane;
       // All epilogue threads agree on the outcome of the (bounded) wait through a reducing
@@ -443,7 +451,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         GEMM_TRACE(9, lt == 0 && et == 0 && c0 == 0);
         GEMM_TRACE(10, lt == 0 && et == 0 && c0 == 32);
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");  // cols[] is rewritten for the next tile
+
       GEMM_TRACE(5, lt == 0 && et == 0);
     }
   }
@@ -610,6 +618,12 @@ int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_ro
     p.a_row_sums = nullptr;
   }
   CUtensorMap ma, mb;
+  // 128-column tiles when 256-column ones would leave half a tile (or more) of padding
+  if (p.N > 64 && (((p.N + 127) / 128) & 1)) {
+    if (int rc = make_map(&ma, a, p.M, p.K, kBlockM)) return rc;
+    if (int rc = make_map(&mb, b, p.N, p.K, 128)) return rc;
+    return launch_tile_kernel<128, 6>(ma, mb, p, s);
+  }
   if (p.N > 64) {
     if (int rc = make_map(&ma, a, p.M, p.K, kBlockM)) return rc;
     if (int rc = make_map(&mb, b, p.N, p.K, 256)) return rc;
