@@ -62,6 +62,9 @@ __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
 #ifndef GLOWB200_SLWS_MIN_BLOCKS
 #define GLOWB200_SLWS_MIN_BLOCKS 3
 #endif
+#ifndef GLOWB200_SLWS_UNROLL_P2
+#define GLOWB200_SLWS_UNROLL_P2 4
+#endif
 __device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
   uint32_t v;
 #if GLOWB200_SLWS_L1_NOALLOC
@@ -846,7 +849,7 @@ cudaError_t launch_gather_p(const SlwsLaunch &L, int P, dim3 grid, cudaStream_t 
       if constexpr (BITS == 4) {
         if (L.lpr_log2 >= 3) return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 2, 8>(L, grid, s);
       }
-      return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 2, 4>(L, grid, s);
+      return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 2, GLOWB200_SLWS_UNROLL_P2>(L, grid, s);
     default: return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 4, 4>(L, grid, s);
   }
 }
