@@ -46,6 +46,8 @@ struct SlwsLaunch {
   int32_t select;
   // 1: the tables are row-range shards (row_begin / global_rows of the descriptors are honoured)
   int32_t sharded;
+  // 1: rows are a multiple of 16 bytes wide and every table starts on a 16-byte boundary
+  int32_t wide16;
 };
 
 __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
@@ -316,7 +318,11 @@ __device__ __forceinline__ float load_weight(const void *weights, int64_t i) {
 // ------------------------------------------------------------------------------------------
 // Gather-pool.  grid = (ceil(max_segments / bags_per_block), num_jobs).
 // ------------------------------------------------------------------------------------------
-template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int kUnroll, bool SHARD = false>
+// WIDE16 (uint8 rows, P = 2, rows a multiple of 16 bytes wide in a 16-byte aligned table -- the
+// padded layouts): a lane owns two ADJACENT chunks and fetches them with one 16-byte load, so a
+// row costs two load instructions (payload, scale/offset) instead of three.
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int kUnroll, bool SHARD = false,
+          bool WIDE16 = false>
 __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
   using RL = RowLoad<BITS, SO16>;
   const int job_id = blockIdx.y;
@@ -344,7 +350,7 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
 
   bool has[P];
 #pragma unroll
-  for (int c = 0; c < P; c++) has[c] = (c * lpr + gl) < chunks;
+  for (int c = 0; c < P; c++) has[c] = (WIDE16 ? gl * P + c : c * lpr + gl) < chunks;
 
   float acc[P][8];
 #pragma unroll
@@ -399,9 +405,18 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
       for (int u = 0; u < kUnroll; u++) {
         if (r[u] >= 0) {
           const uint8_t *row = data + (int64_t)r[u] * in_line;
+          if constexpr (WIDE16) {
+            if (has[0]) {
+              uint4 q;
+              asm("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(row + gl * 16));
+              pay[u][0].lo = q.x; pay[u][0].hi = q.y;
+              pay[u][1].lo = q.z; pay[u][1].hi = q.w;
+            }
+          } else {
 #pragma unroll
-          for (int c = 0; c < P; c++)
-            if (has[c]) pay[u][c] = RL::payload(row, c * lpr + gl);
+            for (int c = 0; c < P; c++)
+              if (has[c]) pay[u][c] = RL::payload(row, c * lpr + gl);
+          }
           tl[u] = RL::tail(row + in_line);
         }
       }
@@ -450,7 +465,7 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
 #pragma unroll
   for (int c = 0; c < P; c++) {
     if (!has[c]) continue;
-    const int64_t col = (int64_t)(c * lpr + gl) * 8;
+    const int64_t col = (int64_t)(WIDE16 ? gl * P + c : c * lpr + gl) * 8;
     float o[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) o[i] = ACC16 ? acc[c][i] : (acc[c][i] + bias_sum);
@@ -709,13 +724,13 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
 // One launch, two thread-to-bag mappings: every table is pooled by the mapping its bag-length
 // profile favours (the word the segments kernel leaves behind the table's boundaries).
 // grid.x covers the larger of the two mappings' block counts; surplus blocks leave at once.
-template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false>
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false, bool WIDE16 = false>
 __global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS)
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
   const bool skewed = p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
   if (skewed) gather_warp_body<BITS, SO16, OUT16, IdxT, P, U, SHARD>(p, bags_per_warp);
-  else gather_group_body<BITS, SO16, OUT16, false, IdxT, P, U, SHARD>(p);
+  else gather_group_body<BITS, SO16, OUT16, false, IdxT, P, U, SHARD, WIDE16>(p);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -825,6 +840,12 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
       const int64_t warps = (max_segments + bpw - 1) / bpw;
       const unsigned wblocks = (unsigned)((warps + 7) / 8);
       dim3 sgrid(wblocks > grid.x ? wblocks : grid.x, grid.y);
+      if constexpr (BITS == 8 && !SO16 && !OUT16 && P == 2 && U == 4) {
+        if (!L.sharded && L.wide16) {  // padded rows: one 16-byte payload load per lane
+          slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, false, true><<<sgrid, kGatherThreads, 0, s>>>(L, bpw);
+          return cudaGetLastError();
+        }
+      }
       if constexpr (!OUT16) {  // shards give fp32 partial sums (checked by the entry point)
         if (L.sharded) {
           slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, true><<<sgrid, kGatherThreads, 0, s>>>(L, bpw);
@@ -990,6 +1011,7 @@ int run_batched(const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_seg
                  (use_fp16_accumulation && out_is_fp16 && (kind & 1)) ? 1 : 0};
   L.select = (P != 0 && !g.acc16) ? 1 : 0;
   L.sharded = sharded ? 1 : 0;
+  L.wide16 = (in_line_size % 16) == 0 ? 1 : 0;  // 16-byte aligned tables are required of the descriptors
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   slws_segments_from_lengths_kernel<<<(unsigned)num_jobs, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
@@ -1067,6 +1089,7 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
   if (segments == 0) return GLOWB200_OK;
   GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
   L.select = (P != 0 && !g.acc16) ? 1 : 0;
+  L.wide16 = ((in_line_size % 16) == 0 && aligned_to(data, 16)) ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
@@ -1178,6 +1201,7 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_stat
     return rc;
   GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
   L.select = (P != 0 && !g.acc16) ? 1 : 0;
+  L.wide16 = ((in_line_size % 16) == 0 && aligned_to(data, 16)) ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // The segments kernel rewrites everything this call reads (segments + 1 boundaries and the
   // table's profile word); nothing in the array has to start at zero, and whatever an earlier
