@@ -1,7 +1,7 @@
 // Host runtime above the kernel ABI: the part of a Glow backend that sits between
 // DeviceManager::runFunction and the kernels, written against this library instead of Glow's
 // headers (Glow itself needs LLVM, folly and glog to compile; the thin glue that adapts these
-// classes to glow::CompiledFunction / glow::DeviceManager is shown in INTEGRATION.md).
+// classes to glow::CompiledFunction / glow::DeviceManager ships as source under integration/glow/lib/Backends/B200).
 //
 //   Function       what Backend::compile produces: a symbol table with byte offsets into three
 //                  slabs -- constants, placeholders ("mutable weights") and activations -- like

@@ -73,5 +73,5 @@ def config2(seed=MASTER_SEED, M=2048, K=4096, N=4096):
         w_offsets=np.zeros(N, np.int32),
         bias=r.integers(-2 ** 16, 2 ** 16 + 1, N).astype(np.int32),
         in_scale=np.float32(0.05), in_offset=3, out_scale=np.float32(0.5), out_offset=0,
-        # BASELINE leaves the bias type open; fixed here: scale = in_scale * mean weight scale, offset 0
+        # the benchmark definition leaves the bias type open; fixed here: scale = in_scale * mean weight scale, offset 0
         bias_scale=np.float32(5e-4), bias_offset=0)
