@@ -24,6 +24,8 @@
 #include <type_traits>
 
 #include "common.cuh"
+
+#include <climits>
 #include "qgemm.cuh"
 
 namespace glowb200 {
@@ -167,7 +169,8 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[32]) {
+template <int N>
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[N]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -230,7 +233,10 @@ struct GemmSmem {
 // (column-tile-major, so CTAs running together share weight tiles in L2).  The accumulators are
 // double-buffered in tensor memory: while the epilogue warps drain tile i, the MMA warp is
 // already accumulating tile i+1 into the other buffer.
-template <int BLOCK_N, int STAGES>
+// MODE 0: no input row sums take part (every weight offset is 0) and the activation is none or
+// Relu -- the common case, with a shorter drain loop; MODE 1: everything else.  One drain body per
+// kernel keeps the register allocation of the 96-register budget tight.
+template <int BLOCK_N, int STAGES, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ GemmParams p) {
@@ -334,7 +340,12 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int quarter = warp & 3;
     const int col_group = (warp - 2) >> 2;     // 0..3
     constexpr int kGroupCols = BLOCK_N / 4;    // columns per warp: 64 (BLOCK_N 256) or 16 (BLOCK_N 64)
-    constexpr int kChunk = kGroupCols >= 32 ? 32 : 16;
+    // columns drained from tensor memory per load: 16 keeps the drain loop inside the 96 registers
+    // a 576-thread CTA leaves (32 spills, and measured slower)
+#ifndef GLOWB200_GEMM_CHUNK
+#define GLOWB200_GEMM_CHUNK 16
+#endif
+    constexpr int kChunk = kGroupCols >= GLOWB200_GEMM_CHUNK ? GLOWB200_GEMM_CHUNK : 16;
     const bool vec_ok = ((p.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     int lt = 0;
     int cols_n0 = -1;  // column block the records in shared memory belong to
@@ -360,9 +371,14 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const uint32_t corr = (uint32_t)term - (uint32_t)p.a_offset * (uint32_t)p.b_row_sums[j] +
                                 (uint32_t)p.k_corr * (uint32_t)p.a_offset * (uint32_t)q.b_off;
           cp.c = (int32_t)corr;
-          cp.b_off = q.b_off;
-          cp.shifts = q.out_pre | (q.out_post << 8);
           cp.scale = q.out_scale;
+          if constexpr (MODE == 0) {  // {c, scale, rounding term, pre | post << 8}
+            cp.shifts = (int32_t)((1u << q.out_post) >> 1);
+            cp.b_off = q.out_pre | (q.out_post << 8);
+          } else {                    // {c, scale, pre | post << 8, weight offset}
+            cp.shifts = q.out_pre | (q.out_post << 8);
+            cp.b_off = q.b_off;
+          }
         }
         cols[c] = cp;
       }
@@ -388,10 +404,11 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const int32_t a_sum = (p.a_row_sums && row < p.M) ? p.a_row_sums[row] : 0;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kAccCols;
       int8_t *out_row = p.out + (size_t)row * p.N + n0;
+      const int32_t relu_floor = p.act_type == 1 ? p.out_offset : INT32_MIN;
 #pragma unroll 1
       for (int c0 = col_group * kGroupCols; c0 < (col_group + 1) * kGroupCols; c0 += kChunk) {
-        uint32_t acc[32];
-        if constexpr (kChunk == 32) tmem_ld_32x32b_x32(lane_addr + (uint32_t)c0, acc);
+        uint32_t acc[kChunk];
+        if constexpr (kChunk == 32) tmem_ld_32x32b_x32(lane_addr + (uint32_t)c0, reinterpret_cast<uint32_t(&)[32]>(acc));
         else tmem_ld_32x32b_x16(lane_addr + (uint32_t)c0, acc);
         tmem_ld_wait();
         GEMM_TRACE(7, lt == 0 && et == 0 && c0 == 0);
@@ -402,39 +419,35 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
         uint32_t packed[kChunk / 4];
-        // the requantisation, specialised on the two things that are uniform over the launch:
-        // whether input row sums take part and which activation follows
-        auto requant = [&](auto with_row_sums, auto act) {
+        // the requantisation: libjit_scale, ((v >> pre) * scale + rtn) >> post, then + offset, with
+        // rtn = 1 << (post - 1) (0 for post 0); Relu is max(x, out_offset), no activation max(x, INT_MIN)
 #pragma unroll
-          for (int i4 = 0; i4 < kChunk / 4; i4++) {
-            int32_t r[4];
+        for (int i4 = 0; i4 < kChunk / 4; i4++) {
+          int32_t r[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-              const int4 cp = *reinterpret_cast<const int4 *>(&cols[c0 + 4 * i4 + e]);  // {c, scale, shifts, b_off}
-              uint32_t v = acc[4 * i4 + e] + (uint32_t)cp.x;
-              if constexpr (decltype(with_row_sums)::value) v -= (uint32_t)cp.w * (uint32_t)a_sum;
-              // libjit_scale: ((v >> pre) * scale + rtn) >> post, then + offset; rtn = 1 << (post-1), 0 for post 0
-              const int32_t pre = cp.z & 0xff, post = cp.z >> 8;
+          for (int e = 0; e < 4; e++) {
+            const int4 cp = *reinterpret_cast<const int4 *>(&cols[c0 + 4 * i4 + e]);
+            uint32_t v = acc[4 * i4 + e] + (uint32_t)cp.x;
+            int32_t m, post;
+            if constexpr (MODE == 0) {
+              const int32_t pre = cp.w & 0xff;
+              post = cp.w >> 8;
+              m = (int32_t)((uint32_t)((int32_t)v >> pre) * (uint32_t)cp.y + (uint32_t)cp.z);
+            } else {
+              v -= (uint32_t)cp.w * (uint32_t)a_sum;  // a_sum is 0 when no row sums take part
+              const int32_t pre = cp.z & 0xff;
+              post = cp.z >> 8;
               const uint32_t rtn = (1u << post) >> 1;
-              const int32_t m = (int32_t)((uint32_t)((int32_t)v >> pre) * (uint32_t)cp.y + rtn);
-              int32_t x = (int32_t)((uint32_t)(m >> post) + (uint32_t)p.out_offset);
-              if constexpr (decltype(act)::value == 1) x = x > p.out_offset ? x : p.out_offset;
-              if constexpr (decltype(act)::value == 2) x = activation_i32(x, p);
-              r[e] = x;
+              m = (int32_t)((uint32_t)((int32_t)v >> pre) * (uint32_t)cp.y + rtn);
             }
-            packed[i4] = clip_pack4(r[0], r[1], r[2], r[3]);
+            int32_t x = (int32_t)((uint32_t)(m >> post) + (uint32_t)p.out_offset);
+            x = x > relu_floor ? x : relu_floor;
+            if constexpr (MODE == 1) {
+              if (p.act_type > 1) x = activation_i32(x, p);
+            }
+            r[e] = x;
           }
-        };
-        using std::integral_constant;
-        const int act_kind = p.act_type == 0 ? 0 : (p.act_type == 1 ? 1 : 2);
-        if (p.a_row_sums == nullptr) {
-          if (act_kind == 0) requant(integral_constant<bool, false>{}, integral_constant<int, 0>{});
-          else if (act_kind == 1) requant(integral_constant<bool, false>{}, integral_constant<int, 1>{});
-          else requant(integral_constant<bool, false>{}, integral_constant<int, 2>{});
-        } else {
-          if (act_kind == 0) requant(integral_constant<bool, true>{}, integral_constant<int, 0>{});
-          else if (act_kind == 1) requant(integral_constant<bool, true>{}, integral_constant<int, 1>{});
-          else requant(integral_constant<bool, true>{}, integral_constant<int, 2>{});
+          packed[i4] = clip_pack4(r[0], r[1], r[2], r[3]);
         }
         GEMM_TRACE(8, lt == 0 && et == 0 && c0 == 0 && packed[0] != 0x12345678u);
         if (row < p.M) {
@@ -568,17 +581,23 @@ int make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows) 
   return GLOWB200_OK;
 }
 
-template <int BLOCK_N, int STAGES>
-int launch_tile_kernel(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, cudaStream_t s) {
+template <int BLOCK_N, int STAGES, int MODE>
+int launch_tile_mode(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, cudaStream_t s) {
   using S = GemmSmem<BLOCK_N, STAGES>;
   // per device and cheap: set on every launch rather than tracked
-  GLOWB200_CUDA_OK(cudaFuncSetAttribute(i8_gemm_requant_kernel<BLOCK_N, STAGES>,
+  GLOWB200_CUDA_OK(cudaFuncSetAttribute(i8_gemm_requant_kernel<BLOCK_N, STAGES, MODE>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
   const int tiles = ((p.N + BLOCK_N - 1) / BLOCK_N) * ((p.M + kBlockM - 1) / kBlockM);
   const int sms = sm_count();
-  i8_gemm_requant_kernel<BLOCK_N, STAGES><<<tiles < sms ? tiles : sms, kGemmThreads, S::kTotal, s>>>(ma, mb, p);
+  i8_gemm_requant_kernel<BLOCK_N, STAGES, MODE><<<tiles < sms ? tiles : sms, kGemmThreads, S::kTotal, s>>>(ma, mb, p);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
+}
+
+template <int BLOCK_N, int STAGES>
+int launch_tile_kernel(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, cudaStream_t s) {
+  if (p.a_row_sums == nullptr && p.act_type <= 1) return launch_tile_mode<BLOCK_N, STAGES, 0>(ma, mb, p, s);
+  return launch_tile_mode<BLOCK_N, STAGES, 1>(ma, mb, p, s);
 }
 
 bool ptr16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
