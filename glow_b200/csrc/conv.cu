@@ -14,6 +14,11 @@
 #include "common.cuh"
 #include "qgemm.cuh"
 
+// 1: stride-1 windows take the shifted-rows path (no im2col matrix) when the shapes allow
+#ifndef GLOWB200_CONV_SHIFTED_ROWS
+#define GLOWB200_CONV_SHIFTED_ROWS 1
+#endif
+
 namespace glowb200 {
 namespace {
 
@@ -123,6 +128,44 @@ __global__ void __launch_bounds__(256) im2col_i8_rows_kernel(const int8_t *__res
   }
 }
 
+// NHWC input with its padding made real: [N, Hp, Wp, C], the cells outside the image filled with
+// `pad_word` (the input offset, which is how the reference's skipped taps read).  16 bytes per thread.
+__global__ void __launch_bounds__(256) pad_nhwc_i8_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ xp,
+                                                           const __grid_constant__ ConvGeom g, int Hp, int Wp, int pad_word) {
+  const int cc = g.C >> 4;
+  const int64_t total = (int64_t)g.N * Hp * Wp * cc;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % cc);
+    int64_t r = i / cc;
+    const int xw = (int)(r % Wp);
+    r /= Wp;
+    const int yh = (int)(r % Hp), n = (int)(r / Hp);
+    const int ih = yh - g.PT, iw = xw - g.PL;
+    int4 v = make_int4(pad_word, pad_word, pad_word, pad_word);
+    if (ih >= 0 && iw >= 0 && ih < g.H && iw < g.W)
+      v = __ldg(reinterpret_cast<const int4 *>(x + (((int64_t)n * g.H + ih) * g.W + iw) * g.C) + c);
+    reinterpret_cast<int4 *>(xp)[i] = v;
+  }
+}
+
+// Filter [OC, KH, KW, 64] -> [OC, KH * ceil(KW / 2), 128]: taps (kh, 2j) and (kh, 2j + 1) side by
+// side, the partner of a last odd tap zero -- the right-hand side that matches left-hand rows made of
+// two neighbouring 64-channel pixels.
+__global__ void __launch_bounds__(256) pair_taps_c64_kernel(const int8_t *__restrict__ f, int8_t *__restrict__ out, int OC,
+                                                             int KH, int KW) {
+  const int pairs = (KW + 1) >> 1;
+  const int64_t total = (int64_t)OC * KH * pairs * 128;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int j = (int)(i & 127);
+    int64_t r = i >> 7;
+    const int pr = (int)(r % pairs);
+    r /= pairs;
+    const int kh = (int)(r % KH), oc = (int)(r / KH);
+    const int kw = 2 * pr + (j >> 6);
+    out[i] = kw < KW ? f[(((int64_t)oc * KH + kh) * KW + kw) * 64 + (j & 63)] : (int8_t)0;
+  }
+}
+
 // [rows, K] -> [rows, Kpad], zero padded
 __global__ void __launch_bounds__(256) pad_rows_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int rows,
                                                            int K, int Kpad) {
@@ -223,6 +266,60 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
     return set_error(GLOWB200_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
   GLOWB200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
+#if GLOWB200_CONV_SHIFTED_ROWS
+  // Stride-1 windows over 64 or a multiple of 128 channels, symmetric filters: no im2col matrix.
+  // The input is copied once into a padded NHWC buffer; tap (kh, kw) of output row q then is row
+  // q + kh * Wp + kw of that buffer, which the contraction's loads address directly (the rows of
+  // the product that fall on the padding are computed and dropped).  The scratch sized for the
+  // im2col matrix is more than this needs.
+  if (pl.need_im2col && g.SH == 1 && g.SW == 1 && g.DH == 1 && g.DW == 1 && (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) &&
+      (g.C == 64 || g.C % 128 == 0) && (reinterpret_cast<uintptr_t>(in) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(filter) & 15) == 0) {
+    const int Hp = g.OH + g.KH - 1, Wp = g.OW + g.KW - 1;
+    const int pairs = (g.KW + 1) / 2;
+    const int entries = g.C == 64 ? g.KH * pairs : g.KH * g.KW;
+    const int64_t rows = (int64_t)g.N * Hp * Wp;
+    const size_t xp_bytes = align_up((size_t)rows * g.C + 256, 256);
+    const size_t fb_bytes = g.C == 64 ? align_up((size_t)g.OC * entries * 128, 256) : 0;
+    if (entries <= 32 && Hp >= g.H + g.PT && Wp >= g.W + g.PL && rows < (1ll << 31) &&
+        xp_bytes + fb_bytes <= pl.a_bytes + pl.f_bytes) {
+      int8_t *xp = reinterpret_cast<int8_t *>(ws);
+      const uint32_t b = (uint8_t)p.a_offset;
+      const int64_t chunks = rows * (g.C >> 4), blocks = (chunks + 255) / 256;
+      pad_nhwc_i8_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(
+          in, xp, g, Hp, Wp, (int)(b | (b << 8) | (b << 16) | (b << 24)));
+      GLOWB200_CUDA_OK(cudaGetLastError());
+      GLOWB200_CUDA_OK(cudaMemsetAsync(xp + rows * g.C, 0, 256, s));  // the window of the last rows reads past them
+      const int8_t *bmat = filter;
+      p.K = g.KH * g.KW * g.C;
+      if (g.C == 64) {
+        int8_t *fb = reinterpret_cast<int8_t *>(ws + xp_bytes);
+        const int64_t fblocks = ((int64_t)g.OC * entries * 128 + 255) / 256;
+        pair_taps_c64_kernel<<<(unsigned)(fblocks < 148 * 16 ? fblocks : 148 * 16), 256, 0, s>>>(filter, fb, g.OC, g.KH, g.KW);
+        GLOWB200_CUDA_OK(cudaGetLastError());
+        bmat = fb;
+        p.K = entries * 128;
+      }
+      p.k_corr = pl.K;
+      p.N = g.OC;
+      p.conv_entries = entries;
+      p.conv_cpb = g.C == 64 ? 1 : g.C / 128;
+      for (int e = 0; e < entries; e++)
+        p.conv_row_off[e] = g.C == 64 ? (e / pairs) * Wp + 2 * (e % pairs) : (e / g.KW) * Wp + (e % g.KW);
+      p.conv_hpwp = Hp * Wp;
+      p.conv_wp = Wp;
+      p.conv_oh = g.OH;
+      p.conv_ow = g.OW;
+      const int32_t *sums = filter_row_sums;
+      if (sums == nullptr) {  // zeros added by the pairing do not change the sums
+        int32_t *bs = reinterpret_cast<int32_t *>(ws + pl.a_bytes + pl.f_bytes);
+        if (int rc = glowb200_i8_row_sums(bmat, g.OC, p.K, bs, reinterpret_cast<glowb200_stream_t>(s))) return rc;
+        sums = bs;
+      }
+      return run_gemm_shifted_rows(p, xp, rows, g.C, bmat, sums, s);
+    }
+  }
+#endif
   const int8_t *a = in;
   if (pl.need_im2col) {
     int8_t *abuf = reinterpret_cast<int8_t *>(ws);

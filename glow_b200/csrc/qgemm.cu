@@ -295,7 +295,12 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           uint8_t *a_dst = smem + s * S::kStageBytes;
           uint8_t *b_dst = a_dst + S::kABytes;
           mbar_expect_tx(&full[s], S::kStageBytes);
-          tma_load_2d(a_dst, &map_a, kb * kBlockK, m0, &full[s]);
+          if (p.conv_entries > 0) {
+            const int e = kb / p.conv_cpb;
+            tma_load_2d(a_dst, &map_a, (kb - e * p.conv_cpb) * kBlockK, m0 + p.conv_row_off[e], &full[s]);
+          } else {
+            tma_load_2d(a_dst, &map_a, kb * kBlockK, m0, &full[s]);
+          }
           tma_load_2d(b_dst, &map_b, kb * kBlockK, n0, &full[s]);
         }
       }
@@ -404,6 +409,13 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const int32_t a_sum = (p.a_row_sums && row < p.M) ? p.a_row_sums[row] : 0;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kAccCols;
       int8_t *out_row = p.out + (size_t)row * p.N + n0;
+      bool row_ok = row < p.M;
+      if (p.conv_entries > 0) {  // padded pixel -> (image, oh, ow); the halo rows are dropped
+        const int img = row / p.conv_hpwp, rem = row - img * p.conv_hpwp;
+        const int oh = rem / p.conv_wp, ow = rem - oh * p.conv_wp;
+        row_ok = row_ok && oh < p.conv_oh && ow < p.conv_ow;
+        out_row = p.out + ((size_t)(img * p.conv_oh + oh) * p.conv_ow + ow) * p.N + n0;
+      }
       const int32_t relu_floor = p.act_type == 1 ? p.out_offset : INT32_MIN;
 #pragma unroll 1
       for (int c0 = col_group * kGroupCols; c0 < (col_group + 1) * kGroupCols; c0 += kChunk) {
@@ -450,7 +462,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           packed[i4] = clip_pack4(r[0], r[1], r[2], r[3]);
         }
         GEMM_TRACE(8, lt == 0 && et == 0 && c0 == 0 && packed[0] != 0x12345678u);
-        if (row < p.M) {
+        if (row_ok) {
           if (vec_ok && n0 + c0 + kChunk <= p.N) {
 #pragma unroll
             for (int v4 = 0; v4 < kChunk / 16; v4++)
@@ -567,11 +579,14 @@ EncodeTiledFn encode_tiled_fn() {
 
 // int8 [rows, K] row-major -> 2-D map with a {128 bytes of K, box_rows} box, 128-byte swizzle;
 // out-of-range elements read as zero.
-int make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows) {
+// [rows, extent] bytes with `pitch` bytes between rows (pitch < extent: rows overlap, a sliding window)
+int make_map(CUtensorMap *map, const void *base, int rows, int extent, int box_rows, int pitch);
+int make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows) { return make_map(map, base, rows, K, box_rows, K); }
+int make_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows, int pitch) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return set_error(GLOWB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch};
   cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
@@ -605,6 +620,30 @@ bool ptr16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 // Runs out = requant(A[M,K] x B[N,K]^T ...) choosing the tensor-core or the any-shape kernel.
 // `ws` holds b_row_sums (when not supplied) and a_row_sums (when needed).
 }  // namespace
+
+int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int C, const int8_t *b,
+                          const int32_t *b_row_sums, cudaStream_t s) {
+  GLOWB200_REQUIRE(rows > 0 && rows < (1ll << 31) && (C == 64 || C % 128 == 0) && p.K % kBlockK == 0 && p.conv_entries > 0 &&
+                       p.conv_entries <= 32 && ptr16(padded) && ptr16(b) && b_row_sums != nullptr,
+                   "shifted-rows convolution: unsupported shape");
+  p.M = (int)rows;
+  p.b_row_sums = b_row_sums;
+  p.a_row_sums = nullptr;
+  if (p.k_corr == 0) p.k_corr = p.K;
+  CUtensorMap ma, mb;
+  // C = 64: a 128-byte window over two neighbouring pixels, sliding by one pixel per row
+  if (int rc = make_map(&ma, padded, (int)rows, C == 64 ? 128 : C, kBlockM, C)) return rc;
+  if (p.N > 64 && (((p.N + 127) / 128) & 1)) {
+    if (int rc = make_map(&mb, b, p.N, p.K, 128)) return rc;
+    return launch_tile_kernel<128, 6>(ma, mb, p, s);
+  }
+  if (p.N > 64) {
+    if (int rc = make_map(&mb, b, p.N, p.K, 256)) return rc;
+    return launch_tile_kernel<256, 4>(ma, mb, p, s);
+  }
+  if (int rc = make_map(&mb, b, p.N, p.K, 64)) return rc;
+  return launch_tile_kernel<64, 6>(ma, mb, p, s);
+}
 
 int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_row_sums_in, bool b_offsets_zero,
              int force_any, void *ws, size_t ws_bytes, cudaStream_t s) {

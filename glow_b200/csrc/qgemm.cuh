@@ -23,6 +23,15 @@ struct GemmParams {
   // per-tensor layers: one set of scalars for every column instead of the arrays above
   int uniform;
   int bias_is_i8;
+  // Shifted-rows convolution (conv_entries > 0; stride 1, no dilation, no groups): the left operand
+  // is the padded NHWC input seen as a matrix [padded pixels, C].  Output pixel (n, oh, ow) is row
+  // q = (n * Hp + oh) * Wp + ow of the product, and filter tap (kh, kw) reads row q + kh * Wp + kw:
+  // k-block kb of a tile starting at row m0 loads rows m0 + conv_row_off[kb / conv_cpb], 128-byte
+  // channel block kb % conv_cpb.  Rows whose (oh, ow) fall outside the output are computed and
+  // dropped; the result is stored densely as [n, oh, ow, N].
+  int conv_entries, conv_cpb;
+  int conv_row_off[32];
+  int conv_hpwp, conv_wp, conv_oh, conv_ow;
   int32_t u_b_offset, u_bias_pre, u_bias_post, u_bias_scale, u_out_pre, u_out_post, u_out_scale;
 };
 
@@ -55,6 +64,12 @@ __device__ __forceinline__ int32_t activation_i32(int32_t x, const GemmParams &p
 // i8_gemm_core_workspace_bytes(M, N) bytes.  b_row_sums_in may be nullptr (computed here).
 int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_row_sums_in, bool b_offsets_zero,
              int force_any, void *ws, size_t ws_bytes, cudaStream_t s);
+
+// The shifted-rows convolution on the same kernel: `padded` holds `rows` padded pixels of `C` bytes
+// (plus 128 readable bytes behind them), p.conv_* describe the taps, p.M = rows, p.K = bytes of a
+// row of b (a multiple of 128).  Weight offsets must all be zero (no input row sums).
+int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int C, const int8_t *b,
+                          const int32_t *b_row_sums, cudaStream_t s);
 
 inline size_t i8_gemm_core_workspace_bytes(int64_t M, int64_t N) {
   return align_up((size_t)N * 4, 256) + align_up((size_t)M * 4, 256);

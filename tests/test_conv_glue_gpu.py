@@ -27,6 +27,13 @@ CONV_CASES = [
     (2, 64, 48, 3, 32, (7, 7), (2, 2), (3, 3, 3, 3), 1, (1, 1), 1),      # stem shape: rows staged in shared memory
     (1, 17, 13, 5, 12, (3, 5), (1, 2), (1, 2, 1, 2), 1, (1, 1), 0),      # odd channel count, rectangular window
     (1, 12, 12, 12, 16, (3, 3), (1, 1), (2, 2, 2, 2), 1, (2, 2), 0),     # dilation with C not a multiple of 16
+    # stride-1 windows over 64 / 128k channels with symmetric filters: the shifted-rows path (no im2col)
+    (2, 9, 13, 128, 96, (3, 3), (1, 1), (1, 1, 1, 1), 1, (1, 1), 1),
+    (1, 10, 7, 256, 300, (3, 3), (1, 1), (1, 1, 1, 1), 1, (1, 1), 0),
+    (3, 8, 8, 64, 64, (5, 5), (1, 1), (2, 2, 2, 2), 1, (1, 1), 1),       # 5 taps per row: an odd tap without partner
+    (2, 11, 6, 64, 40, (2, 2), (1, 1), (0, 0, 0, 0), 1, (1, 1), 0),      # even window, no padding
+    (1, 6, 9, 128, 32, (1, 3), (1, 1), (0, 1, 0, 1), 1, (1, 1), 2),      # one-row window, clip
+    (2, 7, 7, 64, 16, (3, 3), (1, 1), (2, 0, 1, 2), 1, (1, 1), 0),       # unequal pads
 ]
 
 
