@@ -88,6 +88,10 @@ SIGNATURES = {
     "glowb200_device_manager_add_network": (_int, [_vp, _vp]),
     "glowb200_device_manager_evict_network": (_int, [_vp, C.c_char_p]),
     "glowb200_device_manager_run_function": (_int, [_vp, C.c_char_p, _vp, _vp, _vp, _int]),
+    "glowb200_device_manager_run_function_io": (_int, [_vp, C.c_char_p, _vp, _vp, _vp, _vp, _int]),
+    "glowb200_device_manager_placeholder_address": (_int, [_vp, C.c_char_p, C.c_char_p, _vp, _vp]),
+    "glowb200_device_manager_transfer_static_placeholder": (_int, [_vp, C.c_char_p, C.c_char_p, _vp, _sz]),
+    "glowb200_device_manager_run_function_resident": (_int, [_vp, C.c_char_p]),
     "glowb200_device_manager_maximum_memory": (C.c_uint64, [_vp]),
     "glowb200_device_manager_available_memory": (C.c_uint64, [_vp]),
     "glowb200_device_manager_is_memory_available": (_int, [_vp, C.c_uint64]),

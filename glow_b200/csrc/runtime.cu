@@ -466,6 +466,68 @@ int execute(glowb200_device_manager *dm, LoadedNetwork &n) {
 // shorter than the placeholder (a partial tensor, supportsPartialTensors): the rest is zeroed.
 extern "C" int glowb200_device_manager_run_function(glowb200_device_manager *dm, const char *name, const char *const *placeholder_names,
                                                     void *const *host_buffers, const size_t *buffer_bytes, int num_bindings) {
+  return glowb200_device_manager_run_function_io(dm, name, placeholder_names, host_buffers, buffer_bytes, nullptr, num_bindings);
+}
+
+namespace {
+// Finishes a request: the status word, the stream, the mapping of what went wrong.
+int finish_request(glowb200_device_manager *dm, const char *name) {
+  int32_t status = 0;
+  cudaMemcpyAsync(&status, dm->status_dev, 4, cudaMemcpyDeviceToHost, dm->stream);
+  cudaMemsetAsync(dm->status_dev, 0, 4, dm->stream);
+  const cudaError_t e = cudaStreamSynchronize(dm->stream);
+  if (e != cudaSuccess) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "device error while running %s: %s", name, cudaGetErrorString(e));
+  if (status & GLOWB200_STATUS_WAIT_TIMEOUT) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "a device-side wait gave up while running %s", name);
+  if (status) return set_error(GLOWB200_RUNTIME_ERROR, "invalid sparse input to %s (status bits 0x%x: index out of range 1, lengths overrun 2, negative length 4, bad offsets 8)", name, status);
+  return GLOWB200_OK;
+}
+}  // namespace
+
+// Device-resident tensors and static placeholders (DeviceManager::transferToDevice /
+// transferFromDevice / transferStaticPlaceholderToDevice, include/glow/Backends/DeviceManager.h:
+// 163-231): where a placeholder of a loaded network lives on the device.
+extern "C" int glowb200_device_manager_placeholder_address(glowb200_device_manager *dm, const char *name, const char *placeholder,
+                                                           void **device_ptr, size_t *bytes) {
+  if (!dm || !name || !placeholder || !device_ptr) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
+  std::lock_guard<std::mutex> g(dm->lock);
+  auto it = dm->networks.find(name);
+  if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Function %s not found", name);
+  glowb200_function *f = it->second.fn;
+  auto s = f->by_name.find(placeholder);
+  if (s == f->by_name.end() || f->symbols[s->second].kind != kPlaceholder)
+    return set_error(GLOWB200_RUNTIME_ERROR, "%s is not a placeholder of %s", placeholder, name);
+  *device_ptr = it->second.slab[kPlaceholder] + f->symbols[s->second].offset;
+  if (bytes) *bytes = f->symbols[s->second].bytes;
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_device_manager_transfer_static_placeholder(glowb200_device_manager *dm, const char *name,
+                                                                   const char *placeholder, const void *host, size_t bytes) {
+  void *d = nullptr;
+  size_t cap = 0;
+  if (int rc = glowb200_device_manager_placeholder_address(dm, name, placeholder, &d, &cap)) return rc;
+  if (!host || bytes > cap) return set_error(GLOWB200_RUNTIME_ERROR, "static placeholder %s: NULL buffer or more bytes than the placeholder holds", placeholder);
+  std::lock_guard<std::mutex> g(dm->lock);
+  cudaSetDevice(dm->device);
+  if (cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, dm->stream) != cudaSuccess || cudaStreamSynchronize(dm->stream) != cudaSuccess)
+    return set_error(GLOWB200_RUNTIME_ERROR, "host-to-device copy of %s failed", placeholder);
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_device_manager_run_function_resident(glowb200_device_manager *dm, const char *name) {
+  if (!dm || !name) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
+  std::lock_guard<std::mutex> g(dm->lock);
+  if (!dm->running) return set_error(GLOWB200_RUNTIME_ERROR, "device manager is not initialised");
+  auto it = dm->networks.find(name);
+  if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Function %s not found", name);
+  cudaSetDevice(dm->device);
+  if (int rc = execute(dm, it->second)) return rc;
+  return finish_request(dm, name);
+}
+
+extern "C" int glowb200_device_manager_run_function_io(glowb200_device_manager *dm, const char *name, const char *const *placeholder_names,
+                                                       void *const *host_buffers, const size_t *buffer_bytes, const int *directions,
+                                                       int num_bindings) {
   if (!dm || !name) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
   std::lock_guard<std::mutex> g(dm->lock);
   if (!dm->running) return set_error(GLOWB200_RUNTIME_ERROR, "device manager is not initialised");
@@ -483,6 +545,7 @@ extern "C" int glowb200_device_manager_run_function(glowb200_device_manager *dm,
     const Symbol &sym = f->symbols[ids[b]];
     if (buffer_bytes[b] > sym.bytes) return set_error(GLOWB200_RUNTIME_ERROR, "binding of %s is larger than the placeholder", sym.name.c_str());
     uint8_t *d = n.slab[kPlaceholder] + sym.offset;
+    if (directions && !(directions[b] & GLOWB200_BINDING_INPUT)) continue;  // an output: nothing to copy in
     bool ok = cudaMemcpyAsync(d, host_buffers[b], buffer_bytes[b], cudaMemcpyHostToDevice, dm->stream) == cudaSuccess;
     if (ok && buffer_bytes[b] < sym.bytes) ok = cudaMemsetAsync(d + buffer_bytes[b], 0, sym.bytes - buffer_bytes[b], dm->stream) == cudaSuccess;
     if (!ok) return set_error(GLOWB200_RUNTIME_ERROR, "host-to-device copy of %s failed", sym.name.c_str());
@@ -490,15 +553,9 @@ extern "C" int glowb200_device_manager_run_function(glowb200_device_manager *dm,
   if (int rc = execute(dm, n)) return rc;
   for (int b = 0; b < num_bindings; b++) {
     const Symbol &sym = f->symbols[ids[b]];
+    if (directions && !(directions[b] & GLOWB200_BINDING_OUTPUT)) continue;  // an input: nothing to copy back
     if (cudaMemcpyAsync(host_buffers[b], n.slab[kPlaceholder] + sym.offset, buffer_bytes[b], cudaMemcpyDeviceToHost, dm->stream) != cudaSuccess)
       return set_error(GLOWB200_RUNTIME_ERROR, "device-to-host copy of %s failed", sym.name.c_str());
   }
-  int32_t status = 0;
-  cudaMemcpyAsync(&status, dm->status_dev, 4, cudaMemcpyDeviceToHost, dm->stream);
-  cudaMemsetAsync(dm->status_dev, 0, 4, dm->stream);
-  const cudaError_t e = cudaStreamSynchronize(dm->stream);
-  if (e != cudaSuccess) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "device error while running %s: %s", name, cudaGetErrorString(e));
-  if (status & GLOWB200_STATUS_WAIT_TIMEOUT) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "a device-side wait gave up while running %s", name);
-  if (status) return set_error(GLOWB200_RUNTIME_ERROR, "invalid sparse input to %s (status bits 0x%x: index out of range 1, lengths overrun 2, negative length 4, bad offsets 8)", name, status);
-  return GLOWB200_OK;
+  return finish_request(dm, name);
 }

@@ -134,8 +134,9 @@ class DeviceManager:
         _check(_lib.lib().glowb200_device_manager_evict_network(self.h, name.encode()))
         self._functions.pop(name, None)
 
-    def run_function(self, name, bindings):
-        """bindings: dict placeholder name -> numpy array (inputs are read, every array is written back)."""
+    def run_function(self, name, bindings, outputs=None):
+        """bindings: dict placeholder name -> numpy array.  outputs=None: every array is copied in
+        and written back; else the names in `outputs` are copied out only, the others in only."""
         names = list(bindings)
         arrs = [bindings[k] for k in names]
         for a in arrs:
@@ -144,7 +145,28 @@ class DeviceManager:
         cn = (C.c_char_p * len(names))(*[k.encode() for k in names])
         cb = (C.c_void_p * len(names))(*[a.ctypes.data for a in arrs])
         cs = (C.c_size_t * len(names))(*[a.nbytes for a in arrs])
-        _check(_lib.lib().glowb200_device_manager_run_function(self.h, name.encode(), cn, cb, cs, len(names)))
+        if outputs is None:
+            _check(_lib.lib().glowb200_device_manager_run_function(self.h, name.encode(), cn, cb, cs, len(names)))
+        else:
+            cd = (C.c_int * len(names))(*[2 if k in outputs else 1 for k in names])
+            _check(_lib.lib().glowb200_device_manager_run_function_io(self.h, name.encode(), cn, cb, cs, cd, len(names)))
+
+    def placeholder_address(self, name, placeholder):
+        """(device address, bytes) of a placeholder of a loaded network (device-resident tensors)."""
+        ptr, n = C.c_void_p(), C.c_size_t()
+        _check(_lib.lib().glowb200_device_manager_placeholder_address(self.h, name.encode(), placeholder.encode(),
+                                                                      C.byref(ptr), C.byref(n)))
+        return int(ptr.value), int(n.value)
+
+    def transfer_static_placeholder(self, name, placeholder, array):
+        """One host-to-device copy of a placeholder that stays put (an embedding table marked static)."""
+        a = np.ascontiguousarray(array)
+        _check(_lib.lib().glowb200_device_manager_transfer_static_placeholder(self.h, name.encode(), placeholder.encode(),
+                                                                              C.c_void_p(a.ctypes.data), a.nbytes))
+
+    def run_function_resident(self, name):
+        """Runs the network on its placeholders as they are in device memory: no copies."""
+        _check(_lib.lib().glowb200_device_manager_run_function_resident(self.h, name.encode()))
 
     @property
     def maximum_memory(self):

@@ -497,7 +497,30 @@ int glowb200_device_manager_init(glowb200_device_manager *dm);
 int glowb200_device_manager_add_network(glowb200_device_manager *dm, glowb200_function *f);
 int glowb200_device_manager_evict_network(glowb200_device_manager *dm, const char *name);
 /* Placeholder names paired with HOST buffers; every bound buffer is copied in before and out
- * after the run; a buffer shorter than its placeholder is a partial tensor (rest zeroed). */
+ * after the run; a buffer shorter than its placeholder is a partial tensor (rest zeroed).
+ * The _io form takes a direction per binding (GLOWB200_BINDING_INPUT: copied in only, _OUTPUT: copied
+ * out only, both bits: both ways; directions NULL = both for all) -- the input / output marks of
+ * Glow's symbol table (include/glow/Backend/BackendUtils.h:38-60). */
+#define GLOWB200_BINDING_INPUT 1
+#define GLOWB200_BINDING_OUTPUT 2
+int glowb200_device_manager_run_function_io(glowb200_device_manager *dm, const char *name,
+                                            const char *const *placeholder_names,
+                                            void *const *host_buffers, const size_t *buffer_bytes,
+                                            const int *directions, int num_bindings);
+/* Device-resident tensors and static placeholders (DeviceManager::transferToDevice /
+ * transferFromDevice / transferStaticPlaceholderToDevice, include/glow/Backends/DeviceManager.h:
+ * 163-231, and the peer-to-peer hand-off between the partitions of a network): the device address
+ * of a placeholder of a loaded network -- what is written there (by a copy, by another kernel, by a
+ * peer GPU) is what the next run reads, and results can be read from there; _transfer_static_placeholder
+ * copies a host buffer there once (embedding tables marked static); _run_function_resident runs the
+ * network on the placeholders as they are, with no copies. */
+int glowb200_device_manager_placeholder_address(glowb200_device_manager *dm, const char *name,
+                                                const char *placeholder, void **device_ptr,
+                                                size_t *bytes);
+int glowb200_device_manager_transfer_static_placeholder(glowb200_device_manager *dm,
+                                                        const char *name, const char *placeholder,
+                                                        const void *host, size_t bytes);
+int glowb200_device_manager_run_function_resident(glowb200_device_manager *dm, const char *name);
 int glowb200_device_manager_run_function(glowb200_device_manager *dm, const char *name,
                                          const char *const *placeholder_names,
                                          void *const *host_buffers, const size_t *buffer_bytes,

@@ -77,6 +77,20 @@ void B200DeviceManager::freeAllocatedDeviceIOBuffer(void *buffer) {
   if (allocations_.erase(buffer)) cudaFreeHost(buffer);
 }
 
+void B200DeviceManager::transferStaticPlaceholderToDevice(Placeholder *PH, Tensor *T, std::function<void(Error)> resultCB) {
+  // every loaded function that names the placeholder gets the bytes (DeviceManager.h:163-171)
+  workThread_.submit([this, PH, T, resultCB] {
+    Error err = Error::success();
+    for (const auto &func : functions_) {
+      int rc = glowb200_device_manager_transfer_static_placeholder(dm_, func.first.c_str(), PH->getName().str().c_str(),
+                                                                   T->getUnsafePtr(), T->getSizeInBytes());
+      if (rc == GLOWB200_RUNTIME_ERROR) continue;  // this function does not use the placeholder
+      if (rc != GLOWB200_OK) { err = toError(rc); break; }
+    }
+    resultCB(std::move(err));
+  });
+}
+
 void B200DeviceManager::addNetworkImpl(const Module *module, FunctionMapTy functions, ReadyCBTy readyCB) {
   for (const auto &func : functions) {
     if (func.second->getCompileBackendName() != "B200") {

@@ -28,6 +28,8 @@ public:
   /// Pinned host memory for request I/O.
   void *allocateDeviceIOBuffer(dim_t size) override;
   void freeAllocatedDeviceIOBuffer(void *buffer) override;
+  /// Static placeholders (embedding tables) are copied to the device once.
+  void transferStaticPlaceholderToDevice(Placeholder *PH, Tensor *T, std::function<void(Error)> resultCB) override;
 
 protected:
   void addNetworkImpl(const Module *module, FunctionMapTy functions, ReadyCBTy cb) override;

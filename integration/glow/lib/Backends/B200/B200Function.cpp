@@ -141,13 +141,19 @@ Error B200Function::execute(ExecutionContext *context) {
   std::vector<const char *> cnames;
   std::vector<void *> bufs;
   std::vector<size_t> bytes;
+  std::vector<int> dirs;
+  const auto &table = getRuntimeBundle().getSymbolTable();
   for (auto &PH : context->getPlaceholderBindings()->pairs()) {
-    if (!getRuntimeBundle().isPlaceholder(PH.first->getName())) continue;  // helper name illustrative
+    auto it = table.find(PH.first->getName().str());
+    if (it == table.end() || it->second.symbolCategory != glow::runtime::SymbolCategory::Placeholder) continue;
+    if (PH.first->isStatic()) continue;  // moved once by transferStaticPlaceholderToDevice
     names.push_back(PH.first->getName().str());
     bufs.push_back(PH.second.getUnsafePtr());
     bytes.push_back(PH.second.getUnpaddedSizeInBytes());
+    // the input / output marks of the symbol table decide which way a tensor travels
+    dirs.push_back((it->second.input ? GLOWB200_BINDING_INPUT : 0) | (it->second.output ? GLOWB200_BINDING_OUTPUT : 0));
   }
   for (auto &n : names) cnames.push_back(n.c_str());
-  return fromRuntime(glowb200_device_manager_run_function(dm_, F_->getGraph()->getName().str().c_str(), cnames.data(), bufs.data(),
-                                                          bytes.data(), (int)names.size()));
+  return fromRuntime(glowb200_device_manager_run_function_io(dm_, F_->getGraph()->getName().str().c_str(), cnames.data(),
+                                                             bufs.data(), bytes.data(), dirs.data(), (int)names.size()));
 }

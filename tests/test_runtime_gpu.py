@@ -198,3 +198,55 @@ def test_quantized_network_bit_exact(oracle, dm):
     want = oracle.element_dequantize_i8(q, *tq["fc"])
     np.testing.assert_array_equal(out.view(np.uint32), want.view(np.uint32))
     assert len(np.unique(q)) > 5
+
+
+def test_directions_static_and_resident_placeholders(oracle, dm):
+    """Inputs copied in only and outputs out only; a placeholder written once and left on the device
+    (a static placeholder); a run on device-resident placeholders fed and read through their device
+    addresses (what a peer-to-peer hand-off between partitions uses)."""
+    import torch
+    table = workloads.fused_table_u8(4000, 64, 9, 0)
+    S, cap = 64, 64 * 40
+    f = slws_function("drt", table, S, cap)
+    dm.add_network(f)
+    lengths, idx, w = workloads.bags_poisson(S, 20, 0, 40, 4000, 4, 1)
+    want = oracle.frwq_slws_u8_f32(table, w, idx, lengths)
+    wp = np.zeros(cap, np.float32); wp[:w.size] = w
+    ip = np.zeros(cap, np.int64); ip[:idx.size] = idx
+    out = np.full((S, 64), 7.0, np.float32)
+    guard_w, guard_i = wp.copy(), ip.copy()
+    dm.run_function("drt", {"drt_weights": wp, "drt_indices": ip, "drt_lengths": lengths.copy(), "drt_output": out},
+                    outputs={"drt_output"})
+    np.testing.assert_allclose(out, want, rtol=1e-5, atol=1e-5)
+    np.testing.assert_array_equal(wp, guard_w)       # inputs are not written back
+    np.testing.assert_array_equal(ip, guard_i)
+    # static placeholders: weights and indices stay on the device; only lengths travel
+    lengths2 = lengths.copy()
+    lengths2[::2] = 0
+    dm.transfer_static_placeholder("drt", "drt_weights", wp)
+    dm.transfer_static_placeholder("drt", "drt_indices", ip)
+    out2 = np.zeros((S, 64), np.float32)
+    dm.run_function("drt", {"drt_lengths": lengths2, "drt_output": out2}, outputs={"drt_output"})
+    np.testing.assert_allclose(out2, oracle.frwq_slws_u8_f32(table, w, idx, lengths2), rtol=1e-5, atol=1e-5)
+    # device-resident: write the lengths through the placeholder's device address, run without copies,
+    # read the result from its device address
+    addr, nbytes = dm.placeholder_address("drt", "drt_lengths")
+    assert nbytes == S * 4
+    res_addr, res_bytes = dm.placeholder_address("drt", "drt_output")
+    assert res_bytes == S * 64 * 4
+    def view(address, shape, typestr):
+        class Raw:
+            pass
+        raw = Raw()
+        raw.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (address, False), "version": 3}
+        return torch.as_tensor(raw, device="cuda")
+
+    view(addr, (S,), "<i4").copy_(torch.from_numpy(lengths).cuda())     # a device-to-device write
+    torch.cuda.synchronize()
+    dm.run_function_resident("drt")
+    res = view(res_addr, (S, 64), "<f4").clone()
+    np.testing.assert_allclose(res.cpu().numpy(), want, rtol=1e-5, atol=1e-5)
+    with pytest.raises(GlowB200Error):
+        dm.placeholder_address("drt", "drt_data")          # a constant, not a placeholder
+    with pytest.raises(GlowB200Error):
+        dm.run_function_resident("missing")
