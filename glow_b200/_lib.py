@@ -66,6 +66,7 @@ SIGNATURES = {
     "glowb200_element_add_maxsplat_i8": (_int, [_vp, _vp, _vp, _i64] + [_i32] * 10 + [_vp]),
     "glowb200_element_relu_i8": (_int, [_vp, _vp, _i64] + [_i32] * 5 + [_vp]),
     "glowb200_element_maxsplat_i8": (_int, [_vp, _vp, _i64, _i32, _vp]),
+    "glowb200_splat_f": (_int, [_vp, _i64, _f32, _int, _vp]),
     "glowb200_element_rescale_i8": (_int, [_vp, _vp, _i64] + [_i32] * 5 + [_vp]),
     "glowb200_element_quantize_i8": (_int, [_vp, _vp, _i64, _f32, _i32, _vp]),
     "glowb200_element_dequantize_i8": (_int, [_vp, _vp, _i64, _f32, _i32, _vp]),

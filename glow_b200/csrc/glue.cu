@@ -57,6 +57,11 @@ __global__ void __launch_bounds__(kThreads) maxsplat_i8_kernel(int8_t *__restric
     dst[i] = src[i] > splat ? src[i] : splat;
 }
 
+template <typename T>
+__global__ void __launch_bounds__(kThreads) splat_kernel(T *__restrict__ dst, int64_t n, T value) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = value;
+}
+
 // libjit_element_rescale_kernel_i8 (libjit.cpp:3030-3038)
 __global__ void __launch_bounds__(kThreads) rescale_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ src,
                                                               int64_t n, int32_t out_off, int32_t in_off, Triple t) {
@@ -258,6 +263,14 @@ extern "C" int glowb200_element_maxsplat_i8(int8_t *dest, const int8_t *src, int
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
   GLOWB200_REQUIRE(splat >= -128 && splat <= 127, "splat value outside int8");
   maxsplat_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, (int8_t)splat);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_splat_f(void *dest, int64_t n, float value, int dest_is_fp16, glowb200_stream_t stream) {
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest)
+  if (dest_is_fp16) splat_kernel<__half><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(reinterpret_cast<__half *>(dest), n, __float2half_rn(value));
+  else splat_kernel<float><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(reinterpret_cast<float *>(dest), n, value);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }

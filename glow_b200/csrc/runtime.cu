@@ -161,6 +161,17 @@ extern "C" int glowb200_function_add_instruction(glowb200_function *f, int kind,
 //  AVGPOOL     ops {dest, src}  ia {N,H,W,C, OH,OW, KH,KW, SH,SW, PT,PL, in_off, out_off, count_include_pads}  fa {in_scale, out_scale}
 //  TRANSPOSE   ops {dest, src}  ia {ndims, elem_bytes, d0..d3, s0..s3}
 //  COPY        ops {dest, src}  ia {bytes}
+//  ADD_MAXSPLAT ops {dest, lhs, rhs}  ia {n, dest_off, lhs_off, rhs_off, splat}  fa {lhs_scale, rhs_scale, dest_scale}
+//  RELU        ops {dest, src}  ia {n, src_off, dest_off}  fa {src_scale, dest_scale}
+//  RESCALE     ops {dest, src}  ia {n, in_off, out_off}  fa {in_scale, out_scale}
+//  FC_I8       ops {dest, src, weights [K,N], bias}  ia {M, K, N, in_off, w_off, bias_off, out_off}  fa {in_scale, w_scale, bias_scale, out_scale}
+//  MATMUL_I8   ops {dest, lhs, rhs [K,N]}  ia {M, K, N, lhs_off, rhs_off, out_off}  fa {lhs_scale, rhs_scale, out_scale}
+//  SPLAT       ops {dest}  ia {n, is_fp16}  fa {value}
+//  INSERT_TENSOR ops {dest, src}  ia {rows, width_bytes, dest_pitch_bytes, dest_offset_bytes}
+//  PAIRWISE_DOT ops {dest, dense, pooled}  ia {batch, tables, dim, ld_dense, ld_pooled, ld_out, out_is_i8, q_offset}  fa {q_scale}
+//  SLWS_F32    ops {dest, data, weights (-1: unweighted), indices, lengths}  ia {rows, line, segments, num_indices, idx64}
+//  RWQ_SLWS    ops {dest, data, scales, offsets, weights, indices, lengths}  ia {rows, line, segments, num_indices, idx64}
+//  EMBEDDING_BAG ops {dest, data, weights, indices, offsets}  ia {kind, rows, in_line, out_line, num_offsets, num_indices, idx64, has_end_offset, out_fp16, fp16_acc}
 extern "C" int glowb200_function_compile(glowb200_function *f) {
   if (!f || f->compiled) return set_error(GLOWB200_RUNTIME_ERROR, "function is NULL or already compiled");
   size_t ws = 256;
@@ -229,6 +240,58 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
       case GLOWB200_INSTR_MAXPOOL: if (!need(2, 13, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed MAXPOOL", ii); break;
       case GLOWB200_INSTR_TRANSPOSE: if (!need(2, 10, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed TRANSPOSE", ii); break;
       case GLOWB200_INSTR_COPY: if (!need(2, 1, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed COPY", ii); break;
+      case GLOWB200_INSTR_ADD_MAXSPLAT: {
+        if (!need(3, 5, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed ADD_MAXSPLAT", ii);
+        int32_t t[6];
+        glowb200::quantize_scale_32to8(in.fa[0] / in.fa[2], t[0], t[1], t[2]);
+        glowb200::quantize_scale_32to8(in.fa[1] / in.fa[2], t[3], t[4], t[5]);
+        for (int32_t x : t) in.ia.push_back(x);
+        break;
+      }
+      case GLOWB200_INSTR_RELU:
+      case GLOWB200_INSTR_RESCALE: {
+        // LLVMIRGen.cpp:1465-1499, 1630-1698: one triple from srcScale / destScale
+        if (!need(2, 3, 2)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed RELU / RESCALE", ii);
+        int32_t a, b, c;
+        glowb200::quantize_scale_32to8(in.fa[0] / in.fa[1], a, b, c);
+        in.ia.push_back(a); in.ia.push_back(b); in.ia.push_back(c);
+        break;
+      }
+      case GLOWB200_INSTR_FC_I8: {
+        // LLVMIRGen.cpp:2098-2137: bias from biasScale / (inScale * wScale), result from inScale * wScale / outScale
+        if (!need(4, 7, 4)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed FC_I8", ii);
+        const float mm = in.fa[0] * in.fa[1];
+        int32_t t[6];
+        glowb200::quantize_scale_32to8(in.fa[2] / mm, t[0], t[1], t[2]);
+        glowb200::quantize_scale_32to8(mm / in.fa[3], t[3], t[4], t[5]);
+        for (int32_t x : t) in.ia.push_back(x);
+        ws = std::max(ws, glowb200_i8_gemm_workspace_bytes(in.ia[0], in.ia[1], in.ia[2]));
+        break;
+      }
+      case GLOWB200_INSTR_MATMUL_I8: {
+        // LLVMIRGen.cpp:2161-2220: one triple from lhsScale * rhsScale / destScale
+        if (!need(3, 6, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed MATMUL_I8", ii);
+        int32_t a, b, c;
+        glowb200::quantize_scale_32to8(in.fa[0] * in.fa[1] / in.fa[2], a, b, c);
+        in.ia.push_back(a); in.ia.push_back(b); in.ia.push_back(c);
+        ws = std::max(ws, glowb200_i8_gemm_workspace_bytes(in.ia[0], in.ia[1], in.ia[2]));
+        break;
+      }
+      case GLOWB200_INSTR_SPLAT: if (!need(1, 2, 1)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed SPLAT", ii); break;
+      case GLOWB200_INSTR_INSERT_TENSOR: if (!need(2, 4, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed INSERT_TENSOR", ii); break;
+      case GLOWB200_INSTR_PAIRWISE_DOT: if (!need(3, 8, 1)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed PAIRWISE_DOT", ii); break;
+      case GLOWB200_INSTR_SLWS_F32:
+        if (!need(5, 5, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed SLWS_F32", ii);
+        ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[2], 1));
+        break;
+      case GLOWB200_INSTR_RWQ_SLWS:
+        if (!need(7, 5, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed RWQ_SLWS", ii);
+        ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[2], 1));
+        break;
+      case GLOWB200_INSTR_EMBEDDING_BAG:
+        if (!need(5, 10, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed EMBEDDING_BAG", ii);
+        ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[4], 1));
+        break;
       default: return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: unsupported kind %d (isOpSupported would refuse the node)", ii, in.kind);
     }
   }
@@ -444,6 +507,60 @@ int execute(glowb200_device_manager *dm, LoadedNetwork &n) {
       case GLOWB200_INSTR_COPY:
         if (cudaMemcpyAsync(ptr(in.ops[0]), ptr(in.ops[1]), (size_t)a[0], cudaMemcpyDeviceToDevice, dm->stream) != cudaSuccess)
           rc = set_error(GLOWB200_RUNTIME_ERROR, "copy failed");
+        break;
+      case GLOWB200_INSTR_ADD_MAXSPLAT:
+        rc = glowb200_element_add_maxsplat_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
+                                              a[0], (int32_t)a[1], (int32_t)a[2], (int32_t)a[3], (int32_t)a[5], (int32_t)a[6],
+                                              (int32_t)a[7], (int32_t)a[8], (int32_t)a[9], (int32_t)a[10], (int32_t)a[4], st);
+        break;
+      case GLOWB200_INSTR_RELU:
+        rc = glowb200_element_relu_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), a[0], (int32_t)a[1], (int32_t)a[2],
+                                      (int32_t)a[3], (int32_t)a[4], (int32_t)a[5], st);
+        break;
+      case GLOWB200_INSTR_RESCALE:
+        rc = glowb200_element_rescale_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), a[0], (int32_t)a[2], (int32_t)a[1],
+                                         (int32_t)a[3], (int32_t)a[4], (int32_t)a[5], st);
+        break;
+      case GLOWB200_INSTR_FC_I8:
+        rc = glowb200_fc_i8_i32((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
+                                (const int32_t *)ptr(in.ops[3]), a[0], a[1], a[2], (int32_t)a[6], (int32_t)a[3], (int32_t)a[4],
+                                (int32_t)a[5], (int32_t)a[7], (int32_t)a[8], (int32_t)a[9], (int32_t)a[10], (int32_t)a[11],
+                                (int32_t)a[12], nullptr, 0, n.workspace, f->workspace_bytes, dm->status_dev, st);
+        break;
+      case GLOWB200_INSTR_MATMUL_I8:
+        rc = glowb200_matmul_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]), a[0], a[1],
+                                a[2], (int32_t)a[5], (int32_t)a[3], (int32_t)a[4], (int32_t)a[6], (int32_t)a[7], (int32_t)a[8], 0,
+                                n.workspace, f->workspace_bytes, dm->status_dev, st);
+        break;
+      case GLOWB200_INSTR_SPLAT:
+        rc = glowb200_splat_f(ptr(in.ops[0]), a[0], in.fa[0], (int)a[1], st);
+        break;
+      case GLOWB200_INSTR_INSERT_TENSOR:
+        if (cudaMemcpy2DAsync((uint8_t *)ptr(in.ops[0]) + a[3], (size_t)a[2], ptr(in.ops[1]), (size_t)a[1], (size_t)a[1], (size_t)a[0],
+                              cudaMemcpyDeviceToDevice, dm->stream) != cudaSuccess)
+          rc = set_error(GLOWB200_RUNTIME_ERROR, "insert-tensor copy failed");
+        break;
+      case GLOWB200_INSTR_PAIRWISE_DOT:
+        rc = glowb200_pairwise_dot_interaction((const float *)ptr(in.ops[1]), a[3], (const float *)ptr(in.ops[2]), a[4], a[0], a[1], a[2],
+                                               a[6] ? nullptr : (float *)ptr(in.ops[0]), a[6] ? (int8_t *)ptr(in.ops[0]) : nullptr, a[5],
+                                               in.fa[0], (int32_t)a[7], st);
+        break;
+      case GLOWB200_INSTR_SLWS_F32:
+        rc = glowb200_sparse_lengths_weighted_sum_f32((float *)ptr(in.ops[0]), (const float *)ptr(in.ops[1]), a[0],
+                                                      (const float *)ptr(in.ops[2]), ptr(in.ops[3]), (int)a[4],
+                                                      (const int32_t *)ptr(in.ops[4]), a[2], a[3], a[1], n.workspace,
+                                                      f->workspace_bytes, dm->status_dev, st);
+        break;
+      case GLOWB200_INSTR_RWQ_SLWS:
+        rc = glowb200_rowwise_quantized_sparse_lengths_weighted_sum_f32(
+            (float *)ptr(in.ops[0]), (const uint8_t *)ptr(in.ops[1]), (const float *)ptr(in.ops[2]), (const float *)ptr(in.ops[3]), a[0],
+            (const float *)ptr(in.ops[4]), ptr(in.ops[5]), (int)a[4], (const int32_t *)ptr(in.ops[6]), a[2], a[3], a[1], n.workspace,
+            f->workspace_bytes, dm->status_dev, st);
+        break;
+      case GLOWB200_INSTR_EMBEDDING_BAG:
+        rc = glowb200_embedding_bag_byte_rowwise_offsets(ptr(in.ops[0]), ptr(in.ops[1]), (int)a[0], a[1], ptr(in.ops[2]), ptr(in.ops[3]),
+                                                         ptr(in.ops[4]), (int)a[6], a[4], a[5], a[2], a[3], (int)a[7], (int)a[8],
+                                                         (int)a[9], n.workspace, f->workspace_bytes, dm->status_dev, st);
         break;
     }
     if (rc != GLOWB200_OK) {

@@ -14,6 +14,8 @@ from ._lib import GlowB200Error
 
 CONSTANT, PLACEHOLDER, ACTIVATION = 0, 1, 2
 (FRWQ_SLWS, RWQ_FC, CWQ_CONV, ADD, MAXSPLAT, QUANTIZE, DEQUANTIZE, MAXPOOL, AVGPOOL, TRANSPOSE, COPY) = range(1, 12)
+(ADD_MAXSPLAT, RELU, RESCALE, FC_I8, MATMUL_I8, SPLAT, INSERT_TENSOR, PAIRWISE_DOT, SLWS_F32, RWQ_SLWS,
+ EMBEDDING_BAG) = range(12, 23)
 
 RUNTIME_ERROR, OUT_OF_DEVICE_MEMORY, NET_NOT_FOUND, DEVICE_NONRECOVERABLE = 101, 102, 103, 104
 
@@ -107,6 +109,53 @@ class Function:
 
     def copy(self, dest, src, *, nbytes):
         self.instruction(COPY, [dest, src], [nbytes])
+
+    def add_maxsplat(self, dest, lhs, rhs, *, n, lhs_tqp, rhs_tqp, dest_tqp, splat):
+        self.instruction(ADD_MAXSPLAT, [dest, lhs, rhs], [n, dest_tqp[1], lhs_tqp[1], rhs_tqp[1], splat],
+                         [lhs_tqp[0], rhs_tqp[0], dest_tqp[0]])
+
+    def relu(self, dest, src, *, n, src_tqp, dest_tqp):
+        self.instruction(RELU, [dest, src], [n, src_tqp[1], dest_tqp[1]], [src_tqp[0], dest_tqp[0]])
+
+    def rescale(self, dest, src, *, n, in_tqp, out_tqp):
+        self.instruction(RESCALE, [dest, src], [n, in_tqp[1], out_tqp[1]], [in_tqp[0], out_tqp[0]])
+
+    def fully_connected(self, dest, src, weights, bias, *, M, K, N, in_tqp, w_tqp, bias_tqp, out_tqp):
+        """weights: int8 [K, N] (Glow's FullyConnected layout)."""
+        self.instruction(FC_I8, [dest, src, weights, bias], [M, K, N, in_tqp[1], w_tqp[1], bias_tqp[1], out_tqp[1]],
+                         [in_tqp[0], w_tqp[0], bias_tqp[0], out_tqp[0]])
+
+    def matmul(self, dest, lhs, rhs, *, M, K, N, lhs_tqp, rhs_tqp, out_tqp):
+        self.instruction(MATMUL_I8, [dest, lhs, rhs], [M, K, N, lhs_tqp[1], rhs_tqp[1], out_tqp[1]],
+                         [lhs_tqp[0], rhs_tqp[0], out_tqp[0]])
+
+    def splat(self, dest, *, n, value, fp16=False):
+        self.instruction(SPLAT, [dest], [n, int(fp16)], [value])
+
+    def insert_tensor(self, dest, src, *, rows, width_bytes, dest_pitch_bytes, dest_offset_bytes):
+        self.instruction(INSERT_TENSOR, [dest, src], [rows, width_bytes, dest_pitch_bytes, dest_offset_bytes])
+
+    def pairwise_dot(self, dest, dense, pooled, *, batch, tables, dim, ld_out=None, quant=None):
+        width = dim + (tables + 1) * tables // 2
+        self.instruction(PAIRWISE_DOT, [dest, dense, pooled],
+                         [batch, tables, dim, dim, tables * dim, width if ld_out is None else ld_out, int(quant is not None),
+                          quant[1] if quant else 0], [quant[0] if quant else 1.0])
+
+    def sparse_lengths_sum(self, dest, data, weights, indices, lengths, *, rows, line, segments, num_indices, idx64=True):
+        """weights None: SparseLengthsSum."""
+        self.instruction(SLWS_F32, [dest, data, -1 if weights is None else weights, indices, lengths],
+                         [rows, line, segments, num_indices, int(idx64)])
+
+    def rowwise_quantized_slws(self, dest, data, scales, offsets, weights, indices, lengths, *, rows, line, segments,
+                               num_indices, idx64=True):
+        self.instruction(RWQ_SLWS, [dest, data, scales, offsets, weights, indices, lengths],
+                         [rows, line, segments, num_indices, int(idx64)])
+
+    def embedding_bag(self, dest, data, weights, indices, offsets, *, kind, rows, in_line, out_line, num_offsets, num_indices,
+                      idx64=True, has_end_offset=True, out_fp16=False, fp16_acc=False):
+        self.instruction(EMBEDDING_BAG, [dest, data, weights, indices, offsets],
+                         [kind, rows, in_line, out_line, num_offsets, num_indices, int(idx64), int(has_end_offset),
+                          int(out_fp16), int(fp16_acc)])
 
     def compile(self):
         _check(_lib.lib().glowb200_function_compile(self.h))

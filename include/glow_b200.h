@@ -396,6 +396,10 @@ int glowb200_element_relu_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t
  * 39-44), what the CPU backend turns a quantized Relu into (lib/Backends/CPU/Transforms.cpp:83-113). */
 int glowb200_element_maxsplat_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t splat,
                                  glowb200_stream_t stream);
+/* Splat: every element of dest [n] set to `value`, as fp32 or (dest_is_fp16) rounded to fp16
+ * (libjit_splat_kernel_f, libjit.cpp; the ones that weight a lowered SparseLengthsSum,
+ * lib/Optimizer/Lower/Lower.cpp:1590-1606). */
+int glowb200_splat_f(void *dest, int64_t n, float value, int dest_is_fp16, glowb200_stream_t stream);
 /* RescaleQuantized int8: libjit_element_rescale_kernel_i8 (libjit.cpp:3030-3038). */
 int glowb200_element_rescale_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t out_offset,
                                 int32_t in_offset, int32_t pre, int32_t post, int32_t scale,
@@ -476,6 +480,17 @@ int glowb200_peer_buffer_destroy(void *device_ptr);
 #define GLOWB200_INSTR_AVGPOOL 9
 #define GLOWB200_INSTR_TRANSPOSE 10
 #define GLOWB200_INSTR_COPY 11
+#define GLOWB200_INSTR_ADD_MAXSPLAT 12   /* ElementAdd followed by the max-with-immediate of a Relu */
+#define GLOWB200_INSTR_RELU 13
+#define GLOWB200_INSTR_RESCALE 14
+#define GLOWB200_INSTR_FC_I8 15          /* FullyConnected, per-tensor quantized */
+#define GLOWB200_INSTR_MATMUL_I8 16
+#define GLOWB200_INSTR_SPLAT 17          /* fp32 / fp16 fill (the weights of a lowered SparseLengthsSum) */
+#define GLOWB200_INSTR_INSERT_TENSOR 18  /* a [rows, width] block into a wider tensor (lowered Concat) */
+#define GLOWB200_INSTR_PAIRWISE_DOT 19
+#define GLOWB200_INSTR_SLWS_F32 20       /* SparseLengths(Weighted)Sum over an fp32 table */
+#define GLOWB200_INSTR_RWQ_SLWS 21       /* RowwiseQuantizedSparseLengthsWeightedSum */
+#define GLOWB200_INSTR_EMBEDDING_BAG 22  /* EmbeddingBagByteRowwiseOffsets */
 
 typedef struct glowb200_function glowb200_function;
 typedef struct glowb200_device_manager glowb200_device_manager;

@@ -53,6 +53,10 @@ bool B200Backend::isOpSupported(const NodeInfo &NI) const {
   case Kinded::Kind::AvgPoolNodeKind:
   case Kinded::Kind::RescaleQuantizedNodeKind:
     return NI.allInputsAndOutputsHaveSameElemKind({ElemKind::Int8QTy}, /*ignoreIn*/ {FullyConnectedNode::BiasIdx});
+  case Kinded::Kind::SparseLengthsWeightedSumNodeKind:
+    return NI.getInElemTy(SparseLengthsWeightedSumNode::DataIdx) == ElemKind::FloatTy;
+  case Kinded::Kind::SplatNodeKind:
+  case Kinded::Kind::InsertTensorNodeKind:
   case Kinded::Kind::QuantizeNodeKind:
   case Kinded::Kind::DequantizeNodeKind:
   case Kinded::Kind::TransposeNodeKind:

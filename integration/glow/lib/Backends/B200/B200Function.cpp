@@ -124,8 +124,76 @@ Error B200Function::translate(const Module *module) {
       RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_COPY, ops, 2, ia, 1, nullptr, 0)));
       break;
     }
-    // MaxPool / AvgPool / Transpose / Relu (as max with the quantized zero) follow the same pattern
-    // with GLOWB200_INSTR_MAXPOOL / _AVGPOOL / _TRANSPOSE / _MAXSPLAT.
+    case Kinded::Kind::FullyConnectedInstKind: {
+      auto *N = llvm::cast<FullyConnectedInst>(&I);
+      const int32_t ops[4] = {S(N->getDest()), S(N->getSrc()), S(N->getWeights()), S(N->getBias())};
+      const Type *in = N->getSrc()->getType(), *w = N->getWeights()->getType(), *b = N->getBias()->getType(), *o = N->getDest()->getType();
+      const int64_t ia[7] = {(int64_t)in->dims()[0], (int64_t)in->dims()[1], (int64_t)w->dims()[1], in->getOffset(), w->getOffset(),
+                             b->getOffset(), o->getOffset()};
+      const float fa[4] = {in->getScale(), w->getScale(), b->getScale(), o->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_FC_I8, ops, 4, ia, 7, fa, 4)));
+      break;
+    }
+    case Kinded::Kind::MatMulInstKind: {
+      auto *N = llvm::cast<MatMulInst>(&I);
+      const int32_t ops[3] = {S(N->getDest()), S(N->getLHS()), S(N->getRHS())};
+      const Type *l = N->getLHS()->getType(), *r = N->getRHS()->getType(), *o = N->getDest()->getType();
+      const int64_t ia[6] = {(int64_t)l->dims()[0], (int64_t)l->dims()[1], (int64_t)r->dims()[1], l->getOffset(), r->getOffset(), o->getOffset()};
+      const float fa[3] = {l->getScale(), r->getScale(), o->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_MATMUL_I8, ops, 3, ia, 6, fa, 3)));
+      break;
+    }
+    case Kinded::Kind::ReluInstKind:
+    case Kinded::Kind::RescaleQuantizedInstKind: {
+      const bool relu = I.getKind() == Kinded::Kind::ReluInstKind;
+      const Value *dst = I.getOperand(0).first, *src = I.getOperand(1).first;
+      const int32_t ops[2] = {S(dst), S(src)};
+      const int64_t ia[3] = {(int64_t)dst->size(), src->getType()->getOffset(), dst->getType()->getOffset()};
+      const float fa[2] = {src->getType()->getScale(), dst->getType()->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, relu ? GLOWB200_INSTR_RELU : GLOWB200_INSTR_RESCALE, ops, 2, ia, 3, fa, 2)));
+      break;
+    }
+    case Kinded::Kind::SplatInstKind: {
+      auto *N = llvm::cast<SplatInst>(&I);
+      const int32_t ops[1] = {S(N->getDest())};
+      const int64_t ia[2] = {(int64_t)N->getDest()->size(), N->getDest()->getElementType() == ElemKind::Float16Ty};
+      const float fa[1] = {N->getValue()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_SPLAT, ops, 1, ia, 2, fa, 1)));
+      break;
+    }
+    case Kinded::Kind::SparseLengthsWeightedSumInstKind: {
+      auto *N = llvm::cast<SparseLengthsWeightedSumInst>(&I);
+      const int32_t ops[5] = {S(N->getDest()), S(N->getData()), S(N->getWeights()), S(N->getIndices()), S(N->getLengths())};
+      const int64_t ia[5] = {(int64_t)N->getData()->dims()[0], (int64_t)N->getDest()->dims()[1], (int64_t)N->getLengths()->dims()[0],
+                             (int64_t)N->getIndices()->dims()[0], N->getIndices()->getElementType() == ElemKind::Int64ITy};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_SLWS_F32, ops, 5, ia, 5, nullptr, 0)));
+      break;
+    }
+    case Kinded::Kind::EmbeddingBagByteRowwiseOffsetsInstKind: {
+      auto *N = llvm::cast<EmbeddingBagByteRowwiseOffsetsInst>(&I);
+      auto *D = N->getData();
+      const int32_t ops[5] = {S(N->getDest()), S(D), S(N->getWeights()), S(N->getIndices()), S(N->getOffsets())};
+      const int64_t ia[10] = {fusedKind(D->getElementType()), (int64_t)D->dims()[0], (int64_t)D->dims()[1], (int64_t)N->getDest()->dims()[1],
+                              (int64_t)N->getOffsets()->dims()[0], (int64_t)N->getIndices()->dims()[0],
+                              N->getIndices()->getElementType() == ElemKind::Int64ITy, N->getHasEndOffset(),
+                              N->getDest()->getElementType() == ElemKind::Float16Ty, N->getUseFP16Accumulation()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_EMBEDDING_BAG, ops, 5, ia, 10, nullptr, 0)));
+      break;
+    }
+    case Kinded::Kind::InsertTensorInstKind: {
+      // the lowered Concat of pooled vectors: a [rows, width] block into a wider row-major tensor
+      auto *N = llvm::cast<InsertTensorInst>(&I);
+      const auto dd = N->getDest()->dims(), sd = N->getSrc()->dims();
+      const size_t eb = N->getDest()->getType()->getElementSize();
+      if (dd.size() != 2 || N->getCount() != 1 || N->getOffsets()[0] != 0)
+        return MAKE_ERR(ErrorValue::ErrorCode::COMPILE_UNSUPPORTED_NODE_AFTER_OPTIMIZE, "B200: only column-wise InsertTensor is supported");
+      const int32_t ops[2] = {S(N->getDest()), S(N->getSrc())};
+      const int64_t ia[4] = {(int64_t)sd[0], (int64_t)(sd[1] * eb), (int64_t)(dd[1] * eb), (int64_t)(N->getOffsets()[1] * eb)};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_INSERT_TENSOR, ops, 2, ia, 4, nullptr, 0)));
+      break;
+    }
+    // MaxPool / AvgPool / Transpose / CPUMaxSplat-style max-with-immediate follow the same pattern
+    // with GLOWB200_INSTR_MAXPOOL / _AVGPOOL / _TRANSPOSE / _MAXSPLAT (attribute lists in runtime.cu).
     default:
       return MAKE_ERR(ErrorValue::ErrorCode::COMPILE_UNSUPPORTED_NODE_AFTER_OPTIMIZE,
                       "B200: instruction " + std::string(I.getKindName()) + " is not supported");

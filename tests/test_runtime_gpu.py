@@ -250,3 +250,82 @@ def test_directions_static_and_resident_placeholders(oracle, dm):
         dm.placeholder_address("drt", "drt_data")          # a constant, not a placeholder
     with pytest.raises(GlowB200Error):
         dm.run_function_resident("missing")
+
+
+def test_recommendation_style_network_bit_exact(oracle, dm):
+    """A small recommendation model through the runtime, built from the instructions the lowered
+    graph holds: Splat (the ones of a lowered SparseLengthsSum) -> fused gather-pool, an fp32
+    SparseLengthsSum and a rowwise-quantized one, InsertTensor (lowered Concat) into [B, 3, D],
+    Quantize -> per-tensor FullyConnected -> Relu -> Dequantize for the dense features, pairwise dots
+    with Quantize fused, Rescale, MatMul, Dequantize.  Checked stage by stage against the oracle."""
+    rng = np.random.default_rng(21)
+    B, D, rows, cap = 24, 16, 500, 24 * 12
+    t8 = workloads.fused_table_u8(rows, D, 3, 0)
+    tf = rng.normal(0, 1, (rows, D)).astype(np.float32)
+    tq8 = rng.integers(0, 256, (rows, D), dtype=np.uint8)
+    sc8, of8 = rng.uniform(0.001, 0.01, rows).astype(np.float32), rng.uniform(-1, 1, rows).astype(np.float32)
+    lengths, idx, w = workloads.bags_poisson(B, 6, 0, 12, rows, 8, 1)
+    n = int(lengths.sum())
+    din = 20
+    wfc = rng.integers(-127, 128, (din, D)).astype(np.int8)          # [K, N]
+    bfc = rng.integers(-500, 500, D).astype(np.int32)
+    tq = dict(x=(0.04, 3), w=(0.01, 0), b=(0.0004, 0), h=(0.08, -20), r=(0.08, -128), inter=(0.9, -10), rs=(1.3, 4),
+              m=(0.02, 1), mm=(2.5, -3))
+    wm = rng.integers(-127, 128, (D + 6, 5)).astype(np.int8)          # MatMul right-hand side [K, N]
+    width = D + 4 * 3 // 2
+
+    f = runtime.Function("rec")
+    c8, cf, cq = f.constant("t8", t8), f.constant("tf", tf), f.constant("tq8", tq8)
+    csc, cof = f.constant("sc8", sc8), f.constant("of8", of8)
+    p_idx, p_len, p_w = f.placeholder("idx", cap * 8), f.placeholder("len", B * 4), f.placeholder("w", cap * 4)
+    p_x, p_out = f.placeholder("x", B * din * 4), f.placeholder("out", B * 5 * 4)
+    p_pooled = f.placeholder("pooled", B * 3 * D * 4)                  # kept as a placeholder so the test can read it
+    a_ones, a_e0, a_e1, a_e2 = (f.activation(k, s) for k, s in (("ones", cap * 4), ("e0", B * D * 4), ("e1", B * D * 4), ("e2", B * D * 4)))
+    a_xq, a_h, a_hr, a_hf = f.activation("xq", B * din), f.activation("h", B * D), f.activation("hr", B * D), f.activation("hf", B * D * 4)
+    a_i, a_ir, a_m = f.activation("inter", B * width), f.activation("inter_r", B * width), f.activation("m", B * 5)
+    f.splat(a_ones, n=cap, value=1.0)
+    f.frwq_slws(a_e0, c8, a_ones, p_idx, p_len, kind=ops.UINT8_FUSED, rows=rows, in_line=D + 8, out_line=D, segments=B, num_indices=cap)
+    f.sparse_lengths_sum(a_e1, cf, None, p_idx, p_len, rows=rows, line=D, segments=B, num_indices=cap)
+    f.rowwise_quantized_slws(a_e2, cq, csc, cof, p_w, p_idx, p_len, rows=rows, line=D, segments=B, num_indices=cap)
+    for j, a in enumerate((a_e0, a_e1, a_e2)):
+        f.insert_tensor(p_pooled, a, rows=B, width_bytes=D * 4, dest_pitch_bytes=3 * D * 4, dest_offset_bytes=j * D * 4)
+    f.quantize(a_xq, p_x, n=B * din, tqp=tq["x"])
+    f.fully_connected(a_h, a_xq, f.constant("wfc", wfc), f.constant("bfc", bfc), M=B, K=din, N=D, in_tqp=tq["x"], w_tqp=tq["w"],
+                      bias_tqp=tq["b"], out_tqp=tq["h"])
+    f.relu(a_hr, a_h, n=B * D, src_tqp=tq["h"], dest_tqp=tq["r"])
+    f.dequantize(a_hf, a_hr, n=B * D, tqp=tq["r"])
+    f.pairwise_dot(a_i, a_hf, p_pooled, batch=B, tables=3, dim=D, quant=tq["inter"])
+    f.rescale(a_ir, a_i, n=B * width, in_tqp=tq["inter"], out_tqp=tq["rs"])
+    f.matmul(a_m, a_ir, f.constant("wm", wm), M=B, K=width, N=5, lhs_tqp=tq["rs"], rhs_tqp=tq["m"], out_tqp=tq["mm"])
+    f.dequantize(p_out, a_m, n=B * 5, tqp=tq["mm"])
+    f.compile()
+    dm.add_network(f)
+
+    x = rng.normal(0, 1, (B, din)).astype(np.float32)
+    ip = np.zeros(cap, np.int64); ip[:n] = idx
+    wp = np.zeros(cap, np.float32); wp[:n] = w
+    out, pooled = np.zeros((B, 5), np.float32), np.zeros((B, 3, D), np.float32)
+    dm.run_function("rec", {"idx": ip, "len": lengths.copy(), "w": wp, "x": x.copy(), "out": out, "pooled": pooled},
+                    outputs={"out", "pooled"})
+
+    e0 = oracle.frwq_slws_u8_f32(t8, np.ones(n, np.float32), idx, lengths)
+    e1 = oracle.sparse_lengths_sum_f32(tf, idx, lengths)
+    e2 = oracle.rowwise_quantized_slws_f32(tq8, sc8, of8, w, idx, lengths)
+    np.testing.assert_allclose(pooled[:, 0], e0, rtol=1e-5, atol=1e-5)
+    np.testing.assert_array_equal(pooled[:, 1].view(np.uint32), e1.view(np.uint32))
+    np.testing.assert_array_equal(pooled[:, 2].view(np.uint32), e2.view(np.uint32))
+    # the dense part from the pooled vectors the device produced: bit for bit
+    q = oracle.quantize_scale_offset_32to8
+    xq = oracle.element_quantize_i8(x, *tq["x"])
+    mm = np.float32(tq["x"][0]) * np.float32(tq["w"][0])
+    h = oracle.fc_i8_i32(xq, wfc, bfc, tq["h"][1], tq["x"][1], tq["w"][1], tq["b"][1], q(np.float32(tq["b"][0]) / mm),
+                         q(mm / np.float32(tq["h"][0])))
+    hr = oracle.element_relu_i8(h, tq["h"][1], tq["r"][1], q(np.float32(tq["h"][0]) / np.float32(tq["r"][0])))
+    hf = oracle.element_dequantize_i8(hr, *tq["r"])
+    inter = oracle.element_quantize_i8(oracle.pairwise_dot_interaction(hf, pooled), *tq["inter"])
+    ir = oracle.element_rescale_i8(inter, tq["rs"][1], tq["inter"][1], q(np.float32(tq["inter"][0]) / np.float32(tq["rs"][0])))
+    m = oracle.matmul_i8(ir, wm, tq["mm"][1], tq["rs"][1], tq["m"][1],
+                         q(np.float32(tq["rs"][0]) * np.float32(tq["m"][0]) / np.float32(tq["mm"][0])))
+    want = oracle.element_dequantize_i8(m, *tq["mm"])
+    np.testing.assert_array_equal(out.view(np.uint32), want.view(np.uint32))
+    assert len(np.unique(m)) > 5
