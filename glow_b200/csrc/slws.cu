@@ -64,6 +64,12 @@ __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
 #ifndef GLOWB200_SLWS_MIN_BLOCKS
 #define GLOWB200_SLWS_MIN_BLOCKS 3
 #endif
+#ifndef GLOWB200_SLWS_MIN_BLOCKS_P4
+#define GLOWB200_SLWS_MIN_BLOCKS_P4 2
+#endif
+#ifndef GLOWB200_SLWS_P4_FROM
+#define GLOWB200_SLWS_P4_FROM 16
+#endif
 #ifndef GLOWB200_SLWS_UNROLL_P2
 #define GLOWB200_SLWS_UNROLL_P2 4
 #endif
@@ -495,7 +501,7 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
 }
 
 template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int U>
-__global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
+__global__ void __launch_bounds__(kGatherThreads, P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
   gather_group_body<BITS, SO16, OUT16, ACC16, IdxT, P, U>(p);
 }
 
@@ -725,7 +731,7 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
 // profile favours (the word the segments kernel leaves behind the table's boundaries).
 // grid.x covers the larger of the two mappings' block counts; surplus blocks leave at once.
 template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false, bool WIDE16 = false>
-__global__ void __launch_bounds__(kGatherThreads, P == 4 ? 1 : GLOWB200_SLWS_MIN_BLOCKS)
+__global__ void __launch_bounds__(kGatherThreads, P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS)
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
   const bool skewed = p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
@@ -865,12 +871,8 @@ template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT>
 cudaError_t launch_gather_p(const SlwsLaunch &L, int P, dim3 grid, cudaStream_t s) {
   switch (P) {
     case 1: return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 1, 4>(L, grid, s);
-    case 2:
-      // (4-bit rows only: a uint8 chunk is two registers wide and 8 rows in flight would spill)
-      if constexpr (BITS == 4) {
-        if (L.lpr_log2 >= 3) return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 2, 8>(L, grid, s);
-      }
-      return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 2, GLOWB200_SLWS_UNROLL_P2>(L, grid, s);
+    case 2: return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 2, GLOWB200_SLWS_UNROLL_P2>(L, grid, s);
+    // (8 rows in flight per lane were tried for 4-bit rows of 256 and 512 columns: 6 % slower)
     default: return launch_gather_pu<BITS, SO16, OUT16, ACC16, IdxT, 4, 4>(L, grid, s);
   }
 }
@@ -915,8 +917,11 @@ int plan(int kind, int64_t in_line, int64_t out_line, bool pointers_aligned, int
   const int chunks = (int)(out_line / 8);
   if (chunks > 128) return GLOWB200_OK;  // > 1024 columns: any-shape kernel
   // Two chunks per lane once a row has 8 or more chunks: halves the per-row bookkeeping per
-  // byte; four only when 32 lanes cannot cover the row otherwise.
-  P = chunks > 64 ? 4 : (chunks >= 8 ? 2 : 1);
+  // byte. Four when 32 lanes cannot cover the row otherwise, and for 4-bit rows of 128 or more
+  // columns, where a chunk is only 4 payload bytes and a lane's load would otherwise be 8 bytes
+  // (measured on the 4-bit sweep: +12 % at 128 columns, +15 % at 256; at 64 and 32 columns four
+  // chunks per lane leave too few lanes per row and lose 20-25 %).
+  P = chunks > 64 || (kind >= 2 && chunks >= GLOWB200_SLWS_P4_FROM) ? 4 : (chunks >= 8 ? 2 : 1);
   int lpr = 1;
   while (lpr * P < chunks) lpr <<= 1;
   lpr_log2 = 0;
