@@ -101,6 +101,9 @@ SIGNATURES = {
     "glowb200_embedding_bag_byte_rowwise_offsets": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _sz, _vp,
                _vp]),
+    "glowb200_int_nbit_split_embedding_bags": (
+        _int, [_vp, _vp, _i64, _vp, _i64, _vp, _vp, _int, _vp, _vp, _i64, _i64, _vp, _vp, _int, _i64, _i64, _int,
+               _vp, _int, _int, _int, _int, _vp, _vp]),
 }
 
 _lib = None

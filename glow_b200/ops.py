@@ -18,6 +18,7 @@ STATUS_LENGTHS_OVERRUN = 2
 STATUS_NEGATIVE_LENGTH = 4
 STATUS_BAD_OFFSETS = 8
 STATUS_WAIT_TIMEOUT = 16
+STATUS_UNSUPPORTED_TABLE = 32
 
 
 def _stream():
@@ -141,6 +142,53 @@ def embedding_bag_byte_rowwise_offsets(data, weights, indices, offsets, kind=UIN
         _p(out), _p(data), kind, rows, _p(weights), _p(indices), _p(offsets), int(indices.dtype == torch.int64),
         num_offsets, n, in_line, out_line, int(has_end_offset), int(odt == torch.float16),
         int(use_fp16_accumulation), _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
+EST_FLOAT, EST_FLOAT16, EST_INT8, EST_INT4 = 0, 1, 2, 3   # SplitEmbeddingSparseType
+EP_SUM, EP_MEAN, EP_NONE = 0, 1, 2                         # SplitEmbeddingPoolingMode
+PLACEMENT_DEVICE, PLACEMENT_MANAGED, PLACEMENT_MANAGED_CACHING, PLACEMENT_HOST = 0, 1, 2, 3
+
+
+def split_embedding_row_bytes(num_dims, weights_ty, *, scale_offset_is_fp32=False, row_alignment=16):
+    """Bytes of one (padded) row of a split-embedding table (InterpreterNodes.cpp:43-74)."""
+    so = 4 if scale_offset_is_fp32 else 2
+    raw = {EST_FLOAT: num_dims * 4, EST_FLOAT16: num_dims * 2, EST_INT8: num_dims + 2 * so,
+           EST_INT4: num_dims // 2 + 2 * so}[weights_ty]
+    return (raw + row_alignment - 1) // row_alignment * row_alignment
+
+
+def int_nbit_split_embedding_bags(dev_weights, uvm_weights, weights_placements, weights_offsets, weights_tys,
+                                  dim_offsets, total_dims, indices, offsets, pooling_mode=EP_SUM, *,
+                                  indice_weights=None, out_dtype=torch.float32, scale_offset_is_fp32=False,
+                                  row_alignment=16, out=None, status=None):
+    """IntNBitSplitEmbeddingBags (indice_weights None) / IntNBitSplitEmbeddingWeightedBags:
+    T tables in one byte buffer, T*B bags per request, result [B, total_dims]."""
+    _cuda(dev_weights, "dev_weights", (torch.uint8,))
+    _cuda(uvm_weights, "uvm_weights", (torch.uint8,))
+    _cuda(weights_placements, "weights_placements", (torch.int32,))
+    _cuda(weights_offsets, "weights_offsets", (torch.int32, torch.int64))
+    _cuda(weights_tys, "weights_tys", (torch.uint8,))
+    _cuda(dim_offsets, "dim_offsets", (torch.int32,))
+    _cuda(indices, "indices", (torch.int32, torch.int64))
+    _cuda(offsets, "offsets", (indices.dtype,))
+    if indice_weights is not None:
+        _cuda(indice_weights, "indice_weights", (torch.float32, torch.float16))
+    T = dim_offsets.shape[0] - 1
+    if T < 0 or weights_tys.shape[0] != T or weights_placements.shape[0] != T or weights_offsets.shape[0] != T:
+        raise ValueError("table description arrays disagree on the number of tables")
+    if T == 0 or (offsets.shape[0] - 1) % T != 0:
+        raise ValueError("offsets must hold num_tables * bags_per_table + 1 entries")
+    B = (offsets.shape[0] - 1) // T
+    if out is None:
+        out = torch.empty((B, total_dims), dtype=out_dtype, device=indices.device)
+    _cuda(out, "out", (torch.float32, torch.float16))
+    check(_lib.lib().glowb200_int_nbit_split_embedding_bags(
+        _p(out), _p(dev_weights), dev_weights.numel(), _p(uvm_weights), uvm_weights.numel(), _p(weights_placements),
+        _p(weights_offsets), int(weights_offsets.dtype == torch.int64), _p(weights_tys), _p(dim_offsets), T,
+        total_dims, _p(indices), _p(offsets), int(indices.dtype == torch.int64), indices.shape[0], B, pooling_mode,
+        _p(indice_weights), int(indice_weights is not None and indice_weights.dtype == torch.float16),
+        int(out.dtype == torch.float16), int(scale_offset_is_fp32), row_alignment, _p(status), _stream()))
     return out
 
 

@@ -48,6 +48,7 @@ extern "C" {
 #define GLOWB200_STATUS_NEGATIVE_LENGTH 4    /* a negative length: treated as 0                   */
 #define GLOWB200_STATUS_BAD_OFFSETS 8        /* offsets not monotone / out of range: bag is empty */
 #define GLOWB200_STATUS_WAIT_TIMEOUT 16      /* a bounded device-side wait gave up                */
+#define GLOWB200_STATUS_UNSUPPORTED_TABLE 32 /* split-embedding table of an unsupported type      */
 
 /* Fused-rowwise table kinds (glow::ElemKind, include/glow/Base/Type.h:424-433).  A row is the
  * quantized payload followed by scale then offset (include/glow/Base/Tensor.h:1585-1607). */
@@ -156,6 +157,40 @@ int glowb200_embedding_bag_byte_rowwise_offsets(
     int64_t in_line_size, int64_t out_line_size, int has_end_offset, int out_is_fp16,
     int use_fp16_accumulation, void *workspace, size_t workspace_bytes, int32_t *status,
     glowb200_stream_t stream);
+
+/* IntNBitSplitEmbeddingBags / IntNBitSplitEmbeddingWeightedBags: table-batched embedding bags.
+ * Replaces fwdIntNBitSplitEmbeddingBagsInst / fwdIntNBitSplitEmbeddingWeightedBagsInst
+ * (lib/Backends/Interpreter/InterpreterNodes.cpp:6593-6738, row helpers :42-114); the argument
+ * list is the node's operand list (Function::createIntNBitSplitEmbeddingWeightedBags).
+ *   dev_weights / uvm_weights   byte buffers holding the rows of all tables; table t reads
+ *                               dev_weights when weights_placements[t] == 3 (HOST), uvm_weights
+ *                               otherwise; placement 0 (DEVICE) is refused like in the reference
+ *   weights_offsets [T]         byte offset of table t in its buffer (int32 or int64)
+ *   weights_tys [T]             0 fp32, 1 fp16, 2 int8, 3 int4 (SplitEmbeddingSparseType,
+ *                               include/glow/Graph/Nodes.h:302-309); int2 is refused
+ *   dim_offsets [T+1]           table t has dim_offsets[t+1]-dim_offsets[t] columns and fills
+ *                               columns dim_offsets[t].. of the result
+ *   indices [num_indices], offsets [T*bags_per_table + 1]  same integer type; bag (t, b) is
+ *                               offsets[t*B+b] .. offsets[t*B+b+1]
+ *   pooling_mode                0 sum, 1 mean (bag length converted to the result type), 2 as 0
+ *   indice_weights              NULL (unweighted node) or fp32 / fp16 [num_indices]
+ *   dest                        [bags_per_table, total_dims] fp32 or fp16; sums are carried in
+ *                               the result type (an fp16 result rounds after every row)
+ *   scale_offset_is_fp32        int8 / int4 rows start with two fp32 instead of two fp16
+ *                               (glow::flags::ConvertFusedScaleOffsetToFP32)
+ *   row_alignment               rows are padded to this many bytes
+ *                               (glow::interpreter::flags::RowAlignmentBytes, 16)
+ * All table-description arrays are device pointers (they are operands of the node).  Rows that
+ * reach outside their buffer raise GLOWB200_STATUS_INDEX_OUT_OF_RANGE and are skipped; results
+ * are bit-identical to the Interpreter's. */
+int glowb200_int_nbit_split_embedding_bags(
+    void *dest, const void *dev_weights, int64_t dev_weights_bytes, const void *uvm_weights,
+    int64_t uvm_weights_bytes, const int32_t *weights_placements, const void *weights_offsets,
+    int weights_offsets_are_int64, const uint8_t *weights_tys, const int32_t *dim_offsets,
+    int64_t num_tables, int64_t total_dims, const void *indices, const void *offsets,
+    int indices_are_int64, int64_t num_indices, int64_t bags_per_table, int pooling_mode,
+    const void *indice_weights, int indice_weights_are_fp16, int out_is_fp16,
+    int scale_offset_is_fp32, int row_alignment, int32_t *status, glowb200_stream_t stream);
 
 /* SparseLengthsWeightedSum / SparseLengthsSum over an fp32 table.
  * Replaces libjit_sparse_lengths_weighted_sum_f_u / _f_i32 and libjit_sparse_lengths_sum_f_u /

@@ -365,6 +365,76 @@ ORC_API void orc_rowwise_quantized_slws_f32(float *dest, const uint8_t *data, co
     }
 }
 
+/* fwdIntNBitSplitEmbeddingWeightedBagsImpl: InterpreterNodes.cpp:6664-6738, with the row helpers
+ * of InterpreterNodes.cpp:42-114 (table-batched embedding bags: T tables of mixed element types
+ * in one byte buffer).
+ *   weights_tys[t] : 0 fp32, 1 fp16, 2 int8, 3 int4 elements (Nodes.h:302-309)
+ *   row layout     : int8 / int4 rows START with their scale and offset (two fp16, or two fp32
+ *                    when so_fp32), columns follow; rows are padded to row_alignment bytes
+ *   placements[t]  : 3 (HOST) reads dev_weights, anything else uvm_weights
+ *   offsets        : T*B+1 entries, bag (t, b) = offsets[t*B+b] .. offsets[t*B+b+1]
+ *   result         : [B, total_dims], element (b, dim_offsets[t]+d); accumulated in the RESULT
+ *                    type (an fp16 result is rounded to fp16 after every row); mean pooling
+ *                    divides by the bag length converted to the result type
+ *   indice_weights : NULL = 1.0; fp32 or fp16 (iw_fp16)                                        */
+ORC_API void orc_int_nbit_split_embedding_bags(
+    void *dest, const uint8_t *dev_weights, const uint8_t *uvm_weights, const int32_t *placements,
+    const void *weights_offsets, int wo64, const uint8_t *weights_tys, const int32_t *dim_offsets,
+    int64_t num_tables, int64_t total_dims, const void *indices, const void *offsets, int idx64,
+    int64_t num_bags_per_table, int pooling_mode, const void *indice_weights, int iw_fp16,
+    int out_fp16, int so_fp32, int row_alignment) {
+  const size_t esz = out_fp16 ? 2 : 4;
+  memset(dest, 0, (size_t)(num_bags_per_table * total_dims) * esz);
+  const int so = so_fp32 ? 4 : 2;
+  for (int64_t t = 0; t < num_tables; t++) {
+    const int32_t dim_start = dim_offsets[t], num_dims = dim_offsets[t + 1] - dim_offsets[t];
+    const uint8_t *w = placements[t] == 3 ? dev_weights : uvm_weights;
+    const int ty = weights_tys[t];
+    const int64_t wo = load_index(weights_offsets, wo64, t);
+    int32_t unpadded = ty == 0 ? num_dims * 4 : ty == 1 ? num_dims * 2
+                     : ty == 2 ? num_dims + 2 * so : num_dims / 2 + 2 * so;
+    const int64_t row_bytes = ((unpadded + row_alignment - 1) / row_alignment) * (int64_t)row_alignment;
+    for (int64_t b = 0; b < num_bags_per_table; b++) {
+      const int64_t start = load_index(offsets, idx64, t * num_bags_per_table + b);
+      const int64_t end = load_index(offsets, idx64, t * num_bags_per_table + b + 1);
+      for (int32_t d = 0; d < num_dims; d++) {
+        float sum_f = 0.0f;          /* OutputTy sum: fp32, or fp16 kept as its fp32 value */
+        for (int64_t i = start; i < end; i++) {
+          const uint8_t *row = w + wo + load_index(indices, idx64, i) * row_bytes;
+          const float weight = !indice_weights ? 1.0f
+                             : iw_fp16 ? orc_f16_to_f32(((const uint16_t *)indice_weights)[i])
+                                       : ((const float *)indice_weights)[i];
+          float v;
+          if (ty == 0) { memcpy(&v, row + (size_t)d * 4, 4); }
+          else if (ty == 1) { uint16_t h; memcpy(&h, row + (size_t)d * 2, 2); v = orc_f16_to_f32(h); }
+          else {
+            float scale, offset;
+            if (so_fp32) { memcpy(&scale, row, 4); memcpy(&offset, row + 4, 4); }
+            else { uint16_t hs, ho; memcpy(&hs, row, 2); memcpy(&ho, row + 2, 2);
+                   scale = orc_f16_to_f32(hs); offset = orc_f16_to_f32(ho); }
+            const uint8_t byte = ty == 2 ? row[2 * so + d] : row[2 * so + d / 2];
+            const uint8_t q = ty == 2 ? byte : ((d & 1) ? (uint8_t)(byte >> 4) : (uint8_t)(byte & 0xF));
+            volatile float prod = (float)q * scale;   /* two roundings: no contraction */
+            v = prod + offset;
+          }
+          volatile float addend = weight * v;
+          const float s = sum_f + addend;
+          sum_f = out_fp16 ? orc_f16_to_f32(orc_f32_to_f16(s)) : s;
+        }
+        if (pooling_mode == 1 && end > start) {
+          const float n = out_fp16 ? orc_f16_to_f32(orc_f32_to_f16((float)(end - start)))
+                                   : (float)(end - start);
+          sum_f = sum_f / n;
+          if (out_fp16) sum_f = orc_f16_to_f32(orc_f32_to_f16(sum_f));
+        }
+        const int64_t o = b * total_dims + dim_start + d;
+        if (out_fp16) ((uint16_t *)dest)[o] = orc_f32_to_f16(sum_f);
+        else ((float *)dest)[o] = sum_f;
+      }
+    }
+  }
+}
+
 /* ------------------------------------------------------------------------------------ */
 /* Dense int8 layers.  Integer arithmetic wraps mod 2^32 like the reference's int32.      */
 /* Callers that want more host threads split the batch rows over them (oracle.py).       */

@@ -210,6 +210,31 @@ def embedding_bag_byte_rowwise_offsets(data, kind, weights, indices, offsets, ha
     return dest
 
 
+def int_nbit_split_embedding_bags(dev_weights, uvm_weights, placements, weights_offsets, weights_tys,
+                                  dim_offsets, total_dims, indices, offsets, pooling_mode=0,
+                                  indice_weights=None, out_fp16=False, so_fp32=False, row_alignment=16):
+    """Table-batched embedding bags (InterpreterNodes.cpp:6664-6738); result [B, total_dims]."""
+    dev_weights, uvm_weights = _c(dev_weights, np.uint8), _c(uvm_weights, np.uint8)
+    placements, dim_offsets = _c(placements, np.int32), _c(dim_offsets, np.int32)
+    weights_tys = _c(weights_tys, np.uint8)
+    weights_offsets, wo64 = _idx(weights_offsets)
+    indices, idx64 = _idx(indices)
+    offsets = np.ascontiguousarray(offsets, dtype=indices.dtype)
+    T = dim_offsets.shape[0] - 1
+    B = (offsets.shape[0] - 1) // T
+    iw, iw16 = None, 0
+    if indice_weights is not None:
+        iw16 = int(np.asarray(indice_weights).dtype == np.float16)
+        iw = _c(indice_weights, np.float16 if iw16 else np.float32)
+    dest = np.empty((B, total_dims), np.float16 if out_fp16 else np.float32)
+    lib().orc_int_nbit_split_embedding_bags(
+        _ptr(dest), _ptr(dev_weights), _ptr(uvm_weights), _ptr(placements), _ptr(weights_offsets), C.c_int(wo64),
+        _ptr(weights_tys), _ptr(dim_offsets), _i64(T), _i64(total_dims), _ptr(indices), _ptr(offsets),
+        C.c_int(idx64), _i64(B), C.c_int(pooling_mode), _ptr(iw) if iw is not None else None, C.c_int(iw16),
+        C.c_int(int(out_fp16)), C.c_int(int(so_fp32)), C.c_int(row_alignment))
+    return dest
+
+
 def sparse_lengths_weighted_sum_f32(data, weights, indices, lengths):
     data = _c(data, np.float32)
     weights = _c(weights, np.float32)

@@ -115,3 +115,16 @@ def test_fused_4bit_roundtrip(oracle):
         ones = np.ones(rows, np.float16 if kind & 1 else np.float32)
         out = oracle.frwq_slws_interp(table, kind, ones, np.arange(rows, dtype=np.int64), np.ones(rows, np.int32))
         np.testing.assert_allclose(out.astype(np.float32), data, atol=0.02 if kind & 1 else 1e-5)
+
+
+from split_embedding_cases import CASES as SPLIT_CASES, case_inputs as split_case_inputs
+
+
+@pytest.mark.parametrize("name", SPLIT_CASES)
+@pytest.mark.parametrize("idx_dtype", [np.int32, np.int64])
+def test_int_nbit_split_embedding_bags_golden(oracle, name, idx_dtype):
+    """OperatorTest.cpp:21308-21762: table-batched embedding bags, all sixteen cases."""
+    a, expected, tol = split_case_inputs(name, idx_dtype)
+    out = oracle.int_nbit_split_embedding_bags(**a)
+    assert out.dtype == (np.float16 if a["out_fp16"] else np.float32)
+    np.testing.assert_allclose(out.astype(np.float32), expected, atol=tol, rtol=0)
