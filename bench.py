@@ -46,10 +46,13 @@ def parse():
     ap.add_argument("--requests", type=int, default=4, help="distinct pre-generated batches rotated over the steps")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="slws", choices=["slws", "int8_fc", "slws4", "dlrm", "resnet50"],
+    ap.add_argument("--workload", default="slws", choices=["slws", "int8_fc", "slws4", "dlrm", "resnet50", "tbe"],
                     help="slws: the headline gather-pool line (default); int8_fc: the rowwise int8 FC line; "
                          "slws4: the 4-bit fused-rowwise sweep point selected by --dim; dlrm / resnet50: the "
-                         "recommendation model / the int8 ResNet-50 alone (the default line carries both as extras)")
+                         "recommendation model / the int8 ResNet-50 alone (the default line carries both as extras); "
+                         "tbe: table-batched embedding bags (IntNBitSplitEmbeddingBags) over tables of --tbe-type")
+    ap.add_argument("--tbe-type", default="int4", choices=["fp16", "int8", "int4"], help="tbe: element type of the tables")
+    ap.add_argument("--tbe-out", default="fp16", choices=["fp16", "fp32"], help="tbe: element type of the result")
     ap.add_argument("--dim", type=int, default=128, help="slws4: embedding width (32, 64, 128 or 256)")
     ap.add_argument("--table-gb", type=float, default=40.0, help="slws4: total table bytes per GPU, in GB")
     ap.add_argument("--row-bytes", type=int, default=0,
@@ -775,6 +778,115 @@ def run_slws4_line(args):
         dist.destroy_process_group()
 
 
+def run_tbe_line(args):
+    """--workload tbe: table-batched embedding bags (IntNBitSplitEmbeddingBags), the shape of the
+    reference's tests/benchmark/TBEBench.cpp: T tables of 10,000,000 rows x --dim columns of
+    --tbe-type in one byte buffer (rows padded to 16 bytes, scale/offset header first), filling
+    --table-gb per GPU; 8192 bags per table, lengths Poisson(64), uniform int64 indices, sum
+    pooling, fp16 result.  One launch pools all T * 8192 bags.  At N > 1 every rank owns its own
+    tables (weak scaling, no collective)."""
+    import torch
+    import torch.distributed as dist
+    from glow_b200 import ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    D, ROWS, B = args.dim, 10_000_000, 8192
+    ty = {"fp16": ops.EST_FLOAT16, "int8": ops.EST_INT8, "int4": ops.EST_INT4}[args.tbe_type]
+    row_bytes = ops.split_embedding_row_bytes(D, ty)
+    payload = {"fp16": 2 * D, "int8": D + 4, "int4": D // 2 + 4}[args.tbe_type]
+    T = max(1, int(args.table_gb * 1e9 / (ROWS * row_bytes)))
+    g = torch.Generator(device=dev).manual_seed(0x610B200 + 31 * rank + D)
+    weights = torch.empty(T * ROWS * row_bytes, dtype=torch.uint8, device=dev)
+    for k in range(T):     # table by table: bounded temporaries
+        tab = weights[k * ROWS * row_bytes:(k + 1) * ROWS * row_bytes].view(ROWS, row_bytes)
+        if ty == ops.EST_FLOAT16:
+            tab.view(torch.float16).normal_(0, 1, generator=g)
+        else:
+            tab.random_(0, 256, generator=g)
+            so = torch.stack([torch.empty(ROWS, device=dev).uniform_(0.001, 0.01, generator=g),
+                              torch.empty(ROWS, device=dev).uniform_(-1, 1, generator=g)], dim=1).to(torch.float16)
+            tab[:, :4] = so.view(torch.uint8).view(ROWS, 4)
+            del so
+    placements = torch.full((T,), ops.PLACEMENT_HOST, dtype=torch.int32, device=dev)
+    weights_offsets = (torch.arange(T, dtype=torch.int64, device=dev) * (ROWS * row_bytes))
+    tys = torch.full((T,), ty, dtype=torch.uint8, device=dev)
+    dim_offsets = (torch.arange(T + 1, dtype=torch.int32, device=dev) * D).to(torch.int32)
+    R = 2
+    reqs = []
+    for r in range(R):
+        rng = np.random.Generator(np.random.PCG64(777 + 1000 * rank + r))
+        lengths = rng.poisson(64, T * B)
+        offsets = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int64)
+        gi = torch.Generator(device=dev).manual_seed(55 + r + 10 * rank)
+        indices = torch.randint(0, ROWS, (int(offsets[-1]),), device=dev, generator=gi)
+        reqs.append((indices, torch.from_numpy(offsets).to(dev)))
+    out16 = args.tbe_out == "fp16"
+    out = torch.empty((B, T * D), dtype=torch.float16 if out16 else torch.float32, device=dev)
+    status = ops.new_status(dev)
+
+    def step(i):
+        indices, offsets = reqs[i % R]
+        ops.int_nbit_split_embedding_bags(weights, weights, placements, weights_offsets, tys, dim_offsets, T * D,
+                                          indices, offsets, ops.EP_SUM, out=out, status=status)
+
+    nbytes = [int(rq[0].shape[0]) * (payload + 8) + T * B * (8 + (2 if out16 else 4) * D) for rq in reqs]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t_end = time.time() + 1.0
+    while len(sampler.lines) < 8 and time.time() < t_end:
+        step(0)
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    assert int(status.item()) == 0
+    moved = sum(nbytes[i % R] for i in range(args.steps))
+    tm = torch.tensor([ms], dtype=torch.float64, device=dev)
+    mv = torch.tensor([moved], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        dist.all_reduce(mv, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        peak, src = measured_peak_hbm()
+        value = float(mv[0]) / (float(tm[0]) * 1e-3) / 1e9
+        per_gpu = value / world
+        print(json.dumps({
+            "metric": "split_embedding_bags_hbm_gbps", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": float(tm[0]) / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "%s -> %s" % (args.tbe_type, "f16 (fp16 running sum, as the reference)" if out16 else "f32"),
+            "data": "synthetic",
+            "config": {"workload": "IntNBitSplitEmbeddingBags: %d %s tables x 10,000,000 rows x %d cols in one buffer "
+                                   "(%d B rows of which %d B are read, %.1f GB per GPU), 8192 bags/table, lengths "
+                                   "Poisson(64), uniform int64 indices, sum pooling, %s result"
+                                   % (T, args.tbe_type, D, row_bytes, payload, T * ROWS * row_bytes / 1e9, args.tbe_out),
+                       "dim": D, "tables_per_gpu": T, "l2_policy": "tables far larger than L2, uniform indices"},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                         "peak_source": src, "traffic": None, "kernel": "split_embedding_bags_kernel<%s,long>" % ("true" if out16 else "false"),
+                         "rows_per_s": sum(int(reqs[i % R][0].shape[0]) for i in range(args.steps)) / (ms * 1e-3)},
+            "gpu_launches": args.steps, "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_slws4_sharded_line(args):
     """--workload slws4 --shard rows: the 4-bit sweep with every table cut into row ranges over the
     GPUs (rank g holds rows [g*R/G, (g+1)*R/G) of EVERY table).  There are G times as many tables
@@ -922,6 +1034,8 @@ def main():
         return run_slws4_sharded_line(args) if args.shard != "tables" else run_slws4_line(args)
     if args.workload in ("dlrm", "resnet50"):
         return run_model_line(args)
+    if args.workload == "tbe":
+        return run_tbe_line(args)
 
     import torch
     import torch.distributed as dist

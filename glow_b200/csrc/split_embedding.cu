@@ -8,7 +8,7 @@
 // the result is [B, total_dims] with table t's columns at dim_offsets[t].
 //
 // One launch pools every bag of every table.  blockIdx.y is the table; inside a table a group of
-// lanes (a power of two that covers one row in 8- or 16-byte chunks) owns a bag and walks its
+// lanes (as many as a row has 16-byte chunks, 8-byte ones for tables off 16-byte boundaries) owns a bag and walks its
 // rows in index order, each lane keeping the sums of the columns of its own chunk: every result
 // element is accumulated in the reference's order and in the result's type (an fp16 result is
 // rounded after every row, as the reference's float16 sum is), with the multiply and the add
@@ -39,7 +39,16 @@ struct SplitLaunch {
 };
 
 constexpr int kThreads = 256;
-constexpr int kRows = 4;  // rows in flight per lane
+#ifndef GLOWB200_TBE_MIN_BLOCKS
+#define GLOWB200_TBE_MIN_BLOCKS 4
+#endif
+#ifndef GLOWB200_TBE_I4_WIDE
+#define GLOWB200_TBE_I4_WIDE 1
+#endif
+#ifndef GLOWB200_TBE_ROWS
+#define GLOWB200_TBE_ROWS 4
+#endif
+constexpr int kRows = GLOWB200_TBE_ROWS;  // rows in flight per lane
 
 enum : int { TY_F32 = 0, TY_F16 = 1, TY_I8 = 2, TY_I4 = 3 };
 
@@ -70,75 +79,116 @@ __device__ __forceinline__ void load_chunk(const uint8_t *base, int64_t at, int6
   }
 }
 
-__device__ __forceinline__ float half_bits_to_float(uint32_t h) {
-  return __half2float(__ushort_as_half((unsigned short)(h & 0xFFFFu)));
+// float(h) for the fp16 number in the low half of `h`, through the mixed-precision add of sm_100
+// (adding -0 keeps every value, the sign of a zero included) instead of a conversion
+// instruction: conversions issue at an eighth of the rate of adds, and this kernel would be
+// bound by them.
+__device__ __forceinline__ float add_f32_f16(uint16_t h, float c) {
+  float d;
+  asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(h), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float half_bits_to_float(uint32_t h) { return add_f32_f16((uint16_t)(h & 0xFFFFu), -0.0f); }
+// Two floats rounded to fp16 (round to nearest even), packed {lo, hi}: one conversion for two.
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
 }
 
 // Pools the bag [begin, end) of one table for the lanes of one group.
-//   TY   element type of the table; CW words per lane chunk (2 or 4)
+//   TY   element type of the table; CW words per lane chunk (2 or 4); SO32: fp32 row headers
 //   gl / lpr  lane within the group / lanes of the group
-template <int TY, int CW, bool OUT16, typename IdxT>
+// Slots (the elements of a lane's chunk) are handled in pairs.  An fp16 result keeps its running
+// sums as fp16 pairs: per row the sum is widened, added to in fp32 and rounded back
+// (float16::operator+ of the reference, include/glow/Support/Float16.h:47-49).
+// Quantized elements become floats without a conversion instruction: byte or nibble q is merged
+// into the mantissa of the fp16 number 1024 (0x6400 | q = 1024 + q) and 1024 is subtracted in the
+// mixed-precision add.  With fp16 headers q * scale is exact in fp32 (8 + 11 significant bits), so
+// one fused multiply-add gives the reference's separately rounded q * scale + offset.
+template <int TY, int CW, bool OUT16, bool WEIGHTED, bool SO32, typename IdxT>
 __device__ __forceinline__ int32_t pool_bag(const SplitLaunch &p, const uint8_t *base, int64_t limit, int64_t table_at,
                                             int32_t row_bytes, int32_t touched, int32_t num_dims, bool vec,
                                             int64_t begin, int64_t end, int gl, int lpr, void *out_row) {
   constexpr int CB = 4 * CW;                                           // chunk bytes
   constexpr int SLOTS = TY == TY_F32 ? CW : TY == TY_F16 ? 2 * CW : TY == TY_I8 ? 4 * CW : 8 * CW;
-  const int H = (TY == TY_I8 || TY == TY_I4) ? (p.so_fp32 ? 8 : 4) : 0;  // header bytes of a row
+  constexpr int PAIRS = SLOTS / 2;
+  constexpr int H = (TY == TY_I8 || TY == TY_I4) ? (SO32 ? 8 : 4) : 0;  // header bytes of a row
   const IdxT *indices = reinterpret_cast<const IdxT *>(p.indices);
   int32_t flags = 0;
+  // the two slots of pair i: neighbours, except for nibbles, where one mask takes nibbles k and k + 4 of a word
+  auto slot_a = [](int i) { return TY == TY_I4 ? 8 * (i >> 2) + (i & 3) : 2 * i; };
+  auto slot_b = [](int i) { return TY == TY_I4 ? 8 * (i >> 2) + (i & 3) + 4 : 2 * i + 1; };
+  // rows whose touched bytes all lie inside the buffer (InterpreterNodes.cpp:6720): 0 .. max_row
+  int64_t max_row = -1;
+  if (table_at >= 0 && table_at + touched <= limit) max_row = (limit - touched - table_at) / row_bytes;
+  if (max_row > 0x7FFFFFFEll) max_row = 0x7FFFFFFEll;
 
   for (int32_t cbase = 0; cbase < touched; cbase += lpr * CB) {
     const int32_t at = cbase + gl * CB;          // byte of the row this lane's chunk starts at
     const bool has = at < touched;
     // column of slot 0 (negative inside the header)
     const int32_t col0 = TY == TY_F32 ? at / 4 : TY == TY_F16 ? at / 2 : TY == TY_I8 ? at - H : 2 * (at - H);
-    float acc[SLOTS];
+    float acc[OUT16 ? 1 : SLOTS];      // fp32 result: the sums
+    uint32_t acch[OUT16 ? PAIRS : 1];  // fp16 result: the sums as fp16 pairs {slot_a, slot_b}
 #pragma unroll
-    for (int s = 0; s < SLOTS; s++) acc[s] = 0.0f;
+    for (int s = 0; s < (OUT16 ? 1 : SLOTS); s++) acc[s] = 0.0f;
+#pragma unroll
+    for (int s = 0; s < (OUT16 ? PAIRS : 1); s++) acch[s] = 0u;
 
+    // The indices (and weights) of the next kRows rows are requested while the current rows are
+    // in flight: an index fetch and the row fetch that depends on it would otherwise add their
+    // latencies in every trip of the loop.  A row is kept as a 32-bit number: -2 none, -1 refused.
+    int32_t next_r[kRows];
+    float next_w[kRows];
+    auto request = [&](int64_t j) {
+#pragma unroll
+      for (int u = 0; u < kRows; u++) {
+        next_r[u] = -2;
+        next_w[u] = 1.0f;
+        if (j + u < end) {
+          const int64_t r = (int64_t)indices[j + u];
+          next_r[u] = (r < 0 || r > max_row) ? -1 : (int32_t)r;
+          if constexpr (WEIGHTED)
+            next_w[u] = p.iw16 ? __half2float(reinterpret_cast<const __half *>(p.indice_weights)[j + u])
+                               : reinterpret_cast<const float *>(p.indice_weights)[j + u];
+        }
+      }
+    };
+    request(begin);
     for (int64_t j = begin; j < end; j += kRows) {
-      int64_t row_at[kRows];
+      bool live[kRows];
       float w[kRows];
       uint32_t q[kRows][CW];
       uint32_t hdr[kRows][2];
 #pragma unroll
       for (int u = 0; u < kRows; u++) {
-        row_at[u] = -1;
-        w[u] = 1.0f;
-        if (j + u < end) {
-          const int64_t r = (int64_t)indices[j + u];
-          const int64_t a = table_at + r * row_bytes;
-          // every byte the reference reads must lie inside the buffer (InterpreterNodes.cpp:6720)
-          if (r < 0 || r > limit || a < 0 || a + touched > limit) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;
-          else row_at[u] = a;
-          if (p.indice_weights != nullptr)
-            w[u] = p.iw16 ? __half2float(reinterpret_cast<const __half *>(p.indice_weights)[j + u])
-                          : reinterpret_cast<const float *>(p.indice_weights)[j + u];
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kRows; u++) {
-        if (row_at[u] < 0 || !has) continue;
-        load_chunk<CW>(base, row_at[u] + at, limit, vec, q[u]);
+        w[u] = next_w[u];
+        live[u] = next_r[u] >= 0 && has;
+        if (next_r[u] == -1) flags |= GLOWB200_STATUS_INDEX_OUT_OF_RANGE;
+        if (!live[u]) continue;
+        const int64_t row_at = table_at + (int64_t)next_r[u] * row_bytes;
+        load_chunk<CW>(base, row_at + at, limit, vec, q[u]);
         if constexpr (TY == TY_I8 || TY == TY_I4) {
           // all lanes of the group read the same header word(s): one transaction
           if (vec) {
-            hdr[u][0] = __ldg(reinterpret_cast<const uint32_t *>(base + row_at[u]));
-            hdr[u][1] = p.so_fp32 ? __ldg(reinterpret_cast<const uint32_t *>(base + row_at[u] + 4)) : 0u;
+            hdr[u][0] = __ldg(reinterpret_cast<const uint32_t *>(base + row_at));
+            hdr[u][1] = SO32 ? __ldg(reinterpret_cast<const uint32_t *>(base + row_at + 4)) : 0u;
           } else {
             uint32_t h2[2];
-            load_chunk<2>(base, row_at[u], limit, false, h2);
+            load_chunk<2>(base, row_at, limit, false, h2);
             hdr[u][0] = h2[0];
             hdr[u][1] = h2[1];
           }
         }
       }
+      request(j + kRows);
 #pragma unroll
       for (int u = 0; u < kRows; u++) {
-        if (row_at[u] < 0 || !has) continue;
+        if (!live[u]) continue;
         float scale = 0.0f, offset = 0.0f;
         if constexpr (TY == TY_I8 || TY == TY_I4) {
-          if (p.so_fp32) {
+          if constexpr (SO32) {
             scale = __uint_as_float(hdr[u][0]);
             offset = __uint_as_float(hdr[u][1]);
           } else {
@@ -146,17 +196,40 @@ __device__ __forceinline__ int32_t pool_bag(const SplitLaunch &p, const uint8_t 
             offset = half_bits_to_float(hdr[u][0] >> 16);
           }
         }
+        auto dequant = [&](uint16_t h) -> float {  // h = fp16 bits of 1024 + q
+          const float f = add_f32_f16(h, -1024.0f);
+          return SO32 ? __fadd_rn(__fmul_rn(f, scale), offset) : __fmaf_rn(f, scale, offset);
+        };
 #pragma unroll
-        for (int s = 0; s < SLOTS; s++) {
-          float v;
-          if constexpr (TY == TY_F32) v = __uint_as_float(q[u][s]);
-          else if constexpr (TY == TY_F16) v = half_bits_to_float(q[u][s >> 1] >> (16 * (s & 1)));
-          else if constexpr (TY == TY_I8)
-            v = __fadd_rn(__fmul_rn((float)((q[u][s >> 2] >> (8 * (s & 3))) & 0xFFu), scale), offset);
-          else  // even column = low nibble, odd column = high nibble (InterpreterNodes.cpp:104-109)
-            v = __fadd_rn(__fmul_rn((float)((q[u][s >> 3] >> (4 * (s & 7))) & 0xFu), scale), offset);
-          const float sum = __fadd_rn(acc[s], __fmul_rn(w[u], v));
-          acc[s] = OUT16 ? __half2float(__float2half_rn(sum)) : sum;
+        for (int i = 0; i < PAIRS; i++) {
+          float ta, tb;  // the values of the pair's slots in this row
+          if constexpr (TY == TY_F32) {
+            ta = __uint_as_float(q[u][2 * i]);
+            tb = __uint_as_float(q[u][2 * i + 1]);
+          } else if constexpr (TY == TY_F16) {
+            ta = half_bits_to_float(q[u][i]);
+            tb = half_bits_to_float(q[u][i] >> 16);
+          } else if constexpr (TY == TY_I8) {
+            const uint32_t h2 = __byte_perm(q[u][i >> 1], 0x64646464u, (i & 1) ? 0x4342u : 0x4140u);
+            ta = dequant((uint16_t)(h2 & 0xFFFFu));
+            tb = dequant((uint16_t)(h2 >> 16));
+          } else {  // even column = low nibble, odd column = high nibble (InterpreterNodes.cpp:104-109)
+            const uint32_t h2 = ((q[u][i >> 2] >> (4 * (i & 3))) & 0x000F000Fu) | 0x64006400u;
+            ta = dequant((uint16_t)(h2 & 0xFFFFu));
+            tb = dequant((uint16_t)(h2 >> 16));
+          }
+          if constexpr (WEIGHTED) {  // (an unweighted bag multiplies by 1.0)
+            ta = __fmul_rn(w[u], ta);
+            tb = __fmul_rn(w[u], tb);
+          }
+          if constexpr (OUT16) {
+            const float lo = add_f32_f16((uint16_t)(acch[i] & 0xFFFFu), ta);
+            const float hi = add_f32_f16((uint16_t)(acch[i] >> 16), tb);
+            acch[i] = pack_f16x2(lo, hi);
+          } else {
+            acc[slot_a(i)] = __fadd_rn(acc[slot_a(i)], ta);
+            acc[slot_b(i)] = __fadd_rn(acc[slot_b(i)], tb);
+          }
         }
       }
     }
@@ -169,19 +242,26 @@ __device__ __forceinline__ int32_t pool_bag(const SplitLaunch &p, const uint8_t 
       if (OUT16) n = __half2float(__float2half_rn(n));
     }
 #pragma unroll
-    for (int s = 0; s < SLOTS; s++) {
-      const int32_t c = col0 + s;
-      if (c < 0 || c >= num_dims) continue;
-      const float r = mean ? __fdiv_rn(acc[s], n) : acc[s];
-      if (OUT16) reinterpret_cast<__half *>(out_row)[c] = __float2half_rn(r);
-      else reinterpret_cast<float *>(out_row)[c] = r;
+    for (int i = 0; i < PAIRS; i++) {
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int slot = e ? slot_b(i) : slot_a(i);
+        const int32_t c = col0 + slot;
+        if (c < 0 || c >= num_dims) continue;
+        if constexpr (OUT16) {
+          const __half h = __ushort_as_half((unsigned short)((acch[i] >> (16 * e)) & 0xFFFFu));
+          reinterpret_cast<__half *>(out_row)[c] = mean ? __float2half_rn(__fdiv_rn(__half2float(h), n)) : h;
+        } else {
+          reinterpret_cast<float *>(out_row)[c] = mean ? __fdiv_rn(acc[slot], n) : acc[slot];
+        }
+      }
     }
   }
   return flags;
 }
 
 template <bool OUT16, typename IdxT>
-__global__ void __launch_bounds__(kThreads) split_embedding_bags_kernel(const __grid_constant__ SplitLaunch p) {
+__global__ void __launch_bounds__(kThreads, GLOWB200_TBE_MIN_BLOCKS) split_embedding_bags_kernel(const __grid_constant__ SplitLaunch p) {
   const int t = blockIdx.y;
   const int32_t dim_start = p.dim_offsets[t], num_dims = p.dim_offsets[t + 1] - dim_start;
   const int ty = p.weights_tys[t];
@@ -204,16 +284,21 @@ __global__ void __launch_bounds__(kThreads) split_embedding_bags_kernel(const __
   const int64_t limit = placement == 3 ? p.dev_bytes : p.uvm_bytes;
   const int64_t table_at = p.wo64 ? reinterpret_cast<const int64_t *>(p.weights_offsets)[t]
                                   : (int64_t)reinterpret_cast<const int32_t *>(p.weights_offsets)[t];
-  // 16-byte chunks for rows wider than 32 lanes x 8 bytes (int4 rows keep 8: 16 columns a lane)
-  const bool wide = ty != TY_I4 && touched > 256;
-  const int cb = wide ? 16 : 8;
-  const bool vec = ((reinterpret_cast<uintptr_t>(base) + (uint64_t)table_at) % cb) == 0 && (row_bytes % cb) == 0;
-  int lpr_log2 = 0;
-  while (lpr_log2 < 5 && (cb << lpr_log2) < touched) lpr_log2++;
-  const int lpr = 1 << lpr_log2;
-  const int64_t b = (int64_t)blockIdx.x * (kThreads >> lpr_log2) + (threadIdx.x >> lpr_log2);
+  // 16-byte chunks where the table allows them (rows at 16-byte boundaries), else 8-byte chunks.
+  // A bag takes as many lanes as its rows have chunks (32 at most; wider rows take several
+  // passes), not a power of two: a 132-byte int8 row is 9 lanes, three bags to a warp.
+  const uint64_t addr = reinterpret_cast<uintptr_t>(base) + (uint64_t)table_at;
+  const bool wide = (addr % 16) == 0 && (row_bytes % 16) == 0;
+  const int cb = (wide && (ty != TY_I4 || GLOWB200_TBE_I4_WIDE)) ? 16 : 8;
+  const bool vec = wide || ((addr % 8) == 0 && (row_bytes % 8) == 0);
+  int lpr = (touched + cb - 1) / cb;
+  lpr = lpr > 32 ? 32 : lpr;
+  const int bags_per_warp = 32 / lpr;
+  const int lane = threadIdx.x & 31;
+  if (lane >= bags_per_warp * lpr) return;
+  const int64_t b = ((int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * bags_per_warp + lane / lpr;
   if (b >= p.bags_per_table) return;
-  const int gl = threadIdx.x & (lpr - 1);
+  const int gl = lane % lpr;
 
   const IdxT *offsets = reinterpret_cast<const IdxT *>(p.offsets);
   int64_t begin = (int64_t)offsets[(int64_t)t * p.bags_per_table + b];
@@ -225,16 +310,22 @@ __global__ void __launch_bounds__(kThreads) split_embedding_bags_kernel(const __
   }
   void *out_row = reinterpret_cast<char *>(p.dest) + ((size_t)(b * p.total_dims + dim_start)) * (OUT16 ? 2 : 4);
 
-#define GLOWB200_POOL(TY, CW)                                                                                     \
-  flags |= pool_bag<TY, CW, OUT16, IdxT>(p, base, limit, table_at, row_bytes, touched, num_dims, vec, begin, end, \
-                                         gl, lpr, out_row)
+#define GLOWB200_POOL3(TY, CW, WEIGHTED, SO32)                                                                     \
+  flags |= pool_bag<TY, CW, OUT16, WEIGHTED, SO32, IdxT>(p, base, limit, table_at, row_bytes, touched, num_dims, vec, \
+                                                         begin, end, gl, lpr, out_row)
+#define GLOWB200_POOL2(TY, CW, SO32) \
+  do { if (p.indice_weights != nullptr) GLOWB200_POOL3(TY, CW, true, SO32); else GLOWB200_POOL3(TY, CW, false, SO32); } while (0)
+#define GLOWB200_POOLQ(TY, CW) \
+  do { if (p.so_fp32) GLOWB200_POOL2(TY, CW, true); else GLOWB200_POOL2(TY, CW, false); } while (0)
   switch (ty) {
-    case TY_F32: if (wide) GLOWB200_POOL(TY_F32, 4); else GLOWB200_POOL(TY_F32, 2); break;
-    case TY_F16: if (wide) GLOWB200_POOL(TY_F16, 4); else GLOWB200_POOL(TY_F16, 2); break;
-    case TY_I8: if (wide) GLOWB200_POOL(TY_I8, 4); else GLOWB200_POOL(TY_I8, 2); break;
-    default: GLOWB200_POOL(TY_I4, 2); break;
+    case TY_F32: if (wide) GLOWB200_POOL2(TY_F32, 4, false); else GLOWB200_POOL2(TY_F32, 2, false); break;
+    case TY_F16: if (wide) GLOWB200_POOL2(TY_F16, 4, false); else GLOWB200_POOL2(TY_F16, 2, false); break;
+    case TY_I8: if (wide) GLOWB200_POOLQ(TY_I8, 4); else GLOWB200_POOLQ(TY_I8, 2); break;
+    default: if (wide && GLOWB200_TBE_I4_WIDE) GLOWB200_POOLQ(TY_I4, 4); else GLOWB200_POOLQ(TY_I4, 2); break;
   }
-#undef GLOWB200_POOL
+#undef GLOWB200_POOLQ
+#undef GLOWB200_POOL2
+#undef GLOWB200_POOL3
   if (p.status != nullptr && flags != 0) atomicOr(p.status, flags);
 }
 
