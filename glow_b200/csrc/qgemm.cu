@@ -234,7 +234,8 @@ struct GemmSmem {
 // double-buffered in tensor memory: while the epilogue warps drain tile i, the MMA warp is
 // already accumulating tile i+1 into the other buffer.
 // MODE 0: no input row sums take part (every weight offset is 0) and the activation is none or
-// Relu -- the common case, with a shorter drain loop; MODE 1: everything else.  One drain body per
+// Relu -- the common case, with a shorter drain loop; MODE 1: everything else; MODE 2: the
+// floating-point result of the dynamically quantized layers (GemmParams::float_out).  One drain body per
 // kernel keeps the register allocation of the 96-register budget tight.
 template <int BLOCK_N, int STAGES, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -367,6 +368,13 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       for (int c = et; c < BLOCK_N; c += kEpilogueThreads) {
         const int j = n0 + c;
         ColParams cp = {0, 0, 0, 0};
+        if constexpr (MODE == 2) {  // {unused, column scale, float bias, weight offset}
+          if (j < p.N) {
+            cp.scale = __float_as_int(p.col_scales ? p.col_scales[j] : p.u_col_scale);
+            cp.shifts = __float_as_int(p.bias_f32[j]);
+            cp.b_off = p.b_offsets ? p.b_offsets[j] : p.u_b_offset;
+          }
+        } else
         if (j < p.N) {
           const ColQuant q = col_quant(p, j);
           int32_t term = 0;
@@ -430,6 +438,34 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
+        if constexpr (MODE == 2) {
+          // float(sum) * (row scale * column scale) + bias, each operation rounded on its own
+          // (fwdDynRowwiseQuantizedFullyConnectedInstImpl, InterpreterNodes.cpp:4690-4702), then fp16
+          const float row_scale = row < p.M ? p.row_scales[row] : 0.0f;
+          uint32_t h2[kChunk / 2];
+#pragma unroll
+          for (int i2 = 0; i2 < kChunk / 2; i2++) {
+            float f[2];
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              const int4 cp = *reinterpret_cast<const int4 *>(&cols[c0 + 2 * i2 + e]);
+              const int32_t v = (int32_t)(acc[2 * i2 + e] - (uint32_t)cp.w * (uint32_t)a_sum);
+              f[e] = __fadd_rn(__fmul_rn((float)v, __fmul_rn(row_scale, __int_as_float(cp.y))), __int_as_float(cp.z));
+            }
+            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h2[i2]) : "f"(f[1]), "f"(f[0]));
+          }
+          if (row_ok) {
+            __half *orow = p.out_f16 + (size_t)row * p.N + n0 + c0;
+            if (((p.N & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.out_f16) & 15) == 0) && n0 + c0 + kChunk <= p.N) {
+#pragma unroll
+              for (int v4 = 0; v4 < kChunk / 8; v4++)
+                *reinterpret_cast<uint4 *>(orow + 8 * v4) = make_uint4(h2[4 * v4], h2[4 * v4 + 1], h2[4 * v4 + 2], h2[4 * v4 + 3]);
+            } else {
+              for (int i = 0; i < kChunk; i++)
+                if (n0 + c0 + i < p.N) orow[i] = __ushort_as_half((unsigned short)((h2[i >> 1] >> (16 * (i & 1))) & 0xffffu));
+            }
+          }
+        } else {
         uint32_t packed[kChunk / 4];
         // the requantisation: libjit_scale, ((v >> pre) * scale + rtn) >> post, then + offset, with
         // rtn = 1 << (post - 1) (0 for post 0); Relu is max(x, out_offset), no activation max(x, INT_MIN)
@@ -473,6 +509,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
               if (n0 + c0 + i < p.N) out_row[c0 + i] = (int8_t)((packed[i >> 2] >> (8 * (i & 3))) & 0xff);
           }
         }
+        }  // MODE != 2
         GEMM_TRACE(9, lt == 0 && et == 0 && c0 == 0);
         GEMM_TRACE(10, lt == 0 && et == 0 && c0 == 32);
       }
@@ -540,6 +577,21 @@ __global__ void __launch_bounds__(256) i8_gemm_requant_any_kernel(const int8_t *
                              q.bias_scale, 0);
   p.out[(size_t)i * p.N + j] =
       (int8_t)clip_i8(activation_i32(scale32((int32_t)sum, q.out_pre, q.out_post, q.out_scale, p.out_offset), p));
+}
+
+// The floating-point result (GemmParams::float_out) for any shape: b element (j, k) sits at
+// b[j * b_stride_j + k * b_stride_k], so both the [N, K] and the [K, N] form of the weights serve.
+__global__ void __launch_bounds__(256) i8_gemm_float_any_kernel(const int8_t *__restrict__ a, const int8_t *__restrict__ b,
+                                                                 int64_t b_stride_j, int64_t b_stride_k,
+                                                                 const __grid_constant__ GemmParams p) {
+  const int j = blockIdx.x * 16 + (threadIdx.x & 15), i = blockIdx.y * 16 + (threadIdx.x >> 4);
+  if (i >= p.M || j >= p.N) return;
+  const int32_t b_off = p.b_offsets ? p.b_offsets[j] : p.u_b_offset;
+  uint32_t sum = 0;
+  for (int k = 0; k < p.k_corr; k++)
+    sum += (uint32_t)(((int32_t)b[j * b_stride_j + k * b_stride_k] - b_off) * (int32_t)a[(size_t)i * p.K + k]);
+  const float mm = __fmul_rn(p.row_scales[i], p.col_scales ? p.col_scales[j] : p.u_col_scale);
+  p.out_f16[(size_t)i * p.N + j] = __float2half_rn(__fadd_rn(__fmul_rn((float)(int32_t)sum, mm), p.bias_f32[j]));
 }
 
 // [R, C] int8 -> [C, R] int8 (32x32 tiles through shared memory)
@@ -611,6 +663,7 @@ int launch_tile_mode(const CUtensorMap &ma, const CUtensorMap &mb, const GemmPar
 
 template <int BLOCK_N, int STAGES>
 int launch_tile_kernel(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, cudaStream_t s) {
+  if (p.float_out) return launch_tile_mode<BLOCK_N, STAGES, 2>(ma, mb, p, s);
   if (p.a_row_sums == nullptr && p.act_type <= 1) return launch_tile_mode<BLOCK_N, STAGES, 0>(ma, mb, p, s);
   return launch_tile_mode<BLOCK_N, STAGES, 1>(ma, mb, p, s);
 }
@@ -652,7 +705,8 @@ int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_ro
   const bool tc = !force_any && p.K > 0 && (p.K % 16) == 0 && ptr16(a) && ptr16(b);
   if (!tc) {
     dim3 grid((p.N + 15) / 16, (p.M + 15) / 16);
-    i8_gemm_requant_any_kernel<<<grid, 256, 0, s>>>(a, b, p);
+    if (p.float_out) i8_gemm_float_any_kernel<<<grid, 256, 0, s>>>(a, b, p.K, 1, p);
+    else i8_gemm_requant_any_kernel<<<grid, 256, 0, s>>>(a, b, p);
     GLOWB200_CUDA_OK(cudaGetLastError());
     return GLOWB200_OK;
   }
@@ -661,14 +715,16 @@ int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_ro
     return set_error(GLOWB200_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", ws_bytes, need);
   int32_t *bs = reinterpret_cast<int32_t *>(ws);
   int32_t *as = reinterpret_cast<int32_t *>(reinterpret_cast<uint8_t *>(ws) + align_up((size_t)p.N * 4, 256));
-  if (b_row_sums_in) {
+  if (b_row_sums_in || p.float_out) {  // (the float result has no input offset: the sums are never read)
     p.b_row_sums = b_row_sums_in;
   } else {
     i8_row_sums_kernel<<<(p.N + 7) / 8, 256, 0, s>>>(b, p.N, p.K, bs);
     GLOWB200_CUDA_OK(cudaGetLastError());
     p.b_row_sums = bs;
   }
-  if (!b_offsets_zero) {
+  if (p.float_out) {
+    if (b_offsets_zero) p.a_row_sums = nullptr;  // else the caller's, written while it quantized the rows
+  } else if (!b_offsets_zero) {
     i8_row_sums_kernel<<<(p.M + 7) / 8, 256, 0, s>>>(a, p.M, p.K, as);
     GLOWB200_CUDA_OK(cudaGetLastError());
     p.a_row_sums = as;
@@ -690,6 +746,22 @@ int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_ro
   if (int rc = make_map(&ma, a, p.M, p.K, kBlockM)) return rc;
   if (int rc = make_map(&mb, b, p.N, p.K, 64)) return rc;
   return launch_tile_kernel<64, 6>(ma, mb, p, s);
+}
+
+int run_gemm_float_any(const GemmParams &p, const int8_t *a, const int8_t *b_kn, cudaStream_t s) {
+  if (p.M == 0 || p.N == 0) return GLOWB200_OK;
+  dim3 grid((p.N + 15) / 16, (p.M + 15) / 16);
+  i8_gemm_float_any_kernel<<<grid, 256, 0, s>>>(a, b_kn, 1, p.N, p);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+int transpose_i8(const int8_t *in_rc, int8_t *out_cr, int R, int C, cudaStream_t s) {
+  if (R == 0 || C == 0) return GLOWB200_OK;
+  dim3 grid((C + 31) / 32, (R + 31) / 32), block(32, 8);
+  i8_transpose_kernel<<<grid, block, 0, s>>>(in_rc, out_cr, R, C);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
 }
 
 namespace {

@@ -33,6 +33,14 @@ struct GemmParams {
   int conv_row_off[32];
   int conv_hpwp, conv_wp, conv_oh, conv_ow;
   int32_t u_b_offset, u_bias_pre, u_bias_post, u_bias_scale, u_out_pre, u_out_post, u_out_scale;
+  // Floating-point result (dynamically quantized layers; float_out != 0): out_f16[i,j] =
+  // fp16(float(sum_ij) * (row_scales[i] * col_scales[j]) + bias_f32[j]), sum_ij the int32 dot
+  // product of (A - 0) and (B - b_offsets[j]); every product and the sum are rounded separately.
+  // col_scales / b_offsets may be NULL: u_col_scale / u_b_offset for every column.
+  int float_out;
+  __half *out_f16;
+  const float *row_scales, *col_scales, *bias_f32;
+  float u_col_scale;
 };
 
 struct ColQuant {
@@ -70,6 +78,11 @@ int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_ro
 // row of b (a multiple of 128).  Weight offsets must all be zero (no input row sums).
 int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int C, const int8_t *b,
                           const int32_t *b_row_sums, cudaStream_t s);
+
+// The float-result contraction for any shape with the weights in their [K, N] form.
+int run_gemm_float_any(const GemmParams &p, const int8_t *a, const int8_t *b_kn, cudaStream_t s);
+// [R, C] int8 -> [C, R] int8
+int transpose_i8(const int8_t *in_rc, int8_t *out_cr, int R, int C, cudaStream_t s);
 
 inline size_t i8_gemm_core_workspace_bytes(int64_t M, int64_t N) {
   return align_up((size_t)N * 4, 256) + align_up((size_t)M * 4, 256);

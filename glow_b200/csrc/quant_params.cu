@@ -9,6 +9,7 @@
 #include <limits>
 
 #include "common.cuh"
+#include "quant_math.cuh"
 
 namespace glowb200 {
 
@@ -59,35 +60,10 @@ namespace glowb200 {
 // 3 SymmetricWithPower2Scale (include/glow/Quantization/Base/Base.h Schema).
 void choose_quantization_params(float min, float max, int schema, int64_t qmin, int64_t qmax, float &scale_out,
                                 int32_t &offset_out) {
-  min = std::min(min, 0.f);
-  max = std::max(max, 0.f);
-  if (schema == 2) {
-    if (!(min >= 0.f)) schema = 1;
-  }
-  if (schema == 1 || schema == 3) {
-    const double rmin = min / (double)qmin;
-    const double rmax = max / (double)qmax;
-    if (rmin > rmax) max = (float)(rmin * qmax);
-    else min = (float)(rmax * qmin);
-  }
-  min = std::max(min, std::numeric_limits<float>::lowest());
-  max = std::min(max, std::numeric_limits<float>::max());
-  double scale = ((double)max - min) / ((double)qmax - qmin);
-  if (scale == 0) scale = 0.1;
-  const double zp_from_min = qmin - min / scale;
-  const double zp_from_max = qmax - max / scale;
-  const double err_min = std::abs((double)qmin) + std::abs(min / scale);
-  const double err_max = std::abs((double)qmax) + std::abs(max / scale);
-  double zp = err_min < err_max ? zp_from_min : zp_from_max;
-  const float difference = std::abs(max + min);
-  if (difference <= std::numeric_limits<float>::epsilon()) zp = 0;
-  int32_t nudged;
-  if (zp < qmin) nudged = (int32_t)qmin;
-  else if (zp > qmax) nudged = (int32_t)qmax;
-  else nudged = static_cast<int32_t>(std::round(zp));
+  double scale;
+  choose_quantization_params_basic(min, max, schema, qmin, qmax, scale, offset_out);
   if (schema == 3) scale = std::exp2(std::ceil(std::log2(scale)));
   scale_out = static_cast<float>(scale);
-  offset_out = nudged;
 }
 
 // quantization::quantize<int8_t> (include/glow/Quantization/Base/Base.h:322-329)

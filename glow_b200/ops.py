@@ -445,6 +445,41 @@ def matmul_i8(lhs, rhs, out_offset, lhs_offset, rhs_offset, out_triple, *, flags
     return out
 
 
+def dynamic_fc_workspace_bytes(M, K, N):
+    return int(_lib.lib().glowb200_dynamic_fc_workspace_bytes(M, K, N))
+
+
+def dynamic_rowwise_quantized_fc(inp, weights, bias, scales, offsets, *, weights_transposed=None, flags=0, out=None,
+                                 workspace=None, status=None):
+    """DynamicRowwiseQuantizedFullyConnected: inp [M,K] fp16, weights [K,N] int8 (or weights_transposed
+    [N,K]), bias / scales fp32 [N], offsets int32 [N]; result [M,N] fp16."""
+    _cuda(inp, "inp", (torch.float16,))
+    M, K = inp.shape
+    N = bias.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=inp.device)
+    ws = _workspace(workspace, dynamic_fc_workspace_bytes(M, K, N), inp.device)
+    check(_lib.lib().glowb200_dynamic_rowwise_quantized_fc(
+        _p(out), _p(inp), _p(weights), _p(bias), _p(scales), _p(offsets), M, K, N, _p(weights_transposed), int(flags),
+        _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
+def dynamic_quantized_fc(inp, weights, bias, weights_scale, weights_offset, *, weights_transposed=None, flags=0,
+                         out=None, workspace=None, status=None):
+    """DynamicQuantizedFullyConnected: as above with one scale / offset for the whole weights tensor."""
+    _cuda(inp, "inp", (torch.float16,))
+    M, K = inp.shape
+    N = bias.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=inp.device)
+    ws = _workspace(workspace, dynamic_fc_workspace_bytes(M, K, N), inp.device)
+    check(_lib.lib().glowb200_dynamic_quantized_fc(
+        _p(out), _p(inp), _p(weights), _p(bias), float(weights_scale), int(weights_offset), M, K, N,
+        _p(weights_transposed), int(flags), _p(ws), ws.numel(), _p(status), _stream()))
+    return out
+
+
 # ------------------------------------------------------------------------------------------
 # Int8 convolution and glue operators
 # ------------------------------------------------------------------------------------------

@@ -48,7 +48,8 @@ extern "C" {
 #define GLOWB200_STATUS_NEGATIVE_LENGTH 4    /* a negative length: treated as 0                   */
 #define GLOWB200_STATUS_BAD_OFFSETS 8        /* offsets not monotone / out of range: bag is empty */
 #define GLOWB200_STATUS_WAIT_TIMEOUT 16      /* a bounded device-side wait gave up                */
-#define GLOWB200_STATUS_UNSUPPORTED_TABLE 32 /* split-embedding table of an unsupported type      */
+#define GLOWB200_STATUS_UNSUPPORTED_TABLE 32 /* split-embedding table of an unsupported type; a   */
+                                             /* dynamic-FC row whose zero point is not 0          */
 
 /* Fused-rowwise table kinds (glow::ElemKind, include/glow/Base/Type.h:424-433).  A row is the
  * quantized payload followed by scale then offset (include/glow/Base/Tensor.h:1585-1607). */
@@ -352,6 +353,31 @@ int glowb200_fc_i8_i32(int8_t *out, const int8_t *in, const int8_t *weights, con
                        int32_t out_scale, const int8_t *weights_transposed, int flags,
                        void *workspace, size_t workspace_bytes, int32_t *status,
                        glowb200_stream_t stream);
+
+/* DynamicRowwiseQuantizedFullyConnected / DynamicQuantizedFullyConnected.
+ * Replace fwdDynamicRowwiseQuantizedFullyConnectedInst and fwdDynamicQuantizedFullyConnectedInst
+ * (lib/Backends/Interpreter/InterpreterNodes.cpp:4677-4790; symmetric, per batch element -- the
+ * only mode the reference implements).  in [M,K] fp16; weights [K,N] int8 as the node holds
+ * them (weights_transposed: the [N,K] form, e.g. transposed once at load time; either may be
+ * NULL); bias [N] fp32; scales [N] fp32 and offsets [N] int32 per output column (the rowwise
+ * node) or one weights_scale / weights_offset (the per-tensor node); out [M,N] fp16.
+ * Every input row is quantized to int8 with its own Symmetric parameters, the int32 sums come
+ * from the tensor cores, and out = fp16(float(sum) * (row scale * scales[j]) + bias[j]) with the
+ * reference's roundings: results are bit-identical to the Interpreter's.
+ * flags: GLOWB200_FC_WEIGHT_OFFSETS_ZERO, GLOWB200_FC_FORCE_ANY_SHAPE_KERNEL.  The workspace
+ * (256-byte aligned) must hold glowb200_dynamic_fc_workspace_bytes(M, K, N). */
+size_t glowb200_dynamic_fc_workspace_bytes(int64_t M, int64_t K, int64_t N);
+int glowb200_dynamic_rowwise_quantized_fc(void *out, const void *in, const int8_t *weights,
+                                          const float *bias, const float *scales,
+                                          const int32_t *offsets, int64_t M, int64_t K, int64_t N,
+                                          const int8_t *weights_transposed, int flags,
+                                          void *workspace, size_t workspace_bytes, int32_t *status,
+                                          glowb200_stream_t stream);
+int glowb200_dynamic_quantized_fc(void *out, const void *in, const int8_t *weights,
+                                  const float *bias, float weights_scale, int32_t weights_offset,
+                                  int64_t M, int64_t K, int64_t N, const int8_t *weights_transposed,
+                                  int flags, void *workspace, size_t workspace_bytes,
+                                  int32_t *status, glowb200_stream_t stream);
 
 /* MatMul, int8.  Replaces libjit_matmul_i8 (libjit_matmul.cpp:353-371; scalars derived at
  * LLVMIRGen.cpp:2098-2137).  lhs [M,K], rhs [K,N]. */

@@ -691,6 +691,42 @@ ORC_API void orc_tensor_rowwise_quantize_i8(const float *in, int64_t rows, int64
   }
 }
 
+/* fwdDynRowwiseQuantizedFullyConnectedInstPreimpl / ...InstImpl: InterpreterNodes.cpp:4677-4749
+ * (and fwdDynamicQuantizedFullyConnectedInst, :4766-4790, which repeats the weights' type-level
+ * scale and offset for every column).  in [M,K] fp16, weights [K,N] int8, out [M,N] fp16.
+ * Every input row is quantized on its own: Symmetric int8 parameters from its min and max, then
+ * quantization::quantize (Base.h:322-329). */
+ORC_API void orc_dynamic_rowwise_quantized_fc(uint16_t *out, const uint16_t *in, const int8_t *w, const float *bias,
+                                              const float *scales, const int32_t *offsets, int64_t M, int64_t K,
+                                              int64_t N) {
+  int8_t *q = (int8_t *)malloc((size_t)(K > 0 ? K : 1));
+  for (int64_t i = 0; i < M; i++) {
+    float mn = orc_f16_to_f32(in[i * K]), mx = mn;
+    for (int64_t k = 1; k < K; k++) {
+      const float v = orc_f16_to_f32(in[i * K + k]);
+      if (v < mn) mn = v;
+      if (v > mx) mx = v;
+    }
+    float in_scale;
+    int32_t in_offset;
+    orc_choose_quantization_params(mn, mx, 1, -128, 127, &in_scale, &in_offset);
+    for (int64_t k = 0; k < K; k++) {
+      const float t = orc_f16_to_f32(in[i * K + k]) / in_scale + (float)in_offset;
+      const int64_t v = (int64_t)nearbyintf(t);
+      q[k] = (int8_t)(v < -128 ? -128 : (v > 127 ? 127 : v));
+    }
+    for (int64_t j = 0; j < N; j++) {
+      const float mm = in_scale * scales[j];
+      int32_t sum = 0;
+      for (int64_t k = 0; k < K; k++)
+        sum = (int32_t)((uint32_t)sum + (uint32_t)(((int32_t)w[k * N + j] - offsets[j]) * ((int32_t)q[k] - in_offset)));
+      volatile float prod = (float)sum * mm;   /* product and sum rounded separately */
+      out[i * N + j] = orc_f32_to_f16(prod + bias[j]);
+    }
+  }
+  free(q);
+}
+
 /* Pairwise-dot feature interaction of the benchmark's recommendation model: no single kernel in
  * the reference (it composes Concat/Reshape/BatchMatMul, tests/unittests/
  * RecommendationSystemTest.cpp:640-680); this restates the definition the CUDA kernel

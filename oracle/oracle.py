@@ -235,6 +235,19 @@ def int_nbit_split_embedding_bags(dev_weights, uvm_weights, placements, weights_
     return dest
 
 
+def dynamic_rowwise_quantized_fc(inp, weights_kn, bias, scales, offsets):
+    """DynamicRowwiseQuantizedFullyConnected (InterpreterNodes.cpp:4677-4749): fp16 [M,K] x int8 [K,N]."""
+    inp = _c(inp, np.float16)
+    w = _c(weights_kn, np.int8)
+    M, K = inp.shape
+    N = w.shape[1]
+    bias, scales, offsets = _c(bias, np.float32), _c(scales, np.float32), _c(offsets, np.int32)
+    out = np.empty((M, N), np.float16)
+    lib().orc_dynamic_rowwise_quantized_fc(_ptr(out), _ptr(inp), _ptr(w), _ptr(bias), _ptr(scales), _ptr(offsets),
+                                           _i64(M), _i64(K), _i64(N))
+    return out
+
+
 def sparse_lengths_weighted_sum_f32(data, weights, indices, lengths):
     data = _c(data, np.float32)
     weights = _c(weights, np.float32)
