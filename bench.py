@@ -46,11 +46,12 @@ def parse():
     ap.add_argument("--requests", type=int, default=4, help="distinct pre-generated batches rotated over the steps")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="slws", choices=["slws", "int8_fc", "slws4", "dlrm", "resnet50", "tbe"],
+    ap.add_argument("--workload", default="slws", choices=["slws", "int8_fc", "slws4", "dlrm", "resnet50", "tbe", "dyn_fc"],
                     help="slws: the headline gather-pool line (default); int8_fc: the rowwise int8 FC line; "
                          "slws4: the 4-bit fused-rowwise sweep point selected by --dim; dlrm / resnet50: the "
                          "recommendation model / the int8 ResNet-50 alone (the default line carries both as extras); "
-                         "tbe: table-batched embedding bags (IntNBitSplitEmbeddingBags) over tables of --tbe-type")
+                         "tbe: table-batched embedding bags (IntNBitSplitEmbeddingBags) over tables of --tbe-type; "
+                         "dyn_fc: DynamicRowwiseQuantizedFullyConnected at the shape of the int8 FC line")
     ap.add_argument("--tbe-type", default="int4", choices=["fp16", "int8", "int4"], help="tbe: element type of the tables")
     ap.add_argument("--tbe-out", default="fp16", choices=["fp16", "fp32"], help="tbe: element type of the result")
     ap.add_argument("--dim", type=int, default=128, help="slws4: embedding width (32, 64, 128 or 256)")
@@ -778,6 +779,86 @@ def run_slws4_line(args):
         dist.destroy_process_group()
 
 
+def run_dyn_fc_line(args):
+    """--workload dyn_fc: DynamicRowwiseQuantizedFullyConnected, fp16 [2048, 4096] activations
+    N(0,1) x int8 [4096, 4096] weights (held in their [N, K] form), fp16 result.  A step is the row
+    quantiser plus the contraction; operations counted are the contraction's 2*M*N*K.  At N > 1
+    every rank runs its own batch (replicas)."""
+    import torch
+    import torch.distributed as dist
+    from glow_b200 import ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    M, K, N = 2048, 4096, 4096
+    g = torch.Generator(device=dev).manual_seed(0x610B200 + rank)
+    R = 8   # rotating inputs and results: 8 x (16 + 16) MB, larger than L2 together with the weights
+    xs = [torch.randn((M, K), device=dev, generator=g).to(torch.float16) for _ in range(R)]
+    outs = [torch.empty((M, N), dtype=torch.float16, device=dev) for _ in range(R)]
+    wt = torch.randint(-127, 128, (N, K), device=dev, generator=g, dtype=torch.int8)
+    bias = torch.randn(N, device=dev, generator=g)
+    scales = torch.empty(N, device=dev).uniform_(0.001, 0.02, generator=g)
+    offsets = torch.zeros(N, dtype=torch.int32, device=dev)
+    ws = torch.empty(ops.dynamic_fc_workspace_bytes(M, K, N), dtype=torch.uint8, device=dev)
+    status = ops.new_status(dev)
+
+    def step(i):
+        ops.dynamic_rowwise_quantized_fc(xs[i % R], None, bias, scales, offsets, weights_transposed=wt,
+                                         flags=ops.FC_WEIGHT_OFFSETS_ZERO, out=outs[i % R], workspace=ws, status=status)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
+    # the K steps as one CUDA graph: two short launches per step would otherwise be paced by the host
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(args.steps):
+            step(i)
+    graph.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    t_end = time.time() + 1.0
+    while len(sampler.lines) < 8 and time.time() < t_end:
+        step(0)
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    assert int(status.item()) == 0
+    tm = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        peak, src = measured_peak_int8()
+        per_gpu = 2.0 * M * N * K / (float(tm[0]) * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "dynamic_quantized_fc_tops", "value": per_gpu * world, "unit": "TOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(tm[0]), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 -> s8 x s8 -> s32 -> f16", "data": "synthetic",
+            "config": {"workload": "DynamicRowwiseQuantizedFullyConnected: M=2048 K=4096 N=4096, fp16 activations N(0,1) "
+                                   "quantized per row on the device, int8 weights U[-127,127], fp32 bias and column scales",
+                       "l2_policy": "8 rotating inputs and results (256 MB) between repeats"},
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TOP/s", "frac": per_gpu / peak,
+                         "peak_source": src, "traffic": None, "kernel": "dyn_quantize_rows_kernel + i8_gemm_requant_kernel<256,4,2>"},
+            "gpu_launches": 2 * args.steps, "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_tbe_line(args):
     """--workload tbe: table-batched embedding bags (IntNBitSplitEmbeddingBags), the shape of the
     reference's tests/benchmark/TBEBench.cpp: T tables of 10,000,000 rows x --dim columns of
@@ -1036,6 +1117,8 @@ def main():
         return run_model_line(args)
     if args.workload == "tbe":
         return run_tbe_line(args)
+    if args.workload == "dyn_fc":
+        return run_dyn_fc_line(args)
 
     import torch
     import torch.distributed as dist

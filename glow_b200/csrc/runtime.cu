@@ -172,6 +172,12 @@ extern "C" int glowb200_function_add_instruction(glowb200_function *f, int kind,
 //  SLWS_F32    ops {dest, data, weights (-1: unweighted), indices, lengths}  ia {rows, line, segments, num_indices, idx64}
 //  RWQ_SLWS    ops {dest, data, scales, offsets, weights, indices, lengths}  ia {rows, line, segments, num_indices, idx64}
 //  EMBEDDING_BAG ops {dest, data, weights, indices, offsets}  ia {kind, rows, in_line, out_line, num_offsets, num_indices, idx64, has_end_offset, out_fp16, fp16_acc}
+//  SPLIT_EMBEDDING ops {dest, dev_weights, uvm_weights, placements, weights_offsets, weights_tys, dim_offsets, indices, offsets,
+//                   indice_weights (-1: unweighted)}
+//              ia {dev_bytes, uvm_bytes, num_tables, total_dims, num_indices, bags_per_table, idx64, weights_offsets_are_int64,
+//                  pooling_mode, indice_weights_are_fp16, out_fp16, scale_offset_is_fp32, row_alignment}
+//  DYN_QUANTIZED_FC ops {dest (fp16), src (fp16), weights [K,N], bias (fp32), scales (-1: per tensor), offsets (-1: per tensor)}
+//              ia {M, K, N, weights_offset}  fa {weights_scale}
 extern "C" int glowb200_function_compile(glowb200_function *f) {
   if (!f || f->compiled) return set_error(GLOWB200_RUNTIME_ERROR, "function is NULL or already compiled");
   size_t ws = 256;
@@ -291,6 +297,15 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
       case GLOWB200_INSTR_EMBEDDING_BAG:
         if (!need(5, 10, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed EMBEDDING_BAG", ii);
         ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[4], 1));
+        break;
+      case GLOWB200_INSTR_SPLIT_EMBEDDING:
+        if (!need(10, 13, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed SPLIT_EMBEDDING", ii);
+        break;
+      case GLOWB200_INSTR_DYN_QUANTIZED_FC:
+        if (!need(6, 4, 1)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed DYN_QUANTIZED_FC", ii);
+        if ((in.ops[4] < 0) != (in.ops[5] < 0))
+          return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: DYN_QUANTIZED_FC needs both scales and offsets, or neither", ii);
+        ws = std::max(ws, glowb200_dynamic_fc_workspace_bytes(in.ia[0], in.ia[1], in.ia[2]));
         break;
       default: return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: unsupported kind %d (isOpSupported would refuse the node)", ii, in.kind);
     }
@@ -557,6 +572,23 @@ int execute(glowb200_device_manager *dm, LoadedNetwork &n) {
             (const float *)ptr(in.ops[4]), ptr(in.ops[5]), (int)a[4], (const int32_t *)ptr(in.ops[6]), a[2], a[3], a[1], n.workspace,
             f->workspace_bytes, dm->status_dev, st);
         break;
+      case GLOWB200_INSTR_SPLIT_EMBEDDING:
+        rc = glowb200_int_nbit_split_embedding_bags(
+            ptr(in.ops[0]), ptr(in.ops[1]), a[0], ptr(in.ops[2]), a[1], (const int32_t *)ptr(in.ops[3]), ptr(in.ops[4]), (int)a[7],
+            (const uint8_t *)ptr(in.ops[5]), (const int32_t *)ptr(in.ops[6]), a[2], a[3], ptr(in.ops[7]), ptr(in.ops[8]), (int)a[6],
+            a[4], a[5], (int)a[8], ptr(in.ops[9]), (int)a[9], (int)a[10], (int)a[11], (int)a[12], dm->status_dev, st);
+        break;
+      case GLOWB200_INSTR_DYN_QUANTIZED_FC:
+        if (in.ops[4] >= 0)
+          rc = glowb200_dynamic_rowwise_quantized_fc(ptr(in.ops[0]), ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
+                                                     (const float *)ptr(in.ops[3]), (const float *)ptr(in.ops[4]),
+                                                     (const int32_t *)ptr(in.ops[5]), a[0], a[1], a[2], nullptr, 0, n.workspace,
+                                                     f->workspace_bytes, dm->status_dev, st);
+        else
+          rc = glowb200_dynamic_quantized_fc(ptr(in.ops[0]), ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
+                                             (const float *)ptr(in.ops[3]), in.fa[0], (int32_t)a[3], a[0], a[1], a[2], nullptr, 0,
+                                             n.workspace, f->workspace_bytes, dm->status_dev, st);
+        break;
       case GLOWB200_INSTR_EMBEDDING_BAG:
         rc = glowb200_embedding_bag_byte_rowwise_offsets(ptr(in.ops[0]), ptr(in.ops[1]), (int)a[0], a[1], ptr(in.ops[2]), ptr(in.ops[3]),
                                                          ptr(in.ops[4]), (int)a[6], a[4], a[5], a[2], a[3], (int)a[7], (int)a[8],
@@ -595,7 +627,7 @@ int finish_request(glowb200_device_manager *dm, const char *name) {
   const cudaError_t e = cudaStreamSynchronize(dm->stream);
   if (e != cudaSuccess) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "device error while running %s: %s", name, cudaGetErrorString(e));
   if (status & GLOWB200_STATUS_WAIT_TIMEOUT) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "a device-side wait gave up while running %s", name);
-  if (status) return set_error(GLOWB200_RUNTIME_ERROR, "invalid sparse input to %s (status bits 0x%x: index out of range 1, lengths overrun 2, negative length 4, bad offsets 8)", name, status);
+  if (status) return set_error(GLOWB200_RUNTIME_ERROR, "invalid sparse input to %s (status bits 0x%x: index out of range 1, lengths overrun 2, negative length 4, bad offsets 8, unsupported table 32)", name, status);
   return GLOWB200_OK;
 }
 }  // namespace

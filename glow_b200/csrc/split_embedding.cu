@@ -291,8 +291,12 @@ __global__ void __launch_bounds__(kThreads, GLOWB200_TBE_MIN_BLOCKS) split_embed
   const bool wide = (addr % 16) == 0 && (row_bytes % 16) == 0;
   const int cb = (wide && (ty != TY_I4 || GLOWB200_TBE_I4_WIDE)) ? 16 : 8;
   const bool vec = wide || ((addr % 8) == 0 && (row_bytes % 8) == 0);
-  int lpr = (touched + cb - 1) / cb;
-  lpr = lpr > 32 ? 32 : lpr;
+  const int chunks = (touched + cb - 1) / cb;
+  int lpr = chunks > 32 ? 32 : chunks;
+  // Rows of a little more than half a warp (17 chunks: a 260-byte int8 row) would leave the other
+  // half idle: half as many lanes then walk the bag twice, one half of the row per pass, when that
+  // puts over 2.4 times as many bags into the warp.
+  if (chunks <= 32 && 32 / ((chunks + 1) / 2) * 5 > 32 / lpr * 12) lpr = (chunks + 1) / 2;
   const int bags_per_warp = 32 / lpr;
   const int lane = threadIdx.x & 31;
   if (lane >= bags_per_warp * lpr) return;

@@ -15,7 +15,7 @@ from ._lib import GlowB200Error
 CONSTANT, PLACEHOLDER, ACTIVATION = 0, 1, 2
 (FRWQ_SLWS, RWQ_FC, CWQ_CONV, ADD, MAXSPLAT, QUANTIZE, DEQUANTIZE, MAXPOOL, AVGPOOL, TRANSPOSE, COPY) = range(1, 12)
 (ADD_MAXSPLAT, RELU, RESCALE, FC_I8, MATMUL_I8, SPLAT, INSERT_TENSOR, PAIRWISE_DOT, SLWS_F32, RWQ_SLWS,
- EMBEDDING_BAG) = range(12, 23)
+ EMBEDDING_BAG, SPLIT_EMBEDDING, DYN_QUANTIZED_FC) = range(12, 25)
 
 RUNTIME_ERROR, OUT_OF_DEVICE_MEMORY, NET_NOT_FOUND, DEVICE_NONRECOVERABLE = 101, 102, 103, 104
 
@@ -156,6 +156,24 @@ class Function:
         self.instruction(EMBEDDING_BAG, [dest, data, weights, indices, offsets],
                          [kind, rows, in_line, out_line, num_offsets, num_indices, int(idx64), int(has_end_offset),
                           int(out_fp16), int(fp16_acc)])
+
+    def split_embedding_bags(self, dest, dev_weights, uvm_weights, placements, weights_offsets, weights_tys, dim_offsets,
+                             indices, offsets, indice_weights=None, *, dev_bytes, uvm_bytes, num_tables, total_dims,
+                             num_indices, bags_per_table, idx64=False, weights_offsets_are_int64=False, pooling_mode=0,
+                             indice_weights_are_fp16=False, out_fp16=False, scale_offset_is_fp32=False, row_alignment=16):
+        """IntNBitSplitEmbeddingBags; with indice_weights: IntNBitSplitEmbeddingWeightedBags."""
+        self.instruction(SPLIT_EMBEDDING,
+                         [dest, dev_weights, uvm_weights, placements, weights_offsets, weights_tys, dim_offsets, indices,
+                          offsets, -1 if indice_weights is None else indice_weights],
+                         [dev_bytes, uvm_bytes, num_tables, total_dims, num_indices, bags_per_table, int(idx64),
+                          int(weights_offsets_are_int64), pooling_mode, int(indice_weights_are_fp16), int(out_fp16),
+                          int(scale_offset_is_fp32), row_alignment])
+
+    def dynamic_quantized_fc(self, dest, src, weights, bias, scales=None, offsets=None, *, M, K, N, weights_tqp=(0.0, 0)):
+        """DynamicRowwiseQuantizedFullyConnected (scales / offsets per output column) or, without them,
+        DynamicQuantizedFullyConnected (weights_tqp = the weights' scale and offset).  weights: int8 [K, N]."""
+        self.instruction(DYN_QUANTIZED_FC, [dest, src, weights, bias, -1 if scales is None else scales,
+                                            -1 if offsets is None else offsets], [M, K, N, weights_tqp[1]], [weights_tqp[0]])
 
     def compile(self):
         _check(_lib.lib().glowb200_function_compile(self.h))

@@ -552,6 +552,8 @@ int glowb200_peer_buffer_destroy(void *device_ptr);
 #define GLOWB200_INSTR_SLWS_F32 20       /* SparseLengths(Weighted)Sum over an fp32 table */
 #define GLOWB200_INSTR_RWQ_SLWS 21       /* RowwiseQuantizedSparseLengthsWeightedSum */
 #define GLOWB200_INSTR_EMBEDDING_BAG 22  /* EmbeddingBagByteRowwiseOffsets */
+#define GLOWB200_INSTR_SPLIT_EMBEDDING 23 /* IntNBitSplitEmbedding(Weighted)Bags */
+#define GLOWB200_INSTR_DYN_QUANTIZED_FC 24 /* Dynamic(Rowwise)QuantizedFullyConnected */
 
 typedef struct glowb200_function glowb200_function;
 typedef struct glowb200_device_manager glowb200_device_manager;

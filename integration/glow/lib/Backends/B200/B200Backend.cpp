@@ -40,6 +40,15 @@ bool B200Backend::isOpSupported(const NodeInfo &NI) const {
   case Kinded::Kind::FusedRowwiseQuantizedSparseLengthsWeightedSumNodeKind:
     // all four fused kinds, fp32 or fp16 result, int32/int64 indices, int32 lengths
     return NI.getInElemTy(FusedRowwiseQuantizedSparseLengthsWeightedSumNode::LengthsIdx) == ElemKind::Int32ITy;
+  case Kinded::Kind::IntNBitSplitEmbeddingBagsNodeKind:
+  case Kinded::Kind::IntNBitSplitEmbeddingWeightedBagsNodeKind:
+    // int32 / int64 indices and offsets of one type; fp32 or fp16 result
+    return NI.getInElemTy(IntNBitSplitEmbeddingBagsNode::IndicesIdx) == NI.getInElemTy(IntNBitSplitEmbeddingBagsNode::OffsetsIdx);
+  case Kinded::Kind::DynamicRowwiseQuantizedFullyConnectedNodeKind:
+  case Kinded::Kind::DynamicQuantizedFullyConnectedNodeKind:
+    // fp16 activations and result, int8 weights, fp32 bias (what the Interpreter implements)
+    return NI.getInElemTy(DynamicQuantizedFullyConnectedNode::InputIdx) == ElemKind::Float16Ty &&
+           NI.getOutElemTy(DynamicQuantizedFullyConnectedNode::ResultIdx) == ElemKind::Float16Ty;
   case Kinded::Kind::EmbeddingBagByteRowwiseOffsetsNodeKind:
   case Kinded::Kind::RowwiseQuantizedFullyConnectedNodeKind:
   case Kinded::Kind::ChannelwiseQuantizedConvolutionNodeKind:

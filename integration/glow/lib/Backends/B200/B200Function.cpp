@@ -1,6 +1,7 @@
 #include "B200Function.h"
 
 #include "glow/Graph/Graph.h"
+#include "glow/Flags/Flags.h"
 #include "glow/IR/Instrs.h"
 #include "glow/Support/Error.h"
 
@@ -178,6 +179,49 @@ Error B200Function::translate(const Module *module) {
                               N->getIndices()->getElementType() == ElemKind::Int64ITy, N->getHasEndOffset(),
                               N->getDest()->getElementType() == ElemKind::Float16Ty, N->getUseFP16Accumulation()};
       RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_EMBEDDING_BAG, ops, 5, ia, 10, nullptr, 0)));
+      break;
+    }
+    case Kinded::Kind::IntNBitSplitEmbeddingBagsInstKind:
+    case Kinded::Kind::IntNBitSplitEmbeddingWeightedBagsInstKind: {
+      // the two instructions differ by the IndiceWeight operand only
+      auto *W = llvm::dyn_cast<IntNBitSplitEmbeddingWeightedBagsInst>(&I);
+      auto *U = llvm::dyn_cast<IntNBitSplitEmbeddingBagsInst>(&I);
+      Value *dest = W ? W->getDest() : U->getDest(), *dev = W ? W->getDevWeights() : U->getDevWeights();
+      Value *uvm = W ? W->getUvmWeights() : U->getUvmWeights(), *pl = W ? W->getWeightsPlacements() : U->getWeightsPlacements();
+      Value *wo = W ? W->getWeightsOffsets() : U->getWeightsOffsets(), *tys = W ? W->getWeightsTys() : U->getWeightsTys();
+      Value *dimo = W ? W->getDimOffsets() : U->getDimOffsets(), *idx = W ? W->getIndices() : U->getIndices();
+      Value *off = W ? W->getOffsets() : U->getOffsets();
+      const int64_t tables = (int64_t)dimo->dims()[0] - 1;
+      const int32_t ops[10] = {S(dest), S(dev), S(uvm), S(pl), S(wo), S(tys), S(dimo), S(idx), S(off), W ? S(W->getIndiceWeight()) : -1};
+      const int64_t ia[13] = {(int64_t)dev->getType()->getSizeInBytes(), (int64_t)uvm->getType()->getSizeInBytes(), tables,
+                              W ? W->getTotalDims() : U->getTotalDims(), (int64_t)idx->dims()[0],
+                              tables ? ((int64_t)off->dims()[0] - 1) / tables : 0, idx->getElementType() == ElemKind::Int64ITy,
+                              wo->getElementType() == ElemKind::Int64ITy, (int64_t)(W ? W->getPoolingMode() : U->getPoolingMode()),
+                              W && W->getIndiceWeight()->getElementType() == ElemKind::Float16Ty,
+                              dest->getElementType() == ElemKind::Float16Ty, glow::flags::ConvertFusedScaleOffsetToFP32,
+                              glow::interpreter::flags::RowAlignmentBytes};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_SPLIT_EMBEDDING, ops, 10, ia, 13, nullptr, 0)));
+      break;
+    }
+    case Kinded::Kind::DynamicRowwiseQuantizedFullyConnectedInstKind: {
+      auto *N = llvm::cast<DynamicRowwiseQuantizedFullyConnectedInst>(&I);
+      if (!N->getIsSymmetric() || !N->getIsPerBatchElement())  // the Interpreter asserts the same (InterpreterNodes.cpp:4713-4714)
+        return MAKE_ERR(ErrorValue::ErrorCode::COMPILE_UNSUPPORTED_NODE_AFTER_OPTIMIZE, "B200: only symmetric per-batch-element dynamic quantization");
+      const int32_t ops[6] = {S(N->getDest()), S(N->getSrc()), S(N->getWeights()), S(N->getBias()), S(N->getScales()), S(N->getOffsets())};
+      const int64_t ia[4] = {(int64_t)N->getSrc()->dims()[0], (int64_t)N->getSrc()->dims()[1], (int64_t)N->getDest()->dims()[1], 0};
+      const float fa[1] = {0.f};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_DYN_QUANTIZED_FC, ops, 6, ia, 4, fa, 1)));
+      break;
+    }
+    case Kinded::Kind::DynamicQuantizedFullyConnectedInstKind: {
+      auto *N = llvm::cast<DynamicQuantizedFullyConnectedInst>(&I);
+      if (!N->getIsSymmetric() || !N->getIsPerBatchElement())
+        return MAKE_ERR(ErrorValue::ErrorCode::COMPILE_UNSUPPORTED_NODE_AFTER_OPTIMIZE, "B200: only symmetric per-batch-element dynamic quantization");
+      auto *WT = N->getWeights()->getType();
+      const int32_t ops[6] = {S(N->getDest()), S(N->getSrc()), S(N->getWeights()), S(N->getBias()), -1, -1};
+      const int64_t ia[4] = {(int64_t)N->getSrc()->dims()[0], (int64_t)N->getSrc()->dims()[1], (int64_t)N->getDest()->dims()[1], WT->getOffset()};
+      const float fa[1] = {WT->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_DYN_QUANTIZED_FC, ops, 6, ia, 4, fa, 1)));
       break;
     }
     case Kinded::Kind::InsertTensorInstKind: {

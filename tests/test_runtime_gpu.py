@@ -329,3 +329,63 @@ def test_recommendation_style_network_bit_exact(oracle, dm):
     want = oracle.element_dequantize_i8(m, *tq["mm"])
     np.testing.assert_array_equal(out.view(np.uint32), want.view(np.uint32))
     assert len(np.unique(m)) > 5
+
+
+def test_split_embedding_and_dynamic_fc_instructions(oracle, dm):
+    """A table-batched embedding layer feeding a dynamically quantized FC, as one loaded function:
+    IntNBitSplitEmbeddingBags (fp16 result) -> DynamicRowwiseQuantizedFullyConnected."""
+    rng = np.random.default_rng(91)
+    specs = [(ops.EST_INT4, 32, 400), (ops.EST_INT8, 16, 300), (ops.EST_FLOAT16, 16, 200)]
+    B, N = 24, 40
+    chunks, offs, at = [], [], 0
+    for ty, d, rows in specs:
+        rb = ops.split_embedding_row_bytes(d, ty)
+        tab = rng.integers(0, 256, (rows, rb), dtype=np.uint8)
+        if ty == ops.EST_FLOAT16:
+            tab[:, :2 * d] = rng.normal(0, 1, (rows, d)).astype(np.float16).view(np.uint8)
+        else:
+            hdr = np.stack([rng.uniform(0.001, 0.02, rows), rng.uniform(-1, 1, rows)], 1).astype(np.float16)
+            tab[:, :4] = hdr.view(np.uint8)
+        offs.append(at)
+        chunks.append(tab.reshape(-1))
+        at += tab.size
+    weights = np.concatenate(chunks + [np.zeros(16, np.uint8)])
+    T = len(specs)
+    dims = np.array([0] + [d for _, d, _ in specs]).cumsum().astype(np.int32)
+    D = int(dims[-1])
+    lens = rng.poisson(5, (T, B))
+    offsets = np.concatenate([[0], np.cumsum(lens.reshape(-1))]).astype(np.int32)
+    idx = np.concatenate([rng.integers(0, rows, int(lens[i].sum())) for i, (_, _, rows) in enumerate(specs)]).astype(np.int32)
+    max_idx = idx.size + 7
+    w = rng.integers(-128, 128, (D, N), dtype=np.int8)
+    bias = rng.normal(0, 1, N).astype(np.float32)
+    scales = rng.uniform(0.001, 0.02, N).astype(np.float32)
+    woff = rng.integers(-5, 5, N).astype(np.int32)
+
+    f = runtime.Function("tbe_dynfc")
+    cw = f.constant("weights", weights)
+    cpl = f.constant("placements", np.full(T, ops.PLACEMENT_HOST, np.int32))
+    cwo = f.constant("weights_offsets", np.array(offs, np.int32))
+    cty = f.constant("weights_tys", np.array([s[0] for s in specs], np.uint8))
+    cdo = f.constant("dim_offsets", dims)
+    pidx = f.placeholder("indices", max_idx * 4)
+    poff = f.placeholder("offsets", offsets.size * 4)
+    pooled = f.activation("pooled", B * D * 2)
+    cfw = f.constant("fc_weights", w)
+    cfb = f.constant("fc_bias", bias)
+    cfs = f.constant("fc_scales", scales)
+    cfo = f.constant("fc_offsets", woff)
+    out = f.placeholder("out", B * N * 2)
+    f.split_embedding_bags(pooled, cw, cw, cpl, cwo, cty, cdo, pidx, poff, dev_bytes=weights.size, uvm_bytes=weights.size,
+                           num_tables=T, total_dims=D, num_indices=max_idx, bags_per_table=B, out_fp16=True)
+    f.dynamic_quantized_fc(out, pooled, cfw, cfb, cfs, cfo, M=B, K=D, N=N)
+    f.compile()
+    dm.add_network(f)
+    ip = np.zeros(max_idx, np.int32); ip[:idx.size] = idx
+    got = np.zeros((B, N), np.float16)
+    dm.run_function("tbe_dynfc", {"indices": ip, "offsets": offsets, "out": got})
+    want_pooled = oracle.int_nbit_split_embedding_bags(weights, weights, np.full(T, 3, np.int32), np.array(offs, np.int32),
+                                                       np.array([s[0] for s in specs], np.uint8), dims, D, idx, offsets,
+                                                       out_fp16=True)
+    want = oracle.dynamic_rowwise_quantized_fc(want_pooled, w, bias, scales, woff)
+    np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16))
