@@ -62,3 +62,21 @@ def test_dynamic_quantized_fc(oracle, M, K, N, w_offset):
     got = ops.dynamic_quantized_fc(t(x), t(w), t(bias), w_scale, w_offset, status=st)
     np.testing.assert_array_equal(got.cpu().numpy().view(np.uint16), want.view(np.uint16))
     assert int(st.item()) == 0
+
+
+@pytest.mark.parametrize("ci", range(3))
+def test_reference_unit_cases(oracle, ci):
+    """The reference's own operator tests (OperatorTest.cpp:7787-7886) through the C ABI."""
+    import json
+    import os
+    g = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_unit_vectors.json")))
+    c = g["dynamic_quantized_fc"]["cases"][ci]
+    x, w = np.array(c["input"], np.float16), np.array(c["weights"], np.int8)
+    bias = np.array(c["bias"], np.float32)
+    if "scales" in c:
+        got = ops.dynamic_rowwise_quantized_fc(t(x), t(w), t(bias), t(np.array(c["scales"], np.float32)),
+                                               t(np.array(c["offsets"], np.int32)))
+    else:
+        got = ops.dynamic_quantized_fc(t(x), t(w), t(bias), c["weights_scale"], c["weights_offset"])
+    np.testing.assert_allclose(got.cpu().numpy().astype(np.float32), np.array(c["expected"], np.float32),
+                               atol=c["tol"], rtol=0)

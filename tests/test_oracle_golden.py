@@ -128,3 +128,20 @@ def test_int_nbit_split_embedding_bags_golden(oracle, name, idx_dtype):
     out = oracle.int_nbit_split_embedding_bags(**a)
     assert out.dtype == (np.float16 if a["out_fp16"] else np.float32)
     np.testing.assert_allclose(out.astype(np.float32), expected, atol=tol, rtol=0)
+
+
+def _dyn_fc_case(c):
+    x = np.array(c["input"], np.float16)
+    w = np.array(c["weights"], np.int8)
+    n = w.shape[1]
+    scales = np.array(c["scales"], np.float32) if "scales" in c else np.full(n, c["weights_scale"], np.float32)
+    offsets = np.array(c["offsets"], np.int32) if "offsets" in c else np.full(n, c["weights_offset"], np.int32)
+    return x, w, np.array(c["bias"], np.float32), scales, offsets
+
+
+@pytest.mark.parametrize("ci", range(3))
+def test_dynamic_quantized_fc_golden(oracle, ci):
+    """OperatorTest.cpp:7787-7886: the three dynamically quantized FC cases."""
+    c = G["dynamic_quantized_fc"]["cases"][ci]
+    out = oracle.dynamic_rowwise_quantized_fc(*_dyn_fc_case(c))
+    np.testing.assert_allclose(out.astype(np.float32), np.array(c["expected"], np.float32), atol=c["tol"], rtol=0)
