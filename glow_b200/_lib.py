@@ -101,6 +101,10 @@ SIGNATURES = {
     "glowb200_embedding_bag_byte_rowwise_offsets": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _i64, _int, _int, _int, _vp, _sz, _vp,
                _vp]),
+    "glowb200_tensor_rowwise_quantize_i8_device": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
+    "glowb200_quantize_rows_i8_device": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "glowb200_quantization_profile_workspace_bytes": (_sz, [_i64]),
+    "glowb200_quantization_profile": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _sz, _vp]),
     "glowb200_dynamic_fc_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "glowb200_dynamic_rowwise_quantized_fc": (
         _int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _vp, _sz, _vp, _vp]),

@@ -1,5 +1,6 @@
 // Embedding-table preparation and the partial-sum reduction of row-range sharded tables.
 #include "common.cuh"
+#include "quant_math.cuh"
 
 namespace glowb200 {
 namespace {
@@ -127,6 +128,94 @@ extern "C" int glowb200_fused_rowwise_quantize_device(const float *in, int64_t r
   const int64_t want_blocks = (rows + 7) / 8, cap = (int64_t)sm_count() * 16;
   fused_rowwise_quantize_kernel<<<(unsigned)(want_blocks < cap ? want_blocks : cap), 256, 0,
                                   reinterpret_cast<cudaStream_t>(stream)>>>(in, rows, cols, kind, out, out_line_size);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+namespace glowb200 {
+namespace {
+// quantization::quantize<int8_t> (include/glow/Quantization/Base/Base.h:322-329)
+__device__ __forceinline__ int8_t quantize_to_i8(float x, float scale, int32_t offset) {
+  const float r = __fadd_rn(__fdiv_rn(x, scale), (float)offset);
+  long long v = (long long)rintf(r);
+  return (int8_t)(v < -128 ? -128 : (v > 127 ? 127 : v));
+}
+
+// tensorRowwiseQuantization<float, int32_t, int8_t> (Base.h:522-576): a block per row finds the
+// range, thread 0 derives the parameters (chooseQuantizationParams in the reference's double
+// arithmetic), all threads quantize.  given != 0: the parameters are inputs (quantizeTensor with
+// per-row parameters, lib/Quantization/Base/Base.cpp:760-777) and only the last step runs.
+__global__ void __launch_bounds__(256) rowwise_quantize_i8_kernel(const float *__restrict__ in, long long cols, int schema,
+                                                                  int given, int8_t *__restrict__ out, float *scales,
+                                                                  int32_t *offsets) {
+  __shared__ float s_mn[8], s_mx[8];
+  __shared__ float s_scale;
+  __shared__ int32_t s_offset;
+  const long long row = blockIdx.x;
+  const float *x = in + row * cols;
+  if (!given) {
+    float mn = x[0], mx = mn;
+    for (long long k = threadIdx.x; k < cols; k += 256) {
+      const float v = x[k];
+      mn = v < mn ? v : mn;
+      mx = v > mx ? v : mx;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const float a = __shfl_xor_sync(0xffffffffu, mn, d), b = __shfl_xor_sync(0xffffffffu, mx, d);
+      mn = a < mn ? a : mn;
+      mx = b > mx ? b : mx;
+    }
+    if ((threadIdx.x & 31) == 0) { s_mn[threadIdx.x >> 5] = mn; s_mx[threadIdx.x >> 5] = mx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int i = 1; i < 8; i++) {
+        mn = s_mn[i] < mn ? s_mn[i] : mn;
+        mx = s_mx[i] > mx ? s_mx[i] : mx;
+      }
+      double scale;
+      int32_t offset;
+      choose_quantization_params_basic(mn, mx, schema, -128, 127, scale, offset);
+      if (schema == 3) {  // the next power of two at or above the scale: exp2(ceil(log2(scale)))
+        int e;
+        const double m = frexp(scale, &e);
+        scale = ldexp(1.0, m == 0.5 ? e - 1 : e);
+      }
+      s_scale = (float)scale;
+      s_offset = offset;
+      scales[row] = (float)scale;
+      offsets[row] = offset;
+    }
+  } else if (threadIdx.x == 0) {
+    s_scale = scales[row];
+    s_offset = offsets[row];
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  const int32_t offset = s_offset;
+  for (long long k = threadIdx.x; k < cols; k += 256) out[row * cols + k] = quantize_to_i8(x[k], scale, offset);
+}
+}  // namespace
+}  // namespace glowb200
+
+extern "C" int glowb200_tensor_rowwise_quantize_i8_device(const float *in, int64_t rows, int64_t cols, int schema, int8_t *out,
+                                                           float *scales, int32_t *offsets, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(rows >= 0 && rows < (1ll << 31) && cols > 0 && schema >= 0 && schema <= 3, "bad rows / cols / schema");
+  if (rows == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(in && out && scales && offsets, "NULL tensor pointer");
+  rowwise_quantize_i8_kernel<<<(unsigned)rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(in, cols, schema, 0, out,
+                                                                                               scales, offsets);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_quantize_rows_i8_device(const float *in, int64_t rows, int64_t cols, const float *scales,
+                                                 const int32_t *offsets, int8_t *out, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(rows >= 0 && rows < (1ll << 31) && cols > 0, "bad rows / cols");
+  if (rows == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(in && out && scales && offsets, "NULL tensor pointer");
+  rowwise_quantize_i8_kernel<<<(unsigned)rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      in, cols, 0, 1, out, const_cast<float *>(scales), const_cast<int32_t *>(offsets));
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }

@@ -445,6 +445,40 @@ def matmul_i8(lhs, rhs, out_offset, lhs_offset, rhs_offset, out_triple, *, flags
     return out
 
 
+def tensor_rowwise_quantize_i8_device(w, schema=ASYMMETRIC):
+    """tensorRowwiseQuantization on the device: fp32 [rows, cols] -> (int8, scales fp32, offsets int32)."""
+    _cuda(w, "w", (torch.float32,))
+    rows, cols = w.shape
+    q = torch.empty((rows, cols), dtype=torch.int8, device=w.device)
+    scales = torch.empty(rows, dtype=torch.float32, device=w.device)
+    offsets = torch.empty(rows, dtype=torch.int32, device=w.device)
+    check(_lib.lib().glowb200_tensor_rowwise_quantize_i8_device(_p(w), rows, cols, schema, _p(q), _p(scales), _p(offsets),
+                                                                _stream()))
+    return q, scales, offsets
+
+
+def quantize_rows_i8_device(w, scales, offsets):
+    """fp32 [rows, cols] quantized with given per-row parameters."""
+    _cuda(w, "w", (torch.float32,))
+    rows, cols = w.shape
+    q = torch.empty((rows, cols), dtype=torch.int8, device=w.device)
+    check(_lib.lib().glowb200_quantize_rows_i8_device(_p(w), rows, cols, _p(scales), _p(offsets), _p(q), _stream()))
+    return q
+
+
+def quantization_profile(x, comp_info, histogram, *, workspace=None):
+    """QuantizationProfile: folds tensor x into the running {min, max} (comp_info, 2 floats) and the
+    running histogram, both updated in place on the device."""
+    _cuda(x, "x", (torch.float32,))
+    _cuda(comp_info, "comp_info", (torch.float32,))
+    _cuda(histogram, "histogram", (torch.float32,))
+    bins = histogram.numel()
+    ws = _workspace(workspace, int(_lib.lib().glowb200_quantization_profile_workspace_bytes(bins)), x.device)
+    check(_lib.lib().glowb200_quantization_profile(_p(x), x.numel(), _p(comp_info), _p(histogram), bins, _p(ws),
+                                                   ws.numel(), _stream()))
+    return comp_info, histogram
+
+
 def dynamic_fc_workspace_bytes(M, K, N):
     return int(_lib.lib().glowb200_dynamic_fc_workspace_bytes(M, K, N))
 

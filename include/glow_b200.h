@@ -219,6 +219,21 @@ int glowb200_rowwise_quantized_sparse_lengths_weighted_sum_f32(
     int64_t segments, int64_t num_indices, int64_t line_size, void *workspace,
     size_t workspace_bytes, int32_t *status, glowb200_stream_t stream);
 
+/* Weight preparation on the device (SURVEY row 11 for weights already resident on the GPU).
+ * glowb200_tensor_rowwise_quantize_i8_device: tensorRowwiseQuantization<float,int32_t,int8_t>
+ * (include/glow/Quantization/Base/Base.h:522-576) -- every row of an fp32 [rows, cols] matrix gets
+ * its own parameters from its min and max (schema as glowb200_choose_quantization_params) and is
+ * quantized with them; same bytes as the host function glowb200_tensor_rowwise_quantize_i8.
+ * glowb200_quantize_rows_i8_device: quantizeTensor with given per-row parameters
+ * (lib/Quantization/Base/Base.cpp:760-777), the element pass of the channelwise filter
+ * preparation once glowb200_channelwise_conv_prepare's parameter rules have run. */
+int glowb200_tensor_rowwise_quantize_i8_device(const float *in, int64_t rows, int64_t cols,
+                                               int schema, int8_t *out, float *scales,
+                                               int32_t *offsets, glowb200_stream_t stream);
+int glowb200_quantize_rows_i8_device(const float *in, int64_t rows, int64_t cols,
+                                     const float *scales, const int32_t *offsets, int8_t *out,
+                                     glowb200_stream_t stream);
+
 /* tensorFusedRowwiseQuantization<T> (include/glow/Quantization/Base/Base.h:598-678): an fp32
  * [rows, cols] table into the fused-rowwise format of `kind`,
  * out_line_size = cols (+8 | +4) for the 8-bit kinds, cols/2 (+8 | +4) for the 4-bit kinds.
@@ -353,6 +368,18 @@ int glowb200_fc_i8_i32(int8_t *out, const int8_t *in, const int8_t *weights, con
                        int32_t out_scale, const int8_t *weights_transposed, int flags,
                        void *workspace, size_t workspace_bytes, int32_t *status,
                        glowb200_stream_t stream);
+
+/* QuantizationProfile: running min / max and histogram of a tensor on the device.
+ * Replaces libjit_quantization_profile (lib/LLVMIRCodeGen/libjit/libjit.cpp:3440-3523; the same
+ * algorithm as generateTensorHistogram, lib/Quantization/Base/Profile.cpp:36-112).  comp_info
+ * (device, 2 floats) holds the running {min, max}, initialised by the caller to {FLT_MAX,
+ * -FLT_MAX}; histogram (device, `bins` floats) the running counters.  When the range grows the
+ * existing bins are redistributed as the reference does; results are bit-identical to libjit
+ * built without fast-math. */
+size_t glowb200_quantization_profile_workspace_bytes(int64_t bins);
+int glowb200_quantization_profile(const float *input, int64_t size, float *comp_info,
+                                  float *histogram, int64_t bins, void *workspace,
+                                  size_t workspace_bytes, glowb200_stream_t stream);
 
 /* DynamicRowwiseQuantizedFullyConnected / DynamicQuantizedFullyConnected.
  * Replace fwdDynamicRowwiseQuantizedFullyConnectedInst and fwdDynamicQuantizedFullyConnectedInst

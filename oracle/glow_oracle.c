@@ -727,6 +727,47 @@ ORC_API void orc_dynamic_rowwise_quantized_fc(uint16_t *out, const uint16_t *in,
   free(q);
 }
 
+/* libjit_quantization_profile: libjit.cpp:3440-3523 (generateTensorHistogram, Profile.cpp:36-112).
+ * comp_info = {running min, running max}; hist has `bins` float counters. */
+static uint64_t orc_get_bin(uint64_t bins, float width, float minv, float v) {
+  if (width == 0.0f) return 0;
+  uint64_t b = (uint64_t)((v - minv) / width);
+  return b < bins - 1 ? b : bins - 1;
+}
+ORC_API void orc_quantization_profile(const float *x, int64_t n, float *comp_info, float *hist, int64_t bins) {
+  float mn = comp_info[0], mx = comp_info[1];
+  float min_in = x[0], max_in = x[0];
+  for (int64_t i = 1; i < n; i++) { if (x[i] < min_in) min_in = x[i]; if (x[i] > max_in) max_in = x[i]; }
+  const float new_min = min_in < mn ? min_in : mn, new_max = max_in > mx ? max_in : mx;
+  comp_info[0] = new_min;
+  comp_info[1] = new_max;
+  if (bins == 0) return;
+  int all_zero = 1;
+  for (int64_t i = 0; i < bins; i++) if (hist[i] != 0) { all_zero = 0; break; }
+  if (all_zero) { mn = min_in; mx = max_in; }
+  if (new_min < mn || new_max > mx) {
+    const float dest_w = (new_max - new_min) / (float)(uint64_t)bins, src_w = (mx - mn) / (float)(uint64_t)bins;
+    float *scaled = (float *)calloc((size_t)bins, sizeof(float));
+    for (int64_t i = 0; i < bins; i++) {
+      if (hist[i] == 0) continue;
+      const float src_begin = mn + src_w * (float)(uint64_t)i;
+      const uint64_t dest_bin = (uint64_t)((src_begin - new_min) / dest_w);
+      const float dest_end = new_min + dest_w * (float)(dest_bin + 1);
+      const float rounded = (float)round((double)((dest_end - src_begin) / src_w * hist[i]));
+      const uint64_t cnt = (uint64_t)(rounded < hist[i] ? rounded : hist[i]);
+      scaled[orc_get_bin((uint64_t)bins, dest_w, new_min, src_begin)] += (float)cnt;
+      if ((float)cnt < hist[i])
+        scaled[orc_get_bin((uint64_t)bins, dest_w, new_min, src_begin + dest_w)] += hist[i] - (float)cnt;
+    }
+    memcpy(hist, scaled, (size_t)bins * sizeof(float));
+    free(scaled);
+    mn = new_min;
+    mx = new_max;
+  }
+  const float width = (mx - mn) / (float)(uint64_t)bins;
+  for (int64_t i = 0; i < n; i++) hist[orc_get_bin((uint64_t)bins, width, mn, x[i])] += 1.0f;
+}
+
 /* Pairwise-dot feature interaction of the benchmark's recommendation model: no single kernel in
  * the reference (it composes Concat/Reshape/BatchMatMul, tests/unittests/
  * RecommendationSystemTest.cpp:640-680); this restates the definition the CUDA kernel

@@ -248,6 +248,14 @@ def dynamic_rowwise_quantized_fc(inp, weights_kn, bias, scales, offsets):
     return out
 
 
+def quantization_profile(x, comp_info, hist):
+    """libjit_quantization_profile (libjit.cpp:3440-3523): returns the updated (comp_info, hist)."""
+    x = _c(x, np.float32).reshape(-1)
+    ci, h = _c(comp_info, np.float32).copy(), _c(hist, np.float32).copy()
+    lib().orc_quantization_profile(_ptr(x), _i64(x.size), _ptr(ci), _ptr(h), _i64(h.size))
+    return ci, h
+
+
 def sparse_lengths_weighted_sum_f32(data, weights, indices, lengths):
     data = _c(data, np.float32)
     weights = _c(weights, np.float32)
@@ -508,6 +516,13 @@ class LibjitRef:
         fn(_ptr(dest), _ptr(data), _ptr(scales), _ptr(offsets), _ptr(weights), _ptr(indices), _ptr(lengths),
            C.c_uint64(lengths.shape[0]), C.c_uint64(data.shape[1]))
         return dest
+
+    def quantization_profile(self, x, comp_info, hist):
+        x = _c(x, np.float32).reshape(-1)
+        ci, h = _c(comp_info, np.float32).copy(), _c(hist, np.float32).copy()
+        dims = (C.c_uint64 * 1)(h.size)
+        self.l.libjit_quantization_profile(_ptr(x), C.c_uint64(x.size), _ptr(ci), _ptr(h), dims)
+        return ci, h
 
     def embedding_bag_byte_rowwise_offsets(self, data, weights, indices, offsets, has_end_offset):
         data = _c(data, np.uint8)

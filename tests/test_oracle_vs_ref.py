@@ -199,3 +199,21 @@ def test_plain_and_rowwise_quantized_slws(oracle, libjit_ref, d, idt):
     want = libjit_ref.rowwise_quantized_slws(q, sc, off, w, idx, lengths)
     got = oracle.rowwise_quantized_slws_f32(q, sc, off, w, idx, lengths)
     np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("bins", [0, 1, 10, 2000])
+def test_quantization_profile_vs_libjit(oracle, libjit_ref, bins):
+    """Running min / max and histogram over several tensors with growing, shrinking and constant
+    ranges: the restatement against libjit_quantization_profile, bit for bit."""
+    rng = np.random.default_rng(12 + bins)
+    ci_o = np.array([np.finfo(np.float32).max, np.finfo(np.float32).min], np.float32)
+    ci_r, h_o, h_r = ci_o.copy(), np.zeros(bins, np.float32), np.zeros(bins, np.float32)
+    for step, (scale, shift, n) in enumerate([(1.0, 0.0, 5000), (0.3, 0.1, 777), (4.0, -2.0, 9000), (4.0, 5.0, 3000),
+                                              (0.0, 1.5, 100), (20.0, 0.0, 1)]):
+        x = (rng.normal(0, 1, n) * scale + shift).astype(np.float32)
+        ci_o, h_o = oracle.quantization_profile(x, ci_o, h_o)
+        ci_r, h_r = libjit_ref.quantization_profile(x, ci_r, h_r)
+        np.testing.assert_array_equal(ci_o.view(np.uint32), ci_r.view(np.uint32))
+        np.testing.assert_array_equal(h_o.view(np.uint32), h_r.view(np.uint32))
+    if bins:
+        assert h_o.sum() == 5000 + 777 + 9000 + 3000 + 100 + 1
