@@ -422,7 +422,7 @@ def run_int8_fc_line(args):
                              "library_int8_gemm_tops": r["library_int8_gemm_tops"],
                              # DRAM bytes per launch from the ncu capture in profiles/ (the 8 MB result stays in L2)
                              "traffic": 25.4e6,
-                             "kernel": "i8_gemm_requant_kernel<256,4>", "launch_us": r["ms"] * 1e3},
+                             "kernel": "i8_gemm_requant_kernel<240,4,0>", "launch_us": r["ms"] * 1e3},
                 "e2e": {"value": world * r["ops"] / (e2e_ms * 1e-3) / 1e12, "unit": "TOP/s",
                         "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"], "steps": r["e2e_steps"],
                         "ms_per_step": e2e_ms},
@@ -853,7 +853,7 @@ def run_dyn_fc_line(args):
                                    "quantized per row on the device, int8 weights U[-127,127], fp32 bias and column scales",
                        "l2_policy": "8 rotating inputs and results (256 MB) between repeats"},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TOP/s", "frac": per_gpu / peak,
-                         "peak_source": src, "traffic": None, "kernel": "dyn_quantize_rows_kernel + i8_gemm_requant_kernel<256,4,2>"},
+                         "peak_source": src, "traffic": None, "kernel": "dyn_quantize_rows_kernel + i8_gemm_requant_kernel<240,4,2>"},
             "gpu_launches": 2 * args.steps, "clocks": clocks}))
     if world > 1:
         dist.destroy_process_group()

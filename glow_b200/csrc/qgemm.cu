@@ -258,7 +258,8 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   const int m_tiles = (p.M + kBlockM - 1) / kBlockM, n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int tiles = m_tiles * n_tiles;
   const int k_blocks = (p.K + kBlockK - 1) / kBlockK;
-  constexpr uint32_t kAccCols = BLOCK_N < 32 ? 32 : BLOCK_N;
+  // columns of one accumulator buffer: BLOCK_N rounded up to a power of two (240 -> 256)
+  constexpr uint32_t kAccCols = BLOCK_N <= 32 ? 32 : BLOCK_N <= 64 ? 64 : BLOCK_N <= 128 ? 128 : 256;
   constexpr uint32_t kTmemCols = 2 * kAccCols;  // a power of two >= 64
 
   if (threadIdx.x == 0) {
@@ -345,7 +346,8 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int et = threadIdx.x - 64;          // 0..511
     const int quarter = warp & 3;
     const int col_group = (warp - 2) >> 2;     // 0..3
-    constexpr int kGroupCols = BLOCK_N / 4;    // columns per warp: 64 (BLOCK_N 256) or 16 (BLOCK_N 64)
+    // columns per warp, in whole 16-column drains: 64 (BLOCK_N 256 and 240, whose last group has 48) ... 16 (BLOCK_N 64)
+    constexpr int kGroupCols = ((BLOCK_N / 16 + 3) / 4) * 16;
     // columns drained from tensor memory per load: 16 keeps the drain loop inside the 96 registers
     // a 576-thread CTA leaves (32 spills, and measured slower)
 #ifndef GLOWB200_GEMM_CHUNK
@@ -425,14 +427,15 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         out_row = p.out + ((size_t)(img * p.conv_oh + oh) * p.conv_ow + ow) * p.N + n0;
       }
       const int32_t relu_floor = p.act_type == 1 ? p.out_offset : INT32_MIN;
+      const int c_end = (col_group + 1) * kGroupCols < BLOCK_N ? (col_group + 1) * kGroupCols : BLOCK_N;
 #pragma unroll 1
-      for (int c0 = col_group * kGroupCols; c0 < (col_group + 1) * kGroupCols; c0 += kChunk) {
+      for (int c0 = col_group * kGroupCols; c0 < c_end; c0 += kChunk) {
         uint32_t acc[kChunk];
         if constexpr (kChunk == 32) tmem_ld_32x32b_x32(lane_addr + (uint32_t)c0, reinterpret_cast<uint32_t(&)[32]>(acc));
         else tmem_ld_32x32b_x16(lane_addr + (uint32_t)c0, acc);
         tmem_ld_wait();
         GEMM_TRACE(7, lt == 0 && et == 0 && c0 == 0);
-        if (c0 + kChunk >= (col_group + 1) * kGroupCols) {
+        if (c0 + kChunk >= c_end) {
           // everything this warp needs from the buffer is in registers: hand it back
           tc_fence_before();
           __syncwarp();
@@ -670,6 +673,37 @@ int launch_tile_kernel(const CUtensorMap &ma, const CUtensorMap &mb, const GemmP
 
 bool ptr16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+#ifndef GLOWB200_GEMM_TILE_240
+#define GLOWB200_GEMM_TILE_240 1
+#endif
+// Columns of an output tile.  64 for narrow results; 128 when 256-column tiles would leave half
+// a tile (or more) of padding; else 256 -- unless 240-column tiles finish in fewer, or as many
+// but narrower, rounds over the SMs: 2048 x 4096 is 256 tiles of 256 columns (two rounds on 148
+// SMs, the second 73 % full) but 288 tiles of 240 (two rounds, 6 % shorter each).
+int pick_block_n(int M, int N) {
+  if (N <= 64) return 64;
+  if (((N + 127) / 128) & 1) return 128;
+#if GLOWB200_GEMM_TILE_240
+  const long sms = sm_count(), m_tiles = (M + kBlockM - 1) / kBlockM;
+  auto cost = [&](long bn) { return ((m_tiles * ((N + bn - 1) / bn) + sms - 1) / sms) * (bn + 16); };
+  if (cost(240) * 100 < cost(256) * 97) return 240;
+#endif
+  return 256;
+}
+
+int launch_for_block_n(int bn, const void *a, int a_rows, int a_extent, int a_pitch, const void *b, const GemmParams &p,
+                       cudaStream_t s) {
+  CUtensorMap ma, mb;
+  if (int rc = make_map(&ma, a, a_rows, a_extent, kBlockM, a_pitch)) return rc;
+  if (int rc = make_map(&mb, b, p.N, p.K, bn)) return rc;
+  switch (bn) {
+    case 64: return launch_tile_kernel<64, 6>(ma, mb, p, s);
+    case 128: return launch_tile_kernel<128, 6>(ma, mb, p, s);
+    case 240: return launch_tile_kernel<240, 4>(ma, mb, p, s);
+    default: return launch_tile_kernel<256, 4>(ma, mb, p, s);
+  }
+}
+
 // Runs out = requant(A[M,K] x B[N,K]^T ...) choosing the tensor-core or the any-shape kernel.
 // `ws` holds b_row_sums (when not supplied) and a_row_sums (when needed).
 }  // namespace
@@ -683,19 +717,8 @@ int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int 
   p.b_row_sums = b_row_sums;
   p.a_row_sums = nullptr;
   if (p.k_corr == 0) p.k_corr = p.K;
-  CUtensorMap ma, mb;
   // C = 64: a 128-byte window over two neighbouring pixels, sliding by one pixel per row
-  if (int rc = make_map(&ma, padded, (int)rows, C == 64 ? 128 : C, kBlockM, C)) return rc;
-  if (p.N > 64 && (((p.N + 127) / 128) & 1)) {
-    if (int rc = make_map(&mb, b, p.N, p.K, 128)) return rc;
-    return launch_tile_kernel<128, 6>(ma, mb, p, s);
-  }
-  if (p.N > 64) {
-    if (int rc = make_map(&mb, b, p.N, p.K, 256)) return rc;
-    return launch_tile_kernel<256, 4>(ma, mb, p, s);
-  }
-  if (int rc = make_map(&mb, b, p.N, p.K, 64)) return rc;
-  return launch_tile_kernel<64, 6>(ma, mb, p, s);
+  return launch_for_block_n(pick_block_n(p.M, p.N), padded, (int)rows, C == 64 ? 128 : C, C, b, p, s);
 }
 
 int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_row_sums_in, bool b_offsets_zero,
@@ -731,21 +754,7 @@ int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_ro
   } else {
     p.a_row_sums = nullptr;
   }
-  CUtensorMap ma, mb;
-  // 128-column tiles when 256-column ones would leave half a tile (or more) of padding
-  if (p.N > 64 && (((p.N + 127) / 128) & 1)) {
-    if (int rc = make_map(&ma, a, p.M, p.K, kBlockM)) return rc;
-    if (int rc = make_map(&mb, b, p.N, p.K, 128)) return rc;
-    return launch_tile_kernel<128, 6>(ma, mb, p, s);
-  }
-  if (p.N > 64) {
-    if (int rc = make_map(&ma, a, p.M, p.K, kBlockM)) return rc;
-    if (int rc = make_map(&mb, b, p.N, p.K, 256)) return rc;
-    return launch_tile_kernel<256, 4>(ma, mb, p, s);
-  }
-  if (int rc = make_map(&ma, a, p.M, p.K, kBlockM)) return rc;
-  if (int rc = make_map(&mb, b, p.N, p.K, 64)) return rc;
-  return launch_tile_kernel<64, 6>(ma, mb, p, s);
+  return launch_for_block_n(pick_block_n(p.M, p.N), a, p.M, p.K, p.K, b, p, s);
 }
 
 int run_gemm_float_any(const GemmParams &p, const int8_t *a, const int8_t *b_kn, cudaStream_t s) {
