@@ -33,7 +33,7 @@ constexpr int kQuantThreads = 256;
 constexpr int kQuantCache = 4;  // 16-byte loads a thread keeps
 
 template <bool VEC>
-__global__ void __launch_bounds__(kQuantThreads) dyn_quantize_rows_kernel(const __half *__restrict__ in, int M, int K,
+__global__ void __launch_bounds__(kQuantThreads, 6) dyn_quantize_rows_kernel(const __half *__restrict__ in, int M, int K,
                                                                           int8_t *__restrict__ q, float *__restrict__ row_scales,
                                                                           int32_t *__restrict__ row_sums, int32_t *status) {
   __shared__ float s_mn[kQuantThreads / 32], s_mx[kQuantThreads / 32];
