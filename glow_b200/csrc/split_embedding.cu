@@ -89,6 +89,17 @@ __device__ __forceinline__ float add_f32_f16(uint16_t h, float c) {
   return d;
 }
 __device__ __forceinline__ float half_bits_to_float(uint32_t h) { return add_f32_f16((uint16_t)(h & 0xFFFFu), -0.0f); }
+#ifndef GLOWB200_TBE_X2
+#define GLOWB200_TBE_X2 1
+#endif
+__device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpack2f(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
 // Two floats rounded to fp16 (round to nearest even), packed {lo, hi}: one conversion for two.
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   uint32_t d;
@@ -196,9 +207,25 @@ __device__ __forceinline__ int32_t pool_bag(const SplitLaunch &p, const uint8_t 
             offset = half_bits_to_float(hdr[u][0] >> 16);
           }
         }
-        auto dequant = [&](uint16_t h) -> float {  // h = fp16 bits of 1024 + q
-          const float f = add_f32_f16(h, -1024.0f);
-          return SO32 ? __fadd_rn(__fmul_rn(f, scale), offset) : __fmaf_rn(f, scale, offset);
+        // Pairs of fp32 values go through the two-lane fp32 instructions of sm_100 (each lane
+        // rounds like the scalar instruction, subnormals included) for the dequantising FMA and
+        // for the sums of unweighted quantized rows.  The weight multiply and the add behind it
+        // stay scalar: issued as a two-lane multiply followed by a two-lane add they did not
+        // reproduce the reference's two roundings on its own unit vectors, whereas scalar
+        // mul.rn / add.rn are never contracted.
+        auto dequant2 = [&](uint32_t h2, float &ta, float &tb) {  // h2 = two fp16 numbers 1024 + q
+          const float fa = add_f32_f16((uint16_t)(h2 & 0xFFFFu), -1024.0f), fb = add_f32_f16((uint16_t)(h2 >> 16), -1024.0f);
+          if constexpr (SO32) {
+            ta = __fadd_rn(__fmul_rn(fa, scale), offset);
+            tb = __fadd_rn(__fmul_rn(fb, scale), offset);
+          } else if constexpr (GLOWB200_TBE_X2) {
+            uint64_t v2;
+            asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v2) : "l"(pack2f(fa, fb)), "l"(pack2f(scale, scale)), "l"(pack2f(offset, offset)));
+            unpack2f(v2, ta, tb);
+          } else {
+            ta = __fmaf_rn(fa, scale, offset);
+            tb = __fmaf_rn(fb, scale, offset);
+          }
         };
 #pragma unroll
         for (int i = 0; i < PAIRS; i++) {
@@ -210,22 +237,23 @@ __device__ __forceinline__ int32_t pool_bag(const SplitLaunch &p, const uint8_t 
             ta = half_bits_to_float(q[u][i]);
             tb = half_bits_to_float(q[u][i] >> 16);
           } else if constexpr (TY == TY_I8) {
-            const uint32_t h2 = __byte_perm(q[u][i >> 1], 0x64646464u, (i & 1) ? 0x4342u : 0x4140u);
-            ta = dequant((uint16_t)(h2 & 0xFFFFu));
-            tb = dequant((uint16_t)(h2 >> 16));
+            dequant2(__byte_perm(q[u][i >> 1], 0x64646464u, (i & 1) ? 0x4342u : 0x4140u), ta, tb);
           } else {  // even column = low nibble, odd column = high nibble (InterpreterNodes.cpp:104-109)
-            const uint32_t h2 = ((q[u][i >> 2] >> (4 * (i & 3))) & 0x000F000Fu) | 0x64006400u;
-            ta = dequant((uint16_t)(h2 & 0xFFFFu));
-            tb = dequant((uint16_t)(h2 >> 16));
+            dequant2(((q[u][i >> 2] >> (4 * (i & 3))) & 0x000F000Fu) | 0x64006400u, ta, tb);
           }
           if constexpr (WEIGHTED) {  // (an unweighted bag multiplies by 1.0)
             ta = __fmul_rn(w[u], ta);
             tb = __fmul_rn(w[u], tb);
           }
           if constexpr (OUT16) {
+            // (keeping fp32 copies of the sums and converting both ways every row was tried: half the speed)
             const float lo = add_f32_f16((uint16_t)(acch[i] & 0xFFFFu), ta);
             const float hi = add_f32_f16((uint16_t)(acch[i] >> 16), tb);
             acch[i] = pack_f16x2(lo, hi);
+          } else if constexpr (GLOWB200_TBE_X2 && !WEIGHTED && !SO32 && (TY == TY_I8 || TY == TY_I4)) {
+            uint64_t s2;
+            asm("add.rn.f32x2 %0, %1, %2;" : "=l"(s2) : "l"(pack2f(acc[slot_a(i)], acc[slot_b(i)])), "l"(pack2f(ta, tb)));
+            unpack2f(s2, acc[slot_a(i)], acc[slot_b(i)]);
           } else {
             acc[slot_a(i)] = __fadd_rn(acc[slot_a(i)], ta);
             acc[slot_b(i)] = __fadd_rn(acc[slot_b(i)], tb);
