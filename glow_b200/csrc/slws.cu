@@ -829,8 +829,7 @@ struct GatherConfig {
 
 
 // (P, U) pairs that exist: chunks per lane P, rows requested per lane before the first is
-// consumed U.  Wide rows spread over 8 or more lanes leave few bags (or row slots) per warp,
-// so each lane keeps 8 rows in flight instead of 4 to hold the bytes in flight per warp up.
+// consumed U (4 everywhere but the tuning macro of P = 2).
 template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int U>
 cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
 #if GLOWB200_SLWS_WARP_PER_BAG
