@@ -295,7 +295,7 @@ __global__ void __launch_bounds__(kThreads, GLOWB200_TBE_MIN_BLOCKS) split_embed
   const int ty = p.weights_tys[t];
   const int32_t placement = p.placements[t];
   if (num_dims <= 0) return;
-  if (ty > TY_I4 || placement == 0 || dim_start < 0 || (int64_t)dim_start + num_dims > p.total_dims) {
+  if (ty > TY_I4 || placement == 0 || dim_start < 0 || (int64_t)dim_start + num_dims > p.total_dims || num_dims > (1 << 27)) {
     // int2 rows and tables placed in device-only memory are not supported by the reference
     // either (InterpreterNodes.cpp:6696, 6704): the table's columns stay 0
     if (blockIdx.x == 0 && threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, GLOWB200_STATUS_UNSUPPORTED_TABLE);
