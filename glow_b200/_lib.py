@@ -64,6 +64,9 @@ SIGNATURES = {
         _int, [_vp] * 10 + [_i64] + [_i32] * 10 + [_vp, _i32, _vp, _int, _vp, _sz, _vp, _vp]),
     "glowb200_element_add_i8": (_int, [_vp, _vp, _vp, _i64] + [_i32] * 9 + [_vp]),
     "glowb200_element_add_maxsplat_i8": (_int, [_vp, _vp, _vp, _i64] + [_i32] * 10 + [_vp]),
+    "glowb200_element_binary_i8": (_int, [_int, _vp, _vp, _vp, _i64] + [_i32] * 9 + [_vp]),
+    "glowb200_element_muldiv_i8": (_int, [_int, _vp, _vp, _vp, _i64] + [_i32] * 6 + [_vp]),
+    "glowb200_batched_add_i8": (_int, [_vp, _vp, _vp, _int, _i64, _i64] + [_i32] * 9 + [_vp]),
     "glowb200_element_relu_i8": (_int, [_vp, _vp, _i64] + [_i32] * 5 + [_vp]),
     "glowb200_element_maxsplat_i8": (_int, [_vp, _vp, _i64, _i32, _vp]),
     "glowb200_splat_f": (_int, [_vp, _i64, _f32, _int, _vp]),

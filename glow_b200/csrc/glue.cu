@@ -27,6 +27,51 @@ __global__ void __launch_bounds__(kThreads) add_i8_kernel(int8_t *__restrict__ d
   }
 }
 
+// The other arithmetic mini-kernels of DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED (libjit.cpp:1593-1603,
+// 1675-1682): both sides rescaled to the result's scale, then sub / max / min, offset, clip.
+// OP 1 sub, 2 max, 3 min.
+template <int OP>
+__global__ void __launch_bounds__(kThreads) binary_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
+                                                             const int8_t *__restrict__ rhs, int64_t n, int32_t dst_off,
+                                                             int32_t lhs_off, int32_t rhs_off, Triple lt, Triple rt) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t l = scale32((int32_t)lhs[i] - lhs_off, lt.pre, lt.post, lt.scale, 0);
+    const int32_t r = scale32((int32_t)rhs[i] - rhs_off, rt.pre, rt.post, rt.scale, 0);
+    const int32_t v = OP == 1 ? (int32_t)((uint32_t)l - (uint32_t)r) : OP == 2 ? (l > r ? l : r) : (l < r ? l : r);
+    dst[i] = (int8_t)clip_i8((int32_t)((uint32_t)v + (uint32_t)dst_off));
+  }
+}
+
+// libjit_element_mul_kernel_i8 / _div_kernel_i8 (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED_M,
+// libjit.cpp:1610-1619, 1683-1684): the product (quotient) of the offset-free operands, one
+// rescale with the result's offset, clip.  A zero divisor gives the result offset (the
+// reference divides by it).
+template <bool DIV>
+__global__ void __launch_bounds__(kThreads) muldiv_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
+                                                             const int8_t *__restrict__ rhs, int64_t n, int32_t dst_off,
+                                                             int32_t lhs_off, int32_t rhs_off, Triple t) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t l = (int32_t)lhs[i] - lhs_off, r = (int32_t)rhs[i] - rhs_off;
+    const int32_t v = DIV ? (r == 0 ? 0 : l / r) : (int32_t)((uint32_t)l * (uint32_t)r);
+    dst[i] = (int8_t)clip_i8(scale32(v, t.pre, t.post, t.scale, dst_off));
+  }
+}
+
+// libjit_batchedadd_quantized (libjit.cpp:997-1015; entry points libjit_batchedadd_i8 and
+// libjit_batchedadd_i32_i8, :1945-1969): a slice added to every slice of the batch.
+template <typename SliceT>
+__global__ void __launch_bounds__(kThreads) batched_add_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ batch,
+                                                                  const SliceT *__restrict__ slice, int64_t n,
+                                                                  int64_t slice_size, int32_t dst_off, int32_t batch_off,
+                                                                  int32_t slice_off, Triple bt, Triple st) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t b = (int32_t)batch[i] - batch_off;
+    const int32_t sl = (int32_t)((uint32_t)(int32_t)slice[i % slice_size] - (uint32_t)slice_off);
+    const int32_t x = scale32(b, bt.pre, bt.post, bt.scale, 0), y = scale32(sl, st.pre, st.post, st.scale, 0);
+    dst[i] = (int8_t)clip_i8((int32_t)((uint32_t)x + (uint32_t)y + (uint32_t)dst_off));
+  }
+}
+
 // The Add followed by the int8 Relu of a residual block (libjit_element_add_kernel_i8, then
 // libjit_element_maxsplat_kernel_i8 on its result) in one pass over memory.
 __global__ void __launch_bounds__(kThreads) add_maxsplat_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
@@ -232,6 +277,64 @@ extern "C" int glowb200_element_add_i8(int8_t *dest, const int8_t *lhs, const in
   add_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset,
                                                                Triple{lhs_pre, lhs_post, lhs_scale},
                                                                Triple{rhs_pre, rhs_post, rhs_scale});
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_element_binary_i8(int op, int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n,
+                                          int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset, int32_t lhs_pre,
+                                          int32_t lhs_post, int32_t lhs_scale, int32_t rhs_pre, int32_t rhs_post,
+                                          int32_t rhs_scale, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(op >= GLOWB200_BINARY_ADD && op <= GLOWB200_BINARY_MIN, "unknown binary operator %d", op);
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && lhs && rhs)
+  const Triple lt{lhs_pre, lhs_post, lhs_scale}, rt{rhs_pre, rhs_post, rhs_scale};
+  switch (op) {
+    case GLOWB200_BINARY_ADD:
+      add_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset, lt, rt);
+      break;
+    case GLOWB200_BINARY_SUB:
+      binary_i8_kernel<1><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset, lt, rt);
+      break;
+    case GLOWB200_BINARY_MAX:
+      binary_i8_kernel<2><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset, lt, rt);
+      break;
+    default:
+      binary_i8_kernel<3><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset, lt, rt);
+      break;
+  }
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_element_muldiv_i8(int is_div, int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n,
+                                          int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset, int32_t pre,
+                                          int32_t post, int32_t scale, glowb200_stream_t stream) {
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && lhs && rhs)
+  if (is_div)
+    muldiv_i8_kernel<true><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset,
+                                                                         Triple{pre, post, scale});
+  else
+    muldiv_i8_kernel<false><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset,
+                                                                          Triple{pre, post, scale});
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return GLOWB200_OK;
+}
+
+extern "C" int glowb200_batched_add_i8(int8_t *dest, const int8_t *batch, const void *slice, int slice_is_int32,
+                                       int64_t num_slices, int64_t slice_size, int32_t dest_offset, int32_t batch_offset,
+                                       int32_t slice_offset, int32_t batch_pre, int32_t batch_post, int32_t batch_scale,
+                                       int32_t slice_pre, int32_t slice_post, int32_t slice_scale, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(num_slices >= 0 && slice_size >= 0 && num_slices < (1ll << 31) && slice_size < (1ll << 31),
+                   "bad slice count / size");
+  const int64_t n = num_slices * slice_size;
+  GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && batch && slice)
+  const Triple bt{batch_pre, batch_post, batch_scale}, st{slice_pre, slice_post, slice_scale};
+  if (slice_is_int32)
+    batched_add_i8_kernel<int32_t><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(
+        dest, batch, reinterpret_cast<const int32_t *>(slice), n, slice_size, dest_offset, batch_offset, slice_offset, bt, st);
+  else
+    batched_add_i8_kernel<int8_t><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(
+        dest, batch, reinterpret_cast<const int8_t *>(slice), n, slice_size, dest_offset, batch_offset, slice_offset, bt, st);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }

@@ -178,6 +178,10 @@ extern "C" int glowb200_function_add_instruction(glowb200_function *f, int kind,
 //                  pooling_mode, indice_weights_are_fp16, out_fp16, scale_offset_is_fp32, row_alignment}
 //  DYN_QUANTIZED_FC ops {dest (fp16), src (fp16), weights [K,N], bias (fp32), scales (-1: per tensor), offsets (-1: per tensor)}
 //              ia {M, K, N, weights_offset}  fa {weights_scale}
+//  BINARY_I8   ops {dest, lhs, rhs}  ia {n, dest_off, lhs_off, rhs_off, op (GLOWB200_BINARY_*)}  fa {lhs_scale, rhs_scale, dest_scale}
+//  MULDIV_I8   ops {dest, lhs, rhs}  ia {n, dest_off, lhs_off, rhs_off, is_div}  fa {lhs_scale, rhs_scale, dest_scale}
+//  BATCHED_ADD_I8 ops {dest, batch, slice}  ia {num_slices, slice_size, dest_off, batch_off, slice_off, slice_is_int32}
+//              fa {batch_scale, slice_scale, dest_scale}
 extern "C" int glowb200_function_compile(glowb200_function *f) {
   if (!f || f->compiled) return set_error(GLOWB200_RUNTIME_ERROR, "function is NULL or already compiled");
   size_t ws = 256;
@@ -298,6 +302,32 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
         if (!need(5, 10, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed EMBEDDING_BAG", ii);
         ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[4], 1));
         break;
+      case GLOWB200_INSTR_BINARY_I8: {
+        // LLVMIRGen.cpp:1716-1776: each side rescaled by sideScale / destScale
+        if (!need(3, 5, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed BINARY_I8", ii);
+        int32_t t[6];
+        glowb200::quantize_scale_32to8(in.fa[0] / in.fa[2], t[0], t[1], t[2]);
+        glowb200::quantize_scale_32to8(in.fa[1] / in.fa[2], t[3], t[4], t[5]);
+        for (int32_t x : t) in.ia.push_back(x);
+        break;
+      }
+      case GLOWB200_INSTR_MULDIV_I8: {
+        // LLVMIRGen.cpp:1927-2035: lhsScale * rhsScale / destScale, or lhsScale / (rhsScale * destScale)
+        if (!need(3, 5, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed MULDIV_I8", ii);
+        int32_t a, b, c;
+        glowb200::quantize_scale_32to8(in.ia[4] ? in.fa[0] / (in.fa[1] * in.fa[2]) : in.fa[0] * in.fa[1] / in.fa[2], a, b, c);
+        in.ia.push_back(a); in.ia.push_back(b); in.ia.push_back(c);
+        break;
+      }
+      case GLOWB200_INSTR_BATCHED_ADD_I8: {
+        // LLVMIRGen.cpp:2322-2375: batchScale / destScale and sliceScale / destScale
+        if (!need(3, 6, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed BATCHED_ADD_I8", ii);
+        int32_t t[6];
+        glowb200::quantize_scale_32to8(in.fa[0] / in.fa[2], t[0], t[1], t[2]);
+        glowb200::quantize_scale_32to8(in.fa[1] / in.fa[2], t[3], t[4], t[5]);
+        for (int32_t x : t) in.ia.push_back(x);
+        break;
+      }
       case GLOWB200_INSTR_SPLIT_EMBEDDING:
         if (!need(10, 13, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed SPLIT_EMBEDDING", ii);
         break;
@@ -571,6 +601,20 @@ int execute(glowb200_device_manager *dm, LoadedNetwork &n) {
             (float *)ptr(in.ops[0]), (const uint8_t *)ptr(in.ops[1]), (const float *)ptr(in.ops[2]), (const float *)ptr(in.ops[3]), a[0],
             (const float *)ptr(in.ops[4]), ptr(in.ops[5]), (int)a[4], (const int32_t *)ptr(in.ops[6]), a[2], a[3], a[1], n.workspace,
             f->workspace_bytes, dm->status_dev, st);
+        break;
+      case GLOWB200_INSTR_BINARY_I8:
+        rc = glowb200_element_binary_i8((int)a[4], (int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
+                                        a[0], (int32_t)a[1], (int32_t)a[2], (int32_t)a[3], (int32_t)a[5], (int32_t)a[6], (int32_t)a[7],
+                                        (int32_t)a[8], (int32_t)a[9], (int32_t)a[10], st);
+        break;
+      case GLOWB200_INSTR_MULDIV_I8:
+        rc = glowb200_element_muldiv_i8((int)a[4], (int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
+                                        a[0], (int32_t)a[1], (int32_t)a[2], (int32_t)a[3], (int32_t)a[5], (int32_t)a[6], (int32_t)a[7], st);
+        break;
+      case GLOWB200_INSTR_BATCHED_ADD_I8:
+        rc = glowb200_batched_add_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), ptr(in.ops[2]), (int)a[5], a[0], a[1],
+                                     (int32_t)a[2], (int32_t)a[3], (int32_t)a[4], (int32_t)a[6], (int32_t)a[7], (int32_t)a[8],
+                                     (int32_t)a[9], (int32_t)a[10], (int32_t)a[11], st);
         break;
       case GLOWB200_INSTR_SPLIT_EMBEDDING:
         rc = glowb200_int_nbit_split_embedding_bags(

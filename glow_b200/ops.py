@@ -581,6 +581,37 @@ def element_add_i8(lhs, rhs, dest_offset, lhs_offset, rhs_offset, lhs_triple, rh
     return out
 
 
+BINARY_ADD, BINARY_SUB, BINARY_MAX, BINARY_MIN = 0, 1, 2, 3
+
+
+def element_binary_i8(op, lhs, rhs, dest_offset, lhs_offset, rhs_offset, lhs_triple, rhs_triple, out=None):
+    """ElementAdd / Sub / Max / Min on int8 tensors (op: BINARY_*)."""
+    out = torch.empty_like(lhs) if out is None else out
+    check(_lib.lib().glowb200_element_binary_i8(int(op), _p(out), _p(lhs), _p(rhs), lhs.numel(), int(dest_offset),
+                                                int(lhs_offset), int(rhs_offset), *[int(v) for v in lhs_triple],
+                                                *[int(v) for v in rhs_triple], _stream()))
+    return out
+
+
+def element_muldiv_i8(is_div, lhs, rhs, dest_offset, lhs_offset, rhs_offset, triple, out=None):
+    """ElementMul (is_div False) / ElementDiv (True) on int8 tensors."""
+    out = torch.empty_like(lhs) if out is None else out
+    check(_lib.lib().glowb200_element_muldiv_i8(int(bool(is_div)), _p(out), _p(lhs), _p(rhs), lhs.numel(), int(dest_offset),
+                                                int(lhs_offset), int(rhs_offset), *[int(v) for v in triple], _stream()))
+    return out
+
+
+def batched_add_i8(batch, slice_, dest_offset, batch_offset, slice_offset, batch_triple, slice_triple, out=None):
+    """BatchedAdd: slice_ (int8 or int32, [slice_size]) added to every row of batch [num_slices, slice_size]."""
+    out = torch.empty_like(batch) if out is None else out
+    num_slices = batch.shape[0]
+    slice_size = batch.numel() // max(num_slices, 1)
+    check(_lib.lib().glowb200_batched_add_i8(_p(out), _p(batch), _p(slice_), int(slice_.dtype == torch.int32), num_slices,
+                                             slice_size, int(dest_offset), int(batch_offset), int(slice_offset),
+                                             *[int(v) for v in batch_triple], *[int(v) for v in slice_triple], _stream()))
+    return out
+
+
 def element_add_maxsplat_i8(lhs, rhs, dest_offset, lhs_offset, rhs_offset, lhs_triple, rhs_triple, splat, out=None):
     """element_add_i8 followed by element_maxsplat_i8(splat), fused."""
     if out is None:

@@ -15,7 +15,7 @@ from ._lib import GlowB200Error
 CONSTANT, PLACEHOLDER, ACTIVATION = 0, 1, 2
 (FRWQ_SLWS, RWQ_FC, CWQ_CONV, ADD, MAXSPLAT, QUANTIZE, DEQUANTIZE, MAXPOOL, AVGPOOL, TRANSPOSE, COPY) = range(1, 12)
 (ADD_MAXSPLAT, RELU, RESCALE, FC_I8, MATMUL_I8, SPLAT, INSERT_TENSOR, PAIRWISE_DOT, SLWS_F32, RWQ_SLWS,
- EMBEDDING_BAG, SPLIT_EMBEDDING, DYN_QUANTIZED_FC) = range(12, 25)
+ EMBEDDING_BAG, SPLIT_EMBEDDING, DYN_QUANTIZED_FC, BINARY_I8, MULDIV_I8, BATCHED_ADD_I8) = range(12, 28)
 
 RUNTIME_ERROR, OUT_OF_DEVICE_MEMORY, NET_NOT_FOUND, DEVICE_NONRECOVERABLE = 101, 102, 103, 104
 
@@ -174,6 +174,20 @@ class Function:
         DynamicQuantizedFullyConnected (weights_tqp = the weights' scale and offset).  weights: int8 [K, N]."""
         self.instruction(DYN_QUANTIZED_FC, [dest, src, weights, bias, -1 if scales is None else scales,
                                             -1 if offsets is None else offsets], [M, K, N, weights_tqp[1]], [weights_tqp[0]])
+
+    def binary(self, op, dest, lhs, rhs, *, n, lhs_tqp, rhs_tqp, dest_tqp):
+        """ElementAdd / Sub / Max / Min (op: ops.BINARY_*) on int8 tensors."""
+        self.instruction(BINARY_I8, [dest, lhs, rhs], [n, dest_tqp[1], lhs_tqp[1], rhs_tqp[1], op],
+                         [lhs_tqp[0], rhs_tqp[0], dest_tqp[0]])
+
+    def muldiv(self, is_div, dest, lhs, rhs, *, n, lhs_tqp, rhs_tqp, dest_tqp):
+        self.instruction(MULDIV_I8, [dest, lhs, rhs], [n, dest_tqp[1], lhs_tqp[1], rhs_tqp[1], int(bool(is_div))],
+                         [lhs_tqp[0], rhs_tqp[0], dest_tqp[0]])
+
+    def batched_add(self, dest, batch, slice_, *, num_slices, slice_size, batch_tqp, slice_tqp, dest_tqp, slice_is_int32=False):
+        self.instruction(BATCHED_ADD_I8, [dest, batch, slice_],
+                         [num_slices, slice_size, dest_tqp[1], batch_tqp[1], slice_tqp[1], int(slice_is_int32)],
+                         [batch_tqp[0], slice_tqp[0], dest_tqp[0]])
 
     def compile(self):
         _check(_lib.lib().glowb200_function_compile(self.h))

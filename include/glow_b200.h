@@ -466,6 +466,35 @@ int glowb200_element_add_i8(int8_t *dest, const int8_t *lhs, const int8_t *rhs, 
                             int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset,
                             int32_t lhs_pre, int32_t lhs_post, int32_t lhs_scale, int32_t rhs_pre,
                             int32_t rhs_post, int32_t rhs_scale, glowb200_stream_t stream);
+/* ElementAdd / Sub / Max / Min int8: the arithmetic mini-kernels libjit_element_{add,sub,max,min}_kernel_i8
+ * (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED, libjit.cpp:1593-1603, 1675-1682; triples derived at
+ * LLVMIRGen.cpp:1716-1776 from lhsScale / destScale and rhsScale / destScale). */
+#define GLOWB200_BINARY_ADD 0
+#define GLOWB200_BINARY_SUB 1
+#define GLOWB200_BINARY_MAX 2
+#define GLOWB200_BINARY_MIN 3
+int glowb200_element_binary_i8(int op, int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n,
+                               int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset,
+                               int32_t lhs_pre, int32_t lhs_post, int32_t lhs_scale, int32_t rhs_pre,
+                               int32_t rhs_post, int32_t rhs_scale, glowb200_stream_t stream);
+
+/* ElementMul / ElementDiv int8: libjit_element_mul_kernel_i8 / libjit_element_div_kernel_i8
+ * (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED_M, libjit.cpp:1610-1619, 1683-1684); one triple, from
+ * lhsScale * rhsScale / destScale (mul) or lhsScale / (rhsScale * destScale) (div),
+ * LLVMIRGen.cpp:1927-2035.  A zero divisor yields the result offset. */
+int glowb200_element_muldiv_i8(int is_div, int8_t *dest, const int8_t *lhs, const int8_t *rhs,
+                               int64_t n, int32_t dest_offset, int32_t lhs_offset,
+                               int32_t rhs_offset, int32_t pre, int32_t post, int32_t scale,
+                               glowb200_stream_t stream);
+
+/* BatchedAdd int8: libjit_batchedadd_i8 and, with an int32 slice, libjit_batchedadd_i32_i8
+ * (libjit.cpp:997-1015, 1945-1969).  batch / dest [num_slices, slice_size], slice [slice_size]. */
+int glowb200_batched_add_i8(int8_t *dest, const int8_t *batch, const void *slice, int slice_is_int32,
+                            int64_t num_slices, int64_t slice_size, int32_t dest_offset,
+                            int32_t batch_offset, int32_t slice_offset, int32_t batch_pre,
+                            int32_t batch_post, int32_t batch_scale, int32_t slice_pre,
+                            int32_t slice_post, int32_t slice_scale, glowb200_stream_t stream);
+
 /* Add followed by the int8 Relu of a residual block -- glowb200_element_add_i8 then
  * glowb200_element_maxsplat_i8(splat) on its result -- in one pass over memory (the pair is two
  * instructions in Glow's IR: ElementAdd, then the CPU backend's CPUMaxSplat,
@@ -581,6 +610,9 @@ int glowb200_peer_buffer_destroy(void *device_ptr);
 #define GLOWB200_INSTR_EMBEDDING_BAG 22  /* EmbeddingBagByteRowwiseOffsets */
 #define GLOWB200_INSTR_SPLIT_EMBEDDING 23 /* IntNBitSplitEmbedding(Weighted)Bags */
 #define GLOWB200_INSTR_DYN_QUANTIZED_FC 24 /* Dynamic(Rowwise)QuantizedFullyConnected */
+#define GLOWB200_INSTR_BINARY_I8 25       /* ElementSub / Max / Min (and Add) */
+#define GLOWB200_INSTR_MULDIV_I8 26       /* ElementMul / ElementDiv */
+#define GLOWB200_INSTR_BATCHED_ADD_I8 27  /* BatchedAdd, int8 or int32 slice */
 
 typedef struct glowb200_function glowb200_function;
 typedef struct glowb200_device_manager glowb200_device_manager;

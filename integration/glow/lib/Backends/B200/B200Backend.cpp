@@ -57,6 +57,12 @@ bool B200Backend::isOpSupported(const NodeInfo &NI) const {
   case Kinded::Kind::MatMulNodeKind:
   case Kinded::Kind::ConvolutionNodeKind:
   case Kinded::Kind::AddNodeKind:
+  case Kinded::Kind::SubNodeKind:
+  case Kinded::Kind::MaxNodeKind:
+  case Kinded::Kind::MinNodeKind:
+  case Kinded::Kind::MulNodeKind:
+  case Kinded::Kind::DivNodeKind:
+  case Kinded::Kind::BatchedAddNodeKind:
   case Kinded::Kind::ReluNodeKind:
   case Kinded::Kind::MaxPoolNodeKind:
   case Kinded::Kind::AvgPoolNodeKind:

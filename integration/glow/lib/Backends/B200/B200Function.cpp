@@ -107,6 +107,39 @@ Error B200Function::translate(const Module *module) {
       RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_ADD, ops, 3, ia, 4, fa, 3)));
       break;
     }
+    case Kinded::Kind::ElementSubInstKind:
+    case Kinded::Kind::ElementMaxInstKind:
+    case Kinded::Kind::ElementMinInstKind:
+    case Kinded::Kind::ElementMulInstKind:
+    case Kinded::Kind::ElementDivInstKind: {
+      // dest, lhs, rhs are operands 0..2 of every arithmetic instruction
+      const Value *dst = I.getOperand(0).first, *lhs = I.getOperand(1).first, *rhs = I.getOperand(2).first;
+      const auto k = I.getKind();
+      const bool muldiv = k == Kinded::Kind::ElementMulInstKind || k == Kinded::Kind::ElementDivInstKind;
+      const int64_t sel = k == Kinded::Kind::ElementSubInstKind   ? GLOWB200_BINARY_SUB
+                          : k == Kinded::Kind::ElementMaxInstKind ? GLOWB200_BINARY_MAX
+                          : k == Kinded::Kind::ElementMinInstKind ? GLOWB200_BINARY_MIN
+                                                                  : (k == Kinded::Kind::ElementDivInstKind);
+      const int32_t ops[3] = {S(dst), S(lhs), S(rhs)};
+      const int64_t ia[5] = {(int64_t)dst->size(), dst->getType()->getOffset(), lhs->getType()->getOffset(),
+                             rhs->getType()->getOffset(), sel};
+      const float fa[3] = {lhs->getType()->getScale(), rhs->getType()->getScale(), dst->getType()->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, muldiv ? GLOWB200_INSTR_MULDIV_I8 : GLOWB200_INSTR_BINARY_I8,
+                                                                  ops, 3, ia, 5, fa, 3)));
+      break;
+    }
+    case Kinded::Kind::BatchedAddInstKind: {
+      auto *N = llvm::cast<BatchedAddInst>(&I);
+      auto *B = N->getBatch();
+      const int64_t slices = (int64_t)B->dims()[0];
+      const int32_t ops[3] = {S(N->getDest()), S(B), S(N->getSlice())};
+      const int64_t ia[6] = {slices, slices ? (int64_t)B->size() / slices : 0, N->getDest()->getType()->getOffset(),
+                             B->getType()->getOffset(), N->getSlice()->getType()->getOffset(),
+                             N->getSlice()->getElementType() == ElemKind::Int32QTy};
+      const float fa[3] = {B->getType()->getScale(), N->getSlice()->getType()->getScale(), N->getDest()->getType()->getScale()};
+      RETURN_IF_ERR(fromRuntime(glowb200_function_add_instruction(fn_, GLOWB200_INSTR_BATCHED_ADD_I8, ops, 3, ia, 6, fa, 3)));
+      break;
+    }
     case Kinded::Kind::QuantizeInstKind:
     case Kinded::Kind::DequantizeInstKind: {
       const bool q = I.getKind() == Kinded::Kind::QuantizeInstKind;

@@ -554,6 +554,50 @@ ORC_API void orc_element_add_i8(int8_t *dest, const int8_t *lhs, const int8_t *r
   }
 }
 
+/* libjit_element_{sub,max,min}_kernel_i8 (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED): libjit.cpp:1593-1603,
+ * 1677-1682.  op 0 add, 1 sub, 2 max, 3 min. */
+ORC_API void orc_element_binary_i8(int op, int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n,
+                                   int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset,
+                                   int32_t lhs_pre, int32_t lhs_post, int32_t lhs_scale,
+                                   int32_t rhs_pre, int32_t rhs_post, int32_t rhs_scale) {
+  for (int64_t i = 0; i < n; i++) {
+    int32_t l = orc_scale32(lhs[i] - lhs_offset, lhs_pre, lhs_post, lhs_scale, 0);
+    int32_t r = orc_scale32(rhs[i] - rhs_offset, rhs_pre, rhs_post, rhs_scale, 0);
+    int32_t v = op == 0 ? (int32_t)((uint32_t)l + (uint32_t)r) : op == 1 ? (int32_t)((uint32_t)l - (uint32_t)r)
+              : op == 2 ? (l > r ? l : r) : (l < r ? l : r);
+    dest[i] = orc_clip_i8((int32_t)((uint32_t)v + (uint32_t)dest_offset));
+  }
+}
+
+/* libjit_element_mul_kernel_i8 / libjit_element_div_kernel_i8 (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED_M):
+ * libjit.cpp:1610-1619, 1683-1684.  A zero divisor is given the quotient 0 (the reference traps). */
+ORC_API void orc_element_muldiv_i8(int is_div, int8_t *dest, const int8_t *lhs, const int8_t *rhs, int64_t n,
+                                   int32_t dest_offset, int32_t lhs_offset, int32_t rhs_offset,
+                                   int32_t pre, int32_t post, int32_t scale) {
+  for (int64_t i = 0; i < n; i++) {
+    int32_t l = lhs[i] - lhs_offset, r = rhs[i] - rhs_offset;
+    int32_t v = is_div ? (r == 0 ? 0 : l / r) : (int32_t)((uint32_t)l * (uint32_t)r);
+    dest[i] = orc_clip_i8(orc_scale32(v, pre, post, scale, dest_offset));
+  }
+}
+
+/* libjit_batchedadd_quantized: libjit.cpp:997-1015 (libjit_batchedadd_i8, libjit_batchedadd_i32_i8). */
+ORC_API void orc_batched_add_i8(int8_t *dest, const int8_t *batch, const void *slice, int slice_is_i32,
+                                int64_t num_slices, int64_t slice_size, int32_t dest_offset,
+                                int32_t batch_offset, int32_t slice_offset, int32_t batch_pre,
+                                int32_t batch_post, int32_t batch_scale, int32_t slice_pre,
+                                int32_t slice_post, int32_t slice_scale) {
+  for (int64_t n = 0; n < num_slices; n++)
+    for (int64_t i = 0; i < slice_size; i++) {
+      int32_t b = batch[n * slice_size + i] - batch_offset;
+      int32_t sv = slice_is_i32 ? ((const int32_t *)slice)[i] : ((const int8_t *)slice)[i];
+      int32_t s = (int32_t)((uint32_t)sv - (uint32_t)slice_offset);
+      int32_t x = orc_scale32(b, batch_pre, batch_post, batch_scale, 0);
+      int32_t y = orc_scale32(s, slice_pre, slice_post, slice_scale, 0);
+      dest[n * slice_size + i] = orc_clip_i8((int32_t)((uint32_t)x + (uint32_t)y + (uint32_t)dest_offset));
+    }
+}
+
 /* libjit_element_relu_i8: libjit.cpp:1850-1858: max(x, srcOffset) then rescale. */
 ORC_API void orc_element_relu_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t src_offset,
                                  int32_t dest_offset, int32_t pre, int32_t post, int32_t scale) {

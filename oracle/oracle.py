@@ -396,6 +396,36 @@ def element_add_i8(lhs, rhs, dest_offset, lhs_offset, rhs_offset, lhs_triple, rh
     return out
 
 
+def element_binary_i8(op, lhs, rhs, dest_offset, lhs_offset, rhs_offset, lhs_triple, rhs_triple):
+    """op 0 add, 1 sub, 2 max, 3 min."""
+    lhs, rhs = _c(lhs, np.int8), _c(rhs, np.int8)
+    out = np.empty_like(lhs)
+    lib().orc_element_binary_i8(C.c_int(op), _ptr(out), _ptr(lhs), _ptr(rhs), _i64(lhs.size), _i32(dest_offset),
+                                _i32(lhs_offset), _i32(rhs_offset), *[_i32(int(v)) for v in lhs_triple],
+                                *[_i32(int(v)) for v in rhs_triple])
+    return out
+
+
+def element_muldiv_i8(is_div, lhs, rhs, dest_offset, lhs_offset, rhs_offset, triple):
+    lhs, rhs = _c(lhs, np.int8), _c(rhs, np.int8)
+    out = np.empty_like(lhs)
+    lib().orc_element_muldiv_i8(C.c_int(int(is_div)), _ptr(out), _ptr(lhs), _ptr(rhs), _i64(lhs.size), _i32(dest_offset),
+                                _i32(lhs_offset), _i32(rhs_offset), *[_i32(int(v)) for v in triple])
+    return out
+
+
+def batched_add_i8(batch, slice_, dest_offset, batch_offset, slice_offset, batch_triple, slice_triple):
+    batch = _c(batch, np.int8)
+    is32 = np.asarray(slice_).dtype == np.int32
+    slice_ = _c(slice_, np.int32 if is32 else np.int8)
+    out = np.empty_like(batch)
+    lib().orc_batched_add_i8(_ptr(out), _ptr(batch), _ptr(slice_), C.c_int(int(is32)), _i64(batch.shape[0]),
+                             _i64(batch.size // max(batch.shape[0], 1)), _i32(dest_offset), _i32(batch_offset),
+                             _i32(slice_offset), *[_i32(int(v)) for v in batch_triple],
+                             *[_i32(int(v)) for v in slice_triple])
+    return out
+
+
 def element_relu_i8(src, src_offset, dest_offset, triple):
     src = _c(src, np.int8)
     out = np.empty_like(src)
@@ -640,6 +670,31 @@ class LibjitRef:
                        _i32(lhs_offset), _i32(rhs_offset), *[_i32(int(v)) for v in lhs_triple],
                        *[_i32(int(v)) for v in rhs_triple])
         return np.array(r, np.int8).reshape(lhs.shape)
+
+    def element_binary_i8(self, op, lhs, rhs, dest_offset, lhs_offset, rhs_offset, lhs_triple, rhs_triple):
+        lhs, rhs = _c(lhs, np.int8), _c(rhs, np.int8)
+        name = "libjit_element_%s_kernel_i8" % ("add", "sub", "max", "min")[op]
+        r = self._elem(name, C.c_int8, lhs.size, _ptr(lhs), _ptr(rhs), _i32(dest_offset), _i32(lhs_offset),
+                       _i32(rhs_offset), *[_i32(int(v)) for v in lhs_triple], *[_i32(int(v)) for v in rhs_triple])
+        return np.array(r, np.int8).reshape(lhs.shape)
+
+    def element_muldiv_i8(self, is_div, lhs, rhs, dest_offset, lhs_offset, rhs_offset, triple):
+        lhs, rhs = _c(lhs, np.int8), _c(rhs, np.int8)
+        name = "libjit_element_%s_kernel_i8" % ("div" if is_div else "mul")
+        r = self._elem(name, C.c_int8, lhs.size, _ptr(lhs), _ptr(rhs), _i32(dest_offset), _i32(lhs_offset),
+                       _i32(rhs_offset), *[_i32(int(v)) for v in triple])
+        return np.array(r, np.int8).reshape(lhs.shape)
+
+    def batched_add_i8(self, batch, slice_, dest_offset, batch_offset, slice_offset, batch_triple, slice_triple):
+        batch = _c(batch, np.int8)
+        is32 = np.asarray(slice_).dtype == np.int32
+        slice_ = _c(slice_, np.int32 if is32 else np.int8)
+        out = np.empty_like(batch)
+        fn = self.l.libjit_batchedadd_i32_i8 if is32 else self.l.libjit_batchedadd_i8
+        fn(_ptr(out), _ptr(batch), _ptr(slice_), C.c_uint64(batch.shape[0]), C.c_uint64(batch.size // batch.shape[0]),
+           _i32(dest_offset), _i32(batch_offset), _i32(slice_offset), *[_i32(int(v)) for v in batch_triple],
+           *[_i32(int(v)) for v in slice_triple])
+        return out
 
     def element_quantize_i8(self, src, scale, offset):
         src = _c(src, np.float32)

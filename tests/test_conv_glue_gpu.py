@@ -152,3 +152,24 @@ def test_transpose():
     np.testing.assert_array_equal(ops.transpose(t(y), (2, 0, 1)).cpu().numpy(), np.transpose(y, (2, 0, 1)))
     z = rng.integers(-128, 128, (40, 33)).astype(np.int8)
     np.testing.assert_array_equal(ops.transpose(t(z), (1, 0)).cpu().numpy(), z.T)
+
+
+def test_binary_muldiv_batched_add_bit_exact(oracle):
+    """Sub / Max / Min, Mul / Div and BatchedAdd (int8 and int32 slice) against the oracle."""
+    rng = np.random.default_rng(29)
+    a = rng.integers(-128, 128, 70_001).astype(np.int8)
+    b = rng.integers(-128, 128, 70_001).astype(np.int8)
+    lt, rt = ops.quantize_scale_offset_32to8(0.7), ops.quantize_scale_offset_32to8(1.9)
+    for op in (ops.BINARY_ADD, ops.BINARY_SUB, ops.BINARY_MAX, ops.BINARY_MIN):
+        np.testing.assert_array_equal(ops.element_binary_i8(op, t(a), t(b), 5, -3, 9, lt, rt).cpu().numpy(),
+                                      oracle.element_binary_i8(op, a, b, 5, -3, 9, lt, rt))
+    tm, td = ops.quantize_scale_offset_32to8(0.011), ops.quantize_scale_offset_32to8(3.3)
+    np.testing.assert_array_equal(ops.element_muldiv_i8(False, t(a), t(b), 2, -3, 9, tm).cpu().numpy(),
+                                  oracle.element_muldiv_i8(False, a, b, 2, -3, 9, tm))
+    np.testing.assert_array_equal(ops.element_muldiv_i8(True, t(a), t(b), 2, -3, 9, td).cpu().numpy(),
+                                  oracle.element_muldiv_i8(True, a, b, 2, -3, 9, td))      # zero divisors included
+    batch = rng.integers(-128, 128, (333, 517)).astype(np.int8)
+    for sl in (rng.integers(-128, 128, 517).astype(np.int8), rng.integers(-100000, 100000, 517).astype(np.int32)):
+        st = ops.quantize_scale_offset_32to8(0.004 if sl.dtype == np.int32 else 1.3)
+        np.testing.assert_array_equal(ops.batched_add_i8(t(batch), t(sl), -6, 4, 1, lt, st).cpu().numpy(),
+                                      oracle.batched_add_i8(batch, sl, -6, 4, 1, lt, st))

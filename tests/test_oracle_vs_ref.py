@@ -217,3 +217,25 @@ def test_quantization_profile_vs_libjit(oracle, libjit_ref, bins):
         np.testing.assert_array_equal(h_o.view(np.uint32), h_r.view(np.uint32))
     if bins:
         assert h_o.sum() == 5000 + 777 + 9000 + 3000 + 100 + 1
+
+
+def test_binary_muldiv_batched_add_vs_libjit(oracle, libjit_ref):
+    """The remaining arithmetic mini-kernels (sub / max / min, mul / div) and BatchedAdd (int8 and
+    int32 slice): the restatement against libjit, bit for bit."""
+    rng = np.random.default_rng(31)
+    a = rng.integers(-128, 128, 700).astype(np.int8)
+    b = rng.integers(-128, 128, 700).astype(np.int8)
+    lt, rt = oracle.quantize_scale_offset_32to8(0.7), oracle.quantize_scale_offset_32to8(1.9)
+    for op in range(4):
+        np.testing.assert_array_equal(oracle.element_binary_i8(op, a, b, 5, -3, 9, lt, rt),
+                                      libjit_ref.element_binary_i8(op, a, b, 5, -3, 9, lt, rt))
+    np.testing.assert_array_equal(oracle.element_binary_i8(0, a, b, 5, -3, 9, lt, rt), oracle.element_add_i8(a, b, 5, -3, 9, lt, rt))
+    tm = oracle.quantize_scale_offset_32to8(0.011)
+    np.testing.assert_array_equal(oracle.element_muldiv_i8(False, a, b, 2, -3, 9, tm), libjit_ref.element_muldiv_i8(False, a, b, 2, -3, 9, tm))
+    td = oracle.quantize_scale_offset_32to8(3.3)
+    b_nz = np.where(b == 9, np.int8(10), b)            # the reference divides by (rhs - rhsOffset)
+    np.testing.assert_array_equal(oracle.element_muldiv_i8(True, a, b_nz, 2, -3, 9, td), libjit_ref.element_muldiv_i8(True, a, b_nz, 2, -3, 9, td))
+    batch = rng.integers(-128, 128, (13, 40)).astype(np.int8)
+    for sl in (rng.integers(-128, 128, 40).astype(np.int8), rng.integers(-100000, 100000, 40).astype(np.int32)):
+        st = oracle.quantize_scale_offset_32to8(0.004 if sl.dtype == np.int32 else 1.3)
+        np.testing.assert_array_equal(oracle.batched_add_i8(batch, sl, -6, 4, 1, lt, st), libjit_ref.batched_add_i8(batch, sl, -6, 4, 1, lt, st))

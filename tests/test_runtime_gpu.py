@@ -389,3 +389,37 @@ def test_split_embedding_and_dynamic_fc_instructions(oracle, dm):
                                                        out_fp16=True)
     want = oracle.dynamic_rowwise_quantized_fc(want_pooled, w, bias, scales, woff)
     np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def test_arithmetic_glue_instructions(oracle, dm):
+    """Sub, Max, Mul, Div and BatchedAdd as instructions: the runtime derives their integer
+    parameters from the tensors' scales as LLVMIRGen does; results against the oracle."""
+    rng = np.random.default_rng(17)
+    n, rows = 4096, 64
+    a = rng.integers(-128, 128, n).astype(np.int8)
+    b = rng.integers(-128, 128, n).astype(np.int8)
+    sl = rng.integers(-128, 128, n // rows).astype(np.int8)
+    ta, tb, td, ts = (0.02, -3), (0.05, 9), (0.04, 5), (0.03, 1)
+    f = runtime.Function("arith")
+    pa, pb, psl = f.placeholder("a", n), f.placeholder("b", n), f.placeholder("slice", n // rows)
+    outs = {k: f.placeholder(k, n) for k in ("sub", "max", "mul", "div", "badd")}
+    f.binary(ops.BINARY_SUB, outs["sub"], pa, pb, n=n, lhs_tqp=ta, rhs_tqp=tb, dest_tqp=td)
+    f.binary(ops.BINARY_MAX, outs["max"], pa, pb, n=n, lhs_tqp=ta, rhs_tqp=tb, dest_tqp=td)
+    f.muldiv(False, outs["mul"], pa, pb, n=n, lhs_tqp=ta, rhs_tqp=tb, dest_tqp=td)
+    f.muldiv(True, outs["div"], pa, pb, n=n, lhs_tqp=ta, rhs_tqp=tb, dest_tqp=td)
+    f.batched_add(outs["badd"], pa, psl, num_slices=rows, slice_size=n // rows, batch_tqp=ta, slice_tqp=ts, dest_tqp=td)
+    f.compile()
+    dm.add_network(f)
+    got = {k: np.zeros(n, np.int8) for k in outs}
+    dm.run_function("arith", dict(a=a, b=b, slice=sl, **got))
+    q = oracle.quantize_scale_offset_32to8
+    f32 = np.float32
+    lt, rt = q(f32(ta[0]) / f32(td[0])), q(f32(tb[0]) / f32(td[0]))
+    np.testing.assert_array_equal(got["sub"], oracle.element_binary_i8(1, a, b, td[1], ta[1], tb[1], lt, rt))
+    np.testing.assert_array_equal(got["max"], oracle.element_binary_i8(2, a, b, td[1], ta[1], tb[1], lt, rt))
+    np.testing.assert_array_equal(got["mul"], oracle.element_muldiv_i8(False, a, b, td[1], ta[1], tb[1],
+                                                                     q(f32(ta[0]) * f32(tb[0]) / f32(td[0]))))
+    np.testing.assert_array_equal(got["div"], oracle.element_muldiv_i8(True, a, b, td[1], ta[1], tb[1],
+                                                                     q(f32(ta[0]) / (f32(tb[0]) * f32(td[0])))))
+    np.testing.assert_array_equal(got["badd"], oracle.batched_add_i8(a.reshape(rows, -1), sl, td[1], ta[1], ts[1], lt,
+                                                                      q(f32(ts[0]) / f32(td[0]))).reshape(-1))
