@@ -679,6 +679,48 @@ def run_model_line(args):
         dist.destroy_process_group()
 
 
+def slws4_cpu_rate(D, seconds, threads):
+    """The fifth configuration's CPU baseline: the reference has no CPU-backend kernel for the
+    4-bit kinds, so this times the restatement of its Interpreter kernel (oracle, plain C, one
+    call per thread on its own slice of bags) over one 10,000,000-row host table with the
+    workload's bag law.  -> (GB/s, passes, seconds)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import oracle as orc
+    orc.lib()
+    rows, line = 10_000_000, D // 2 + 4
+    rng = np.random.Generator(np.random.PCG64(0x610B200 + D))
+    table = rng.integers(0, 256, (rows, line), dtype=np.uint8)
+    so = np.stack([rng.uniform(0.001, 0.01, rows), rng.uniform(-1, 1, rows)], 1).astype(np.float16)
+    table[:, D // 2:] = so.view(np.uint8)
+    bags = 64          # per thread and pass
+    reqs = []
+    for r in range(6):
+        per = []
+        for k in range(threads):
+            lengths = rng.poisson(64, bags).astype(np.int32)
+            n = int(lengths.sum())
+            per.append((lengths, rng.integers(0, rows, n).astype(np.int64), rng.uniform(0, 1, n).astype(np.float16)))
+        reqs.append(per)
+
+    def one(job):
+        lengths, idx, w = job
+        orc.frwq_slws_interp(table, 3, w, idx, lengths, out_fp16=True, fp16_acc=False)
+        return int(lengths.sum())
+
+    moved = 0
+    with ThreadPoolExecutor(threads) as ex:
+        list(ex.map(one, reqs[0]))
+        passes, t0 = 0, time.perf_counter()
+        while True:
+            n = sum(ex.map(one, reqs[(passes + 1) % len(reqs)]))
+            moved += n * (line + 8 + 2) + threads * bags * (4 + 2 * D)
+            passes += 1
+            dt = time.perf_counter() - t0
+            if dt >= seconds:
+                break
+    return moved / dt / 1e9, passes, dt
+
+
 def run_slws4_line(args):
     """--workload slws4: one point of the 4-bit embedding bandwidth sweep (fifth benchmark
     configuration): UInt4FusedFP16QTy tables of 10,000,000 rows x D (D/2 + 4 bytes per row),
@@ -763,7 +805,7 @@ def run_slws4_line(args):
         peak, src = measured_peak_hbm()
         value = float(mv[0]) / (float(tm[0]) * 1e-3) / 1e9
         per_gpu = value / world
-        print(json.dumps({
+        line = {
             "metric": "frwq_slws_4bit_hbm_gbps", "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": float(tm[0]) / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u4 -> f32 accumulate -> f16", "data": "synthetic",
@@ -774,7 +816,15 @@ def run_slws4_line(args):
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "peak_source": src, "traffic": None, "kernel": "slws_gather_select_kernel<4,1,1,long,P>",
                          "rows_per_s": sum(int(reqs[i % R][3][-1]) for i in range(args.steps)) / (ms * 1e-3)},
-            "gpu_launches": 2 * args.steps, "clocks": clocks}))
+            "gpu_launches": 2 * args.steps, "clocks": clocks}
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            v, passes, dt = slws4_cpu_rate(D, min(args.cpu_seconds, 10.0), threads)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": "restatement of the reference's Interpreter kernel (the CPU backend has none "
+                                              "for 4-bit tables): one 10,000,000-row table, 64 bags per thread per pass, "
+                                              "%d passes in %.1f s" % (passes, dt)}
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
