@@ -163,3 +163,64 @@ def test_empty_request():
         t(np.array([3], np.int32)), t(np.array([0], np.int32)), t(np.array([2], np.uint8)),
         t(np.array([0, 4], np.int32)), 4, z32, t(np.zeros(4, np.int32)))
     assert out.shape == (3, 4) and not out.any()
+
+
+def test_properties_on_large_tables():
+    """Sizes the oracle does not reach in seconds (three tables, 8.5 M rows, 0.9 GB; 12,288 bags of
+    about 50 rows): properties that hold bit for bit whatever the size -- weights of 1 equal the
+    unweighted operator, a power-of-two weight scales an fp32 result exactly, mean pooling is the
+    sum divided by the bag length, and the batched launch equals one launch per table."""
+    g = torch.Generator(device=DEV).manual_seed(11)
+    specs = [(ops.EST_INT4, 128, 4_000_000), (ops.EST_INT8, 64, 3_000_000), (ops.EST_FLOAT16, 96, 1_500_000)]
+    B = 4096
+    parts, offs, at = [], [], 0
+    for ty, d, rows in specs:
+        rb = ops.split_embedding_row_bytes(d, ty)
+        tab = torch.randint(0, 256, (rows, rb), dtype=torch.uint8, device=DEV, generator=g)
+        if ty == ops.EST_FLOAT16:
+            tab.view(torch.float16).normal_(0, 1, generator=g)
+        else:
+            so = torch.stack([torch.empty(rows, device=DEV).uniform_(0.001, 0.01, generator=g),
+                              torch.empty(rows, device=DEV).uniform_(-1, 1, generator=g)], 1).to(torch.float16)
+            tab[:, :4] = so.view(torch.uint8).view(rows, 4)
+        offs.append(at)
+        parts.append(tab.reshape(-1))
+        at += tab.numel()
+    weights = torch.cat(parts)
+    T = len(specs)
+    tys = t(np.array([s[0] for s in specs], np.uint8))
+    place = t(np.full(T, ops.PLACEMENT_HOST, np.int32))
+    wo = t(np.array(offs, np.int64))
+    dims = np.array([0] + [d for _, d, _ in specs]).cumsum().astype(np.int32)
+    D = int(dims[-1])
+    rng = np.random.default_rng(2)
+    lens = rng.poisson(50, (T, B))
+    offsets_h = np.concatenate([[0], np.cumsum(lens.reshape(-1))]).astype(np.int64)
+    idx = torch.cat([torch.randint(0, rows, (int(lens[i].sum()),), device=DEV, generator=g)
+                     for i, (_, _, rows) in enumerate(specs)])
+    offsets = t(offsets_h)
+    st = ops.new_status(DEV)
+
+    def run(pool=ops.EP_SUM, iw=None, dt=torch.float32):
+        return ops.int_nbit_split_embedding_bags(weights, weights, place, wo, tys, t(dims), D, idx, offsets, pool,
+                                                 indice_weights=iw, out_dtype=dt, status=st)
+
+    base = run()
+    assert torch.isfinite(base).all() and base.abs().max() > 1
+    ones = torch.ones(idx.numel(), device=DEV)
+    assert torch.equal(run(iw=ones), base)
+    assert torch.equal(run(iw=ones * 0.25), base * 0.25)
+    n = torch.from_numpy(lens.T.astype(np.float32)).to(DEV)                      # [B, T]
+    per_col = torch.repeat_interleave(n, torch.tensor([d for _, d, _ in specs], device=DEV), dim=1)
+    want_mean = torch.where(per_col > 0, base / per_col.clamp(min=1), base)
+    assert torch.equal(run(pool=ops.EP_MEAN), want_mean)
+    base16 = run(dt=torch.float16)
+    assert torch.equal(run(iw=ones.to(torch.float16), dt=torch.float16), base16)
+    # one launch per table
+    for i, (ty, d, rows) in enumerate(specs):
+        lo, hi = int(offsets_h[i * B]), int(offsets_h[(i + 1) * B])
+        single = ops.int_nbit_split_embedding_bags(
+            weights, weights, place[i:i + 1], wo[i:i + 1], tys[i:i + 1], t(np.array([0, d], np.int32)), d,
+            idx[lo:hi], t(offsets_h[i * B:(i + 1) * B + 1] - lo), ops.EP_SUM, status=st)
+        assert torch.equal(single, base[:, int(dims[i]):int(dims[i + 1])])
+    assert int(st.item()) == 0
