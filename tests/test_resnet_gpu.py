@@ -10,6 +10,47 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+def run_oracle(oracle, layers, q, x_nchw):
+    """The same quantized network through the CPU oracle (numpy in, int8 logits out)."""
+    tqp = q["tqp"]
+    x = oracle.element_quantize_i8(np.ascontiguousarray(np.transpose(x_nchw, (0, 2, 3, 1))), *tqp["input"])
+
+    def conv(name, t):
+        c = q["conv"][name]
+        spec = c["spec"]
+        k, s, p = (spec["k"],) * 2, (spec["stride"],) * 2, (spec["pad"],) * 4
+        ohw = ops.conv_out_hw(t.shape[1:3], k, s, p)
+        return oracle.conv2d_i8_i32(t, c["filter"], c["bias"], ohw, k, s, p, 1, (1, 1), c["out_offset"], c["in_offset"],
+                                    c["filter_offsets"], c["bias_offsets"], c["params"][:3], c["params"][3:],
+                                    1 if spec["relu"] else 0, None)
+
+    for l in layers:
+        if l[0] == "conv":
+            x = conv(l[1]["name"], x)
+        elif l[0] == "maxpool":
+            x = oracle.max_pool_i8(x, ops.conv_out_hw(x.shape[1:3], (3, 3), (2, 2), (1, 1, 1, 1)), (3, 3), (2, 2), (1, 1, 1, 1),
+                                   tqp["conv1"][1])
+        elif l[0] == "block":
+            y = x
+            for c in l[2]:
+                y = conv(c["name"], y)
+            sc = conv(l[3]["name"], x) if l[3] else x
+            a = q["add"][l[1]]
+            out_off = tqp[a["out"]][1]
+            x = oracle.element_add_i8(y, sc, out_off, tqp[a["lhs"]][1], tqp[a["rhs"]][1], a["lhs_triple"], a["rhs_triple"])
+            x = oracle.element_maxsplat_i8(x, out_off)
+        elif l[0] == "avgpool":
+            src = q["avgpool_in"]
+            hw = x.shape[1]
+            tr = ops.quantize_scale_offset_32to8(np.float32(tqp[src][0]) / np.float32(tqp["avgpool"][0]) / np.float32(hw * hw))
+            x = oracle.avg_pool_i8(x, (1, 1), (hw, hw), (1, 1), (0, 0, 0, 0), True, tqp["avgpool"][1], tqp[src][1], tr)
+        elif l[0] == "fc":
+            f = q["fc"]
+            x = oracle.rowwise_quantized_fc_i8_i32(x.reshape(x.shape[0], -1), f["w"], f["bias"], f["w_offsets"], f["params"][:3],
+                                                   f["params"][3:], tqp["fc"][1], tqp[f["in_name"]][1], 0)
+    return x
+
+
 @pytest.fixture(scope="module")
 def net():
     layers = resnet.architecture(num_classes=100)
@@ -29,7 +70,7 @@ def test_resnet50_int8_bit_exact_against_oracle(oracle, net):
     logits = model.forward(x.to(DEV))
     torch.cuda.synchronize()
     assert int(model.status.item()) == 0
-    want = resnet.run_oracle(oracle, layers, q, x.numpy())
+    want = run_oracle(oracle, layers, q, x.numpy())
     np.testing.assert_array_equal(model.logits_q.cpu().numpy(), want)
     assert len(np.unique(want)) > 20
     # and the quantized network still tracks the fp32 one (quantisation error only)
