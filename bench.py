@@ -1366,10 +1366,24 @@ def main():
         q1.record()
         torch.cuda.synchronize()
         us = q0.elapsed_time(q1) * 1e3 / 200
+        # the same 200 launches replayed as one CUDA graph: the device's own latency per launch pair,
+        # without the host's call-and-launch pace
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(200):
+                one.run(status)
+        graph.replay()
+        torch.cuda.synchronize()
+        q0.record()
+        graph.replay()
+        q1.record()
+        torch.cuda.synchronize()
+        us_graph = q0.elapsed_time(q1) * 1e3 / 200
         single_extra = {"metric": METRIC, "value": algorithmic_bytes(int(starts[1]), BATCH) / (us * 1e-6) / 1e9,
-                        "unit": UNIT, "us_per_launch": us,
+                        "unit": UNIT, "us_per_launch": us, "us_per_launch_in_graph": us_graph,
                         "note": "one 1,000,000 x 64 table per launch (segments + gather kernels back to back, "
-                                "200 launches): the table stays in L2, the figure is launch latency"}
+                                "200 launches from the host, then the same 200 as one CUDA graph): the table "
+                                "stays in L2, the figure is launch latency"}
 
     sample_tables = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
