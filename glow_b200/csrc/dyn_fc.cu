@@ -137,6 +137,97 @@ __global__ void __launch_bounds__(kQuantThreads, 6) dyn_quantize_rows_kernel(con
   if (tid == 0) row_scales[row] = scale;
 }
 
+// fp16 bits -> float through the mixed-precision add (adding -0 keeps every value): conversion
+// instructions issue at an eighth of the rate.
+__device__ __forceinline__ float widen_f16(uint32_t h) {
+  float d;
+  asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"((uint16_t)(h & 0xFFFFu)), "f"(-0.0f));
+  return d;
+}
+
+// A WARP per row (K a multiple of 8, 16-byte aligned rows): the range is found on the fp16 pairs
+// themselves and reduced with shuffles, the second pass reads the row again (from L1 / L2) so
+// that few registers are held and many warps stay resident, and no block-wide barrier sits
+// between the load and the store.  Eight elements are quantized by reciprocal at a time; a tie
+// candidate among them sends the eight through the exact division.
+__global__ void __launch_bounds__(256) dyn_quantize_rows_warp_kernel(const __half *__restrict__ in, int M, int K,
+                                                                     int8_t *__restrict__ q, float *__restrict__ row_scales,
+                                                                     int32_t *__restrict__ row_sums, int32_t *status) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const __half *x = in + (size_t)row * K;
+  // minMaxArg over the row (NaNs never win a comparison; min / max of fp16 numbers is exact)
+  __half2 mn2 = __half2half2(x[0]), mx2 = mn2;
+#pragma unroll 4
+  for (int k = lane * 8; k < K; k += 256) {
+    const uint4 v = *reinterpret_cast<const uint4 *>(x + k);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const __half2 h = *reinterpret_cast<const __half2 *>(&w[i]);
+      mn2 = __hmin2(mn2, h);
+      mx2 = __hmax2(mx2, h);
+    }
+  }
+  float mn = fminf(__low2float(mn2), __high2float(mn2)), mx = fmaxf(__low2float(mx2), __high2float(mx2));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, d));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+  }
+  double scale_d;
+  int32_t offset;
+  choose_quantization_params_basic(mn, mx, /*Symmetric*/ 1, -128, 127, scale_d, offset);
+  const float scale = (float)scale_d, foffset = (float)offset;
+  const float rcp = __frcp_rn(scale);
+  if (offset != 0 && lane == 0 && status != nullptr) atomicOr(status, GLOWB200_STATUS_UNSUPPORTED_TABLE);
+  int32_t sum = 0;
+  int8_t *o = q + (size_t)row * K;
+#pragma unroll 2
+  for (int k = lane * 8; k < K; k += 256) {
+    const uint4 v = *reinterpret_cast<const uint4 *>(x + k);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      f[2 * i] = widen_f16(w[i]);
+      f[2 * i + 1] = widen_f16(w[i] >> 16);
+    }
+    int32_t r[8];
+    bool exact = offset != 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      // x times the row's reciprocal, rounded to the nearest integer by the 1.5 * 2^23 trick, which
+      // leaves the integer in the mantissa; within 1e-4 of a tie (the product is within 3e-5 of
+      // the true quotient at |quotient| <= 128), or when not small, the exact division decides
+      const float p = __fmul_rn(f[i], rcp);
+      const float m = __fadd_rn(p, 12582912.0f);
+      const float d = fabsf(__fsub_rn(p, __fsub_rn(m, 12582912.0f)));
+      exact |= !(d < 0.4999f) || !(fabsf(p) < 1000.0f);
+      const int32_t t = __float_as_int(m) - 0x4B400000;
+      r[i] = t < -128 ? -128 : (t > 127 ? 127 : t);
+    }
+    if (exact) {  // (unrolled: a loop would put f and r into local memory)
+#pragma unroll
+      for (int i = 0; i < 8; i++) r[i] = quantize_i8(f[i], scale, foffset);
+    }
+    uint32_t packed[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      sum += r[4 * h] + r[4 * h + 1] + r[4 * h + 2] + r[4 * h + 3];
+      packed[h] = (uint32_t)(r[4 * h] & 0xff) | ((uint32_t)(r[4 * h + 1] & 0xff) << 8) | ((uint32_t)(r[4 * h + 2] & 0xff) << 16) |
+                  ((uint32_t)(r[4 * h + 3] & 0xff) << 24);
+    }
+    *reinterpret_cast<uint2 *>(o + k) = make_uint2(packed[0], packed[1]);
+  }
+  if (row_sums != nullptr) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    if (lane == 0) row_sums[row] = sum;
+  }
+  if (lane == 0) row_scales[row] = scale;
+}
+
 int run(void *out, const void *in, const int8_t *weights, const float *bias, const float *scales, const int32_t *offsets,
         float u_scale, int32_t u_offset, int64_t M, int64_t K, int64_t N, const int8_t *weights_transposed, int flags,
         void *workspace, size_t workspace_bytes, int32_t *status, cudaStream_t s) {
@@ -158,9 +249,11 @@ int run(void *out, const void *in, const int8_t *weights, const float *bias, con
   int8_t *wt = reinterpret_cast<int8_t *>(w);
   w += align_up((size_t)N * K, 256);
   const bool offsets_zero = (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) != 0 || (offsets == nullptr && u_offset == 0);
-  if ((K % 8) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0)
-    dyn_quantize_rows_kernel<true><<<(unsigned)M, kQuantThreads, 0, s>>>(reinterpret_cast<const __half *>(in), (int)M, (int)K, q,
-                                                                          row_scales, offsets_zero ? nullptr : row_sums, status);
+  const bool vec = (K % 8) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0;
+  int32_t *sums = offsets_zero ? nullptr : row_sums;
+  const __half *x = reinterpret_cast<const __half *>(in);
+  if (vec)
+    dyn_quantize_rows_warp_kernel<<<(unsigned)((M + 7) / 8), 256, 0, s>>>(x, (int)M, (int)K, q, row_scales, sums, status);
   else
     dyn_quantize_rows_kernel<false><<<(unsigned)M, kQuantThreads, 0, s>>>(reinterpret_cast<const __half *>(in), (int)M, (int)K, q,
                                                                            row_scales, offsets_zero ? nullptr : row_sums, status);

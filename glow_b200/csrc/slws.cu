@@ -70,6 +70,9 @@ __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
 #ifndef GLOWB200_SLWS_P4_FROM
 #define GLOWB200_SLWS_P4_FROM 16
 #endif
+#ifndef GLOWB200_SLWS_MAX_BPW
+#define GLOWB200_SLWS_MAX_BPW 8
+#endif
 #ifndef GLOWB200_SLWS_UNROLL_P2
 #define GLOWB200_SLWS_UNROLL_P2 4
 #endif
@@ -841,7 +844,7 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
       const int64_t max_segments = (int64_t)grid.x * (kGatherThreads >> L.lpr_log2);
       const int64_t total = max_segments * grid.y, want = (int64_t)sm_count() * 24 * 4;
       int bpw = (int)(total / want);
-      bpw = bpw < 1 ? 1 : (bpw > 8 ? 8 : bpw);
+      bpw = bpw < 1 ? 1 : (bpw > GLOWB200_SLWS_MAX_BPW ? GLOWB200_SLWS_MAX_BPW : bpw);
       const int64_t warps = (max_segments + bpw - 1) / bpw;
       const unsigned wblocks = (unsigned)((warps + 7) / 8);
       dim3 sgrid(wblocks > grid.x ? wblocks : grid.x, grid.y);

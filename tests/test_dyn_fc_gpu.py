@@ -31,7 +31,7 @@ def make(seed, M, K, N, zero_offsets):
 
 
 @pytest.mark.parametrize("M,K,N", [(5, 64, 48), (130, 256, 300), (64, 100, 33), (257, 1024, 512), (1, 16, 1),
-                                   (128, 2048, 64)])
+                                   (128, 2048, 64), (33, 4096, 40), (16, 8192, 32), (9, 4104, 16), (7, 9000, 8)])
 @pytest.mark.parametrize("zero_offsets", [True, False])
 @pytest.mark.parametrize("transposed", [False, True])
 def test_dynamic_rowwise_quantized_fc(oracle, M, K, N, zero_offsets, transposed):
