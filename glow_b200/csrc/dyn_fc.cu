@@ -9,7 +9,7 @@
 // include/glow/Quantization/Base/Base.h:322-329), multiplied with the int8 weights into int32
 // sums, and the result is fp16(float(sum) * (row scale * weight scale[j]) + bias[j]).
 //
-// Two launches: a block per input row finds the range, derives the parameters in the reference's
+// Two launches: a warp per input row finds the range, derives the parameters in the reference's
 // double arithmetic and writes the int8 row, its scale and (for weights with offsets) its sum;
 // then the tcgen05 contraction of qgemm.cu runs with its floating-point drain.
 #include "qgemm.cuh"
@@ -26,14 +26,10 @@ __device__ __forceinline__ int32_t quantize_i8(float x, float scale, float offse
 }
 
 // in [M, K] fp16 -> q [M, K] int8, row_scales [M], row_sums [M] (may be nullptr).  A block per
-// row.  VEC: 8 elements per thread per step through 16-byte loads and 8-byte stores (K a
-// multiple of 8, 16-byte aligned rows); rows of up to 8192 elements stay in registers between
-// the range pass and the quantizing pass, longer ones are read again.
+// row, element by element: the form for rows that are not 16-byte aligned multiples of 8.
 constexpr int kQuantThreads = 256;
-constexpr int kQuantCache = 4;  // 16-byte loads a thread keeps
 
-template <bool VEC>
-__global__ void __launch_bounds__(kQuantThreads, 6) dyn_quantize_rows_kernel(const __half *__restrict__ in, int M, int K,
+__global__ void __launch_bounds__(kQuantThreads) dyn_quantize_rows_kernel(const __half *__restrict__ in, int M, int K,
                                                                           int8_t *__restrict__ q, float *__restrict__ row_scales,
                                                                           int32_t *__restrict__ row_sums, int32_t *status) {
   __shared__ float s_mn[kQuantThreads / 32], s_mx[kQuantThreads / 32];
@@ -42,36 +38,10 @@ __global__ void __launch_bounds__(kQuantThreads, 6) dyn_quantize_rows_kernel(con
   const __half *x = in + (size_t)row * K;
   // minMaxArg over the row: NaNs never win a comparison
   float mn = __half2float(x[0]), mx = mn;
-  uint4 cache[kQuantCache];
-  const bool cached = VEC && K <= kQuantThreads * 8 * kQuantCache;
-  auto range8 = [&](const uint4 &v) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-      mn = f.x < mn ? f.x : mn; mx = f.x > mx ? f.x : mx;
-      mn = f.y < mn ? f.y : mn; mx = f.y > mx ? f.y : mx;
-    }
-  };
-  if constexpr (VEC) {
-    if (cached) {
-#pragma unroll
-      for (int c = 0; c < kQuantCache; c++) {
-        const int k = (c * kQuantThreads + tid) * 8;
-        if (k < K) cache[c] = *reinterpret_cast<const uint4 *>(x + k);
-      }
-#pragma unroll
-      for (int c = 0; c < kQuantCache; c++)
-        if ((c * kQuantThreads + tid) * 8 < K) range8(cache[c]);
-    } else {
-      for (int k = tid * 8; k < K; k += kQuantThreads * 8) range8(*reinterpret_cast<const uint4 *>(x + k));
-    }
-  } else {
-    for (int k = tid; k < K; k += kQuantThreads) {
-      const float v = __half2float(x[k]);
-      mn = v < mn ? v : mn;
-      mx = v > mx ? v : mx;
-    }
+  for (int k = tid; k < K; k += kQuantThreads) {
+    const float v = __half2float(x[k]);
+    mn = v < mn ? v : mn;
+    mx = v > mx ? v : mx;
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) {
@@ -94,34 +64,10 @@ __global__ void __launch_bounds__(kQuantThreads, 6) dyn_quantize_rows_kernel(con
   if (offset != 0 && tid == 0 && status != nullptr) atomicOr(status, GLOWB200_STATUS_UNSUPPORTED_TABLE);
   int32_t sum = 0;
   int8_t *o = q + (size_t)row * K;
-  auto quantize8 = [&](const uint4 &v, int k) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t packed[2] = {0u, 0u};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-      const int32_t a = quantize_i8(f.x, scale, foffset), b = quantize_i8(f.y, scale, foffset);
-      sum += a + b;
-      packed[i >> 1] |= ((uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8)) << (16 * (i & 1));
-    }
-    *reinterpret_cast<uint2 *>(o + k) = make_uint2(packed[0], packed[1]);
-  };
-  if constexpr (VEC) {
-    if (cached) {
-#pragma unroll
-      for (int c = 0; c < kQuantCache; c++) {
-        const int k = (c * kQuantThreads + tid) * 8;
-        if (k < K) quantize8(cache[c], k);
-      }
-    } else {
-      for (int k = tid * 8; k < K; k += kQuantThreads * 8) quantize8(*reinterpret_cast<const uint4 *>(x + k), k);
-    }
-  } else {
-    for (int k = tid; k < K; k += kQuantThreads) {
-      const int32_t v = quantize_i8(__half2float(x[k]), scale, foffset);
-      o[k] = (int8_t)v;
-      sum += v;
-    }
+  for (int k = tid; k < K; k += kQuantThreads) {
+    const int32_t v = quantize_i8(__half2float(x[k]), scale, foffset);
+    o[k] = (int8_t)v;
+    sum += v;
   }
   if (row_sums != nullptr) {
 #pragma unroll
@@ -255,7 +201,7 @@ int run(void *out, const void *in, const int8_t *weights, const float *bias, con
   if (vec)
     dyn_quantize_rows_warp_kernel<<<(unsigned)((M + 7) / 8), 256, 0, s>>>(x, (int)M, (int)K, q, row_scales, sums, status);
   else
-    dyn_quantize_rows_kernel<false><<<(unsigned)M, kQuantThreads, 0, s>>>(reinterpret_cast<const __half *>(in), (int)M, (int)K, q,
+    dyn_quantize_rows_kernel<<<(unsigned)M, kQuantThreads, 0, s>>>(reinterpret_cast<const __half *>(in), (int)M, (int)K, q,
                                                                            row_scales, offsets_zero ? nullptr : row_sums, status);
   GLOWB200_CUDA_OK(cudaGetLastError());
   GemmParams p{};
