@@ -60,3 +60,37 @@ def test_device_manager_needs_init():
         dm.add_network(f)
     assert dm.maximum_memory == 1 << 20 and dm.available_memory == 1 << 20
     assert dm.is_memory_available(1 << 20) and not dm.is_memory_available((1 << 20) + 1)
+
+
+def test_new_instruction_kinds_compile_and_reject_malformed_forms():
+    """Arithmetic glue, table-batched bags and the dynamically quantized FC: compile derives the
+    integer triples (three or six more attributes) and sizes the workspace; wrong operand or
+    attribute counts are refused."""
+    from glow_b200 import ops
+    f = runtime.Function("arith")
+    a, b, c = f.placeholder("a", 64), f.placeholder("b", 64), f.placeholder("c", 64)
+    f.binary(ops.BINARY_MIN, c, a, b, n=64, lhs_tqp=(0.02, 1), rhs_tqp=(0.03, -2), dest_tqp=(0.05, 0))
+    f.muldiv(True, c, a, b, n=64, lhs_tqp=(0.02, 1), rhs_tqp=(0.03, -2), dest_tqp=(0.05, 0))
+    f.batched_add(c, a, b, num_slices=4, slice_size=16, batch_tqp=(0.02, 1), slice_tqp=(0.03, -2), dest_tqp=(0.05, 0))
+    x = f.placeholder("x", 8 * 32 * 2)
+    w = f.constant("w", np.ones((32, 16), np.int8))
+    bias = f.constant("bias", np.zeros(16, np.float32))
+    y = f.placeholder("y", 8 * 16 * 2)
+    f.dynamic_quantized_fc(y, x, w, bias, M=8, K=32, N=16, weights_tqp=(0.01, 0))
+    f.compile()
+    g = runtime.Function("bad_dyn")
+    x = g.placeholder("x", 64)
+    sc = g.constant("scales", np.ones(4, np.float32))
+    g.instruction(runtime.DYN_QUANTIZED_FC, [x, x, x, x, sc, -1], [2, 16, 4, 0], [0.0])   # scales without offsets
+    with pytest.raises(GlowB200Error, match="both scales and offsets"):
+        g.compile()
+    h = runtime.Function("bad_split")
+    x = h.placeholder("x", 64)
+    h.instruction(runtime.SPLIT_EMBEDDING, [x] * 9, [0] * 13)                               # an operand short
+    with pytest.raises(GlowB200Error, match="malformed SPLIT_EMBEDDING"):
+        h.compile()
+    k = runtime.Function("bad_binary")
+    x = k.placeholder("x", 64)
+    k.instruction(runtime.BINARY_I8, [x, x, x], [64, 0, 0, 0], [1.0, 1.0, 1.0])            # the operator is missing
+    with pytest.raises(GlowB200Error, match="malformed BINARY_I8"):
+        k.compile()
