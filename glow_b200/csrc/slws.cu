@@ -70,6 +70,9 @@ __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
 #ifndef GLOWB200_SLWS_P4_FROM
 #define GLOWB200_SLWS_P4_FROM 16
 #endif
+#ifndef GLOWB200_SLWS_FORCE_WARP
+#define GLOWB200_SLWS_FORCE_WARP 0
+#endif
 #ifndef GLOWB200_SLWS_MAX_BPW
 #define GLOWB200_SLWS_MAX_BPW 8
 #endif
@@ -737,7 +740,7 @@ template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHA
 __global__ void __launch_bounds__(kGatherThreads, P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS)
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
-  const bool skewed = p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
+  const bool skewed = GLOWB200_SLWS_FORCE_WARP || p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
   if (skewed) gather_warp_body<BITS, SO16, OUT16, IdxT, P, U, SHARD>(p, bags_per_warp);
   else gather_group_body<BITS, SO16, OUT16, false, IdxT, P, U, SHARD, WIDE16>(p);
 }
