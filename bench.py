@@ -1379,8 +1379,34 @@ def main():
         q1.record()
         torch.cuda.synchronize()
         us_graph = q0.elapsed_time(q1) * 1e3 / 200
+        # the low-latency entry point (a warp per bag) on the same request
+        def ll():
+            ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(
+                tables[0], weights_d[:starts[1]], indices_d[:starts[1]], lengths_d[0], ops.UINT8_FUSED, out=out[0],
+                status=status, workspace=one_ws, out_line=DIM, low_latency=True)
+        one_ws = torch.empty(ops.slws_workspace_bytes(BATCH, 1), dtype=torch.uint8, device=dev)
+        for i in range(10):
+            ll()
+        graph_ll = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph_ll):
+            for i in range(200):
+                ll()
+        graph_ll.replay()
+        torch.cuda.synchronize()
+        q0.record()
+        graph_ll.replay()
+        q1.record()
+        torch.cuda.synchronize()
+        us_ll_graph = q0.elapsed_time(q1) * 1e3 / 200
+        q0.record()
+        for i in range(200):
+            ll()
+        q1.record()
+        torch.cuda.synchronize()
+        us_ll = q0.elapsed_time(q1) * 1e3 / 200
         single_extra = {"metric": METRIC, "value": algorithmic_bytes(int(starts[1]), BATCH) / (us * 1e-6) / 1e9,
                         "unit": UNIT, "us_per_launch": us, "us_per_launch_in_graph": us_graph,
+                        "low_latency_entry_point": {"us_per_launch": us_ll, "us_per_launch_in_graph": us_ll_graph},
                         "note": "one 1,000,000 x 64 table per launch (segments + gather kernels back to back, "
                                 "200 launches from the host, then the same 200 as one CUDA graph): the table "
                                 "stays in L2, the figure is launch latency"}

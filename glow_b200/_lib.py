@@ -27,6 +27,8 @@ SIGNATURES = {
     "glowb200_slws_workspace_bytes": (_sz, [_i64, _i64]),
     "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum": (
         _int, [_vp, _vp, _int, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp, _vp]),
+    "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_low_latency": (
+        _int, [_vp, _vp, _int, _i64, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp, _vp]),
     "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched": (
         _int, [_vp, _i64, _i64, _int, _int, _i64, _i64, _int, _int, _vp, _sz, _vp, _vp]),
     "glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_row_sharded": (

@@ -48,6 +48,7 @@ struct SlwsLaunch {
   int32_t sharded;
   // 1: rows are a multiple of 16 bytes wide and every table starts on a 16-byte boundary
   int32_t wide16;
+  int32_t warp_per_bag;  // every table of the launch takes the warp-per-run mapping
 };
 
 __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
@@ -740,7 +741,8 @@ template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHA
 __global__ void __launch_bounds__(kGatherThreads, P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS)
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
-  const bool skewed = GLOWB200_SLWS_FORCE_WARP || p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
+  const bool skewed = GLOWB200_SLWS_FORCE_WARP || p.warp_per_bag != 0 ||
+                      p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
   if (skewed) gather_warp_body<BITS, SO16, OUT16, IdxT, P, U, SHARD>(p, bags_per_warp);
   else gather_group_body<BITS, SO16, OUT16, false, IdxT, P, U, SHARD, WIDE16>(p);
 }
@@ -1100,6 +1102,28 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
   GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
   L.select = (P != 0 && !g.acc16) ? 1 : 0;
   L.wide16 = ((in_line_size % 16) == 0 && aligned_to(data, 16)) ? 1 : 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  return run_gather(L, g, P, segments, 1, s);
+}
+
+extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_low_latency(
+    void *dest, const void *data, int kind, int64_t rows, const void *weights, const void *indices,
+    int indices_are_int64, const int32_t *lengths, int64_t segments, int64_t num_indices, int64_t in_line_size,
+    int64_t out_line_size, int out_is_fp16, void *workspace, size_t workspace_bytes, int32_t *status,
+    glowb200_stream_t stream) {
+  SlwsLaunch L;
+  GatherConfig g;
+  int P;
+  if (int rc = fill_single(L, g, P, dest, data, kind, rows, weights, indices, indices_are_int64, lengths, segments,
+                           num_indices, in_line_size, out_line_size, out_is_fp16, 0, workspace, workspace_bytes, status))
+    return rc;
+  if (segments == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
+  L.select = (P != 0) ? 1 : 0;
+  L.warp_per_bag = 1;
+  L.wide16 = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());

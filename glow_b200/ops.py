@@ -67,7 +67,8 @@ def _workspace(workspace, need, device):
 
 def fused_rowwise_quantized_sparse_lengths_weighted_sum(data, weights, indices, lengths, kind=UINT8_FUSED, *,
                                                         use_fp16_accumulation=False, out=None, status=None,
-                                                        workspace=None, num_indices=None, out_line=None):
+                                                        workspace=None, num_indices=None, out_line=None,
+                                                        low_latency=False):
     """FusedRowwiseQuantizedSparseLengthsWeightedSum.  data: uint8 [rows, in_line] fused table;
     weights: result dtype [n]; indices: int32/int64 [n]; lengths: int32 [segments].
     out_line: columns of the result when the rows are padded (see pad_fused_rows); default: the
@@ -85,6 +86,13 @@ def fused_rowwise_quantized_sparse_lengths_weighted_sum(data, weights, indices, 
     n = indices.shape[0] if num_indices is None else int(num_indices)
     need = slws_workspace_bytes(segments, 1)
     ws = _workspace(workspace, need, data.device)
+    if low_latency:   # a warp per bag: for small requests; another summation order (see the header)
+        if use_fp16_accumulation:
+            raise ValueError("the low-latency form accumulates in fp32")
+        check(_lib.lib().glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_low_latency(
+            _p(out), _p(data), kind, rows, _p(weights), _p(indices), int(indices.dtype == torch.int64), _p(lengths),
+            segments, n, in_line, out_line, int(odt == torch.float16), _p(ws), ws.numel(), _p(status), _stream()))
+        return out
     check(_lib.lib().glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
         _p(out), _p(data), kind, rows, _p(weights), _p(indices), int(indices.dtype == torch.int64), _p(lengths),
         segments, n, in_line, out_line, int(odt == torch.float16), int(use_fp16_accumulation), _p(ws), ws.numel(),

@@ -122,6 +122,19 @@ int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
     int64_t in_line_size, int64_t out_line_size, int out_is_fp16, int use_fp16_accumulation,
     void *workspace, size_t workspace_bytes, int32_t *status, glowb200_stream_t stream);
 
+/* The same operator for small requests where latency counts: every bag gets a whole warp (the
+ * thread mapping the entry point above gives tables with very uneven bags), so a bag's rows are
+ * fetched together instead of four at a time -- the launch of benchmark configuration 1 (1024
+ * bags of about 32 rows) takes a third of the time.  fp32 accumulation only.  The rows of a bag
+ * are summed in another order than above: results agree within the operator's tolerance (1e-5
+ * relative) but are not bit-identical to the other entry points', which is why the choice is the
+ * caller's and not made from the size of the launch. */
+int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_low_latency(
+    void *dest, const void *data, int kind, int64_t rows, const void *weights, const void *indices,
+    int indices_are_int64, const int32_t *lengths, int64_t segments, int64_t num_indices,
+    int64_t in_line_size, int64_t out_line_size, int out_is_fp16, void *workspace,
+    size_t workspace_bytes, int32_t *status, glowb200_stream_t stream);
+
 /* The same operator over `num_jobs` tables of one kind and one row width in ONE launch
  * (how Glow's SLS benchmark and the SparseNN partitioner present many tables to a device:
  * tests/benchmark/SLSBench.cpp:49-104, lib/Partitioner/Partitioner.cpp:1611-1685).

@@ -295,3 +295,24 @@ def test_properties_on_a_large_table():
     # against a torch fp32 restatement of the pooled sum
     ref = ((table[idx, :dim].float() * scale[idx, None] + offset[idx, None]) * w[:, None]).view(B, L, dim).sum(1)
     assert torch.allclose(base, ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("kind,dim", [(0, 64), (0, 128), (1, 32), (3, 128), (2, 64), (0, 1000)])
+def test_low_latency_form(oracle, kind, dim):
+    """The warp-per-bag entry point for small requests: the operator's tolerance against the
+    oracle, the same bits on every call, invalid input reported the same way."""
+    rows, B = 20000, 300
+    table = make_table(kind, rows, dim, 7 + dim)
+    lengths, idx, w = workloads.bags_poisson(B, 30, 0, 120, rows, 90, 3)
+    odt = np.float16 if kind & 1 else np.float32
+    w = w.astype(odt)
+    st = ops.new_status(DEV)
+    got = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(t(table), t(w), t(idx), t(lengths), kind, low_latency=True,
+                                                                  status=st)
+    again = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(t(table), t(w), t(idx), t(lengths), kind, low_latency=True)
+    assert torch.equal(got, again) and int(st.item()) == 0
+    want = oracle.frwq_slws_interp(table, kind, w, idx, lengths)
+    assert_close(got.cpu().numpy(), want, magnitudes(oracle, table, kind, w, idx, lengths), 2e-3 if kind & 1 else 1e-5)
+    bad = idx.copy(); bad[5] = rows + 3
+    ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(t(table), t(w), t(bad), t(lengths), kind, low_latency=True, status=st)
+    assert int(st.item()) == ops.STATUS_INDEX_OUT_OF_RANGE
