@@ -49,6 +49,7 @@ struct SlwsLaunch {
   // 1: rows are a multiple of 16 bytes wide and every table starts on a 16-byte boundary
   int32_t wide16;
   int32_t warp_per_bag;  // every table of the launch takes the warp-per-run mapping
+  int32_t inline_lengths;  // single table, few bags: no boundary array, see slws_gather_small_kernel
 };
 
 __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
@@ -527,7 +528,9 @@ __global__ void __launch_bounds__(kGatherThreads, P == 4 ? GLOWB200_SLWS_MIN_BLO
 // group-per-bag kernel above.
 // grid = (ceil(ceil(max_segments / bags_per_warp) / 8), num_jobs), 8 warps per block.
 // ------------------------------------------------------------------------------------------
-template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int kUnroll, bool SHARD = false>
+// INLINE_LEN: no bag-boundary array exists; the warp adds up the lengths before its run itself
+// (for requests of a few thousand bags, where that costs less than a launch of its own).
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int kUnroll, bool SHARD = false, bool INLINE_LEN = false>
 __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_per_warp) {
   using RL = RowLoad<BITS, SO16>;
   constexpr int V = 8 * P;  // sums a lane carries
@@ -543,8 +546,30 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
 
   const uint8_t *data = reinterpret_cast<const uint8_t *>(jp->data);
   const int64_t rows = jp->rows;
-  const int64_t *sb = p.seg_begin + (int64_t)job_id * p.seg_stride + first_bag;
-  const int64_t run0 = sb[0];
+  const int64_t *sb = INLINE_LEN ? nullptr : p.seg_begin + (int64_t)job_id * p.seg_stride + first_bag;
+  int32_t flags = 0;
+  int64_t prefix = 0;  // INLINE_LEN: sum of the (non-negative) lengths before the bag in hand, not clamped
+  if constexpr (INLINE_LEN) {
+    for (int64_t i = threadIdx.x & 31; i < first_bag; i += 32) {
+      const int32_t l = jp->lengths[i];
+      prefix += l > 0 ? l : 0;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) prefix += __shfl_xor_sync(0xffffffffu, prefix, d);
+  }
+  // end of bag `b` of the run, as seg_begin would hold it: min(sum of lengths, num_indices)
+  auto end_of_bag = [&](int b) -> int64_t {
+    if constexpr (INLINE_LEN) {
+      int32_t l = jp->lengths[first_bag + b];
+      if (l < 0) { l = 0; flags |= GLOWB200_STATUS_NEGATIVE_LENGTH; }
+      prefix += l;
+      if (prefix > jp->num_indices) flags |= GLOWB200_STATUS_LENGTHS_OVERRUN;
+      return prefix < jp->num_indices ? prefix : jp->num_indices;
+    } else {
+      return sb[b + 1];
+    }
+  };
+  const int64_t run0 = INLINE_LEN ? (prefix < jp->num_indices ? prefix : jp->num_indices) : sb[0];
   // positions below are relative to run0 (a warp's run is far shorter than 2^31 indices)
   const IdxT *indices = reinterpret_cast<const IdxT *>(jp->indices) + run0;
   const void *weights = OUT16 ? (const void *)(reinterpret_cast<const __half *>(jp->weights) + run0)
@@ -552,7 +577,6 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
   const int avail = (int)((jp->num_indices - run0) < (int64_t)INT32_MAX ? (jp->num_indices - run0) : (int64_t)INT32_MAX);
   const int in_line = p.in_line;
   const int chunks = p.out_line >> 3;
-  int32_t flags = 0;
 
   bool has[P];
 #pragma unroll
@@ -671,7 +695,7 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
   // together, then pooled.  When the bag ends its sums are flushed and the next bag continues
   // in the same block.
   int bag = 0;
-  int pos = 0, bag_end = (int)(sb[1] - run0);
+  int pos = 0, bag_end = (int)(end_of_bag(0) - run0);
   int blk = 0;  // the 32 indices in hand are positions blk .. blk + 31
   int32_t r_mine, r_next;
   float w_mine, w_next;
@@ -722,7 +746,7 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
       if (bag == n_bags - 1) break;
       reset();
       bag++;
-      bag_end = (int)(sb[bag + 1] - run0);  // bags of a lengths array are back to back: the next one starts at pos
+      bag_end = (int)(end_of_bag(bag) - run0);  // bags of a lengths array are back to back: the next one starts at pos
     }
     if (pos == blk + 32) {  // the block is used up: the prefetched one becomes current
       blk += 32;
@@ -732,6 +756,14 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
     }
   }
   raise(p.status, flags);
+}
+
+// The warp-per-run mapping alone, bag boundaries computed in place: the whole of a small request
+// in one launch.
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U>
+__global__ void __launch_bounds__(kGatherThreads, GLOWB200_SLWS_MIN_BLOCKS)
+slws_gather_small_kernel(const __grid_constant__ SlwsLaunch p) {
+  gather_warp_body<BITS, SO16, OUT16, IdxT, P, U, false, true>(p, 1);
 }
 
 // One launch, two thread-to-bag mappings: every table is pooled by the mapping its bag-length
@@ -846,6 +878,11 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
       // fp32 accumulation with lengths: the kernel that picks a mapping per table.  The
       // warp-per-run mapping takes runs of up to 8 bags once that still leaves every SM a few
       // waves of warps; single bags for small launches.
+      if (L.inline_lengths) {  // one warp per bag, boundaries computed by the warps: a single launch
+        const unsigned blocks = (unsigned)((L.single.segments + 7) / 8);
+        slws_gather_small_kernel<BITS, SO16, OUT16, IdxT, P, U><<<blocks, kGatherThreads, 0, s>>>(L);
+        return cudaGetLastError();
+      }
       const int64_t max_segments = (int64_t)grid.x * (kGatherThreads >> L.lpr_log2);
       const int64_t total = max_segments * grid.y, want = (int64_t)sm_count() * 24 * 4;
       int bpw = (int)(total / want);
@@ -1125,8 +1162,12 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_low_
   L.warp_per_bag = 1;
   L.wide16 = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  // up to 2048 bags every warp adds up the lengths before its bag itself (at most 64 loads a lane)
+  L.inline_lengths = (P != 0 && segments <= 2048) ? 1 : 0;
+  if (!L.inline_lengths) {
+    slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
+    GLOWB200_CUDA_OK(cudaGetLastError());
+  }
   return run_gather(L, g, P, segments, 1, s);
 }
 

@@ -125,7 +125,8 @@ int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
 /* The same operator for small requests where latency counts: every bag gets a whole warp (the
  * thread mapping the entry point above gives tables with very uneven bags), so a bag's rows are
  * fetched together instead of four at a time -- the launch of benchmark configuration 1 (1024
- * bags of about 32 rows) takes a third of the time.  fp32 accumulation only.  The rows of a bag
+ * bags of about 32 rows) takes a quarter of the time; up to 2048 bags the warps also add up the
+ * lengths before their bag themselves, so the request is a single launch.  fp32 accumulation only.  The rows of a bag
  * are summed in another order than above: results agree within the operator's tolerance (1e-5
  * relative) but are not bit-identical to the other entry points', which is why the choice is the
  * caller's and not made from the size of the launch. */

@@ -298,10 +298,12 @@ def test_properties_on_a_large_table():
 
 
 @pytest.mark.parametrize("kind,dim", [(0, 64), (0, 128), (1, 32), (3, 128), (2, 64), (0, 1000)])
-def test_low_latency_form(oracle, kind, dim):
-    """The warp-per-bag entry point for small requests: the operator's tolerance against the
-    oracle, the same bits on every call, invalid input reported the same way."""
-    rows, B = 20000, 300
+@pytest.mark.parametrize("B", [300, 2048, 2500])
+def test_low_latency_form(oracle, kind, dim, B):
+    """The warp-per-bag entry point for small requests (up to 2048 bags in a single launch, the
+    warps adding up the lengths themselves; more through the boundary array): the operator's
+    tolerance against the oracle, the same bits on every call, invalid input reported the same way."""
+    rows = 20000
     table = make_table(kind, rows, dim, 7 + dim)
     lengths, idx, w = workloads.bags_poisson(B, 30, 0, 120, rows, 90, 3)
     odt = np.float16 if kind & 1 else np.float32
@@ -316,3 +318,11 @@ def test_low_latency_form(oracle, kind, dim):
     bad = idx.copy(); bad[5] = rows + 3
     ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(t(table), t(w), t(bad), t(lengths), kind, low_latency=True, status=st)
     assert int(st.item()) == ops.STATUS_INDEX_OUT_OF_RANGE
+    st.zero_()
+    # a negative length counts as 0, lengths that overrun the indices are cut: both reported
+    l2 = lengths.copy(); l2[3] = -4; l2[-1] += 50
+    got2 = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(t(table), t(w), t(idx), t(l2), kind, low_latency=True, status=st)
+    assert int(st.item()) == (ops.STATUS_NEGATIVE_LENGTH | ops.STATUS_LENGTHS_OVERRUN)
+    ref2 = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(t(table), t(w), t(idx), t(l2), kind)
+    assert not got2[3].any()
+    assert_close(got2.cpu().numpy(), ref2.cpu().numpy(), magnitudes(oracle, table, kind, w, idx, lengths), 2e-3 if kind & 1 else 1e-5)
