@@ -814,7 +814,11 @@ def run_slws4_line(args):
                                    "indices, fp16 weights and result" % (T, D, line_bytes, T * ROWS4 * line_bytes / 1e9),
                        "dim": D, "tables_per_gpu": T, "l2_policy": "tables far larger than L2, uniform indices"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                         "peak_source": src, "traffic": None, "kernel": "slws_gather_select_kernel<4,1,1,long,P>",
+                         "peak_source": src,
+                         # DRAM bytes per launch: 196 B per row in the ncu capture of a smaller case of D=128
+                         # (profiles/), scaled by the rows of a launch; not captured for the other widths
+                         "traffic": 196.0 * float(np.mean([int(rq[3][-1]) for rq in reqs])) if D == 128 else None,
+                         "kernel": "slws_gather_select_kernel<4,1,1,long,P>",
                          "rows_per_s": sum(int(reqs[i % R][3][-1]) for i in range(args.steps)) / (ms * 1e-3)},
             "gpu_launches": 2 * args.steps, "clocks": clocks}
         if world == 1 and not args.no_cpu_baseline:
@@ -1011,7 +1015,11 @@ def run_tbe_line(args):
                                    % (T, args.tbe_type, D, row_bytes, payload, T * ROWS * row_bytes / 1e9, args.tbe_out),
                        "dim": D, "tables_per_gpu": T, "l2_policy": "tables far larger than L2, uniform indices"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                         "peak_source": src, "traffic": None, "kernel": "split_embedding_bags_kernel<%s,long>" % ("true" if out16 else "false"),
+                         "peak_source": src,
+                         # DRAM bytes per launch from the ncu captures of smaller cases (profiles/), per row x rows
+                         "traffic": ({("int4", 128): 198.0, ("fp16", 128): 264.0}.get((args.tbe_type, D), 0.0) *
+                                     float(np.mean([int(rq[0].shape[0]) for rq in reqs]))) or None,
+                         "kernel": "split_embedding_bags_kernel<%s,long>" % ("true" if out16 else "false"),
                          "rows_per_s": sum(int(reqs[i % R][0].shape[0]) for i in range(args.steps)) / (ms * 1e-3)},
             "gpu_launches": args.steps, "clocks": clocks}))
     if world > 1:
