@@ -121,6 +121,14 @@ __global__ void __launch_bounds__(256) dyn_quantize_rows_warp_kernel(const __hal
     mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, d));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
   }
+  // Handle::minMaxArg starts from element 0 and keeps what no later element beats: a NaN there
+  // stays (every comparison with it is false), a NaN anywhere else never gets in.  The min / max
+  // instructions above drop NaNs wherever they are, so the first element is looked at again --
+  // the row then quantizes as it does in the kernel that compares with '<' and '>'.
+  {
+    const float x0 = __half2float(x[0]);
+    if (x0 != x0) mn = mx = x0;
+  }
   double scale_d;
   int32_t offset;
   choose_quantization_params_basic(mn, mx, /*Symmetric*/ 1, -128, 127, scale_d, offset);

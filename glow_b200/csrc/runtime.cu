@@ -148,6 +148,151 @@ extern "C" int glowb200_function_add_instruction(glowb200_function *f, int kind,
   return GLOWB200_OK;
 }
 
+namespace {
+
+// What an instruction addresses, checked against the sizes of the symbols it names: a
+// malformed or mistranslated instruction must fail here, not overwrite a neighbour in the slab.
+// Layouts as in the table above glowb200_function_compile.
+int validate_instruction(const glowb200_function *f, const Instruction &in, size_t ii) {
+  const auto &a = in.ia;
+  struct Need { int op; int64_t bytes; bool optional; };
+  std::vector<Need> needs;
+  auto need = [&](int op, int64_t bytes, bool optional = false) { needs.push_back({op, bytes, optional}); };
+  auto bad = [&](const char *what) { return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: %s", ii, what); };
+  auto nonneg = [&](std::initializer_list<int> idx) {
+    for (int i : idx)
+      if (a[i] < 0) return false;
+    return true;
+  };
+  switch (in.kind) {
+    case GLOWB200_INSTR_FRWQ_SLWS: {
+      if (!nonneg({1, 2, 3, 4, 5})) return bad("negative size");
+      const int64_t es = a[7] ? 2 : 4;
+      need(0, a[4] * a[3] * es); need(1, a[1] * a[2]); need(2, a[5] * es); need(3, a[5] * (a[6] ? 8 : 4)); need(4, a[4] * 4);
+      break;
+    }
+    case GLOWB200_INSTR_RWQ_FC:
+      if (!nonneg({0, 1, 2})) return bad("negative size");
+      need(0, a[0] * a[2]); need(1, a[0] * a[1]); need(2, a[2] * a[1]); need(3, a[2] * 4); need(4, a[2] * 4); need(5, a[2] * 4);
+      break;
+    case GLOWB200_INSTR_CWQ_CONV: {
+      if (!nonneg({0, 1, 2, 3, 4, 5, 6, 7, 8})) return bad("negative size");
+      if (a[15] <= 0 || a[3] % a[15] || a[6] % a[15]) return bad("group must be positive and divide the channel counts");
+      const int64_t OC = a[6];
+      need(0, a[0] * a[4] * a[5] * OC); need(1, a[0] * a[1] * a[2] * a[3]); need(2, OC * a[7] * a[8] * (a[3] / a[15]));
+      need(3, OC * 4); need(4, OC * 4); need(5, OC * 4); need(6, OC * 4); need(7, OC * 4);
+      break;
+    }
+    case GLOWB200_INSTR_ADD: case GLOWB200_INSTR_ADD_MAXSPLAT: case GLOWB200_INSTR_BINARY_I8: case GLOWB200_INSTR_MULDIV_I8:
+      if (a[0] < 0) return bad("negative size");
+      need(0, a[0]); need(1, a[0]); need(2, a[0]);
+      break;
+    case GLOWB200_INSTR_MAXSPLAT: case GLOWB200_INSTR_RELU: case GLOWB200_INSTR_RESCALE:
+      if (a[0] < 0) return bad("negative size");
+      need(0, a[0]); need(1, a[0]);
+      break;
+    case GLOWB200_INSTR_QUANTIZE:
+      if (a[0] < 0) return bad("negative size");
+      need(0, a[0]); need(1, a[0] * 4);
+      break;
+    case GLOWB200_INSTR_DEQUANTIZE:
+      if (a[0] < 0) return bad("negative size");
+      need(0, a[0] * 4); need(1, a[0]);
+      break;
+    case GLOWB200_INSTR_MAXPOOL: case GLOWB200_INSTR_AVGPOOL:
+      if (!nonneg({0, 1, 2, 3, 4, 5})) return bad("negative size");
+      need(0, a[0] * a[4] * a[5] * a[3]); need(1, a[0] * a[1] * a[2] * a[3]);
+      break;
+    case GLOWB200_INSTR_TRANSPOSE: {
+      if (a[0] < 1 || a[0] > 4 || a[1] < 1) return bad("transpose of 1 to 4 dimensions");
+      int64_t n = a[1];
+      for (int i = 0; i < a[0]; i++) {
+        if (a[2 + i] < 0 || a[6 + i] < 0 || a[6 + i] >= a[0]) return bad("bad transpose shape or shuffle");
+        n *= a[2 + i];
+      }
+      need(0, n); need(1, n);
+      break;
+    }
+    case GLOWB200_INSTR_COPY:
+      if (a[0] < 0) return bad("negative size");
+      need(0, a[0]); need(1, a[0]);
+      break;
+    case GLOWB200_INSTR_FC_I8:
+      if (!nonneg({0, 1, 2})) return bad("negative size");
+      need(0, a[0] * a[2]); need(1, a[0] * a[1]); need(2, a[1] * a[2]); need(3, a[2] * 4);
+      break;
+    case GLOWB200_INSTR_MATMUL_I8:
+      if (!nonneg({0, 1, 2})) return bad("negative size");
+      need(0, a[0] * a[2]); need(1, a[0] * a[1]); need(2, a[1] * a[2]);
+      break;
+    case GLOWB200_INSTR_SPLAT:
+      if (a[0] < 0) return bad("negative size");
+      need(0, a[0] * (a[1] ? 2 : 4));
+      break;
+    case GLOWB200_INSTR_INSERT_TENSOR:
+      if (!nonneg({0, 1, 2, 3}) || a[2] < a[1]) return bad("bad insert-tensor pitch or offset");
+      need(0, a[0] > 0 ? a[3] + (a[0] - 1) * a[2] + a[1] : 0); need(1, a[0] * a[1]);
+      break;
+    case GLOWB200_INSTR_PAIRWISE_DOT: {
+      if (!nonneg({0, 1, 2, 3, 4, 5})) return bad("negative size");
+      const int64_t B = a[0], T = a[1], D = a[2], width = D + (T + 1) * T / 2;
+      if (a[3] < D || a[4] < T * D || a[5] < width) return bad("leading dimension smaller than a row");
+      need(0, B > 0 ? ((B - 1) * a[5] + width) * (a[6] ? 1 : 4) : 0); need(1, B > 0 ? ((B - 1) * a[3] + D) * 4 : 0);
+      need(2, B > 0 ? ((B - 1) * a[4] + T * D) * 4 : 0);
+      break;
+    }
+    case GLOWB200_INSTR_SLWS_F32:
+      if (!nonneg({0, 1, 2, 3})) return bad("negative size");
+      need(0, a[2] * a[1] * 4); need(1, a[0] * a[1] * 4); need(2, a[3] * 4, true); need(3, a[3] * (a[4] ? 8 : 4)); need(4, a[2] * 4);
+      break;
+    case GLOWB200_INSTR_RWQ_SLWS:
+      if (!nonneg({0, 1, 2, 3})) return bad("negative size");
+      need(0, a[2] * a[1] * 4); need(1, a[0] * a[1]); need(2, a[0] * 4); need(3, a[0] * 4); need(4, a[3] * 4);
+      need(5, a[3] * (a[4] ? 8 : 4)); need(6, a[2] * 4);
+      break;
+    case GLOWB200_INSTR_EMBEDDING_BAG: {
+      if (!nonneg({1, 2, 3, 4, 5})) return bad("negative size");
+      const int64_t es = a[8] ? 2 : 4, bags = a[7] ? (a[4] > 0 ? a[4] - 1 : 0) : a[4], ib = a[6] ? 8 : 4;
+      need(0, bags * a[3] * es); need(1, a[1] * a[2]); need(2, a[5] * es); need(3, a[5] * ib); need(4, a[4] * ib);
+      break;
+    }
+    case GLOWB200_INSTR_SPLIT_EMBEDDING: {
+      if (!nonneg({0, 1, 2, 3, 4, 5})) return bad("negative size");
+      const int64_t ib = a[6] ? 8 : 4, T = a[2];
+      need(0, a[5] * a[3] * (a[10] ? 2 : 4)); need(1, a[0], a[0] == 0); need(2, a[1], a[1] == 0); need(3, T * 4);
+      need(4, T * (a[7] ? 8 : 4)); need(5, T); need(6, (T + 1) * 4); need(7, a[4] * ib); need(8, (T * a[5] + 1) * ib);
+      need(9, a[4] * (a[9] ? 2 : 4), true);
+      break;
+    }
+    case GLOWB200_INSTR_DYN_QUANTIZED_FC:
+      if (!nonneg({0, 1, 2})) return bad("negative size");
+      need(0, a[0] * a[2] * 2); need(1, a[0] * a[1] * 2); need(2, a[1] * a[2]); need(3, a[2] * 4); need(4, a[2] * 4, true);
+      need(5, a[2] * 4, true);
+      break;
+    case GLOWB200_INSTR_BATCHED_ADD_I8:
+      if (!nonneg({0, 1})) return bad("negative size");
+      need(0, a[0] * a[1]); need(1, a[0] * a[1]); need(2, a[1] * (a[5] ? 4 : 1));
+      break;
+    default: break;
+  }
+  if (needs.size() != in.ops.size()) return bad("operand table out of step with the instruction");
+  for (const Need &n : needs) {
+    const int id = in.ops[n.op];
+    if (id < 0) {
+      if (!n.optional) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: operand %d is required", ii, n.op);
+      continue;
+    }
+    const Symbol &s = f->symbols[id];
+    if ((int64_t)s.bytes < n.bytes)
+      return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: operand %d ('%s', %zu bytes) is smaller than the %lld bytes the instruction addresses",
+                       ii, n.op, s.name.c_str(), s.bytes, (long long)n.bytes);
+    if (n.op == 0 && s.kind == kConstant) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: the destination '%s' is a constant", ii, s.name.c_str());
+  }
+  return GLOWB200_OK;
+}
+
+}  // namespace
+
 // Instruction operand / attribute layouts (ia = integer attributes, fa = float attributes):
 //  FRWQ_SLWS   ops {dest, data, weights, indices, lengths}  ia {kind, rows, in_line, out_line, segments, num_indices, idx64, out_fp16, fp16_acc}
 //  RWQ_FC      ops {dest, src, weights, scales(f32 const), offsets, bias}  ia {M, K, N, in_off, bias_off, out_off, relu}  fa {in_scale, bias_scale, out_scale}
@@ -185,19 +330,30 @@ extern "C" int glowb200_function_add_instruction(glowb200_function *f, int kind,
 extern "C" int glowb200_function_compile(glowb200_function *f) {
   if (!f || f->compiled) return set_error(GLOWB200_RUNTIME_ERROR, "function is NULL or already compiled");
   size_t ws = 256;
+  bool sizes_bad = false;  // validate_instruction has set the message
   for (size_t ii = 0; ii < f->instrs.size(); ii++) {
     Instruction &in = f->instrs[ii];
     const std::string tag = "i" + std::to_string(ii);
+    bool counts_ok = false;
     auto need = [&](size_t nops, size_t nia, size_t nfa) {
-      return in.ops.size() == nops && in.ia.size() == nia && in.fa.size() == nfa;
+      counts_ok = in.ops.size() == nops && in.ia.size() == nia && in.fa.size() == nfa;
+      if (counts_ok && validate_instruction(f, in, ii) != GLOWB200_OK) {
+        counts_ok = false;
+        sizes_bad = true;
+      }
+      return counts_ok;
+    };
+    auto malformed = [&](const char *what) {
+      if (sizes_bad) return (int)GLOWB200_RUNTIME_ERROR;  // validate_instruction's message stands
+      return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed %s", ii, what);
     };
     switch (in.kind) {
       case GLOWB200_INSTR_FRWQ_SLWS:
-        if (!need(5, 9, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed FRWQ_SLWS", ii);
+        if (!need(5, 9, 0)) return malformed("FRWQ_SLWS");
         ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[4], 1));
         break;
       case GLOWB200_INSTR_RWQ_FC: {
-        if (!need(6, 7, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed RWQ_FC", ii);
+        if (!need(6, 7, 3)) return malformed("RWQ_FC");
         const int64_t N = in.ia[2];
         if (f->symbols[in.ops[3]].host.size() != (size_t)N * 4) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: scales must be a float constant of N entries", ii);
         in.derived = add_row_triples(f, tag, host_f32(f, in.ops[3]), N, in.fa[0], &in.fa[1], 1, in.fa[2]);
@@ -215,7 +371,7 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
         break;
       }
       case GLOWB200_INSTR_CWQ_CONV: {
-        if (!need(8, 21, 2)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed CWQ_CONV", ii);
+        if (!need(8, 21, 2)) return malformed("CWQ_CONV");
         const int64_t OC = in.ia[6];
         if (f->symbols[in.ops[4]].host.size() != (size_t)OC * 4 || f->symbols[in.ops[6]].host.size() != (size_t)OC * 4)
           return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: filter/bias scales must be float constants of outC entries", ii);
@@ -227,7 +383,7 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
         break;
       }
       case GLOWB200_INSTR_ADD: {
-        if (!need(3, 4, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed ADD", ii);
+        if (!need(3, 4, 3)) return malformed("ADD");
         std::vector<int32_t> t(6);
         glowb200::quantize_scale_32to8(in.fa[0] / in.fa[2], t[0], t[1], t[2]);  // LLVMIRGen.cpp:1740-1743
         glowb200::quantize_scale_32to8(in.fa[1] / in.fa[2], t[3], t[4], t[5]);
@@ -235,7 +391,7 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
         break;
       }
       case GLOWB200_INSTR_AVGPOOL: {
-        if (!need(2, 15, 2)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed AVGPOOL", ii);
+        if (!need(2, 15, 2)) return malformed("AVGPOOL");
         // LLVMIRGen.cpp:3003-3046: the kernel area is folded into the scale when pads are counted
         float sc = in.fa[0] / in.fa[1];
         if (in.ia[14]) sc = sc / (float)(in.ia[6] * in.ia[7]);
@@ -244,14 +400,14 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
         in.ia.push_back(a); in.ia.push_back(b); in.ia.push_back(c);
         break;
       }
-      case GLOWB200_INSTR_MAXSPLAT: if (!need(2, 2, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed MAXSPLAT", ii); break;
+      case GLOWB200_INSTR_MAXSPLAT: if (!need(2, 2, 0)) return malformed("MAXSPLAT"); break;
       case GLOWB200_INSTR_QUANTIZE:
-      case GLOWB200_INSTR_DEQUANTIZE: if (!need(2, 2, 1)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed (de)quantize", ii); break;
-      case GLOWB200_INSTR_MAXPOOL: if (!need(2, 13, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed MAXPOOL", ii); break;
-      case GLOWB200_INSTR_TRANSPOSE: if (!need(2, 10, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed TRANSPOSE", ii); break;
-      case GLOWB200_INSTR_COPY: if (!need(2, 1, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed COPY", ii); break;
+      case GLOWB200_INSTR_DEQUANTIZE: if (!need(2, 2, 1)) return malformed("(de)quantize"); break;
+      case GLOWB200_INSTR_MAXPOOL: if (!need(2, 13, 0)) return malformed("MAXPOOL"); break;
+      case GLOWB200_INSTR_TRANSPOSE: if (!need(2, 10, 0)) return malformed("TRANSPOSE"); break;
+      case GLOWB200_INSTR_COPY: if (!need(2, 1, 0)) return malformed("COPY"); break;
       case GLOWB200_INSTR_ADD_MAXSPLAT: {
-        if (!need(3, 5, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed ADD_MAXSPLAT", ii);
+        if (!need(3, 5, 3)) return malformed("ADD_MAXSPLAT");
         int32_t t[6];
         glowb200::quantize_scale_32to8(in.fa[0] / in.fa[2], t[0], t[1], t[2]);
         glowb200::quantize_scale_32to8(in.fa[1] / in.fa[2], t[3], t[4], t[5]);
@@ -261,7 +417,7 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
       case GLOWB200_INSTR_RELU:
       case GLOWB200_INSTR_RESCALE: {
         // LLVMIRGen.cpp:1465-1499, 1630-1698: one triple from srcScale / destScale
-        if (!need(2, 3, 2)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed RELU / RESCALE", ii);
+        if (!need(2, 3, 2)) return malformed("RELU / RESCALE");
         int32_t a, b, c;
         glowb200::quantize_scale_32to8(in.fa[0] / in.fa[1], a, b, c);
         in.ia.push_back(a); in.ia.push_back(b); in.ia.push_back(c);
@@ -269,7 +425,7 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
       }
       case GLOWB200_INSTR_FC_I8: {
         // LLVMIRGen.cpp:2098-2137: bias from biasScale / (inScale * wScale), result from inScale * wScale / outScale
-        if (!need(4, 7, 4)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed FC_I8", ii);
+        if (!need(4, 7, 4)) return malformed("FC_I8");
         const float mm = in.fa[0] * in.fa[1];
         int32_t t[6];
         glowb200::quantize_scale_32to8(in.fa[2] / mm, t[0], t[1], t[2]);
@@ -280,31 +436,31 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
       }
       case GLOWB200_INSTR_MATMUL_I8: {
         // LLVMIRGen.cpp:2161-2220: one triple from lhsScale * rhsScale / destScale
-        if (!need(3, 6, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed MATMUL_I8", ii);
+        if (!need(3, 6, 3)) return malformed("MATMUL_I8");
         int32_t a, b, c;
         glowb200::quantize_scale_32to8(in.fa[0] * in.fa[1] / in.fa[2], a, b, c);
         in.ia.push_back(a); in.ia.push_back(b); in.ia.push_back(c);
         ws = std::max(ws, glowb200_i8_gemm_workspace_bytes(in.ia[0], in.ia[1], in.ia[2]));
         break;
       }
-      case GLOWB200_INSTR_SPLAT: if (!need(1, 2, 1)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed SPLAT", ii); break;
-      case GLOWB200_INSTR_INSERT_TENSOR: if (!need(2, 4, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed INSERT_TENSOR", ii); break;
-      case GLOWB200_INSTR_PAIRWISE_DOT: if (!need(3, 8, 1)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed PAIRWISE_DOT", ii); break;
+      case GLOWB200_INSTR_SPLAT: if (!need(1, 2, 1)) return malformed("SPLAT"); break;
+      case GLOWB200_INSTR_INSERT_TENSOR: if (!need(2, 4, 0)) return malformed("INSERT_TENSOR"); break;
+      case GLOWB200_INSTR_PAIRWISE_DOT: if (!need(3, 8, 1)) return malformed("PAIRWISE_DOT"); break;
       case GLOWB200_INSTR_SLWS_F32:
-        if (!need(5, 5, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed SLWS_F32", ii);
+        if (!need(5, 5, 0)) return malformed("SLWS_F32");
         ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[2], 1));
         break;
       case GLOWB200_INSTR_RWQ_SLWS:
-        if (!need(7, 5, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed RWQ_SLWS", ii);
+        if (!need(7, 5, 0)) return malformed("RWQ_SLWS");
         ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[2], 1));
         break;
       case GLOWB200_INSTR_EMBEDDING_BAG:
-        if (!need(5, 10, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed EMBEDDING_BAG", ii);
+        if (!need(5, 10, 0)) return malformed("EMBEDDING_BAG");
         ws = std::max(ws, glowb200_slws_workspace_bytes(in.ia[4], 1));
         break;
       case GLOWB200_INSTR_BINARY_I8: {
         // LLVMIRGen.cpp:1716-1776: each side rescaled by sideScale / destScale
-        if (!need(3, 5, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed BINARY_I8", ii);
+        if (!need(3, 5, 3)) return malformed("BINARY_I8");
         int32_t t[6];
         glowb200::quantize_scale_32to8(in.fa[0] / in.fa[2], t[0], t[1], t[2]);
         glowb200::quantize_scale_32to8(in.fa[1] / in.fa[2], t[3], t[4], t[5]);
@@ -313,7 +469,7 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
       }
       case GLOWB200_INSTR_MULDIV_I8: {
         // LLVMIRGen.cpp:1927-2035: lhsScale * rhsScale / destScale, or lhsScale / (rhsScale * destScale)
-        if (!need(3, 5, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed MULDIV_I8", ii);
+        if (!need(3, 5, 3)) return malformed("MULDIV_I8");
         int32_t a, b, c;
         glowb200::quantize_scale_32to8(in.ia[4] ? in.fa[0] / (in.fa[1] * in.fa[2]) : in.fa[0] * in.fa[1] / in.fa[2], a, b, c);
         in.ia.push_back(a); in.ia.push_back(b); in.ia.push_back(c);
@@ -321,7 +477,7 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
       }
       case GLOWB200_INSTR_BATCHED_ADD_I8: {
         // LLVMIRGen.cpp:2322-2375: batchScale / destScale and sliceScale / destScale
-        if (!need(3, 6, 3)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed BATCHED_ADD_I8", ii);
+        if (!need(3, 6, 3)) return malformed("BATCHED_ADD_I8");
         int32_t t[6];
         glowb200::quantize_scale_32to8(in.fa[0] / in.fa[2], t[0], t[1], t[2]);
         glowb200::quantize_scale_32to8(in.fa[1] / in.fa[2], t[3], t[4], t[5]);
@@ -329,10 +485,10 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
         break;
       }
       case GLOWB200_INSTR_SPLIT_EMBEDDING:
-        if (!need(10, 13, 0)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed SPLIT_EMBEDDING", ii);
+        if (!need(10, 13, 0)) return malformed("SPLIT_EMBEDDING");
         break;
       case GLOWB200_INSTR_DYN_QUANTIZED_FC:
-        if (!need(6, 4, 1)) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: malformed DYN_QUANTIZED_FC", ii);
+        if (!need(6, 4, 1)) return malformed("DYN_QUANTIZED_FC");
         if ((in.ops[4] < 0) != (in.ops[5] < 0))
           return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: DYN_QUANTIZED_FC needs both scales and offsets, or neither", ii);
         ws = std::max(ws, glowb200_dynamic_fc_workspace_bytes(in.ia[0], in.ia[1], in.ia[2]));
@@ -676,13 +832,24 @@ int finish_request(glowb200_device_manager *dm, const char *name) {
 }
 }  // namespace
 
-// Device-resident tensors and static placeholders (DeviceManager::transferToDevice /
-// transferFromDevice / transferStaticPlaceholderToDevice, include/glow/Backends/DeviceManager.h:
-// 163-231): where a placeholder of a loaded network lives on the device.
-extern "C" int glowb200_device_manager_placeholder_address(glowb200_device_manager *dm, const char *name, const char *placeholder,
-                                                           void **device_ptr, size_t *bytes) {
-  if (!dm || !name || !placeholder || !device_ptr) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
-  std::lock_guard<std::mutex> g(dm->lock);
+namespace {
+// A request that failed on the host part-way through: kernels and copies already queued are
+// waited for (the caller may reuse its buffers as soon as the error returns) and whatever they
+// raised in the status word is dropped with the request, so the next one starts clean.  The
+// message of the failure that led here is kept.
+int abort_request(glowb200_device_manager *dm, int rc) {
+  char msg[512];
+  snprintf(msg, sizeof(msg), "%s", glowb200_last_error());
+  cudaMemsetAsync(dm->status_dev, 0, 4, dm->stream);
+  if (cudaStreamSynchronize(dm->stream) != cudaSuccess) {
+    cudaGetLastError();
+    return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "device error after a failed request (%s)", msg);
+  }
+  return set_error(rc, "%s", msg);
+}
+
+// Where a placeholder of a loaded network lives; dm->lock is held by the caller.
+int find_placeholder(glowb200_device_manager *dm, const char *name, const char *placeholder, void **device_ptr, size_t *bytes) {
   auto it = dm->networks.find(name);
   if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Function %s not found", name);
   glowb200_function *f = it->second.fn;
@@ -693,14 +860,28 @@ extern "C" int glowb200_device_manager_placeholder_address(glowb200_device_manag
   if (bytes) *bytes = f->symbols[s->second].bytes;
   return GLOWB200_OK;
 }
+}  // namespace
+
+// Device-resident tensors and static placeholders (DeviceManager::transferToDevice /
+// transferFromDevice / transferStaticPlaceholderToDevice, include/glow/Backends/DeviceManager.h:
+// 163-231): where a placeholder of a loaded network lives on the device.
+extern "C" int glowb200_device_manager_placeholder_address(glowb200_device_manager *dm, const char *name, const char *placeholder,
+                                                           void **device_ptr, size_t *bytes) {
+  if (!dm || !name || !placeholder || !device_ptr) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
+  std::lock_guard<std::mutex> g(dm->lock);
+  return find_placeholder(dm, name, placeholder, device_ptr, bytes);
+}
 
 extern "C" int glowb200_device_manager_transfer_static_placeholder(glowb200_device_manager *dm, const char *name,
                                                                    const char *placeholder, const void *host, size_t bytes) {
+  if (!dm || !name || !placeholder) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
   void *d = nullptr;
   size_t cap = 0;
-  if (int rc = glowb200_device_manager_placeholder_address(dm, name, placeholder, &d, &cap)) return rc;
-  if (!host || bytes > cap) return set_error(GLOWB200_RUNTIME_ERROR, "static placeholder %s: NULL buffer or more bytes than the placeholder holds", placeholder);
+  // one critical section from the lookup to the end of the copy: an eviction in between would
+  // free the slab the copy writes
   std::lock_guard<std::mutex> g(dm->lock);
+  if (int rc = find_placeholder(dm, name, placeholder, &d, &cap)) return rc;
+  if (!host || bytes > cap) return set_error(GLOWB200_RUNTIME_ERROR, "static placeholder %s: NULL buffer or more bytes than the placeholder holds", placeholder);
   cudaSetDevice(dm->device);
   if (cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, dm->stream) != cudaSuccess || cudaStreamSynchronize(dm->stream) != cudaSuccess)
     return set_error(GLOWB200_RUNTIME_ERROR, "host-to-device copy of %s failed", placeholder);
@@ -714,7 +895,7 @@ extern "C" int glowb200_device_manager_run_function_resident(glowb200_device_man
   auto it = dm->networks.find(name);
   if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Function %s not found", name);
   cudaSetDevice(dm->device);
-  if (int rc = execute(dm, it->second)) return rc;
+  if (int rc = execute(dm, it->second)) return abort_request(dm, rc);
   return finish_request(dm, name);
 }
 
@@ -741,14 +922,14 @@ extern "C" int glowb200_device_manager_run_function_io(glowb200_device_manager *
     if (directions && !(directions[b] & GLOWB200_BINDING_INPUT)) continue;  // an output: nothing to copy in
     bool ok = cudaMemcpyAsync(d, host_buffers[b], buffer_bytes[b], cudaMemcpyHostToDevice, dm->stream) == cudaSuccess;
     if (ok && buffer_bytes[b] < sym.bytes) ok = cudaMemsetAsync(d + buffer_bytes[b], 0, sym.bytes - buffer_bytes[b], dm->stream) == cudaSuccess;
-    if (!ok) return set_error(GLOWB200_RUNTIME_ERROR, "host-to-device copy of %s failed", sym.name.c_str());
+    if (!ok) return abort_request(dm, set_error(GLOWB200_RUNTIME_ERROR, "host-to-device copy of %s failed", sym.name.c_str()));
   }
-  if (int rc = execute(dm, n)) return rc;
+  if (int rc = execute(dm, n)) return abort_request(dm, rc);
   for (int b = 0; b < num_bindings; b++) {
     const Symbol &sym = f->symbols[ids[b]];
     if (directions && !(directions[b] & GLOWB200_BINDING_OUTPUT)) continue;  // an input: nothing to copy back
     if (cudaMemcpyAsync(host_buffers[b], n.slab[kPlaceholder] + sym.offset, buffer_bytes[b], cudaMemcpyDeviceToHost, dm->stream) != cudaSuccess)
-      return set_error(GLOWB200_RUNTIME_ERROR, "device-to-host copy of %s failed", sym.name.c_str());
+      return abort_request(dm, set_error(GLOWB200_RUNTIME_ERROR, "device-to-host copy of %s failed", sym.name.c_str()));
   }
   return finish_request(dm, name);
 }

@@ -37,6 +37,7 @@ struct SlwsLaunch {
   glowb200_slws_job single;
   int64_t *seg_begin;  // workspace: per job an int64 [segments + 1] array
   int64_t seg_stride;  // int64 elements between the arrays of consecutive jobs
+  int64_t max_segments;  // bags a table's array has room for (a descriptor naming more is cut short)
   int32_t *status;
   int32_t in_line, out_line;
   int32_t lpr_log2;
@@ -46,11 +47,14 @@ struct SlwsLaunch {
   int32_t select;
   // 1: the tables are row-range shards (row_begin / global_rows of the descriptors are honoured)
   int32_t sharded;
-  // 1: rows are a multiple of 16 bytes wide and every table starts on a 16-byte boundary
-  int32_t wide16;
   int32_t warp_per_bag;  // every table of the launch takes the warp-per-run mapping
   int32_t inline_lengths;  // single table, few bags: no boundary array, see slws_gather_small_kernel
 };
+
+// Bags of a table as the kernels walk them: never more than its boundary array has room for.
+__device__ __forceinline__ int64_t bags_of(const SlwsLaunch &p, const glowb200_slws_job *jp) {
+  return jp->segments < p.max_segments ? jp->segments : p.max_segments;
+}
 
 __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
   if (status != nullptr && bits != 0) atomicOr(status, bits);
@@ -60,6 +64,15 @@ __device__ __forceinline__ void raise(int32_t *status, int32_t bits) {
 // 3 resident blocks per SM (<= 85 registers) pooled 2278 GB/s, 2 blocks 2096, 4 blocks (64
 // registers, spills) 1486; letting the row loads allocate in L1 or not, and prefetching the
 // next index chunk or not, changed nothing measurable.
+// Two other structures were built and measured on the same 256-table launch (346 us as it is):
+//  * one 16-byte load per lane over the aligned window of a row (a single request per row, the
+//    scale/offset pair handed round by shuffle): 8 lanes a row instead of 4 halves the rows a
+//    warp has in flight -- 522 us;
+//  * rows copied by cp.async.bulk into a per-warp shared-memory ring two blocks of 32 indices
+//    ahead, pooled out of shared memory in index order: the copies alone (no pooling) take
+//    344 us, the pooling alone 288 us, both in one warp 420 us.  The fetch side of that kernel
+//    runs at the rate this one reaches with everything included, which is the evidence that
+//    24 G rows/s is what the memory system gives 72-byte rows at 8-byte boundaries.
 #ifndef GLOWB200_SLWS_L1_NOALLOC
 #define GLOWB200_SLWS_L1_NOALLOC 0
 #endif
@@ -138,10 +151,12 @@ __global__ void __launch_bounds__(kSegThreads) slws_segments_from_lengths_kernel
   __shared__ int64_t warp_tot[33];
   const glowb200_slws_job job = p.jobs ? p.jobs[blockIdx.x] : p.single;
   int64_t *out = p.seg_begin + (int64_t)blockIdx.x * p.seg_stride;
-  const int64_t S = job.segments, N = job.num_indices;
+  int32_t flags = 0;
+  int64_t S = job.segments;
+  if (S > p.max_segments) { S = p.max_segments; flags |= GLOWB200_STATUS_BAD_OFFSETS; }
+  const int64_t N = job.num_indices;
   constexpr int kItems = 4;
   int64_t carry = 0;
-  int32_t flags = 0;
   int64_t longest = 0;
   for (int64_t tile = 0; tile < S; tile += (int64_t)kSegThreads * kItems) {
     const int64_t first = tile + (int64_t)threadIdx.x * kItems;
@@ -332,16 +347,12 @@ __device__ __forceinline__ float load_weight(const void *weights, int64_t i) {
 // ------------------------------------------------------------------------------------------
 // Gather-pool.  grid = (ceil(max_segments / bags_per_block), num_jobs).
 // ------------------------------------------------------------------------------------------
-// WIDE16 (uint8 rows, P = 2, rows a multiple of 16 bytes wide in a 16-byte aligned table -- the
-// padded layouts): a lane owns two ADJACENT chunks and fetches them with one 16-byte load, so a
-// row costs two load instructions (payload, scale/offset) instead of three.
-template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int kUnroll, bool SHARD = false,
-          bool WIDE16 = false>
+template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int kUnroll, bool SHARD = false>
 __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
   using RL = RowLoad<BITS, SO16>;
   const int job_id = blockIdx.y;
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + job_id) : &p.single;
-  const int64_t segments = jp->segments;
+  const int64_t segments = bags_of(p, jp);
   const int lpr = 1 << p.lpr_log2;
   const int gl = threadIdx.x & (lpr - 1);
   const int64_t bag = (int64_t)blockIdx.x * (kGatherThreads >> p.lpr_log2) + (threadIdx.x >> p.lpr_log2);
@@ -364,7 +375,7 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
 
   bool has[P];
 #pragma unroll
-  for (int c = 0; c < P; c++) has[c] = (WIDE16 ? gl * P + c : c * lpr + gl) < chunks;
+  for (int c = 0; c < P; c++) has[c] = (c * lpr + gl) < chunks;
 
   float acc[P][8];
 #pragma unroll
@@ -419,18 +430,9 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
       for (int u = 0; u < kUnroll; u++) {
         if (r[u] >= 0) {
           const uint8_t *row = data + (int64_t)r[u] * in_line;
-          if constexpr (WIDE16) {
-            if (has[0]) {
-              uint4 q;
-              asm("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(row + gl * 16));
-              pay[u][0].lo = q.x; pay[u][0].hi = q.y;
-              pay[u][1].lo = q.z; pay[u][1].hi = q.w;
-            }
-          } else {
 #pragma unroll
-            for (int c = 0; c < P; c++)
-              if (has[c]) pay[u][c] = RL::payload(row, c * lpr + gl);
-          }
+          for (int c = 0; c < P; c++)
+            if (has[c]) pay[u][c] = RL::payload(row, c * lpr + gl);
           tl[u] = RL::tail(row + in_line);
         }
       }
@@ -479,7 +481,7 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
 #pragma unroll
   for (int c = 0; c < P; c++) {
     if (!has[c]) continue;
-    const int64_t col = (int64_t)(WIDE16 ? gl * P + c : c * lpr + gl) * 8;
+    const int64_t col = (int64_t)(c * lpr + gl) * 8;
     float o[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) o[i] = ACC16 ? acc[c][i] : (acc[c][i] + bias_sum);
@@ -536,7 +538,7 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
   constexpr int V = 8 * P;  // sums a lane carries
   const int job_id = blockIdx.y;
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + job_id) : &p.single;
-  const int64_t segments = jp->segments;
+  const int64_t segments = bags_of(p, jp);
   const int64_t first_bag = ((int64_t)blockIdx.x * (kGatherThreads >> 5) + (threadIdx.x >> 5)) * bags_per_warp;
   if (first_bag >= segments) return;  // whole warps leave together
   const int n_bags = (int)((first_bag + bags_per_warp < segments ? first_bag + bags_per_warp : segments) - first_bag);
@@ -694,8 +696,12 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
   // of the current bag are dealt to the slots kUnroll steps at a time: their loads are issued
   // together, then pooled.  When the bag ends its sums are flushed and the next bag continues
   // in the same block.
+  // A row's slot is its index within the bag modulo the slot count, wherever the bag begins in
+  // its block and however many bags the run holds: every slot then adds the same rows in the
+  // same order for any launch size, and a table pooled alone gives the same bits as the table
+  // pooled beside others.
   int bag = 0;
-  int pos = 0, bag_end = (int)(end_of_bag(0) - run0);
+  int pos = 0, bag_start = 0, bag_end = (int)(end_of_bag(0) - run0);
   int blk = 0;  // the 32 indices in hand are positions blk .. blk + 31
   int32_t r_mine, r_next;
   float w_mine, w_next;
@@ -704,6 +710,7 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
   while (true) {
     const int lim = bag_end < blk + 32 ? bag_end : blk + 32;
     const int q0 = pos - blk, n = lim - blk;
+    const int rot = (slot - (pos - bag_start)) & (slots - 1);  // this slot's first row of the piece, counted from q0
     for (int k = 0; q0 + k * slots < n; k += kUnroll) {
       int32_t r[kUnroll];
       float w[kUnroll];
@@ -711,7 +718,7 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
       uint2 tl[kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; u++) {
-        const int src = q0 + (k + u) * slots + slot;  // position of this slot's row in the block
+        const int src = q0 + (k + u) * slots + rot;  // position of this slot's row in the block
         r[u] = __shfl_sync(0xffffffffu, r_mine, src & 31);
         w[u] = __shfl_sync(0xffffffffu, w_mine, src & 31);
         if (src >= n) r[u] = -2;                       // no row for this slot in this step
@@ -746,6 +753,7 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
       if (bag == n_bags - 1) break;
       reset();
       bag++;
+      bag_start = pos;
       bag_end = (int)(end_of_bag(bag) - run0);  // bags of a lengths array are back to back: the next one starts at pos
     }
     if (pos == blk + 32) {  // the block is used up: the prefetched one becomes current
@@ -769,14 +777,14 @@ slws_gather_small_kernel(const __grid_constant__ SlwsLaunch p) {
 // One launch, two thread-to-bag mappings: every table is pooled by the mapping its bag-length
 // profile favours (the word the segments kernel leaves behind the table's boundaries).
 // grid.x covers the larger of the two mappings' block counts; surplus blocks leave at once.
-template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false, bool WIDE16 = false>
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false>
 __global__ void __launch_bounds__(kGatherThreads, P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS)
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
   const bool skewed = GLOWB200_SLWS_FORCE_WARP || p.warp_per_bag != 0 ||
-                      p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + jp->segments + 1] != 0;
+                      p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + bags_of(p, jp) + 1] != 0;
   if (skewed) gather_warp_body<BITS, SO16, OUT16, IdxT, P, U, SHARD>(p, bags_per_warp);
-  else gather_group_body<BITS, SO16, OUT16, false, IdxT, P, U, SHARD, WIDE16>(p);
+  else gather_group_body<BITS, SO16, OUT16, false, IdxT, P, U, SHARD>(p);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -790,7 +798,7 @@ __global__ void __launch_bounds__(256) slws_gather_any_kernel(const __grid_const
   const int job_id = blockIdx.y;
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + job_id) : &p.single;
   const int64_t bag = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (bag >= jp->segments) return;
+  if (bag >= bags_of(p, jp)) return;
   const int lane = threadIdx.x & 31;
   const uint8_t *data = reinterpret_cast<const uint8_t *>(jp->data);
   const int64_t *sb = p.seg_begin + (int64_t)job_id * p.seg_stride;
@@ -890,12 +898,6 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
       const int64_t warps = (max_segments + bpw - 1) / bpw;
       const unsigned wblocks = (unsigned)((warps + 7) / 8);
       dim3 sgrid(wblocks > grid.x ? wblocks : grid.x, grid.y);
-      if constexpr (BITS == 8 && !SO16 && !OUT16 && P == 2 && U == 4) {
-        if (!L.sharded && L.wide16) {  // padded rows: one 16-byte payload load per lane
-          slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, false, true><<<sgrid, kGatherThreads, 0, s>>>(L, bpw);
-          return cudaGetLastError();
-        }
-      }
       if constexpr (!OUT16) {  // shards give fp32 partial sums (checked by the entry point)
         if (L.sharded) {
           slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, true><<<sgrid, kGatherThreads, 0, s>>>(L, bpw);
@@ -1018,6 +1020,7 @@ int glowb200::launch_segments_from_lengths(const int32_t *lengths, int64_t segme
   L.single.num_indices = num_indices;
   L.seg_begin = reinterpret_cast<int64_t *>(workspace);
   L.seg_stride = (int64_t)seg_stride_elems(segments);
+  L.max_segments = segments;
   L.status = status;
   slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, stream>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
@@ -1052,6 +1055,7 @@ int run_batched(const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_seg
   L.jobs = jobs;
   L.seg_begin = reinterpret_cast<int64_t *>(workspace);
   L.seg_stride = (int64_t)seg_stride_elems(max_segments);
+  L.max_segments = max_segments;
   L.status = status;
   L.in_line = (int32_t)in_line_size;
   L.out_line = (int32_t)out_line_size;
@@ -1060,7 +1064,6 @@ int run_batched(const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_seg
                  (use_fp16_accumulation && out_is_fp16 && (kind & 1)) ? 1 : 0};
   L.select = (P != 0 && !g.acc16) ? 1 : 0;
   L.sharded = sharded ? 1 : 0;
-  L.wide16 = (in_line_size % 16) == 0 ? 1 : 0;  // 16-byte aligned tables are required of the descriptors
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   slws_segments_from_lengths_kernel<<<(unsigned)num_jobs, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
@@ -1114,6 +1117,7 @@ int fill_single(SlwsLaunch &L, GatherConfig &g, int &P, void *dest, const void *
   L.single.segments = segments;
   L.seg_begin = reinterpret_cast<int64_t *>(workspace);
   L.seg_stride = (int64_t)seg_stride_elems(segments);
+  L.max_segments = segments;
   L.status = status;
   L.in_line = (int32_t)in_line;
   L.out_line = (int32_t)out_line;
@@ -1138,7 +1142,6 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
   if (segments == 0) return GLOWB200_OK;
   GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
   L.select = (P != 0 && !g.acc16) ? 1 : 0;
-  L.wide16 = ((in_line_size % 16) == 0 && aligned_to(data, 16)) ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   slws_segments_from_lengths_kernel<<<1, kSegThreads, 0, s>>>(L);
   GLOWB200_CUDA_OK(cudaGetLastError());
@@ -1160,7 +1163,6 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_low_
   GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
   L.select = (P != 0) ? 1 : 0;
   L.warp_per_bag = 1;
-  L.wide16 = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // up to 2048 bags every warp adds up the lengths before its bag itself (at most 64 loads a lane)
   L.inline_lengths = (P != 0 && segments <= 2048) ? 1 : 0;
@@ -1276,7 +1278,6 @@ extern "C" int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_stat
     return rc;
   GLOWB200_REQUIRE(lengths != nullptr, "lengths is NULL");
   L.select = (P != 0 && !g.acc16) ? 1 : 0;
-  L.wide16 = ((in_line_size % 16) == 0 && aligned_to(data, 16)) ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // The segments kernel rewrites everything this call reads (segments + 1 boundaries and the
   // table's profile word); nothing in the array has to start at zero, and whatever an earlier

@@ -788,6 +788,11 @@ class SlwsBatch:
             _cuda(lengths[i], "lengths", (torch.int32,))
             if tables[i].shape[1] != self.in_line:
                 raise ValueError("all tables of a batch share one row width")
+            # the batched kernels use vector loads on the strength of these alignments
+            for what, ten, al in (("table", tables[i], 16), ("weights", weights[i], weights[i].element_size()),
+                                  ("indices", indices[i], indices[i].element_size()), ("lengths", lengths[i], 4)):
+                if ten.data_ptr() % al:
+                    raise ValueError("%s %d of a batched launch must start on a %d-byte boundary" % (what, i, al))
             j = arr[i]
             j.data, j.weights, j.indices = tables[i].data_ptr(), weights[i].data_ptr(), indices[i].data_ptr()
             j.lengths = lengths[i].data_ptr()

@@ -69,7 +69,13 @@ const char *glowb200_version(void);
  * Embedding gather-pool
  * ------------------------------------------------------------------------------------- */
 
-/* One table's worth of work in a batched launch (all pointers are device pointers). */
+/* One table's worth of work in a batched launch (all pointers are device pointers).
+ * Alignment: `data` must start on a 16-byte boundary (any offset of a cudaMalloc'ed slab that
+ * keeps Glow's 64-byte tensor alignment does); weights, indices and lengths on the boundary of
+ * their element type.  The batched entry points read the descriptors on the device and use
+ * vector loads on the strength of this -- a misaligned table is not detected, it faults.
+ * `segments` must not exceed the max_segments the launch is given: surplus bags are left out
+ * and reported through GLOWB200_STATUS_BAD_OFFSETS. */
 typedef struct glowb200_slws_job {
   const void *data;       /* fused table [rows, in_line_size] bytes                         */
   const void *weights;    /* per-index weights, the result's element type, [num_indices]     */

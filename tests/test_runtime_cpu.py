@@ -94,3 +94,66 @@ def test_new_instruction_kinds_compile_and_reject_malformed_forms():
     k.instruction(runtime.BINARY_I8, [x, x, x], [64, 0, 0, 0], [1.0, 1.0, 1.0])            # the operator is missing
     with pytest.raises(GlowB200Error, match="malformed BINARY_I8"):
         k.compile()
+
+
+def _fc_function(name, *, y_bytes=None, scales=True, M=4, K=32, N=8):
+    f = runtime.Function(name)
+    w = f.constant("w", np.ones((N, K), np.int8))
+    sc = f.constant("scales", np.full(N, 0.01, np.float32)) if scales else -1
+    off = f.constant("offsets", np.zeros(N, np.int32))
+    b = f.constant("bias", np.zeros(N, np.int32))
+    x = f.placeholder("x", M * K)
+    y = f.placeholder("y", M * N if y_bytes is None else y_bytes)
+    return f, (y, x, w, sc, off, b), dict(M=M, K=K, N=N, in_tqp=(0.05, 3), bias_tqp=(5e-4, 0), out_tqp=(0.5, 0))
+
+
+def test_compile_rejects_what_would_leave_a_symbol():
+    """An instruction is checked against the byte sizes of the symbols it names: nothing that
+    would read or write outside one of them compiles."""
+    f, ops_, kw = _fc_function("short_dest", y_bytes=4 * 8 - 1)
+    f.rowwise_fc(*ops_, **kw)
+    with pytest.raises(GlowB200Error, match="smaller than"):
+        f.compile()
+    # a required operand left out
+    f, ops_, kw = _fc_function("no_scales", scales=False)
+    f.rowwise_fc(*ops_, **kw)
+    with pytest.raises(GlowB200Error, match="is required"):
+        f.compile()
+    # a constant as destination
+    f, ops_, kw = _fc_function("const_dest")
+    f.rowwise_fc(ops_[2], *ops_[1:], **dict(kw, M=8, K=32, N=8))
+    with pytest.raises(GlowB200Error, match="smaller than|is a constant"):
+        f.compile()
+    g = runtime.Function("copy_into_const")
+    c = g.constant("c", np.zeros(16, np.int8))
+    a = g.placeholder("a", 16)
+    g.copy(c, a, nbytes=16)
+    with pytest.raises(GlowB200Error, match="is a constant"):
+        g.compile()
+    # copies, element-wise kernels and insert-tensor are bounded too
+    g = runtime.Function("long_copy")
+    a, b = g.placeholder("a", 16), g.placeholder("b", 8)
+    g.copy(a, b, nbytes=16)
+    with pytest.raises(GlowB200Error, match="smaller than"):
+        g.compile()
+    g = runtime.Function("insert")
+    a, b = g.placeholder("a", 64), g.placeholder("b", 32)
+    g.insert_tensor(a, b, rows=4, width_bytes=8, dest_pitch_bytes=16, dest_offset_bytes=12)  # last row ends at 68
+    with pytest.raises(GlowB200Error, match="smaller than"):
+        g.compile()
+    g = runtime.Function("insert_ok")
+    a, b = g.placeholder("a", 64), g.placeholder("b", 32)
+    g.insert_tensor(a, b, rows=4, width_bytes=8, dest_pitch_bytes=16, dest_offset_bytes=8)
+    g.compile()
+
+
+def test_convolution_group_is_checked_before_it_divides():
+    f = runtime.Function("conv_group0")
+    ids = [f.placeholder("y", 16), f.placeholder("x", 16), f.constant("w", np.zeros(16, np.int8)),
+           f.constant("b", np.zeros(4, np.int32)), f.constant("fs", np.ones(4, np.float32)),
+           f.constant("fo", np.zeros(4, np.int32)), f.constant("bs", np.ones(4, np.float32)),
+           f.constant("bo", np.zeros(4, np.int32))]
+    ia = [1, 2, 2, 4, 2, 2, 4, 1, 1, 1, 1, 0, 0, 0, 0, 0, 1, 1, 0, 0, 0]  # group = 0
+    f.instruction(runtime.CWQ_CONV, ids, ia, [0.1, 0.1])
+    with pytest.raises(GlowB200Error, match="group"):
+        f.compile()
