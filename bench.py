@@ -63,6 +63,10 @@ def parse():
                          "rank filtering the whole request; or row ranges with the request routed to the owning rank "
                          "beforehand (each rank is handed only the indices of its rows)")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary int8 FC measurement")
+    ap.add_argument("--as-rank-of", type=int, default=0,
+                    help="dlrm on ONE GPU: run only what rank 0 of an N-way table partition runs in a step (its "
+                         "tables for the whole batch, the dense layers for a 1/N slice of the batch; the exchange "
+                         "stores go to its own slab) -- the per-rank launch list of an N-GPU step, for profiling")
     return ap.parse_args()
 
 
@@ -436,7 +440,58 @@ def run_int8_fc_line(args):
         dist.destroy_process_group()
 
 
-def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges):
+def dlrm_partition_checks(torch, dist, dev, rank, world, cfg, qm, tables):
+    """Result checks of the partitioned model on the real GPUs, before anything is timed
+    (the reference requires a partitioned run to equal the unpartitioned one bit for bit,
+    tests/unittests/RecommendationSystemTest.cpp:1155-1226):
+      exchange_forms_agree   the fused peer-store exchange and the NCCL all-to-all give the same
+                             pooled slabs and the same scores on every rank;
+      matches_unpartitioned  the scores of all ranks, gathered, equal what rank 0 computes with
+                             all tables on one GPU.
+    Raises if either is false."""
+    from glow_b200 import dlrm
+    mine = dlrm.tables_of_rank(cfg, rank, world)
+    lo, hi = dlrm.batch_slice(cfg, rank, world)
+    dense, lengths, indices = dlrm.make_request(cfg, 4242, tables=mine, device=dev)
+    got = {}
+    for exchange in ("fused", "nccl"):
+        model = dlrm.DLRMRank(cfg, qm, tables, rank, world, dev, exchange)
+        if exchange == "fused":
+            model.connect_peers()
+        outs = []
+        for _ in range(2):  # both receive slabs
+            out = model.forward_request(dense[lo:hi].contiguous(), lengths, indices)
+            torch.cuda.synchronize()
+            dist.barrier()
+            outs.append((out.clone(), model.slabs[(model.step - 1) & 1].clone()))
+        assert int(model.status.item()) == 0
+        got[exchange] = outs
+        dist.barrier()
+        model.release()
+        del model
+    same = all(torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) for a, b in zip(got["fused"], got["nccl"]))
+    same = same and torch.equal(got["fused"][0][0], got["fused"][1][0])
+    gathered = [torch.empty_like(got["fused"][0][0]) for _ in range(world)]
+    dist.all_gather(gathered, got["fused"][0][0])
+    whole_ok = True
+    if rank == 0:
+        all_tables = {t: (tables[t] if t in tables else dlrm.make_table(cfg, t, dev)) for t in range(cfg.tables)}
+        d1, l1, i1 = dlrm.make_request(cfg, 4242, device=dev)
+        single = dlrm.DLRMRank(cfg, qm, all_tables, 0, 1, dev, "local")
+        want = single.forward_request(d1, l1, i1)
+        torch.cuda.synchronize()
+        whole_ok = torch.equal(torch.cat(gathered, 0), want)
+        del single, all_tables
+        torch.cuda.empty_cache()
+    flags = torch.tensor([int(same), int(whole_ok)], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    res = {"exchange_forms_agree": bool(int(flags[0])), "matches_unpartitioned": bool(int(flags[1]))}
+    if not (res["exchange_forms_agree"] and res["matches_unpartitioned"]):
+        raise AssertionError("partitioned DLRM results differ: %r" % res)
+    return res
+
+
+def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges, as_rank_of=0):
     """DLRM-style model of the fourth benchmark configuration: 64 tables x 4,000,000 rows x 128
     (uint8 fused rows), batch 4096, power-law bag lengths (mean 40, max 200) and row indices,
     bottom MLP 256-512-256-128, pairwise-dot interaction (2208 wide), top MLP 2208-1024-1024-512-1,
@@ -445,12 +500,19 @@ def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges):
     Returns {exchange: {...}} for every exchange form in `exchanges`."""
     from glow_b200 import dlrm
     cfg = dlrm.DLRMConfig()
-    mine = dlrm.tables_of_rank(cfg, rank, world)
+    part = as_rank_of if (as_rank_of and world == 1) else world   # ways the model is partitioned
+    mine = dlrm.tables_of_rank(cfg, rank, part)
     tables = {t: dlrm.make_table(cfg, t, dev) for t in mine}
     fm = dlrm.float_model(cfg)
-    ranges = dlrm.calibrate(cfg, fm, tables, dev, rank, world)
+    if part != world:
+        ranges = dlrm.fixed_ranges(cfg)   # one rank alone cannot calibrate: timing only
+    else:
+        ranges = dlrm.calibrate(cfg, fm, tables, dev, rank, world)
     qm = dlrm.quantize_model(cfg, fm, ranges)
-    lo, hi = dlrm.batch_slice(cfg, rank, world)
+    lo, hi = dlrm.batch_slice(cfg, rank, part)
+    checks = {}
+    if world > 1:
+        checks = dlrm_partition_checks(torch, dist, dev, rank, world, cfg, qm, tables)
     R = 2
     host = []
     for r in range(R):
@@ -459,9 +521,11 @@ def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges):
                      {t: v.pin_memory() for t, v in indices.items()}))
     results = {}
     for exchange in exchanges:
-        model = dlrm.DLRMRank(cfg, qm, tables, rank, world, dev, exchange)
+        model = dlrm.DLRMRank(cfg, qm, tables, rank, part, dev, exchange)
         if exchange == "fused":
             model.connect_peers()
+        elif exchange == "emulated":
+            model.set_peers([model] * part)
         devr = [(h[0].to(dev), {t: v.to(dev) for t, v in h[1].items()}, {t: v.to(dev) for t, v in h[2].items()})
                 for h in host]
         bound = [[model.prepare(d[1], d[2], slab) for slab in range(2)] for d in devr]
@@ -562,6 +626,7 @@ def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges):
                              "e2e_samples_per_s": cfg.batch / (float(t[1]) * 1e-3), "e2e_ms_per_step": float(t[1]),
                              "h2d_bytes_per_step_per_rank": int(h2d), "d2h_bytes_per_step_per_rank": (hi - lo) * 4,
                              "launches_per_step": model.launches_per_step, "cuda_graph": graphed}
+        results[exchange].update(checks)
         model.release()
         del model, bound, ebound, devr, stage
         torch.cuda.empty_cache()
@@ -654,8 +719,14 @@ def run_model_line(args):
     sampler.start()
     if args.workload == "dlrm":
         forms = ["local"] if world == 1 else ["fused", "nccl"]
-        res, cfg = dlrm_measure(torch, dist, dev, rank, world, max(10, args.steps), max(3, args.warmup), forms)
+        if world == 1 and args.as_rank_of > 1:
+            forms = ["emulated"]
+        res, cfg = dlrm_measure(torch, dist, dev, rank, world, max(10, args.steps), max(3, args.warmup), forms,
+                                as_rank_of=args.as_rank_of)
         best = max(res.values(), key=lambda r: r["samples_per_s"])
+        if world == 1 and args.as_rank_of > 1:
+            cfg = dict(cfg, as_rank_of=args.as_rank_of,
+                       note="one rank's share of a %d-way partition on one GPU: NOT a throughput of the model" % args.as_rank_of)
         line = {"metric": "dlrm_samples_per_s", "value": best["samples_per_s"], "unit": "samples/s", "n_gpus": world,
                 "steps": max(10, args.steps), "warmup": max(3, args.warmup), "ms_per_step": best["ms_per_step"],
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8 -> f32 pooling, s8 x s8 -> s32 layers",

@@ -680,15 +680,25 @@ bool ptr16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 // a tile (or more) of padding; else 256 -- unless 240-column tiles finish in fewer, or as many
 // but narrower, rounds over the SMs: 2048 x 4096 is 256 tiles of 256 columns (two rounds on 148
 // SMs, the second 73 % full) but 288 tiles of 240 (two rounds, 6 % shorter each).
+// A product with few rows (a batch-sharded layer: 512 x 1024 is 20 tiles of 240 columns on 148
+// SMs) takes narrower tiles until at least half of the SMs have one: the k loop of a tile is a
+// chain of load and MMA latencies that narrower tiles run side by side.
 int pick_block_n(int M, int N) {
   if (N <= 64) return 64;
-  if (((N + 127) / 128) & 1) return 128;
-#if GLOWB200_GEMM_TILE_240
   const long sms = sm_count(), m_tiles = (M + kBlockM - 1) / kBlockM;
-  auto cost = [&](long bn) { return ((m_tiles * ((N + bn - 1) / bn) + sms - 1) / sms) * (bn + 16); };
-  if (cost(240) * 100 < cost(256) * 97) return 240;
+  auto tiles = [&](long bn) { return m_tiles * ((N + bn - 1) / bn); };
+  int bn = 256;
+  if (((N + 127) / 128) & 1) {
+    bn = 128;
+  } else {
+#if GLOWB200_GEMM_TILE_240
+    auto cost = [&](long b) { return ((tiles(b) + sms - 1) / sms) * (b + 16); };
+    if (cost(240) * 100 < cost(256) * 97) bn = 240;
 #endif
-  return 256;
+  }
+  if (bn > 128 && tiles(bn) * 2 <= sms) bn = 128;
+  if (bn == 128 && tiles(128) * 2 <= sms) bn = 64;
+  return bn;
 }
 
 int launch_for_block_n(int bn, const void *a, int a_rows, int a_extent, int a_pitch, const void *b, const GemmParams &p,

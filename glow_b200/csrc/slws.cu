@@ -29,7 +29,17 @@
 namespace glowb200 {
 namespace {
 
-constexpr int kGatherThreads = 256;
+// Threads of a gather block.  A block's SM slots stay taken until its slowest warp is done, and
+// bags differ a lot in length (power-law pooling factors), so blocks are kept small: against
+// 256 threads, 64 pool the 256-table launch 4.7 % faster (329 us), the recommendation model's
+// 64 skewed tables 9.5 % and one rank's eight of them 11 %.  (A persistent form -- warps taking
+// pieces of work from a counter -- was tried first: the loop round both mappings cost 250 bytes
+// of spills a thread and the launch 60 %.)
+#ifndef GLOWB200_SLWS_THREADS
+#define GLOWB200_SLWS_THREADS 64
+#endif
+constexpr int kGatherThreads = GLOWB200_SLWS_THREADS;
+constexpr int kGatherBlockScale = 256 / kGatherThreads;  // blocks per SM scale with it
 constexpr int kSegThreads = 1024;
 
 struct SlwsLaunch {
@@ -511,7 +521,7 @@ __device__ __forceinline__ void gather_group_body(const SlwsLaunch &p) {
 }
 
 template <int BITS, bool SO16, bool OUT16, bool ACC16, typename IdxT, int P, int U>
-__global__ void __launch_bounds__(kGatherThreads, P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
+__global__ void __launch_bounds__(kGatherThreads, kGatherBlockScale * (P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS)) slws_gather_kernel(const __grid_constant__ SlwsLaunch p) {
   gather_group_body<BITS, SO16, OUT16, ACC16, IdxT, P, U>(p);
 }
 
@@ -769,7 +779,7 @@ __device__ __forceinline__ void gather_warp_body(const SlwsLaunch &p, int bags_p
 // The warp-per-run mapping alone, bag boundaries computed in place: the whole of a small request
 // in one launch.
 template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U>
-__global__ void __launch_bounds__(kGatherThreads, GLOWB200_SLWS_MIN_BLOCKS)
+__global__ void __launch_bounds__(kGatherThreads, kGatherBlockScale * GLOWB200_SLWS_MIN_BLOCKS)
 slws_gather_small_kernel(const __grid_constant__ SlwsLaunch p) {
   gather_warp_body<BITS, SO16, OUT16, IdxT, P, U, false, true>(p, 1);
 }
@@ -778,7 +788,7 @@ slws_gather_small_kernel(const __grid_constant__ SlwsLaunch p) {
 // profile favours (the word the segments kernel leaves behind the table's boundaries).
 // grid.x covers the larger of the two mappings' block counts; surplus blocks leave at once.
 template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false>
-__global__ void __launch_bounds__(kGatherThreads, P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS)
+__global__ void __launch_bounds__(kGatherThreads, kGatherBlockScale * (P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS))
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
   const bool skewed = GLOWB200_SLWS_FORCE_WARP || p.warp_per_bag != 0 ||
@@ -887,7 +897,7 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
       // warp-per-run mapping takes runs of up to 8 bags once that still leaves every SM a few
       // waves of warps; single bags for small launches.
       if (L.inline_lengths) {  // one warp per bag, boundaries computed by the warps: a single launch
-        const unsigned blocks = (unsigned)((L.single.segments + 7) / 8);
+        const unsigned blocks = (unsigned)((L.single.segments + (kGatherThreads >> 5) - 1) / (kGatherThreads >> 5));
         slws_gather_small_kernel<BITS, SO16, OUT16, IdxT, P, U><<<blocks, kGatherThreads, 0, s>>>(L);
         return cudaGetLastError();
       }
@@ -896,7 +906,7 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
       int bpw = (int)(total / want);
       bpw = bpw < 1 ? 1 : (bpw > GLOWB200_SLWS_MAX_BPW ? GLOWB200_SLWS_MAX_BPW : bpw);
       const int64_t warps = (max_segments + bpw - 1) / bpw;
-      const unsigned wblocks = (unsigned)((warps + 7) / 8);
+      const unsigned wblocks = (unsigned)((warps + (kGatherThreads >> 5) - 1) / (kGatherThreads >> 5));
       dim3 sgrid(wblocks > grid.x ? wblocks : grid.x, grid.y);
       if constexpr (!OUT16) {  // shards give fp32 partial sums (checked by the entry point)
         if (L.sharded) {

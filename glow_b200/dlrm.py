@@ -40,6 +40,11 @@ class DLRMConfig:
     max_len: int = 200
     zipf_s: float = 1.05
     seed: int = 0x610B200
+    # Schema of the rowwise-quantized MLP weights (the `schema` argument of
+    # Function::createRowwiseQuantizedFullyConnected, lib/Graph/Graph.cpp:1198-1246).  Symmetric
+    # rows have offset 0, which takes the activation row sums (one more pass over every layer's
+    # input) out of the step; He-normal weights are centred, so the ranges lose next to nothing.
+    weights_schema: str = "symmetric"
 
     @property
     def interaction_width(self):
@@ -166,10 +171,12 @@ def float_forward(cfg, fm, dense, pooled):
 
 
 def quantize_model(cfg, fm, ranges):
-    """Quantized constants for every FC: rowwise int8 weights (asymmetric), int32 bias with scale
+    """Quantized constants for every FC: rowwise int8 weights (cfg.weights_schema), int32 bias with scale
     in_scale * (per-tensor weight scale), activation types from the calibrated ranges."""
     def tqp(name):
         return ops.choose_quantization_params(*ranges[name], ops.ASYMMETRIC)
+
+    w_schema = ops.SYMMETRIC if cfg.weights_schema == "symmetric" else ops.ASYMMETRIC
 
     out = {"bottom": [], "top": []}
     prev = tqp("dense")
@@ -177,8 +184,8 @@ def quantize_model(cfg, fm, ranges):
     for part, first_in in (("bottom", "dense"), ("top", "interaction")):
         prev = tqp(first_in)
         for i, (w, b) in enumerate(fm[part]):
-            q, sc, off = ops.tensor_rowwise_quantize_i8(w, ops.ASYMMETRIC)
-            w_tensor_scale, _ = ops.choose_quantization_params(float(w.min()), float(w.max()), ops.ASYMMETRIC)
+            q, sc, off = ops.tensor_rowwise_quantize_i8(w, w_schema)
+            w_tensor_scale, _ = ops.choose_quantization_params(float(w.min()), float(w.max()), w_schema)
             bias_scale = float(np.float32(prev[0]) * np.float32(w_tensor_scale))
             o = tqp("%s%d" % (part, i))
             relu = not (part == "top" and i + 1 == len(fm[part]))
@@ -272,6 +279,10 @@ class DLRMRank:
                    zip([cfg.dense_in] + list(cfg.bottom) + [cfg.interaction_width] + list(cfg.top),
                        list(cfg.bottom) + [0] + list(cfg.top)) if n)
         self.ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        # the bottom MLP does not depend on the pooled vectors: it runs on a stream of its own,
+        # beside the pooling kernel, with a workspace of its own
+        self.ws_bottom = torch.empty(need, dtype=torch.uint8, device=dev)
+        self.side = torch.cuda.Stream(device=dev)
         self.ones = None
         # receive slabs [per, T, D] (two, alternating by step) and, for "nccl", the send buffer
         self.step = 0
@@ -342,12 +353,19 @@ class DLRMRank:
         return self.slabs[slab]
 
     # -- dense part ----------------------------------------------------------------------
-    def dense_forward(self, dense_slice, pooled):
+    def bottom_forward(self, dense_slice):
         ops.element_quantize_i8(dense_slice, self.dense_tqp[0], self.dense_tqp[1], out=self.act_b[0])
         for i, fc in enumerate(self.bottom):
-            fc(self.act_b[i], self.act_b[i + 1], self.ws, self.status)
+            fc(self.act_b[i], self.act_b[i + 1], self.ws_bottom, self.status)
         last = self.bottom[-1].fc
         ops.element_dequantize_i8(self.act_b[-1], last.out_scale, last.out_offset, out=self.x0)
+        return self.x0
+
+    def dense_forward(self, dense_slice, pooled):
+        self.bottom_forward(dense_slice)
+        return self.top_forward(pooled)
+
+    def top_forward(self, pooled):
         ops.pairwise_dot_interaction(self.x0, pooled, quant=self.inter_tqp, out=self.act_t[0])
         for i, fc in enumerate(self.top):
             fc(self.act_t[i], self.act_t[i + 1], self.ws, self.status)
@@ -358,8 +376,13 @@ class DLRMRank:
     def forward(self, dense_slice, bound_pair):
         """One step: bound_pair[slab] is the request bound to each of the two receive slabs."""
         slab = self.step & 1
+        main = torch.cuda.current_stream(self.device)
+        self.side.wait_stream(main)          # the dense features (and the last step's x0 readers) are ready
+        with torch.cuda.stream(self.side):
+            self.bottom_forward(dense_slice)
         pooled = self.pool_and_exchange(bound_pair[slab], slab)
-        out = self.dense_forward(dense_slice, pooled)
+        main.wait_stream(self.side)
+        out = self.top_forward(pooled)
         self.step += 1
         return out
 
@@ -373,6 +396,17 @@ class DLRMRank:
     def launches_per_step(self):
         # segments + gather, quantize, FCs, dequantize x2, interaction
         return 2 + 1 + len(self.bottom) + 1 + 1 + len(self.top) + 1
+
+
+def fixed_ranges(cfg):
+    """Activation ranges of about the calibrated size, for runs that only time one rank's share
+    of a partitioned model and cannot calibrate (no pooled vectors of the other ranks)."""
+    r = {"dense": (-4.5, 4.5), "interaction": (-60.0, 60.0)}
+    for i in range(len(cfg.bottom)):
+        r["bottom%d" % i] = (0.0, 6.0)
+    for i in range(len(cfg.top)):
+        r["top%d" % i] = (0.0, 30.0) if i + 1 < len(cfg.top) else (-30.0, 30.0)
+    return r
 
 
 def calibrate(cfg, fm, tables, device, rank=0, world=1, group=None):

@@ -14,9 +14,9 @@ CFG = dict(tables=6, rows=3000, dim=32, batch=64, dense_in=48, bottom=(64, 32), 
            max_len=40)
 
 
-@pytest.fixture(scope="module")
-def model():
-    cfg = dlrm.DLRMConfig(**CFG)
+@pytest.fixture(scope="module", params=["symmetric", "asymmetric"])
+def model(request):
+    cfg = dlrm.DLRMConfig(**CFG, weights_schema=request.param)
     tables = {t: dlrm.make_table(cfg, t, DEV) for t in range(cfg.tables)}
     fm = dlrm.float_model(cfg)
     ranges = dlrm.calibrate(cfg, fm, tables, DEV)
