@@ -31,7 +31,12 @@ sys.path.insert(0, ROOT)
 
 ROWS, DIM, BATCH = 1_000_000, 64, 1024
 IN_LINE = DIM + 8
-NCU_DRAM_BYTES_PER_ROW = 203.7  # 72-byte rows, uint8 gather kernel (see profiles/)
+# DRAM bytes per gathered 72-byte row of the uint8 gather kernel: dram__bytes_read.sum +
+# dram__bytes_write.sum of one launch over 64 tables (4.6 waves of blocks, 2.10 M rows), from the
+# ncu capture summarised in profiles/.  ncu cannot run inside the timed region, so `traffic` is
+# this figure x the rows of the timed launch (traffic is proportional to rows: every row is
+# fetched once, L2 hit rate 13 %).
+NCU_DRAM_BYTES_PER_ROW = 205.6
 METRIC = "frwq_slws_hbm_gbps"
 UNIT = "GB/s"
 
@@ -259,16 +264,22 @@ def run_reference(args):
         "gpu_launches": 0}))
 
 
-def measured_peak_int8():
-    """No int8 figure is written by the driver: the denominator is twice the measured bf16
-    burst throughput (int8 issues at twice the bf16 rate on this tensor core)."""
+def measured_peak_int8(ops=None):
+    """The int8 ceiling, measured in this run: the tensor pipe issuing 128 x 256 x 32 int8 MMAs
+    back to back on resident tiles, one CTA per SM, nothing loaded or stored (the driver's file of
+    measured peaks has bf16 only).  -> (TOP/s, how)."""
+    if ops is not None:
+        try:
+            return float(ops.i8_mma_issue_rate()), "measured here: tcgen05 kind::i8 issue loop on resident tiles, all SMs"
+        except Exception as ex:  # noqa: BLE001
+            print("int8 ceiling probe failed: %r" % (ex,), file=sys.stderr)
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         try:
-            return 2.0 * float(json.load(open(p))["bf16_tflops"]), "2 x measured bf16 burst"
+            return 2.0 * float(json.load(open(p))["bf16_tflops"]), "2 x measured bf16 burst (the probe did not run)"
         except Exception:
             pass
-    return 2.0 * 1590.0, "2 x fallback bf16"
+    return 2.0 * 1590.0, "2 x fallback bf16 (the probe did not run)"
 
 
 FC_M, FC_K, FC_N = 2048, 4096, 4096
@@ -416,13 +427,14 @@ def run_int8_fc_line(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(times[0]), float(times[1])
     if rank == 0:
-        peak, src = measured_peak_int8()
+        peak, src = measured_peak_int8(ops)
         tops = world * r["ops"] / (ms * 1e-3) / 1e12
         line = {"metric": "int8_fc_tops", "value": tops, "unit": "TOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "s8 x s8 -> s32", "data": "synthetic", "config": fc_config(),
                 "roofline": {"bound": "tensor", "achieved": r["tops"], "peak": peak, "unit": "TOP/s",
                              "frac": r["tops"] / peak, "peak_source": src, "nominal_dense_int8_tops": 4500.0,
+                             "frac_of_nominal": r["tops"] / 4500.0,
                              "library_int8_gemm_tops": r["library_int8_gemm_tops"],
                              # DRAM bytes per launch from the ncu capture in profiles/ (the 8 MB result stays in L2)
                              "traffic": 25.4e6,
@@ -638,7 +650,7 @@ def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges, as_ran
                                  "interaction; dense layers batch-sharded", "tables": 64, "batch": 4096}
 
 
-def resnet_measure(torch, dev, steps):
+def resnet_measure(torch, dev, steps, cpu_threads=0):
     """ResNet-50 v1.5, fully int8 channelwise-quantized, batch 64 at 224x224x3 (third benchmark
     configuration): images/s with the batch resident in HBM (CUDA-graph replay of the whole
     network) and end to end (fp32 NCHW batch from pinned host memory in, logits out)."""
@@ -695,13 +707,148 @@ def resnet_measure(torch, dev, steps):
     e2e_ms = pipe.timed(e2e, n_e2e) / n_e2e
     assert int(model.status.item()) == 0
     ops_per_batch = resnet.conv_ops_per_image(layers) * 64
-    return {"metric": "resnet50_int8_images_per_s", "value": 64 / (ms * 1e-3), "unit": "images/s", "ms_per_batch": ms,
+    cpu = None
+    if cpu_threads:
+        v, kind, sample = resnet_cpu_rate(layers, q, cpu_threads)
+        cpu = {"value": v, "unit": "images/s", "cores": cpu_threads, "kind": kind, "sample": sample}
+    return {"metric": "resnet50_int8_images_per_s", "cpu_baseline": cpu, "value": 64 / (ms * 1e-3), "unit": "images/s", "ms_per_batch": ms,
             "e2e_value": 64 / (e2e_ms * 1e-3), "e2e_ms_per_batch": e2e_ms, "h2d_bytes_per_step": host_x.numel() * 4,
             "d2h_bytes_per_step": out.numel() * 4, "launches_per_batch": launches,
             "effective_tops": ops_per_batch / (ms * 1e-3) / 1e12,
             "config": {"workload": "ResNet-50 v1.5 int8: channelwise symmetric filters (He-normal, BN folded), asymmetric "
                                    "int8 activations calibrated on 16 seeded N(0,1) images, int32 bias, batch 64 at "
                                    "224x224x3, every node on the library's kernels", "batch": 64}}
+
+
+def _cpu_kernels():
+    """The reference's libjit compiled here (fast-math build, as Glow ships it) when it was built,
+    else the plain-C port: an object with the kernel methods the two model walks below call."""
+    from oracle import oracle as orc
+    if orc.ref_available("fast"):
+        k = orc.LibjitRef("fast")
+        return k, "reference", k.channelwise_quantized_conv2d_i8_i32
+    orc.lib()
+    return orc, "port", orc.conv2d_i8_i32
+
+
+def resnet_cpu_rate(layers, q, threads, seconds=8.0):
+    """ResNet-50 int8 on the host through the reference's own kernels
+    (libjit_channelwise_quantized_conv2d_i8_i32, max/avg pool, element add, rowwise FC): one
+    224x224 image per host thread, all threads at once -- Glow's CPU backend runs one device per
+    core with the batch split (tests/benchmark/Bench.h:54-68).  -> (images/s, kind, sample)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from glow_b200 import ops
+    from oracle import oracle as orc
+    k, kind, conv_fn = _cpu_kernels()
+    tqp = q["tqp"]
+    # libjit's element-wise kernels (add, quantize) are per-element bodies that Glow's JIT wraps in
+    # a loop; compiled natively they have no loop of their own, so these two nodes run through the
+    # C restatement's loops (the same arithmetic, bit for bit) -- they are a few per cent of the time
+
+    def conv(name, t):
+        c = q["conv"][name]
+        spec = c["spec"]
+        kk, s, p = (spec["k"],) * 2, (spec["stride"],) * 2, (spec["pad"],) * 4
+        ohw = ops.conv_out_hw(t.shape[1:3], kk, s, p)
+        return conv_fn(t, c["filter"], c["bias"], ohw, kk, s, p, 1, (1, 1), c["out_offset"], c["in_offset"],
+                       c["filter_offsets"], c["bias_offsets"], c["params"][:3], c["params"][3:], 1 if spec["relu"] else 0, None)
+
+    def image(seed):
+        x = np.random.default_rng(seed).standard_normal((1, 224, 224, 3)).astype(np.float32)
+        x = orc.element_quantize_i8(x, *tqp["input"])
+        for l in layers:
+            if l[0] == "conv":
+                x = conv(l[1]["name"], x)
+            elif l[0] == "maxpool":
+                x = k.max_pool_i8(x, ops.conv_out_hw(x.shape[1:3], (3, 3), (2, 2), (1, 1, 1, 1)), (3, 3), (2, 2), (1, 1, 1, 1),
+                                  tqp["conv1"][1])
+            elif l[0] == "block":
+                y = x
+                for c in l[2]:
+                    y = conv(c["name"], y)
+                sc = conv(l[3]["name"], x) if l[3] else x
+                a = q["add"][l[1]]
+                out_off = tqp[a["out"]][1]
+                x = orc.element_add_i8(y, sc, out_off, tqp[a["lhs"]][1], tqp[a["rhs"]][1], a["lhs_triple"], a["rhs_triple"])
+                x = np.maximum(x, np.int8(out_off))  # Relu as max with the offset (CPUMaxSplat)
+            elif l[0] == "avgpool":
+                src, hw = q["avgpool_in"], x.shape[1]
+                tr = ops.quantize_scale_offset_32to8(np.float32(tqp[src][0]) / np.float32(tqp["avgpool"][0]) / np.float32(hw * hw))
+                x = k.avg_pool_i8(x, (1, 1), (hw, hw), (1, 1), (0, 0, 0, 0), True, tqp["avgpool"][1], tqp[src][1], tr)
+            elif l[0] == "fc":
+                f = q["fc"]
+                x = k.rowwise_quantized_fc_i8_i32(x.reshape(x.shape[0], -1), f["w"], f["bias"], f["w_offsets"], f["params"][:3],
+                                                  f["params"][3:], tqp["fc"][1], tqp[f["in_name"]][1], 0)
+        return x
+
+    with ThreadPoolExecutor(threads) as ex:
+        list(ex.map(image, range(threads)))  # warm-up pass
+        passes, t0 = 0, time.perf_counter()
+        while True:
+            list(ex.map(image, range(passes * threads, (passes + 1) * threads)))
+            passes += 1
+            dt = time.perf_counter() - t0
+            if dt >= seconds:
+                break
+    return passes * threads / dt, kind, "%d passes of %d images of 224x224x3 (one per host thread, batch 1 each) in %.1f s" % (
+        passes, threads, dt)
+
+
+def dlrm_cpu_rate(threads, sample=256, tables_timed=4):
+    """The recommendation model on the host through the reference's kernels, for a slice of
+    `sample` samples: FRWQ-SLS pooling of `tables_timed` of the 64 tables (one libjit call per
+    table, tables over the host threads; the cost is linear in the tables, so it is scaled to 64),
+    the int8 rowwise-FC MLPs (batch rows over the host threads) and the pairwise-dot interaction.
+    -> (samples/s, kind, sample description)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from glow_b200 import dlrm, ops
+    from oracle import oracle as orc
+    k, kind, _ = _cpu_kernels()
+    cfg = dlrm.DLRMConfig(batch=sample)
+    fm = dlrm.float_model(cfg)
+    qm = dlrm.quantize_model(cfg, fm, dlrm.fixed_ranges(cfg))
+    rng = np.random.default_rng(77)
+    tabs = []
+    for t in range(tables_timed):
+        tab = rng.integers(0, 256, (cfg.rows, cfg.dim + 8), dtype=np.uint8)
+        tab[:, cfg.dim:cfg.dim + 4] = rng.uniform(0.001, 0.01, cfg.rows).astype(np.float32).view(np.uint8).reshape(cfg.rows, 4)
+        tab[:, cfg.dim + 4:] = rng.uniform(-1, 1, cfg.rows).astype(np.float32).view(np.uint8).reshape(cfg.rows, 4)
+        tabs.append(tab)
+    dense, lengths, indices = dlrm.make_request(cfg, 31, tables=range(tables_timed))
+    dense = dense.numpy()
+    pool = k.frwq_slws if kind == "reference" else orc.frwq_slws_u8_f32
+
+    def pool_table(t):
+        idx = indices[t].numpy()
+        return pool(tabs[t], np.ones(len(idx), np.float32), idx, lengths[t].numpy())
+
+    pool_table(0)  # warm-up
+    t0 = time.perf_counter()
+    pooled_some = [pool_table(t) for t in range(tables_timed)]
+    # one libjit call per table on one thread each; 64 such calls spread over the host threads
+    t_pool = (time.perf_counter() - t0) / tables_timed * cfg.tables / min(threads, cfg.tables)
+    pooled = np.stack([pooled_some[t % tables_timed] for t in range(cfg.tables)], axis=1)  # [sample, 64, D]
+    t0 = time.perf_counter()
+    x = orc.element_quantize_i8(dense, *qm["dense_tqp"])
+    for fc in qm["bottom"]:
+        x = k.rowwise_quantized_fc_i8_i32(x, fc.w, fc.bias, fc.w_offsets, fc.params[:3], fc.params[3:], fc.out_offset,
+                                          fc.in_offset, 0, threads=threads)
+        if fc.relu:
+            x = np.maximum(x, np.int8(fc.out_offset))
+    last = qm["bottom"][-1]
+    x0 = (x.astype(np.float32) - np.float32(last.out_offset)) * np.float32(last.out_scale)
+    z = orc.pairwise_dot_interaction(x0, pooled.reshape(sample, -1).astype(np.float32))
+    y = orc.element_quantize_i8(z, *qm["interaction_tqp"])
+    for fc in qm["top"]:
+        y = k.rowwise_quantized_fc_i8_i32(y, fc.w, fc.bias, fc.w_offsets, fc.params[:3], fc.params[3:], fc.out_offset,
+                                          fc.in_offset, 0, threads=threads)
+        if fc.relu:
+            y = np.maximum(y, np.int8(fc.out_offset))
+    t_dense = time.perf_counter() - t0
+    return sample / (t_pool + t_dense), kind, (
+        "%d of 4096 samples: pooling of %d of the 64 tables timed one thread each and scaled to 64 tables over the host "
+        "threads (%.4f s), MLPs and interaction of the slice with the rows over the threads (%.3f s), %d host threads"
+        % (sample, tables_timed, t_pool, t_dense, threads))
 
 
 def run_model_line(args):
@@ -735,14 +882,19 @@ def run_model_line(args):
                         "h2d_bytes_per_step": best["h2d_bytes_per_step_per_rank"] * world,
                         "d2h_bytes_per_step": best["d2h_bytes_per_step_per_rank"] * world},
                 "gpu_launches": best["launches_per_step"] * max(10, args.steps)}
+        if rank == 0 and not args.no_cpu_baseline:
+            v, kind, sample = dlrm_cpu_rate(os.cpu_count() or 1)
+            line["cpu_baseline"] = {"value": v, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": kind, "sample": sample}
     else:
-        r = resnet_measure(torch, dev, max(5, args.steps))
+        r = resnet_measure(torch, dev, max(5, args.steps), 0 if args.no_cpu_baseline else (os.cpu_count() or 1))
         line = {"metric": r["metric"], "value": r["value"], "unit": r["unit"], "n_gpus": 1, "steps": max(5, args.steps),
                 "warmup": 3, "ms_per_step": r["ms_per_batch"], "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "s8 x s8 -> s32", "data": "synthetic", "config": r["config"],
                 "e2e": {"value": r["e2e_value"], "unit": r["unit"], "h2d_bytes_per_step": r["h2d_bytes_per_step"],
                         "d2h_bytes_per_step": r["d2h_bytes_per_step"]},
                 "effective_tops": r["effective_tops"], "gpu_launches": r["launches_per_batch"] * max(5, args.steps)}
+        if r.get("cpu_baseline"):
+            line["cpu_baseline"] = r["cpu_baseline"]
     line["clocks"] = sampler.stop()
     if rank == 0:
         print(json.dumps(line))
@@ -790,6 +942,59 @@ def slws4_cpu_rate(D, seconds, threads):
             if dt >= seconds:
                 break
     return moved / dt / 1e9, passes, dt
+
+
+def slws4_point(torch, ops, dev, D, table_gb, steps):
+    """One point of the 4-bit sweep for the default line's extras: the workload of --workload slws4
+    (10,000,000-row UInt4FusedFP16QTy tables, 8192 bags per table, Poisson(64) lengths, fp16 weights
+    and result) on a smaller set of tables (table_gb, still far larger than L2), device-resident."""
+    ROWS4, B = 10_000_000, 8192
+    line_bytes = D // 2 + 4
+    T = max(1, int(table_gb * 1e9 / (ROWS4 * line_bytes)))
+    g = torch.Generator(device=dev).manual_seed(0x610B200 + D)
+    tables = []
+    for k in range(T):
+        t = torch.randint(0, 256, (ROWS4, line_bytes), dtype=torch.uint8, device=dev, generator=g)
+        so = torch.stack([torch.empty(ROWS4, device=dev).uniform_(0.001, 0.01, generator=g),
+                          torch.empty(ROWS4, device=dev).uniform_(-1, 1, generator=g)], dim=1).to(torch.float16)
+        t[:, D // 2:] = so.view(torch.uint8).view(ROWS4, 4)
+        tables.append(t)
+    del so
+    out = torch.empty((T, B, D), dtype=torch.float16, device=dev)
+    status = ops.new_status(dev)
+    batches, nbytes = [], []
+    for r in range(2):
+        rng = np.random.Generator(np.random.PCG64(4242 + r))
+        lengths = rng.poisson(64, (T, B)).astype(np.int32)
+        starts = np.concatenate([[0], np.cumsum(lengths.sum(1))]).astype(np.int64)
+        total = int(starts[-1])
+        gi = torch.Generator(device=dev).manual_seed(99 + r)
+        indices = torch.randint(0, ROWS4, (total,), device=dev, generator=gi)
+        weights = torch.rand(total, device=dev, generator=gi).to(torch.float16)
+        lengths_d = torch.from_numpy(lengths).to(dev)
+        b = ops.SlwsBatch(ops.UINT4_FUSED_FP16, line_bytes, torch.int64, device=dev)
+        b.bind(tables, [weights[starts[k]:starts[k + 1]] for k in range(T)],
+               [indices[starts[k]:starts[k + 1]] for k in range(T)], [lengths_d[k] for k in range(T)],
+               [out[k] for k in range(T)])
+        batches.append(b)
+        nbytes.append(total * (line_bytes + 8 + 2) + T * B * (4 + 2 * D))
+    for i in range(3):
+        batches[i % 2].run(status)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        batches[i % 2].run(status)
+    e1.record()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ms = e0.elapsed_time(e1)
+    gbs = sum(nbytes[i % 2] for i in range(steps)) / (ms * 1e-3) / 1e9
+    peak, _ = measured_peak_hbm()
+    del tables, batches, out
+    torch.cuda.empty_cache()
+    return {"dim": D, "value": gbs, "unit": "GB/s", "frac": gbs / peak, "tables": T, "table_gb": T * ROWS4 * line_bytes / 1e9,
+            "us_per_launch": ms * 1e3 / steps}
 
 
 def run_slws4_line(args):
@@ -968,7 +1173,7 @@ def run_dyn_fc_line(args):
     if world > 1:
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
     if rank == 0:
-        peak, src = measured_peak_int8()
+        peak, src = measured_peak_int8(ops)
         per_gpu = 2.0 * M * N * K / (float(tm[0]) * 1e-3) / 1e12
         print(json.dumps({
             "metric": "dynamic_quantized_fc_tops", "value": per_gpu * world, "unit": "TOP/s", "n_gpus": world,
@@ -1522,9 +1727,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": peak_src,
                          "nominal_peak": 8000.0, "frac_of_nominal": achieved / 8000.0,
-                         # DRAM bytes per launch: bytes per gathered row measured by ncu on a 32-table
-                         # launch (dram__bytes_read.sum + dram__bytes_write.sum over its rows; traffic is
-                         # proportional to rows) x the rows of this launch
+                         # DRAM bytes per launch: bytes per gathered row from the ncu capture x the rows
                          "traffic": (None if args.row_bytes else NCU_DRAM_BYTES_PER_ROW * rows_per_launch),
                          "kernel": "slws_gather_select_kernel<8,0,0,long,2,4> (+ slws_segments_from_lengths_kernel, timed together)",
                          "launch_us": launch_us, "algorithmic_bytes_per_launch": moved / args.steps},
@@ -1543,15 +1746,31 @@ def main():
         if world == 1 and not args.no_extras:
             # secondary metric of the same benchmark definition: int8 FC throughput
             fc = int8_fc_measure(torch, ops, dev, max(10, min(args.steps, 50)), 3)
-            ipeak, isrc = measured_peak_int8()
+            ipeak, isrc = measured_peak_int8(ops)
             line.setdefault("extras", {})["int8_fc"] = {
                 "metric": "int8_fc_tops", "value": fc["tops"], "unit": "TOP/s", "us_per_launch": fc["ms"] * 1e3,
                 "e2e_value": fc["e2e_tops"], "config": fc_config(),
                 "roofline": {"bound": "tensor", "achieved": fc["tops"], "peak": ipeak, "frac": fc["tops"] / ipeak,
-                             "peak_source": isrc, "nominal_dense_int8_tops": 4500.0,
+                             "peak_source": isrc, "nominal_dense_int8_tops": 4500.0, "frac_of_nominal": fc["tops"] / 4500.0,
                              "library_int8_gemm_tops": fc["library_int8_gemm_tops"]}}
+            if not args.no_cpu_baseline:
+                tv, tkind, tsample = int8_fc_cpu_rate(4.0, os.cpu_count() or 1)
+                line["extras"]["int8_fc"]["cpu_baseline"] = {"value": tv, "unit": "TOP/s", "cores": os.cpu_count() or 1,
+                                                             "kind": tkind, "sample": tsample}
         if world == 1 and not args.no_extras:
-            line["extras"]["resnet50"] = resnet_measure(torch, dev, max(5, min(args.steps, 20)))
+            line["extras"]["resnet50"] = resnet_measure(torch, dev, max(5, min(args.steps, 20)),
+                                                        0 if args.no_cpu_baseline else (os.cpu_count() or 1))
+            # the 4-bit sweep, one short point per width (8 GB of tables each; the full-size points
+            # are --workload slws4 --dim D)
+            line["extras"]["slws_4bit_sweep"] = {
+                "metric": "frwq_slws_4bit_hbm_gbps",
+                "note": "UInt4FusedFP16QTy, 10,000,000-row tables, 8192 bags of Poisson(64) indices per table, fp16 "
+                        "weights and result, fp32 accumulation; 8 GB of tables per point, 10 launches",
+                "points": [slws4_point(torch, ops, dev, D, 8.0, 10) for D in (32, 64, 128, 256)]}
+        if dlrm_extra is not None and world == 1 and not args.no_cpu_baseline:
+            dv, dkind, dsample = dlrm_cpu_rate(os.cpu_count() or 1)
+            dlrm_extra["cpu_baseline"] = {"value": dv, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": dkind,
+                                          "sample": dsample}
         if world == 1 and not args.no_cpu_baseline:
             threads, S = cpu_threads, len(sample_tables)
             v, kind, passes, dt = cpu_reference_rate(sample_tables, args.cpu_seconds, threads)

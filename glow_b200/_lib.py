@@ -51,6 +51,7 @@ SIGNATURES = {
     "glowb200_quantize_bias_i32": (_int, [_vp, _i64, _f32, _i32, _vp]),
     "glowb200_channelwise_conv_prepare": (_int, [_vp, _vp, _i64, _i64, _f32, _int] + [_vp] * 6),
     "glowb200_wait_limit_selftest": (_int, [_i64, _vp, _vp, _vp]),
+    "glowb200_i8_mma_issue_probe": (_int, [_i64, _vp, _vp, _vp]),
     "glowb200_i8_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "glowb200_i8_row_sums": (_int, [_vp, _i64, _i64, _vp, _vp]),
     "glowb200_rowwise_quantized_fc_i8_i32": (

@@ -200,6 +200,55 @@ __host__ __device__ constexpr uint32_t idesc_i8(int m, int n) {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// The tensor pipe's own int8 rate, measured rather than quoted: every CTA (one per SM) issues
+// `mmas` 128 x 256 x 32 int8 MMAs back to back on operand tiles that already sit in shared
+// memory (their contents do not matter to the timing), into two alternating accumulators in
+// tensor memory, then waits -- bounded -- for the last one.  Nothing is loaded, drained or
+// stored, so the time of a launch is what the MMA pipe itself needs under full load at the
+// clocks the GPU holds: the ceiling a contraction kernel is measured against.
+__global__ void __launch_bounds__(128) i8_mma_issue_probe_kernel(int mmas, int32_t *status) {
+  extern __shared__ __align__(1024) uint8_t probe_smem[];
+  __shared__ uint64_t done_bar;
+  __shared__ uint32_t tmem_base;
+  __shared__ int abort_flag_storage;
+  volatile int *abort_flag = &abort_flag_storage;
+  uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(probe_smem) + 1023) & ~(uintptr_t)1023);
+  constexpr int kN = 256;
+  if (threadIdx.x == 0) {
+    mbar_init(&done_bar, 1);
+    abort_flag_storage = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // defined operand bytes (the values are irrelevant, but nothing reads uninitialised memory)
+  for (int i = threadIdx.x; i < (kBlockM + kN) * kBlockK / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(tiles)[i] = 0x01020304u * (uint32_t)(i + 1);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (threadIdx.x < 32) {
+    tmem_alloc(&tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  bool ok = true;
+  if (threadIdx.x == 0) {
+    const uint32_t a_addr = smem_u32(tiles), b_addr = a_addr + kBlockM * kBlockK;
+    const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
+    constexpr uint32_t idesc = idesc_i8(kBlockM, kN);
+    for (int i = 0; i < mmas; i++) {
+      const int k = i & 3;  // the four 32-byte k steps of the 128-byte tile rows
+      umma_i8(tmem_base + (uint32_t)((i >> 2) & 1) * kN, a_desc + (uint64_t)(k * kUmmaK >> 4), b_desc + (uint64_t)(k * kUmmaK >> 4),
+              idesc, k != 0);
+    }
+    umma_commit(&done_bar);
+    ok = mbar_wait(&done_bar, 0, abort_flag);
+    if (!ok && status != nullptr) atomicOr(status, GLOWB200_STATUS_WAIT_TIMEOUT);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (threadIdx.x < 32) tmem_dealloc(tmem_base, 512);
+}
+
 // Optional phase tracing for tuning builds (-DGLOWB200_GEMM_TRACE): CTA 0 writes globaltimer
 // stamps to a device buffer the tuning harness reads back.  Compiled out by default.
 #ifdef GLOWB200_GEMM_TRACE
@@ -805,6 +854,18 @@ extern "C" size_t glowb200_i8_gemm_workspace_bytes(int64_t M, int64_t K, int64_t
   if (M < 0 || N < 0 || K < 0) return 0;
   // row sums of both operands + room for a transposed copy of a [K, N] right-hand side
   return align_up((size_t)N * 4, 256) + align_up((size_t)M * 4, 256) + align_up((size_t)N * (size_t)K, 256);
+}
+
+extern "C" int glowb200_i8_mma_issue_probe(int64_t mmas_per_sm, int64_t *ops_per_launch, int32_t *status,
+                                           glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(mmas_per_sm > 0 && mmas_per_sm <= (1 << 24), "mmas_per_sm must be in (0, 2^24]");
+  const int sms = sm_count();
+  const int smem = (kBlockM + 256) * kBlockK + 1024;
+  GLOWB200_CUDA_OK(cudaFuncSetAttribute(i8_mma_issue_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  i8_mma_issue_probe_kernel<<<sms, 128, smem, reinterpret_cast<cudaStream_t>(stream)>>>((int)mmas_per_sm, status);
+  GLOWB200_CUDA_OK(cudaGetLastError());
+  if (ops_per_launch) *ops_per_launch = (int64_t)sms * mmas_per_sm * 2 * kBlockM * 256 * kUmmaK;
+  return GLOWB200_OK;
 }
 
 extern "C" int glowb200_wait_limit_selftest(int64_t limit_cycles, int32_t *status, int32_t *waiters_that_gave_up,

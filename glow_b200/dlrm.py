@@ -294,7 +294,9 @@ class DLRMRank:
         else:
             self.slabs = [torch.empty((per, T, D), dtype=torch.float32, device=dev) for _ in range(2)]
         if exchange == "nccl":
+            # send: bags grouped by destination rank; recv: one [per, T_r, D] block from every rank
             self.send = torch.empty((world, per, len(self.my_tables), D), dtype=torch.float32, device=dev)
+            self.recv = torch.empty((per * T * D,), dtype=torch.float32, device=dev)
 
     def connect_peers(self):
         """fused exchange: swap IPC handles of the receive slabs with every rank."""
@@ -344,7 +346,16 @@ class DLRMRank:
         import torch.distributed as dist
         bound.run(self.status)
         if self.exchange == "nccl":
-            self.slabs[slab].copy_(exchange_all_to_all(self.send, self.cfg, self.rank, self.world, self.group))
+            T, D, tl = self.cfg.tables, self.cfg.dim, len(self.my_tables)
+            if T % self.world == 0:
+                # every buffer exists already and nothing below touches the host, so the step can be
+                # captured in a CUDA graph like the fused form: equal blocks out, equal blocks in,
+                # then one strided copy puts table j of rank r at column j * world + r
+                dist.all_to_all_single(self.recv, self.send.view(-1), group=self.group)
+                self.slabs[slab].view(self.per, tl, self.world, D).copy_(
+                    self.recv.view(self.world, self.per, tl, D).permute(1, 2, 0, 3))
+            else:
+                self.slabs[slab].copy_(exchange_all_to_all(self.send, self.cfg, self.rank, self.world, self.group))
         elif self.exchange == "fused":
             # every rank's stores into every slab are complete once all pooling kernels have
             # finished: a one-element all-reduce, enqueued on the stream, is that rendezvous (it

@@ -387,6 +387,22 @@ def wait_limit_selftest(limit_cycles, status):
     return gave_up
 
 
+def i8_mma_issue_rate(mmas_per_sm=32768, repeats=4, status=None):
+    """TOP/s of the tensor pipe issuing int8 MMAs on resident tiles (best of `repeats` launches,
+    device-timed): the measured ceiling an int8 contraction is compared with."""
+    ops_out = C.c_int64(0)
+    best = 0.0
+    for i in range(repeats + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        check(_lib.lib().glowb200_i8_mma_issue_probe(int(mmas_per_sm), C.byref(ops_out), _p(status), _stream()))
+        e1.record()
+        e1.synchronize()
+        if i:  # the first launch warms up
+            best = max(best, ops_out.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best
+
+
 def i8_gemm_workspace_bytes(M, K, N):
     return int(_lib.lib().glowb200_i8_gemm_workspace_bytes(int(M), int(K), int(N)))
 

@@ -354,6 +354,15 @@ int glowb200_channelwise_conv_prepare(const float *filter, const float *bias, in
 int glowb200_wait_limit_selftest(int64_t limit_cycles, int32_t *status, int32_t *waiters_that_gave_up,
                                  glowb200_stream_t stream);
 
+/* The int8 rate of the tensor pipe itself, for use as a roofline denominator: one CTA per SM
+ * issues `mmas_per_sm` 128 x 256 x 32 int8 MMAs back to back on operand tiles resident in shared
+ * memory (no loads, no epilogue) and waits, bounded, for the last.  *ops_per_launch (host, may be
+ * NULL) receives the integer operations of one launch (2 per multiply-add); the caller times the
+ * launch with events.  The reference defines the metric, not a ceiling
+ * (tests/benchmark/Int8GemmBench.h:222-224); no reference counterpart. */
+int glowb200_i8_mma_issue_probe(int64_t mmas_per_sm, int64_t *ops_per_launch, int32_t *status,
+                                glowb200_stream_t stream);
+
 /* Scratch bytes the three entry points below may need for an [M,K] x [N,K]^T problem. */
 size_t glowb200_i8_gemm_workspace_bytes(int64_t M, int64_t K, int64_t N);
 
