@@ -88,6 +88,8 @@ SIGNATURES = {
     "glowb200_function_destroy": (None, [_vp]),
     "glowb200_function_add_symbol": (_int, [_vp, C.c_char_p, _int, _sz, _vp]),
     "glowb200_function_add_instruction": (_int, [_vp, _int, _vp, _int, _vp, _int, _vp, _int]),
+    "glowb200_function_batched_pooling_launches": (_int, [_vp]),
+    "glowb200_function_add_instruction_views": (_int, [_vp, _int, _vp, _vp, _int, _vp, _int, _vp, _int]),
     "glowb200_function_compile": (_int, [_vp]),
     "glowb200_function_constant_bytes": (_sz, [_vp]),
     "glowb200_device_manager_create": (_vp, [_int, C.c_uint64]),
@@ -96,6 +98,11 @@ SIGNATURES = {
     "glowb200_device_manager_evict_network": (_int, [_vp, C.c_char_p]),
     "glowb200_device_manager_run_function": (_int, [_vp, C.c_char_p, _vp, _vp, _vp, _int]),
     "glowb200_device_manager_run_function_io": (_int, [_vp, C.c_char_p, _vp, _vp, _vp, _vp, _int]),
+    "glowb200_device_manager_set_context_count": (_int, [_vp, _int]),
+    "glowb200_device_manager_run_function_async": (_int, [_vp, C.c_char_p, _vp, _vp, _vp, _vp, _int, _vp]),
+    "glowb200_device_manager_wait": (_int, [_vp, _i64]),
+    "glowb200_device_manager_allocate_io_buffer": (_vp, [_vp, C.c_size_t]),
+    "glowb200_device_manager_free_io_buffer": (None, [_vp, _vp]),
     "glowb200_device_manager_placeholder_address": (_int, [_vp, C.c_char_p, C.c_char_p, _vp, _vp]),
     "glowb200_device_manager_transfer_static_placeholder": (_int, [_vp, C.c_char_p, C.c_char_p, _vp, _sz]),
     "glowb200_device_manager_run_function_resident": (_int, [_vp, C.c_char_p]),

@@ -36,7 +36,11 @@ namespace {
 using glowb200::align_up;
 using glowb200::set_error;
 
-enum SymbolKind { kConstant = 0, kPlaceholder = 1, kActivation = 2 };
+// kStatic: a placeholder that is written once and then stays put (Placeholder::isStatic: the
+// embedding tables of a recommendation model).  It lives beside the constants, shared by all
+// execution contexts of a network; ordinary placeholders and activations exist once per context.
+enum SymbolKind { kConstant = 0, kPlaceholder = 1, kActivation = 2, kStatic = 3 };
+constexpr int kSlabs = 4;
 
 struct Symbol {
   std::string name;
@@ -48,6 +52,9 @@ struct Symbol {
 struct Instruction {
   int kind;
   std::vector<int> ops;       // symbol ids
+  std::vector<int64_t> off;   // byte offset of each operand inside its symbol (a view of a larger tensor)
+  int group = -1;             // FRWQ_SLWS: index of the batched launch this instruction is part of
+  bool group_leader = false;  // ... and whether it is the one that launches it
   std::vector<int64_t> ia;    // integer attributes
   std::vector<float> fa;      // float attributes
   std::vector<int> derived;   // ids of constants compile() added (triples, row sums ...)
@@ -60,8 +67,10 @@ struct glowb200_function {
   std::vector<Symbol> symbols;
   std::vector<Instruction> instrs;
   bool compiled = false;
-  size_t slab_bytes[3] = {0, 0, 0};
+  size_t slab_bytes[kSlabs] = {0, 0, 0, 0};
   size_t workspace_bytes = 0;
+  // Runs of pooling instructions that become ONE batched launch each: their members, in order.
+  std::vector<std::vector<int>> slws_groups;
   std::map<std::string, int> by_name;
 
   int add_symbol(const std::string &n, int kind, size_t bytes, const void *data) {
@@ -83,10 +92,24 @@ struct glowb200_function {
 
 namespace {
 
+// One execution context of a loaded network (Backend::getContextCount / bindContexts,
+// include/glow/Backend/Backend.h:272-276): its own placeholders and activations, so that the
+// inputs of the next request can arrive while this one runs and the last one's results leave.
+struct Context {
+  uint8_t *slab[kSlabs] = {nullptr, nullptr, nullptr, nullptr};  // [kConstant], [kStatic]: the network's, shared
+  uint8_t *workspace = nullptr;
+  int32_t *status_dev = nullptr;
+  int32_t *status_host = nullptr;      // pinned
+  std::vector<glowb200_slws_job *> jobs;  // device descriptor arrays, one per batched pooling launch
+  cudaEvent_t in_done = nullptr, run_done = nullptr, out_done = nullptr;
+  int64_t ticket = 0;                  // the request in flight on this context (0: none)
+};
+
 struct LoadedNetwork {
   glowb200_function *fn;
-  uint8_t *slab[3] = {nullptr, nullptr, nullptr};
-  uint8_t *workspace = nullptr;
+  uint8_t *shared[2] = {nullptr, nullptr};  // constants, static placeholders
+  std::vector<Context> ctx;
+  size_t next_ctx = 0;
   size_t device_bytes = 0;
 };
 
@@ -123,7 +146,7 @@ extern "C" glowb200_function *glowb200_function_create(const char *name) {
 extern "C" void glowb200_function_destroy(glowb200_function *f) { delete f; }
 
 extern "C" int glowb200_function_add_symbol(glowb200_function *f, const char *name, int kind, size_t bytes, const void *host_data) {
-  if (!f || !name || f->compiled || kind < 0 || kind > 2 || (kind == kConstant) != (host_data != nullptr)) {
+  if (!f || !name || f->compiled || kind < 0 || kind >= kSlabs || (kind == kConstant) != (host_data != nullptr)) {
     set_error(GLOWB200_RUNTIME_ERROR, "bad symbol '%s'", name ? name : "?");
     return -1;
   }
@@ -135,12 +158,23 @@ extern "C" int glowb200_function_add_symbol(glowb200_function *f, const char *na
 extern "C" int glowb200_function_add_instruction(glowb200_function *f, int kind, const int32_t *operands, int num_operands,
                                                  const int64_t *int_attrs, int num_int_attrs, const float *float_attrs,
                                                  int num_float_attrs) {
+  return glowb200_function_add_instruction_views(f, kind, operands, nullptr, num_operands, int_attrs, num_int_attrs,
+                                                 float_attrs, num_float_attrs);
+}
+
+extern "C" int glowb200_function_add_instruction_views(glowb200_function *f, int kind, const int32_t *operands,
+                                                       const int64_t *operand_byte_offsets, int num_operands,
+                                                       const int64_t *int_attrs, int num_int_attrs, const float *float_attrs,
+                                                       int num_float_attrs) {
   if (!f || f->compiled) return set_error(GLOWB200_RUNTIME_ERROR, "function is NULL or already compiled");
   Instruction in;
   in.kind = kind;
   for (int i = 0; i < num_operands; i++) {
     if (operands[i] < -1 || operands[i] >= (int)f->symbols.size()) return set_error(GLOWB200_RUNTIME_ERROR, "operand %d: no such symbol", i);
+    const int64_t o = operand_byte_offsets ? operand_byte_offsets[i] : 0;
+    if (o < 0 || (operands[i] < 0 && o != 0)) return set_error(GLOWB200_RUNTIME_ERROR, "operand %d: bad byte offset", i);
     in.ops.push_back(operands[i]);
+    in.off.push_back(o);
   }
   in.ia.assign(int_attrs, int_attrs + num_int_attrs);
   in.fa.assign(float_attrs, float_attrs + num_float_attrs);
@@ -283,9 +317,9 @@ int validate_instruction(const glowb200_function *f, const Instruction &in, size
       continue;
     }
     const Symbol &s = f->symbols[id];
-    if ((int64_t)s.bytes < n.bytes)
-      return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: operand %d ('%s', %zu bytes) is smaller than the %lld bytes the instruction addresses",
-                       ii, n.op, s.name.c_str(), s.bytes, (long long)n.bytes);
+    if ((int64_t)s.bytes < in.off[n.op] + n.bytes)
+      return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: operand %d ('%s', %zu bytes) is smaller than the %lld bytes the instruction addresses at offset %lld",
+                       ii, n.op, s.name.c_str(), s.bytes, (long long)n.bytes, (long long)in.off[n.op]);
     if (n.op == 0 && s.kind == kConstant) return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: the destination '%s' is a constant", ii, s.name.c_str());
   }
   return GLOWB200_OK;
@@ -496,6 +530,62 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
       default: return set_error(GLOWB200_RUNTIME_ERROR, "instruction %zu: unsupported kind %d (isOpSupported would refuse the node)", ii, in.kind);
     }
   }
+  // Pooling instructions that follow one another, read the same kind of table with the same row
+  // width and do not feed each other become ONE batched launch (a recommendation model's tables
+  // are so many independent SparseLengthsSum nodes): the descriptors are built when the network
+  // is loaded.  The batched kernels want 16-byte aligned operands; views at other offsets stay
+  // single launches.
+  {
+    auto groupable = [&](const Instruction &in) {
+      if (in.kind != GLOWB200_INSTR_FRWQ_SLWS) return false;
+      for (int64_t o : in.off)
+        if (o % 16) return false;
+      return true;
+    };
+    auto same_shape = [](const Instruction &a, const Instruction &b) {
+      return a.ia[0] == b.ia[0] && a.ia[2] == b.ia[2] && a.ia[3] == b.ia[3] && a.ia[6] == b.ia[6] && a.ia[7] == b.ia[7] &&
+             a.ia[8] == b.ia[8];
+    };
+    size_t i = 0;
+    while (i < f->instrs.size()) {
+      if (!groupable(f->instrs[i])) { i++; continue; }
+      std::vector<int> members{(int)i};
+      size_t j = i + 1;
+      for (; j < f->instrs.size() && groupable(f->instrs[j]) && same_shape(f->instrs[i], f->instrs[j]); j++) {
+        // an earlier member must not write what this one reads, nor the bytes it writes
+        auto dest_range = [](const Instruction &in, int64_t &lo, int64_t &hi) {
+          lo = in.off[0];
+          hi = lo + in.ia[4] * in.ia[3] * (in.ia[7] ? 2 : 4);
+        };
+        bool feeds = false;
+        const Instruction &cand = f->instrs[j];
+        for (int m : members) {
+          const Instruction &prev = f->instrs[m];
+          for (size_t o = 1; o < cand.ops.size(); o++) feeds = feeds || cand.ops[o] == prev.ops[0];
+          for (size_t o = 1; o < prev.ops.size(); o++) feeds = feeds || prev.ops[o] == cand.ops[0];
+          if (cand.ops[0] == prev.ops[0]) {
+            int64_t a0, a1, b0, b1;
+            dest_range(cand, a0, a1);
+            dest_range(prev, b0, b1);
+            feeds = feeds || (a0 < b1 && b0 < a1);
+          }
+        }
+        if (feeds) break;
+        members.push_back((int)j);
+      }
+      if (members.size() > 1 && members.size() <= 65535) {
+        int64_t max_segments = 0;
+        for (int m : members) {
+          f->instrs[m].group = (int)f->slws_groups.size();
+          max_segments = std::max(max_segments, f->instrs[m].ia[4]);
+        }
+        f->instrs[members[0]].group_leader = true;
+        ws = std::max(ws, glowb200_slws_workspace_bytes(max_segments, (int64_t)members.size()));
+        f->slws_groups.push_back(members);
+      }
+      i = j;
+    }
+  }
   // slab offsets: 64-byte alignment like glow::TensorAlignment (include/glow/Support/Memory.h:29)
   for (Symbol &s : f->symbols) {
     s.offset = f->slab_bytes[s.kind];
@@ -507,6 +597,9 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
 }
 
 extern "C" size_t glowb200_function_constant_bytes(const glowb200_function *f) { return f ? f->slab_bytes[kConstant] : 0; }
+extern "C" int glowb200_function_batched_pooling_launches(const glowb200_function *f) {
+  return (f && f->compiled) ? (int)f->slws_groups.size() : 0;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Device manager
@@ -515,8 +608,12 @@ struct glowb200_device_manager {
   int device = 0;
   uint64_t max_memory = 0, used_memory = 0;
   bool running = false;
-  cudaStream_t stream = nullptr;
-  int32_t *status_dev = nullptr;
+  cudaStream_t stream = nullptr;      // kernels
+  cudaStream_t in_stream = nullptr;   // host-to-device copies of asynchronous requests
+  cudaStream_t out_stream = nullptr;  // device-to-host copies of asynchronous requests
+  int contexts = 1;                   // execution contexts every network is loaded with
+  int64_t next_ticket = 1;
+  std::map<int64_t, int> finished;    // results of requests that were completed on behalf of a later one
   std::map<std::string, LoadedNetwork> networks;
   std::mutex lock;
 };
@@ -541,9 +638,9 @@ extern "C" int glowb200_device_manager_init(glowb200_device_manager *dm) {
     dm->max_memory = fr;
   }
   if (cudaStreamCreateWithFlags(&dm->stream, cudaStreamNonBlocking) != cudaSuccess ||
-      cudaMalloc(&dm->status_dev, 4) != cudaSuccess)
-    return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "cannot create stream / status word on device %d", dm->device);
-  cudaMemsetAsync(dm->status_dev, 0, 4, dm->stream);
+      cudaStreamCreateWithFlags(&dm->in_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&dm->out_stream, cudaStreamNonBlocking) != cudaSuccess)
+    return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "cannot create the streams of device %d", dm->device);
   dm->running = true;
   return GLOWB200_OK;
 }
@@ -557,8 +654,28 @@ extern "C" int glowb200_device_manager_is_memory_available(glowb200_device_manag
 }
 
 static void free_network(LoadedNetwork &n) {
-  for (auto &p : n.slab) if (p) cudaFree(p);
-  if (n.workspace) cudaFree(n.workspace);
+  for (auto &p : n.shared) if (p) cudaFree(p);
+  for (Context &c : n.ctx) {
+    if (c.slab[kPlaceholder]) cudaFree(c.slab[kPlaceholder]);
+    if (c.slab[kActivation]) cudaFree(c.slab[kActivation]);
+    if (c.workspace) cudaFree(c.workspace);
+    if (c.status_dev) cudaFree(c.status_dev);
+    if (c.status_host) cudaFreeHost(c.status_host);
+    for (auto *j : c.jobs) if (j) cudaFree(j);
+    if (c.in_done) cudaEventDestroy(c.in_done);
+    if (c.run_done) cudaEventDestroy(c.run_done);
+    if (c.out_done) cudaEventDestroy(c.out_done);
+  }
+  n.ctx.clear();
+}
+
+// Number of execution contexts networks are loaded with from now on (1 by default: one set of
+// placeholders and activations, requests one after the other).
+extern "C" int glowb200_device_manager_set_context_count(glowb200_device_manager *dm, int contexts) {
+  if (!dm || contexts < 1 || contexts > 8) return set_error(GLOWB200_RUNTIME_ERROR, "context count must be in [1, 8]");
+  std::lock_guard<std::mutex> g(dm->lock);
+  dm->contexts = contexts;
+  return GLOWB200_OK;
 }
 
 // addNetwork: name must be new, the network must fit the memory budget; uploads the constants.
@@ -568,20 +685,54 @@ extern "C" int glowb200_device_manager_add_network(glowb200_device_manager *dm, 
   if (!dm->running) return set_error(GLOWB200_RUNTIME_ERROR, "device manager is not initialised");
   if (!f->compiled) return set_error(GLOWB200_RUNTIME_ERROR, "function %s is not compiled", f->name.c_str());
   if (dm->networks.count(f->name)) return set_error(GLOWB200_RUNTIME_ERROR, "Failed to add network: already have a function called %s", f->name.c_str());
-  const uint64_t total = f->slab_bytes[0] + f->slab_bytes[1] + f->slab_bytes[2] + f->workspace_bytes;
+  size_t jobs_bytes = 0;
+  for (const auto &grp : f->slws_groups) jobs_bytes += align_up(grp.size() * sizeof(glowb200_slws_job), 256);
+  const uint64_t per_context = f->slab_bytes[kPlaceholder] + f->slab_bytes[kActivation] + f->workspace_bytes + jobs_bytes + 256;
+  const uint64_t total = f->slab_bytes[kConstant] + f->slab_bytes[kStatic] + (uint64_t)dm->contexts * per_context;
   if (dm->used_memory + total > dm->max_memory) return set_error(GLOWB200_RUNTIME_OUT_OF_DEVICE_MEMORY, "Failed to add network: not enough memory");
   cudaSetDevice(dm->device);
   LoadedNetwork n;
   n.fn = f;
   n.device_bytes = total;
   bool ok = true;
-  for (int k = 0; k < 3 && ok; k++)
-    if (f->slab_bytes[k]) ok = cudaMalloc(&n.slab[k], f->slab_bytes[k]) == cudaSuccess;
-  if (ok) ok = cudaMalloc(&n.workspace, f->workspace_bytes) == cudaSuccess;
+  if (f->slab_bytes[kConstant]) ok = cudaMalloc(&n.shared[0], f->slab_bytes[kConstant]) == cudaSuccess;
+  if (ok && f->slab_bytes[kStatic]) ok = cudaMalloc(&n.shared[1], f->slab_bytes[kStatic]) == cudaSuccess;
+  n.ctx.resize(dm->contexts);
+  for (Context &c : n.ctx) {
+    if (!ok) break;
+    c.slab[kConstant] = n.shared[0];
+    c.slab[kStatic] = n.shared[1];
+    if (f->slab_bytes[kPlaceholder]) ok = ok && cudaMalloc(&c.slab[kPlaceholder], f->slab_bytes[kPlaceholder]) == cudaSuccess;
+    if (f->slab_bytes[kActivation]) ok = ok && cudaMalloc(&c.slab[kActivation], f->slab_bytes[kActivation]) == cudaSuccess;
+    ok = ok && cudaMalloc(&c.workspace, f->workspace_bytes) == cudaSuccess;
+    ok = ok && cudaMalloc(&c.status_dev, 4) == cudaSuccess && cudaMemsetAsync(c.status_dev, 0, 4, dm->stream) == cudaSuccess;
+    ok = ok && cudaMallocHost(&c.status_host, 4) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&c.in_done, cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&c.run_done, cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&c.out_done, cudaEventDisableTiming) == cudaSuccess;
+    // descriptors of the batched pooling launches: device addresses of this context's operands
+    for (const auto &grp : f->slws_groups) {
+      if (!ok) break;
+      std::vector<glowb200_slws_job> jobs(grp.size());
+      for (size_t k = 0; k < grp.size(); k++) {
+        const Instruction &in = f->instrs[grp[k]];
+        auto at = [&](int o) -> uint8_t * { const Symbol &sy = f->symbols[in.ops[o]]; return c.slab[sy.kind] + sy.offset + in.off[o]; };
+        glowb200_slws_job &j = jobs[k];
+        memset(&j, 0, sizeof(j));
+        j.dest = at(0); j.data = at(1); j.weights = at(2); j.indices = at(3);
+        j.lengths = reinterpret_cast<const int32_t *>(at(4));
+        j.rows = in.ia[1]; j.num_indices = in.ia[5]; j.dest_stride = in.ia[3]; j.segments = in.ia[4];
+      }
+      glowb200_slws_job *dj = nullptr;
+      ok = cudaMalloc(&dj, jobs.size() * sizeof(glowb200_slws_job)) == cudaSuccess &&
+           cudaMemcpy(dj, jobs.data(), jobs.size() * sizeof(glowb200_slws_job), cudaMemcpyHostToDevice) == cudaSuccess;
+      c.jobs.push_back(dj);
+    }
+  }
   if (ok)
     for (const Symbol &s : f->symbols)
       if (s.kind == kConstant && s.bytes)
-        ok = ok && cudaMemcpyAsync(n.slab[0] + s.offset, s.host.data(), s.bytes, cudaMemcpyHostToDevice, dm->stream) == cudaSuccess;
+        ok = ok && cudaMemcpyAsync(n.shared[0] + s.offset, s.host.data(), s.bytes, cudaMemcpyHostToDevice, dm->stream) == cudaSuccess;
   if (ok) ok = cudaStreamSynchronize(dm->stream) == cudaSuccess;
   if (!ok) {
     free_network(n);
@@ -589,7 +740,7 @@ extern "C" int glowb200_device_manager_add_network(glowb200_device_manager *dm, 
     return set_error(GLOWB200_RUNTIME_OUT_OF_DEVICE_MEMORY, "Failed to add network: device allocation or upload failed");
   }
   dm->used_memory += total;
-  dm->networks[f->name] = n;
+  dm->networks[f->name] = std::move(n);
   return GLOWB200_OK;
 }
 
@@ -599,7 +750,9 @@ extern "C" int glowb200_device_manager_evict_network(glowb200_device_manager *dm
   auto it = dm->networks.find(name);
   if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Could not find function with name %s to evict", name);
   cudaSetDevice(dm->device);
+  cudaStreamSynchronize(dm->in_stream);
   cudaStreamSynchronize(dm->stream);
+  cudaStreamSynchronize(dm->out_stream);
   free_network(it->second);
   dm->used_memory -= it->second.device_bytes;
   dm->networks.erase(it);
@@ -611,14 +764,17 @@ extern "C" int glowb200_device_manager_stop(glowb200_device_manager *dm) {
   std::lock_guard<std::mutex> g(dm->lock);
   if (!dm->running) return GLOWB200_OK;
   cudaSetDevice(dm->device);
+  cudaStreamSynchronize(dm->in_stream);
   cudaStreamSynchronize(dm->stream);
+  cudaStreamSynchronize(dm->out_stream);
   for (auto &kv : dm->networks) free_network(kv.second);
   dm->networks.clear();
+  dm->finished.clear();
   dm->used_memory = 0;
-  cudaFree(dm->status_dev);
   cudaStreamDestroy(dm->stream);
-  dm->status_dev = nullptr;
-  dm->stream = nullptr;
+  cudaStreamDestroy(dm->in_stream);
+  cudaStreamDestroy(dm->out_stream);
+  dm->stream = dm->in_stream = dm->out_stream = nullptr;
   dm->running = false;
   return GLOWB200_OK;
 }
@@ -632,31 +788,48 @@ extern "C" void glowb200_device_manager_destroy(glowb200_device_manager *dm) {
 
 namespace {
 
-int execute(glowb200_device_manager *dm, LoadedNetwork &n) {
+int execute(glowb200_device_manager *dm, LoadedNetwork &n, Context &c) {
   glowb200_function *f = n.fn;
-  auto ptr = [&](int id) -> void * {
+  auto ptr = [&](int id) -> void * {  // a whole symbol (the constants compile() derived)
     if (id < 0) return nullptr;
     const Symbol &s = f->symbols[id];
-    return n.slab[s.kind] + s.offset;
+    return c.slab[s.kind] + s.offset;
   };
   void *st = dm->stream;
   for (size_t ii = 0; ii < f->instrs.size(); ii++) {
     const Instruction &in = f->instrs[ii];
     const auto &a = in.ia;
+    auto P = [&](int o) -> void * {  // operand o: its symbol's address plus the view's offset
+      const int id = in.ops[o];
+      if (id < 0) return nullptr;
+      const Symbol &s = f->symbols[id];
+      return c.slab[s.kind] + s.offset + in.off[o];
+    };
     int rc = GLOWB200_OK;
     switch (in.kind) {
       case GLOWB200_INSTR_FRWQ_SLWS:
+        if (in.group >= 0) {  // part of a batched launch: the first member launches it for all
+          if (in.group_leader) {
+            const auto &grp = f->slws_groups[in.group];
+            int64_t max_segments = 0;
+            for (int m : grp) max_segments = std::max(max_segments, f->instrs[m].ia[4]);
+            rc = glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_batched(
+                c.jobs[in.group], (int64_t)grp.size(), max_segments, (int)a[0], (int)a[6], a[2], a[3], (int)a[7], (int)a[8],
+                c.workspace, f->workspace_bytes, c.status_dev, st);
+          }
+          break;
+        }
         rc = glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
-            ptr(in.ops[0]), ptr(in.ops[1]), (int)a[0], a[1], ptr(in.ops[2]), ptr(in.ops[3]), (int)a[6],
-            (const int32_t *)ptr(in.ops[4]), a[4], a[5], a[2], a[3], (int)a[7], (int)a[8], n.workspace, f->workspace_bytes,
-            dm->status_dev, st);
+            P(0), P(1), (int)a[0], a[1], P(2), P(3), (int)a[6],
+            (const int32_t *)P(4), a[4], a[5], a[2], a[3], (int)a[7], (int)a[8], c.workspace, f->workspace_bytes,
+            c.status_dev, st);
         break;
       case GLOWB200_INSTR_RWQ_FC: {
         auto d = [&](int i) { return (const int32_t *)ptr(in.derived[i]); };
         rc = glowb200_rowwise_quantized_fc_i8_i32(
-            (int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]), (const int32_t *)ptr(in.ops[5]),
-            (const int32_t *)ptr(in.ops[4]), d(0), d(1), d(2), d(3), d(4), d(5), a[0], a[1], a[2], (int32_t)a[5], (int32_t)a[3],
-            (int32_t)a[4], d(6), a[6] ? GLOWB200_FC_FUSE_RELU : 0, n.workspace, f->workspace_bytes, dm->status_dev, st);
+            (int8_t *)P(0), (const int8_t *)P(1), (const int8_t *)P(2), (const int32_t *)P(5),
+            (const int32_t *)P(4), d(0), d(1), d(2), d(3), d(4), d(5), a[0], a[1], a[2], (int32_t)a[5], (int32_t)a[3],
+            (int32_t)a[4], d(6), a[6] ? GLOWB200_FC_FUSE_RELU : 0, c.workspace, f->workspace_bytes, c.status_dev, st);
         break;
       }
       case GLOWB200_INSTR_CWQ_CONV: {
@@ -664,36 +837,36 @@ int execute(glowb200_device_manager *dm, LoadedNetwork &n) {
         const int64_t od[4] = {a[0], a[4], a[5], a[6]}, id[4] = {a[0], a[1], a[2], a[3]}, fd[4] = {a[6], a[7], a[8], a[3] / a[15]};
         const int64_t k[2] = {a[7], a[8]}, s[2] = {a[9], a[10]}, p[4] = {a[11], a[12], a[13], a[14]}, dl[2] = {a[16], a[17]};
         rc = glowb200_channelwise_quantized_conv2d_i8_i32(
-            (int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]), (const int32_t *)ptr(in.ops[3]),
-            od, id, fd, k, s, p, a[15], dl, (int32_t)a[19], (int32_t)a[18], (const int32_t *)ptr(in.ops[5]),
-            (const int32_t *)ptr(in.ops[7]), d(0), d(1), d(2), d(3), d(4), d(5), (int32_t)a[20], nullptr, nullptr, 0, n.workspace,
-            f->workspace_bytes, dm->status_dev, st);
+            (int8_t *)P(0), (const int8_t *)P(1), (const int8_t *)P(2), (const int32_t *)P(3),
+            od, id, fd, k, s, p, a[15], dl, (int32_t)a[19], (int32_t)a[18], (const int32_t *)P(5),
+            (const int32_t *)P(7), d(0), d(1), d(2), d(3), d(4), d(5), (int32_t)a[20], nullptr, nullptr, 0, c.workspace,
+            f->workspace_bytes, c.status_dev, st);
         break;
       }
       case GLOWB200_INSTR_ADD:
-        rc = glowb200_element_add_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]), a[0],
+        rc = glowb200_element_add_i8((int8_t *)P(0), (const int8_t *)P(1), (const int8_t *)P(2), a[0],
                                      (int32_t)a[1], (int32_t)a[2], (int32_t)a[3], (int32_t)a[4], (int32_t)a[5], (int32_t)a[6],
                                      (int32_t)a[7], (int32_t)a[8], (int32_t)a[9], st);
         break;
       case GLOWB200_INSTR_MAXSPLAT:
-        rc = glowb200_element_maxsplat_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), a[0], (int32_t)a[1], st);
+        rc = glowb200_element_maxsplat_i8((int8_t *)P(0), (const int8_t *)P(1), a[0], (int32_t)a[1], st);
         break;
       case GLOWB200_INSTR_QUANTIZE:
-        rc = glowb200_element_quantize_i8((int8_t *)ptr(in.ops[0]), (const float *)ptr(in.ops[1]), a[0], in.fa[0], (int32_t)a[1], st);
+        rc = glowb200_element_quantize_i8((int8_t *)P(0), (const float *)P(1), a[0], in.fa[0], (int32_t)a[1], st);
         break;
       case GLOWB200_INSTR_DEQUANTIZE:
-        rc = glowb200_element_dequantize_i8((float *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), a[0], in.fa[0], (int32_t)a[1], st);
+        rc = glowb200_element_dequantize_i8((float *)P(0), (const int8_t *)P(1), a[0], in.fa[0], (int32_t)a[1], st);
         break;
       case GLOWB200_INSTR_MAXPOOL: {
         const int64_t id[4] = {a[0], a[1], a[2], a[3]}, od[4] = {a[0], a[4], a[5], a[3]}, k[2] = {a[6], a[7]}, s[2] = {a[8], a[9]};
         const int64_t p[4] = {a[10], a[11], a[10], a[11]};
-        rc = glowb200_max_pool_i8((const int8_t *)ptr(in.ops[1]), (int8_t *)ptr(in.ops[0]), id, od, k, s, p, (int32_t)a[12], st);
+        rc = glowb200_max_pool_i8((const int8_t *)P(1), (int8_t *)P(0), id, od, k, s, p, (int32_t)a[12], st);
         break;
       }
       case GLOWB200_INSTR_AVGPOOL: {
         const int64_t id[4] = {a[0], a[1], a[2], a[3]}, od[4] = {a[0], a[4], a[5], a[3]}, k[2] = {a[6], a[7]}, s[2] = {a[8], a[9]};
         const int64_t p[4] = {a[10], a[11], a[10], a[11]};
-        rc = glowb200_avg_pool_i8((const int8_t *)ptr(in.ops[1]), (int8_t *)ptr(in.ops[0]), id, od, k, s, p, (int)a[14], (int32_t)a[13],
+        rc = glowb200_avg_pool_i8((const int8_t *)P(1), (int8_t *)P(0), id, od, k, s, p, (int)a[14], (int32_t)a[13],
                                   (int32_t)a[12], (int32_t)a[15], (int32_t)a[16], (int32_t)a[17], st);
         break;
       }
@@ -702,97 +875,97 @@ int execute(glowb200_device_manager *dm, LoadedNetwork &n) {
         int64_t dims[4];
         int32_t sh[4];
         for (int i = 0; i < nd; i++) { dims[i] = a[2 + i]; sh[i] = (int32_t)a[6 + i]; }
-        rc = glowb200_transpose(ptr(in.ops[1]), ptr(in.ops[0]), dims, sh, nd, (int)a[1], st);
+        rc = glowb200_transpose(P(1), P(0), dims, sh, nd, (int)a[1], st);
         break;
       }
       case GLOWB200_INSTR_COPY:
-        if (cudaMemcpyAsync(ptr(in.ops[0]), ptr(in.ops[1]), (size_t)a[0], cudaMemcpyDeviceToDevice, dm->stream) != cudaSuccess)
+        if (cudaMemcpyAsync(P(0), P(1), (size_t)a[0], cudaMemcpyDeviceToDevice, dm->stream) != cudaSuccess)
           rc = set_error(GLOWB200_RUNTIME_ERROR, "copy failed");
         break;
       case GLOWB200_INSTR_ADD_MAXSPLAT:
-        rc = glowb200_element_add_maxsplat_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
+        rc = glowb200_element_add_maxsplat_i8((int8_t *)P(0), (const int8_t *)P(1), (const int8_t *)P(2),
                                               a[0], (int32_t)a[1], (int32_t)a[2], (int32_t)a[3], (int32_t)a[5], (int32_t)a[6],
                                               (int32_t)a[7], (int32_t)a[8], (int32_t)a[9], (int32_t)a[10], (int32_t)a[4], st);
         break;
       case GLOWB200_INSTR_RELU:
-        rc = glowb200_element_relu_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), a[0], (int32_t)a[1], (int32_t)a[2],
+        rc = glowb200_element_relu_i8((int8_t *)P(0), (const int8_t *)P(1), a[0], (int32_t)a[1], (int32_t)a[2],
                                       (int32_t)a[3], (int32_t)a[4], (int32_t)a[5], st);
         break;
       case GLOWB200_INSTR_RESCALE:
-        rc = glowb200_element_rescale_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), a[0], (int32_t)a[2], (int32_t)a[1],
+        rc = glowb200_element_rescale_i8((int8_t *)P(0), (const int8_t *)P(1), a[0], (int32_t)a[2], (int32_t)a[1],
                                          (int32_t)a[3], (int32_t)a[4], (int32_t)a[5], st);
         break;
       case GLOWB200_INSTR_FC_I8:
-        rc = glowb200_fc_i8_i32((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
-                                (const int32_t *)ptr(in.ops[3]), a[0], a[1], a[2], (int32_t)a[6], (int32_t)a[3], (int32_t)a[4],
+        rc = glowb200_fc_i8_i32((int8_t *)P(0), (const int8_t *)P(1), (const int8_t *)P(2),
+                                (const int32_t *)P(3), a[0], a[1], a[2], (int32_t)a[6], (int32_t)a[3], (int32_t)a[4],
                                 (int32_t)a[5], (int32_t)a[7], (int32_t)a[8], (int32_t)a[9], (int32_t)a[10], (int32_t)a[11],
-                                (int32_t)a[12], nullptr, 0, n.workspace, f->workspace_bytes, dm->status_dev, st);
+                                (int32_t)a[12], nullptr, 0, c.workspace, f->workspace_bytes, c.status_dev, st);
         break;
       case GLOWB200_INSTR_MATMUL_I8:
-        rc = glowb200_matmul_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]), a[0], a[1],
+        rc = glowb200_matmul_i8((int8_t *)P(0), (const int8_t *)P(1), (const int8_t *)P(2), a[0], a[1],
                                 a[2], (int32_t)a[5], (int32_t)a[3], (int32_t)a[4], (int32_t)a[6], (int32_t)a[7], (int32_t)a[8], 0,
-                                n.workspace, f->workspace_bytes, dm->status_dev, st);
+                                c.workspace, f->workspace_bytes, c.status_dev, st);
         break;
       case GLOWB200_INSTR_SPLAT:
-        rc = glowb200_splat_f(ptr(in.ops[0]), a[0], in.fa[0], (int)a[1], st);
+        rc = glowb200_splat_f(P(0), a[0], in.fa[0], (int)a[1], st);
         break;
       case GLOWB200_INSTR_INSERT_TENSOR:
-        if (cudaMemcpy2DAsync((uint8_t *)ptr(in.ops[0]) + a[3], (size_t)a[2], ptr(in.ops[1]), (size_t)a[1], (size_t)a[1], (size_t)a[0],
+        if (cudaMemcpy2DAsync((uint8_t *)P(0) + a[3], (size_t)a[2], P(1), (size_t)a[1], (size_t)a[1], (size_t)a[0],
                               cudaMemcpyDeviceToDevice, dm->stream) != cudaSuccess)
           rc = set_error(GLOWB200_RUNTIME_ERROR, "insert-tensor copy failed");
         break;
       case GLOWB200_INSTR_PAIRWISE_DOT:
-        rc = glowb200_pairwise_dot_interaction((const float *)ptr(in.ops[1]), a[3], (const float *)ptr(in.ops[2]), a[4], a[0], a[1], a[2],
-                                               a[6] ? nullptr : (float *)ptr(in.ops[0]), a[6] ? (int8_t *)ptr(in.ops[0]) : nullptr, a[5],
+        rc = glowb200_pairwise_dot_interaction((const float *)P(1), a[3], (const float *)P(2), a[4], a[0], a[1], a[2],
+                                               a[6] ? nullptr : (float *)P(0), a[6] ? (int8_t *)P(0) : nullptr, a[5],
                                                in.fa[0], (int32_t)a[7], st);
         break;
       case GLOWB200_INSTR_SLWS_F32:
-        rc = glowb200_sparse_lengths_weighted_sum_f32((float *)ptr(in.ops[0]), (const float *)ptr(in.ops[1]), a[0],
-                                                      (const float *)ptr(in.ops[2]), ptr(in.ops[3]), (int)a[4],
-                                                      (const int32_t *)ptr(in.ops[4]), a[2], a[3], a[1], n.workspace,
-                                                      f->workspace_bytes, dm->status_dev, st);
+        rc = glowb200_sparse_lengths_weighted_sum_f32((float *)P(0), (const float *)P(1), a[0],
+                                                      (const float *)P(2), P(3), (int)a[4],
+                                                      (const int32_t *)P(4), a[2], a[3], a[1], c.workspace,
+                                                      f->workspace_bytes, c.status_dev, st);
         break;
       case GLOWB200_INSTR_RWQ_SLWS:
         rc = glowb200_rowwise_quantized_sparse_lengths_weighted_sum_f32(
-            (float *)ptr(in.ops[0]), (const uint8_t *)ptr(in.ops[1]), (const float *)ptr(in.ops[2]), (const float *)ptr(in.ops[3]), a[0],
-            (const float *)ptr(in.ops[4]), ptr(in.ops[5]), (int)a[4], (const int32_t *)ptr(in.ops[6]), a[2], a[3], a[1], n.workspace,
-            f->workspace_bytes, dm->status_dev, st);
+            (float *)P(0), (const uint8_t *)P(1), (const float *)P(2), (const float *)P(3), a[0],
+            (const float *)P(4), P(5), (int)a[4], (const int32_t *)P(6), a[2], a[3], a[1], c.workspace,
+            f->workspace_bytes, c.status_dev, st);
         break;
       case GLOWB200_INSTR_BINARY_I8:
-        rc = glowb200_element_binary_i8((int)a[4], (int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
+        rc = glowb200_element_binary_i8((int)a[4], (int8_t *)P(0), (const int8_t *)P(1), (const int8_t *)P(2),
                                         a[0], (int32_t)a[1], (int32_t)a[2], (int32_t)a[3], (int32_t)a[5], (int32_t)a[6], (int32_t)a[7],
                                         (int32_t)a[8], (int32_t)a[9], (int32_t)a[10], st);
         break;
       case GLOWB200_INSTR_MULDIV_I8:
-        rc = glowb200_element_muldiv_i8((int)a[4], (int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
+        rc = glowb200_element_muldiv_i8((int)a[4], (int8_t *)P(0), (const int8_t *)P(1), (const int8_t *)P(2),
                                         a[0], (int32_t)a[1], (int32_t)a[2], (int32_t)a[3], (int32_t)a[5], (int32_t)a[6], (int32_t)a[7], st);
         break;
       case GLOWB200_INSTR_BATCHED_ADD_I8:
-        rc = glowb200_batched_add_i8((int8_t *)ptr(in.ops[0]), (const int8_t *)ptr(in.ops[1]), ptr(in.ops[2]), (int)a[5], a[0], a[1],
+        rc = glowb200_batched_add_i8((int8_t *)P(0), (const int8_t *)P(1), P(2), (int)a[5], a[0], a[1],
                                      (int32_t)a[2], (int32_t)a[3], (int32_t)a[4], (int32_t)a[6], (int32_t)a[7], (int32_t)a[8],
                                      (int32_t)a[9], (int32_t)a[10], (int32_t)a[11], st);
         break;
       case GLOWB200_INSTR_SPLIT_EMBEDDING:
         rc = glowb200_int_nbit_split_embedding_bags(
-            ptr(in.ops[0]), ptr(in.ops[1]), a[0], ptr(in.ops[2]), a[1], (const int32_t *)ptr(in.ops[3]), ptr(in.ops[4]), (int)a[7],
-            (const uint8_t *)ptr(in.ops[5]), (const int32_t *)ptr(in.ops[6]), a[2], a[3], ptr(in.ops[7]), ptr(in.ops[8]), (int)a[6],
-            a[4], a[5], (int)a[8], ptr(in.ops[9]), (int)a[9], (int)a[10], (int)a[11], (int)a[12], dm->status_dev, st);
+            P(0), P(1), a[0], P(2), a[1], (const int32_t *)P(3), P(4), (int)a[7],
+            (const uint8_t *)P(5), (const int32_t *)P(6), a[2], a[3], P(7), P(8), (int)a[6],
+            a[4], a[5], (int)a[8], P(9), (int)a[9], (int)a[10], (int)a[11], (int)a[12], c.status_dev, st);
         break;
       case GLOWB200_INSTR_DYN_QUANTIZED_FC:
         if (in.ops[4] >= 0)
-          rc = glowb200_dynamic_rowwise_quantized_fc(ptr(in.ops[0]), ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
-                                                     (const float *)ptr(in.ops[3]), (const float *)ptr(in.ops[4]),
-                                                     (const int32_t *)ptr(in.ops[5]), a[0], a[1], a[2], nullptr, 0, n.workspace,
-                                                     f->workspace_bytes, dm->status_dev, st);
+          rc = glowb200_dynamic_rowwise_quantized_fc(P(0), P(1), (const int8_t *)P(2),
+                                                     (const float *)P(3), (const float *)P(4),
+                                                     (const int32_t *)P(5), a[0], a[1], a[2], nullptr, 0, c.workspace,
+                                                     f->workspace_bytes, c.status_dev, st);
         else
-          rc = glowb200_dynamic_quantized_fc(ptr(in.ops[0]), ptr(in.ops[1]), (const int8_t *)ptr(in.ops[2]),
-                                             (const float *)ptr(in.ops[3]), in.fa[0], (int32_t)a[3], a[0], a[1], a[2], nullptr, 0,
-                                             n.workspace, f->workspace_bytes, dm->status_dev, st);
+          rc = glowb200_dynamic_quantized_fc(P(0), P(1), (const int8_t *)P(2),
+                                             (const float *)P(3), in.fa[0], (int32_t)a[3], a[0], a[1], a[2], nullptr, 0,
+                                             c.workspace, f->workspace_bytes, c.status_dev, st);
         break;
       case GLOWB200_INSTR_EMBEDDING_BAG:
-        rc = glowb200_embedding_bag_byte_rowwise_offsets(ptr(in.ops[0]), ptr(in.ops[1]), (int)a[0], a[1], ptr(in.ops[2]), ptr(in.ops[3]),
-                                                         ptr(in.ops[4]), (int)a[6], a[4], a[5], a[2], a[3], (int)a[7], (int)a[8],
-                                                         (int)a[9], n.workspace, f->workspace_bytes, dm->status_dev, st);
+        rc = glowb200_embedding_bag_byte_rowwise_offsets(P(0), P(1), (int)a[0], a[1], P(2), P(3),
+                                                         P(4), (int)a[6], a[4], a[5], a[2], a[3], (int)a[7], (int)a[8],
+                                                         (int)a[9], c.workspace, f->workspace_bytes, c.status_dev, st);
         break;
     }
     if (rc != GLOWB200_OK) {
@@ -819,45 +992,78 @@ extern "C" int glowb200_device_manager_run_function(glowb200_device_manager *dm,
 }
 
 namespace {
-// Finishes a request: the status word, the stream, the mapping of what went wrong.
-int finish_request(glowb200_device_manager *dm, const char *name) {
-  int32_t status = 0;
-  cudaMemcpyAsync(&status, dm->status_dev, 4, cudaMemcpyDeviceToHost, dm->stream);
-  cudaMemsetAsync(dm->status_dev, 0, 4, dm->stream);
-  const cudaError_t e = cudaStreamSynchronize(dm->stream);
-  if (e != cudaSuccess) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "device error while running %s: %s", name, cudaGetErrorString(e));
+int status_to_error(int32_t status, const char *name) {
   if (status & GLOWB200_STATUS_WAIT_TIMEOUT) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "a device-side wait gave up while running %s", name);
   if (status) return set_error(GLOWB200_RUNTIME_ERROR, "invalid sparse input to %s (status bits 0x%x: index out of range 1, lengths overrun 2, negative length 4, bad offsets 8, unsupported table 32)", name, status);
   return GLOWB200_OK;
 }
-}  // namespace
 
-namespace {
+// Finishes a synchronous request: the status word, the stream, the mapping of what went wrong.
+int finish_request(glowb200_device_manager *dm, Context &c, const char *name) {
+  int32_t status = 0;
+  cudaMemcpyAsync(&status, c.status_dev, 4, cudaMemcpyDeviceToHost, dm->stream);
+  cudaMemsetAsync(c.status_dev, 0, 4, dm->stream);
+  const cudaError_t e = cudaStreamSynchronize(dm->stream);
+  if (e != cudaSuccess) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "device error while running %s: %s", name, cudaGetErrorString(e));
+  return status_to_error(status, name);
+}
+
 // A request that failed on the host part-way through: kernels and copies already queued are
 // waited for (the caller may reuse its buffers as soon as the error returns) and whatever they
 // raised in the status word is dropped with the request, so the next one starts clean.  The
 // message of the failure that led here is kept.
-int abort_request(glowb200_device_manager *dm, int rc) {
+int abort_request(glowb200_device_manager *dm, Context &c, int rc) {
   char msg[512];
   snprintf(msg, sizeof(msg), "%s", glowb200_last_error());
-  cudaMemsetAsync(dm->status_dev, 0, 4, dm->stream);
-  if (cudaStreamSynchronize(dm->stream) != cudaSuccess) {
+  bool ok = cudaStreamSynchronize(dm->in_stream) == cudaSuccess;
+  cudaMemsetAsync(c.status_dev, 0, 4, dm->stream);
+  ok = cudaStreamSynchronize(dm->stream) == cudaSuccess && ok;
+  ok = cudaStreamSynchronize(dm->out_stream) == cudaSuccess && ok;
+  c.ticket = 0;
+  if (!ok) {
     cudaGetLastError();
     return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "device error after a failed request (%s)", msg);
   }
   return set_error(rc, "%s", msg);
 }
 
-// Where a placeholder of a loaded network lives; dm->lock is held by the caller.
+// Completes the asynchronous request in flight on a context (if any) and returns its result.
+int complete_context(glowb200_device_manager *dm, Context &c, const char *name) {
+  if (c.ticket == 0) return GLOWB200_OK;
+  const cudaError_t e = cudaEventSynchronize(c.out_done);
+  c.ticket = 0;
+  if (e != cudaSuccess) return set_error(GLOWB200_RUNTIME_DEVICE_NONRECOVERABLE, "device error while running %s: %s", name, cudaGetErrorString(e));
+  const int32_t status = *c.status_host;
+  return status_to_error(status, name);
+}
+
+// Where a placeholder of a loaded network lives (context 0 for the per-context kind); dm->lock
+// is held by the caller.
 int find_placeholder(glowb200_device_manager *dm, const char *name, const char *placeholder, void **device_ptr, size_t *bytes) {
   auto it = dm->networks.find(name);
   if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Function %s not found", name);
   glowb200_function *f = it->second.fn;
   auto s = f->by_name.find(placeholder);
-  if (s == f->by_name.end() || f->symbols[s->second].kind != kPlaceholder)
+  if (s == f->by_name.end() || (f->symbols[s->second].kind != kPlaceholder && f->symbols[s->second].kind != kStatic))
     return set_error(GLOWB200_RUNTIME_ERROR, "%s is not a placeholder of %s", placeholder, name);
-  *device_ptr = it->second.slab[kPlaceholder] + f->symbols[s->second].offset;
-  if (bytes) *bytes = f->symbols[s->second].bytes;
+  const Symbol &sym = f->symbols[s->second];
+  *device_ptr = it->second.ctx[0].slab[sym.kind] + sym.offset;
+  if (bytes) *bytes = sym.bytes;
+  return GLOWB200_OK;
+}
+
+// Resolves the bindings of a request against the network's placeholders.
+int resolve_bindings(glowb200_function *f, const char *name, const char *const *placeholder_names, const size_t *buffer_bytes,
+                     int num_bindings, std::vector<int> &ids) {
+  ids.resize(num_bindings);
+  for (int b = 0; b < num_bindings; b++) {
+    auto s = f->by_name.find(placeholder_names[b]);
+    if (s == f->by_name.end() || f->symbols[s->second].kind != kPlaceholder)
+      return set_error(GLOWB200_RUNTIME_ERROR, "%s is not a placeholder of %s", placeholder_names[b], name);
+    ids[b] = s->second;
+    if (buffer_bytes[b] > f->symbols[ids[b]].bytes)
+      return set_error(GLOWB200_RUNTIME_ERROR, "binding of %s is larger than the placeholder", f->symbols[ids[b]].name.c_str());
+  }
   return GLOWB200_OK;
 }
 }  // namespace
@@ -895,8 +1101,13 @@ extern "C" int glowb200_device_manager_run_function_resident(glowb200_device_man
   auto it = dm->networks.find(name);
   if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Function %s not found", name);
   cudaSetDevice(dm->device);
-  if (int rc = execute(dm, it->second)) return abort_request(dm, rc);
-  return finish_request(dm, name);
+  Context &c = it->second.ctx[0];
+  if (c.ticket) {  // an asynchronous request still owns the context: let it finish, keep its result
+    const int64_t t = c.ticket;
+    dm->finished[t] = complete_context(dm, c, name);
+  }
+  if (int rc = execute(dm, it->second, c)) return abort_request(dm, c, rc);
+  return finish_request(dm, c, name);
 }
 
 extern "C" int glowb200_device_manager_run_function_io(glowb200_device_manager *dm, const char *name, const char *const *placeholder_names,
@@ -910,26 +1121,119 @@ extern "C" int glowb200_device_manager_run_function_io(glowb200_device_manager *
   LoadedNetwork &n = it->second;
   glowb200_function *f = n.fn;
   cudaSetDevice(dm->device);
-  std::vector<int> ids(num_bindings);
+  std::vector<int> ids;
+  if (int rc = resolve_bindings(f, name, placeholder_names, buffer_bytes, num_bindings, ids)) return rc;
+  Context &c = n.ctx[0];
+  if (c.ticket) {
+    const int64_t t = c.ticket;
+    dm->finished[t] = complete_context(dm, c, name);
+  }
   for (int b = 0; b < num_bindings; b++) {
-    auto s = f->by_name.find(placeholder_names[b]);
-    if (s == f->by_name.end() || f->symbols[s->second].kind != kPlaceholder)
-      return set_error(GLOWB200_RUNTIME_ERROR, "%s is not a placeholder of %s", placeholder_names[b], name);
-    ids[b] = s->second;
     const Symbol &sym = f->symbols[ids[b]];
-    if (buffer_bytes[b] > sym.bytes) return set_error(GLOWB200_RUNTIME_ERROR, "binding of %s is larger than the placeholder", sym.name.c_str());
-    uint8_t *d = n.slab[kPlaceholder] + sym.offset;
+    uint8_t *d = c.slab[kPlaceholder] + sym.offset;
     if (directions && !(directions[b] & GLOWB200_BINDING_INPUT)) continue;  // an output: nothing to copy in
     bool ok = cudaMemcpyAsync(d, host_buffers[b], buffer_bytes[b], cudaMemcpyHostToDevice, dm->stream) == cudaSuccess;
     if (ok && buffer_bytes[b] < sym.bytes) ok = cudaMemsetAsync(d + buffer_bytes[b], 0, sym.bytes - buffer_bytes[b], dm->stream) == cudaSuccess;
-    if (!ok) return abort_request(dm, set_error(GLOWB200_RUNTIME_ERROR, "host-to-device copy of %s failed", sym.name.c_str()));
+    if (!ok) return abort_request(dm, c, set_error(GLOWB200_RUNTIME_ERROR, "host-to-device copy of %s failed", sym.name.c_str()));
   }
-  if (int rc = execute(dm, n)) return abort_request(dm, rc);
+  if (int rc = execute(dm, n, c)) return abort_request(dm, c, rc);
   for (int b = 0; b < num_bindings; b++) {
     const Symbol &sym = f->symbols[ids[b]];
     if (directions && !(directions[b] & GLOWB200_BINDING_OUTPUT)) continue;  // an input: nothing to copy back
-    if (cudaMemcpyAsync(host_buffers[b], n.slab[kPlaceholder] + sym.offset, buffer_bytes[b], cudaMemcpyDeviceToHost, dm->stream) != cudaSuccess)
-      return abort_request(dm, set_error(GLOWB200_RUNTIME_ERROR, "device-to-host copy of %s failed", sym.name.c_str()));
+    if (cudaMemcpyAsync(host_buffers[b], c.slab[kPlaceholder] + sym.offset, buffer_bytes[b], cudaMemcpyDeviceToHost, dm->stream) != cudaSuccess)
+      return abort_request(dm, c, set_error(GLOWB200_RUNTIME_ERROR, "device-to-host copy of %s failed", sym.name.c_str()));
   }
-  return finish_request(dm, name);
+  return finish_request(dm, c, name);
+}
+
+// The asynchronous request: the inputs go in on one stream, the kernels run on a second, the
+// results leave on a third, ordered by events -- so that with two or more execution contexts
+// (glowb200_device_manager_set_context_count) the inputs of request i + 1 arrive while request
+// i runs and the results of request i - 1 leave, as Glow's executor overlaps them when a
+// backend offers several contexts.  The host buffers must stay valid, and should be pinned,
+// until glowb200_device_manager_wait has returned the ticket's result.  Contexts are taken in
+// turn; a context whose last request has not been waited for is completed first (its result is
+// kept for its own wait call).
+extern "C" int glowb200_device_manager_run_function_async(glowb200_device_manager *dm, const char *name,
+                                                          const char *const *placeholder_names, void *const *host_buffers,
+                                                          const size_t *buffer_bytes, const int *directions, int num_bindings,
+                                                          int64_t *ticket) {
+  if (!dm || !name || !ticket) return set_error(GLOWB200_RUNTIME_ERROR, "NULL argument");
+  std::lock_guard<std::mutex> g(dm->lock);
+  if (!dm->running) return set_error(GLOWB200_RUNTIME_ERROR, "device manager is not initialised");
+  auto it = dm->networks.find(name);
+  if (it == dm->networks.end()) return set_error(GLOWB200_RUNTIME_NET_NOT_FOUND, "Function %s not found", name);
+  LoadedNetwork &n = it->second;
+  glowb200_function *f = n.fn;
+  cudaSetDevice(dm->device);
+  std::vector<int> ids;
+  if (int rc = resolve_bindings(f, name, placeholder_names, buffer_bytes, num_bindings, ids)) return rc;
+  Context &c = n.ctx[n.next_ctx];
+  n.next_ctx = (n.next_ctx + 1) % n.ctx.size();
+  if (c.ticket) {
+    const int64_t t = c.ticket;
+    dm->finished[t] = complete_context(dm, c, name);
+  }
+  // inputs: the context's previous kernels and copies are complete (completed above, or waited
+  // for by the caller), so nothing still reads or writes these placeholders
+  for (int b = 0; b < num_bindings; b++) {
+    const Symbol &sym = f->symbols[ids[b]];
+    uint8_t *d = c.slab[kPlaceholder] + sym.offset;
+    if (directions && !(directions[b] & GLOWB200_BINDING_INPUT)) continue;
+    bool ok = cudaMemcpyAsync(d, host_buffers[b], buffer_bytes[b], cudaMemcpyHostToDevice, dm->in_stream) == cudaSuccess;
+    if (ok && buffer_bytes[b] < sym.bytes) ok = cudaMemsetAsync(d + buffer_bytes[b], 0, sym.bytes - buffer_bytes[b], dm->in_stream) == cudaSuccess;
+    if (!ok) return abort_request(dm, c, set_error(GLOWB200_RUNTIME_ERROR, "host-to-device copy of %s failed", sym.name.c_str()));
+  }
+  bool ok = cudaEventRecord(c.in_done, dm->in_stream) == cudaSuccess && cudaStreamWaitEvent(dm->stream, c.in_done, 0) == cudaSuccess;
+  if (!ok) return abort_request(dm, c, set_error(GLOWB200_RUNTIME_ERROR, "cannot order the streams of %s", name));
+  if (int rc = execute(dm, n, c)) return abort_request(dm, c, rc);
+  ok = cudaEventRecord(c.run_done, dm->stream) == cudaSuccess && cudaStreamWaitEvent(dm->out_stream, c.run_done, 0) == cudaSuccess;
+  for (int b = 0; b < num_bindings && ok; b++) {
+    const Symbol &sym = f->symbols[ids[b]];
+    if (directions && !(directions[b] & GLOWB200_BINDING_OUTPUT)) continue;
+    ok = cudaMemcpyAsync(host_buffers[b], c.slab[kPlaceholder] + sym.offset, buffer_bytes[b], cudaMemcpyDeviceToHost, dm->out_stream) == cudaSuccess;
+  }
+  ok = ok && cudaMemcpyAsync(c.status_host, c.status_dev, 4, cudaMemcpyDeviceToHost, dm->out_stream) == cudaSuccess &&
+       cudaMemsetAsync(c.status_dev, 0, 4, dm->out_stream) == cudaSuccess && cudaEventRecord(c.out_done, dm->out_stream) == cudaSuccess;
+  if (!ok) return abort_request(dm, c, set_error(GLOWB200_RUNTIME_ERROR, "device-to-host copies of %s failed", name));
+  c.ticket = dm->next_ticket++;
+  *ticket = c.ticket;
+  return GLOWB200_OK;
+}
+
+// Blocks until the request behind `ticket` is complete (its outputs are in the host buffers)
+// and returns its result: GLOWB200_OK, or the error the synchronous call would have returned.
+extern "C" int glowb200_device_manager_wait(glowb200_device_manager *dm, int64_t ticket) {
+  if (!dm || ticket <= 0) return set_error(GLOWB200_RUNTIME_ERROR, "bad ticket");
+  std::lock_guard<std::mutex> g(dm->lock);
+  auto done = dm->finished.find(ticket);
+  if (done != dm->finished.end()) {
+    const int rc = done->second;
+    dm->finished.erase(done);
+    if (rc != GLOWB200_OK) return set_error(rc, "request %lld failed (completed on behalf of a later request)", (long long)ticket);
+    return GLOWB200_OK;
+  }
+  cudaSetDevice(dm->device);
+  for (auto &kv : dm->networks)
+    for (Context &c : kv.second.ctx)
+      if (c.ticket == ticket) return complete_context(dm, c, kv.first.c_str());
+  return set_error(GLOWB200_RUNTIME_ERROR, "no request with ticket %lld is in flight", (long long)ticket);
+}
+
+// Pinned host memory for the buffers of asynchronous requests (DeviceManager::allocateDeviceIOBuffer,
+// include/glow/Backends/DeviceManager.h:150-160).
+extern "C" void *glowb200_device_manager_allocate_io_buffer(glowb200_device_manager *dm, size_t bytes) {
+  if (!dm || bytes == 0) return nullptr;
+  cudaSetDevice(dm->device);
+  void *p = nullptr;
+  if (cudaMallocHost(&p, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    set_error(GLOWB200_RUNTIME_ERROR, "cannot allocate %zu bytes of pinned host memory", bytes);
+    return nullptr;
+  }
+  return p;
+}
+
+extern "C" void glowb200_device_manager_free_io_buffer(glowb200_device_manager *dm, void *buffer) {
+  if (dm && buffer) cudaFreeHost(buffer);
 }

@@ -12,7 +12,7 @@ import numpy as np
 from . import _lib
 from ._lib import GlowB200Error
 
-CONSTANT, PLACEHOLDER, ACTIVATION = 0, 1, 2
+CONSTANT, PLACEHOLDER, ACTIVATION, STATIC = 0, 1, 2, 3
 (FRWQ_SLWS, RWQ_FC, CWQ_CONV, ADD, MAXSPLAT, QUANTIZE, DEQUANTIZE, MAXPOOL, AVGPOOL, TRANSPOSE, COPY) = range(1, 12)
 (ADD_MAXSPLAT, RELU, RESCALE, FC_I8, MATMUL_I8, SPLAT, INSERT_TENSOR, PAIRWISE_DOT, SLWS_F32, RWQ_SLWS,
  EMBEDDING_BAG, SPLIT_EMBEDDING, DYN_QUANTIZED_FC, BINARY_I8, MULDIV_I8, BATCHED_ADD_I8) = range(12, 28)
@@ -54,12 +54,24 @@ class Function:
     def activation(self, name, nbytes):
         return self._symbol(name, ACTIVATION, nbytes)
 
+    def static_placeholder(self, name, nbytes):
+        """A placeholder written once (transfer_static_placeholder) and shared by all contexts."""
+        return self._symbol(name, STATIC, nbytes)
+
     def instruction(self, kind, operands, int_attrs=(), float_attrs=()):
-        ops = (C.c_int32 * len(operands))(*operands)
+        """operands: symbol ids, or (symbol id, byte offset) pairs for views of a larger tensor."""
+        ids = [o[0] if isinstance(o, tuple) else o for o in operands]
+        offs = [int(o[1]) if isinstance(o, tuple) else 0 for o in operands]
+        ops = (C.c_int32 * len(ids))(*ids)
+        of = (C.c_int64 * max(1, len(offs)))(*offs)
         ia = (C.c_int64 * max(1, len(int_attrs)))(*[int(v) for v in int_attrs])
         fa = (C.c_float * max(1, len(float_attrs)))(*[float(v) for v in float_attrs])
-        _check(_lib.lib().glowb200_function_add_instruction(self.h, kind, ops, len(operands), ia, len(int_attrs), fa,
-                                                            len(float_attrs)))
+        if any(offs):
+            _check(_lib.lib().glowb200_function_add_instruction_views(self.h, kind, ops, of, len(ids), ia, len(int_attrs),
+                                                                      fa, len(float_attrs)))
+        else:
+            _check(_lib.lib().glowb200_function_add_instruction(self.h, kind, ops, len(ids), ia, len(int_attrs), fa,
+                                                                len(float_attrs)))
 
     # readable wrappers over the attribute layouts documented in runtime.cu
     def frwq_slws(self, dest, data, weights, indices, lengths, *, kind, rows, in_line, out_line, segments, num_indices,
@@ -194,6 +206,10 @@ class Function:
         return self
 
     @property
+    def batched_pooling_launches(self):
+        return int(_lib.lib().glowb200_function_batched_pooling_launches(self.h))
+
+    @property
     def constant_bytes(self):
         return int(_lib.lib().glowb200_function_constant_bytes(self.h))
 
@@ -202,6 +218,8 @@ class DeviceManager:
     def __init__(self, device_id=0, max_memory_bytes=0):
         self.h = _lib.lib().glowb200_device_manager_create(int(device_id), int(max_memory_bytes))
         self._functions = {}
+        self._io = []
+        self._inflight = {}
 
     def init(self):
         _check(_lib.lib().glowb200_device_manager_init(self.h))
@@ -231,6 +249,43 @@ class DeviceManager:
         else:
             cd = (C.c_int * len(names))(*[2 if k in outputs else 1 for k in names])
             _check(_lib.lib().glowb200_device_manager_run_function_io(self.h, name.encode(), cn, cb, cs, cd, len(names)))
+
+    def set_context_count(self, contexts):
+        """Execution contexts (own placeholders and activations each) of networks added from now on."""
+        _check(_lib.lib().glowb200_device_manager_set_context_count(self.h, int(contexts)))
+
+    def io_buffer(self, shape, dtype):
+        """A numpy array over pinned host memory from the device manager (allocateDeviceIOBuffer)."""
+        dtype = np.dtype(dtype)
+        n = int(np.prod(shape)) * dtype.itemsize
+        p = _lib.lib().glowb200_device_manager_allocate_io_buffer(self.h, max(n, 1))
+        if not p:
+            raise GlowB200Error(RUNTIME_ERROR, _lib.lib().glowb200_last_error().decode())
+        buf = (C.c_uint8 * max(n, 1)).from_address(p)
+        arr = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+        self._io.append(p)
+        return arr
+
+    def run_function_async(self, name, bindings, outputs=()):
+        """Enqueues a request (inputs in, kernels, outputs out on three streams) and returns its
+        ticket; the arrays must stay alive and untouched until wait(ticket) has returned."""
+        names = list(bindings)
+        arrs = [bindings[k] for k in names]
+        cn = (C.c_char_p * len(names))(*[k.encode() for k in names])
+        cb = (C.c_void_p * len(names))(*[a.ctypes.data for a in arrs])
+        cs = (C.c_size_t * len(names))(*[a.nbytes for a in arrs])
+        cd = (C.c_int * len(names))(*[2 if k in outputs else 1 for k in names])
+        ticket = C.c_int64(0)
+        _check(_lib.lib().glowb200_device_manager_run_function_async(self.h, name.encode(), cn, cb, cs, cd, len(names),
+                                                                     C.byref(ticket)))
+        self._inflight[ticket.value] = (cn, cb, cs, cd, arrs)
+        return int(ticket.value)
+
+    def wait(self, ticket):
+        try:
+            _check(_lib.lib().glowb200_device_manager_wait(self.h, int(ticket)))
+        finally:
+            self._inflight.pop(ticket, None)
 
     def placeholder_address(self, name, placeholder):
         """(device address, bytes) of a placeholder of a loaded network (device-resident tensors)."""
@@ -266,5 +321,8 @@ class DeviceManager:
 
     def __del__(self):
         if getattr(self, "h", None):
+            for p in self._io:
+                _lib.lib().glowb200_device_manager_free_io_buffer(self.h, C.c_void_p(p))
+            self._io = []
             _lib.lib().glowb200_device_manager_destroy(self.h)
             self.h = None

@@ -606,14 +606,18 @@ int glowb200_peer_buffer_destroy(void *device_ptr);
  * integer requantisation parameters from the float scales the way LLVMIRGen does and lays the
  * slabs out.  The device manager mirrors glow::DeviceManager (include/glow/Backends/
  * DeviceManager.h:47-241) as CPUDeviceManager implements it
- * (lib/Backends/CPU/CPUDeviceManager.cpp:65-179).  Calls are synchronous; a Glow
- * QueueBackedDeviceManager would make them from its one worker thread.
+ * (lib/Backends/CPU/CPUDeviceManager.cpp:65-179).  Calls are synchronous unless they say
+ * otherwise; a Glow QueueBackedDeviceManager would make them from its one worker thread.
  * Operand and attribute layouts of every instruction kind are listed above
  * glowb200_function_compile in runtime.cu.
  * ------------------------------------------------------------------------------------- */
 #define GLOWB200_SYMBOL_CONSTANT 0
 #define GLOWB200_SYMBOL_PLACEHOLDER 1
 #define GLOWB200_SYMBOL_ACTIVATION 2
+/* A placeholder that is written once and stays put (Placeholder::isStatic, include/glow/Graph/
+ * Nodes.h; the embedding tables of a recommendation model): lives beside the constants, shared
+ * by all execution contexts, filled by glowb200_device_manager_transfer_static_placeholder. */
+#define GLOWB200_SYMBOL_STATIC 3
 
 #define GLOWB200_INSTR_FRWQ_SLWS 1
 #define GLOWB200_INSTR_RWQ_FC 2
@@ -654,14 +658,31 @@ int glowb200_function_add_symbol(glowb200_function *f, const char *name, int kin
 int glowb200_function_add_instruction(glowb200_function *f, int kind, const int32_t *operands,
                                       int num_operands, const int64_t *int_attrs, int num_int_attrs,
                                       const float *float_attrs, int num_float_attrs);
+/* The same with a byte offset per operand: operand i is the part of its symbol that starts
+ * operand_byte_offsets[i] bytes in -- a TensorView of a larger tensor (include/glow/IR/Instrs.h,
+ * TensorViewInst with its offsets).  compile checks offset + size against the symbol. */
+int glowb200_function_add_instruction_views(glowb200_function *f, int kind, const int32_t *operands,
+                                            const int64_t *operand_byte_offsets, int num_operands,
+                                            const int64_t *int_attrs, int num_int_attrs,
+                                            const float *float_attrs, int num_float_attrs);
+/* Besides laying out the slabs and deriving the integer parameters, compile turns every run of
+ * consecutive, mutually independent FusedRowwiseQuantizedSparseLengthsWeightedSum instructions
+ * over tables of one kind and row width into ONE batched launch (the per-table SparseLengthsSum
+ * nodes of a recommendation model); results are bit-identical to the single launches. */
 int glowb200_function_compile(glowb200_function *f);
 size_t glowb200_function_constant_bytes(const glowb200_function *f);
+/* How many batched pooling launches compile formed (0 before compile). */
+int glowb200_function_batched_pooling_launches(const glowb200_function *f);
 
 /* max_memory_bytes 0 = the device's free memory at init. */
 glowb200_device_manager *glowb200_device_manager_create(int device_id, uint64_t max_memory_bytes);
 int glowb200_device_manager_init(glowb200_device_manager *dm);
 int glowb200_device_manager_add_network(glowb200_device_manager *dm, glowb200_function *f);
 int glowb200_device_manager_evict_network(glowb200_device_manager *dm, const char *name);
+/* Execution contexts networks are loaded with from now on (Backend::getContextCount,
+ * include/glow/Backend/Backend.h:272-276): each has its own placeholders and activations
+ * (constants and static placeholders are shared), so requests can overlap.  1 by default. */
+int glowb200_device_manager_set_context_count(glowb200_device_manager *dm, int contexts);
 /* Placeholder names paired with HOST buffers; every bound buffer is copied in before and out
  * after the run; a buffer shorter than its placeholder is a partial tensor (rest zeroed).
  * The _io form takes a direction per binding (GLOWB200_BINDING_INPUT: copied in only, _OUTPUT: copied
@@ -673,6 +694,22 @@ int glowb200_device_manager_run_function_io(glowb200_device_manager *dm, const c
                                             const char *const *placeholder_names,
                                             void *const *host_buffers, const size_t *buffer_bytes,
                                             const int *directions, int num_bindings);
+/* The asynchronous form of _run_function_io (DeviceManager::runFunction returns at once and
+ * calls back, include/glow/Backends/DeviceManager.h:120-135; CPUDeviceManager.cpp:141-179 is the
+ * synchronous body behind it): inputs go in on one stream, the kernels run on a second, results
+ * leave on a third, ordered by events.  With two or more contexts the copies of neighbouring
+ * requests overlap the kernels.  *ticket identifies the request; _wait blocks until its outputs
+ * are in the host buffers and returns its result (what _run_function_io would have returned).
+ * The host buffers must stay valid until then and should be pinned (_allocate_io_buffer:
+ * DeviceManager::allocateDeviceIOBuffer, DeviceManager.h:150-160). */
+int glowb200_device_manager_run_function_async(glowb200_device_manager *dm, const char *name,
+                                               const char *const *placeholder_names,
+                                               void *const *host_buffers, const size_t *buffer_bytes,
+                                               const int *directions, int num_bindings,
+                                               int64_t *ticket);
+int glowb200_device_manager_wait(glowb200_device_manager *dm, int64_t ticket);
+void *glowb200_device_manager_allocate_io_buffer(glowb200_device_manager *dm, size_t bytes);
+void glowb200_device_manager_free_io_buffer(glowb200_device_manager *dm, void *buffer);
 /* Device-resident tensors and static placeholders (DeviceManager::transferToDevice /
  * transferFromDevice / transferStaticPlaceholderToDevice, include/glow/Backends/DeviceManager.h:
  * 163-231, and the peer-to-peer hand-off between the partitions of a network): the device address

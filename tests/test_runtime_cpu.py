@@ -157,3 +157,16 @@ def test_convolution_group_is_checked_before_it_divides():
     f.instruction(runtime.CWQ_CONV, ids, ia, [0.1, 0.1])
     with pytest.raises(GlowB200Error, match="group"):
         f.compile()
+
+
+def test_views_are_checked_against_their_symbol():
+    g = runtime.Function("view_too_far")
+    a, b = g.placeholder("a", 64), g.placeholder("b", 32)
+    g.copy((a, 48), b, nbytes=32)  # 48 + 32 > 64
+    with pytest.raises(GlowB200Error, match="smaller than"):
+        g.compile()
+    g = runtime.Function("view_ok")
+    a, b = g.placeholder("a", 64), g.placeholder("b", 32)
+    g.copy((a, 32), b, nbytes=32)
+    g.compile()
+    assert g.batched_pooling_launches == 0

@@ -423,3 +423,122 @@ def test_arithmetic_glue_instructions(oracle, dm):
                                                                      q(f32(ta[0]) / (f32(tb[0]) * f32(td[0])))))
     np.testing.assert_array_equal(got["badd"], oracle.batched_add_i8(a.reshape(rows, -1), sl, td[1], ta[1], ts[1], lt,
                                                                       q(f32(ts[0]) / f32(td[0]))).reshape(-1))
+
+
+def _pooling_network(name, tables, B, max_n, idx_dtype=np.int32, static=True):
+    """T FRWQ-SLWS nodes over T tables whose indices, weights and lengths are views of three
+    shared placeholders ([T, max_n] indices and weights, [T, B] lengths) and whose results are
+    the T row blocks of one [T, B, D] output -- the per-table SparseLengthsSum nodes of a
+    recommendation model with its inputs in one arena."""
+    T = len(tables)
+    rows, in_line = tables[0].shape
+    D = in_line - 8
+    isz = np.dtype(idx_dtype).itemsize
+    f = runtime.Function(name)
+    tabs = [(f.static_placeholder if static else f.placeholder)("%s_table%d" % (name, t), tables[t].nbytes) for t in range(T)]
+    idx = f.placeholder(name + "_indices", T * max_n * isz)
+    w = f.placeholder(name + "_weights", T * max_n * 4)
+    ln = f.placeholder(name + "_lengths", T * B * 4)
+    out = f.placeholder(name + "_output", T * B * D * 4)
+    for t in range(T):
+        f.frwq_slws((out, t * B * D * 4), tabs[t], (w, t * max_n * 4), (idx, t * max_n * isz), (ln, t * B * 4),
+                    kind=ops.UINT8_FUSED, rows=rows, in_line=in_line, out_line=D, segments=B, num_indices=max_n,
+                    idx64=isz == 8)
+    return f.compile()
+
+
+def _pooling_request(dm, T, B, max_n, rows, seed, idx_dtype=np.int32):
+    idx = dm.io_buffer((T, max_n), idx_dtype)
+    w = dm.io_buffer((T, max_n), np.float32)
+    ln = dm.io_buffer((T, B), np.int32)
+    idx[:], w[:] = 0, 0
+    per_table = []
+    for t in range(T):
+        l, i, ww = workloads.bags_poisson(B, 12, 0, 30, rows, seed, t)
+        assert i.size <= max_n
+        ln[t], idx[t, :i.size], w[t, :i.size] = l, i, ww
+        per_table.append((l, i, ww))
+    return idx, w, ln, per_table
+
+
+def test_views_batched_pooling_and_asynchronous_requests(oracle, dm):
+    """Operands that are views of larger tensors; consecutive pooling nodes fused into one batched
+    launch; int32 indices; static tables shared by two execution contexts; four requests through
+    the asynchronous call with two in flight -- every result against the oracle."""
+    T, B, rows, D, max_n = 6, 64, 4000, 64, 64 * 30
+    tables = [workloads.fused_table_u8(rows, D, 90, t) for t in range(T)]
+    f = _pooling_network("pool", tables, B, max_n)
+    assert f.batched_pooling_launches == 1
+    dm.set_context_count(2)
+    dm.add_network(f)
+    for t in range(T):
+        dm.transfer_static_placeholder("pool", "pool_table%d" % t, tables[t])
+    reqs = [_pooling_request(dm, T, B, max_n, rows, 200 + r) for r in range(4)]
+    outs = [dm.io_buffer((T, B, D), np.float32) for _ in range(4)]
+    tickets = []
+    for r in range(4):
+        idx, w, ln, _ = reqs[r]
+        outs[r][:] = np.nan
+        tickets.append(dm.run_function_async("pool", {"pool_indices": idx, "pool_weights": w, "pool_lengths": ln,
+                                                      "pool_output": outs[r]}, outputs=("pool_output",)))
+        if r >= 1:
+            dm.wait(tickets[r - 1])  # two requests in flight at most, as a serving loop keeps them
+    dm.wait(tickets[-1])
+    for r in range(4):
+        for t in range(T):
+            l, i, ww = reqs[r][3][t]
+            want = oracle.frwq_slws_u8_f32(tables[t], ww, i.astype(np.int64), l)
+            np.testing.assert_allclose(outs[r][t], want, rtol=1e-5, atol=1e-5)
+    # the synchronous call on the same network gives the same bits
+    idx, w, ln, _ = reqs[0]
+    again = np.zeros((T, B, D), np.float32)
+    dm.run_function("pool", {"pool_indices": idx, "pool_weights": w, "pool_lengths": ln, "pool_output": again},
+                    outputs=("pool_output",))
+    np.testing.assert_array_equal(again, outs[0])
+    # a bad index surfaces from wait(), and the next request is clean
+    idx2 = idx.copy()
+    idx2[3, 0] = rows + 5
+    t_bad = dm.run_function_async("pool", {"pool_indices": idx2, "pool_weights": w, "pool_lengths": ln,
+                                           "pool_output": again}, outputs=("pool_output",))
+    t_ok = dm.run_function_async("pool", {"pool_indices": idx, "pool_weights": w, "pool_lengths": ln,
+                                          "pool_output": outs[1]}, outputs=("pool_output",))
+    with pytest.raises(GlowB200Error, match="invalid sparse input"):
+        dm.wait(t_bad)
+    dm.wait(t_ok)
+    np.testing.assert_array_equal(outs[1], outs[0])
+
+
+def test_batched_pooling_equals_single_launches(oracle, dm):
+    """The same network with its pooling nodes kept apart (a Copy between them breaks the run)
+    gives the same bits as the fused launch."""
+    T, B, rows, D, max_n = 4, 40, 3000, 128, 40 * 30
+    tables = [workloads.fused_table_u8(rows, D, 95, t) for t in range(T)]
+    fused = _pooling_network("fusedp", tables, B, max_n, np.int64, static=False)
+    apart = runtime.Function("apartp")
+    isz = 8
+    tabs = [apart.placeholder("apartp_table%d" % t, tables[t].nbytes) for t in range(T)]
+    idx = apart.placeholder("apartp_indices", T * max_n * isz)
+    w = apart.placeholder("apartp_weights", T * max_n * 4)
+    ln = apart.placeholder("apartp_lengths", T * B * 4)
+    out = apart.placeholder("apartp_output", T * B * D * 4)
+    scratch = apart.activation("apartp_scratch", 64)
+    for t in range(T):
+        apart.frwq_slws((out, t * B * D * 4), tabs[t], (w, t * max_n * 4), (idx, t * max_n * isz), (ln, t * B * 4),
+                        kind=ops.UINT8_FUSED, rows=rows, in_line=D + 8, out_line=D, segments=B, num_indices=max_n)
+        apart.copy(scratch, scratch, nbytes=64)
+    apart.compile()
+    assert fused.batched_pooling_launches == 1 and apart.batched_pooling_launches == 0
+    dm.add_network(fused)
+    dm.add_network(apart)
+    idxh, wh, lnh, per = _pooling_request(dm, T, B, max_n, rows, 300, np.int64)
+    res = {}
+    for name in ("fusedp", "apartp"):
+        o = np.zeros((T, B, D), np.float32)
+        b = {name + "_indices": idxh, name + "_weights": wh, name + "_lengths": lnh, name + "_output": o}
+        b.update({"%s_table%d" % (name, t): tables[t] for t in range(T)})
+        dm.run_function(name, b, outputs=(name + "_output",))
+        res[name] = o
+    np.testing.assert_array_equal(res["fusedp"], res["apartp"])
+    for t in range(T):
+        l, i, ww = per[t]
+        np.testing.assert_allclose(res["fusedp"][t], oracle.frwq_slws_u8_f32(tables[t], ww, i, l), rtol=1e-5, atol=1e-5)
