@@ -727,6 +727,19 @@ def pairwise_dot_interaction(dense, pooled, *, quant=None, out=None):
     return out
 
 
+def device_tensor(ptr, shape, dtype, device="cuda"):
+    """A torch view (no copy) of device memory the library owns -- a placeholder of a loaded
+    network (DeviceManager.placeholder_address), for device-resident tensors."""
+    class _Raw:
+        pass
+    raw = _Raw()
+    typestr = {torch.float32: "<f4", torch.uint8: "|u1", torch.int8: "|i1", torch.float16: "<f2", torch.int32: "<i4",
+               torch.int64: "<i8"}[dtype]
+    raw.__cuda_array_interface__ = {"shape": tuple(int(v) for v in shape), "typestr": typestr, "data": (int(ptr), False),
+                                    "version": 3}
+    return torch.as_tensor(raw, device=device)
+
+
 class PeerBuffer:
     """Device memory the other GPUs of the node can store into (set-up time object).
     `handle` (64 bytes) is what the owning process sends to its peers; `open` maps a peer's."""
