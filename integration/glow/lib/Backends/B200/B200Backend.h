@@ -29,8 +29,14 @@ public:
   bool supportsFusedActivation(Node *parent, Node *activation) const override;
   bool supportsPartialTensors() const override { return true; }
   bool supportsStaticPlaceholders() const override { return true; }
-  // Index tensors keep their type for the SLS family (CPUBackend.cpp:147-160).
+  // int64 index tensors may be demoted to int32, the SLS family included (the CPU backend keeps
+  // theirs, CPUBackend.cpp:147-160): tables have fewer than 2^31 rows and the host link carries
+  // half the bytes.
   bool canDoIndexTypeDemotion(ElemKind fromTy, ElemKind toTy, PrecisionConfiguration &precConfig) const override;
+
+  unsigned getContextCount(CompilationContext &cctx) const override;
+  Error bindContexts(llvm::ArrayRef<runtime::ContextBinding> bindings, const runtime::DAGNode *root, bool enableP2P,
+                     bool enableDRT, int64_t stateId) override;
 
   runtime::DeviceManager *createDeviceManager(const runtime::DeviceConfig &deviceConfig) override;
 };

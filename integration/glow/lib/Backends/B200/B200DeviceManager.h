@@ -31,6 +31,13 @@ public:
   /// Static placeholders (embedding tables) are copied to the device once.
   void transferStaticPlaceholderToDevice(Placeholder *PH, Tensor *T, std::function<void(Error)> resultCB) override;
 
+  /// Device-resident tensors: a tensor lives at the device address of a placeholder.
+  void transferToDevice(Tensor &tensor, void *locationContext, std::function<void(Error)> resultCB = GLOW_DRT_DEFAULT_CB) override;
+  void transferFromDevice(Tensor &tensor, bool release = true, std::function<void(Error)> resultCB = GLOW_DRT_DEFAULT_CB) override;
+  bool releaseDeviceTensor(void *locationContext) override;
+  /// Device address of a placeholder of a loaded network (context 0), or nullptr.
+  void *placeholderAddress(const std::string &network, const std::string &placeholder);
+
 protected:
   void addNetworkImpl(const Module *module, FunctionMapTy functions, ReadyCBTy cb) override;
   void evictNetworkImpl(std::string functionName, EvictFunctionCBTy evictCb) override;
