@@ -533,7 +533,11 @@ def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges, as_ran
                      {t: v.pin_memory() for t, v in indices.items()}))
     results = {}
     for exchange in exchanges:
-        model = dlrm.DLRMRank(cfg, qm, tables, rank, part, dev, exchange)
+        form = exchange
+        rendezvous = "flags"
+        if exchange == "fused_nccl_rendezvous":  # the fused exchange with a one-element all-reduce as the rendezvous
+            exchange, rendezvous = "fused", "nccl"
+        model = dlrm.DLRMRank(cfg, qm, tables, rank, part, dev, exchange, rendezvous=rendezvous)
         if exchange == "fused":
             model.connect_peers()
         elif exchange == "emulated":
@@ -634,6 +638,7 @@ def dlrm_measure(torch, dist, dev, rank, world, steps, warmup, exchanges, as_ran
         t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        exchange = form
         results[exchange] = {"samples_per_s": cfg.batch / (float(t[0]) * 1e-3), "ms_per_step": float(t[0]),
                              "e2e_samples_per_s": cfg.batch / (float(t[1]) * 1e-3), "e2e_ms_per_step": float(t[1]),
                              "h2d_bytes_per_step_per_rank": int(h2d), "d2h_bytes_per_step_per_rank": (hi - lo) * 4,
@@ -865,7 +870,7 @@ def run_model_line(args):
     sampler = ClockSampler(local)
     sampler.start()
     if args.workload == "dlrm":
-        forms = ["local"] if world == 1 else ["fused", "nccl"]
+        forms = ["local"] if world == 1 else ["fused", "fused_nccl_rendezvous", "nccl"]
         if world == 1 and args.as_rank_of > 1:
             forms = ["emulated"]
         res, cfg = dlrm_measure(torch, dist, dev, rank, world, max(10, args.steps), max(3, args.warmup), forms,

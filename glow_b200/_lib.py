@@ -84,6 +84,7 @@ SIGNATURES = {
     "glowb200_peer_buffer_open": (_int, [_vp, _vp]),
     "glowb200_peer_buffer_close": (_int, [_vp]),
     "glowb200_peer_buffer_destroy": (_int, [_vp]),
+    "glowb200_peer_rendezvous": (_int, [_vp, _vp, _int, _int, _i64, _vp, _vp]),
     "glowb200_function_create": (_vp, [C.c_char_p]),
     "glowb200_function_destroy": (None, [_vp]),
     "glowb200_function_add_symbol": (_int, [_vp, C.c_char_p, _int, _sz, _vp]),

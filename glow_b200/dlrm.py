@@ -258,7 +258,7 @@ class DLRMRank:
     its slice of the batch.  exchange: "local" (world 1), "nccl", "fused", or "emulated" (several
     ranks living in one process on one GPU, for tests: peers are wired with set_peers)."""
 
-    def __init__(self, cfg, qm, tables, rank=0, world=1, device="cuda", exchange="local", group=None):
+    def __init__(self, cfg, qm, tables, rank=0, world=1, device="cuda", exchange="local", group=None, rendezvous="flags"):
         self.cfg, self.rank, self.world, self.device = cfg, rank, world, torch.device(device)
         self.exchange, self.group = exchange, group
         self.my_tables = tables_of_rank(cfg, rank, world)
@@ -291,6 +291,12 @@ class DLRMRank:
         if exchange == "fused":
             self.slab_buf = [ops.PeerBuffer(per * T * D * 4) for _ in range(2)]
             self.slabs = [b.as_tensor((per, T, D), torch.float32) for b in self.slab_buf]
+            # the ranks' rendezvous: a flag per peer plus this rank's step count, written by a small
+            # kernel of the library (ops.peer_rendezvous); "nccl" keeps a one-element all-reduce instead
+            self.rendezvous = rendezvous
+            self.flag_buf = ops.PeerBuffer(8 * (world + 1))
+            self.flag_buf.as_tensor((8 * (world + 1),), torch.uint8).zero_()
+            self.flag_peers = None
         else:
             self.slabs = [torch.empty((per, T, D), dtype=torch.float32, device=dev) for _ in range(2)]
         if exchange == "nccl":
@@ -302,11 +308,15 @@ class DLRMRank:
         """fused exchange: swap IPC handles of the receive slabs with every rank."""
         import torch.distributed as dist
         handles = [None] * self.world
-        dist.all_gather_object(handles, [b.handle for b in self.slab_buf], group=self.group)
+        dist.all_gather_object(handles, [b.handle for b in self.slab_buf] + [self.flag_buf.handle], group=self.group)
         self.peers = []  # [slab][rank] -> base address
         for s in range(2):
             self.peers.append([self.slab_buf[s].ptr if r == self.rank else self.slab_buf[s].open(handles[r][s])
                                for r in range(self.world)])
+        flags = [self.flag_buf.ptr if r == self.rank else self.flag_buf.open(handles[r][2]) for r in range(self.world)]
+        self.flag_peers = torch.tensor(flags, dtype=torch.int64).to(self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # every rank's flags are zeroed and mapped before the first rendezvous
 
     def set_peers(self, ranks):
         """emulated exchange: every rank's slabs are plain tensors of this process."""
@@ -314,7 +324,7 @@ class DLRMRank:
 
     def release(self):
         if self.exchange == "fused":
-            for b in self.slab_buf:
+            for b in self.slab_buf + [self.flag_buf]:
                 b.release()
 
     # -- sparse part ---------------------------------------------------------------------
@@ -358,9 +368,12 @@ class DLRMRank:
                 self.slabs[slab].copy_(exchange_all_to_all(self.send, self.cfg, self.rank, self.world, self.group))
         elif self.exchange == "fused":
             # every rank's stores into every slab are complete once all pooling kernels have
-            # finished: a one-element all-reduce, enqueued on the stream, is that rendezvous (it
-            # never blocks the host and can be captured in a CUDA graph, unlike a barrier)
-            dist.all_reduce(self.token, group=self.group)
+            # finished: the rendezvous is a kernel on the stream (it never blocks the host and can
+            # be captured in a CUDA graph, unlike a barrier)
+            if self.rendezvous == "flags":
+                ops.peer_rendezvous(self.flag_buf.ptr, self.flag_peers, self.world, self.rank, self.status)
+            else:
+                dist.all_reduce(self.token, group=self.group)
         return self.slabs[slab]
 
     # -- dense part ----------------------------------------------------------------------

@@ -776,6 +776,13 @@ class PeerBuffer:
             self.ptr = 0
 
 
+def peer_rendezvous(my_flags_ptr, peer_ptrs_dev, world, rank, status=None, limit_cycles=4_000_000_000):
+    """One rendezvous of the ranks whose flag buffers are listed in the device array
+    `peer_ptrs_dev` (int64 tensor of `world` addresses); see glowb200_peer_rendezvous."""
+    check(_lib.lib().glowb200_peer_rendezvous(C.c_void_p(int(my_flags_ptr)), _p(peer_ptrs_dev), int(world), int(rank),
+                                              int(limit_cycles), _p(status), _stream()))
+
+
 class SlwsBatch:
     """A fixed set of tables of one kind and row width, pooled by ONE launch per request.
 

@@ -597,6 +597,18 @@ int glowb200_peer_buffer_create(size_t bytes, void **device_ptr, void *ipc_handl
 int glowb200_peer_buffer_open(const void *ipc_handle_64_bytes, void **device_ptr);
 int glowb200_peer_buffer_close(void *device_ptr);
 int glowb200_peer_buffer_destroy(void *device_ptr);
+/* Rendezvous of the ranks that store into each other's peer buffers, as one small kernel on
+ * the stream (no collective library call, replayable from a CUDA graph): `my_flags` is this
+ * rank's flag buffer -- a peer buffer of 8 * (world + 1) bytes, zeroed once -- and
+ * `peer_flags_device_array` a DEVICE array of the `world` ranks' flag-buffer addresses as this
+ * rank has them mapped (its own at index `rank`).  The kernel tells every peer that the work
+ * queued before it on the stream is stored, then waits until every peer has said the same for
+ * the same step; what is queued behind it may read what the peers stored.  The wait gives up
+ * after `limit_cycles` SM clocks and raises GLOWB200_STATUS_WAIT_TIMEOUT.  Replaces the
+ * host-mediated hand-off between the partitions of a network
+ * (lib/Runtime/Executor/NetworkExecutionState.cpp:129-255); no kernel counterpart in the reference. */
+int glowb200_peer_rendezvous(void *my_flags, void *const *peer_flags_device_array, int world, int rank,
+                             int64_t limit_cycles, int32_t *status, glowb200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Host runtime: the compiled-function and device-manager layer of a Glow backend, written

@@ -114,3 +114,30 @@ def test_partitioned_equals_unpartitioned(model, world):
     torch.cuda.synchronize()
     assert torch.equal(torch.cat(outs), want)
     assert torch.equal(torch.cat([r.slabs[0] for r in ranks]), whole.slabs[0])
+
+
+def test_peer_rendezvous_kernel_and_its_bounded_wait():
+    """The flag rendezvous of the fused exchange on one GPU: a rank alone meets itself (twice:
+    the step count advances), and a rank whose peer never signals gives up after its limit and
+    says so through the status word -- the context stays usable."""
+    buf = ops.PeerBuffer(8 * 3)
+    flags = buf.as_tensor((24,), torch.uint8)
+    flags.zero_()
+    st = ops.new_status(DEV)
+    alone = torch.tensor([buf.ptr], dtype=torch.int64, device=DEV)
+    ops.peer_rendezvous(buf.ptr, alone, 1, 0, st)
+    ops.peer_rendezvous(buf.ptr, alone, 1, 0, st)
+    torch.cuda.synchronize()
+    words = flags.view(torch.int64)
+    assert int(st.item()) == 0 and int(words[0]) == 2 and int(words[1]) == 2
+    # "two ranks", both mapped to this buffer, of which only rank 0 exists: slot 1 is never written
+    flags.zero_()
+    both = torch.tensor([buf.ptr, buf.ptr], dtype=torch.int64, device=DEV)
+    ops.peer_rendezvous(buf.ptr, both, 2, 0, st, limit_cycles=2_000_000)  # about a millisecond
+    torch.cuda.synchronize()
+    assert int(st.item()) == 16
+    st.zero_()
+    ops.peer_rendezvous(buf.ptr, alone, 1, 0, st)  # and the next launch is fine
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    buf.release()
