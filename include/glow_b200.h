@@ -239,7 +239,7 @@ int glowb200_rowwise_quantized_sparse_lengths_weighted_sum_f32(
     int64_t segments, int64_t num_indices, int64_t line_size, void *workspace,
     size_t workspace_bytes, int32_t *status, glowb200_stream_t stream);
 
-/* Weight preparation on the device (SURVEY row 11 for weights already resident on the GPU).
+/* Weight preparation on the device (host weight preparation for weights already resident on the GPU).
  * glowb200_tensor_rowwise_quantize_i8_device: tensorRowwiseQuantization<float,int32_t,int8_t>
  * (include/glow/Quantization/Base/Base.h:522-576) -- every row of an fp32 [rows, cols] matrix gets
  * its own parameters from its min and max (schema as glowb200_choose_quantization_params) and is
@@ -762,7 +762,13 @@ void glowb200_device_manager_destroy(glowb200_device_manager *dm);
  *   - All calls on a device share the one array.  Calls on the same stream are ordered and
  *     safe; calls that can overlap on the GPU (different streams, different host threads on
  *     different streams) race on it and must be serialised by the caller.
- *   - This entry point calls no cudaMalloc / cudaFree or any other allocating routine. */
+ *   - This entry point calls no cudaMalloc / cudaFree or any other allocating routine.  What it
+ *     cannot rule out is the CUDA runtime's own lazy module loading: the first launch of each
+ *     kernel variant (table kind x index type x row width class) may load its code then, and the
+ *     set-up call warms only the variant it uses -- make one set-up call per shape that will be
+ *     served, or run with CUDA_MODULE_LOADING=EAGER.
+ *   - The looked-up address is kept per device ordinal for the life of the process; it does not
+ *     survive a cudaDeviceReset (a process that resets a device must not call this afterwards). */
 int64_t glowb200_slws_static_scratch_max_segments(void);
 int glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum_static_scratch(
     void *dest, const void *data, int kind, int64_t rows, const void *weights, const void *indices,

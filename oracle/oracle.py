@@ -24,9 +24,19 @@ KIND_U8_F32, KIND_U8_F16, KIND_U4_F32, KIND_U4_F16 = 0, 1, 2, 3
 _i64, _i32, _f32, _vp = C.c_int64, C.c_int32, C.c_float, C.c_void_p
 
 
+def reference_dir():
+    """The checkout of pytorch/glow the reference libraries are compiled from: GLOW_REFERENCE_DIR,
+    else the `reference` directory beside the repository, when either exists."""
+    for d in (os.environ.get("GLOW_REFERENCE_DIR"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if d and os.path.exists(os.path.join(d, "lib", "LLVMIRCodeGen", "libjit", "libjit.cpp")):
+            return d
+    return ""
+
+
 def build(with_ref=True):
     """Compile liboracle.so (and, where the reference tree exists, oracle/_ref)."""
-    subprocess.check_call(["make", "-s", "-C", HERE, "all" if with_ref else HERE + "/liboracle.so"])
+    subprocess.check_call(["make", "-s", "-C", HERE, "all" if with_ref else HERE + "/liboracle.so",
+                           "REF=" + (reference_dir() if with_ref else "")])
 
 
 class _Ptr(C.c_void_p):
