@@ -902,7 +902,10 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
         return cudaGetLastError();
       }
       const int64_t max_segments = (int64_t)grid.x * (kGatherThreads >> L.lpr_log2);
-      const int64_t total = max_segments * grid.y, want = (int64_t)sm_count() * 24 * 4;
+      // (measured on the recommendation model's power-law bags: 262 144 bags in a launch pool
+      // fastest in runs of 4, 32 768 -- one rank's share of eight -- in single bags; the sums do
+      // not depend on the choice)
+      const int64_t total = max_segments * grid.y, want = (int64_t)sm_count() * 24 * 16;
       int bpw = (int)(total / want);
       bpw = bpw < 1 ? 1 : (bpw > GLOWB200_SLWS_MAX_BPW ? GLOWB200_SLWS_MAX_BPW : bpw);
       const int64_t warps = (max_segments + bpw - 1) / bpw;
