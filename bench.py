@@ -1363,6 +1363,7 @@ def run_slws4_sharded_line(args):
             reqs.append((torch.from_numpy(lengths).to(dev), indices, weights, starts))
     nbytes = [n * (line_bytes + 8 + 2) + T * B * (4 + 2 * D) for n in logical]
     results = {}
+    checked = {}
     clocks = None
     for form in (["local"] if world == 1 else ["fused", "nccl"]):
         op = sharded.RowShardedSLWS(ops.UINT4_FUSED_FP16, shards, [ROWS4] * T, B, rank, world, exchange=form)
@@ -1409,14 +1410,50 @@ def run_slws4_sharded_line(args):
             dist.all_reduce(tm, op=dist.ReduceOp.MAX)
         moved = sum(nbytes[i % R] for i in range(args.steps))
         results[form] = {"gbps": moved / (float(tm[0]) * 1e-3) / 1e9, "ms_per_step": float(tm[0]) / args.steps}
+        if world > 1:  # request 0 once more, from step 0 (slab 0), kept for the result checks below
+            op.step = 0
+            checked[form] = op.run(pair).clone()
+            barrier()
         op.release()
         del op, pair
         torch.cuda.empty_cache()
+    flags = {}
+    if world > 1:
+        # Result checks on the real GPUs: the two exchange forms against each other (they add the
+        # shards' fp32 partials in different orders, then round once to fp16), and table 0 against
+        # the unsharded operator -- its row shards gathered from all ranks, this rank's bags of the
+        # logical request pooled by the plain entry point (fp16 result: 2e-3 relative).
+        a, b = checked["fused"].float(), checked["nccl"].float()
+        forms_ok = bool(torch.allclose(a, b, rtol=4e-3, atol=0.05))
+        parts = [torch.empty_like(shards[0]) for _ in range(world)]
+        dist.all_gather(parts, shards[0])
+        whole = torch.cat(parts, 0)
+        rng = np.random.Generator(np.random.PCG64(4242))
+        lengths0 = rng.poisson(64, (T, B)).astype(np.int32)
+        starts0 = np.concatenate([[0], np.cumsum(lengths0.sum(1))]).astype(np.int64)
+        gi = torch.Generator(device=dev).manual_seed(99)
+        idx_all = torch.randint(0, ROWS4, (int(starts0[-1]),), device=dev, generator=gi)
+        w_all = torch.rand(int(starts0[-1]), device=dev, generator=gi).to(torch.float16)
+        per = B // world
+        cum = np.concatenate([[0], np.cumsum(lengths0[0])])
+        i0, i1 = int(cum[rank * per]), int(cum[(rank + 1) * per])
+        want = ops.fused_rowwise_quantized_sparse_lengths_weighted_sum(
+            whole, w_all[i0:i1].contiguous(), idx_all[i0:i1].contiguous(),
+            torch.from_numpy(lengths0[0, rank * per:(rank + 1) * per].copy()).to(dev), ops.UINT4_FUSED_FP16)
+        torch.cuda.synchronize()
+        whole_ok = bool(torch.allclose(checked["fused"][0].float(), want.float(), rtol=4e-3, atol=0.05))
+        fl = torch.tensor([int(forms_ok), int(whole_ok)], device=dev)
+        dist.all_reduce(fl, op=dist.ReduceOp.MIN)
+        flags = {"exchange_forms_agree": bool(int(fl[0])), "matches_unsharded": bool(int(fl[1]))}
+        del parts, whole, idx_all, w_all
+        if not all(flags.values()):
+            raise AssertionError("row-sharded results differ: %r" % flags)
     if rank == 0:
         peak, src = measured_peak_hbm()
         best = max(results.values(), key=lambda r: r["gbps"])
         per_gpu = best["gbps"] / world
         print(json.dumps({
+            "checks": flags,
             "metric": "frwq_slws_4bit_row_sharded_hbm_gbps", "value": best["gbps"], "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": best["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u4 -> f32 partial sums -> f16", "data": "synthetic",
