@@ -16,45 +16,119 @@ inline unsigned grid_for(int64_t work_items) {
 
 struct Triple { int32_t pre, post, scale; };
 
-// libjit_element_add_kernel_i8 (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED, libjit.cpp:1593-1603)
-__global__ void __launch_bounds__(kThreads) add_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
-                                                          const int8_t *__restrict__ rhs, int64_t n, int32_t dst_off,
-                                                          int32_t lhs_off, int32_t rhs_off, Triple lt, Triple rt) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    const int32_t l = scale32((int32_t)lhs[i] - lhs_off, lt.pre, lt.post, lt.scale, 0);
-    const int32_t r = scale32((int32_t)rhs[i] - rhs_off, rt.pre, rt.post, rt.scale, 0);
-    dst[i] = (int8_t)clip_i8(l + r + dst_off);
+// ------------------------------------------------------------------------------------------
+// Element-wise int8 kernels.  Each operator is a functor holding its constants; one kernel
+// applies it sixteen elements per thread (16-byte loads and stores, when all tensors start on
+// 16-byte boundaries) and finishes the tail -- or does everything, for unaligned tensors --
+// one element at a time.  These kernels only stream memory: a byte per thread, as they were
+// first written, reached a third of the copy bandwidth on a residual block's Add.
+// ------------------------------------------------------------------------------------------
+// libjit_element_add_kernel_i8 (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED, libjit.cpp:1593-1603),
+// optionally followed by libjit_element_maxsplat_kernel_i8 on its result (the Add and the int8
+// Relu of a residual block in one pass over memory).
+struct AddF {
+  int32_t dst_off, lhs_off, rhs_off;
+  Triple lt, rt;
+  int32_t splat;  // -128: no max-with-constant behind the add
+  __device__ __forceinline__ int32_t operator()(int32_t a, int32_t b) const {
+    const int32_t l = scale32(a - lhs_off, lt.pre, lt.post, lt.scale, 0);
+    const int32_t r = scale32(b - rhs_off, rt.pre, rt.post, rt.scale, 0);
+    const int32_t v = clip_i8(l + r + dst_off);
+    return v > splat ? v : splat;
   }
-}
+};
 
 // The other arithmetic mini-kernels of DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED (libjit.cpp:1593-1603,
 // 1675-1682): both sides rescaled to the result's scale, then sub / max / min, offset, clip.
 // OP 1 sub, 2 max, 3 min.
 template <int OP>
-__global__ void __launch_bounds__(kThreads) binary_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
-                                                             const int8_t *__restrict__ rhs, int64_t n, int32_t dst_off,
-                                                             int32_t lhs_off, int32_t rhs_off, Triple lt, Triple rt) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    const int32_t l = scale32((int32_t)lhs[i] - lhs_off, lt.pre, lt.post, lt.scale, 0);
-    const int32_t r = scale32((int32_t)rhs[i] - rhs_off, rt.pre, rt.post, rt.scale, 0);
+struct BinaryF {
+  int32_t dst_off, lhs_off, rhs_off;
+  Triple lt, rt;
+  __device__ __forceinline__ int32_t operator()(int32_t a, int32_t b) const {
+    const int32_t l = scale32(a - lhs_off, lt.pre, lt.post, lt.scale, 0);
+    const int32_t r = scale32(b - rhs_off, rt.pre, rt.post, rt.scale, 0);
     const int32_t v = OP == 1 ? (int32_t)((uint32_t)l - (uint32_t)r) : OP == 2 ? (l > r ? l : r) : (l < r ? l : r);
-    dst[i] = (int8_t)clip_i8((int32_t)((uint32_t)v + (uint32_t)dst_off));
+    return clip_i8((int32_t)((uint32_t)v + (uint32_t)dst_off));
   }
-}
+};
 
 // libjit_element_mul_kernel_i8 / _div_kernel_i8 (DEFINE_DATA_PARALLEL_KERNEL_QUANTIZED_M,
 // libjit.cpp:1610-1619, 1683-1684): the product (quotient) of the offset-free operands, one
 // rescale with the result's offset, clip.  A zero divisor gives the result offset (the
 // reference divides by it).
 template <bool DIV>
-__global__ void __launch_bounds__(kThreads) muldiv_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
-                                                             const int8_t *__restrict__ rhs, int64_t n, int32_t dst_off,
-                                                             int32_t lhs_off, int32_t rhs_off, Triple t) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    const int32_t l = (int32_t)lhs[i] - lhs_off, r = (int32_t)rhs[i] - rhs_off;
+struct MulDivF {
+  int32_t dst_off, lhs_off, rhs_off;
+  Triple t;
+  __device__ __forceinline__ int32_t operator()(int32_t a, int32_t b) const {
+    const int32_t l = a - lhs_off, r = b - rhs_off;
     const int32_t v = DIV ? (r == 0 ? 0 : l / r) : (int32_t)((uint32_t)l * (uint32_t)r);
-    dst[i] = (int8_t)clip_i8(scale32(v, t.pre, t.post, t.scale, dst_off));
+    return clip_i8(scale32(v, t.pre, t.post, t.scale, dst_off));
   }
+};
+
+// libjit_element_relu_i8 (libjit.cpp:1850-1858): max(x, srcOffset), then rescale
+struct ReluF {
+  int32_t src_off, dst_off;
+  Triple t;
+  __device__ __forceinline__ int32_t operator()(int32_t a, int32_t) const {
+    const int32_t v = a > src_off ? a : src_off;
+    return clip_i8(scale32(v - src_off, t.pre, t.post, t.scale, dst_off));
+  }
+};
+
+// libjit_element_maxsplat_kernel_i8 (lib/Backends/CPU/libjit_cpu/libjit_cpu.cpp:39-44)
+struct MaxSplatF {
+  int32_t splat;
+  __device__ __forceinline__ int32_t operator()(int32_t a, int32_t) const { return a > splat ? a : splat; }
+};
+
+// libjit_element_rescale_kernel_i8 (libjit.cpp:3030-3038)
+struct RescaleF {
+  int32_t out_off, in_off;
+  Triple t;
+  __device__ __forceinline__ int32_t operator()(int32_t a, int32_t) const {
+    return clip_i8(scale32(a - in_off, t.pre, t.post, t.scale, out_off));
+  }
+};
+
+template <typename F>
+__device__ __forceinline__ uint32_t map_word(uint32_t a, uint32_t b, const F &f) {
+  uint32_t o = 0;
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int32_t x = (int32_t)(int8_t)(a >> (8 * j)), y = (int32_t)(int8_t)(b >> (8 * j));
+    o |= ((uint32_t)f(x, y) & 0xFFu) << (8 * j);
+  }
+  return o;
+}
+
+// dst[i] = f(lhs[i], rhs[i]) (rhs may be NULL: f ignores its second argument).  vec: all three
+// pointers are 16-byte aligned.
+template <typename F>
+__global__ void __launch_bounds__(kThreads) map_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
+                                                          const int8_t *__restrict__ rhs, int64_t n, int vec, const F f) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t nv = vec ? (n >> 4) : 0;
+  for (int64_t i = tid; i < nv; i += stride) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4 *>(lhs) + i);
+    const uint4 b = rhs ? __ldg(reinterpret_cast<const uint4 *>(rhs) + i) : make_uint4(0u, 0u, 0u, 0u);
+    uint4 o;
+    o.x = map_word(a.x, b.x, f);
+    o.y = map_word(a.y, b.y, f);
+    o.z = map_word(a.z, b.z, f);
+    o.w = map_word(a.w, b.w, f);
+    reinterpret_cast<uint4 *>(dst)[i] = o;
+  }
+  for (int64_t i = (nv << 4) + tid; i < n; i += stride) dst[i] = (int8_t)f((int32_t)lhs[i], rhs ? (int32_t)rhs[i] : 0);
+}
+
+template <typename F>
+cudaError_t launch_map(int8_t *dst, const int8_t *lhs, const int8_t *rhs, int64_t n, const F &f, cudaStream_t s) {
+  const int vec = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15u) == 0;
+  map_i8_kernel<F><<<grid_for(vec ? (n + 15) / 16 : n), kThreads, 0, s>>>(dst, lhs, rhs, n, vec, f);
+  return cudaGetLastError();
 }
 
 // libjit_batchedadd_quantized (libjit.cpp:997-1015; entry points libjit_batchedadd_i8 and
@@ -72,65 +146,48 @@ __global__ void __launch_bounds__(kThreads) batched_add_i8_kernel(int8_t *__rest
   }
 }
 
-// The Add followed by the int8 Relu of a residual block (libjit_element_add_kernel_i8, then
-// libjit_element_maxsplat_kernel_i8 on its result) in one pass over memory.
-__global__ void __launch_bounds__(kThreads) add_maxsplat_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
-                                                                   const int8_t *__restrict__ rhs, int64_t n, int32_t dst_off,
-                                                                   int32_t lhs_off, int32_t rhs_off, Triple lt, Triple rt,
-                                                                   int32_t splat) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    const int32_t l = scale32((int32_t)lhs[i] - lhs_off, lt.pre, lt.post, lt.scale, 0);
-    const int32_t r = scale32((int32_t)rhs[i] - rhs_off, rt.pre, rt.post, rt.scale, 0);
-    const int32_t v = clip_i8(l + r + dst_off);
-    dst[i] = (int8_t)(v > splat ? v : splat);
-  }
-}
-
-// libjit_element_relu_i8 (libjit.cpp:1850-1858): max(x, srcOffset), then rescale
-__global__ void __launch_bounds__(kThreads) relu_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ src, int64_t n,
-                                                           int32_t src_off, int32_t dst_off, Triple t) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    const int32_t v = (int32_t)src[i] > src_off ? (int32_t)src[i] : src_off;
-    dst[i] = (int8_t)clip_i8(scale32(v - src_off, t.pre, t.post, t.scale, dst_off));
-  }
-}
-
-// libjit_element_maxsplat_kernel_i8 (lib/Backends/CPU/libjit_cpu/libjit_cpu.cpp:39-44)
-__global__ void __launch_bounds__(kThreads) maxsplat_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ src,
-                                                               int64_t n, int8_t splat) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-    dst[i] = src[i] > splat ? src[i] : splat;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kThreads) splat_kernel(T *__restrict__ dst, int64_t n, T value) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = value;
 }
 
-// libjit_element_rescale_kernel_i8 (libjit.cpp:3030-3038)
-__global__ void __launch_bounds__(kThreads) rescale_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ src,
-                                                              int64_t n, int32_t out_off, int32_t in_off, Triple t) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-    dst[i] = (int8_t)clip_i8(scale32((int32_t)src[i] - in_off, t.pre, t.post, t.scale, out_off));
-}
-
 // libjit_element_quantize_kernel_i8 (libjit.cpp:2997-3002): nearbyintf(x / scale + offset) in
 // fp32 with round-half-even, then clip.  The division and the addition are separate roundings.
+__device__ __forceinline__ int32_t quantize_one(float x, float scale, int32_t offset) {
+  const float t = __fadd_rn(__fdiv_rn(x, scale), (float)offset);
+  // values beyond the int32 range clip either way; keep the conversion defined
+  const float c = fminf(fmaxf(nearbyintf(t), -2147483648.0f), 2147483520.0f);
+  return clip_i8((int32_t)c);
+}
+// vec: both tensors 16-byte aligned -- four floats in, four bytes out per step
 __global__ void __launch_bounds__(kThreads) quantize_i8_kernel(int8_t *__restrict__ dst, const float *__restrict__ src,
-                                                               int64_t n, float scale, int32_t offset) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    const float t = __fadd_rn(__fdiv_rn(src[i], scale), (float)offset);
-    // values beyond the int32 range clip either way; keep the conversion defined
-    const float c = fminf(fmaxf(nearbyintf(t), -2147483648.0f), 2147483520.0f);
-    dst[i] = (int8_t)clip_i8((int32_t)c);
+                                                               int64_t n, float scale, int32_t offset, int vec) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t nv = vec ? (n >> 2) : 0;
+  for (int64_t i = tid; i < nv; i += stride) {
+    const float4 x = __ldg(reinterpret_cast<const float4 *>(src) + i);
+    const uint32_t o = ((uint32_t)quantize_one(x.x, scale, offset) & 0xFFu) | (((uint32_t)quantize_one(x.y, scale, offset) & 0xFFu) << 8) |
+                       (((uint32_t)quantize_one(x.z, scale, offset) & 0xFFu) << 16) | (((uint32_t)quantize_one(x.w, scale, offset) & 0xFFu) << 24);
+    reinterpret_cast<uint32_t *>(dst)[i] = o;
   }
+  for (int64_t i = (nv << 2) + tid; i < n; i += stride) dst[i] = (int8_t)quantize_one(src[i], scale, offset);
 }
 
 // libjit_element_dequantize_kernel_i8 (libjit.cpp:3014-3018)
 __global__ void __launch_bounds__(kThreads) dequantize_i8_kernel(float *__restrict__ dst, const int8_t *__restrict__ src,
-                                                                 int64_t n, float scale, int32_t offset) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-    dst[i] = __fmul_rn(scale, (float)((int32_t)src[i] - offset));
+                                                                 int64_t n, float scale, int32_t offset, int vec) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t nv = vec ? (n >> 2) : 0;
+  for (int64_t i = tid; i < nv; i += stride) {
+    const uint32_t q = __ldg(reinterpret_cast<const uint32_t *>(src) + i);
+    float4 o;
+    o.x = __fmul_rn(scale, (float)((int32_t)(int8_t)q - offset));
+    o.y = __fmul_rn(scale, (float)((int32_t)(int8_t)(q >> 8) - offset));
+    o.z = __fmul_rn(scale, (float)((int32_t)(int8_t)(q >> 16) - offset));
+    o.w = __fmul_rn(scale, (float)((int32_t)(int8_t)(q >> 24) - offset));
+    reinterpret_cast<float4 *>(dst)[i] = o;
+  }
+  for (int64_t i = (nv << 2) + tid; i < n; i += stride) dst[i] = __fmul_rn(scale, (float)((int32_t)src[i] - offset));
 }
 
 struct PoolGeom { int N, H, W, C, OH, OW, KH, KW, SH, SW, PT, PL; };
@@ -274,10 +331,10 @@ extern "C" int glowb200_element_add_i8(int8_t *dest, const int8_t *lhs, const in
                                        int32_t lhs_scale, int32_t rhs_pre, int32_t rhs_post, int32_t rhs_scale,
                                        glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && lhs && rhs)
-  add_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset,
-                                                               Triple{lhs_pre, lhs_post, lhs_scale},
-                                                               Triple{rhs_pre, rhs_post, rhs_scale});
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(launch_map(dest, lhs, rhs, n,
+                              AddF{dest_offset, lhs_offset, rhs_offset, Triple{lhs_pre, lhs_post, lhs_scale},
+                                   Triple{rhs_pre, rhs_post, rhs_scale}, -128},
+                              GLOWB200_STREAM));
   return GLOWB200_OK;
 }
 
@@ -288,21 +345,22 @@ extern "C" int glowb200_element_binary_i8(int op, int8_t *dest, const int8_t *lh
   GLOWB200_REQUIRE(op >= GLOWB200_BINARY_ADD && op <= GLOWB200_BINARY_MIN, "unknown binary operator %d", op);
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && lhs && rhs)
   const Triple lt{lhs_pre, lhs_post, lhs_scale}, rt{rhs_pre, rhs_post, rhs_scale};
+  cudaError_t e;
   switch (op) {
     case GLOWB200_BINARY_ADD:
-      add_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset, lt, rt);
+      e = launch_map(dest, lhs, rhs, n, AddF{dest_offset, lhs_offset, rhs_offset, lt, rt, -128}, GLOWB200_STREAM);
       break;
     case GLOWB200_BINARY_SUB:
-      binary_i8_kernel<1><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset, lt, rt);
+      e = launch_map(dest, lhs, rhs, n, BinaryF<1>{dest_offset, lhs_offset, rhs_offset, lt, rt}, GLOWB200_STREAM);
       break;
     case GLOWB200_BINARY_MAX:
-      binary_i8_kernel<2><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset, lt, rt);
+      e = launch_map(dest, lhs, rhs, n, BinaryF<2>{dest_offset, lhs_offset, rhs_offset, lt, rt}, GLOWB200_STREAM);
       break;
     default:
-      binary_i8_kernel<3><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset, lt, rt);
+      e = launch_map(dest, lhs, rhs, n, BinaryF<3>{dest_offset, lhs_offset, rhs_offset, lt, rt}, GLOWB200_STREAM);
       break;
   }
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(e);
   return GLOWB200_OK;
 }
 
@@ -311,12 +369,11 @@ extern "C" int glowb200_element_muldiv_i8(int is_div, int8_t *dest, const int8_t
                                           int32_t post, int32_t scale, glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && lhs && rhs)
   if (is_div)
-    muldiv_i8_kernel<true><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset,
-                                                                         Triple{pre, post, scale});
+    GLOWB200_CUDA_OK(launch_map(dest, lhs, rhs, n, MulDivF<true>{dest_offset, lhs_offset, rhs_offset, Triple{pre, post, scale}},
+                                GLOWB200_STREAM));
   else
-    muldiv_i8_kernel<false><<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset,
-                                                                          Triple{pre, post, scale});
-  GLOWB200_CUDA_OK(cudaGetLastError());
+    GLOWB200_CUDA_OK(launch_map(dest, lhs, rhs, n, MulDivF<false>{dest_offset, lhs_offset, rhs_offset, Triple{pre, post, scale}},
+                                GLOWB200_STREAM));
   return GLOWB200_OK;
 }
 
@@ -345,19 +402,18 @@ extern "C" int glowb200_element_add_maxsplat_i8(int8_t *dest, const int8_t *lhs,
                                                 int32_t rhs_scale, int32_t splat, glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && lhs && rhs)
   GLOWB200_REQUIRE(splat >= -128 && splat <= 127, "splat value outside int8");
-  add_maxsplat_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, lhs, rhs, n, dest_offset, lhs_offset, rhs_offset,
-                                                                        Triple{lhs_pre, lhs_post, lhs_scale},
-                                                                        Triple{rhs_pre, rhs_post, rhs_scale}, splat);
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(launch_map(dest, lhs, rhs, n,
+                              AddF{dest_offset, lhs_offset, rhs_offset, Triple{lhs_pre, lhs_post, lhs_scale},
+                                   Triple{rhs_pre, rhs_post, rhs_scale}, splat},
+                              GLOWB200_STREAM));
   return GLOWB200_OK;
 }
 
 extern "C" int glowb200_element_relu_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t src_offset, int32_t dest_offset,
                                         int32_t dest_pre, int32_t dest_post, int32_t dest_scale, glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
-  relu_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, src_offset, dest_offset,
-                                                                Triple{dest_pre, dest_post, dest_scale});
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(launch_map(dest, src, nullptr, n, ReluF{src_offset, dest_offset, Triple{dest_pre, dest_post, dest_scale}},
+                              GLOWB200_STREAM));
   return GLOWB200_OK;
 }
 
@@ -365,8 +421,7 @@ extern "C" int glowb200_element_maxsplat_i8(int8_t *dest, const int8_t *src, int
                                             glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
   GLOWB200_REQUIRE(splat >= -128 && splat <= 127, "splat value outside int8");
-  maxsplat_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, (int8_t)splat);
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(launch_map(dest, src, nullptr, n, MaxSplatF{splat}, GLOWB200_STREAM));
   return GLOWB200_OK;
 }
 
@@ -381,15 +436,15 @@ extern "C" int glowb200_splat_f(void *dest, int64_t n, float value, int dest_is_
 extern "C" int glowb200_element_rescale_i8(int8_t *dest, const int8_t *src, int64_t n, int32_t out_offset, int32_t in_offset,
                                            int32_t pre, int32_t post, int32_t scale, glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
-  rescale_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, out_offset, in_offset, Triple{pre, post, scale});
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(launch_map(dest, src, nullptr, n, RescaleF{out_offset, in_offset, Triple{pre, post, scale}}, GLOWB200_STREAM));
   return GLOWB200_OK;
 }
 
 extern "C" int glowb200_element_quantize_i8(int8_t *dest, const float *src, int64_t n, float scale, int32_t offset,
                                             glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
-  quantize_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, scale, offset);
+  const int vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dest) & 3u) == 0;
+  quantize_i8_kernel<<<grid_for(vec ? (n + 3) / 4 : n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, scale, offset, vec);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }
@@ -397,7 +452,8 @@ extern "C" int glowb200_element_quantize_i8(int8_t *dest, const float *src, int6
 extern "C" int glowb200_element_dequantize_i8(float *dest, const int8_t *src, int64_t n, float scale, int32_t offset,
                                               glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
-  dequantize_i8_kernel<<<grid_for(n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, scale, offset);
+  const int vec = (reinterpret_cast<uintptr_t>(dest) & 15u) == 0 && (reinterpret_cast<uintptr_t>(src) & 3u) == 0;
+  dequantize_i8_kernel<<<grid_for(vec ? (n + 3) / 4 : n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, scale, offset, vec);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }

@@ -135,6 +135,25 @@ def test_elementwise_and_pools_bit_exact(oracle):
                                           oracle.avg_pool_i8(x, ohw, k, s, p, cip, 3, -4, tr))
 
 
+def test_elementwise_kernels_on_unaligned_tensors(oracle):
+    """Tensors that do not start on 16-byte boundaries take the element-at-a-time path of the
+    element-wise kernels: same results."""
+    rng = np.random.default_rng(17)
+    a = rng.integers(-128, 128, 5_001).astype(np.int8)
+    b = rng.integers(-128, 128, 5_001).astype(np.int8)
+    lt, rt = ops.quantize_scale_offset_32to8(0.7), ops.quantize_scale_offset_32to8(1.9)
+    da, dl, dr = t(a)[1:], t(a)[1:4_999], t(b)[3:5_001]
+    assert da.data_ptr() % 16 and dr.data_ptr() % 16 and dl.numel() == dr.numel()
+    np.testing.assert_array_equal(ops.element_add_maxsplat_i8(dl, dr, 5, -3, 9, lt, rt, -20).cpu().numpy(),
+                                  oracle.element_maxsplat_i8(oracle.element_add_i8(a[1:4_999], b[3:5_001], 5, -3, 9, lt, rt), -20))
+    np.testing.assert_array_equal(ops.element_relu_i8(da, -10, 4, lt).cpu().numpy(), oracle.element_relu_i8(a[1:], -10, 4, lt))
+    np.testing.assert_array_equal(ops.element_rescale_i8(da, 3, -2, rt).cpu().numpy(), oracle.element_rescale_i8(a[1:], 3, -2, rt))
+    f = (rng.standard_normal(1_003) * 3).astype(np.float32)
+    np.testing.assert_array_equal(ops.element_quantize_i8(t(f)[1:], 0.05, 3).cpu().numpy(), oracle.element_quantize_i8(f[1:], 0.05, 3))
+    np.testing.assert_array_equal(ops.element_dequantize_i8(da, 0.037, -4).cpu().numpy().view(np.uint32),
+                                  oracle.element_dequantize_i8(a[1:], 0.037, -4).view(np.uint32))
+
+
 def test_max_pool_sixteen_channels_per_thread(oracle):
     rng = np.random.default_rng(29)
     x = rng.integers(-128, 128, (3, 21, 18, 64)).astype(np.int8)
