@@ -39,26 +39,14 @@ constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kGemmThreads = 64 + kEpilogueThreads;  // TMA warp, MMA warp, epilogue warps
 constexpr long long kWaitCycles = 2000000000ll;  // ~1 s: far beyond any legitimate wait
 
-// Per output column, built once per tile in shared memory and read back with ONE 16-byte
-// broadcast load per element.  Measured on B200: shared-memory loads issue at about one per
-// clock per SM and 32-bit integer instructions at about two warps per clock per SM, so the
-// epilogue spends integer work (unpacking the shifts, rebuilding the rounding term) to save
-// loads -- a 32-byte record with everything precomputed (two loads per element) was slower.
+// Per output column, built once per column block in shared memory and read back with one
+// 16-byte load per record.
 struct __align__(16) ColParams {
   int32_t c;        // bias term - aOff*rowsum(B_j) + K*aOff*bOff_j
   int32_t scale;    // integer multiplier of the output rescale
   int32_t shifts;   // pre | post << 8
-  int32_t b_off;
+  int32_t b_off;    // weight offset
 };
-
-// sat8(v3) sat8(v2) sat8(v1) sat8(v0) packed little-endian: libjit_clip_i8 on four values and the
-// byte packing in two instructions.
-__device__ __forceinline__ uint32_t clip_pack4(int32_t v0, int32_t v1, int32_t v2, int32_t v3) {
-  uint32_t hi, d;
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(v3), "r"(v2), "r"(0));
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v1), "r"(v0), "r"(hi));
-  return d;
-}
 
 // ---------------------------------------------------------------------------------------
 // PTX wrappers
@@ -157,18 +145,6 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
 template <int N>
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[N]) {
   asm volatile(
@@ -178,6 +154,13 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+// rows 16 lanes from the address's lane on, 16 columns: see the drain of the int8 result for the layout
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t *r) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -249,6 +232,17 @@ __global__ void __launch_bounds__(128) i8_mma_issue_probe_kernel(int mmas, int32
   if (threadIdx.x < 32) tmem_dealloc(tmem_base, 512);
 }
 
+// Byte offset of 16-byte piece q16 of row r (0..31) in a quarter's staging area of PITCH-byte rows.
+// The piece index is xor-ed with the row's position among the rows that share 128 bytes of banks, so
+// eight lanes writing the same piece of eight consecutive rows, and eight lanes reading consecutive
+// pieces of one row (or of neighbouring short rows), each cover all 32 banks once.
+template <int PITCH>
+__device__ __forceinline__ int stage_offset(int r, int q16) {
+  constexpr int n = PITCH / 16;
+  const int x = n >= 8 ? (r & 7) : ((r / (8 / n)) & (n - 1));
+  return r * PITCH + 16 * (q16 ^ x);
+}
+
 // Optional phase tracing for tuning builds (-DGLOWB200_GEMM_TRACE): CTA 0 writes globaltimer
 // stamps to a device buffer the tuning harness reads back.  Compiled out by default.
 #ifdef GLOWB200_GEMM_TRACE
@@ -275,7 +269,11 @@ struct GemmSmem {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTileBytes = STAGES * kStageBytes;
   static constexpr int kColBytes = BLOCK_N * (int)sizeof(ColParams);
-  static constexpr int kTotal = kTileBytes + kColBytes + 256 /*barriers*/ + 1024 /*alignment slack*/;
+  // The int8 result of a tile on its way out: 128 rows of kOutPitch bytes, then the output row of each.
+  static constexpr int kOutPitch = BLOCK_N <= 32 ? 32 : BLOCK_N <= 64 ? 64 : BLOCK_N <= 128 ? 128 : 256;
+  static constexpr int kOutBytes = kBlockM * kOutPitch + kBlockM * 4;
+  static constexpr int kTotal = kTileBytes + kColBytes + kOutBytes + 256 /*barriers*/ + 1024 /*alignment slack*/;
+  static_assert(kTotal <= 232448, "more shared memory than a CTA can have");
 };
 
 // Persistent: gridDim.x CTAs walk the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...
@@ -295,7 +293,9 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   // 128-byte swizzled tiles must start on 1024-byte boundaries.
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   ColParams *cols = reinterpret_cast<ColParams *>(smem + S::kTileBytes);
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem + S::kTileBytes + S::kColBytes);
+  uint8_t *out_stage = smem + S::kTileBytes + S::kColBytes;
+  int32_t *out_rows = reinterpret_cast<int32_t *>(out_stage + kBlockM * S::kOutPitch);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem + S::kTileBytes + S::kColBytes + S::kOutBytes);
   uint64_t *empty = full + STAGES;
   uint64_t *acc_full = empty + STAGES;   // [2]
   uint64_t *acc_empty = acc_full + 2;    // [2]
@@ -397,12 +397,9 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int col_group = (warp - 2) >> 2;     // 0..3
     // columns per warp, in whole 16-column drains: 64 (BLOCK_N 256 and 240, whose last group has 48) ... 16 (BLOCK_N 64)
     constexpr int kGroupCols = ((BLOCK_N / 16 + 3) / 4) * 16;
-    // columns drained from tensor memory per load: 16 keeps the drain loop inside the 96 registers
-    // a 576-thread CTA leaves (32 spills, and measured slower)
-#ifndef GLOWB200_GEMM_CHUNK
-#define GLOWB200_GEMM_CHUNK 16
-#endif
-    constexpr int kChunk = kGroupCols >= GLOWB200_GEMM_CHUNK ? GLOWB200_GEMM_CHUNK : 16;
+    // columns drained from tensor memory per step: 16 keeps the drain loop inside the 96 registers
+    // a 576-thread CTA leaves
+    constexpr int kChunk = 16;
     const bool vec_ok = ((p.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     int lt = 0;
     int cols_n0 = -1;  // column block the records in shared memory belong to
@@ -414,39 +411,32 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       // column block: the records are rebuilt only when it changes (all epilogue threads see the
       // same n0, so the barriers stay matched).
       if (n0 != cols_n0) {
-      if (cols_n0 >= 0) asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");  // everyone is done with the old records
-      cols_n0 = n0;
-      for (int c = et; c < BLOCK_N; c += kEpilogueThreads) {
-        const int j = n0 + c;
+        if (cols_n0 >= 0) asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");  // everyone is done with the old records
+        cols_n0 = n0;
+        static_assert(BLOCK_N <= kEpilogueThreads, "one column record per epilogue thread");
+        const int j = n0 + et;
         ColParams cp = {0, 0, 0, 0};
-        if constexpr (MODE == 2) {  // {unused, column scale, float bias, weight offset}
-          if (j < p.N) {
+        if (et < BLOCK_N && j < p.N) {
+          if constexpr (MODE == 2) {  // {unused, column scale, float bias, weight offset}
             cp.scale = __float_as_int(p.col_scales ? p.col_scales[j] : p.u_col_scale);
             cp.shifts = __float_as_int(p.bias_f32[j]);
             cp.b_off = p.b_offsets ? p.b_offsets[j] : p.u_b_offset;
-          }
-        } else
-        if (j < p.N) {
-          const ColQuant q = col_quant(p, j);
-          int32_t term = 0;
-          if (p.bias)
-            term = scale32(load_bias(p, j) - (p.bias_offsets ? p.bias_offsets[j] : p.bias_offset), q.bias_pre, q.bias_post,
-                           q.bias_scale, 0);
-          const uint32_t corr = (uint32_t)term - (uint32_t)p.a_offset * (uint32_t)p.b_row_sums[j] +
-                                (uint32_t)p.k_corr * (uint32_t)p.a_offset * (uint32_t)q.b_off;
-          cp.c = (int32_t)corr;
-          cp.scale = q.out_scale;
-          if constexpr (MODE == 0) {  // {c, scale, rounding term, pre | post << 8}
-            cp.shifts = (int32_t)((1u << q.out_post) >> 1);
-            cp.b_off = q.out_pre | (q.out_post << 8);
           } else {                    // {c, scale, pre | post << 8, weight offset}
+            const ColQuant q = col_quant(p, j);
+            int32_t term = 0;
+            if (p.bias)
+              term = scale32(load_bias(p, j) - (p.bias_offsets ? p.bias_offsets[j] : p.bias_offset), q.bias_pre, q.bias_post,
+                             q.bias_scale, 0);
+            const uint32_t corr = (uint32_t)term - (uint32_t)p.a_offset * (uint32_t)p.b_row_sums[j] +
+                                  (uint32_t)p.k_corr * (uint32_t)p.a_offset * (uint32_t)q.b_off;
+            cp.c = (int32_t)corr;
+            cp.scale = q.out_scale;
             cp.shifts = q.out_pre | (q.out_post << 8);
             cp.b_off = q.b_off;
           }
         }
-        cols[c] = cp;
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");  // epilogue warps only
+        if (et < BLOCK_N) cols[et] = cp;
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");  // epilogue warps only
       }
       // (2) drain the accumulators of this tile
       const int row = m0 + quarter * 32 + lane;
@@ -465,35 +455,33 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       tc_fence_after();
       if (!ok) break;
       GEMM_TRACE(4, lt == 0 && et == 0);
-      const int32_t a_sum = (p.a_row_sums && row < p.M) ? p.a_row_sums[row] : 0;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kAccCols;
-      int8_t *out_row = p.out + (size_t)row * p.N + n0;
+      int out_index = row;  // row of the result this accumulator row becomes
       bool row_ok = row < p.M;
       if (p.conv_entries > 0) {  // padded pixel -> (image, oh, ow); the halo rows are dropped
         const int img = row / p.conv_hpwp, rem = row - img * p.conv_hpwp;
         const int oh = rem / p.conv_wp, ow = rem - oh * p.conv_wp;
         row_ok = row_ok && oh < p.conv_oh && ow < p.conv_ow;
-        out_row = p.out + ((size_t)(img * p.conv_oh + oh) * p.conv_ow + ow) * p.N + n0;
+        out_index = (img * p.conv_oh + oh) * p.conv_ow + ow;
       }
-      const int32_t relu_floor = p.act_type == 1 ? p.out_offset : INT32_MIN;
       const int c_end = (col_group + 1) * kGroupCols < BLOCK_N ? (col_group + 1) * kGroupCols : BLOCK_N;
+      if constexpr (MODE == 2) {
+        // float(sum) * (row scale * column scale) + bias, each operation rounded on its own
+        // (fwdDynRowwiseQuantizedFullyConnectedInstImpl, InterpreterNodes.cpp:4690-4702), then fp16.
+        // One accumulator row per lane (the 32x32b shape), a 16-byte record per element.
+        const int32_t a_sum = (p.a_row_sums && row < p.M) ? p.a_row_sums[row] : 0;
+        const float row_scale = row < p.M ? p.row_scales[row] : 0.0f;
 #pragma unroll 1
-      for (int c0 = col_group * kGroupCols; c0 < c_end; c0 += kChunk) {
-        uint32_t acc[kChunk];
-        if constexpr (kChunk == 32) tmem_ld_32x32b_x32(lane_addr + (uint32_t)c0, reinterpret_cast<uint32_t(&)[32]>(acc));
-        else tmem_ld_32x32b_x16(lane_addr + (uint32_t)c0, acc);
-        tmem_ld_wait();
-        GEMM_TRACE(7, lt == 0 && et == 0 && c0 == 0);
-        if (c0 + kChunk >= c_end) {
-          // everything this warp needs from the buffer is in registers: hand it back
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        }
-        if constexpr (MODE == 2) {
-          // float(sum) * (row scale * column scale) + bias, each operation rounded on its own
-          // (fwdDynRowwiseQuantizedFullyConnectedInstImpl, InterpreterNodes.cpp:4690-4702), then fp16
-          const float row_scale = row < p.M ? p.row_scales[row] : 0.0f;
+        for (int c0 = col_group * kGroupCols; c0 < c_end; c0 += kChunk) {
+          uint32_t acc[kChunk];
+          tmem_ld_32x32b_x16(lane_addr + (uint32_t)c0, acc);
+          tmem_ld_wait();
+          if (c0 + kChunk >= c_end) {
+            // everything this warp needs from the buffer is in registers: hand it back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
           uint32_t h2[kChunk / 2];
 #pragma unroll
           for (int i2 = 0; i2 < kChunk / 2; i2++) {
@@ -517,53 +505,99 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 if (n0 + c0 + i < p.N) orow[i] = __ushort_as_half((unsigned short)((h2[i >> 1] >> (16 * (i & 1))) & 0xffffu));
             }
           }
-        } else {
-        uint32_t packed[kChunk / 4];
-        // the requantisation: libjit_scale, ((v >> pre) * scale + rtn) >> post, then + offset, with
-        // rtn = 1 << (post - 1) (0 for post 0); Relu is max(x, out_offset), no activation max(x, INT_MIN)
+        }
+      } else {
+        // The int8 result.  A column's record is 16 bytes, and shared memory delivers 128 bytes
+        // per clock per SM whether the lanes of a load read one address or 32: with one accumulator
+        // row per lane (the 32x32b shape) every element costs a 16-byte broadcast load, 4096 clocks
+        // for a 128 x 256 tile and, measured, the whole duration of its drain.  The 16x256b shape
+        // hands each lane two neighbouring columns of four rows per eight columns instead -- register
+        // i of the load of rows 16h..16h+15 holds row 16h + lane/4 + 8*((i>>1)&1), column
+        // 8*(i>>2) + 2*(lane%4) + (i&1) -- so a record is loaded once per four elements.
+        // A lane then owns two bytes of a row, and a warp's stores would be scattered over 32
+        // lines either way (16-byte stores by row took 6500 clocks per 128 x 256 tile): the tile
+        // passes through shared memory, swizzled in 16-byte pieces so that neither the writes nor
+        // the reads along rows meet in a bank, and leaves as whole rows.
+        const int jq = lane & 3, r0 = lane >> 2;
+        uint8_t *stage_q = out_stage + quarter * 32 * S::kOutPitch;
+        int32_t a_sums[4] = {0, 0, 0, 0};
+        if constexpr (MODE == 1) {
+          if (p.a_row_sums) {
 #pragma unroll
-        for (int i4 = 0; i4 < kChunk / 4; i4++) {
-          int32_t r[4];
+            for (int i = 0; i < 4; i++) {
+              const int rr = m0 + quarter * 32 + 8 * i + r0;
+              a_sums[i] = rr < p.M ? p.a_row_sums[rr] : 0;
+            }
+          }
+        }
+        const int32_t relu_floor = p.act_type == 1 ? p.out_offset : INT32_MIN;
+        asm volatile("bar.sync %0, 128;" ::"r"(2 + quarter) : "memory");  // the quarter has read the last tile back
+#pragma unroll 1
+        for (int c0 = col_group * kGroupCols; c0 < c_end; c0 += kChunk) {
+          uint32_t acc[16];  // [row half h][column group g][row rr][column cc] -> 8h + 4g + 2rr + cc
+          tmem_ld_16x256b_x2(lane_addr + (uint32_t)c0, &acc[0]);
+          tmem_ld_16x256b_x2(lane_addr + (16u << 16) + (uint32_t)c0, &acc[8]);
+          tmem_ld_wait();
+          GEMM_TRACE(7, lt == 0 && et == 0 && c0 == 0);
+          if (c0 + kChunk >= c_end) {
+            // everything this warp needs from the buffer is in registers: hand it back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+          // the requantisation: libjit_scale, ((v >> pre) * scale + rtn) >> post, then + offset, with
+          // rtn = 1 << (post - 1) (0 for post 0); Relu is max(x, out_offset), no activation max(x, INT_MIN)
 #pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const int4 cp = *reinterpret_cast<const int4 *>(&cols[c0 + 4 * i4 + e]);
-            uint32_t v = acc[4 * i4 + e] + (uint32_t)cp.x;
-            int32_t m, post;
-            if constexpr (MODE == 0) {
-              const int32_t pre = cp.w & 0xff;
-              post = cp.w >> 8;
-              m = (int32_t)((uint32_t)((int32_t)v >> pre) * (uint32_t)cp.y + (uint32_t)cp.z);
-            } else {
-              v -= (uint32_t)cp.w * (uint32_t)a_sum;  // a_sum is 0 when no row sums take part
-              const int32_t pre = cp.z & 0xff;
-              post = cp.z >> 8;
+          for (int g = 0; g < 2; g++) {
+            int32_t res[2][4];  // [cc][row 8*i + r0 of the quarter]
+#pragma unroll
+            for (int cc = 0; cc < 2; cc++) {
+              const int4 cp = *reinterpret_cast<const int4 *>(&cols[c0 + 8 * g + 2 * jq + cc]);
+              const int32_t pre = cp.z & 0xff, post = cp.z >> 8;
               const uint32_t rtn = (1u << post) >> 1;
-              m = (int32_t)((uint32_t)((int32_t)v >> pre) * (uint32_t)cp.y + rtn);
-            }
-            int32_t x = (int32_t)((uint32_t)(m >> post) + (uint32_t)p.out_offset);
-            x = x > relu_floor ? x : relu_floor;
-            if constexpr (MODE == 1) {
-              if (p.act_type > 1) x = activation_i32(x, p);
-            }
-            r[e] = x;
-          }
-          packed[i4] = clip_pack4(r[0], r[1], r[2], r[3]);
-        }
-        GEMM_TRACE(8, lt == 0 && et == 0 && c0 == 0 && packed[0] != 0x12345678u);
-        if (row_ok) {
-          if (vec_ok && n0 + c0 + kChunk <= p.N) {
 #pragma unroll
-            for (int v4 = 0; v4 < kChunk / 16; v4++)
-              *reinterpret_cast<uint4 *>(out_row + c0 + 16 * v4) =
-                  make_uint4(packed[4 * v4], packed[4 * v4 + 1], packed[4 * v4 + 2], packed[4 * v4 + 3]);
+              for (int i = 0; i < 4; i++) {  // i = 2h + rr
+                uint32_t v = acc[8 * (i >> 1) + 4 * g + 2 * (i & 1) + cc] + (uint32_t)cp.x;
+                if constexpr (MODE == 1) v -= (uint32_t)cp.w * (uint32_t)a_sums[i];  // 0 when no row sums take part
+                const int32_t m = (int32_t)((uint32_t)((int32_t)v >> pre) * (uint32_t)cp.y + rtn);
+                int32_t x = (int32_t)((uint32_t)(m >> post) + (uint32_t)p.out_offset);
+                x = x > relu_floor ? x : relu_floor;
+                if constexpr (MODE == 1) {
+                  if (p.act_type > 1) x = activation_i32(x, p);
+                }
+                res[cc][i] = x;
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              uint32_t two;  // sat8(column cc = 1) << 8 | sat8(column cc = 0): libjit_clip_i8 and the packing in one
+              asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(two) : "r"(res[1][i]), "r"(res[0][i]), "r"(0));
+              const int col = c0 + 8 * g + 2 * jq;
+              *reinterpret_cast<uint16_t *>(stage_q + stage_offset<S::kOutPitch>(8 * i + r0, col >> 4) + (col & 15)) = (uint16_t)two;
+            }
+          }
+          GEMM_TRACE(9, lt == 0 && et == 0 && c0 == 0);
+        }
+        constexpr int kRowPieces = S::kOutPitch / 16;
+        if (col_group == 0) out_rows[quarter * 32 + lane] = row_ok ? out_index : -1;
+        asm volatile("bar.sync %0, 128;" ::"r"(2 + quarter) : "memory");  // the quarter's 32 rows are complete
+        const bool whole = vec_ok && n0 + BLOCK_N <= p.N;
+#pragma unroll
+        for (int piece = col_group * 32 + lane; piece < 32 * kRowPieces; piece += 128) {
+          const int r = piece / kRowPieces, q16 = piece % kRowPieces;
+          const int dst = out_rows[quarter * 32 + r];
+          if (q16 * 16 >= BLOCK_N || dst < 0) continue;
+          const uint4 v = *reinterpret_cast<const uint4 *>(stage_q + stage_offset<S::kOutPitch>(r, q16));
+          int8_t *o = p.out + (size_t)dst * p.N + n0 + q16 * 16;
+          if (whole) {
+            *reinterpret_cast<uint4 *>(o) = v;
           } else {
-            for (int i = 0; i < kChunk; i++)
-              if (n0 + c0 + i < p.N) out_row[c0 + i] = (int8_t)((packed[i >> 2] >> (8 * (i & 3))) & 0xff);
+            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int b = 0; b < 16; b++)
+              if (n0 + q16 * 16 + b < p.N) o[b] = (int8_t)((w4[b >> 2] >> (8 * (b & 3))) & 0xff);
           }
         }
-        }  // MODE != 2
-        GEMM_TRACE(9, lt == 0 && et == 0 && c0 == 0);
-        GEMM_TRACE(10, lt == 0 && et == 0 && c0 == 32);
       }
 
       GEMM_TRACE(5, lt == 0 && et == 0);
@@ -759,7 +793,7 @@ int launch_for_block_n(int bn, const void *a, int a_rows, int a_extent, int a_pi
     case 64: return launch_tile_kernel<64, 6>(ma, mb, p, s);
     case 128: return launch_tile_kernel<128, 6>(ma, mb, p, s);
     case 240: return launch_tile_kernel<240, 4>(ma, mb, p, s);
-    default: return launch_tile_kernel<256, 4>(ma, mb, p, s);
+    default: return launch_tile_kernel<256, 3>(ma, mb, p, s);  // (a fourth stage would leave no room for the result's staging area)
   }
 }
 
