@@ -20,6 +20,8 @@
 // kernel returns.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <cstdio>
 #include <mutex>
 #include <type_traits>
 
@@ -119,6 +121,59 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
       : "memory");
+}
+
+// ---- CTA pairs (a cluster of two CTAs issuing one MMA over both SMs, cta_group::2) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `p` (a shared-memory address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(const void *p, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(p)), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// A load into this CTA's shared memory whose bytes are counted on a barrier of the pair's even CTA
+// (every CTA loads its own tiles).
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int c0, int c1, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// One MMA over the pair: 256 rows (128 per CTA, each from its own shared memory and into its own
+// tensor memory) by N columns, whose right operand is split by rows between the two CTAs.
+__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this address in both CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+               : "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
@@ -262,10 +317,10 @@ __device__ __forceinline__ void trace(int slot) {
 // ---------------------------------------------------------------------------------------
 // The tile kernel
 // ---------------------------------------------------------------------------------------
-template <int BLOCK_N, int STAGES>
+template <int BLOCK_N, int STAGES, int PAIR = 0>
 struct GemmSmem {
   static constexpr int kABytes = kBlockM * kBlockK;
-  static constexpr int kBBytes = BLOCK_N * kBlockK;
+  static constexpr int kBBytes = (PAIR ? BLOCK_N / 2 : BLOCK_N) * kBlockK;  // a pair's CTAs hold half of the rows each
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTileBytes = STAGES * kStageBytes;
   static constexpr int kColBytes = BLOCK_N * (int)sizeof(ColParams);
@@ -284,11 +339,22 @@ struct GemmSmem {
 // Relu -- the common case, with a shorter drain loop; MODE 1: everything else; MODE 2: the
 // floating-point result of the dynamically quantized layers (GemmParams::float_out).  One drain body per
 // kernel keeps the register allocation of the 96-register budget tight.
-template <int BLOCK_N, int STAGES, int MODE>
+// PAIR: the grid is clusters of two CTAs and a tile is 256 rows -- 128 per CTA, whose tensor core
+// reads its own rows of the left operand and HALF of the right operand's rows from its own shared
+// memory and the other half from its partner's (tcgen05.mma.cta_group::2, issued by the even CTA
+// for both), so every SM loads and reads a third fewer operand bytes per MMA.
+// Barriers: full[] of the even CTA counts the bytes of both CTAs' loads; empty[] and acc_full[] are
+// signalled in both CTAs by multicast commits; acc_empty[] of the even CTA collects the epilogue
+// warps of both.
+template <int BLOCK_N, int STAGES, int MODE, int PAIR = 0>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ GemmParams p) {
-  using S = GemmSmem<BLOCK_N, STAGES>;
+  using S = GemmSmem<BLOCK_N, STAGES, PAIR>;
+  constexpr int kTileM = PAIR ? 2 * kBlockM : kBlockM;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;                 // CTA of the pair
+  const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;   // which tile sequence this CTA follows
+  const int walkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles must start on 1024-byte boundaries.
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -304,7 +370,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   GEMM_TRACE(0, threadIdx.x == 0);
-  const int m_tiles = (p.M + kBlockM - 1) / kBlockM, n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const int m_tiles = (p.M + kTileM - 1) / kTileM, n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int tiles = m_tiles * n_tiles;
   const int k_blocks = (p.K + kBlockK - 1) / kBlockK;
   // columns of one accumulator buffer: BLOCK_N rounded up to a power of two (240 -> 256)
@@ -318,17 +384,23 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], kEpilogueWarps);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], (PAIR ? 2 : 1) * kEpilogueWarps);  // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_slot, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();  // the partner's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   GEMM_TRACE(1, threadIdx.x == 0);
@@ -338,13 +410,20 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     if (lane == 0) {
       int it = 0;  // k-blocks issued so far, over all tiles of this CTA
       bool live = true;
-      for (int t = blockIdx.x; t < tiles && live; t += gridDim.x) {
-        const int m0 = (t % m_tiles) * kBlockM, n0 = (t / m_tiles) * BLOCK_N;
+      for (int t = walker; t < tiles && live; t += walkers) {
+        const int m0 = (t % m_tiles) * kTileM + (int)rank * kBlockM, n0 = (t / m_tiles) * BLOCK_N;
         for (int kb = 0; kb < k_blocks; kb++, it++) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag)) { live = false; break; }
           uint8_t *a_dst = smem + s * S::kStageBytes;
           uint8_t *b_dst = a_dst + S::kABytes;
+          if constexpr (PAIR) {
+            if (rank == 0) mbar_expect_tx(&full[s], 2 * S::kStageBytes);
+            const uint32_t leader_full = map_to_cta(&full[s], 0);
+            tma_load_2d_pair(a_dst, &map_a, kb * kBlockK, m0, leader_full);
+            tma_load_2d_pair(b_dst, &map_b, kb * kBlockK, n0 + (int)rank * (BLOCK_N / 2), leader_full);
+            continue;
+          }
           mbar_expect_tx(&full[s], S::kStageBytes);
           if (p.conv_entries > 0) {
             const int e = kb / p.conv_cpb;
@@ -358,11 +437,11 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_i8(kBlockM, BLOCK_N);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = idesc_i8(kTileM, BLOCK_N);
       int it = 0, lt = 0;
       bool live = true;
-      for (int t = blockIdx.x; t < tiles && live; t += gridDim.x, lt++) {
+      for (int t = walker; t < tiles && live; t += walkers, lt++) {
         const int buf = lt & 1;
         // wait until the epilogue has drained this buffer (passes at once on its first use)
         if (!mbar_wait(&acc_empty[buf], ((lt >> 1) & 1) ^ 1, abort_flag)) break;
@@ -379,12 +458,21 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; k++) {
             // advancing K inside the swizzle atom = advancing the start address by 32 bytes
-            umma_i8(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)), b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc,
-                    (kb | k) != 0);
+            if constexpr (PAIR)
+              umma_i8_pair(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)), b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc,
+                           (kb | k) != 0);
+            else
+              umma_i8(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)), b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc,
+                      (kb | k) != 0);
           }
-          umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+          // the stage may be refilled once these MMAs have read it
+          if constexpr (PAIR) umma_commit_pair(&empty[s]);
+          else umma_commit(&empty[s]);
         }
-        if (live) umma_commit(&acc_full[buf]);  // this tile's accumulators are complete
+        if (live) {  // this tile's accumulators are complete
+          if constexpr (PAIR) umma_commit_pair(&acc_full[buf]);
+          else umma_commit(&acc_full[buf]);
+        }
         GEMM_TRACE(3, lt == 0);
       }
     }
@@ -403,8 +491,9 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const bool vec_ok = ((p.N & 15) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     int lt = 0;
     int cols_n0 = -1;  // column block the records in shared memory belong to
-    for (int t = blockIdx.x; t < tiles; t += gridDim.x, lt++) {
-      const int m0 = (t % m_tiles) * kBlockM, n0 = (t / m_tiles) * BLOCK_N;
+    const uint32_t leader_acc_empty[2] = {PAIR ? map_to_cta(&acc_empty[0], 0) : 0u, PAIR ? map_to_cta(&acc_empty[1], 0) : 0u};
+    for (int t = walker; t < tiles; t += walkers, lt++) {
+      const int m0 = (t % m_tiles) * kTileM + (int)rank * kBlockM, n0 = (t / m_tiles) * BLOCK_N;
       const int buf = lt & 1;
       // (1) per-column constants of this tile (the main loop of this or the next tile is running).
       // Tiles are numbered row-block fastest, so a CTA's consecutive tiles mostly share their
@@ -480,7 +569,10 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             // everything this warp needs from the buffer is in registers: hand it back
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (lane == 0) {
+              if constexpr (PAIR) mbar_arrive_cluster(leader_acc_empty[buf]);
+              else mbar_arrive(&acc_empty[buf]);
+            }
           }
           uint32_t h2[kChunk / 2];
 #pragma unroll
@@ -543,7 +635,10 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             // everything this warp needs from the buffer is in registers: hand it back
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (lane == 0) {
+              if constexpr (PAIR) mbar_arrive_cluster(leader_acc_empty[buf]);
+              else mbar_arrive(&acc_empty[buf]);
+            }
           }
           // the requantisation: libjit_scale, ((v >> pre) * scale + rtn) >> post, then + offset, with
           // rtn = 1 << (post - 1) (0 for post 0); Relu is max(x, out_offset), no activation max(x, INT_MIN)
@@ -615,9 +710,11 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
     __syncthreads();
   }
+  if constexpr (PAIR) cluster_sync();  // neither CTA leaves while its partner may still read its tiles or signal its barriers
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
   GEMM_TRACE(6, threadIdx.x == 32);
 }
@@ -747,6 +844,48 @@ int launch_tile_mode(const CUtensorMap &ma, const CUtensorMap &mb, const GemmPar
   return GLOWB200_OK;
 }
 
+// CTA pairs of the int8 kernel that fit the device at once (0: not asked yet).  The kernels' shapes differ
+// only in shared memory, of which every one takes more than half an SM: one number serves them all.
+int &resident_pairs() {
+  static int n = 0;
+  return n;
+}
+
+// The same for clusters of two CTAs walking 256-row tiles (int8 results only).
+template <int BLOCK_N, int STAGES>
+int launch_pair_kernel(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, cudaStream_t s) {
+  using S = GemmSmem<BLOCK_N, STAGES, 1>;
+  const bool plain = p.a_row_sums == nullptr && p.act_type <= 1;
+  auto kernel = plain ? i8_gemm_requant_kernel<BLOCK_N, STAGES, 0, 1> : i8_gemm_requant_kernel<BLOCK_N, STAGES, 1, 1>;
+  GLOWB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  const int tiles = ((p.N + BLOCK_N - 1) / BLOCK_N) * ((p.M + 2 * kBlockM - 1) / (2 * kBlockM));
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // Pairs that can be resident at once: the kernel is persistent, so a pair that had to wait for
+  // another to retire would start its tiles a whole kernel late.
+  int pairs = resident_pairs();
+  if (pairs <= 0) {
+    cfg.gridDim = dim3(2u * (unsigned)(sm_count() / 2));
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) n = sm_count() / 2;
+    pairs = n < sm_count() / 2 ? n : sm_count() / 2;
+    resident_pairs() = pairs;
+    if (getenv("GLOWB200_DEBUG_PAIRS")) fprintf(stderr, "glow_b200: %d CTA pairs resident at once\n", pairs);
+  }
+  cfg.gridDim = dim3(2u * (unsigned)(tiles < pairs ? tiles : pairs));
+  GLOWB200_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, p));
+  return GLOWB200_OK;
+}
+
 template <int BLOCK_N, int STAGES>
 int launch_tile_kernel(const CUtensorMap &ma, const CUtensorMap &mb, const GemmParams &p, cudaStream_t s) {
   if (p.float_out) return launch_tile_mode<BLOCK_N, STAGES, 2>(ma, mb, p, s);
@@ -784,11 +923,34 @@ int pick_block_n(int M, int N) {
   return bn;
 }
 
-int launch_for_block_n(int bn, const void *a, int a_rows, int a_extent, int a_pitch, const void *b, const GemmParams &p,
+// Tile shape of a product: the columns pick_block_n chooses, walked by single CTAs.  CTA pairs are
+// an option the environment switches on (GLOWB200_GEMM_PAIR = 1: 240-column tiles, 2: 256-column
+// tiles; int8 results of 256 rows or more): measured on 2048 x 4096 x 4096 a pair kernel took
+// 32.1 - 33.5 us against 31.5 us for single CTAs.  Both main loops ran near 600 clocks per k-block
+// (480 is the MMAs' own time) at an SM clock of 1.65 - 1.69 GHz instead of 1.965: with random int8
+// operands the GPU sits at its power limit, and the pair's smaller operand traffic bought nothing
+// that its cross-SM signalling did not cost.
+struct TilePick { int bn, pair; };
+TilePick pick_tile(int M, int N, bool allow_pair) {
+  TilePick t{pick_block_n(M, N), 0};
+  if (!allow_pair || N < 240 || M < 2 * kBlockM || sm_count() < 2) return t;
+  if (const char *e = getenv("GLOWB200_GEMM_PAIR")) {
+    if (e[0] == '1') t = {240, 1};
+    if (e[0] == '2') t = {256, 1};
+  }
+  return t;
+}
+
+int launch_for_block_n(TilePick tile, const void *a, int a_rows, int a_extent, int a_pitch, const void *b, const GemmParams &p,
                        cudaStream_t s) {
+  const int bn = tile.bn;
   CUtensorMap ma, mb;
   if (int rc = make_map(&ma, a, a_rows, a_extent, kBlockM, a_pitch)) return rc;
-  if (int rc = make_map(&mb, b, p.N, p.K, bn)) return rc;
+  if (int rc = make_map(&mb, b, p.N, p.K, tile.pair ? bn / 2 : bn)) return rc;
+  if (tile.pair) {
+    if (bn == 240) return launch_pair_kernel<240, 6>(ma, mb, p, s);
+    return launch_pair_kernel<256, 5>(ma, mb, p, s);
+  }
   switch (bn) {
     case 64: return launch_tile_kernel<64, 6>(ma, mb, p, s);
     case 128: return launch_tile_kernel<128, 6>(ma, mb, p, s);
@@ -811,7 +973,7 @@ int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int 
   p.a_row_sums = nullptr;
   if (p.k_corr == 0) p.k_corr = p.K;
   // C = 64: a 128-byte window over two neighbouring pixels, sliding by one pixel per row
-  return launch_for_block_n(pick_block_n(p.M, p.N), padded, (int)rows, C == 64 ? 128 : C, C, b, p, s);
+  return launch_for_block_n(pick_tile(p.M, p.N, false), padded, (int)rows, C == 64 ? 128 : C, C, b, p, s);
 }
 
 int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_row_sums_in, bool b_offsets_zero,
@@ -847,7 +1009,7 @@ int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_ro
   } else {
     p.a_row_sums = nullptr;
   }
-  return launch_for_block_n(pick_block_n(p.M, p.N), a, p.M, p.K, p.K, b, p, s);
+  return launch_for_block_n(pick_tile(p.M, p.N, !p.float_out), a, p.M, p.K, p.K, b, p, s);
 }
 
 int run_gemm_float_any(const GemmParams &p, const int8_t *a, const int8_t *b_kn, cudaStream_t s) {

@@ -83,6 +83,25 @@ def test_tensor_core_kernel_equals_plain_kernel():
     np.testing.assert_array_equal(a, b)
 
 
+@pytest.mark.parametrize("pair", ["1", "2"])
+@pytest.mark.parametrize("w_off_zero", [True, False])
+def test_cta_pair_kernel_equals_plain_kernel(monkeypatch, w_off_zero, pair):
+    """The kernel that walks 256-row tiles with pairs of CTAs (one MMA over two SMs), switched on
+    through the environment: a ragged last row block (the odd CTA of the last pair has 80 rows)
+    and a partial last column tile, against the plain kernel on every element."""
+    rng = np.random.default_rng(7)
+    c = make_rwq_fc(rng, 2000, 2048, 4000, w_off_zero=w_off_zero)
+    flags = ops.FC_WEIGHT_OFFSETS_ZERO if w_off_zero else 0
+    single, st0 = run_rwq(c, flags=flags)
+    monkeypatch.setenv("GLOWB200_GEMM_PAIR", pair)
+    paired, st1 = run_rwq(c, flags=flags)
+    monkeypatch.delenv("GLOWB200_GEMM_PAIR")
+    plain, _ = run_rwq(c, flags=flags | ops.FC_FORCE_ANY_SHAPE_KERNEL)
+    assert st0 == 0 and st1 == 0
+    np.testing.assert_array_equal(paired, plain)
+    np.testing.assert_array_equal(single, plain)
+
+
 def test_config2_sampled_rows(oracle):
     """The benchmark's second configuration at full size (M2048 K4096 N4096); the oracle checks
     a seeded sample of 96 batch rows (every output of those rows), the plain kernel all rows."""
