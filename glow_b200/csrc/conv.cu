@@ -74,57 +74,79 @@ __global__ void __launch_bounds__(256) im2col_i8_kernel(const int8_t *__restrict
   }
 }
 
-// Any channel count, one block per output image row (n, oh): the KH input rows the image row
-// needs are staged in shared memory once (coalesced reads; rows outside the image are filled
-// with `pad`), then every thread assembles 16-byte pieces of the im2col rows from it -- walking
-// (kh, kw, c) with counters instead of dividing per byte -- and writes them whole.  For a 7 x 7
-// stride-2 stem over 3 channels this replaces 160 byte stores and 160 index decodes per output
-// pixel by 10 vector stores.  Needs KH * W * C bytes of shared memory (checked by the launcher).
+// Bytes of a staged input row of im2col_i8_rows_kernel: the image row, its left padding and as much
+// on the right as the last output pixel's window reaches.
+__host__ __device__ inline int64_t rows_pitch(const ConvGeom &g) {
+  const int64_t last = (int64_t)(g.OW - 1) * g.SW + (int64_t)(g.KW - 1) * g.DW + 1;  // pixels from the padded row's start
+  const int64_t have = (int64_t)g.PL + g.W;
+  return (last > have ? last : have) * g.C;
+}
+
+// Any channel count, one block per output image row (n, oh).  The KH input rows the image row
+// needs are staged in shared memory with their horizontal padding made real (`pad` left and right
+// of the image, whole rows of it above and below), so a tap is a plain offset from the pixel's
+// window.  A thread keeps ONE 16-byte piece of the im2col row (piece = thread % pieces per row) for
+// all the pixels it visits: the sixteen offsets of its bytes are worked out once, and a piece then
+// costs sixteen byte loads, the packing and one vector store.  (Walking (kh, kw, c) with counters
+// for every piece, as this kernel first did, took 163 us for a 7 x 7 stride-2 stem over 3 channels
+// at batch 64: about 170 instructions per 16 bytes.)
+// Shared memory: KH rows of `pitch` bytes (checked by the launcher).
 __global__ void __launch_bounds__(256) im2col_i8_rows_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ a,
-                                                              const __grid_constant__ ConvGeom g, int K, int Kpad, int8_t pad) {
+                                                              const __grid_constant__ ConvGeom g, int K, int Kpad, int8_t pad,
+                                                              int pitch) {
   extern __shared__ __align__(16) int8_t rows_smem[];
   const int n = blockIdx.x / g.OH, oh = blockIdx.x - n * g.OH;
-  const int row_bytes = g.W * g.C;
+  const int row_bytes = g.W * g.C, left = g.PL * g.C;
   for (int kh = 0; kh < g.KH; kh++) {
     const int ih = oh * g.SH - g.PT + kh * g.DH;
-    int8_t *dst = rows_smem + kh * row_bytes;
+    int8_t *dst = rows_smem + kh * pitch;
     if (ih < 0 || ih >= g.H) {
-      for (int j = threadIdx.x; j < row_bytes; j += blockDim.x) dst[j] = pad;
-    } else {
-      const int8_t *src = x + ((int64_t)n * g.H + ih) * row_bytes;
-      if (((reinterpret_cast<uintptr_t>(src) | (uintptr_t)row_bytes) & 15) == 0) {
-        for (int j = threadIdx.x * 16; j < row_bytes; j += blockDim.x * 16)
-          *reinterpret_cast<int4 *>(dst + j) = __ldg(reinterpret_cast<const int4 *>(src + j));
-      } else {
-        for (int j = threadIdx.x; j < row_bytes; j += blockDim.x) dst[j] = src[j];
+      for (int j = threadIdx.x; j < pitch; j += blockDim.x) dst[j] = pad;
+      continue;
+    }
+    const int8_t *src = x + ((int64_t)n * g.H + ih) * row_bytes;
+    for (int j = threadIdx.x; j < pitch - row_bytes; j += blockDim.x) dst[j < left ? j : j + row_bytes] = pad;
+    if (((reinterpret_cast<uintptr_t>(src) | (uintptr_t)row_bytes) & 3) == 0) {
+      for (int j = threadIdx.x * 4; j < row_bytes; j += blockDim.x * 4) {
+        const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(src + j));
+        dst[left + j] = (int8_t)v;
+        dst[left + j + 1] = (int8_t)(v >> 8);
+        dst[left + j + 2] = (int8_t)(v >> 16);
+        dst[left + j + 3] = (int8_t)(v >> 24);
       }
+    } else {
+      for (int j = threadIdx.x; j < row_bytes; j += blockDim.x) dst[left + j] = src[j];
+    }
+  }
+  const int pieces = Kpad >> 4;
+  const int ch = threadIdx.x % pieces, slot = threadIdx.x / pieces, slots = blockDim.x / pieces;
+  int off[16];
+  uint32_t keep[4] = {0u, 0u, 0u, 0u};  // bytes of the piece that are taps (the rest is the zero padding of K)
+#pragma unroll
+  for (int b = 0; b < 16; b++) {
+    const int k = ch * 16 + b;
+    off[b] = 0;
+    if (k < K) {
+      const int tap = k / g.C, c = k - tap * g.C;
+      const int kh = tap / g.KW, kw = tap - kh * g.KW;
+      off[b] = kh * pitch + kw * g.DW * g.C + c;
+      keep[b >> 2] |= 0xffu << (8 * (b & 3));
     }
   }
   __syncthreads();
-  const int chunks_per_row = Kpad >> 4;
-  const int total = g.OW * chunks_per_row;
-  int8_t *out = a + ((int64_t)n * g.OH + oh) * g.OW * Kpad;
-  for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-    const int ow = idx / chunks_per_row, ch = idx - ow * chunks_per_row;
-    int k = ch * 16;
-    int tap = k / g.C, c = k - tap * g.C;
-    int kh = tap / g.KW, kw = tap - kh * g.KW;
-    const int iw0 = ow * g.SW - g.PL;
-    uint32_t w[4] = {0u, 0u, 0u, 0u};
+  int8_t *out = a + ((int64_t)n * g.OH + oh) * g.OW * Kpad + ch * 16;
+  if (slot < slots) {
+    for (int ow = slot; ow < g.OW; ow += slots) {
+      const uint8_t *win = reinterpret_cast<const uint8_t *>(rows_smem) + ow * g.SW * g.C;
+      uint32_t w[4];
 #pragma unroll
-    for (int b = 0; b < 16; b++, k++) {
-      int8_t v = 0;  // zero padding of K beyond the real taps
-      if (k < K) {
-        const int iw = iw0 + kw * g.DW;
-        v = (iw >= 0 && iw < g.W) ? rows_smem[kh * row_bytes + iw * g.C + c] : pad;
-        if (++c == g.C) {
-          c = 0;
-          if (++kw == g.KW) { kw = 0; kh++; }
-        }
+      for (int q = 0; q < 4; q++) {
+        const uint32_t lo = __byte_perm(win[off[4 * q]], win[off[4 * q + 1]], 0x0040);
+        const uint32_t hi = __byte_perm(win[off[4 * q + 2]], win[off[4 * q + 3]], 0x0040);
+        w[q] = __byte_perm(lo, hi, 0x5410) & keep[q];
       }
-      w[b >> 2] |= (uint32_t)(uint8_t)v << (8 * (b & 3));
+      *reinterpret_cast<int4 *>(out + (int64_t)ow * Kpad) = make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]);
     }
-    *reinterpret_cast<int4 *>(out + (int64_t)ow * Kpad + ch * 16) = make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]);
   }
 }
 
@@ -330,10 +352,11 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
       const uint32_t b = (uint8_t)pad;
       im2col_i8_vec_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(
           in, abuf, g, pl.Kpad, (int)(b | (b << 8) | (b << 16) | (b << 24)));
-    } else if ((int64_t)g.KH * g.W * g.C <= 48 * 1024 && (int64_t)g.N * g.OH < (1ll << 31) &&
+    } else if ((int64_t)g.KH * rows_pitch(g) <= 48 * 1024 && (int64_t)g.N * g.OH < (1ll << 31) && (pl.Kpad >> 4) <= 256 &&
                (reinterpret_cast<uintptr_t>(abuf) & 15) == 0) {
-      // the KH input rows of an output image row fit the default shared-memory window
-      im2col_i8_rows_kernel<<<(unsigned)(g.N * g.OH), 256, (size_t)g.KH * g.W * g.C, s>>>(in, abuf, g, pl.K, pl.Kpad, pad);
+      // the KH input rows of an output image row, with their padding, fit the default shared-memory window
+      const int pitch = (int)rows_pitch(g);
+      im2col_i8_rows_kernel<<<(unsigned)(g.N * g.OH), 256, (size_t)g.KH * pitch, s>>>(in, abuf, g, pl.K, pl.Kpad, pad, pitch);
     } else {
       const int64_t blocks = (pl.M * pl.Kpad + 255) / 256;
       im2col_i8_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(in, abuf, g, pl.K, pl.Kpad, pad);
