@@ -169,6 +169,8 @@ def test_transpose():
         np.testing.assert_array_equal(ops.transpose(t(x), sh).cpu().numpy(), np.transpose(x, sh))
     y = rng.integers(-128, 128, (6, 9, 4)).astype(np.int8)
     np.testing.assert_array_equal(ops.transpose(t(y), (2, 0, 1)).cpu().numpy(), np.transpose(y, (2, 0, 1)))
+    q = rng.integers(-128, 128, (2, 3, 10, 12)).astype(np.int8)   # NCHW -> NHWC with few channels
+    np.testing.assert_array_equal(ops.transpose(t(q), (0, 2, 3, 1)).cpu().numpy(), np.transpose(q, (0, 2, 3, 1)))
     z = rng.integers(-128, 128, (40, 33)).astype(np.int8)
     np.testing.assert_array_equal(ops.transpose(t(z), (1, 0)).cpu().numpy(), z.T)
 
