@@ -150,6 +150,52 @@ __global__ void __launch_bounds__(256) im2col_i8_rows_kernel(const int8_t *__res
   }
 }
 
+// Row windows of a stride-2 convolution over few channels (KW * C <= 32, no dilation): plane e
+// (e = 0, 1), image n, row y, output column ow holds the KW * C bytes x[n, 2y - PT + e, 2ow - PL .. + KW - 1, :]
+// and zeros up to 32 bytes; cells outside the image hold `pad` (the input offset).  Tap (kh = 2a + e, kw)
+// of output pixel (n, oh, ow) is byte kw * C + c of window (n, oh + a, ow) of plane e, so the
+// convolution is a contraction whose left-hand rows are four windows of one plane, Y = OH + 3 rows
+// per image: 2 * 32 bytes per (y, ow) instead of KH * KW * C per output pixel, and no im2col matrix.
+// One thread per window.
+__global__ void __launch_bounds__(256) row_windows_i8_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ planes,
+                                                              const __grid_constant__ ConvGeom g, int Y, int64_t plane_bytes,
+                                                              int8_t pad) {
+  const int64_t per_plane = (int64_t)g.N * Y * g.OW, total = 2 * per_plane;
+  const int run = g.KW * g.C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int e = (int)(i / per_plane);
+    int64_t r = i - e * per_plane;
+    const int ow = (int)(r % g.OW);
+    r /= g.OW;
+    const int y = (int)(r % Y), n = (int)(r / Y);
+    const int ih = 2 * y - g.PT + e, b0 = (2 * ow - g.PL) * g.C;  // first byte of the window in its image row
+    const bool row_in = ih >= 0 && ih < g.H;
+    const int8_t *src = x + ((int64_t)n * g.H + (row_in ? ih : 0)) * g.W * g.C;
+    uint32_t w[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    for (int b = 0; b < run; b++) {
+      const int o = b0 + b;
+      const int8_t v = (row_in && o >= 0 && o < g.W * g.C) ? src[o] : pad;
+      w[b >> 2] |= (uint32_t)(uint8_t)v << (8 * (b & 3));
+    }
+    int4 *dst = reinterpret_cast<int4 *>(planes + e * plane_bytes + (i - e * per_plane) * 32);
+    dst[0] = make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]);
+    dst[1] = make_int4((int)w[4], (int)w[5], (int)w[6], (int)w[7]);
+  }
+}
+
+// Filter [OC, KH, KW, C] -> [OC, 2 planes, 4 rows a, 32 bytes]: tap (kh = 2a + e, kw, c) at byte
+// kw * C + c of (e, a); everything else zero.
+__global__ void __launch_bounds__(256) window_filter_i8_kernel(const int8_t *__restrict__ f, int8_t *__restrict__ out, int OC,
+                                                               int KH, int KW, int C) {
+  const int64_t total = (int64_t)OC * 256;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int oc = (int)(i >> 8), k = (int)(i & 255);
+    const int e = k >> 7, a = (k >> 5) & 3, b = k & 31;
+    const int kh = 2 * a + e, kw = b / C, c = b - kw * C;
+    out[i] = (kh < KH && kw < KW) ? f[(((int64_t)oc * KH + kh) * KW + kw) * C + c] : (int8_t)0;
+  }
+}
+
 // NHWC input with its padding made real: [N, Hp, Wp, C], the cells outside the image filled with
 // `pad_word` (the input offset, which is how the reference's skipped taps read).  16 bytes per thread.
 __global__ void __launch_bounds__(256) pad_nhwc_i8_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ xp,
@@ -342,6 +388,38 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
     }
   }
 #endif
+  // Stride-2 windows over few channels with symmetric filters (the 7 x 7 stem over 3 channels): row
+  // windows instead of an im2col matrix (see row_windows_i8_kernel).
+  if (pl.need_im2col && g.SH == 2 && g.SW == 2 && g.DH == 1 && g.DW == 1 && (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) &&
+      g.KW * g.C <= 32 && g.KH <= 8 && (reinterpret_cast<uintptr_t>(filter) & 15) == 0) {
+    const int Y = g.OH + 3;
+    const int64_t rows = (int64_t)g.N * Y * g.OW;
+    const int64_t plane_bytes = rows * 32;
+    const size_t wp_bytes = align_up((size_t)(2 * plane_bytes + (3 * (int64_t)g.OW + 1) * 32), 256);
+    const size_t fb_bytes = align_up((size_t)g.OC * 256, 256);
+    if (rows < (1ll << 31) && wp_bytes + fb_bytes <= pl.a_bytes + pl.f_bytes) {
+      int8_t *planes = reinterpret_cast<int8_t *>(ws);
+      int8_t *fb = reinterpret_cast<int8_t *>(ws + wp_bytes);
+      const int64_t blocks = (2 * rows + 255) / 256;
+      row_windows_i8_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(in, planes, g, Y, plane_bytes,
+                                                                                              (int8_t)p.a_offset);
+      GLOWB200_CUDA_OK(cudaGetLastError());
+      // the four windows of the last rows reach past the second plane
+      GLOWB200_CUDA_OK(cudaMemsetAsync(planes + 2 * plane_bytes, 0, wp_bytes - 2 * plane_bytes, s));
+      window_filter_i8_kernel<<<(unsigned)((g.OC * 256 + 255) / 256), 256, 0, s>>>(filter, fb, g.OC, g.KH, g.KW, g.C);
+      GLOWB200_CUDA_OK(cudaGetLastError());
+      int32_t *bs = reinterpret_cast<int32_t *>(ws + pl.a_bytes + pl.f_bytes);  // zeros do not change the sums, but one path
+      if (int rc = glowb200_i8_row_sums(fb, g.OC, 256, bs, reinterpret_cast<glowb200_stream_t>(s))) return rc;
+      p.K = 256;
+      p.k_corr = pl.K;
+      p.N = g.OC;
+      p.conv_hpwp = Y * g.OW;
+      p.conv_wp = g.OW;
+      p.conv_oh = g.OH;
+      p.conv_ow = g.OW;
+      return run_gemm_row_windows(p, planes, rows, g.OW, fb, bs, s);
+    }
+  }
   const int8_t *a = in;
   if (pl.need_im2col) {
     int8_t *abuf = reinterpret_cast<int8_t *>(ws);

@@ -233,6 +233,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// The same for a K-major tile of 32-byte rows in the 32-byte swizzle (CU_TENSOR_MAP_SWIZZLE_32B):
+// 8-row groups are 256 bytes apart, layout type 6.
+__device__ __forceinline__ uint64_t smem_desc_sw32(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(256 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)6 << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::i8: D = s32, A = B = signed 8-bit, both K-major, dense.
 __host__ __device__ constexpr uint32_t idesc_i8(int m, int n) {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
@@ -425,7 +437,11 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             continue;
           }
           mbar_expect_tx(&full[s], S::kStageBytes);
-          if (p.conv_entries > 0) {
+          if (p.conv_windows) {
+            // four 128 x 32-byte sub-tiles: window a of plane kb of the 128 pixels, one per MMA k-step
+            for (int a4 = 0; a4 < 4; a4++)
+              tma_load_2d(a_dst + a4 * (kBlockM * 32), &map_a, 0, kb * p.conv_windows + m0 + a4 * p.conv_wp, &full[s]);
+          } else if (p.conv_entries > 0) {
             const int e = kb / p.conv_cpb;
             tma_load_2d(a_dst, &map_a, (kb - e * p.conv_cpb) * kBlockK, m0 + p.conv_row_off[e], &full[s]);
           } else {
@@ -455,6 +471,13 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const uint32_t a_addr = smem_u32(smem + s * S::kStageBytes);
           const uint32_t b_addr = a_addr + S::kABytes;
           const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(b_addr);
+          if (!PAIR && p.conv_windows) {
+            // the left operand of k-step k is its own 128 x 32-byte tile in the 32-byte swizzle
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; k++)
+              umma_i8(d_tmem, smem_desc_sw32(a_addr + (uint32_t)k * (kBlockM * 32)), b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc,
+                      (kb | k) != 0);
+          } else
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; k++) {
             // advancing K inside the swizzle atom = advancing the start address by 32 bytes
@@ -547,7 +570,7 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * kAccCols;
       int out_index = row;  // row of the result this accumulator row becomes
       bool row_ok = row < p.M;
-      if (p.conv_entries > 0) {  // padded pixel -> (image, oh, ow); the halo rows are dropped
+      if (p.conv_entries > 0 || p.conv_windows) {  // padded pixel -> (image, oh, ow); the halo rows are dropped
         const int img = row / p.conv_hpwp, rem = row - img * p.conv_hpwp;
         const int oh = rem / p.conv_wp, ow = rem - oh * p.conv_wp;
         row_ok = row_ok && oh < p.conv_oh && ow < p.conv_ow;
@@ -941,11 +964,28 @@ TilePick pick_tile(int M, int N, bool allow_pair) {
   return t;
 }
 
+// `windows` 32-byte windows as a plain [windows, 32] matrix; a box is the same window of 128
+// consecutive pixels, in the 32-byte swizzle the MMA descriptor of such a tile names.
+int make_window_map(CUtensorMap *map, const void *base, int64_t windows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return set_error(GLOWB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {32, (cuuint64_t)windows};
+  cuuint64_t strides[1] = {32};
+  cuuint32_t box[2] = {32, (cuuint32_t)kBlockM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(GLOWB200_ERR_CUDA, "cuTensorMapEncodeTiled (row windows) failed with CUresult %d", (int)r);
+  return GLOWB200_OK;
+}
+
 int launch_for_block_n(TilePick tile, const void *a, int a_rows, int a_extent, int a_pitch, const void *b, const GemmParams &p,
-                       cudaStream_t s) {
+                       cudaStream_t s, const CUtensorMap *a_map = nullptr) {
   const int bn = tile.bn;
   CUtensorMap ma, mb;
-  if (int rc = make_map(&ma, a, a_rows, a_extent, kBlockM, a_pitch)) return rc;
+  if (a_map) ma = *a_map;
+  else if (int rc = make_map(&ma, a, a_rows, a_extent, kBlockM, a_pitch)) return rc;
   if (int rc = make_map(&mb, b, p.N, p.K, tile.pair ? bn / 2 : bn)) return rc;
   if (tile.pair) {
     if (bn == 240) return launch_pair_kernel<240, 6>(ma, mb, p, s);
@@ -974,6 +1014,22 @@ int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int 
   if (p.k_corr == 0) p.k_corr = p.K;
   // C = 64: a 128-byte window over two neighbouring pixels, sliding by one pixel per row
   return launch_for_block_n(pick_tile(p.M, p.N, false), padded, (int)rows, C == 64 ? 128 : C, C, b, p, s);
+}
+
+int run_gemm_row_windows(GemmParams p, const int8_t *planes, int64_t rows, int ow, const int8_t *b, const int32_t *b_row_sums,
+                         cudaStream_t s) {
+  GLOWB200_REQUIRE(rows > 0 && 2 * rows + 3 * (int64_t)ow < (1ll << 31) && ow > 0 && p.K == 2 * kBlockK && ptr16(planes) &&
+                       ptr16(b) && b_row_sums != nullptr,
+                   "row-window convolution: unsupported shape");
+  p.M = (int)rows;
+  p.conv_windows = (int)rows;  // windows per plane: plane e starts at window e * rows
+  p.conv_wp = ow;
+  p.b_row_sums = b_row_sums;
+  p.a_row_sums = nullptr;
+  if (p.k_corr == 0) p.k_corr = p.K;
+  CUtensorMap ma;
+  if (int rc = make_window_map(&ma, planes, 2 * rows + 3 * (int64_t)ow + 1)) return rc;
+  return launch_for_block_n(pick_tile(p.M, p.N, false), nullptr, 0, 0, 0, b, p, s, &ma);
 }
 
 int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_row_sums_in, bool b_offsets_zero,

@@ -30,6 +30,14 @@ struct GemmParams {
   // channel block kb % conv_cpb.  Rows whose (oh, ow) fall outside the output are computed and
   // dropped; the result is stored densely as [n, oh, ow, N].
   int conv_entries, conv_cpb;
+  // Row-window convolution (conv_windows = windows per plane, != 0; stride 2, few channels -- a stem):
+  // the left operand is two planes of 32-byte windows [plane e][n][y][ow], one after the other (the
+  // taps (kh = 2a + e, kw = 0..7) of output pixel (n, oh, ow) are window (n, oh + a, ow) of plane e).
+  // k-block kb is plane kb: four loads bring windows q + a * conv_wp (a = 0..3) of the tile's 128
+  // pixels q as four 128 x 32-byte tiles, one per MMA k-step.  Output pixel (n, oh, ow) is row
+  // (n * Y + oh) * OW + ow of the product (conv_hpwp = Y * OW, conv_wp = OW); rows with oh >= conv_oh
+  // are computed and dropped.
+  int conv_windows;
   int conv_row_off[32];
   int conv_hpwp, conv_wp, conv_oh, conv_ow;
   int32_t u_b_offset, u_bias_pre, u_bias_post, u_bias_scale, u_out_pre, u_out_post, u_out_scale;
@@ -83,6 +91,11 @@ int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int 
 int run_gemm_float_any(const GemmParams &p, const int8_t *a, const int8_t *b_kn, cudaStream_t s);
 // [R, C] int8 -> [C, R] int8
 int transpose_i8(const int8_t *in_rc, int8_t *out_cr, int R, int C, cudaStream_t s);
+
+// The row-window convolution: `planes` holds two planes of `rows` 32-byte windows each, back to back,
+// with 3 * ow + 1 readable windows behind the second; b is [N, 256] (plane, a, 32 bytes).
+int run_gemm_row_windows(GemmParams p, const int8_t *planes, int64_t rows, int ow, const int8_t *b, const int32_t *b_row_sums,
+                         cudaStream_t s);
 
 inline size_t i8_gemm_core_workspace_bytes(int64_t M, int64_t N) {
   return align_up((size_t)N * 4, 256) + align_up((size_t)M * 4, 256);

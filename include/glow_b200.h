@@ -376,7 +376,10 @@ int glowb200_i8_row_sums(const int8_t *matrix, int64_t rows, int64_t K, int32_t 
  * body :284-316).  in [M,K]; weights [N,K] (not transposed: out = in * weights^T); bias,
  * weights_offsets and the six per-row requantisation arrays have N entries and are derived by
  * the caller exactly as lib/LLVMIRCodeGen/LLVMIRGen.cpp:2222-2320 derives them.
- * weights_row_sums: optional int32 [N] from glowb200_i8_row_sums (NULL: computed per call). */
+ * weights_row_sums: optional int32 [N] from glowb200_i8_row_sums (NULL: computed per call).
+ * Environment: GLOWB200_GEMM_PAIR=1 (240-column tiles) or 2 (256-column tiles) makes products of
+ * 256 rows or more, of this and the two entry points below, run on pairs of CTAs (one MMA over two
+ * SMs, tcgen05 cta_group::2) -- same results; the default is one CTA per tile, which measured faster. */
 int glowb200_rowwise_quantized_fc_i8_i32(
     int8_t *out, const int8_t *in, const int8_t *weights, const int32_t *bias,
     const int32_t *weights_offsets, const int32_t *bias_pre, const int32_t *bias_post,
