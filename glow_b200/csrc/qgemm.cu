@@ -310,16 +310,21 @@ __device__ __forceinline__ int stage_offset(int r, int q16) {
   return r * PITCH + 16 * (q16 ^ x);
 }
 
-// Optional phase tracing for tuning builds (-DGLOWB200_GEMM_TRACE): CTA 0 writes globaltimer
-// stamps to a device buffer the tuning harness reads back.  Compiled out by default.
+// Optional tracing for tuning builds (python -m glow_b200.build -DGLOWB200_GEMM_TRACE): every CTA
+// stamps %globaltimer (ns) at entry and exit -- entries 2b and 2b + 1 of a device buffer -- and
+// CTA 0 its clock64 at the same two points (entries 510, 511), from which the SM clock a launch really
+// ran at follows; CTA 0 also stamps the phases of its first tile (entries 496 + slot).
+// glowb200_debug_gemm_trace copies the 512 entries out.  Compiled out by default.
 #ifdef GLOWB200_GEMM_TRACE
-__device__ unsigned long long g_gemm_trace[16];
+__device__ unsigned long long g_gemm_trace[512];
 __device__ __forceinline__ void trace(int slot) {
-  if (blockIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_gemm_trace[slot] = t;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  if ((slot == 0 || slot == 6) && blockIdx.x < 248) {
+    g_gemm_trace[2 * blockIdx.x + (slot == 6)] = t;
+    if (blockIdx.x == 0) g_gemm_trace[510 + (slot == 6)] = (unsigned long long)clock64();
   }
+  if (blockIdx.x == 0 && slot < 14) g_gemm_trace[496 + slot] = t;
 }
 #define GEMM_TRACE(slot, cond) do { if (cond) trace(slot); } while (0)
 #else
@@ -1097,8 +1102,8 @@ int check_dims(int64_t M, int64_t K, int64_t N) {
 using namespace glowb200;
 
 #ifdef GLOWB200_GEMM_TRACE
-extern "C" int glowb200_debug_gemm_trace(unsigned long long *host16) {
-  return cudaMemcpyFromSymbol(host16, glowb200::g_gemm_trace, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 4;
+extern "C" int glowb200_debug_gemm_trace(unsigned long long *host512) {
+  return cudaMemcpyFromSymbol(host512, glowb200::g_gemm_trace, 512 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 4;
 }
 #endif
 
