@@ -216,6 +216,29 @@ __global__ void __launch_bounds__(256) pad_nhwc_i8_kernel(const int8_t *__restri
   }
 }
 
+// The same for a stride-2 window, split by the parity of the padded coordinates: plane (ph, pw) holds
+// the padded input at (2y + ph, 2x + pw), [4][N, Hq, Wq, C].  Tap (kh, kw) of output pixel (n, oh, ow)
+// is then pixel (n, oh + kh / 2, ow + kw / 2) of plane (kh & 1, kw & 1): a row offset again.
+__global__ void __launch_bounds__(256) pad_parity_nhwc_i8_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ xp,
+                                                                  const __grid_constant__ ConvGeom g, int Hq, int Wq, int pad_word) {
+  const int cc = g.C >> 4;
+  const int64_t total = 4ll * g.N * Hq * Wq * cc;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % cc);
+    int64_t r = i / cc;
+    const int xq = (int)(r % Wq);
+    r /= Wq;
+    const int yq = (int)(r % Hq);
+    r /= Hq;
+    const int n = (int)(r % g.N), plane = (int)(r / g.N);
+    const int ih = 2 * yq + (plane >> 1) - g.PT, iw = 2 * xq + (plane & 1) - g.PL;
+    int4 v = make_int4(pad_word, pad_word, pad_word, pad_word);
+    if (ih >= 0 && iw >= 0 && ih < g.H && iw < g.W)
+      v = __ldg(reinterpret_cast<const int4 *>(x + (((int64_t)n * g.H + ih) * g.W + iw) * g.C) + c);
+    reinterpret_cast<int4 *>(xp)[i] = v;
+  }
+}
+
 // Filter [OC, KH, KW, 64] -> [OC, KH * ceil(KW / 2), 128]: taps (kh, 2j) and (kh, 2j + 1) side by
 // side, the partner of a last odd tap zero -- the right-hand side that matches left-hand rows made of
 // two neighbouring 64-channel pixels.
@@ -388,6 +411,43 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
     }
   }
 #endif
+  // Stride-2 windows over a multiple of 128 channels, symmetric filters: the shifted-rows form over
+  // four parity planes of the padded input (see pad_parity_nhwc_i8_kernel) instead of an im2col matrix.
+  if (pl.need_im2col && g.SH == 2 && g.SW == 2 && g.DH == 1 && g.DW == 1 && (g.KH > 1 || g.KW > 1) &&
+      (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) && g.C % 128 == 0 && g.KH * g.KW <= 32 &&
+      (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(filter) & 15) == 0) {
+    const int Hq = g.OH + (g.KH - 1) / 2, Wq = g.OW + (g.KW - 1) / 2;
+    const int64_t rows = (int64_t)g.N * Hq * Wq;  // per plane
+    const size_t xp_bytes = align_up((size_t)(4 * rows) * g.C + 256, 256);
+    if (4 * rows < (1ll << 31) && xp_bytes <= pl.a_bytes + pl.f_bytes) {
+      int8_t *xp = reinterpret_cast<int8_t *>(ws);
+      const uint32_t b = (uint8_t)p.a_offset;
+      const int64_t chunks = 4 * rows * (g.C >> 4), blocks = (chunks + 255) / 256;
+      pad_parity_nhwc_i8_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(
+          in, xp, g, Hq, Wq, (int)(b | (b << 8) | (b << 16) | (b << 24)));
+      GLOWB200_CUDA_OK(cudaGetLastError());
+      p.K = g.KH * g.KW * g.C;
+      p.k_corr = pl.K;
+      p.N = g.OC;
+      p.conv_entries = g.KH * g.KW;
+      p.conv_cpb = g.C / 128;
+      for (int e = 0; e < p.conv_entries; e++) {
+        const int kh = e / g.KW, kw = e % g.KW;
+        p.conv_row_off[e] = (int)(((kh & 1) * 2 + (kw & 1)) * rows) + (kh >> 1) * Wq + (kw >> 1);
+      }
+      p.conv_hpwp = Hq * Wq;
+      p.conv_wp = Wq;
+      p.conv_oh = g.OH;
+      p.conv_ow = g.OW;
+      const int32_t *sums = filter_row_sums;
+      if (sums == nullptr) {
+        int32_t *bs = reinterpret_cast<int32_t *>(ws + pl.a_bytes + pl.f_bytes);
+        if (int rc = glowb200_i8_row_sums(filter, g.OC, p.K, bs, reinterpret_cast<glowb200_stream_t>(s))) return rc;
+        sums = bs;
+      }
+      return run_gemm_shifted_rows(p, xp, rows, g.C, filter, sums, s, 4 * rows);
+    }
+  }
   // Stride-2 windows over few channels with symmetric filters (the 7 x 7 stem over 3 channels): row
   // windows instead of an im2col matrix (see row_windows_i8_kernel).
   if (pl.need_im2col && g.SH == 2 && g.SW == 2 && g.DH == 1 && g.DW == 1 && (flags & GLOWB200_FC_WEIGHT_OFFSETS_ZERO) &&

@@ -683,8 +683,8 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 uint32_t v = acc[8 * (i >> 1) + 4 * g + 2 * (i & 1) + cc] + (uint32_t)cp.x;
                 if constexpr (MODE == 1) v -= (uint32_t)cp.w * (uint32_t)a_sums[i];  // 0 when no row sums take part
                 const int32_t m = (int32_t)((uint32_t)((int32_t)v >> pre) * (uint32_t)cp.y + rtn);
-                int32_t x = (int32_t)((uint32_t)(m >> post) + (uint32_t)p.out_offset);
-                x = x > relu_floor ? x : relu_floor;
+                // max((m >> post) + offset, floor) in one instruction (a wrapping add, like the two it replaces)
+                int32_t x = __viaddmax_s32(m >> post, p.out_offset, relu_floor);
                 if constexpr (MODE == 1) {
                   if (p.act_type > 1) x = activation_i32(x, p);
                 }
@@ -1009,8 +1009,9 @@ int launch_for_block_n(TilePick tile, const void *a, int a_rows, int a_extent, i
 }  // namespace
 
 int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int C, const int8_t *b,
-                          const int32_t *b_row_sums, cudaStream_t s) {
-  GLOWB200_REQUIRE(rows > 0 && rows < (1ll << 31) && (C == 64 || C % 128 == 0) && p.K % kBlockK == 0 && p.conv_entries > 0 &&
+                          const int32_t *b_row_sums, cudaStream_t s, int64_t buffer_rows) {
+  if (buffer_rows < rows) buffer_rows = rows;
+  GLOWB200_REQUIRE(rows > 0 && buffer_rows < (1ll << 31) && (C == 64 || C % 128 == 0) && p.K % kBlockK == 0 && p.conv_entries > 0 &&
                        p.conv_entries <= 32 && ptr16(padded) && ptr16(b) && b_row_sums != nullptr,
                    "shifted-rows convolution: unsupported shape");
   p.M = (int)rows;
@@ -1018,7 +1019,7 @@ int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int 
   p.a_row_sums = nullptr;
   if (p.k_corr == 0) p.k_corr = p.K;
   // C = 64: a 128-byte window over two neighbouring pixels, sliding by one pixel per row
-  return launch_for_block_n(pick_tile(p.M, p.N, false), padded, (int)rows, C == 64 ? 128 : C, C, b, p, s);
+  return launch_for_block_n(pick_tile(p.M, p.N, false), padded, (int)buffer_rows, C == 64 ? 128 : C, C, b, p, s);
 }
 
 int run_gemm_row_windows(GemmParams p, const int8_t *planes, int64_t rows, int ow, const int8_t *b, const int32_t *b_row_sums,

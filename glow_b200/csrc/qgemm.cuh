@@ -84,8 +84,9 @@ int run_gemm(GemmParams p, const int8_t *a, const int8_t *b, const int32_t *b_ro
 // The shifted-rows convolution on the same kernel: `padded` holds `rows` padded pixels of `C` bytes
 // (plus 128 readable bytes behind them), p.conv_* describe the taps, p.M = rows, p.K = bytes of a
 // row of b (a multiple of 128).  Weight offsets must all be zero (no input row sums).
+// buffer_rows: rows the padded buffer holds when the taps reach beyond `rows` (several planes); 0 = rows.
 int run_gemm_shifted_rows(GemmParams p, const int8_t *padded, int64_t rows, int C, const int8_t *b,
-                          const int32_t *b_row_sums, cudaStream_t s);
+                          const int32_t *b_row_sums, cudaStream_t s, int64_t buffer_rows = 0);
 
 // The float-result contraction for any shape with the weights in their [K, N] form.
 int run_gemm_float_any(const GemmParams &p, const int8_t *a, const int8_t *b_kn, cudaStream_t s);

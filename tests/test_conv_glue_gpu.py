@@ -34,6 +34,12 @@ CONV_CASES = [
     (2, 11, 6, 64, 40, (2, 2), (1, 1), (0, 0, 0, 0), 1, (1, 1), 0),      # even window, no padding
     (1, 6, 9, 128, 32, (1, 3), (1, 1), (0, 1, 0, 1), 1, (1, 1), 2),      # one-row window, clip
     (2, 7, 7, 64, 16, (3, 3), (1, 1), (2, 0, 1, 2), 1, (1, 1), 0),       # unequal pads
+    # stride-2 windows over 128k channels with symmetric filters: shifted rows over four parity planes
+    (2, 9, 11, 128, 48, (3, 3), (2, 2), (1, 1, 1, 1), 1, (1, 1), 1),
+    (1, 12, 10, 256, 40, (3, 3), (2, 2), (1, 1, 1, 1), 1, (1, 1), 0),
+    (2, 8, 8, 128, 32, (5, 5), (2, 2), (2, 2, 2, 2), 1, (1, 1), 2),
+    (1, 9, 9, 128, 16, (3, 3), (2, 2), (0, 1, 1, 0), 1, (1, 1), 0),      # unequal pads
+    (1, 10, 10, 128, 24, (2, 2), (2, 2), (0, 0, 0, 0), 1, (1, 1), 0),    # window = stride
 ]
 
 
