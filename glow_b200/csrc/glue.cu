@@ -303,9 +303,18 @@ __global__ void __launch_bounds__(kThreads) avg_pool_i8_kernel(const int8_t *__r
 
 // 4-D transpose by an arbitrary permutation (libjit_transpose_*, libjit.cpp:1945-...):
 // dst dims = src dims permuted by `shuffle`; one thread per destination element.
-template <typename T>
-__global__ void __launch_bounds__(kThreads) transpose4_kernel(const T *__restrict__ src, T *__restrict__ dst, int d0, int d1,
-                                                              int d2, int d3, int s0, int s1, int s2, int s3) {
+// (F converts an element on its way: the identity, or the Quantize that a Transpose was sunk below.)
+struct KeepF {
+  template <typename T> __device__ __forceinline__ T operator()(T v) const { return v; }
+};
+struct QuantizeF {
+  float scale;
+  int32_t offset;
+  __device__ __forceinline__ int8_t operator()(float v) const { return (int8_t)quantize_one(v, scale, offset); }
+};
+template <typename T, typename TO = T, typename F = KeepF>
+__global__ void __launch_bounds__(kThreads) transpose4_kernel(const T *__restrict__ src, TO *__restrict__ dst, int d0, int d1,
+                                                              int d2, int d3, int s0, int s1, int s2, int s3, F f = F()) {
   // d*: destination dims; s*: source element stride of each destination axis
   const int64_t total = (int64_t)d0 * d1 * d2 * d3;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -314,7 +323,7 @@ __global__ void __launch_bounds__(kThreads) transpose4_kernel(const T *__restric
     const int i2 = (int)(r % d2);
     r /= d2;
     const int i1 = (int)(r % d1), i0 = (int)(r / d1);
-    dst[i] = src[(int64_t)i0 * s0 + (int64_t)i1 * s1 + (int64_t)i2 * s2 + (int64_t)i3 * s3];
+    dst[i] = f(src[(int64_t)i0 * s0 + (int64_t)i1 * s1 + (int64_t)i2 * s2 + (int64_t)i3 * s3]);
   }
 }
 
@@ -322,17 +331,18 @@ __global__ void __launch_bounds__(kThreads) transpose4_kernel(const T *__restric
 // one (NCHW -> NHWC with few channels): one thread per destination "pixel" reads its d3 elements
 // s3 apart -- neighbouring threads read neighbouring source elements -- and writes them side by side.
 // (One thread per element read single bytes 50176 apart: 51 us for a 64 x 3 x 224 x 224 int8 tensor.)
-template <typename T>
-__global__ void __launch_bounds__(kThreads) transpose4_short_inner_kernel(const T *__restrict__ src, T *__restrict__ dst, int d0,
-                                                                          int d1, int d2, int d3, int s0, int s1, int s3) {
+template <typename T, typename TO = T, typename F = KeepF>
+__global__ void __launch_bounds__(kThreads) transpose4_short_inner_kernel(const T *__restrict__ src, TO *__restrict__ dst, int d0,
+                                                                          int d1, int d2, int d3, int s0, int s1, int s3,
+                                                                          F f = F()) {
   const int64_t pixels = (int64_t)d0 * d1 * d2;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pixels; i += (int64_t)gridDim.x * blockDim.x) {
     const int i2 = (int)(i % d2);
     const int64_t r = i / d2;
     const int i1 = (int)(r % d1), i0 = (int)(r / d1);
     const T *from = src + (int64_t)i0 * s0 + (int64_t)i1 * s1 + i2;
-    T *to = dst + i * d3;
-    for (int c = 0; c < d3; c++) to[c] = from[(int64_t)c * s3];
+    TO *to = dst + i * d3;
+    for (int c = 0; c < d3; c++) to[c] = f(from[(int64_t)c * s3]);
   }
 }
 
@@ -525,10 +535,11 @@ extern "C" int glowb200_avg_pool_i8(const int8_t *in, int8_t *out, const int64_t
   return GLOWB200_OK;
 }
 
-extern "C" int glowb200_transpose(const void *src, void *dest, const int64_t *src_dims, const int32_t *shuffle, int num_dims,
-                                  int element_bytes, glowb200_stream_t stream) {
+namespace {
+// Destination dims d[] and, per destination axis, the source's element stride st[] of a shuffle of up to 4 axes.
+struct TransposePlan { int d[4], st[4]; int64_t total; };
+int plan_transpose(TransposePlan &t, const int64_t *src_dims, const int32_t *shuffle, int num_dims) {
   GLOWB200_REQUIRE(src_dims && shuffle && num_dims >= 1 && num_dims <= 4, "1 to 4 dimensions are supported");
-  GLOWB200_REQUIRE(element_bytes == 1 || element_bytes == 4, "element size must be 1 or 4 bytes");
   int64_t sd[4] = {1, 1, 1, 1}, sstride[4];
   int sh[4] = {0, 1, 2, 3};
   const int lead = 4 - num_dims;  // pad with leading unit axes
@@ -542,26 +553,46 @@ extern "C" int glowb200_transpose(const void *src, void *dest, const int64_t *sr
   }
   sstride[3] = 1;
   for (int i = 2; i >= 0; i--) sstride[i] = sstride[i + 1] * sd[i + 1];
-  int64_t total = sd[0] * sd[1] * sd[2] * sd[3];
-  if (total == 0) return GLOWB200_OK;
-  GLOWB200_REQUIRE(src && dest, "NULL tensor pointer");
-  GLOWB200_REQUIRE(total < (1ll << 31), "tensor too large for this kernel");
-  const int d0 = (int)sd[sh[0]], d1 = (int)sd[sh[1]], d2 = (int)sd[sh[2]], d3 = (int)sd[sh[3]];
-  const int s0 = (int)sstride[sh[0]], s1 = (int)sstride[sh[1]], s2 = (int)sstride[sh[2]], s3 = (int)sstride[sh[3]];
-  if (d3 <= 16 && s2 == 1 && s3 != 1) {
-    const int64_t pixels = total / d3;
-    if (element_bytes == 1)
-      transpose4_short_inner_kernel<int8_t><<<grid_for(pixels), kThreads, 0, GLOWB200_STREAM>>>(
-          reinterpret_cast<const int8_t *>(src), reinterpret_cast<int8_t *>(dest), d0, d1, d2, d3, s0, s1, s3);
-    else
-      transpose4_short_inner_kernel<float><<<grid_for(pixels), kThreads, 0, GLOWB200_STREAM>>>(
-          reinterpret_cast<const float *>(src), reinterpret_cast<float *>(dest), d0, d1, d2, d3, s0, s1, s3);
-  } else if (element_bytes == 1)
-    transpose4_kernel<int8_t><<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(
-        reinterpret_cast<const int8_t *>(src), reinterpret_cast<int8_t *>(dest), d0, d1, d2, d3, s0, s1, s2, s3);
+  t.total = sd[0] * sd[1] * sd[2] * sd[3];
+  GLOWB200_REQUIRE(t.total < (1ll << 31), "tensor too large for this kernel");
+  for (int i = 0; i < 4; i++) {
+    t.d[i] = (int)sd[sh[i]];
+    t.st[i] = (int)sstride[sh[i]];
+  }
+  return GLOWB200_OK;
+}
+
+template <typename T, typename TO, typename F>
+int run_transpose(const TransposePlan &t, const T *src, TO *dest, F f, cudaStream_t s) {
+  if (t.d[3] <= 16 && t.st[2] == 1 && t.st[3] != 1)
+    transpose4_short_inner_kernel<T, TO, F><<<grid_for(t.total / t.d[3]), kThreads, 0, s>>>(src, dest, t.d[0], t.d[1], t.d[2],
+                                                                                            t.d[3], t.st[0], t.st[1], t.st[3], f);
   else
-    transpose4_kernel<float><<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(
-        reinterpret_cast<const float *>(src), reinterpret_cast<float *>(dest), d0, d1, d2, d3, s0, s1, s2, s3);
+    transpose4_kernel<T, TO, F><<<grid_for(t.total), kThreads, 0, s>>>(src, dest, t.d[0], t.d[1], t.d[2], t.d[3], t.st[0],
+                                                                        t.st[1], t.st[2], t.st[3], f);
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
+}
+}  // namespace
+
+extern "C" int glowb200_transpose(const void *src, void *dest, const int64_t *src_dims, const int32_t *shuffle, int num_dims,
+                                  int element_bytes, glowb200_stream_t stream) {
+  GLOWB200_REQUIRE(element_bytes == 1 || element_bytes == 4, "element size must be 1 or 4 bytes");
+  TransposePlan t;
+  if (int rc = plan_transpose(t, src_dims, shuffle, num_dims)) return rc;
+  if (t.total == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(src && dest, "NULL tensor pointer");
+  if (element_bytes == 1)
+    return run_transpose(t, reinterpret_cast<const int8_t *>(src), reinterpret_cast<int8_t *>(dest), KeepF(), GLOWB200_STREAM);
+  return run_transpose(t, reinterpret_cast<const float *>(src), reinterpret_cast<float *>(dest), KeepF(), GLOWB200_STREAM);
+}
+
+extern "C" int glowb200_quantize_transpose_i8(int8_t *dest, const float *src, const int64_t *src_dims, const int32_t *shuffle,
+                                              int num_dims, float scale, int32_t offset, glowb200_stream_t stream) {
+  TransposePlan t;
+  if (int rc = plan_transpose(t, src_dims, shuffle, num_dims)) return rc;
+  if (t.total == 0) return GLOWB200_OK;
+  GLOWB200_REQUIRE(src && dest, "NULL tensor pointer");
+  GLOWB200_REQUIRE(scale != 0.0f, "scale must not be zero");
+  return run_transpose(t, src, dest, QuantizeF{scale, offset}, GLOWB200_STREAM);
 }

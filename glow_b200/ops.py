@@ -709,6 +709,15 @@ def transpose(src, shuffle):
     return out
 
 
+def quantize_transpose_i8(src, shuffle, scale, offset):
+    """transpose(quantize(src)) in one pass: fp32 in, int8 out with dims[i] = src dims[shuffle[i]]."""
+    _cuda(src, "src", (torch.float32,))
+    out = torch.empty([src.shape[i] for i in shuffle], dtype=torch.int8, device=src.device)
+    check(_lib.lib().glowb200_quantize_transpose_i8(_p(out), _p(src), _i64arr(src.shape), (C.c_int32 * len(shuffle))(*shuffle),
+                                                    len(shuffle), C.c_float(float(scale)), int(offset), _stream()))
+    return out
+
+
 def pairwise_dot_interaction(dense, pooled, *, quant=None, out=None):
     """dense fp32 [B, D]; pooled fp32 [B, T, D] (or [B, T*D]).  Returns fp32 [B, D + n(n-1)/2]
     (n = T + 1), or int8 when quant=(scale, offset) (the following Quantize node fused)."""

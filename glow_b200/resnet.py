@@ -1,7 +1,7 @@
 """ResNet-50 v1.5, fully int8 (channelwise-quantized convolutions), on the glow_b200 kernels:
 the third benchmark configuration.
 
-    fp32 NCHW input -> Quantize -> Transpose (NHWC) -> conv 7x7/2 + Relu -> MaxPool 3x3/2
+    fp32 NCHW input -> Quantize + Transpose (NHWC) -> conv 7x7/2 + Relu -> MaxPool 3x3/2
     -> 16 bottleneck blocks (1x1, 3x3 [stride here: v1.5], 1x1, shortcut 1x1 where shapes change,
        ElementAdd, Relu) -> AvgPool 7x7 -> rowwise-quantized FC -> Dequantize
 
@@ -214,9 +214,8 @@ class ResNet50Int8:
         self.launches = 0
         # Quantize, then Transpose: the order Glow's optimizer leaves (it sinks a Transpose below the
         # Quantize that consumes it, GraphOptimizer.cpp:1076-1086) -- the layout change moves bytes, not floats
-        x = ops.element_quantize_i8(x_nchw, *tqp["input"])
-        x = ops.transpose(x, (0, 2, 3, 1))
-        self.launches += 2
+        x = ops.quantize_transpose_i8(x_nchw, (0, 2, 3, 1), *tqp["input"])   # one kernel for the pair
+        self.launches += 1
         for l in self.layers:
             if l[0] == "conv":
                 x = self._conv(l[1]["name"], x)

@@ -573,6 +573,14 @@ int glowb200_avg_pool_i8(const int8_t *in, int8_t *out, const int64_t *in_dims,
  * _f, libjit.cpp:1945-...): dest dims[i] = src_dims[shuffle[i]].  src_dims / shuffle are HOST arrays. */
 int glowb200_transpose(const void *src, void *dest, const int64_t *src_dims, const int32_t *shuffle,
                        int num_dims, int element_bytes, glowb200_stream_t stream);
+/* Quantize fp32 -> int8 and Transpose in one pass: dest = transpose(quantize(src)), the pair Glow's
+ * optimizer leaves when it sinks a Transpose below the Quantize that consumes it
+ * (lib/Optimizer/GraphOptimizer/GraphOptimizer.cpp:1076-1086) -- an NCHW float input becoming the
+ * NHWC int8 input of the first convolution.  Element for element the result of
+ * glowb200_element_quantize_i8 (libjit.cpp:2997-3002) followed by glowb200_transpose. */
+int glowb200_quantize_transpose_i8(int8_t *dest, const float *src, const int64_t *src_dims,
+                                   const int32_t *shuffle, int num_dims, float scale, int32_t offset,
+                                   glowb200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Recommendation-model pieces

@@ -177,6 +177,11 @@ def test_transpose():
     np.testing.assert_array_equal(ops.transpose(t(y), (2, 0, 1)).cpu().numpy(), np.transpose(y, (2, 0, 1)))
     q = rng.integers(-128, 128, (2, 3, 10, 12)).astype(np.int8)   # NCHW -> NHWC with few channels
     np.testing.assert_array_equal(ops.transpose(t(q), (0, 2, 3, 1)).cpu().numpy(), np.transpose(q, (0, 2, 3, 1)))
+    # Quantize + Transpose in one pass == the two kernels one after the other
+    f = (rng.standard_normal((2, 3, 10, 12)) * 3).astype(np.float32)
+    for sh in [(0, 2, 3, 1), (0, 3, 1, 2), (3, 2, 1, 0)]:
+        two = ops.transpose(ops.element_quantize_i8(t(f), 0.037, -5), sh)
+        assert torch.equal(ops.quantize_transpose_i8(t(f), sh, 0.037, -5), two)
     z = rng.integers(-128, 128, (40, 33)).astype(np.int8)
     np.testing.assert_array_equal(ops.transpose(t(z), (1, 0)).cpu().numpy(), z.T)
 
