@@ -353,9 +353,10 @@ struct GemmSmem {
 // double-buffered in tensor memory: while the epilogue warps drain tile i, the MMA warp is
 // already accumulating tile i+1 into the other buffer.
 // MODE 0: no input row sums take part (every weight offset is 0) and the activation is none or
-// Relu -- the common case, with a shorter drain loop; MODE 1: everything else; MODE 2: the
-// floating-point result of the dynamically quantized layers (GemmParams::float_out).  One drain body per
-// kernel keeps the register allocation of the 96-register budget tight.
+// Relu -- the common case, whose drain has neither the row-sum term nor the activation switch;
+// MODE 1: everything else with an int8 result; MODE 2: the floating-point result of the
+// dynamically quantized layers (GemmParams::float_out).  One drain body per kernel keeps the
+// register allocation inside the 96 registers a 576-thread CTA leaves.
 // PAIR: the grid is clusters of two CTAs and a tile is 256 rows -- 128 per CTA, whose tensor core
 // reads its own rows of the left operand and HALF of the right operand's rows from its own shared
 // memory and the other half from its partner's (tcgen05.mma.cta_group::2, issued by the even CTA
