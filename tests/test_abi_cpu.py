@@ -50,3 +50,10 @@ def test_host_side_argument_errors_need_no_gpu(built):
     rc = l.glowb200_fused_rowwise_quantized_sparse_lengths_weighted_sum(
         None, None, 0, 10, None, None, 1, None, 0, 0, 72, 64, 0, 0, None, 0, None, None)
     assert rc == 0
+    # Quantize + Transpose: the shuffle is checked on the host; an empty tensor is a no-op
+    import ctypes as C
+    dims, bad, good = (C.c_int64 * 4)(2, 3, 0, 5), (C.c_int32 * 4)(0, 2, 2, 1), (C.c_int32 * 4)(0, 2, 3, 1)
+    rc = l.glowb200_quantize_transpose_i8(None, None, dims, bad, 4, C.c_float(0.1), 0, None)
+    assert rc == 1 and b"permutation" in l.glowb200_last_error()
+    assert l.glowb200_quantize_transpose_i8(None, None, dims, good, 4, C.c_float(0.1), 0, None) == 0
+    assert l.glowb200_transpose(None, None, dims, good, 5, 1, None) == 1
