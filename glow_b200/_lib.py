@@ -79,6 +79,7 @@ SIGNATURES = {
     "glowb200_max_pool_i8": (_int, [_vp] * 7 + [_i32, _vp]),
     "glowb200_avg_pool_i8": (_int, [_vp] * 7 + [_int] + [_i32] * 5 + [_vp]),
     "glowb200_transpose": (_int, [_vp, _vp, _vp, _vp, _int, _int, _vp]),
+    "glowb200_set_programmatic_launch": (_int, [_int]),
     "glowb200_quantize_transpose_i8": (_int, [_vp, _vp, _vp, _vp, _int, _f32, _i32, _vp]),
     "glowb200_pairwise_dot_interaction": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _f32, _i32, _vp]),
     "glowb200_peer_buffer_create": (_int, [_sz, _vp, _vp]),

@@ -1,5 +1,7 @@
 #include "common.cuh"
 
+#include <atomic>
+#include <cstdlib>
 #include <cstring>
 
 namespace glowb200 {
@@ -30,7 +32,24 @@ int sm_count() {
   return cached;
 }
 
+std::atomic<int> g_pdl_override{-1};  // -1: the environment decides
+
+bool pdl_enabled() {
+  const int o = g_pdl_override.load(std::memory_order_relaxed);
+  if (o >= 0) return o != 0;
+  static const bool on = [] {
+    const char *e = getenv("GLOWB200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 }  // namespace glowb200
 
 extern "C" const char *glowb200_last_error(void) { return glowb200::last_error_buffer(); }
 extern "C" const char *glowb200_version(void) { return "glow_b200 0.1 (sm_100a)"; }
+extern "C" int glowb200_set_programmatic_launch(int enabled) {
+  const bool before = glowb200::pdl_enabled();
+  glowb200::g_pdl_override.store(enabled < 0 ? -1 : (enabled != 0), std::memory_order_relaxed);
+  return before ? 1 : 0;
+}

@@ -57,4 +57,31 @@ __host__ __device__ __forceinline__ int32_t clip_i8(int32_t v) {
   return v < -128 ? -128 : (v > 127 ? 127 : v);
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start (set up its barriers, tensor memory, shared memory) while the kernel before it in the stream
+// is still running, once every block of that kernel has passed pdl_launch_dependents(); it must not
+// touch global memory before pdl_wait(), which returns when the earlier kernel has completed and its
+// writes are visible.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Programmatic launches are on unless the environment says GLOWB200_PDL=0 (read once).  A waiting
+// kernel holds its shared memory and thread slots, which costs a kernel that runs beside it on
+// another stream: a caller that overlaps streams can switch them off.
+bool pdl_enabled();
+// Launches `kernel` so that it may start beside the tail of the kernel before it (see pdl_wait()).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace glowb200

@@ -30,6 +30,8 @@ struct ConvGeom {
 // straddles two taps)
 __global__ void __launch_bounds__(256) im2col_i8_vec_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ a,
                                                              const __grid_constant__ ConvGeom g, int Kpad, int pad_word) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int chunks_per_row = Kpad >> 4;
   const int64_t total = (int64_t)g.N * g.OH * g.OW * chunks_per_row;
   const int c_chunks = g.C >> 4;
@@ -160,6 +162,8 @@ __global__ void __launch_bounds__(256) im2col_i8_rows_kernel(const int8_t *__res
 __global__ void __launch_bounds__(256) row_windows_i8_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ planes,
                                                               const __grid_constant__ ConvGeom g, int Y, int64_t plane_bytes,
                                                               int8_t pad) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t per_plane = (int64_t)g.N * Y * g.OW, total = 2 * per_plane;
   const int run = g.KW * g.C;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -187,6 +191,8 @@ __global__ void __launch_bounds__(256) row_windows_i8_kernel(const int8_t *__res
 // kw * C + c of (e, a); everything else zero.
 __global__ void __launch_bounds__(256) window_filter_i8_kernel(const int8_t *__restrict__ f, int8_t *__restrict__ out, int OC,
                                                                int KH, int KW, int C) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t total = (int64_t)OC * 256;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int oc = (int)(i >> 8), k = (int)(i & 255);
@@ -200,6 +206,8 @@ __global__ void __launch_bounds__(256) window_filter_i8_kernel(const int8_t *__r
 // `pad_word` (the input offset, which is how the reference's skipped taps read).  16 bytes per thread.
 __global__ void __launch_bounds__(256) pad_nhwc_i8_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ xp,
                                                            const __grid_constant__ ConvGeom g, int Hp, int Wp, int pad_word) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int cc = g.C >> 4;
   const int64_t total = (int64_t)g.N * Hp * Wp * cc;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -221,6 +229,8 @@ __global__ void __launch_bounds__(256) pad_nhwc_i8_kernel(const int8_t *__restri
 // is then pixel (n, oh + kh / 2, ow + kw / 2) of plane (kh & 1, kw & 1): a row offset again.
 __global__ void __launch_bounds__(256) pad_parity_nhwc_i8_kernel(const int8_t *__restrict__ x, int8_t *__restrict__ xp,
                                                                   const __grid_constant__ ConvGeom g, int Hq, int Wq, int pad_word) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int cc = g.C >> 4;
   const int64_t total = 4ll * g.N * Hq * Wq * cc;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -244,6 +254,8 @@ __global__ void __launch_bounds__(256) pad_parity_nhwc_i8_kernel(const int8_t *_
 // two neighbouring 64-channel pixels.
 __global__ void __launch_bounds__(256) pair_taps_c64_kernel(const int8_t *__restrict__ f, int8_t *__restrict__ out, int OC,
                                                              int KH, int KW) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int pairs = (KW + 1) >> 1;
   const int64_t total = (int64_t)OC * KH * pairs * 128;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -381,8 +393,8 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
       int8_t *xp = reinterpret_cast<int8_t *>(ws);
       const uint32_t b = (uint8_t)p.a_offset;
       const int64_t chunks = rows * (g.C >> 4), blocks = (chunks + 255) / 256;
-      pad_nhwc_i8_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(
-          in, xp, g, Hp, Wp, (int)(b | (b << 8) | (b << 16) | (b << 24)));
+      GLOWB200_CUDA_OK(launch_pdl(pad_nhwc_i8_kernel, (unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s, in, xp, g, Hp, Wp,
+                                  (int)(b | (b << 8) | (b << 16) | (b << 24))));
       GLOWB200_CUDA_OK(cudaGetLastError());
       GLOWB200_CUDA_OK(cudaMemsetAsync(xp + rows * g.C, 0, 256, s));  // the window of the last rows reads past them
       const int8_t *bmat = filter;
@@ -390,7 +402,8 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
       if (g.C == 64) {
         int8_t *fb = reinterpret_cast<int8_t *>(ws + xp_bytes);
         const int64_t fblocks = ((int64_t)g.OC * entries * 128 + 255) / 256;
-        pair_taps_c64_kernel<<<(unsigned)(fblocks < 148 * 16 ? fblocks : 148 * 16), 256, 0, s>>>(filter, fb, g.OC, g.KH, g.KW);
+        GLOWB200_CUDA_OK(launch_pdl(pair_taps_c64_kernel, (unsigned)(fblocks < 148 * 16 ? fblocks : 148 * 16), 256, 0, s, filter, fb, g.OC,
+                                    g.KH, g.KW));
         GLOWB200_CUDA_OK(cudaGetLastError());
         bmat = fb;
         p.K = entries * 128;
@@ -427,8 +440,8 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
       int8_t *xp = reinterpret_cast<int8_t *>(ws);
       const uint32_t b = (uint8_t)p.a_offset;
       const int64_t chunks = 4 * rows * (g.C >> 4), blocks = (chunks + 255) / 256;
-      pad_parity_nhwc_i8_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(
-          in, xp, g, Hq, Wq, (int)(b | (b << 8) | (b << 16) | (b << 24)));
+      GLOWB200_CUDA_OK(launch_pdl(pad_parity_nhwc_i8_kernel, (unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s, in, xp, g, Hq,
+                                  Wq, (int)(b | (b << 8) | (b << 16) | (b << 24))));
       GLOWB200_CUDA_OK(cudaGetLastError());
       p.K = g.KH * g.KW * g.C;
       p.k_corr = pl.K;
@@ -465,12 +478,13 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
       int8_t *planes = reinterpret_cast<int8_t *>(ws);
       int8_t *fb = reinterpret_cast<int8_t *>(ws + wp_bytes);
       const int64_t blocks = (2 * rows + 255) / 256;
-      row_windows_i8_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(in, planes, g, Y, plane_bytes,
-                                                                                              (int8_t)p.a_offset);
+      GLOWB200_CUDA_OK(launch_pdl(row_windows_i8_kernel, (unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s, in, planes, g, Y,
+                                  plane_bytes, (int8_t)p.a_offset));
       GLOWB200_CUDA_OK(cudaGetLastError());
       // the four windows of the last rows reach past the second plane
       GLOWB200_CUDA_OK(cudaMemsetAsync(planes + 2 * plane_bytes, 0, wp_bytes - 2 * plane_bytes, s));
-      window_filter_i8_kernel<<<(unsigned)((g.OC * 256 + 255) / 256), 256, 0, s>>>(filter, fb, g.OC, g.KH, g.KW, g.C);
+      GLOWB200_CUDA_OK(launch_pdl(window_filter_i8_kernel, (unsigned)((g.OC * 256 + 255) / 256), 256, 0, s, filter, fb, g.OC, g.KH, g.KW,
+                                  g.C));
       GLOWB200_CUDA_OK(cudaGetLastError());
       int32_t *bs = reinterpret_cast<int32_t *>(ws + pl.a_bytes + pl.f_bytes);  // zeros do not change the sums, but one path
       if (int rc = glowb200_i8_row_sums(fb, g.OC, 256, bs, reinterpret_cast<glowb200_stream_t>(s))) return rc;
@@ -492,8 +506,8 @@ int run_conv(GemmParams p, const int8_t *in, const int8_t *filter, const ConvGeo
       const int64_t chunks = pl.M * (pl.Kpad >> 4);
       const int64_t blocks = (chunks + 255) / 256;
       const uint32_t b = (uint8_t)pad;
-      im2col_i8_vec_kernel<<<(unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s>>>(
-          in, abuf, g, pl.Kpad, (int)(b | (b << 8) | (b << 16) | (b << 24)));
+      GLOWB200_CUDA_OK(launch_pdl(im2col_i8_vec_kernel, (unsigned)(blocks < 148 * 64 ? blocks : 148 * 64), 256, 0, s, in, abuf, g, pl.Kpad,
+                                  (int)(b | (b << 8) | (b << 16) | (b << 24))));
     } else if ((int64_t)g.KH * rows_pitch(g) <= 48 * 1024 && (int64_t)g.N * g.OH < (1ll << 31) && (pl.Kpad >> 4) <= 256 &&
                (reinterpret_cast<uintptr_t>(abuf) & 15) == 0) {
       // the KH input rows of an output image row, with their padding, fit the default shared-memory window

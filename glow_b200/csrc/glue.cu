@@ -109,6 +109,8 @@ __device__ __forceinline__ uint32_t map_word(uint32_t a, uint32_t b, const F &f)
 template <typename F>
 __global__ void __launch_bounds__(kThreads) map_i8_kernel(int8_t *__restrict__ dst, const int8_t *__restrict__ lhs,
                                                           const int8_t *__restrict__ rhs, int64_t n, int vec, const F f) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t nv = vec ? (n >> 4) : 0;
   for (int64_t i = tid; i < nv; i += stride) {
@@ -127,7 +129,7 @@ __global__ void __launch_bounds__(kThreads) map_i8_kernel(int8_t *__restrict__ d
 template <typename F>
 cudaError_t launch_map(int8_t *dst, const int8_t *lhs, const int8_t *rhs, int64_t n, const F &f, cudaStream_t s) {
   const int vec = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15u) == 0;
-  map_i8_kernel<F><<<grid_for(vec ? (n + 15) / 16 : n), kThreads, 0, s>>>(dst, lhs, rhs, n, vec, f);
+  if (cudaError_t e = launch_pdl(map_i8_kernel<F>, grid_for(vec ? (n + 15) / 16 : n), kThreads, 0, s, dst, lhs, rhs, n, vec, f)) return e;
   return cudaGetLastError();
 }
 
@@ -219,6 +221,8 @@ __global__ void __launch_bounds__(kThreads) max_pool_i8_kernel(const int8_t *__r
 // byte-wise signed maxima per instruction.
 __global__ void __launch_bounds__(kThreads) max_pool_i8_vec_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
                                                                    const __grid_constant__ PoolGeom g, int8_t def) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int cc = g.C >> 4;
   const int64_t total = (int64_t)g.N * g.OH * g.OW * cc;
   const uint32_t lowest = 0x80808080u;  // four times -128
@@ -253,6 +257,8 @@ __global__ void __launch_bounds__(kThreads) max_pool_i8_vec_kernel(const int8_t 
 __global__ void __launch_bounds__(kThreads) avg_pool_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
                                                                const __grid_constant__ PoolGeom g, int count_include_pads,
                                                                int32_t out_off, int32_t in_off, Triple t) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t total = (int64_t)g.N * g.OH * g.OW * g.C;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int c = (int)(i % g.C);
@@ -315,6 +321,8 @@ struct QuantizeF {
 template <typename T, typename TO = T, typename F = KeepF>
 __global__ void __launch_bounds__(kThreads) transpose4_kernel(const T *__restrict__ src, TO *__restrict__ dst, int d0, int d1,
                                                               int d2, int d3, int s0, int s1, int s2, int s3, F f = F()) {
+  pdl_wait();
+  pdl_launch_dependents();
   // d*: destination dims; s*: source element stride of each destination axis
   const int64_t total = (int64_t)d0 * d1 * d2 * d3;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -335,6 +343,8 @@ template <typename T, typename TO = T, typename F = KeepF>
 __global__ void __launch_bounds__(kThreads) transpose4_short_inner_kernel(const T *__restrict__ src, TO *__restrict__ dst, int d0,
                                                                           int d1, int d2, int d3, int s0, int s1, int s3,
                                                                           F f = F()) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int64_t pixels = (int64_t)d0 * d1 * d2;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pixels; i += (int64_t)gridDim.x * blockDim.x) {
     const int i2 = (int)(i % d2);
@@ -513,7 +523,7 @@ extern "C" int glowb200_max_pool_i8(const int8_t *in, int8_t *out, const int64_t
   if (total == 0) return GLOWB200_OK;
   GLOWB200_REQUIRE(in && out, "NULL tensor pointer");
   if ((g.C & 15) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
-    max_pool_i8_vec_kernel<<<grid_for(total >> 4), kThreads, 0, GLOWB200_STREAM>>>(in, out, g, (int8_t)out_offset);
+    GLOWB200_CUDA_OK(launch_pdl(max_pool_i8_vec_kernel, grid_for(total >> 4), kThreads, 0, GLOWB200_STREAM, in, out, g, (int8_t)out_offset));
   else
     max_pool_i8_kernel<<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(in, out, g, (int8_t)out_offset);
   GLOWB200_CUDA_OK(cudaGetLastError());
@@ -529,8 +539,8 @@ extern "C" int glowb200_avg_pool_i8(const int8_t *in, int8_t *out, const int64_t
   const int64_t total = (int64_t)g.N * g.OH * g.OW * g.C;
   if (total == 0) return GLOWB200_OK;
   GLOWB200_REQUIRE(in && out, "NULL tensor pointer");
-  avg_pool_i8_kernel<<<grid_for(total), kThreads, 0, GLOWB200_STREAM>>>(in, out, g, count_include_pads ? 1 : 0, out_offset,
-                                                                        in_offset, Triple{out_pre, out_post, out_scale});
+  GLOWB200_CUDA_OK(launch_pdl(avg_pool_i8_kernel, grid_for(total), kThreads, 0, GLOWB200_STREAM, in, out, g, count_include_pads ? 1 : 0,
+                              out_offset, in_offset, Triple{out_pre, out_post, out_scale}));
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }
@@ -565,11 +575,11 @@ int plan_transpose(TransposePlan &t, const int64_t *src_dims, const int32_t *shu
 template <typename T, typename TO, typename F>
 int run_transpose(const TransposePlan &t, const T *src, TO *dest, F f, cudaStream_t s) {
   if (t.d[3] <= 16 && t.st[2] == 1 && t.st[3] != 1)
-    transpose4_short_inner_kernel<T, TO, F><<<grid_for(t.total / t.d[3]), kThreads, 0, s>>>(src, dest, t.d[0], t.d[1], t.d[2],
-                                                                                            t.d[3], t.st[0], t.st[1], t.st[3], f);
+    GLOWB200_CUDA_OK(launch_pdl(transpose4_short_inner_kernel<T, TO, F>, grid_for(t.total / t.d[3]), kThreads, 0, s, src, dest, t.d[0],
+                                t.d[1], t.d[2], t.d[3], t.st[0], t.st[1], t.st[3], f));
   else
-    transpose4_kernel<T, TO, F><<<grid_for(t.total), kThreads, 0, s>>>(src, dest, t.d[0], t.d[1], t.d[2], t.d[3], t.st[0],
-                                                                        t.st[1], t.st[2], t.st[3], f);
+    GLOWB200_CUDA_OK(launch_pdl(transpose4_kernel<T, TO, F>, grid_for(t.total), kThreads, 0, s, src, dest, t.d[0], t.d[1], t.d[2], t.d[3],
+                                t.st[0], t.st[1], t.st[2], t.st[3], f));
   GLOWB200_CUDA_OK(cudaGetLastError());
   return GLOWB200_OK;
 }

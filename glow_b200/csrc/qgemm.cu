@@ -420,6 +420,10 @@ i8_gemm_requant_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   __syncthreads();
   if constexpr (PAIR) cluster_sync();  // the partner's barriers exist before anything signals them
   tc_fence_after();
+  // Everything above touched only this CTA's shared and tensor memory, so it may have run beside the
+  // tail of the kernel before this one in the stream; the operands and the result are global memory.
+  pdl_wait();
+  pdl_launch_dependents();
   const uint32_t tmem_base = *tmem_slot;
   GEMM_TRACE(1, threadIdx.x == 0);
 
@@ -868,8 +872,17 @@ int launch_tile_mode(const CUtensorMap &ma, const CUtensorMap &mb, const GemmPar
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
   const int tiles = ((p.N + BLOCK_N - 1) / BLOCK_N) * ((p.M + kBlockM - 1) / kBlockM);
   const int sms = sm_count();
-  i8_gemm_requant_kernel<BLOCK_N, STAGES, MODE><<<tiles < sms ? tiles : sms, kGemmThreads, S::kTotal, s>>>(ma, mb, p);
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles < sms ? tiles : sms));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see pdl_wait() in the kernel
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  GLOWB200_CUDA_OK(cudaLaunchKernelEx(&cfg, i8_gemm_requant_kernel<BLOCK_N, STAGES, MODE>, ma, mb, p));
   return GLOWB200_OK;
 }
 

@@ -402,7 +402,9 @@ class DLRMRank:
         slab = self.step & 1
         main = torch.cuda.current_stream(self.device)
         self.side.wait_stream(main)          # the dense features (and the last step's x0 readers) are ready
-        with torch.cuda.stream(self.side):
+        # (ordinary launches on the side stream: a contraction waiting for its predecessor there would
+        # hold an SM's shared memory that the pooling kernel on the main stream can use)
+        with torch.cuda.stream(self.side), ops.programmatic_launch(False):
             self.bottom_forward(dense_slice)
         pooled = self.pool_and_exchange(bound_pair[slab], slab)
         main.wait_stream(self.side)

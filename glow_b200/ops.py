@@ -709,6 +709,22 @@ def transpose(src, shuffle):
     return out
 
 
+class programmatic_launch:
+    """with programmatic_launch(False): ...  -- ordinary launches inside (e.g. for a stream that runs
+    beside another one); the previous setting comes back on exit."""
+
+    def __init__(self, enabled):
+        self.enabled = enabled
+
+    def __enter__(self):
+        self.before = _lib.lib().glowb200_set_programmatic_launch(1 if self.enabled else 0)
+        return self
+
+    def __exit__(self, *exc):
+        _lib.lib().glowb200_set_programmatic_launch(self.before)
+        return False
+
+
 def quantize_transpose_i8(src, shuffle, scale, offset):
     """transpose(quantize(src)) in one pass: fp32 in, int8 out with dims[i] = src dims[shuffle[i]]."""
     _cuda(src, "src", (torch.float32,))

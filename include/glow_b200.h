@@ -65,6 +65,16 @@ const char *glowb200_last_error(void);
 /* Library version string. */
 const char *glowb200_version(void);
 
+/* Programmatic dependent launch.  The library launches its contraction, convolution-preparation and
+ * NHWC element-wise kernels so that a kernel may set up (barriers, tensor memory) beside the tail of
+ * the kernel before it in the stream; it touches global memory only after that kernel has completed
+ * (griddepcontrol.wait), so results do not change.  A kernel that waits this way holds its shared
+ * memory and thread slots: a caller that runs another stream beside it (Glow's executor running two
+ * partitions on one device) may prefer ordinary launches for that stream.  enabled: 1 on, 0 off,
+ * -1 back to the default (on, unless the environment has GLOWB200_PDL=0).  Process-wide; takes
+ * effect for the launches (or CUDA-graph captures) that follow.  Returns the previous state (0 / 1). */
+int glowb200_set_programmatic_launch(int enabled);
+
 /* ---------------------------------------------------------------------------------------
  * Embedding gather-pool
  * ------------------------------------------------------------------------------------- */

@@ -57,3 +57,9 @@ def test_host_side_argument_errors_need_no_gpu(built):
     assert rc == 1 and b"permutation" in l.glowb200_last_error()
     assert l.glowb200_quantize_transpose_i8(None, None, dims, good, 4, C.c_float(0.1), 0, None) == 0
     assert l.glowb200_transpose(None, None, dims, good, 5, 1, None) == 1
+    # the programmatic-launch switch is host state: set, read back, restore
+    before = l.glowb200_set_programmatic_launch(0)
+    assert l.glowb200_set_programmatic_launch(1) == 0
+    assert l.glowb200_set_programmatic_launch(-1) == 1
+    assert l.glowb200_set_programmatic_launch(before) in (0, 1)
+    l.glowb200_set_programmatic_launch(-1)
