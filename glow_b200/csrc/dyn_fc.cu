@@ -32,6 +32,7 @@ constexpr int kQuantThreads = 256;
 __global__ void __launch_bounds__(kQuantThreads) dyn_quantize_rows_kernel(const __half *__restrict__ in, int M, int K,
                                                                           int8_t *__restrict__ q, float *__restrict__ row_scales,
                                                                           int32_t *__restrict__ row_sums, int32_t *status) {
+  pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   __shared__ float s_mn[kQuantThreads / 32], s_mx[kQuantThreads / 32];
   __shared__ int32_t s_sum[kQuantThreads / 32];
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -99,6 +100,7 @@ __device__ __forceinline__ float widen_f16(uint32_t h) {
 __global__ void __launch_bounds__(256) dyn_quantize_rows_warp_kernel(const __half *__restrict__ in, int M, int K,
                                                                      int8_t *__restrict__ q, float *__restrict__ row_scales,
                                                                      int32_t *__restrict__ row_sums, int32_t *status) {
+  pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= M) return;
   const __half *x = in + (size_t)row * K;

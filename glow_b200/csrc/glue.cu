@@ -164,6 +164,7 @@ __device__ __forceinline__ int32_t quantize_one(float x, float scale, int32_t of
 // vec: both tensors 16-byte aligned -- four floats in, four bytes out per step
 __global__ void __launch_bounds__(kThreads) quantize_i8_kernel(int8_t *__restrict__ dst, const float *__restrict__ src,
                                                                int64_t n, float scale, int32_t offset, int vec) {
+  pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t nv = vec ? (n >> 2) : 0;
   for (int64_t i = tid; i < nv; i += stride) {
@@ -178,6 +179,7 @@ __global__ void __launch_bounds__(kThreads) quantize_i8_kernel(int8_t *__restric
 // libjit_element_dequantize_kernel_i8 (libjit.cpp:3014-3018)
 __global__ void __launch_bounds__(kThreads) dequantize_i8_kernel(float *__restrict__ dst, const int8_t *__restrict__ src,
                                                                  int64_t n, float scale, int32_t offset, int vec) {
+  pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t nv = vec ? (n >> 2) : 0;
   for (int64_t i = tid; i < nv; i += stride) {

@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(256) pairwise_dot_kernel(const float *__restri
                                                            const float *__restrict__ pooled, int64_t ld_pooled, int tables,
                                                            int D, float *__restrict__ out_f, int8_t *__restrict__ out_q,
                                                            int64_t ld_out, float q_scale, int32_t q_offset) {
+  pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   extern __shared__ float v[];  // [n][D + 1]
   const int n = tables + 1, pitch = D + 1;
   const int64_t b = blockIdx.x;
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(256) pairwise_dot_tiled_kernel(const float *__
                                                                  int tables, int D, float *__restrict__ out_f,
                                                                  int8_t *__restrict__ out_q, int64_t ld_out, float q_scale,
                                                                  int32_t q_offset, int vec_in) {
+  pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   extern __shared__ __align__(16) float v[];  // [4 * ceil(n / 4)][D + 4]; rows beyond n are zero
   const int n = tables + 1, pitch = D + 4, nb = (n + 3) >> 2;
   const int64_t b = blockIdx.x;
