@@ -70,9 +70,9 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 bool pdl_enabled();
 // Launches `kernel` so that it may start beside the tail of the kernel before it (see pdl_wait()).
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t s, Args... args) {
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, unsigned block, size_t smem, cudaStream_t s, Args... args) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = grid;
   cfg.blockDim = dim3(block);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;

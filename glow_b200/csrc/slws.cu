@@ -158,6 +158,8 @@ __device__ __forceinline__ int64_t block_exclusive_scan(int64_t v, int64_t *warp
 }
 
 __global__ void __launch_bounds__(kSegThreads) slws_segments_from_lengths_kernel(const __grid_constant__ SlwsLaunch p) {
+  pdl_wait();               // the gather before this one may still read the boundaries this kernel rewrites
+  pdl_launch_dependents();  // this launch's gather may take its place on the SMs (it waits before reading them)
   __shared__ int64_t warp_tot[33];
   const glowb200_slws_job job = p.jobs ? p.jobs[blockIdx.x] : p.single;
   int64_t *out = p.seg_begin + (int64_t)blockIdx.x * p.seg_stride;
@@ -790,6 +792,8 @@ slws_gather_small_kernel(const __grid_constant__ SlwsLaunch p) {
 template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false>
 __global__ void __launch_bounds__(kGatherThreads, kGatherBlockScale * (P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS))
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
+  pdl_wait();
+  pdl_launch_dependents();
   const glowb200_slws_job *jp = p.jobs ? (p.jobs + blockIdx.y) : &p.single;
   const bool skewed = GLOWB200_SLWS_FORCE_WARP || p.warp_per_bag != 0 ||
                       p.seg_begin[(int64_t)blockIdx.y * p.seg_stride + bags_of(p, jp) + 1] != 0;
@@ -913,12 +917,10 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
       dim3 sgrid(wblocks > grid.x ? wblocks : grid.x, grid.y);
       if constexpr (!OUT16) {  // shards give fp32 partial sums (checked by the entry point)
         if (L.sharded) {
-          slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, true><<<sgrid, kGatherThreads, 0, s>>>(L, bpw);
-          return cudaGetLastError();
+          return launch_pdl(slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, true>, sgrid, kGatherThreads, 0, s, L, bpw);
         }
       }
-      slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U><<<sgrid, kGatherThreads, 0, s>>>(L, bpw);
-      return cudaGetLastError();
+      return launch_pdl(slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, false>, sgrid, kGatherThreads, 0, s, L, bpw);
     }
   }
 #endif
@@ -1078,8 +1080,7 @@ int run_batched(const glowb200_slws_job *jobs, int64_t num_jobs, int64_t max_seg
   L.select = (P != 0 && !g.acc16) ? 1 : 0;
   L.sharded = sharded ? 1 : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  slws_segments_from_lengths_kernel<<<(unsigned)num_jobs, kSegThreads, 0, s>>>(L);
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(launch_pdl(slws_segments_from_lengths_kernel, dim3((unsigned)num_jobs), kSegThreads, 0, s, L));
   return run_gather(L, g, P, max_segments, num_jobs, s);
 }
 }  // namespace
