@@ -164,6 +164,7 @@ __device__ __forceinline__ int32_t quantize_one(float x, float scale, int32_t of
 // vec: both tensors 16-byte aligned -- four floats in, four bytes out per step
 __global__ void __launch_bounds__(kThreads) quantize_i8_kernel(int8_t *__restrict__ dst, const float *__restrict__ src,
                                                                int64_t n, float scale, int32_t offset, int vec) {
+  pdl_wait();
   pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t nv = vec ? (n >> 2) : 0;
@@ -179,6 +180,7 @@ __global__ void __launch_bounds__(kThreads) quantize_i8_kernel(int8_t *__restric
 // libjit_element_dequantize_kernel_i8 (libjit.cpp:3014-3018)
 __global__ void __launch_bounds__(kThreads) dequantize_i8_kernel(float *__restrict__ dst, const int8_t *__restrict__ src,
                                                                  int64_t n, float scale, int32_t offset, int vec) {
+  pdl_wait();
   pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t nv = vec ? (n >> 2) : 0;
@@ -502,8 +504,7 @@ extern "C" int glowb200_element_quantize_i8(int8_t *dest, const float *src, int6
                                             glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
   const int vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dest) & 3u) == 0;
-  quantize_i8_kernel<<<grid_for(vec ? (n + 3) / 4 : n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, scale, offset, vec);
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(launch_pdl(quantize_i8_kernel, grid_for(vec ? (n + 3) / 4 : n), kThreads, 0, GLOWB200_STREAM, dest, src, n, scale, offset, vec));
   return GLOWB200_OK;
 }
 
@@ -511,8 +512,7 @@ extern "C" int glowb200_element_dequantize_i8(float *dest, const int8_t *src, in
                                               glowb200_stream_t stream) {
   GLOWB200_ELEMENTWISE_PROLOGUE(n, dest && src)
   const int vec = (reinterpret_cast<uintptr_t>(dest) & 15u) == 0 && (reinterpret_cast<uintptr_t>(src) & 3u) == 0;
-  dequantize_i8_kernel<<<grid_for(vec ? (n + 3) / 4 : n), kThreads, 0, GLOWB200_STREAM>>>(dest, src, n, scale, offset, vec);
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(launch_pdl(dequantize_i8_kernel, grid_for(vec ? (n + 3) / 4 : n), kThreads, 0, GLOWB200_STREAM, dest, src, n, scale, offset, vec));
   return GLOWB200_OK;
 }
 

@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(256) pairwise_dot_kernel(const float *__restri
                                                            const float *__restrict__ pooled, int64_t ld_pooled, int tables,
                                                            int D, float *__restrict__ out_f, int8_t *__restrict__ out_q,
                                                            int64_t ld_out, float q_scale, int32_t q_offset) {
+  pdl_wait();               // (launched as a programmatic dependent of the pooling kernel)
   pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   extern __shared__ float v[];  // [n][D + 1]
   const int n = tables + 1, pitch = D + 1;
@@ -67,6 +68,7 @@ __global__ void __launch_bounds__(256) pairwise_dot_tiled_kernel(const float *__
                                                                  int tables, int D, float *__restrict__ out_f,
                                                                  int8_t *__restrict__ out_q, int64_t ld_out, float q_scale,
                                                                  int32_t q_offset, int vec_in) {
+  pdl_wait();               // (launched as a programmatic dependent of the pooling kernel)
   pdl_launch_dependents();  // a contraction that follows may set up now (it waits for this kernel before its loads)
   extern __shared__ __align__(16) float v[];  // [4 * ceil(n / 4)][D + 4]; rows beyond n are zero
   const int n = tables + 1, pitch = D + 4, nb = (n + 3) >> 2;
@@ -171,18 +173,15 @@ extern "C" int glowb200_pairwise_dot_interaction(const float *dense, int64_t ld_
     }
     const int vec_in = (reinterpret_cast<uintptr_t>(dense) % 16 == 0) && (ld_dense % 4 == 0) &&
                        (tables == 0 || (reinterpret_cast<uintptr_t>(pooled) % 16 == 0 && ld_pooled % 4 == 0));
-    pairwise_dot_tiled_kernel<<<(unsigned)batch, 256, tiled_smem, cs>>>(dense, ld_dense, pooled, ld_pooled, (int)tables,
-                                                                       (int)dim, out_f32, out_i8, ld_out, quant_scale,
-                                                                       quant_offset, vec_in);
-    GLOWB200_CUDA_OK(cudaGetLastError());
+    GLOWB200_CUDA_OK(launch_pdl(pairwise_dot_tiled_kernel, (unsigned)batch, 256, tiled_smem, cs, dense, ld_dense, pooled, ld_pooled,
+                                (int)tables, (int)dim, out_f32, out_i8, ld_out, quant_scale, quant_offset, vec_in));
     return GLOWB200_OK;
   }
   const size_t smem = (size_t)n * (dim + 1) * sizeof(float);
   GLOWB200_REQUIRE(smem <= 200 * 1024, "tables x dim too large for one block's shared memory");
   if (smem > 48 * 1024)
     GLOWB200_CUDA_OK(cudaFuncSetAttribute(pairwise_dot_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  pairwise_dot_kernel<<<(unsigned)batch, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      dense, ld_dense, pooled, ld_pooled, (int)tables, (int)dim, out_f32, out_i8, ld_out, quant_scale, quant_offset);
-  GLOWB200_CUDA_OK(cudaGetLastError());
+  GLOWB200_CUDA_OK(launch_pdl(pairwise_dot_kernel, (unsigned)batch, 256, smem, reinterpret_cast<cudaStream_t>(stream), dense, ld_dense,
+                              pooled, ld_pooled, (int)tables, (int)dim, out_f32, out_i8, ld_out, quant_scale, quant_offset));
   return GLOWB200_OK;
 }
