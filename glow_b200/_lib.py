@@ -92,6 +92,7 @@ SIGNATURES = {
     "glowb200_function_add_symbol": (_int, [_vp, C.c_char_p, _int, _sz, _vp]),
     "glowb200_function_add_instruction": (_int, [_vp, _int, _vp, _int, _vp, _int, _vp, _int]),
     "glowb200_function_batched_pooling_launches": (_int, [_vp]),
+    "glowb200_function_fused_quantize_transposes": (_int, [_vp]),
     "glowb200_function_add_instruction_views": (_int, [_vp, _int, _vp, _vp, _int, _vp, _int, _vp, _int]),
     "glowb200_function_compile": (_int, [_vp]),
     "glowb200_function_constant_bytes": (_sz, [_vp]),

@@ -55,6 +55,8 @@ struct Instruction {
   std::vector<int64_t> off;   // byte offset of each operand inside its symbol (a view of a larger tensor)
   int group = -1;             // FRWQ_SLWS: index of the batched launch this instruction is part of
   bool group_leader = false;  // ... and whether it is the one that launches it
+  bool absorbed = false;      // QUANTIZE: done by the TRANSPOSE behind it (nothing to launch)
+  bool quantizes = false;     // TRANSPOSE: reads floats (operand 2) and quantizes them on the way (fa[0], ia[10])
   std::vector<int64_t> ia;    // integer attributes
   std::vector<float> fa;      // float attributes
   std::vector<int> derived;   // ids of constants compile() added (triples, row sums ...)
@@ -71,6 +73,7 @@ struct glowb200_function {
   size_t workspace_bytes = 0;
   // Runs of pooling instructions that become ONE batched launch each: their members, in order.
   std::vector<std::vector<int>> slws_groups;
+  int fused_quantize_transposes = 0;
   std::map<std::string, int> by_name;
 
   int add_symbol(const std::string &n, int kind, size_t bytes, const void *data) {
@@ -586,6 +589,32 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
       i = j;
     }
   }
+  // A Quantize whose result nothing reads but the Transpose right behind it (the NCHW float input
+  // of a network on its way to NHWC int8; Glow's optimizer leaves the pair in this order,
+  // GraphOptimizer.cpp:1076-1086) becomes one kernel: the Transpose reads the floats and quantizes.
+  for (size_t i = 0; i + 1 < f->instrs.size(); i++) {
+    Instruction &q = f->instrs[i], &t = f->instrs[i + 1];
+    if (q.kind != GLOWB200_INSTR_QUANTIZE || t.kind != GLOWB200_INSTR_TRANSPOSE || t.ia[1] != 1) continue;
+    const int mid = q.ops[0];
+    if (mid < 0 || t.ops[1] != mid || t.off[1] != q.off[0] || f->symbols[mid].kind != kActivation) continue;
+    int64_t n = 1;
+    for (int d = 0; d < t.ia[0]; d++) n *= t.ia[2 + d];
+    if (n != q.ia[0]) continue;
+    bool read_elsewhere = false;
+    for (size_t k = 0; k < f->instrs.size(); k++) {
+      if (k == i || k == i + 1) continue;
+      for (int o : f->instrs[k].ops) read_elsewhere = read_elsewhere || o == mid;
+    }
+    if (read_elsewhere) continue;
+    q.absorbed = true;
+    t.quantizes = true;
+    t.ops.push_back(q.ops[1]);
+    t.off.push_back(q.off[1]);
+    t.fa.assign(1, q.fa[0]);
+    t.ia.resize(11, 0);
+    t.ia[10] = q.ia[1];
+    f->fused_quantize_transposes++;
+  }
   // slab offsets: 64-byte alignment like glow::TensorAlignment (include/glow/Support/Memory.h:29)
   for (Symbol &s : f->symbols) {
     s.offset = f->slab_bytes[s.kind];
@@ -597,6 +626,9 @@ extern "C" int glowb200_function_compile(glowb200_function *f) {
 }
 
 extern "C" size_t glowb200_function_constant_bytes(const glowb200_function *f) { return f ? f->slab_bytes[kConstant] : 0; }
+extern "C" int glowb200_function_fused_quantize_transposes(const glowb200_function *f) {
+  return (f && f->compiled) ? f->fused_quantize_transposes : 0;
+}
 extern "C" int glowb200_function_batched_pooling_launches(const glowb200_function *f) {
   return (f && f->compiled) ? (int)f->slws_groups.size() : 0;
 }
@@ -852,6 +884,7 @@ int execute(glowb200_device_manager *dm, LoadedNetwork &n, Context &c) {
         rc = glowb200_element_maxsplat_i8((int8_t *)P(0), (const int8_t *)P(1), a[0], (int32_t)a[1], st);
         break;
       case GLOWB200_INSTR_QUANTIZE:
+        if (in.absorbed) break;  // the Transpose behind it does both
         rc = glowb200_element_quantize_i8((int8_t *)P(0), (const float *)P(1), a[0], in.fa[0], (int32_t)a[1], st);
         break;
       case GLOWB200_INSTR_DEQUANTIZE:
@@ -875,7 +908,8 @@ int execute(glowb200_device_manager *dm, LoadedNetwork &n, Context &c) {
         int64_t dims[4];
         int32_t sh[4];
         for (int i = 0; i < nd; i++) { dims[i] = a[2 + i]; sh[i] = (int32_t)a[6 + i]; }
-        rc = glowb200_transpose(P(1), P(0), dims, sh, nd, (int)a[1], st);
+        if (in.quantizes) rc = glowb200_quantize_transpose_i8((int8_t *)P(0), (const float *)P(2), dims, sh, nd, in.fa[0], (int32_t)a[10], st);
+        else rc = glowb200_transpose(P(1), P(0), dims, sh, nd, (int)a[1], st);
         break;
       }
       case GLOWB200_INSTR_COPY:

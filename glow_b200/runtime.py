@@ -210,6 +210,10 @@ class Function:
         return int(_lib.lib().glowb200_function_batched_pooling_launches(self.h))
 
     @property
+    def fused_quantize_transposes(self):
+        return int(_lib.lib().glowb200_function_fused_quantize_transposes(self.h))
+
+    @property
     def constant_bytes(self):
         return int(_lib.lib().glowb200_function_constant_bytes(self.h))
 

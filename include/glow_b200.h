@@ -706,6 +706,9 @@ int glowb200_function_compile(glowb200_function *f);
 size_t glowb200_function_constant_bytes(const glowb200_function *f);
 /* How many batched pooling launches compile formed (0 before compile). */
 int glowb200_function_batched_pooling_launches(const glowb200_function *f);
+/* How many Quantize + Transpose pairs compile turned into one kernel each: a Quantize into an
+ * activation that only the Transpose right behind it reads (0 before compile).  Same results. */
+int glowb200_function_fused_quantize_transposes(const glowb200_function *f);
 
 /* max_memory_bytes 0 = the device's free memory at init. */
 glowb200_device_manager *glowb200_device_manager_create(int device_id, uint64_t max_memory_bytes);

@@ -170,3 +170,22 @@ def test_views_are_checked_against_their_symbol():
     g.copy((a, 32), b, nbytes=32)
     g.compile()
     assert g.batched_pooling_launches == 0
+
+
+def test_quantize_feeding_only_a_transpose_becomes_one_kernel():
+    """Quantize into an activation that nothing but the Transpose right behind it reads is absorbed by
+    that Transpose at compile; a second reader of the activation keeps the two kernels."""
+    def build(extra_reader):
+        f = runtime.Function("stem" + str(int(extra_reader)))
+        n = 2 * 3 * 4 * 5
+        x = f.placeholder("x", n * 4)
+        q = f.activation("q", n)
+        y = f.placeholder("y", n)
+        f.quantize(q, x, n=n, tqp=(0.05, 3))
+        f.transpose(y, q, dims=(2, 3, 4, 5), shuffle=(0, 2, 3, 1), elem_bytes=1)
+        if extra_reader:
+            z = f.placeholder("z", n)
+            f.copy(z, q, nbytes=n)
+        return f.compile()
+    assert build(False).fused_quantize_transposes == 1
+    assert build(True).fused_quantize_transposes == 0

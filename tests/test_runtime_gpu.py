@@ -115,8 +115,10 @@ def test_partial_tensor_binding(oracle, dm):
     np.testing.assert_allclose(out, oracle.frwq_slws_u8_f32(table, w, idx, lengths), rtol=1e-5, atol=1e-5)
 
 
-def test_quantized_network_bit_exact(oracle, dm):
-    """NCHW fp32 -> Transpose -> Quantize -> conv3x3+Relu -> MaxPool -> [conv1x1, shortcut] -> Add -> Relu
+@pytest.mark.parametrize("quantize_first", [False, True])
+def test_quantized_network_bit_exact(oracle, dm, quantize_first):
+    """NCHW fp32 -> Transpose -> Quantize (or Quantize -> Transpose, the order Glow's optimizer leaves:
+    the runtime then makes one kernel of the pair) -> conv3x3+Relu -> MaxPool -> [conv1x1, shortcut] -> Add -> Relu
     -> AvgPool -> rowwise FC -> Dequantize, every integer parameter derived by the runtime's compile()."""
     rng = np.random.default_rng(12)
     n, cin, hw, c1, c2, classes = 3, 16, 12, 32, 32, 10
@@ -150,8 +152,13 @@ def test_quantized_network_bit_exact(oracle, dm):
         c = conv_c[name]
         return [f.constant(name + "_" + k, c[k]) for k in ("filter", "bias", "filter_scales", "filter_offsets", "bias_scales", "bias_offsets")]
 
-    f.transpose(a_nhwc, x_in, dims=(n, cin, hw, hw), shuffle=(0, 2, 3, 1), elem_bytes=4)
-    f.quantize(a_q, a_nhwc, n=n * hw * hw * cin, tqp=tq["inp"])
+    if quantize_first:
+        a_qn = f.activation("q_nchw", n * hw * hw * cin)
+        f.quantize(a_qn, x_in, n=n * hw * hw * cin, tqp=tq["inp"])
+        f.transpose(a_q, a_qn, dims=(n, cin, hw, hw), shuffle=(0, 2, 3, 1), elem_bytes=1)
+    else:
+        f.transpose(a_nhwc, x_in, dims=(n, cin, hw, hw), shuffle=(0, 2, 3, 1), elem_bytes=4)
+        f.quantize(a_q, a_nhwc, n=n * hw * hw * cin, tqp=tq["inp"])
     s = conv_syms("c1")
     f.channelwise_conv(a_c1, a_q, *s, in_dims=(n, hw, hw, cin), out_dims=(n, oh, oh, c1), kernels=(3, 3), strides=(1, 1),
                        pads=(1, 1, 1, 1), in_tqp=tq["inp"], out_tqp=tq["c1"], act=1)
@@ -170,6 +177,7 @@ def test_quantized_network_bit_exact(oracle, dm):
                  f.constant("fc_bias", fbias), M=n, K=c2, N=classes, in_tqp=tq["pool"], bias_tqp=(fbias_scale, 0), out_tqp=tq["fc"])
     f.dequantize(result, a_fc, n=n * classes, tqp=tq["fc"])
     f.compile()
+    assert f.fused_quantize_transposes == (1 if quantize_first else 0)
     dm.add_network(f)
 
     x = rng.standard_normal((n, cin, hw, hw)).astype(np.float32)
