@@ -921,7 +921,6 @@ int launch_pair_kernel(const CUtensorMap &ma, const CUtensorMap &mb, const GemmP
     if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) n = sm_count() / 2;
     pairs = n < sm_count() / 2 ? n : sm_count() / 2;
     resident_pairs() = pairs;
-    if (getenv("GLOWB200_DEBUG_PAIRS")) fprintf(stderr, "glow_b200: %d CTA pairs resident at once\n", pairs);
   }
   cfg.gridDim = dim3(2u * (unsigned)(tiles < pairs ? tiles : pairs));
   GLOWB200_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, p));
