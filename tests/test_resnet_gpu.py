@@ -85,7 +85,7 @@ def test_every_conv_takes_the_tensor_core_path(net):
     (im2col or direct); their results equal the direct kernel's on a real activation."""
     layers, w, q = net
     rng = np.random.default_rng(3)
-    for name in ("conv1", "s1b0_b", "s2b0_sc", "s4b2_c"):
+    for name in ("conv1", "s1b0_b", "s2b0_b", "s3b0_b", "s2b0_sc", "s4b2_c"):
         c = q["conv"][name]
         spec = c["spec"]
         x = torch.from_numpy(rng.integers(-128, 128, (2, 20, 20, spec["cin"]), dtype=np.int8)).to(DEV)
@@ -98,3 +98,33 @@ def test_every_conv_takes_the_tensor_core_path(net):
         a = ops.channelwise_quantized_conv2d(*args, flags=ops.FC_WEIGHT_OFFSETS_ZERO)
         b = ops.channelwise_quantized_conv2d(*args, flags=ops.FC_FORCE_ANY_SHAPE_KERNEL)
         assert torch.equal(a, b)
+
+
+
+def test_programmatic_launches_do_not_change_results(net):
+    """The library's kernels start beside their predecessors' tails (programmatic dependent launch)
+    and touch global memory only after them: the whole network gives the same bytes with the
+    switch off, on, and replayed from a CUDA graph captured with it on."""
+    layers, w, q = net
+    model = resnet.ResNet50Int8(layers, q, DEV)
+    x = torch.randn((3, 3, 96, 96), generator=torch.Generator().manual_seed(5)).to(DEV)
+    with ops.programmatic_launch(False):
+        model.forward(x)
+        plain = model.logits_q.clone()
+    with ops.programmatic_launch(True):
+        for _ in range(3):
+            model.forward(x)
+            assert torch.equal(model.logits_q, plain)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            model.forward(x)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                model.forward(x)
+                captured = model.logits_q
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(captured, plain)
+    assert int(model.status.item()) == 0
