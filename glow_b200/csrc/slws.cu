@@ -789,8 +789,13 @@ slws_gather_small_kernel(const __grid_constant__ SlwsLaunch p) {
 // One launch, two thread-to-bag mappings: every table is pooled by the mapping its bag-length
 // profile favours (the word the segments kernel leaves behind the table's boundaries).
 // grid.x covers the larger of the two mappings' block counts; surplus blocks leave at once.
-template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false>
-__global__ void __launch_bounds__(kGatherThreads, kGatherBlockScale * (P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS))
+// MINB: blocks of 256 threads' worth per SM the register allocation must allow.  Three (85 registers)
+// is best for narrow rows in uniform bags (four, 64 registers: 360 against 335 us on 72-byte rows);
+// four for uint8 rows of 128 columns and more, whose lane groups are wide and whose tables in the
+// recommendation model are skewed (one rank's share of eight 177 -> 172 us, the whole model +3 %).
+template <int BITS, bool SO16, bool OUT16, typename IdxT, int P, int U, bool SHARD = false,
+          int MINB = (P == 4 ? GLOWB200_SLWS_MIN_BLOCKS_P4 : GLOWB200_SLWS_MIN_BLOCKS)>
+__global__ void __launch_bounds__(kGatherThreads, kGatherBlockScale * MINB)
 slws_gather_select_kernel(const __grid_constant__ SlwsLaunch p, int bags_per_warp) {
   pdl_wait();
   pdl_launch_dependents();
@@ -919,6 +924,10 @@ cudaError_t launch_gather_pu(const SlwsLaunch &L, dim3 grid, cudaStream_t s) {
         if (L.sharded) {
           return launch_pdl(slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, true>, sgrid, kGatherThreads, 0, s, L, bpw);
         }
+      }
+      if constexpr (P == 2 && BITS == 8) {
+        if (L.lpr_log2 >= 3)
+          return launch_pdl(slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, false, 4>, sgrid, kGatherThreads, 0, s, L, bpw);
       }
       return launch_pdl(slws_gather_select_kernel<BITS, SO16, OUT16, IdxT, P, U, false>, sgrid, kGatherThreads, 0, s, L, bpw);
     }
